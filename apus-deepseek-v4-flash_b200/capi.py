@@ -1,0 +1,152 @@
+"""ctypes view of include/apus_b200.h: structures and function signatures.
+
+The structures are layout-identical to the reference's (c/st.h:88-89,
+c/moe.h:37-71, c/fp4.h:184-188), so the same Python objects can be handed to
+this library and, in the tests, to the reference build.
+"""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+HEADER = ROOT.parent / "include" / "apus_b200.h"
+LIB_PATH = ROOT / "libapus_b200.so"
+
+u8p = C.POINTER(C.c_uint8)
+f32p = C.POINTER(C.c_float)
+i32p = C.POINTER(C.c_int32)
+i64p = C.POINTER(C.c_int64)
+u16p = C.POINTER(C.c_uint16)
+
+
+class QW(C.Structure):
+    """ApusFp8W / ApusFp4W (c/st.h:88-89): codes|packed, scales, O, K."""
+    _fields_ = [("codes", C.c_void_p), ("scales", C.c_void_p),
+                ("O", C.c_int64), ("K", C.c_int64)]
+
+
+RESOLVE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int,
+                         C.POINTER(QW), C.POINTER(QW), C.POINTER(QW))
+HINT_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int, C.c_int)
+LAYER_END_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int)
+
+
+class MoeW(C.Structure):
+    """ApusMoeW (c/moe.h:37-63)."""
+    _fields_ = [("E", C.c_int), ("topk", C.c_int), ("inter", C.c_int),
+                ("dim", C.c_int), ("hash", C.c_int),
+                ("route_scale", C.c_float), ("limit", C.c_float),
+                ("gate_w", C.c_void_p), ("gate_bias", C.c_void_p),
+                ("tid2eid", C.c_void_p),
+                ("w1", C.POINTER(QW)), ("w2", C.POINTER(QW)), ("w3", C.POINTER(QW)),
+                ("sw1", QW), ("sw2", QW), ("sw3", QW),
+                ("hook_ctx", C.c_void_p),
+                ("hook_resolve", C.c_void_p), ("hook_hint", C.c_void_p),
+                ("hook_layer_end", C.c_void_p),
+                ("hook_hint_ctx", C.c_void_p), ("hook_layer_end_ctx", C.c_void_p),
+                ("layer_id", C.c_int)]
+
+
+class MoeInterm(C.Structure):
+    """ApusMoeInterm (c/moe.h:67-71)."""
+    _fields_ = [("router_scores", C.c_void_p), ("router_scores_biased", C.c_void_p),
+                ("router_w", C.c_void_p), ("router_idx", C.c_void_p),
+                ("moe_routed", C.c_void_p), ("moe_shared", C.c_void_p)]
+
+
+class Fp4GemmEnt(C.Structure):
+    """ApusFp4GemmEnt (c/fp4.h:184-188)."""
+    _fields_ = [("w", C.c_void_p), ("ws", C.c_void_p), ("out", C.c_void_p),
+                ("m0", C.c_size_t), ("M", C.c_size_t)]
+
+
+class Hooks(C.Structure):
+    """ApusCudaHooks == ApusBackendHooks (c/backend_metal.h:73-80)."""
+    _fields_ = [("fp8_linear", C.c_void_p), ("f32_linear", C.c_void_p),
+                ("head_gemv", C.c_void_p)]
+
+
+def ptr(a):
+    """Address of a numpy array's (or torch tensor's) first element."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    if hasattr(a, "data_ptr"):
+        return a.data_ptr()
+    return a
+
+
+def qw(codes, scales, O, K):
+    return QW(ptr(codes), ptr(scales), int(O), int(K))
+
+
+def declared_symbols():
+    """Every function name include/apus_b200.h declares."""
+    text = HEADER.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(apus_cuda_\w+)\s*\(", text)))
+
+
+def load(path=LIB_PATH):
+    """dlopen the backend and attach argument/return types."""
+    if not Path(path).exists():
+        raise RuntimeError(
+            f"{path} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()'); "
+            "there is no CPU fallback")
+    lib = C.CDLL(str(path))
+    vp, ci, cf, sz, i64 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_int64
+    sigs = {
+        "apus_cuda_enable": (ci, [C.c_char_p, sz]),
+        "apus_cuda_disable": (None, []),
+        "apus_cuda_is_enabled": (ci, []),
+        "apus_cuda_bytes_uploaded": (C.c_uint64, []),
+        "apus_cuda_dispatches": (C.c_uint64, []),
+        "apus_cuda_fill_hooks": (ci, [C.POINTER(Hooks), sz, sz]),
+        "apus_cuda_last_error": (C.c_char_p, []),
+        "apus_cuda_forget": (None, [vp]),
+        "apus_cuda_fp8_linear": (ci, [C.POINTER(QW), vp, vp, ci, ci, ci]),
+        "apus_cuda_fp4_linear": (ci, [C.POINTER(QW), vp, vp, ci, ci, ci]),
+        "apus_cuda_f32_linear": (ci, [vp, vp, vp, ci, ci, ci, ci]),
+        "apus_cuda_head_gemv_bf16": (ci, [vp, vp, vp, i64, i64]),
+        "apus_cuda_fp8_gemm": (ci, [vp, vp, vp, vp, vp, ci, ci, ci]),
+        "apus_cuda_fp4_gemm": (ci, [vp, vp, vp, vp, vp, ci, ci, ci]),
+        "apus_cuda_fp4_gemm_grouped": (ci, [C.POINTER(Fp4GemmEnt), sz, vp, vp, sz, sz, sz]),
+        "apus_cuda_fp8_act_quant": (ci, [vp, ci, ci, vp, vp]),
+        "apus_cuda_rmsnorm": (ci, [vp, vp, cf, vp, i64, i64]),
+        "apus_cuda_expert": (ci, [vp, vp, vp, ci, cf, vp, ci, ci, ci, vp]),
+        "apus_cuda_topk_stable": (ci, [vp, ci, ci, vp, ci]),
+        "apus_cuda_router_score": (ci, [C.POINTER(MoeW), vp, ci, vp, vp]),
+        "apus_cuda_moe_forward": (ci, [C.POINTER(MoeW), vp, vp, ci, vp, C.POINTER(MoeInterm)]),
+        "apus_cuda_sparse_attn": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, i64, vp]),
+        "apus_cuda_mhc_prepost": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, vp, vp, ci]),
+        "apus_cuda_hc_pre": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, cf, vp, vp, vp, vp, ci]),
+        "apus_cuda_hc_post": (ci, [vp, vp, vp, vp, vp, sz, sz, ci]),
+        "apus_cuda_hc_head": (ci, [vp, sz, sz, vp, cf, vp, cf, cf, vp, ci]),
+        "apus_cuda_moe_create": (vp, [C.POINTER(MoeW), ci, ci]),
+        "apus_cuda_moe_destroy": (None, [vp]),
+        "apus_cuda_moe_bytes": (C.c_uint64, [vp]),
+        "apus_cuda_moe_set_hash_table": (ci, [vp, vp, i64]),
+        "apus_cuda_moe_route_dev": (ci, [vp, vp, vp, ci, vp, vp, vp, vp, vp]),
+        "apus_cuda_moe_experts_dev": (ci, [vp, vp, ci, vp, vp, ci, vp, vp]),
+        "apus_cuda_moe_combine_dev": (ci, [vp, vp, vp, vp, ci, vp, vp, vp]),
+        "apus_cuda_moe_shared_dev": (ci, [vp, vp, ci, vp, vp]),
+        "apus_cuda_moe_forward_dev": (ci, [vp, vp, vp, ci, vp, vp]),
+        "apus_cuda_moe_last_routing": (ci, [vp, ci, vp, vp, vp]),
+        "apus_cuda_fp4_upload": (vp, [C.POINTER(QW)]),
+        "apus_cuda_fp8_upload": (vp, [C.POINTER(QW)]),
+        "apus_cuda_fp4_free": (None, [vp]),
+        "apus_cuda_fp8_free": (None, [vp]),
+        "apus_cuda_fp4_linear_dev": (ci, [vp, vp, vp, ci, vp]),
+        "apus_cuda_fp8_linear_dev": (ci, [vp, vp, vp, ci, vp]),
+        "apus_cuda_expert_fp4_dev": (ci, [vp, vp, vp, cf, vp, ci, vp, vp]),
+        "apus_cuda_topk_stable_dev": (ci, [vp, ci, ci, vp, ci, vp]),
+        "apus_cuda_sparse_attn_dev": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, i64, vp, vp]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib

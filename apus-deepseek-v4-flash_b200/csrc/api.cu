@@ -1,0 +1,685 @@
+// C ABI, part 1: lifecycle, weight cache, kernel-level host-pointer entry points
+// and the single-matrix device-resident entry points (include/apus_b200.h).
+#include <stdarg.h>
+#include <stdlib.h>
+
+#include "runtime.cuh"
+
+namespace apus {
+
+// ---- errors / counters -----------------------------------------------------------
+static thread_local char t_err[512] = "";
+unsigned long long g_dispatches = 0;
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof t_err, fmt, ap);
+    va_end(ap);
+}
+
+// ---- device buffers ------------------------------------------------------------------
+int DevBuf::get(size_t bytes, void **out) {
+    if (bytes > cap) {
+        if (p) { cudaDeviceSynchronize(); cudaFree(p); p = nullptr; cap = 0; }
+        size_t want = bytes + (bytes >> 2) + 256;
+        APUS_CUDA_OK(cudaMalloc(&p, want));
+        cap = want;
+    }
+    if (out) *out = p;
+    return 0;
+}
+void DevBuf::release() {
+    if (p) cudaFree(p);
+    p = nullptr; cap = 0;
+}
+
+size_t DevQW::bytes() const {
+    if (fmt == 4) return (size_t)O * K / 2 + (size_t)O * K / 32;
+    return (size_t)O * K + (size_t)((O + 127) / 128) * (K / 128);
+}
+void DevQW::release() {
+    for (auto &kv : tables) cudaFree(kv.second);
+    tables.clear();
+    if (owned) { if (codes) cudaFree(codes); if (scales) cudaFree(scales); }
+    codes = scales = nullptr;
+}
+
+// Work-item table for M rows against this matrix (chunks of 32 rows), cached on
+// the handle so that steady-state calls do no host->device copies.
+int DevQW::table_for(int M, bool pair, const DevQW *other, GemmGroup **out, int *n_groups) {
+    int n = ceil_div(M, 32);
+    int key = M * 2 + (pair ? 1 : 0);
+    auto it = tables.find(key);
+    if (it == tables.end()) {
+        std::vector<GemmGroup> h(n);
+        for (int i = 0; i < n; i++) {
+            h[i].wa = codes; h[i].sa = scales;
+            h[i].wb = pair ? other->codes : nullptr;
+            h[i].sb = pair ? other->scales : nullptr;
+            h[i].row0 = i * 32;
+            h[i].nrows = M - i * 32 < 32 ? M - i * 32 : 32;
+        }
+        GemmGroup *d = nullptr;
+        APUS_CUDA_OK(cudaMalloc(&d, n * sizeof(GemmGroup)));
+        APUS_CUDA_OK(cudaMemcpy(d, h.data(), n * sizeof(GemmGroup), cudaMemcpyHostToDevice));
+        it = tables.emplace(key, d).first;
+    }
+    *out = it->second;
+    *n_groups = n;
+    return 0;
+}
+
+// ---- context ----------------------------------------------------------------------------
+Ctx &ctx() {
+    static Ctx c;
+    return c;
+}
+
+int ensure_enabled() {
+    Ctx &c = ctx();
+    if (c.enabled) return 0;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        set_error("no CUDA device available (%s); this backend has no CPU fallback",
+                  e == cudaSuccess ? "device count 0" : cudaGetErrorString(e));
+        return 1;
+    }
+    APUS_CUDA_OK(cudaGetDevice(&c.device));
+    cudaDeviceProp prop;
+    APUS_CUDA_OK(cudaGetDeviceProperties(&prop, c.device));
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; this library is built for sm_100a only", c.device,
+                  prop.major, prop.minor);
+        return 1;
+    }
+    APUS_CUDA_OK(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    c.enabled = true;
+    return 0;
+}
+
+// ---- uploads ----------------------------------------------------------------------------------
+int upload_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K,
+              uint8_t *dst_codes, uint8_t *dst_scales, int *zero_scale) {
+    Ctx &c = ctx();
+    size_t cb = fmt == 4 ? (size_t)O * K / 2 : (size_t)O * K;
+    size_t sb = fmt == 4 ? (size_t)O * K / 32 : (size_t)((O + 127) / 128) * ((K + 127) / 128);
+    void *stg = nullptr;
+    const size_t off_s = (cb + 255) & ~(size_t)255;
+    if (c.stage.get(off_s + sb + 256, &stg)) return 1;
+    uint8_t *sc = (uint8_t *)stg, *ss = sc + off_s;
+    APUS_CUDA_OK(cudaMemcpyAsync(sc, codes, cb, cudaMemcpyHostToDevice, c.stream));
+    if (fmt == 4) {
+        APUS_CUDA_OK(cudaMemcpyAsync(ss, scales, sb, cudaMemcpyHostToDevice, c.stream));
+        int *flag = nullptr;
+        void *fp = nullptr;
+        if (c.ws[15].get(256, &fp)) return 1;
+        flag = (int *)fp;
+        APUS_CUDA_OK(cudaMemsetAsync(flag, 0, sizeof(int), c.stream));
+        if (repack_fp4(sc, ss, O, K, dst_codes, dst_scales, flag, c.stream)) return 1;
+        int hz = 0;
+        APUS_CUDA_OK(cudaMemcpyAsync(&hz, flag, sizeof(int), cudaMemcpyDeviceToHost, c.stream));
+        APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+        if (zero_scale) *zero_scale = hz;
+    } else {
+        if (repack_fp8(sc, O, K, dst_codes, c.stream)) return 1;
+        APUS_CUDA_OK(cudaMemcpyAsync(dst_scales, scales, sb, cudaMemcpyHostToDevice, c.stream));
+        APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+        if (zero_scale) *zero_scale = 0;
+    }
+    c.bytes_uploaded += cb + sb;
+    return 0;
+}
+
+DevQW *new_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K) {
+    if (ensure_enabled()) return nullptr;
+    if (O % 16 || K % 128) {
+        set_error("quantised weight [%d,%d]: O must be a multiple of 16 and K of 128", O, K);
+        return nullptr;
+    }
+    DevQW *w = new DevQW();
+    w->fmt = fmt; w->O = O; w->K = K;
+    size_t cb = fmt == 4 ? (size_t)O * K / 2 : (size_t)O * K;
+    size_t sb = fmt == 4 ? (size_t)O * K / 32 : (size_t)((O + 127) / 128) * (K / 128);
+    if (cudaMalloc(&w->codes, cb) != cudaSuccess || cudaMalloc(&w->scales, sb) != cudaSuccess) {
+        set_error("cudaMalloc of %zu weight bytes failed", cb + sb);
+        w->release(); delete w;
+        return nullptr;
+    }
+    if (upload_qw(fmt, codes, scales, O, K, w->codes, w->scales, &w->zero_scale)) {
+        w->release(); delete w;
+        return nullptr;
+    }
+    return w;
+}
+
+DevQW *cached_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K) {
+    Ctx &c = ctx();
+    auto it = c.qcache.find(codes);
+    if (it != c.qcache.end() && it->second->fmt == fmt && it->second->O == O && it->second->K == K)
+        return it->second;
+    if (it != c.qcache.end()) { it->second->release(); delete it->second; c.qcache.erase(it); }
+    DevQW *w = new_qw(fmt, codes, scales, O, K);
+    if (w) c.qcache[codes] = w;
+    return w;
+}
+
+const void *cached_dense(const void *host, size_t bytes) {
+    Ctx &c = ctx();
+    auto it = c.dcache.find(host);
+    if (it != c.dcache.end() && it->second->cap >= bytes) return it->second->p;
+    DevBuf *b = it != c.dcache.end() ? it->second : new DevBuf();
+    if (b->get(bytes, nullptr)) return nullptr;
+    if (cudaMemcpy(b->p, host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+        set_error("upload of %zu dense weight bytes failed", bytes);
+        return nullptr;
+    }
+    c.bytes_uploaded += bytes;
+    c.dcache[host] = b;
+    return b->p;
+}
+
+// ---- composite device ops ----------------------------------------------------------------------
+int qlinear_dev(DevQW *w, const float *x, float *out, int M, uint8_t *xq, float *xs,
+                bool round_out, cudaStream_t st) {
+    if (M <= 0) return 0;
+    if (act_quant(x, nullptr, M, w->K, xq, xs, nullptr, st)) return 1;
+    GemmSmallArgs a = {};
+    a.fmt = w->fmt; a.pair = 0; a.round_out = round_out; a.O = w->O; a.K = w->K;
+    if (w->table_for(M, false, nullptr, const_cast<GemmGroup **>(&a.groups), &a.n_groups)) return 1;
+    a.max_rows = M < 32 ? M : 32;
+    a.acodes = xq; a.ascales = xs; a.out = out; a.zero_scale = w->zero_scale;
+    return gemm_small(a, st);
+}
+
+int expert_dev(DevQW *w1, DevQW *w2, DevQW *w3, float limit, const float *x, int rows,
+               float *out, const ExpertWs &ws, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    APUS_REQUIRE(w1->fmt == w3->fmt && w1->fmt == w2->fmt && w1->O == w3->O && w1->K == w3->K &&
+                 w2->K == w1->O && w2->O == w1->K, "expert: inconsistent weight shapes");
+    if (act_quant(x, nullptr, rows, w1->K, ws.xq, ws.xs, nullptr, st)) return 1;
+    GemmSmallArgs a = {};
+    a.fmt = w1->fmt; a.pair = 1; a.limit = limit; a.O = w1->O; a.K = w1->K;
+    if (w1->table_for(rows, true, w3, const_cast<GemmGroup **>(&a.groups), &a.n_groups)) return 1;
+    a.max_rows = rows < 32 ? rows : 32;
+    a.acodes = ws.xq; a.ascales = ws.xs; a.out = ws.h;
+    a.zero_scale = w1->zero_scale | w3->zero_scale;
+    if (gemm_small(a, st)) return 1;
+    return qlinear_dev(w2, ws.h, out, rows, ws.hq, ws.hs, true, st);
+}
+
+}  // namespace apus
+
+using namespace apus;
+
+// =====================================================================================
+extern "C" {
+
+int apus_cuda_enable(char *err, size_t errcap) {
+    if (ensure_enabled()) {
+        if (err && errcap) snprintf(err, errcap, "%s", t_err);
+        return 1;
+    }
+    return 0;
+}
+
+void apus_cuda_moe_destroy(ApusCudaMoe *m);
+
+void apus_cuda_disable(void) {
+    Ctx &c = ctx();
+    if (!c.enabled) return;
+    cudaDeviceSynchronize();
+    for (auto &kv : c.qcache) { kv.second->release(); delete kv.second; }
+    c.qcache.clear();
+    for (auto &kv : c.dcache) { kv.second->release(); delete kv.second; }
+    c.dcache.clear();
+    for (auto &kv : c.moes) apus_cuda_moe_destroy(kv.second);
+    c.moes.clear();
+    for (auto &b : c.ws) b.release();
+    c.stage.release();
+    if (c.stream) cudaStreamDestroy(c.stream);
+    c.stream = nullptr;
+    c.enabled = false;
+}
+
+int apus_cuda_is_enabled(void) { return ctx().enabled ? 1 : 0; }
+uint64_t apus_cuda_bytes_uploaded(void) { return ctx().bytes_uploaded; }
+uint64_t apus_cuda_dispatches(void) { return g_dispatches; }
+const char *apus_cuda_last_error(void) { return t_err; }
+
+void apus_cuda_forget(const void *host_ptr) {
+    Ctx &c = ctx();
+    auto q = c.qcache.find(host_ptr);
+    if (q != c.qcache.end()) { cudaDeviceSynchronize(); q->second->release(); delete q->second; c.qcache.erase(q); }
+    auto d = c.dcache.find(host_ptr);
+    if (d != c.dcache.end()) { cudaDeviceSynchronize(); d->second->release(); delete d->second; c.dcache.erase(d); }
+    auto m = c.moes.find(host_ptr);
+    if (m != c.moes.end()) { cudaDeviceSynchronize(); apus_cuda_moe_destroy(m->second); c.moes.erase(m); }
+}
+
+// ---- hook table ----------------------------------------------------------------------
+static size_t g_st_dtype_off = 0, g_st_data_off = 0;
+
+static int hook_fp8_linear(const ApusFp8W *w, const float *x, float *out, int M, int K, int O) {
+    return apus_cuda_fp8_linear(w, x, out, M, K, O);
+}
+static int hook_f32_linear(const float *w, const float *x, float *out, int M, int K, int O,
+                           int flags) {
+    return apus_cuda_f32_linear(w, x, out, M, K, O, flags);
+}
+static int hook_head_gemv(const void *head, const float *x, float *out, int64_t O, int64_t K) {
+    // reference c/st.h:42-46: dtype enum, BF16 = 4, F32 = 6
+    int dtype = *(const int *)((const char *)head + g_st_dtype_off);
+    const void *data = *(const void *const *)((const char *)head + g_st_data_off);
+    if (dtype == 4) return apus_cuda_head_gemv_bf16(data, x, out, O, K);
+    if (dtype == 6) return apus_cuda_f32_linear((const float *)data, x, out, 1, (int)K, (int)O, 0);
+    set_error("head_gemv: unsupported tensor dtype %d", dtype);
+    return 1;
+}
+
+int apus_cuda_fill_hooks(ApusCudaHooks *hooks, size_t struct_dtype_off, size_t struct_data_off) {
+    if (!hooks) { set_error("fill_hooks: NULL table"); return 1; }
+    if (ensure_enabled()) return 1;
+    g_st_dtype_off = struct_dtype_off;
+    g_st_data_off = struct_data_off;
+    hooks->fp8_linear = hook_fp8_linear;
+    hooks->f32_linear = hook_f32_linear;
+    hooks->head_gemv = hook_head_gemv;
+    return 0;
+}
+
+// ---- kernel-level host-pointer entry points ---------------------------------------------
+static int host_qlinear(int fmt, const uint8_t *codes, const uint8_t *scales, int64_t wO,
+                        int64_t wK, const float *x, float *out, int M, int K, int O) {
+    if (ensure_enabled()) return 1;
+    APUS_REQUIRE(wO == O && wK == K, "linear: weight is [%lld,%lld] but call says O=%d K=%d",
+                 (long long)wO, (long long)wK, O, K);
+    if (M <= 0) return 0;
+    Ctx &c = ctx();
+    DevQW *w = cached_qw(fmt, codes, scales, O, K);
+    if (!w) return 1;
+    void *dx, *dq, *ds, *dout;
+    if (c.ws[0].get((size_t)M * K * 4, &dx) || c.ws[1].get((size_t)M * K, &dq) ||
+        c.ws[2].get((size_t)M * (K / 128) * 4, &ds) || c.ws[3].get((size_t)M * O * 4, &dout))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)M * K * 4, cudaMemcpyHostToDevice, c.stream));
+    if (qlinear_dev(w, (float *)dx, (float *)dout, M, (uint8_t *)dq, (float *)ds, true, c.stream))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)M * O * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_fp8_linear(const ApusFp8W *w, const float *x, float *out, int M, int K, int O) {
+    return host_qlinear(8, w->codes, w->scales, w->O, w->K, x, out, M, K, O);
+}
+int apus_cuda_fp4_linear(const ApusFp4W *w, const float *x, float *out, int M, int K, int O) {
+    return host_qlinear(4, w->packed, w->scales, w->O, w->K, x, out, M, K, O);
+}
+
+int apus_cuda_f32_linear(const float *w, const float *x, float *out, int M, int K, int O,
+                         int flags) {
+    if (ensure_enabled()) return 1;
+    if (M <= 0) return 0;
+    Ctx &c = ctx();
+    size_t wbytes = (size_t)O * K * ((flags & APUS_CUDA_W_BF16) ? 2 : 4);
+    const void *dw = cached_dense(w, wbytes);
+    if (!dw) return 1;
+    void *dx, *dout;
+    if (c.ws[0].get((size_t)M * K * 4, &dx) || c.ws[3].get((size_t)M * O * 4, &dout)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)M * K * 4, cudaMemcpyHostToDevice, c.stream));
+    if (f32_linear(dw, (float *)dx, (float *)dout, M, K, O, flags, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)M * O * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_head_gemv_bf16(const void *w_bf16, const float *x, float *out, int64_t O,
+                             int64_t K) {
+    return apus_cuda_f32_linear((const float *)w_bf16, x, out, 1, (int)K, (int)O,
+                                APUS_CUDA_W_BF16);
+}
+
+static int host_qgemm(int fmt, const uint8_t *w, const uint8_t *ws, const uint8_t *acodes,
+                      const float *as, float *out, int M, int O, int K) {
+    if (ensure_enabled()) return 1;
+    if (M <= 0) return 0;
+    Ctx &c = ctx();
+    DevQW *dw = cached_qw(fmt, w, ws, O, K);
+    if (!dw) return 1;
+    void *dq, *ds, *dout;
+    if (c.ws[1].get((size_t)M * K, &dq) || c.ws[2].get((size_t)M * (K / 128) * 4, &ds) ||
+        c.ws[3].get((size_t)M * O * 4, &dout))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dq, acodes, (size_t)M * K, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(ds, as, (size_t)M * (K / 128) * 4, cudaMemcpyHostToDevice, c.stream));
+    GemmSmallArgs a = {};
+    a.fmt = fmt; a.O = O; a.K = K; a.round_out = 0;
+    if (dw->table_for(M, false, nullptr, const_cast<GemmGroup **>(&a.groups), &a.n_groups)) return 1;
+    a.max_rows = M < 32 ? M : 32;
+    a.acodes = (uint8_t *)dq; a.ascales = (float *)ds; a.out = (float *)dout;
+    a.zero_scale = dw->zero_scale;
+    if (gemm_small(a, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)M * O * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_fp8_gemm(const uint8_t *w, const uint8_t *ws, const uint8_t *acodes,
+                       const float *as, float *out, int M, int O, int K) {
+    return host_qgemm(8, w, ws, acodes, as, out, M, O, K);
+}
+int apus_cuda_fp4_gemm(const uint8_t *w, const uint8_t *ws, const uint8_t *acodes,
+                       const float *as, float *out, int M, int O, int K) {
+    return host_qgemm(4, w, ws, acodes, as, out, M, O, K);
+}
+
+int apus_cuda_fp4_gemm_grouped(const ApusFp4GemmEnt *ents, size_t n_ent, const uint8_t *acodes,
+                               const float *as, size_t rows, size_t O, size_t K) {
+    if (ensure_enabled()) return 1;
+    if (!n_ent) return 0;
+    Ctx &c = ctx();
+    // work items: each entry cut into runs of <= 32 rows; outputs land in one
+    // device buffer laid out entry after entry, copied back per entry.
+    std::vector<GemmGroup> items;
+    std::vector<int> orow;           // output row (in the packed out buffer) of activation-space position
+    std::vector<size_t> out_off(n_ent);
+    size_t out_rows = 0;
+    int zs = 0;
+    std::vector<int> arow;           // activation row of each work-item position
+    for (size_t e = 0; e < n_ent; e++) {
+        DevQW *dw = cached_qw(4, ents[e].w, ents[e].ws, (int)O, (int)K);
+        if (!dw) return 1;
+        zs |= dw->zero_scale;
+        out_off[e] = out_rows;
+        APUS_REQUIRE(ents[e].m0 + ents[e].M <= rows, "grouped gemm: entry %zu exceeds the row space", e);
+        for (size_t r = 0; r < ents[e].M; r += 32) {
+            GemmGroup g = {};
+            g.wa = dw->codes; g.sa = dw->scales;
+            g.row0 = (int)arow.size();
+            g.nrows = (int)(ents[e].M - r < 32 ? ents[e].M - r : 32);
+            for (int i = 0; i < g.nrows; i++) {
+                arow.push_back((int)(ents[e].m0 + r + i));
+                orow.push_back((int)(out_rows + r + i));
+            }
+            items.push_back(g);
+        }
+        out_rows += ents[e].M;
+    }
+    if (!out_rows) return 0;
+    void *dq, *ds, *dout, *dtab, *darow, *dorow;
+    if (c.ws[1].get(rows * K, &dq) || c.ws[2].get(rows * (K / 128) * 4, &ds) ||
+        c.ws[3].get(out_rows * O * 4, &dout) || c.ws[4].get(items.size() * sizeof(GemmGroup), &dtab) ||
+        c.ws[5].get(arow.size() * 4, &darow) || c.ws[6].get(orow.size() * 4, &dorow))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dq, acodes, rows * K, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(ds, as, rows * (K / 128) * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dtab, items.data(), items.size() * sizeof(GemmGroup), cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(darow, arow.data(), arow.size() * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dorow, orow.data(), orow.size() * 4, cudaMemcpyHostToDevice, c.stream));
+    GemmSmallArgs a = {};
+    a.fmt = 4; a.O = (int)O; a.K = (int)K; a.round_out = 0;
+    a.groups = (GemmGroup *)dtab; a.n_groups = (int)items.size(); a.max_rows = 32;
+    a.acodes = (uint8_t *)dq; a.ascales = (float *)ds; a.arow = (int *)darow; a.orow = (int *)dorow;
+    a.out = (float *)dout; a.zero_scale = zs;
+    if (gemm_small(a, c.stream)) return 1;
+    for (size_t e = 0; e < n_ent; e++)
+        if (ents[e].M)
+            APUS_CUDA_OK(cudaMemcpyAsync(ents[e].out, (float *)dout + out_off[e] * O,
+                                         ents[e].M * O * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_fp8_act_quant(const float *x, int M, int K, uint8_t *codes, float *scales) {
+    if (ensure_enabled()) return 1;
+    if (M <= 0) return 0;
+    Ctx &c = ctx();
+    void *dx, *dq, *ds;
+    if (c.ws[0].get((size_t)M * K * 4, &dx) || c.ws[1].get((size_t)M * K, &dq) ||
+        c.ws[2].get((size_t)M * (K / 128) * 4, &ds))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)M * K * 4, cudaMemcpyHostToDevice, c.stream));
+    if (act_quant((float *)dx, nullptr, M, K, (uint8_t *)dq, (float *)ds, nullptr, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(codes, dq, (size_t)M * K, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(scales, ds, (size_t)M * (K / 128) * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_rmsnorm(const float *x, const float *w, float eps, float *y, int64_t n,
+                      int64_t rows) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    Ctx &c = ctx();
+    void *dx, *dw, *dy;
+    if (c.ws[0].get(rows * n * 4, &dx) || c.ws[1].get(n * 4, &dw) || c.ws[3].get(rows * n * 4, &dy))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, rows * n * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dw, w, n * 4, cudaMemcpyHostToDevice, c.stream));
+    if (rms_norm((float *)dx, (float *)dw, eps, (float *)dy, n, rows, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(y, dy, rows * n * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+static int get_expert_ws(int rows, int dim, int inter, ExpertWs *ws, int base_slot) {
+    Ctx &c = ctx();
+    void *h, *xq, *hq, *xs, *hs;
+    if (c.ws[base_slot].get((size_t)rows * inter * 4, &h) ||
+        c.ws[base_slot + 1].get((size_t)rows * dim, &xq) ||
+        c.ws[base_slot + 2].get((size_t)rows * inter, &hq) ||
+        c.ws[base_slot + 3].get((size_t)rows * (dim / 128) * 4, &xs) ||
+        c.ws[base_slot + 4].get((size_t)rows * (inter / 128) * 4, &hs))
+        return 1;
+    ws->h = (float *)h; ws->xq = (uint8_t *)xq; ws->hq = (uint8_t *)hq;
+    ws->xs = (float *)xs; ws->hs = (float *)hs;
+    return 0;
+}
+
+int apus_cuda_expert(const void *w1, const void *w2, const void *w3, int kind, float limit,
+                     const float *x, int rows, int dim, int inter, float *out) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    Ctx &c = ctx();
+    // ApusFp4W and ApusFp8W share one layout (c/st.h:88-89)
+    const ApusFp4W *a1 = (const ApusFp4W *)w1, *a2 = (const ApusFp4W *)w2, *a3 = (const ApusFp4W *)w3;
+    int fmt = kind == 0 ? 4 : 8;
+    APUS_REQUIRE(a1->O == inter && a1->K == dim && a3->O == inter && a3->K == dim &&
+                 a2->O == dim && a2->K == inter, "expert: weight shapes do not match dim=%d inter=%d", dim, inter);
+    DevQW *d1 = cached_qw(fmt, a1->packed, a1->scales, inter, dim);
+    DevQW *d3 = cached_qw(fmt, a3->packed, a3->scales, inter, dim);
+    DevQW *d2 = cached_qw(fmt, a2->packed, a2->scales, dim, inter);
+    if (!d1 || !d2 || !d3) return 1;
+    void *dx, *dout;
+    ExpertWs ws;
+    if (c.ws[0].get((size_t)rows * dim * 4, &dx) || c.ws[3].get((size_t)rows * dim * 4, &dout) ||
+        get_expert_ws(rows, dim, inter, &ws, 7))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)rows * dim * 4, cudaMemcpyHostToDevice, c.stream));
+    if (expert_dev(d1, d2, d3, limit, (float *)dx, rows, (float *)dout, ws, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)rows * dim * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_topk_stable(const float *row, int n, int k, int32_t *idx, int rows) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    Ctx &c = ctx();
+    void *dx, *di;
+    if (c.ws[0].get((size_t)rows * n * 4, &dx) || c.ws[3].get((size_t)rows * k * 4, &di)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, row, (size_t)rows * n * 4, cudaMemcpyHostToDevice, c.stream));
+    if (topk_stable((float *)dx, n, k, (int32_t *)di, rows, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(idx, di, (size_t)rows * k * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_sparse_attn(const float *q, const float *sink, int h, int d, const int32_t *idxs,
+                          int idxw, int s, float scale, const float *kv_a, int64_t na,
+                          const float *kv_b, int64_t nb, float *o) {
+    if (ensure_enabled()) return 1;
+    if (s <= 0) return 0;
+    Ctx &c = ctx();
+    size_t qb = (size_t)s * h * d * 4;
+    void *dq, *dsink, *di, *da, *db, *dout;
+    if (c.ws[0].get(qb, &dq) || c.ws[1].get((size_t)h * 4, &dsink) ||
+        c.ws[2].get((size_t)s * idxw * 4 + 16, &di) || c.ws[4].get((size_t)na * d * 4 + 16, &da) ||
+        c.ws[5].get((size_t)nb * d * 4 + 16, &db) || c.ws[3].get(qb, &dout))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dq, q, qb, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dsink, sink, (size_t)h * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(di, idxs, (size_t)s * idxw * 4, cudaMemcpyHostToDevice, c.stream));
+    if (na) APUS_CUDA_OK(cudaMemcpyAsync(da, kv_a, (size_t)na * d * 4, cudaMemcpyHostToDevice, c.stream));
+    if (nb) APUS_CUDA_OK(cudaMemcpyAsync(db, kv_b, (size_t)nb * d * 4, cudaMemcpyHostToDevice, c.stream));
+    if (sparse_attn((float *)dq, (float *)dsink, h, d, (int32_t *)di, idxw, s, scale, da, na, db, nb,
+                    0, (float *)dout, c.stream))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(o, dout, qb, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+// ---- mHC host-pointer entry points ------------------------------------------------------------
+static int mhc_host(const float *x4, size_t d, size_t n, const float *fn, const float *scale,
+                    float head_scale, const float *base, float norm_eps, float hc_eps, int iters,
+                    const float *norm_w, float rms_eps, float *pre, float *post, float *comb,
+                    float *y, float *y_normed, int rows, int head) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    Ctx &c = ctx();
+    size_t nmix = head ? n : (2 + n) * n, nx = n * d;
+    const float *dfn = (const float *)cached_dense(fn, nmix * nx * 4);
+    if (!dfn) return 1;
+    void *dx, *dsc, *dbase, *dnw, *dpre, *dpost, *dcomb, *dy, *dyn;
+    if (c.ws[0].get((size_t)rows * nx * 4, &dx) || c.ws[1].get(64, &dsc) ||
+        c.ws[2].get(nmix * 4, &dbase) || c.ws[4].get(d * 4, &dnw) ||
+        c.ws[5].get((size_t)rows * n * 4, &dpre) || c.ws[6].get((size_t)rows * n * 4, &dpost) ||
+        c.ws[7].get((size_t)rows * n * n * 4, &dcomb) || c.ws[3].get((size_t)rows * d * 4, &dy) ||
+        c.ws[8].get((size_t)rows * d * 4, &dyn))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x4, (size_t)rows * nx * 4, cudaMemcpyHostToDevice, c.stream));
+    if (!head) APUS_CUDA_OK(cudaMemcpyAsync(dsc, scale, 3 * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dbase, base, nmix * 4, cudaMemcpyHostToDevice, c.stream));
+    if (norm_w) APUS_CUDA_OK(cudaMemcpyAsync(dnw, norm_w, d * 4, cudaMemcpyHostToDevice, c.stream));
+    int rc;
+    if (head)
+        rc = mhc_head((float *)dx, (int)d, (int)n, dfn, head_scale, (float *)dbase, norm_eps, hc_eps,
+                      (float *)dy, rows, c.stream);
+    else
+        rc = mhc_pre((float *)dx, (int)d, (int)n, dfn, (float *)dsc, (float *)dbase, norm_eps, hc_eps,
+                     iters, norm_w ? (float *)dnw : nullptr, rms_eps, (float *)dpre, (float *)dpost,
+                     (float *)dcomb, y ? (float *)dy : nullptr, (float *)dyn, rows, c.stream);
+    if (rc) return 1;
+    if (pre) APUS_CUDA_OK(cudaMemcpyAsync(pre, dpre, (size_t)rows * n * 4, cudaMemcpyDeviceToHost, c.stream));
+    if (post) APUS_CUDA_OK(cudaMemcpyAsync(post, dpost, (size_t)rows * n * 4, cudaMemcpyDeviceToHost, c.stream));
+    if (comb) APUS_CUDA_OK(cudaMemcpyAsync(comb, dcomb, (size_t)rows * n * n * 4, cudaMemcpyDeviceToHost, c.stream));
+    if (y) APUS_CUDA_OK(cudaMemcpyAsync(y, dy, (size_t)rows * d * 4, cudaMemcpyDeviceToHost, c.stream));
+    if (y_normed && norm_w)
+        APUS_CUDA_OK(cudaMemcpyAsync(y_normed, dyn, (size_t)rows * d * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_mhc_prepost(const float *x4, size_t d, size_t n, const float *fn, const float *scale,
+                          const float *base, float norm_eps, float hc_eps, int iters, float *pre,
+                          float *post, float *comb, int rows) {
+    return mhc_host(x4, d, n, fn, scale, 0.f, base, norm_eps, hc_eps, iters, nullptr, 0.f, pre, post,
+                    comb, nullptr, nullptr, rows, 0);
+}
+
+int apus_cuda_hc_pre(const float *x4, size_t d, size_t n, const float *fn, const float *scale,
+                     const float *base, float norm_eps, float hc_eps, int iters, const float *norm_w,
+                     float rms_eps, float *y, float *y_normed, float *post, float *comb, int rows) {
+    APUS_REQUIRE(y != nullptr, "hc_pre: y must not be NULL");
+    return mhc_host(x4, d, n, fn, scale, 0.f, base, norm_eps, hc_eps, iters, norm_w, rms_eps, nullptr,
+                    post, comb, y, y_normed, rows, 0);
+}
+
+int apus_cuda_hc_head(const float *x4, size_t d, size_t n, const float *fn, float scale,
+                      const float *base, float norm_eps, float hc_eps, float *y, int rows) {
+    return mhc_host(x4, d, n, fn, nullptr, scale, base, norm_eps, hc_eps, 0, nullptr, 0.f, nullptr,
+                    nullptr, nullptr, y, nullptr, rows, 1);
+}
+
+int apus_cuda_hc_post(const float *f, const float *res4, const float *post, const float *comb,
+                      float *y4, size_t d, size_t n, int rows) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    Ctx &c = ctx();
+    void *df, *dres, *dpost, *dcomb, *dy;
+    if (c.ws[0].get((size_t)rows * d * 4, &df) || c.ws[1].get((size_t)rows * n * d * 4, &dres) ||
+        c.ws[5].get((size_t)rows * n * 4, &dpost) || c.ws[6].get((size_t)rows * n * n * 4, &dcomb) ||
+        c.ws[3].get((size_t)rows * n * d * 4, &dy))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(df, f, (size_t)rows * d * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dres, res4, (size_t)rows * n * d * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dpost, post, (size_t)rows * n * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dcomb, comb, (size_t)rows * n * n * 4, cudaMemcpyHostToDevice, c.stream));
+    if (mhc_post((float *)df, (float *)dres, (float *)dpost, (float *)dcomb, (float *)dy, (int)d,
+                 (int)n, rows, c.stream))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(y4, dy, (size_t)rows * n * d * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+// ---- single matrices, device-resident ------------------------------------------------------------
+ApusCudaFp4 *apus_cuda_fp4_upload(const ApusFp4W *w) {
+    return static_cast<ApusCudaFp4 *>(new_qw(4, w->packed, w->scales, (int)w->O, (int)w->K));
+}
+ApusCudaFp8 *apus_cuda_fp8_upload(const ApusFp8W *w) {
+    return static_cast<ApusCudaFp8 *>(new_qw(8, w->codes, w->scales, (int)w->O, (int)w->K));
+}
+void apus_cuda_fp4_free(ApusCudaFp4 *w) { if (w) { cudaDeviceSynchronize(); w->release(); delete static_cast<DevQW *>(w); } }
+void apus_cuda_fp8_free(ApusCudaFp8 *w) { if (w) { cudaDeviceSynchronize(); w->release(); delete static_cast<DevQW *>(w); } }
+
+// per-handle activation workspaces for the *_dev calls (grown on demand)
+static DevBuf g_dev_ws[8];
+
+static int qlinear_handle(DevQW *w, const float *x, float *out, int M, void *stream) {
+    if (ensure_enabled()) return 1;
+    void *dq, *ds;
+    if (g_dev_ws[0].get((size_t)M * w->K, &dq) || g_dev_ws[1].get((size_t)M * (w->K / 128) * 4, &ds))
+        return 1;
+    return qlinear_dev(w, x, out, M, (uint8_t *)dq, (float *)ds, true, (cudaStream_t)stream);
+}
+int apus_cuda_fp4_linear_dev(const ApusCudaFp4 *w, const float *x, float *out, int M, void *stream) {
+    return qlinear_handle(const_cast<ApusCudaFp4 *>(w), x, out, M, stream);
+}
+int apus_cuda_fp8_linear_dev(const ApusCudaFp8 *w, const float *x, float *out, int M, void *stream) {
+    return qlinear_handle(const_cast<ApusCudaFp8 *>(w), x, out, M, stream);
+}
+
+int apus_cuda_expert_fp4_dev(const ApusCudaFp4 *w1, const ApusCudaFp4 *w2, const ApusCudaFp4 *w3,
+                             float limit, const float *x, int rows, float *out, void *stream) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    int dim = w1->K, inter = w1->O;
+    void *h, *xq, *hq, *xs, *hs;
+    if (g_dev_ws[2].get((size_t)rows * inter * 4, &h) || g_dev_ws[3].get((size_t)rows * dim, &xq) ||
+        g_dev_ws[4].get((size_t)rows * inter, &hq) || g_dev_ws[5].get((size_t)rows * (dim / 128) * 4, &xs) ||
+        g_dev_ws[6].get((size_t)rows * (inter / 128) * 4, &hs))
+        return 1;
+    ExpertWs ws = {(float *)h, (uint8_t *)xq, (uint8_t *)hq, (float *)xs, (float *)hs};
+    return expert_dev(const_cast<ApusCudaFp4 *>(w1), const_cast<ApusCudaFp4 *>(w2),
+                      const_cast<ApusCudaFp4 *>(w3), limit, x, rows, out, ws, (cudaStream_t)stream);
+}
+
+int apus_cuda_topk_stable_dev(const float *scores, int n, int k, int32_t *idx, int rows,
+                              void *stream) {
+    if (ensure_enabled()) return 1;
+    return topk_stable(scores, n, k, idx, rows, (cudaStream_t)stream);
+}
+
+int apus_cuda_sparse_attn_dev(const float *q, const float *sink, int h, int d, const int32_t *idxs,
+                              int idxw, int s, float scale, const uint16_t *kv_a, int64_t na,
+                              const uint16_t *kv_b, int64_t nb, float *o, void *stream) {
+    if (ensure_enabled()) return 1;
+    return sparse_attn(q, sink, h, d, idxs, idxw, s, scale, kv_a, na, kv_b, nb, 1, o,
+                       (cudaStream_t)stream);
+}
+
+}  // extern "C"

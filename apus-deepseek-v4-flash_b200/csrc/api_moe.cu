@@ -1,0 +1,384 @@
+// C ABI, part 2: the MoE sublayer (include/apus_b200.h; reference c/moe.h).
+//
+// An ApusCudaMoe holds, in HBM, the tiled weights of the local experts
+// [e_lo, e_hi) as three slabs (w1, w3, w2 — expert-major), the f32 gate, the
+// selection bias and the FP8 shared expert, plus the per-call workspaces
+// (grown on demand, never shrunk).  A forward is a fixed sequence of kernels
+// on the caller's stream, with no host synchronisation and no host-side
+// decisions that depend on device data:
+//   gate matmul -> router finish -> act quant(x) -> group routings by expert
+//   -> gate/up GEMM + SwiGLU -> act quant(h) -> down GEMM (scatter to (t,j))
+//   -> shared expert (3 FP8 GEMMs) -> ordered combine.
+#include <vector>
+
+#include "runtime.cuh"
+
+using namespace apus;
+
+struct ApusCudaMoe {
+    int E = 0, topk = 0, inter = 0, dim = 0, hash = 0, e_lo = 0, e_hi = 0;
+    float route_scale = 0.f, limit = 0.f;
+    const void *host_key = nullptr;
+    float *gate_w = nullptr, *gate_bias = nullptr;
+    int64_t *tid2eid = nullptr;           // device [vocab, topk] (hash layers)
+    int64_t vocab = 0;
+    uint8_t *slab = nullptr;              // all local expert tensors
+    MoeSlab sl = {};
+    int zero_scale = 0;
+    DevQW sw1, sw2, sw3;                  // shared expert
+    uint64_t weight_bytes = 0;
+    // workspaces
+    int cap_s = 0, cap_r = 0;
+    DevBuf b_logits, b_sp, b_biased, b_idx, b_wgt, b_xq, b_xs, b_routrow, b_spos, b_srow,
+        b_g13, b_g2, b_ng, b_h, b_hq, b_hs, b_eo, b_shared, b_sh_h, b_sh_hq, b_sh_hs, b_ids,
+        b_tab;
+    int ensure(int s, int n_rout);
+};
+
+int ApusCudaMoe::ensure(int s, int n_rout) {
+    const size_t S = (size_t)(s > 0 ? s : 1), R = (size_t)(n_rout > 0 ? n_rout : 1);
+    if (s > cap_s) {
+        if (b_logits.get(S * E * 4, nullptr) || b_sp.get(S * E * 4, nullptr) ||
+            b_biased.get(S * E * 4, nullptr) || b_idx.get(S * topk * 4, nullptr) ||
+            b_wgt.get(S * topk * 4, nullptr) || b_shared.get(S * dim * 4, nullptr) ||
+            b_sh_h.get(S * inter * 4, nullptr) || b_sh_hq.get(S * inter, nullptr) ||
+            b_sh_hs.get(S * (inter / 128) * 4, nullptr) || b_ids.get(S * 8, nullptr) ||
+            b_tab.get(S * topk * 8, nullptr))
+            return 1;
+        cap_s = s;
+    }
+    // the activation-quant buffers serve both the token rows (route/forward)
+    // and explicit xrows (experts_dev): size them by the larger of the two
+    const size_t XR = S > R ? S : R;
+    if ((int)XR > cap_r || n_rout > cap_r) {
+        const size_t max_groups = R + (size_t)(e_hi - e_lo);
+        if (b_xq.get(XR * dim, nullptr) || b_xs.get(XR * (dim / 128) * 4, nullptr) ||
+            b_routrow.get(R * 4, nullptr) || b_spos.get(R * 4, nullptr) || b_srow.get(R * 4, nullptr) ||
+            b_g13.get(max_groups * sizeof(GemmGroup), nullptr) ||
+            b_g2.get(max_groups * sizeof(GemmGroup), nullptr) || b_ng.get(256, nullptr) ||
+            b_h.get(R * inter * 4, nullptr) || b_hq.get(R * inter, nullptr) ||
+            b_hs.get(R * (inter / 128) * 4, nullptr) || b_eo.get(R * dim * 4, nullptr))
+            return 1;
+        cap_r = (int)XR;
+    }
+    return 0;
+}
+
+static int pick_chunk(int n_rout, int n_local) {
+    // rows per work item: small batches keep one 8-column MMA tile
+    long long avg = n_local > 0 ? ((long long)n_rout + n_local - 1) / n_local : n_rout;
+    if (avg <= 4) return 8;
+    if (avg <= 12) return 16;
+    return 32;
+}
+
+// Routed experts for arbitrary local routings (device pointers).
+static int experts_run(ApusCudaMoe *m, const float *xrows, int n_rows, const int32_t *rout_row,
+                       const int32_t *rout_eid, int n_rout, float *eo, cudaStream_t st) {
+    if (n_rout <= 0) return 0;
+    const int dim = m->dim, inter = m->inter;
+    const int n_local = m->e_hi - m->e_lo;
+    const int chunk = pick_chunk(n_rout, n_local);
+    const int max_groups = n_rout < n_local + n_rout / chunk + 1 ? n_rout : n_local + n_rout / chunk + 1;
+    if (act_quant(xrows, nullptr, n_rows, dim, m->b_xq.as<uint8_t>(), m->b_xs.as<float>(), nullptr, st))
+        return 1;
+    if (moe_group(rout_eid, rout_row, n_rout, m->sl, chunk, m->b_spos.as<int>(), m->b_srow.as<int>(),
+                  m->b_g13.as<GemmGroup>(), m->b_g2.as<GemmGroup>(), m->b_ng.as<int>(), max_groups, st))
+        return 1;
+    GemmSmallArgs a = {};
+    a.fmt = 4; a.pair = 1; a.limit = m->limit; a.O = inter; a.K = dim;
+    a.groups = m->b_g13.as<GemmGroup>(); a.n_groups_dev = m->b_ng.as<int>(); a.n_groups = max_groups;
+    a.max_rows = chunk;
+    a.acodes = m->b_xq.as<uint8_t>(); a.ascales = m->b_xs.as<float>();
+    a.arow = m->b_srow.as<int>(); a.orow = nullptr; a.out = m->b_h.as<float>();
+    a.zero_scale = m->zero_scale;
+    if (gemm_small(a, st)) return 1;
+    // h rows are in sorted order; rows past the local routings are never read
+    if (act_quant(m->b_h.as<float>(), nullptr, n_rout, inter, m->b_hq.as<uint8_t>(),
+                  m->b_hs.as<float>(), nullptr, st))
+        return 1;
+    GemmSmallArgs b = {};
+    b.fmt = 4; b.pair = 0; b.round_out = 1; b.O = dim; b.K = inter;
+    b.groups = m->b_g2.as<GemmGroup>(); b.n_groups_dev = m->b_ng.as<int>(); b.n_groups = max_groups;
+    b.max_rows = chunk;
+    b.acodes = m->b_hq.as<uint8_t>(); b.ascales = m->b_hs.as<float>();
+    b.arow = nullptr; b.orow = m->b_spos.as<int>(); b.out = eo;
+    b.zero_scale = m->zero_scale;
+    return gemm_small(b, st);
+}
+
+static int shared_run(ApusCudaMoe *m, const float *x, int s, float *shared, cudaStream_t st) {
+    ExpertWs ws = {m->b_sh_h.as<float>(), m->b_xq.as<uint8_t>(), m->b_sh_hq.as<uint8_t>(),
+                   m->b_xs.as<float>(), m->b_sh_hs.as<float>()};
+    return expert_dev(&m->sw1, &m->sw2, &m->sw3, m->limit, x, s, shared, ws, st);
+}
+
+static int route_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const int64_t *table,
+                     int s, int32_t *idx, float *wgt, float *sp, float *biased, cudaStream_t st) {
+    if (f32_linear(m->gate_w, x, m->b_logits.as<float>(), s, m->dim, m->E, 0, st)) return 1;
+    if (!sp) sp = m->b_sp.as<float>();
+    if (m->hash) {
+        APUS_REQUIRE(table && ids, "hash-routed layer: no tid2eid table / ids on device");
+        return router_finish(m->b_logits.as<float>(), nullptr, table, ids, s, m->E, m->topk,
+                             m->route_scale, sp, nullptr, idx, wgt, st);
+    }
+    if (!biased) biased = m->b_biased.as<float>();
+    return router_finish(m->b_logits.as<float>(), m->gate_bias, nullptr, nullptr, s, m->E, m->topk,
+                         m->route_scale, sp, biased, idx, wgt, st);
+}
+
+__global__ void iota_rows_kernel(int32_t *rout_row, int n, int topk) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) rout_row[i] = i / topk;
+}
+
+static int forward_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const int64_t *table,
+                       int s, float *out, float *routed, cudaStream_t st) {
+    const int R = s * m->topk;
+    if (m->ensure(s, R)) return 1;
+    APUS_REQUIRE(m->e_lo == 0 && m->e_hi == m->E,
+                 "moe_forward_dev needs all experts local (this handle holds [%d,%d) of %d)",
+                 m->e_lo, m->e_hi, m->E);
+    if (route_run(m, x, ids, table, s, m->b_idx.as<int32_t>(), m->b_wgt.as<float>(), nullptr, nullptr, st))
+        return 1;
+    iota_rows_kernel<<<ceil_div(R, 256), 256, 0, st>>>(m->b_routrow.as<int32_t>(), R, m->topk);
+    APUS_LAUNCHED();
+    if (experts_run(m, x, s, m->b_routrow.as<int32_t>(), m->b_idx.as<int32_t>(), R,
+                    m->b_eo.as<float>(), st))
+        return 1;
+    if (shared_run(m, x, s, m->b_shared.as<float>(), st)) return 1;
+    return moe_combine(m->b_eo.as<float>(), m->b_wgt.as<float>(), m->b_shared.as<float>(), s,
+                       m->topk, m->dim, out, routed, st);
+}
+
+extern "C" {
+
+ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi) {
+    if (ensure_enabled()) return nullptr;
+    if (!w || e_lo < 0 || e_hi > w->E || e_lo > e_hi) { set_error("moe_create: bad expert range [%d,%d)", e_lo, e_hi); return nullptr; }
+    if (w->dim % 128 || w->inter % 128) { set_error("moe_create: dim=%d inter=%d must be multiples of 128", w->dim, w->inter); return nullptr; }
+    Ctx &c = ctx();
+    ApusCudaMoe *m = new ApusCudaMoe();
+    m->E = w->E; m->topk = w->topk; m->inter = w->inter; m->dim = w->dim; m->hash = w->hash;
+    m->route_scale = w->route_scale; m->limit = w->limit; m->e_lo = e_lo; m->e_hi = e_hi;
+    m->host_key = w->gate_w;
+    const int nl = e_hi - e_lo;
+    const size_t c13 = (size_t)w->inter * w->dim / 2, s13 = (size_t)w->inter * w->dim / 32;
+    const size_t c2 = (size_t)w->dim * w->inter / 2, s2 = (size_t)w->dim * w->inter / 32;
+    const size_t total = (size_t)nl * (2 * (c13 + s13) + c2 + s2);
+    bool ok = true;
+    ok = ok && cudaMalloc(&m->gate_w, (size_t)w->E * w->dim * 4) == cudaSuccess;
+    ok = ok && cudaMemcpy(m->gate_w, w->gate_w, (size_t)w->E * w->dim * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+    if (ok && !w->hash) {
+        ok = ok && cudaMalloc(&m->gate_bias, (size_t)w->E * 4) == cudaSuccess;
+        ok = ok && cudaMemcpy(m->gate_bias, w->gate_bias, (size_t)w->E * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+    }
+    if (ok && total) ok = cudaMalloc(&m->slab, total) == cudaSuccess;
+    if (!ok) { set_error("moe_create: device allocation of %zu bytes failed", total); apus_cuda_moe_destroy(m); return nullptr; }
+    uint8_t *p = m->slab;
+    m->sl.w1 = p; p += (size_t)nl * c13;
+    m->sl.w3 = p; p += (size_t)nl * c13;
+    m->sl.w2 = p; p += (size_t)nl * c2;
+    m->sl.s1 = p; p += (size_t)nl * s13;
+    m->sl.s3 = p; p += (size_t)nl * s13;
+    m->sl.s2 = p;
+    m->sl.code_stride13 = c13; m->sl.scale_stride13 = s13;
+    m->sl.code_stride2 = c2; m->sl.scale_stride2 = s2;
+    m->sl.e_lo = e_lo; m->sl.e_hi = e_hi;
+    for (int e = e_lo; e < e_hi; e++) {
+        ApusFp4W r1, r2, r3;
+        if (w->hook_resolve) {
+            if (w->hook_resolve(w->hook_ctx, w->layer_id, e, &r1, &r2, &r3)) {
+                set_error("moe_create: hook_resolve failed for expert %d", e);
+                apus_cuda_moe_destroy(m); return nullptr;
+            }
+        } else { r1 = w->w1[e]; r2 = w->w2[e]; r3 = w->w3[e]; }
+        const int le = e - e_lo;
+        int z1 = 0, z2 = 0, z3 = 0;
+        if (r1.O != w->inter || r1.K != w->dim || r3.O != w->inter || r3.K != w->dim ||
+            r2.O != w->dim || r2.K != w->inter) {
+            set_error("moe_create: expert %d has unexpected shapes", e);
+            apus_cuda_moe_destroy(m); return nullptr;
+        }
+        if (upload_qw(4, r1.packed, r1.scales, w->inter, w->dim, (uint8_t *)m->sl.w1 + le * c13,
+                      (uint8_t *)m->sl.s1 + le * s13, &z1) ||
+            upload_qw(4, r3.packed, r3.scales, w->inter, w->dim, (uint8_t *)m->sl.w3 + le * c13,
+                      (uint8_t *)m->sl.s3 + le * s13, &z3) ||
+            upload_qw(4, r2.packed, r2.scales, w->dim, w->inter, (uint8_t *)m->sl.w2 + le * c2,
+                      (uint8_t *)m->sl.s2 + le * s2, &z2)) {
+            apus_cuda_moe_destroy(m); return nullptr;
+        }
+        m->zero_scale |= z1 | z2 | z3;
+    }
+    // shared expert
+    struct { DevQW *d; const ApusFp8W *h; int O, K; } sh[3] = {
+        {&m->sw1, &w->sw1, w->inter, w->dim}, {&m->sw3, &w->sw3, w->inter, w->dim},
+        {&m->sw2, &w->sw2, w->dim, w->inter}};
+    for (auto &q : sh) {
+        DevQW *d = new_qw(8, q.h->codes, q.h->scales, q.O, q.K);
+        if (!d) { apus_cuda_moe_destroy(m); return nullptr; }
+        *q.d = *d;
+        delete d;                               // storage now owned by the member copy
+    }
+    m->weight_bytes = total + m->sw1.bytes() + m->sw2.bytes() + m->sw3.bytes() +
+                      (size_t)w->E * w->dim * 4 + (w->hash ? 0 : (size_t)w->E * 4);
+    (void)c;
+    return m;
+}
+
+void apus_cuda_moe_destroy(ApusCudaMoe *m) {
+    if (!m) return;
+    cudaDeviceSynchronize();
+    if (m->gate_w) cudaFree(m->gate_w);
+    if (m->gate_bias) cudaFree(m->gate_bias);
+    if (m->tid2eid) cudaFree(m->tid2eid);
+    if (m->slab) cudaFree(m->slab);
+    m->sw1.release(); m->sw2.release(); m->sw3.release();
+    DevBuf *bufs[] = {&m->b_logits, &m->b_sp, &m->b_biased, &m->b_idx, &m->b_wgt, &m->b_xq, &m->b_xs,
+                      &m->b_routrow, &m->b_spos, &m->b_srow, &m->b_g13, &m->b_g2, &m->b_ng, &m->b_h,
+                      &m->b_hq, &m->b_hs, &m->b_eo, &m->b_shared, &m->b_sh_h, &m->b_sh_hq,
+                      &m->b_sh_hs, &m->b_ids, &m->b_tab};
+    for (DevBuf *b : bufs) b->release();
+    delete m;
+}
+
+uint64_t apus_cuda_moe_bytes(const ApusCudaMoe *m) { return m ? m->weight_bytes : 0; }
+
+int apus_cuda_moe_set_hash_table(ApusCudaMoe *m, const int64_t *tid2eid, int64_t vocab) {
+    if (!m || !m->hash) { set_error("set_hash_table: not a hash-routed layer"); return 1; }
+    if (m->tid2eid) { cudaDeviceSynchronize(); cudaFree(m->tid2eid); m->tid2eid = nullptr; }
+    size_t bytes = (size_t)vocab * m->topk * 8;
+    APUS_CUDA_OK(cudaMalloc(&m->tid2eid, bytes));
+    APUS_CUDA_OK(cudaMemcpy(m->tid2eid, tid2eid, bytes, cudaMemcpyHostToDevice));
+    m->vocab = vocab;
+    return 0;
+}
+
+int apus_cuda_moe_route_dev(const ApusCudaMoe *mc, const float *x, const int64_t *ids, int s,
+                            int32_t *idx, float *wgt, float *sp, float *biased, void *stream) {
+    ApusCudaMoe *m = const_cast<ApusCudaMoe *>(mc);
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    if (s <= 0) return 0;
+    if (m->ensure(s, s * m->topk)) return 1;
+    return route_run(m, x, ids, m->tid2eid, s, idx, wgt, sp, biased, (cudaStream_t)stream);
+}
+
+int apus_cuda_moe_experts_dev(ApusCudaMoe *m, const float *xrows, int n_rows, const int32_t *rout_row,
+                              const int32_t *rout_eid, int n_rout, float *eo, void *stream) {
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    if (n_rout <= 0) return 0;
+    if (m->ensure(n_rows, n_rout)) return 1;
+    return experts_run(m, xrows, n_rows, rout_row, rout_eid, n_rout, eo, (cudaStream_t)stream);
+}
+
+int apus_cuda_moe_shared_dev(ApusCudaMoe *m, const float *x, int s, float *shared, void *stream) {
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    if (s <= 0) return 0;
+    if (m->ensure(s, s * m->topk)) return 1;
+    return shared_run(m, x, s, shared, (cudaStream_t)stream);
+}
+
+int apus_cuda_moe_combine_dev(const ApusCudaMoe *m, const float *eo, const float *wgt,
+                              const float *shared, int s, float *out, float *routed, void *stream) {
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    return moe_combine(eo, wgt, shared, s, m->topk, m->dim, out, routed, (cudaStream_t)stream);
+}
+
+int apus_cuda_moe_forward_dev(ApusCudaMoe *m, const float *x, const int64_t *ids, int s, float *out,
+                              void *stream) {
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    if (s <= 0) return 0;
+    return forward_run(m, x, ids, m->tid2eid, s, out, nullptr, (cudaStream_t)stream);
+}
+
+int apus_cuda_moe_last_routing(ApusCudaMoe *m, int s, int32_t *idx, float *wgt, void *stream) {
+    if (!m || s > m->cap_s) { set_error("last_routing: no routing of %d tokens recorded", s); return 1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    APUS_CUDA_OK(cudaMemcpyAsync(idx, m->b_idx.p, (size_t)s * m->topk * 4, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaMemcpyAsync(wgt, m->b_wgt.p, (size_t)s * m->topk * 4, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    return 0;
+}
+
+// ---- host-pointer tier ----------------------------------------------------------------------------
+static ApusCudaMoe *moe_for(const ApusMoeW *w) {
+    Ctx &c = ctx();
+    auto it = c.moes.find(w->gate_w);
+    if (it != c.moes.end()) return it->second;
+    ApusCudaMoe *m = apus_cuda_moe_create(w, 0, w->E);
+    if (m) c.moes[w->gate_w] = m;
+    return m;
+}
+
+int apus_cuda_router_score(const ApusMoeW *w, const float *x, int s, float *sp, float *biased) {
+    if (ensure_enabled()) return 1;
+    if (s <= 0) return 0;
+    Ctx &c = ctx();
+    const float *gw = (const float *)cached_dense(w->gate_w, (size_t)w->E * w->dim * 4);
+    if (!gw) return 1;
+    void *dx, *dl, *dsp, *db, *dbias, *didx, *dwgt;
+    const size_t se = (size_t)s * w->E * 4;
+    if (c.ws[0].get((size_t)s * w->dim * 4, &dx) || c.ws[1].get(se, &dl) || c.ws[2].get(se, &dsp) ||
+        c.ws[3].get(se, &db) || c.ws[4].get((size_t)w->E * 4, &dbias) ||
+        c.ws[5].get((size_t)s * w->topk * 4, &didx) || c.ws[6].get((size_t)s * w->topk * 4, &dwgt))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)s * w->dim * 4, cudaMemcpyHostToDevice, c.stream));
+    if (f32_linear(gw, (float *)dx, (float *)dl, s, w->dim, w->E, 0, c.stream)) return 1;
+    // scores only: run the finish kernel with a zero bias when none is wanted
+    if (biased && w->gate_bias)
+        APUS_CUDA_OK(cudaMemcpyAsync(dbias, w->gate_bias, (size_t)w->E * 4, cudaMemcpyHostToDevice, c.stream));
+    else
+        APUS_CUDA_OK(cudaMemsetAsync(dbias, 0, (size_t)w->E * 4, c.stream));
+    if (router_finish((float *)dl, (float *)dbias, nullptr, nullptr, s, w->E, w->topk, w->route_scale,
+                      (float *)dsp, (float *)db, (int32_t *)didx, (float *)dwgt, c.stream))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(sp, dsp, se, cudaMemcpyDeviceToHost, c.stream));
+    if (biased) APUS_CUDA_OK(cudaMemcpyAsync(biased, db, se, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_moe_forward(const ApusMoeW *w, const float *x, const int64_t *ids, int s, float *out,
+                          ApusMoeInterm *interm) {
+    if (ensure_enabled()) return 1;
+    if (s <= 0) return 0;
+    Ctx &c = ctx();
+    ApusCudaMoe *m = moe_for(w);
+    if (!m) return 1;
+    const int R = s * m->topk;
+    if (m->ensure(s, R)) return 1;
+    void *dx, *dout, *drouted;
+    if (c.ws[0].get((size_t)s * m->dim * 4, &dx) || c.ws[3].get((size_t)s * m->dim * 4, &dout) ||
+        c.ws[4].get((size_t)s * m->dim * 4, &drouted))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)s * m->dim * 4, cudaMemcpyHostToDevice, c.stream));
+    const int64_t *d_ids = nullptr, *d_tab = nullptr;
+    if (m->hash) {
+        // compact lookup table: row t holds tid2eid[ids[t]] (c/moe.h:391-394)
+        APUS_REQUIRE(w->tid2eid && ids, "hash-routed layer needs tid2eid and ids");
+        std::vector<int64_t> tab((size_t)R), iota((size_t)s);
+        for (int t = 0; t < s; t++) {
+            iota[t] = t;
+            for (int j = 0; j < m->topk; j++) tab[(size_t)t * m->topk + j] = w->tid2eid[ids[t] * m->topk + j];
+        }
+        APUS_CUDA_OK(cudaMemcpyAsync(m->b_ids.p, iota.data(), (size_t)s * 8, cudaMemcpyHostToDevice, c.stream));
+        APUS_CUDA_OK(cudaMemcpyAsync(m->b_tab.p, tab.data(), (size_t)R * 8, cudaMemcpyHostToDevice, c.stream));
+        APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+        d_ids = m->b_ids.as<int64_t>(); d_tab = m->b_tab.as<int64_t>();
+    }
+    if (forward_run(m, (float *)dx, d_ids, d_tab, s, (float *)dout, (float *)drouted, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)s * m->dim * 4, cudaMemcpyDeviceToHost, c.stream));
+    if (interm) {
+        const size_t se = (size_t)s * m->E * 4, sd = (size_t)s * m->dim * 4, sk = (size_t)s * m->topk * 4;
+        if (interm->router_scores) APUS_CUDA_OK(cudaMemcpyAsync(interm->router_scores, m->b_sp.p, se, cudaMemcpyDeviceToHost, c.stream));
+        if (interm->router_scores_biased && !m->hash) APUS_CUDA_OK(cudaMemcpyAsync(interm->router_scores_biased, m->b_biased.p, se, cudaMemcpyDeviceToHost, c.stream));
+        if (interm->router_w) APUS_CUDA_OK(cudaMemcpyAsync(interm->router_w, m->b_wgt.p, sk, cudaMemcpyDeviceToHost, c.stream));
+        if (interm->router_idx) APUS_CUDA_OK(cudaMemcpyAsync(interm->router_idx, m->b_idx.p, sk, cudaMemcpyDeviceToHost, c.stream));
+        if (interm->moe_routed) APUS_CUDA_OK(cudaMemcpyAsync(interm->moe_routed, drouted, sd, cudaMemcpyDeviceToHost, c.stream));
+        if (interm->moe_shared) APUS_CUDA_OK(cudaMemcpyAsync(interm->moe_shared, m->b_shared.p, sd, cudaMemcpyDeviceToHost, c.stream));
+    }
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+}  // extern "C"

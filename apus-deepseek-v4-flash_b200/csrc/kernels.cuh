@@ -1,0 +1,106 @@
+// Host-callable launchers of the device kernels (one group per .cu file).
+// Every launcher is asynchronous on `st`, returns 0 on success and nonzero
+// after recording a message with apus::set_error().
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace apus {
+
+// ---- fragment-tiled weight layouts (repack.cu) --------------------------------
+//
+// Weights are re-tiled once, at upload, into the order in which the tensor-core
+// fragments of the streaming kernels consume them (same number of bytes as the
+// reference storage; see repack.cu for the exact bit layout).
+int repack_fp4(const uint8_t *packed, const uint8_t *scales, int O, int K,
+               uint8_t *out_codes, uint8_t *out_scales, int *zero_scale_flag,
+               cudaStream_t st);
+int repack_fp8(const uint8_t *codes, int O, int K, uint8_t *out_codes,
+               cudaStream_t st);
+
+// ---- quantisation / norms (quant.cu) ----------------------------------------------
+// BF16 round + per-128 E4M3 quant of M rows (reference c/attn.h:393-402).
+// arow (nullable) gathers input rows: row m is read from x[arow[m]].
+int act_quant(const float *x, const int *arow, int M, int K, uint8_t *codes,
+              float *scales, const int *m_dev, cudaStream_t st);
+// RMSNorm rows (reference c/attn.h:371-378).
+int rms_norm(const float *x, const float *w, float eps, float *y, int64_t n,
+             int64_t rows, cudaStream_t st);
+
+// ---- small-M block-scaled GEMM (gemm_small.cu) ---------------------------------------
+//
+// One work item = one weight matrix (or a gate/up pair) times a contiguous run
+// of activation rows.  Used for decode GEMVs, expert groups and the prefill of
+// short prompts.
+struct GemmGroup {
+    const uint8_t *wa, *sa;   // matrix A: tiled codes / scales
+    const uint8_t *wb, *sb;   // matrix B (gate/up pair mode), else unused
+    int row0, nrows;          // activation rows [row0, row0+nrows), nrows <= 32
+};
+
+struct GemmSmallArgs {
+    int fmt;                  // 4 = MXFP4, 8 = FP8
+    int pair;                 // 1: out = swiglu(A x, B x) (reference c/moe.h:113-126)
+    int round_out;            // BF16-round outputs (ignored in pair mode: always)
+    float limit;              // SwiGLU clamp (pair mode)
+    int O, K;
+    const GemmGroup *groups;  // device array
+    const int *n_groups_dev;  // device scalar, or NULL to use n_groups
+    int n_groups;             // launch bound (grid.y)
+    int max_rows;             // largest nrows of any group (<= 32), picks the tile count
+    const uint8_t *acodes;    // [*, K]
+    const float *ascales;     // [*, K/128]
+    const int *arow;          // nullable: activation row of sorted position p
+    const int *orow;          // nullable: output row of sorted position p
+    float *out;               // [*, O]
+    int zero_scale;           // MXFP4: some weight scale byte is 0 (slow exact path)
+};
+int gemm_small(const GemmSmallArgs &a, cudaStream_t st);
+
+// ---- dense f32 / bf16 linears (linear.cu) ------------------------------------------------
+// out[m,o] = sum_k x[m,k]*w[o,k]; flags as APUS_CUDA_R_IN/R_OUT/W_BF16.
+int f32_linear(const void *w, const float *x, float *out, int M, int K, int O,
+               int flags, cudaStream_t st);
+
+// ---- MoE glue (moe.cu) ---------------------------------------------------------------------
+// sqrtsoftplus of gate logits, bias, stable top-k or hash lookup, weights.
+int router_finish(const float *logits, const float *bias, const int64_t *tid2eid,
+                  const int64_t *ids, int s, int E, int topk, float route_scale,
+                  float *sp, float *biased, int32_t *idx, float *wgt,
+                  cudaStream_t st);
+// Stable counting sort of routings by expert + work-item table.
+struct MoeSlab {            // where expert e's tiled tensors live
+    const uint8_t *w1, *s1, *w3, *s3, *w2, *s2;
+    size_t code_stride13, scale_stride13, code_stride2, scale_stride2;
+    int e_lo, e_hi;
+};
+int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int n_rout,
+              const MoeSlab &slab, int chunk, int *sorted_pos, int *sorted_row,
+              GemmGroup *g13, GemmGroup *g2, int *n_groups, int max_groups,
+              cudaStream_t st);
+// y[t] = sum_j wgt[t,j]*eo[t*topk+j] (j order) ; out = bf16(y + shared).
+int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
+                int topk, int dim, float *out, float *routed, cudaStream_t st);
+
+// ---- selection + attention (attn.cu) ----------------------------------------------------------
+int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
+                cudaStream_t st);
+int sparse_attn(const float *q, const float *sink, int h, int d,
+                const int32_t *idxs, int idxw, int s, float scale,
+                const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
+                int kv_bf16, float *o, cudaStream_t st);
+
+// ---- mHC (mhc.cu) -----------------------------------------------------------------------------------
+int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
+            const float *base, float norm_eps, float hc_eps, int iters,
+            const float *norm_w, float rms_eps, float *pre, float *post,
+            float *comb, float *y, float *y_normed, int rows, cudaStream_t st);
+int mhc_post(const float *f, const float *res4, const float *post,
+             const float *comb, float *y4, int d, int n, int rows,
+             cudaStream_t st);
+int mhc_head(const float *x4, int d, int n, const float *fn, float scale,
+             const float *base, float norm_eps, float hc_eps, float *y,
+             int rows, cudaStream_t st);
+
+}  // namespace apus

@@ -1,0 +1,225 @@
+// mHC (manifold-constrained hyper-connections): per-token pre/post/comb maps,
+// Sinkhorn normalisation, and the collapse fused with the adjacent RMSNorm.
+//
+// Reference: c/mhc.h:159-285 (maps, Sinkhorn order, collapse/apply/head) and
+// c/layer.h:401-468 (where the BF16 rounds sit).  Two kernels per hc_pre:
+//   1. mhc_mix_kernel: the (2+n)*n dots of the f32 map matrix fn [nmix, n*d]
+//      with the token state, plus the sum of squares, one CTA per (mix, token);
+//   2. mhc_pre_finish_kernel: one CTA per token turns the raw dots into
+//      pre/post/comb (rsqrt applied AFTER the dot, sigmoid gates, Sinkhorn with
+//      the reference's eps placement), collapses the n streams with `pre`,
+//      BF16-rounds and, when a norm weight is given, applies RMSNorm to the
+//      collapsed row in the same kernel (reference c/attn.h:371-378).
+// Bytes per token: fn (nmix*n*d*4, L2-resident across tokens) + 2 reads of the
+// n*d state.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace apus {
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    v = warp_sum(v);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[0] = t;
+    }
+    __syncthreads();
+    return red[0];
+}
+
+// grid (nmix + 1, rows): blockIdx.x < nmix -> raw[row, j] = fn_j . x ;
+// blockIdx.x == nmix -> raw[row, nmix] = sum x^2.
+__global__ void __launch_bounds__(256)
+mhc_mix_kernel(const float *__restrict__ x4, const float *__restrict__ fn, int nx, int nmix,
+               float *__restrict__ raw) {
+    __shared__ float red[32];
+    const int j = blockIdx.x, row = blockIdx.y;
+    const float *x = x4 + (size_t)row * nx;
+    float acc = 0.f;
+    if (j < nmix) {
+        const float *f = fn + (size_t)j * nx;
+        for (int i = threadIdx.x * 4; i < nx; i += blockDim.x * 4) {
+            float4 a = __ldg(reinterpret_cast<const float4 *>(f + i));
+            float4 b = *reinterpret_cast<const float4 *>(x + i);
+            acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
+            acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+        }
+    } else {
+        for (int i = threadIdx.x * 4; i < nx; i += blockDim.x * 4) {
+            float4 b = *reinterpret_cast<const float4 *>(x + i);
+            acc = fmaf(b.x, b.x, acc); acc = fmaf(b.y, b.y, acc);
+            acc = fmaf(b.z, b.z, acc); acc = fmaf(b.w, b.w, acc);
+        }
+    }
+    float tot = block_sum(acc, red);
+    if (threadIdx.x == 0) raw[(size_t)row * (nmix + 1) + j] = tot;
+}
+
+__device__ __forceinline__ float sigm(float x) { return __fdiv_rn(1.0f, 1.0f + expf(-x)); }
+
+// Sinkhorn on an n x n matrix held by one thread (reference c/mhc.h:181-218).
+__device__ void sinkhorn(float *c, int n, int iters, float eps) {
+    for (int j = 0; j < n; j++) {
+        float *r = c + j * n, mx = r[0], sum = 0.f;
+        for (int k = 1; k < n; k++) mx = fmaxf(mx, r[k]);
+        for (int k = 0; k < n; k++) { r[k] = expf(r[k] - mx); sum = __fadd_rn(sum, r[k]); }
+        for (int k = 0; k < n; k++) r[k] = __fadd_rn(__fdiv_rn(r[k], sum), eps);
+    }
+    for (int it = 0; it < iters; it++) {
+        if (it) for (int j = 0; j < n; j++) {
+            float sum = 0.f;
+            for (int k = 0; k < n; k++) sum = __fadd_rn(sum, c[j * n + k]);
+            float den = __fadd_rn(sum, eps);
+            for (int k = 0; k < n; k++) c[j * n + k] = __fdiv_rn(c[j * n + k], den);
+        }
+        for (int k = 0; k < n; k++) {
+            float sum = 0.f;
+            for (int j = 0; j < n; j++) sum = __fadd_rn(sum, c[j * n + k]);
+            float den = __fadd_rn(sum, eps);
+            for (int j = 0; j < n; j++) c[j * n + k] = __fdiv_rn(c[j * n + k], den);
+        }
+    }
+}
+
+#define MHC_MAX_N 8
+
+// One CTA per token. head_mode: only `pre` gates (scalar scale), no post/comb.
+__global__ void __launch_bounds__(256)
+mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ raw, int d, int n,
+                      int nmix, const float *__restrict__ scale, float head_scale,
+                      const float *__restrict__ base, float norm_eps, float hc_eps, int iters,
+                      int head_mode, const float *__restrict__ norm_w, float rms_eps,
+                      float *__restrict__ pre_out, float *__restrict__ post_out,
+                      float *__restrict__ comb_out, float *__restrict__ y,
+                      float *__restrict__ y_normed) {
+    __shared__ float s_pre[MHC_MAX_N];
+    __shared__ float red[32];
+    const int row = blockIdx.x;
+    const float *rw = raw + (size_t)row * (nmix + 1);
+    if (threadIdx.x == 0) {
+        float mean = __fdiv_rn(rw[nmix], (float)(n * d));
+        float r = __fdiv_rn(1.0f, sqrtf(__fadd_rn(mean, norm_eps)));
+        if (head_mode) {
+            for (int j = 0; j < n; j++) {
+                float m = __fmul_rn(rw[j], r);
+                s_pre[j] = __fadd_rn(sigm(__fadd_rn(__fmul_rn(m, head_scale), base[j])), hc_eps);
+            }
+        } else {
+            float comb[MHC_MAX_N * MHC_MAX_N];
+            for (int j = 0; j < n; j++) {
+                float m = __fmul_rn(rw[j], r);
+                s_pre[j] = __fadd_rn(sigm(__fadd_rn(__fmul_rn(m, scale[0]), base[j])), hc_eps);
+                float m2 = __fmul_rn(rw[n + j], r);
+                float po = __fmul_rn(2.0f, sigm(__fadd_rn(__fmul_rn(m2, scale[1]), base[n + j])));
+                if (post_out) post_out[(size_t)row * n + j] = po;
+            }
+            for (int i = 0; i < n * n; i++) {
+                float m = __fmul_rn(rw[2 * n + i], r);
+                comb[i] = __fadd_rn(__fmul_rn(m, scale[2]), base[2 * n + i]);
+            }
+            sinkhorn(comb, n, iters, hc_eps);
+            if (comb_out)
+                for (int i = 0; i < n * n; i++) comb_out[(size_t)row * n * n + i] = comb[i];
+        }
+        if (pre_out) for (int j = 0; j < n; j++) pre_out[(size_t)row * n + j] = s_pre[j];
+    }
+    __syncthreads();
+    if (!y) return;
+    // collapse: y[i] = sum_j pre[j] * X[j,i], j ascending, mul then add; BF16 round
+    const float *x = x4 + (size_t)row * n * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < n; j++) acc = __fadd_rn(acc, __fmul_rn(s_pre[j], x[(size_t)j * d + i]));
+        acc = bf16_round(acc);
+        y[(size_t)row * d + i] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    if (!y_normed) return;
+    float tot = block_sum(ss, red);
+    float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)d), rms_eps)));
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = y[(size_t)row * d + i];
+        y_normed[(size_t)row * d + i] = bf16_round(__fmul_rn(norm_w[i], __fmul_rn(v, inv)));
+    }
+}
+
+// Y[j,i] = bf16(post[j]*f[i] + sum_k comb[k,j]*R[k,i]) (reference c/mhc.h:259-270,
+// c/layer.h:445-456).
+__global__ void mhc_post_kernel(const float *__restrict__ f, const float *__restrict__ res,
+                                const float *__restrict__ post, const float *__restrict__ comb,
+                                float *__restrict__ y4, int d, int n) {
+    const int row = blockIdx.y;
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= d) return;
+    const float *R = res + (size_t)row * n * d;
+    const float *po = post + (size_t)row * n, *cb = comb + (size_t)row * n * n;
+    float fv = f[(size_t)row * d + i];
+    float rv[MHC_MAX_N];
+    for (int k = 0; k < n; k++) rv[k] = R[(size_t)k * d + i];
+    for (int j = 0; j < n; j++) {
+        float acc = __fmul_rn(po[j], fv);
+        for (int k = 0; k < n; k++) acc = __fadd_rn(acc, __fmul_rn(cb[k * n + j], rv[k]));
+        y4[((size_t)row * n + j) * d + i] = bf16_round(acc);
+    }
+}
+
+static float *g_raw = nullptr;
+static size_t g_raw_cap = 0;
+static int ensure_raw(size_t floats) {
+    if (floats <= g_raw_cap) return 0;
+    if (g_raw) cudaFree(g_raw);
+    g_raw = nullptr; g_raw_cap = 0;
+    APUS_CUDA_OK(cudaMalloc(&g_raw, floats * sizeof(float)));
+    g_raw_cap = floats;
+    return 0;
+}
+
+int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
+            const float *base, float norm_eps, float hc_eps, int iters,
+            const float *norm_w, float rms_eps, float *pre, float *post,
+            float *comb, float *y, float *y_normed, int rows, cudaStream_t st) {
+    APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N && (n * d) % 4 == 0, "mhc: n=%d d=%d unsupported", n, d);
+    if (rows <= 0) return 0;
+    int nmix = (2 + n) * n;
+    if (ensure_raw((size_t)rows * (nmix + 1))) return 1;
+    mhc_mix_kernel<<<dim3(nmix + 1, rows), 256, 0, st>>>(x4, fn, n * d, nmix, g_raw);
+    APUS_LAUNCHED();
+    mhc_pre_finish_kernel<<<rows, 256, 0, st>>>(x4, g_raw, d, n, nmix, scale, 0.f, base,
+                                                norm_eps, hc_eps, iters, 0, norm_w, rms_eps,
+                                                pre, post, comb, y, norm_w ? y_normed : nullptr);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+int mhc_head(const float *x4, int d, int n, const float *fn, float scale,
+             const float *base, float norm_eps, float hc_eps, float *y,
+             int rows, cudaStream_t st) {
+    APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N && (n * d) % 4 == 0, "mhc: n=%d d=%d unsupported", n, d);
+    if (rows <= 0) return 0;
+    if (ensure_raw((size_t)rows * (n + 1))) return 1;
+    mhc_mix_kernel<<<dim3(n + 1, rows), 256, 0, st>>>(x4, fn, n * d, n, g_raw);
+    APUS_LAUNCHED();
+    mhc_pre_finish_kernel<<<rows, 256, 0, st>>>(x4, g_raw, d, n, n, nullptr, scale, base,
+                                                norm_eps, hc_eps, 0, 1, nullptr, 0.f,
+                                                nullptr, nullptr, nullptr, y, nullptr);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+int mhc_post(const float *f, const float *res4, const float *post,
+             const float *comb, float *y4, int d, int n, int rows,
+             cudaStream_t st) {
+    APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N, "mhc: n=%d unsupported", n);
+    if (rows <= 0) return 0;
+    mhc_post_kernel<<<dim3(ceil_div(d, 256), rows), 256, 0, st>>>(f, res4, post, comb, y4, d, n);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+}  // namespace apus

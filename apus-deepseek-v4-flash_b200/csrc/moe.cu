@@ -1,0 +1,223 @@
+// MoE glue kernels: router finish (sqrtsoftplus, bias, stable top-k / hash,
+// weights), stable grouping of routings by expert, and the ordered combine.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace apus {
+
+// ---- router ---------------------------------------------------------------------
+//
+// One CTA per token, one thread per expert (E <= 1024).  Reference
+// c/moe.h:96-100, 352-367 (scores), c/attn.h:668-687 (stable top-k: strict
+// greater-than, lowest index wins ties, descending order), c/moe.h:383-406
+// (hash lookup; weights from the UNBIASED scores, summed in slot order,
+// w = s / sum * route_scale).
+__global__ void router_finish_kernel(const float *__restrict__ logits,
+                                     const float *__restrict__ bias,
+                                     const int64_t *__restrict__ tid2eid,
+                                     const int64_t *__restrict__ ids, int E, int topk,
+                                     float route_scale, float *__restrict__ sp_out,
+                                     float *__restrict__ biased_out,
+                                     int32_t *__restrict__ idx_out,
+                                     float *__restrict__ wgt_out) {
+    extern __shared__ float s_sp[];          // [E] unbiased scores
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    __shared__ int s_sel[64];
+    const int t = blockIdx.x, e = threadIdx.x;
+    const int lane = e & 31, warp = e >> 5, nwarp = (blockDim.x + 31) >> 5;
+    float sp = 0.f, key = -INFINITY;
+    if (e < E) {
+        float z = logits[(size_t)t * E + e];
+        float soft = z > 20.0f ? z : log1pf(expf(z));
+        sp = sqrtf(soft);
+        s_sp[e] = sp;
+        if (sp_out) sp_out[(size_t)t * E + e] = sp;
+        if (bias) {
+            key = __fadd_rn(sp, bias[e]);
+            if (biased_out) biased_out[(size_t)t * E + e] = key;
+        }
+    }
+    __syncthreads();
+    if (tid2eid) {
+        if (e < topk) s_sel[e] = (int)tid2eid[ids[t] * topk + e];
+    } else {
+        bool used = (e >= E);
+        for (int j = 0; j < topk; j++) {
+            // argmax over unused entries; ties -> lowest index
+            float v = used ? -INFINITY : key;
+            int vi = used ? 0x7fffffff : e;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                int oi = __shfl_xor_sync(0xffffffffu, vi, o);
+                if (ov > v || (ov == v && oi < vi)) { v = ov; vi = oi; }
+            }
+            if (lane == 0) { s_val[warp] = v; s_idx[warp] = vi; }
+            __syncthreads();
+            if (warp == 0) {
+                v = lane < nwarp ? s_val[lane] : -INFINITY;
+                vi = lane < nwarp ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+                for (int o = 16; o; o >>= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                    int oi = __shfl_xor_sync(0xffffffffu, vi, o);
+                    if (ov > v || (ov == v && oi < vi)) { v = ov; vi = oi; }
+                }
+                if (lane == 0) s_sel[j] = vi;
+            }
+            __syncthreads();
+            if (s_sel[j] == e) used = true;
+        }
+    }
+    __syncthreads();
+    if (e == 0) {
+        float sum = 0.f;
+        for (int j = 0; j < topk; j++) sum = __fadd_rn(sum, s_sp[s_sel[j]]);
+        for (int j = 0; j < topk; j++) {
+            idx_out[(size_t)t * topk + j] = s_sel[j];
+            wgt_out[(size_t)t * topk + j] =
+                __fmul_rn(__fdiv_rn(s_sp[s_sel[j]], sum), route_scale);
+        }
+    }
+}
+
+int router_finish(const float *logits, const float *bias, const int64_t *tid2eid,
+                  const int64_t *ids, int s, int E, int topk, float route_scale,
+                  float *sp, float *biased, int32_t *idx, float *wgt,
+                  cudaStream_t st) {
+    APUS_REQUIRE(E <= 1024 && topk <= 64 && topk <= E, "router: E=%d topk=%d unsupported", E, topk);
+    APUS_REQUIRE(bias || tid2eid, "router: neither a selection bias nor a hash table");
+    if (s <= 0) return 0;
+    int threads = ((E + 31) / 32) * 32;
+    if (threads < 64) threads = 64;
+    router_finish_kernel<<<s, threads, E * sizeof(float), st>>>(
+        logits, tid2eid ? nullptr : bias, tid2eid, ids, E, topk, route_scale, sp, biased,
+        idx, wgt);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// ---- grouping -----------------------------------------------------------------------
+//
+// Stable counting sort of the routings by local expert (the reference's
+// counting sort, c/moe.h:465-474), done by one CTA with warp ballots so that
+// rows of one expert keep their (token, slot) order, followed by the work-item
+// table for the two GEMM passes: each expert's rows are cut into runs of at
+// most `chunk` rows.  Routings whose expert is not local are skipped.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ row, int n,
+                 MoeSlab slab, int chunk, int *__restrict__ sorted_pos,
+                 int *__restrict__ sorted_row, GemmGroup *__restrict__ g13,
+                 GemmGroup *__restrict__ g2, int *__restrict__ n_groups, int max_groups) {
+    __shared__ int s_cnt[1024], s_off[1024], s_goff[1024];
+    const int nE = slab.e_hi - slab.e_lo;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    for (int le = warp; le < nE; le += nwarp) {
+        int cnt = 0;
+        for (int base = 0; base < n; base += 32) {
+            int i = base + lane;
+            bool hit = i < n && eid[i] == slab.e_lo + le;
+            cnt += __popc(__ballot_sync(0xffffffffu, hit));
+        }
+        if (lane == 0) s_cnt[le] = cnt;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int off = 0, goff = 0;
+        for (int le = 0; le < nE; le++) {
+            s_off[le] = off; s_goff[le] = goff;
+            off += s_cnt[le];
+            goff += (s_cnt[le] + chunk - 1) / chunk;
+        }
+        *n_groups = goff < max_groups ? goff : max_groups;
+    }
+    __syncthreads();
+    for (int le = warp; le < nE; le += nwarp) {
+        int pos = s_off[le];
+        for (int base = 0; base < n; base += 32) {
+            int i = base + lane;
+            bool hit = i < n && eid[i] == slab.e_lo + le;
+            unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                int p = pos + __popc(m & ((1u << lane) - 1u));
+                sorted_pos[p] = i;
+                sorted_row[p] = row ? row[i] : i;
+            }
+            pos += __popc(m);
+        }
+    }
+    for (int le = tid; le < nE; le += blockDim.x) {
+        int cnt = s_cnt[le], gi = s_goff[le];
+        for (int r = 0; r < cnt && gi < max_groups; r += chunk, gi++) {
+            GemmGroup a, b;
+            a.wa = slab.w1 + (size_t)le * slab.code_stride13;
+            a.sa = slab.s1 + (size_t)le * slab.scale_stride13;
+            a.wb = slab.w3 + (size_t)le * slab.code_stride13;
+            a.sb = slab.s3 + (size_t)le * slab.scale_stride13;
+            a.row0 = s_off[le] + r;
+            a.nrows = min(chunk, cnt - r);
+            b.wa = slab.w2 + (size_t)le * slab.code_stride2;
+            b.sa = slab.s2 + (size_t)le * slab.scale_stride2;
+            b.wb = nullptr; b.sb = nullptr;
+            b.row0 = a.row0; b.nrows = a.nrows;
+            g13[gi] = a; g2[gi] = b;
+        }
+    }
+}
+
+int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int n_rout,
+              const MoeSlab &slab, int chunk, int *sorted_pos, int *sorted_row,
+              GemmGroup *g13, GemmGroup *g2, int *n_groups, int max_groups,
+              cudaStream_t st) {
+    APUS_REQUIRE(slab.e_hi - slab.e_lo <= 1024, "moe_group: more than 1024 local experts");
+    moe_group_kernel<<<1, 1024, 0, st>>>(rout_eid, rout_row, n_rout, slab, chunk, sorted_pos,
+                                         sorted_row, g13, g2, n_groups, max_groups);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// ---- combine ---------------------------------------------------------------------------
+//
+// y[t,i] = sum_j wgt[t,j] * eo[t*topk+j, i], j ascending, each step a rounded
+// multiply then a rounded add (reference c/moe.h:148-158 is compiled without
+// contraction); out = bf16(y + shared) (reference c/moe.h:584-585).
+__global__ void moe_combine_kernel(const float *__restrict__ eo, const float *__restrict__ wgt,
+                                   const float *__restrict__ shared, int topk, int dim,
+                                   float *__restrict__ out, float *__restrict__ routed) {
+    int t = blockIdx.y;
+    int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= dim) return;
+    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < topk; j++) {
+        float w = wgt[(size_t)t * topk + j];
+        float4 v = *reinterpret_cast<const float4 *>(eo + ((size_t)t * topk + j) * dim + i);
+        y.x = __fadd_rn(y.x, __fmul_rn(w, v.x));
+        y.y = __fadd_rn(y.y, __fmul_rn(w, v.y));
+        y.z = __fadd_rn(y.z, __fmul_rn(w, v.z));
+        y.w = __fadd_rn(y.w, __fmul_rn(w, v.w));
+    }
+    if (routed) *reinterpret_cast<float4 *>(routed + (size_t)t * dim + i) = y;
+    if (out) {
+        float4 s = shared ? *reinterpret_cast<const float4 *>(shared + (size_t)t * dim + i)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 o;
+        o.x = bf16_round(__fadd_rn(y.x, s.x));
+        o.y = bf16_round(__fadd_rn(y.y, s.y));
+        o.z = bf16_round(__fadd_rn(y.z, s.z));
+        o.w = bf16_round(__fadd_rn(y.w, s.w));
+        *reinterpret_cast<float4 *>(out + (size_t)t * dim + i) = o;
+    }
+}
+
+int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
+                int topk, int dim, float *out, float *routed, cudaStream_t st) {
+    APUS_REQUIRE(dim % 4 == 0, "moe_combine: dim=%d", dim);
+    if (s <= 0) return 0;
+    dim3 grid((unsigned)ceil_div(dim / 4, 256), (unsigned)s);
+    moe_combine_kernel<<<grid, 256, 0, st>>>(eo, wgt, shared, topk, dim, out, routed);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+}  // namespace apus

@@ -1,0 +1,306 @@
+/*
+ * apus_b200.h — C ABI of libapus_b200.so: the B200 (sm_100a) backend for the
+ * decode/prefill arithmetic of the apus DeepSeek-V4-Flash engine.
+ *
+ * Two tiers, both plain C (pointers + sizes, no C++/torch types):
+ *
+ *  1. HOST-POINTER tier — drop-in twins of the reference's backend plugin table
+ *     and of the kernel/sublayer functions it calls.  Every buffer is
+ *     caller-owned host memory, results are in the host `out` buffer on return
+ *     (synchronous), weights are uploaded once and cached by host address.
+ *     Same names (apus_cuda_* for apus_metal_* / apus_*), argument meaning and
+ *     error convention as the reference: 0 = result produced, nonzero =
+ *     failed (message in apus_cuda_last_error()).  There is NO CPU fallback
+ *     inside this library: without a usable CUDA device every call fails.
+ *
+ *  2. DEVICE-RESIDENT tier (`*_dev`) — the same operators on device pointers and
+ *     a caller-supplied CUDA stream (passed as void*), asynchronous, no
+ *     host<->device copies.  This is what a fused token loop and the
+ *     expert-parallel multi-GPU path are built from.
+ *
+ * Each declaration cites the reference interface it replaces as
+ * `file:line` relative to the reference project root.
+ *
+ * Data formats (reference c/st.h:88-89, c/fp4.h:8-11, c/fp8.h:11-14):
+ *   MXFP4 weight  packed u8 [O, K/2] row-major, low nibble = even K; E2M1 codes
+ *                 scales u8 [O, K/32] UE8M0 (value 2^(b-127))
+ *   FP8 weight    codes  u8 [O, K] E4M3; scales u8 [ceil(O/128), ceil(K/128)] UE8M0
+ *   activations   f32 carrying BF16 values; quantised per token per 128 along K
+ *                 to E4M3 codes with a power-of-two f32 scale
+ */
+#ifndef APUS_B200_H
+#define APUS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- types shared with the reference (layout-identical) ------------------ */
+
+#ifndef APUS_ST_H
+/* c/st.h:88 */
+typedef struct { const uint8_t *codes, *scales; int64_t O, K; } ApusFp8W;
+/* c/st.h:89 */
+typedef struct { const uint8_t *packed, *scales; int64_t O, K; } ApusFp4W;
+#endif
+
+#ifndef APUS_MOE_H
+/* c/moe.h:37-63 */
+typedef struct {
+    int E, topk, inter, dim, hash;
+    float route_scale, limit;
+    const float *gate_w;      /* [E, dim] BF16-valued f32 */
+    const float *gate_bias;   /* [E] f32, NULL when hash */
+    const int64_t *tid2eid;   /* [vocab, topk], NULL unless hash */
+    ApusFp4W *w1, *w2, *w3;   /* [E] routed experts (MXFP4) */
+    ApusFp8W sw1, sw2, sw3;   /* shared expert (FP8) */
+    void *hook_ctx;
+    int  (*hook_resolve)(void *ctx, int layer, int eid,
+                         ApusFp4W *w1, ApusFp4W *w2, ApusFp4W *w3);
+    void (*hook_hint)(void *ctx, int layer, int eid);
+    void (*hook_layer_end)(void *ctx, int layer);
+    void *hook_hint_ctx;
+    void *hook_layer_end_ctx;
+    int layer_id;
+} ApusMoeW;
+
+/* c/moe.h:67-71 — optional named intermediates (NULL members are skipped). */
+typedef struct {
+    float *router_scores, *router_scores_biased, *router_w;
+    int32_t *router_idx;
+    float *moe_routed, *moe_shared;
+} ApusMoeInterm;
+#endif
+
+#ifndef APUS_FP4_H
+/* c/fp4.h:184-188 — one entry of a grouped MXFP4 GEMM. */
+typedef struct {
+    const uint8_t *w, *ws;   /* [O, K/2] / [O, K/32] */
+    float *out;              /* [M, O] row-major */
+    size_t m0, M;            /* rows [m0, m0+M) of the shared activation space */
+} ApusFp4GemmEnt;
+#endif
+
+/* c/backend_metal.h:57-61 — f32_linear flags. */
+#define APUS_CUDA_R_IN   1   /* BF16-round the input elements */
+#define APUS_CUDA_R_OUT  2   /* BF16-round the outputs */
+#define APUS_CUDA_W_BF16 4   /* w points at BF16 bits (u16), not f32 */
+
+/* c/backend_metal.h:73-80 — the plugin table.  head_gemv's first argument is
+ * the reference's ApusStTensor*; only its dtype/data members are read (see
+ * apus_cuda_fill_hooks). */
+typedef struct {
+    int (*fp8_linear)(const ApusFp8W *w, const float *x, float *out,
+                      int M, int K, int O);
+    int (*f32_linear)(const float *w, const float *x, float *out,
+                      int M, int K, int O, int flags);
+    int (*head_gemv)(const void *head_sttensor, const float *x, float *out,
+                     int64_t O, int64_t K);
+} ApusCudaHooks;
+
+/* ---- lifecycle (c/backend_metal.h:88-97) ---------------------------------- */
+
+/* c/backend_metal.h:88 apus_metal_enable. Selects the current CUDA device,
+ * creates the backend stream and workspace. Idempotent. */
+int  apus_cuda_enable(char *err, size_t errcap);
+/* c/backend_metal.h:90 apus_metal_disable. Drops the weight cache and frees
+ * all device memory held by the host-pointer tier. */
+void apus_cuda_disable(void);
+/* c/backend_metal.h:91 */
+int  apus_cuda_is_enabled(void);
+/* c/backend_metal.h:96 — weight bytes uploaded into the device cache. */
+uint64_t apus_cuda_bytes_uploaded(void);
+/* c/backend_metal.h:97 — kernels launched by this library since load. */
+uint64_t apus_cuda_dispatches(void);
+/* Fills the three hook slots (c/backend_metal.h:73-80; the assignment done by
+ * apus_metal_enable at c/backend_metal.mm:738). `struct_dtype_off` and
+ * `struct_data_off` are offsetof(ApusStTensor, dtype) / offsetof(.., data) in
+ * the caller's build, so this library need not know that struct. */
+int  apus_cuda_fill_hooks(ApusCudaHooks *hooks, size_t struct_dtype_off,
+                          size_t struct_data_off);
+/* Message of the most recent failure on the calling thread ("" if none). */
+const char *apus_cuda_last_error(void);
+/* Forget the cached device copy of a weight buffer (the reference frees and
+ * reuses host addresses between tests, tests/m7b/README.md:90-94). */
+void apus_cuda_forget(const void *host_ptr);
+
+/* ---- host-pointer tier: kernel-level entry points ------------------------- */
+
+/* c/backend_metal.h:102 apus_metal_fp8_linear == c/attn.h:408 apus_fp8_linear:
+ * BF16-round x, per-128 act quant, block-scaled FP8 GEMM, BF16-rounded out. */
+int apus_cuda_fp8_linear(const ApusFp8W *w, const float *x, float *out,
+                         int M, int K, int O);
+/* c/attn.h:432 apus_fp4_linear (no reference hook exists for it). */
+int apus_cuda_fp4_linear(const ApusFp4W *w, const float *x, float *out,
+                         int M, int K, int O);
+/* c/backend_metal.h:104 apus_metal_f32_linear == c/attn.h:621/652
+ * apus_bf16_linear / apus_f32_linear and the wo_a groups (c/attn.h:1698). */
+int apus_cuda_f32_linear(const float *w, const float *x, float *out,
+                         int M, int K, int O, int flags);
+/* c/backend_metal.h:106 apus_metal_head_gemv_bf16 == c/model.h:638. */
+int apus_cuda_head_gemv_bf16(const void *w_bf16, const float *x, float *out,
+                             int64_t O, int64_t K);
+/* c/backend_metal.h:110 apus_metal_fp8_gemm == c/fp8.h:136 apus_fp8_gemm_mt:
+ * pre-quantised activations, unrounded f32 out. */
+int apus_cuda_fp8_gemm(const uint8_t *w, const uint8_t *ws,
+                       const uint8_t *acodes, const float *as, float *out,
+                       int M, int O, int K);
+/* c/fp4.h:166 apus_fp4_gemm_mt: pre-quantised activations, unrounded out. */
+int apus_cuda_fp4_gemm(const uint8_t *w, const uint8_t *ws,
+                       const uint8_t *acodes, const float *as, float *out,
+                       int M, int O, int K);
+/* c/fp4.h:190 apus_fp4_gemm_mt_grouped: several same-(O,K) GEMMs sharing one
+ * activation row space of `rows` rows (rows = max(m0+M) over the entries). */
+int apus_cuda_fp4_gemm_grouped(const ApusFp4GemmEnt *ents, size_t n_ent,
+                               const uint8_t *acodes, const float *as,
+                               size_t rows, size_t O, size_t K);
+/* c/backend_metal.h:115 apus_metal_fp8_act_quant == c/attn.h:393 row worker:
+ * BF16 round + per-128 E4M3 quant. codes [M,K], scales [M, ceil(K/128)]. */
+int apus_cuda_fp8_act_quant(const float *x, int M, int K,
+                            uint8_t *codes, float *scales);
+/* c/backend_metal.h:118 apus_metal_rmsnorm == c/attn.h:371 apus_rms_norm,
+ * extended to `rows` independent rows of n (rows = 1 is the reference call). */
+int apus_cuda_rmsnorm(const float *x, const float *w, float eps, float *y,
+                      int64_t n, int64_t rows);
+/* c/moe.h:333 apus_expert (static there) for `rows` tokens: SwiGLU FFN with
+ * the limit clamps; kind 0 = MXFP4 (ApusFp4W*), 1 = FP8 (ApusFp8W*). */
+int apus_cuda_expert(const void *w1, const void *w2, const void *w3, int kind,
+                     float limit, const float *x, int rows, int dim, int inter,
+                     float *out);
+/* c/attn.h:668 apus_topk_stable for `rows` independent rows of n: strict
+ * greater-than selection, lowest index wins ties, descending order out. */
+int apus_cuda_topk_stable(const float *row, int n, int k, int32_t *idx,
+                          int rows);
+
+/* ---- host-pointer tier: sublayer entry points ------------------------------ */
+
+/* c/moe.h:77 apus_router_score. */
+int apus_cuda_router_score(const ApusMoeW *w, const float *x, int s,
+                           float *sp, float *biased);
+/* c/moe.h:82 apus_moe_forward. Expert weights are taken from w->w1/w2/w3 or,
+ * when w->hook_resolve is set, resolved through it once per expert and
+ * cached (the resolve/hint/layer_end hooks are storage tiering in the
+ * reference; here every resolved expert stays resident in HBM). */
+int apus_cuda_moe_forward(const ApusMoeW *w, const float *x,
+                          const int64_t *ids, int s, float *out,
+                          ApusMoeInterm *interm);
+/* c/attn.h:1308 apus_sparse_attn (static there): index-gathered attention with
+ * BF16 softmax numerator and the per-head sink in the denominator. */
+int apus_cuda_sparse_attn(const float *q, const float *sink, int h, int d,
+                          const int32_t *idxs, int idxw, int s, float scale,
+                          const float *kv_a, int64_t na, const float *kv_b,
+                          int64_t nb, float *o);
+/* c/mhc.h:103 apus_mhc_prepost_scalar for `rows` tokens (x4 [rows, n*d]). */
+int apus_cuda_mhc_prepost(const float *x4, size_t d, size_t n,
+                          const float *fn, const float *scale,
+                          const float *base, float norm_eps, float hc_eps,
+                          int iters, float *pre, float *post, float *comb,
+                          int rows);
+/* c/layer.h:401 apus_hc_pre_rows: mHC pre maps + collapse (c/mhc.h:110) + BF16
+ * round, optionally followed by RMSNorm (c/attn.h:371) in the same kernel
+ * when norm_w != NULL.  y [rows, d]; post [rows,n], comb [rows,n,n] out. */
+int apus_cuda_hc_pre(const float *x4, size_t d, size_t n, const float *fn,
+                     const float *scale, const float *base, float norm_eps,
+                     float hc_eps, int iters, const float *norm_w,
+                     float rms_eps, float *y, float *y_normed, float *post,
+                     float *comb, int rows);
+/* c/layer.h:445 apus_hc_post_rows: c/mhc.h:116 apply + BF16 round. */
+int apus_cuda_hc_post(const float *f, const float *res4, const float *post,
+                      const float *comb, float *y4, size_t d, size_t n,
+                      int rows);
+/* c/mhc.h:123 apus_mhc_head_scalar (+ BF16 round as c/model.h:711). */
+int apus_cuda_hc_head(const float *x4, size_t d, size_t n, const float *fn,
+                      float scale, const float *base, float norm_eps,
+                      float hc_eps, float *y, int rows);
+
+/* ---- device-resident tier --------------------------------------------------- */
+
+/* Quantised-weight handles living in HBM. */
+typedef struct ApusCudaFp4 ApusCudaFp4;   /* one MXFP4 matrix */
+typedef struct ApusCudaFp8 ApusCudaFp8;   /* one FP8 matrix */
+typedef struct ApusCudaMoe ApusCudaMoe;   /* one MoE sublayer (local experts) */
+
+/* Upload the experts [e_lo, e_hi) of a MoE sublayer plus its gate and shared
+ * expert (c/moe.h:37-63 describes the fields) into HBM.  e_lo/e_hi implement
+ * the contiguous expert-parallel partition (expert e lives on rank
+ * e / (E / world)).  Returns NULL on failure. */
+ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi);
+void apus_cuda_moe_destroy(ApusCudaMoe *m);
+/* Bytes of expert + dense weights resident for this sublayer. */
+uint64_t apus_cuda_moe_bytes(const ApusCudaMoe *m);
+/* Hash-routed layers (c/moe.h:42, 391-394): place the tid2eid table
+ * [vocab, topk] in HBM so that apus_cuda_moe_route_dev / _forward_dev can look
+ * token ids up on device.  (The host-pointer apus_cuda_moe_forward does not
+ * need it: it reads w->tid2eid on the host.) */
+int apus_cuda_moe_set_hash_table(ApusCudaMoe *m, const int64_t *tid2eid,
+                                 int64_t vocab);
+
+/* c/moe.h:352-412 on device: gate matmul, sqrtsoftplus, bias, stable top-k or
+ * hash lookup, normalised weights.  x [s,dim] f32; ids [s] i64 (hash layers,
+ * else may be NULL); idx [s,topk] i32 and wgt [s,topk] f32 out; sp/biased
+ * [s,E] optional (NULL to skip). */
+int apus_cuda_moe_route_dev(const ApusCudaMoe *m, const float *x,
+                            const int64_t *ids, int s, int32_t *idx,
+                            float *wgt, float *sp, float *biased,
+                            void *stream);
+/* c/moe.h:435-563 on device for routings whose expert is local: `n_rout`
+ * (token row, expert) pairs; xrows [n_rows, dim] f32 are the distinct token
+ * rows, rout_row[i] indexes into them, rout_eid[i] is the GLOBAL expert id
+ * (must lie in [e_lo, e_hi)).  eo [n_rout, dim] receives each routing's
+ * BF16-rounded expert output (c/attn.h:447).  Routings may come in any
+ * order; the library groups them by expert internally. */
+int apus_cuda_moe_experts_dev(ApusCudaMoe *m, const float *xrows, int n_rows,
+                              const int32_t *rout_row,
+                              const int32_t *rout_eid, int n_rout, float *eo,
+                              void *stream);
+/* c/moe.h:148-158 + 570-585 on device: y[t] = sum_j wgt[t,j]*eo[t,j] strictly
+ * in j order, shared expert added, BF16 round.  eo [s*topk, dim] in (t,j)
+ * order; `shared` [s,dim] from apus_cuda_moe_shared_dev. */
+int apus_cuda_moe_combine_dev(const ApusCudaMoe *m, const float *eo,
+                              const float *wgt, const float *shared, int s,
+                              float *out, float *routed, void *stream);
+/* c/moe.h:570-581 on device: the FP8 shared expert for s tokens. */
+int apus_cuda_moe_shared_dev(ApusCudaMoe *m, const float *x, int s,
+                             float *shared, void *stream);
+/* The whole sublayer on one GPU (all experts local): route + experts +
+ * shared + combine, c/moe.h:369-595.  x/out device f32 [s,dim]. */
+int apus_cuda_moe_forward_dev(ApusCudaMoe *m, const float *x,
+                              const int64_t *ids, int s, float *out,
+                              void *stream);
+/* Copy back the router decisions of the last *_forward_dev / route call
+ * (device-to-host, synchronises the stream): idx [s,topk], wgt [s,topk]. */
+int apus_cuda_moe_last_routing(ApusCudaMoe *m, int s, int32_t *idx,
+                               float *wgt, void *stream);
+
+/* Single matrices on device (c/attn.h:408-449 semantics). */
+ApusCudaFp4 *apus_cuda_fp4_upload(const ApusFp4W *w);
+ApusCudaFp8 *apus_cuda_fp8_upload(const ApusFp8W *w);
+void apus_cuda_fp4_free(ApusCudaFp4 *w);
+void apus_cuda_fp8_free(ApusCudaFp8 *w);
+int apus_cuda_fp4_linear_dev(const ApusCudaFp4 *w, const float *x, float *out,
+                             int M, void *stream);
+int apus_cuda_fp8_linear_dev(const ApusCudaFp8 *w, const float *x, float *out,
+                             int M, void *stream);
+/* c/moe.h:333 on device, MXFP4 kind: out = w2(swiglu(w1 x, w3 x)). */
+int apus_cuda_expert_fp4_dev(const ApusCudaFp4 *w1, const ApusCudaFp4 *w2,
+                             const ApusCudaFp4 *w3, float limit,
+                             const float *x, int rows, float *out,
+                             void *stream);
+/* c/attn.h:668 on device, `rows` rows of n scores -> idx [rows,k]. */
+int apus_cuda_topk_stable_dev(const float *scores, int n, int k, int32_t *idx,
+                              int rows, void *stream);
+/* c/attn.h:1308 on device. kv_a [na,d] and kv_b [nb,d] are BF16 (u16 bits,
+ * value-identical to the reference's f32-carrying-BF16 caches). */
+int apus_cuda_sparse_attn_dev(const float *q, const float *sink, int h, int d,
+                              const int32_t *idxs, int idxw, int s,
+                              float scale, const uint16_t *kv_a, int64_t na,
+                              const uint16_t *kv_b, int64_t nb, float *o,
+                              void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APUS_B200_H */

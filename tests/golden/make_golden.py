@@ -1,0 +1,170 @@
+#!/usr/bin/env python3
+"""Regenerates the committed golden vectors from the reference itself.
+
+Run in a container where the reference checkout is mounted (default
+/root/reference):
+
+  1. m3/ and m4a/: the reference's OWN golden generators
+     (tests/m3/gen_golden.py, tests/m4a/gen_golden.py; seed 20260729) are
+     imported and run with their output directory redirected here.  These are
+     the known-answer fixtures its C tests check the kernels against.
+  2. ref_cases.npz: outputs of the unmodified reference C code
+     (oracle/_ref/libapus_ref.so) on the seeded cases of tests/cases.py.
+
+Nothing on the GPU box reads the reference checkout; it only reads these files.
+"""
+import ctypes as C
+import importlib.util
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+REF = Path(os.environ.get("APUS_REFERENCE", "/root/reference"))
+
+import cases                                   # noqa: E402
+from _oracle import P, ref                     # noqa: E402
+from apus_b200 import capi                     # noqa: E402
+
+
+def run_reference_generators():
+    for name in ("m3", "m4a"):
+        spec = importlib.util.spec_from_file_location(
+            f"gen_{name}", REF / "tests" / name / "gen_golden.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.OUT = str(HERE / name)
+        os.makedirs(mod.OUT, exist_ok=True)
+        mod.main()
+
+
+def ref_linear(L, fmt, c):
+    M, K = c["x"].shape
+    O = c["codes"].shape[0]
+    out = np.empty((M, O), np.float32)
+    w = capi.qw(c["codes"], c["scales"], O, K)
+    (L.apus_fp4_linear if fmt == 4 else L.apus_fp8_linear)(C.byref(w), P(c["x"]), P(out), M, K, O)
+    xb = np.empty_like(c["x"])
+    codes = np.empty((M, K), np.uint8)
+    scales = np.empty((M, K // 128), np.float32)
+    L.ref_act_quant_rows(P(c["x"]), P(xb), P(codes), P(scales), M, K)
+    raw = np.empty((M, O), np.float32)
+    scratch = np.empty((M, K), np.float32)
+    (L.apus_fp4_gemm_mt if fmt == 4 else L.apus_fp8_gemm_mt)(
+        P(c["codes"]), P(c["scales"]), P(codes), P(scales), P(scratch), P(raw), M, O, K)
+    return dict(out=out, acodes=codes, ascales=scales, raw=raw)
+
+
+def main():
+    L = ref()
+    assert L is not None, "reference build not available"
+    run_reference_generators()
+    G = {}
+    for tag, args in LINEAR_CASES.items():
+        r = ref_linear(L, args[1], cases.linear_case(*args))
+        for k, v in r.items():
+            G[f"{tag}.{k}"] = v
+    for tag, args in EXPERT_CASES.items():
+        c = cases.expert_case(*args)
+        _, kind, rows, dim, inter = args
+        out = np.empty((rows, dim), np.float32)
+        w1, w2, w3 = capi.qw(*c["w1"], inter, dim), capi.qw(*c["w2"], dim, inter), capi.qw(*c["w3"], inter, dim)
+        for t in range(rows):                 # the reference's expert is per token
+            L.ref_expert(C.byref(w1), C.byref(w2), C.byref(w3), kind, 10.0,
+                         P(c["x"][t]), dim, inter, P(out[t]))
+        G[f"{tag}.out"] = out
+    for tag, kw in MOE_CASES.items():
+        W, x, ids = cases.moe_case(**kw)
+        s = x.shape[0]
+        w = W.moew()
+        out = np.empty((s, W.dim), np.float32)
+        sp = np.empty((s, W.E), np.float32)
+        biased = np.zeros((s, W.E), np.float32)
+        rw = np.empty((s, W.topk), np.float32)
+        ri = np.empty((s, W.topk), np.int32)
+        routed = np.empty((s, W.dim), np.float32)
+        shared = np.empty((s, W.dim), np.float32)
+        it = capi.MoeInterm(P(sp), P(biased), P(rw), P(ri), P(routed), P(shared))
+        L.apus_moe_forward(C.byref(w), P(x), P(ids), s, P(out), C.byref(it))
+        G.update({f"{tag}.out": out, f"{tag}.sp": sp, f"{tag}.biased": biased, f"{tag}.w": rw,
+                  f"{tag}.idx": ri, f"{tag}.routed": routed, f"{tag}.shared": shared})
+    for tag, args in TOPK_CASES.items():
+        sc = cases.topk_case(*args)
+        rows, n = sc.shape
+        k = args[3]
+        idx = np.empty((rows, k), np.int32)
+        for r in range(rows):
+            L.apus_topk_stable(P(sc[r]), n, k, P(idx[r]))
+        G[f"{tag}.idx"] = idx
+    for tag, args in ATTN_CASES.items():
+        c = cases.sparse_attn_case(*args)
+        _, s, h, d, na, nb, idxw, _ = args
+        o = np.empty((s, h, d), np.float32)
+        L.ref_sparse_attn(P(c["q"]), P(c["sink"]), h, d, P(c["idx"]), idxw, s, d ** -0.5,
+                          P(c["kv_a"]), na, P(c["kv_b"]), P(o))
+        G[f"{tag}.o"] = o
+    for tag, args in MHC_CASES.items():
+        c = cases.mhc_case(*args)
+        _, rows, d = args
+        n = 4
+        pre = np.empty((rows, n), np.float32)
+        post = np.empty((rows, n), np.float32)
+        comb = np.empty((rows, n, n), np.float32)
+        y = np.empty((rows, d), np.float32)
+        y4 = np.empty((rows, n, d), np.float32)
+        yh = np.empty((rows, d), np.float32)
+        for t in range(rows):
+            L.apus_mhc_prepost_scalar(P(c["x4"][t]), d, n, P(c["fn"]), P(c["scale"]), P(c["base"]),
+                                      1e-6, 1e-6, 20, P(pre[t]), P(post[t]), P(comb[t]), None)
+            L.apus_mhc_collapse_scalar(P(c["x4"][t]), P(pre[t]), P(y[t]), d, n)
+            L.apus_mhc_apply_scalar(P(c["f"][t]), P(c["x4"][t]), P(post[t]), P(comb[t]), P(y4[t]), d, n)
+            L.apus_mhc_head_scalar(P(c["x4"][t]), d, n, P(c["hfn"]), 0.8, P(c["hbase"]), 1e-6, 1e-6,
+                                   P(yh[t]), None)
+        yn = np.empty((rows, d), np.float32)
+        from apus_b200.synth import bf16_round
+        yb = bf16_round(y)
+        for t in range(rows):
+            L.apus_rms_norm(P(yb[t]), P(c["norm_w"]), 1e-6, P(yn[t]), d)
+        G.update({f"{tag}.pre": pre, f"{tag}.post": post, f"{tag}.comb": comb, f"{tag}.y": y,
+                  f"{tag}.y4": y4, f"{tag}.yhead": yh, f"{tag}.ynorm": yn})
+    np.savez_compressed(HERE / "ref_cases.npz", **G)
+    print(f"wrote {len(G)} arrays; avx2 hits {L.ref_avx2_hits()}, threads {L.ref_pool_threads()}")
+
+
+# tag -> arguments of the case builders in tests/cases.py
+LINEAR_CASES = {
+    "fp4_small": (11, 4, 3, 64, 256, True),
+    "fp4_wide": (12, 4, 9, 256, 1024, False),
+    "fp8_small": (13, 8, 8, 320, 384, True),
+    "fp8_wide": (14, 8, 5, 256, 1024, False),
+}
+EXPERT_CASES = {
+    "expert_fp4": (21, 0, 3, 256, 128),
+    "expert_fp8": (22, 1, 3, 256, 128),
+}
+MOE_CASES = {
+    "moe_bias": dict(seed=31, s=5),
+    "moe_hash": dict(seed=32, s=4, hash_vocab=50),
+    "moe_one": dict(seed=33, s=1),
+    "moe_many": dict(seed=34, s=70, E=8, topk=2),
+}
+TOPK_CASES = {
+    "topk_plain": (41, 3, 300, 6, False),
+    "topk_ties": (42, 3, 2000, 512, True),
+    "topk_all": (43, 2, 64, 64, True),
+}
+ATTN_CASES = {
+    "attn_holes": (51, 3, 4, 64, 16, 40, 24, "holes"),
+    "attn_empty": (52, 2, 2, 64, 8, 8, 12, "empty"),
+    "attn_dups": (53, 2, 3, 128, 0, 50, 33, "dups"),
+    "attn_full": (54, 1, 2, 64, 128, 30, 140, "full"),
+}
+MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
+
+if __name__ == "__main__":
+    main()
