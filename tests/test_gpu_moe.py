@@ -1,0 +1,133 @@
+"""GPU parity: router, experts and the whole MoE sublayer through the C ABI
+against the CPU oracle and the committed reference outputs.
+
+Bars: router top-k indices bit-exact except at documented ties (a mismatch is
+excused only when the reference's own gap between the last selected and the
+first rejected biased score is below 1e-5, and is reported); routed / shared /
+final outputs rel-L2 <= 1e-3 on tokens whose selection matches.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+from _gpu import bf16_ulps, bits, cuda_moe, lib
+from _oracle import ora_moe, rel_l2
+from apus_b200 import capi, synth
+from golden.make_golden import MOE_CASES
+
+pytestmark = pytest.mark.gpu
+G = np.load(__import__("pathlib").Path(__file__).resolve().parent / "golden" / "ref_cases.npz")
+TIE_GAP = 1e-5
+
+
+def check_routing(got_idx, ref_idx, ref_biased):
+    """Returns the mask of tokens whose expert selection matches; asserts that
+    every mismatch is a documented near-tie."""
+    same = np.all(got_idx == ref_idx, axis=1)
+    for t in np.nonzero(~same)[0]:
+        srt = np.sort(ref_biased[t])[::-1]
+        k = ref_idx.shape[1]
+        gaps = np.abs(np.diff(srt[:k + 1]))
+        assert gaps.min() <= TIE_GAP, f"token {t}: selection differs without a near-tie (gaps {gaps})"
+        print(f"documented tie: token {t} min gap {gaps.min():.3g}")
+    return same
+
+
+@pytest.mark.parametrize("tag", list(MOE_CASES))
+def test_moe_vs_reference_outputs(tag):
+    W, x, ids = cases.moe_case(**MOE_CASES[tag])
+    r = cuda_moe(W, x, ids)
+    if W.tid2eid is None:
+        same = check_routing(r["idx"], G[f"{tag}.idx"], G[f"{tag}.biased"])
+        assert rel_l2(r["biased"], G[f"{tag}.biased"]) <= 1e-6
+    else:
+        assert np.array_equal(r["idx"], G[f"{tag}.idx"])
+        same = np.ones(x.shape[0], bool)
+    assert same.mean() >= 0.9
+    assert rel_l2(r["sp"], G[f"{tag}.sp"]) <= 1e-6
+    assert rel_l2(r["w"][same], G[f"{tag}.w"][same]) <= 1e-5
+    assert rel_l2(r["shared"], G[f"{tag}.shared"]) <= 1e-3
+    assert rel_l2(r["routed"][same], G[f"{tag}.routed"][same]) <= 1e-3
+    assert rel_l2(r["out"][same], G[f"{tag}.out"][same]) <= 1e-3
+
+
+@pytest.mark.parametrize("s", [1, 32])
+def test_moe_layer_flash_dims(s):
+    """Config 2 at V4-Flash dimensions with a reduced expert count (32) so that
+    the CPU oracle finishes in seconds; s = 1 and 32 decode tokens."""
+    W = synth.MoeWeights(seed=200 + s, E=32, topk=6)
+    rng = np.random.default_rng(s)
+    x = synth.activations(rng, s, W.dim)
+    want = ora_moe(W, x)
+    r = cuda_moe(W, x)
+    same = np.all(r["idx"] == want[1], axis=1)
+    assert same.mean() >= 0.9
+    assert rel_l2(r["out"][same], want[0][same]) <= 1e-3
+    assert rel_l2(r["routed"][same], want[3][same]) <= 1e-3
+    assert rel_l2(r["shared"], want[4]) <= 1e-3
+    # determinism: same bits on a second run
+    r2 = cuda_moe(W, x)
+    assert np.array_equal(bits(r["out"]), bits(r2["out"]))
+
+
+def test_moe_batched_equals_per_token():
+    """s tokens in one call == s single-token calls, bitwise (reference
+    tests/m9e/test_m9e.c:278-330)."""
+    W, x, _ = cases.moe_case(seed=91, s=9, E=8, topk=2)
+    full = cuda_moe(W, x)["out"]
+    for t in (0, 4, 8):
+        one = cuda_moe(W, x[t:t + 1].copy())["out"]
+        assert np.array_equal(bits(one[0]), bits(full[t]))
+
+
+def test_router_score_entry_point():
+    W, x, _ = cases.moe_case(seed=31, s=5)
+    w = W.moew()
+    sp = np.empty((5, W.E), np.float32)
+    biased = np.empty((5, W.E), np.float32)
+    assert lib().apus_cuda_router_score(C.byref(w), capi.ptr(x), 5, capi.ptr(sp), capi.ptr(biased)) == 0
+    assert rel_l2(sp, G["moe_bias.sp"]) <= 1e-6
+    assert rel_l2(biased, G["moe_bias.biased"]) <= 1e-6
+
+
+def test_expert_parallel_split_equals_whole():
+    """Experts split over two 'ranks' (two handles on one GPU, e_lo/e_hi) and
+    recombined in (t, j) order give the same bits as the single-handle run —
+    the invariant the multi-GPU dispatch/combine relies on."""
+    import torch
+    W, x, _ = cases.moe_case(seed=92, s=6, E=8, topk=3)
+    L = lib()
+    w = W.moew()
+    whole = cuda_moe(W, x)
+    dev = torch.device("cuda")
+    xd = torch.from_numpy(x).to(dev)
+    s, topk, dim, E = 6, W.topk, W.dim, W.E
+    idx = torch.from_numpy(whole["idx"]).to(dev).reshape(-1).contiguous()
+    wgt = torch.from_numpy(whole["w"]).to(dev).contiguous()
+    rows = torch.arange(s, device=dev, dtype=torch.int32).repeat_interleave(topk).contiguous()
+    eo = torch.zeros(s * topk, dim, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    hs = []
+    for lo, hi in ((0, E // 2), (E // 2, E)):
+        h = L.apus_cuda_moe_create(C.byref(w), lo, hi)
+        assert h
+        hs.append(h)
+        sel = torch.nonzero((idx >= lo) & (idx < hi)).reshape(-1)
+        n = int(sel.numel())
+        eo_part = torch.zeros(max(n, 1), dim, device=dev)
+        r_sel = rows[sel].contiguous()
+        e_sel = idx[sel].contiguous()
+        assert L.apus_cuda_moe_experts_dev(h, xd.data_ptr(), s, r_sel.data_ptr(), e_sel.data_ptr(), n,
+                                           eo_part.data_ptr(), st) == 0
+        eo[sel] = eo_part[:n]
+    shared = torch.zeros(s, dim, device=dev)
+    out = torch.zeros(s, dim, device=dev)
+    assert L.apus_cuda_moe_shared_dev(hs[0], xd.data_ptr(), s, shared.data_ptr(), st) == 0
+    assert L.apus_cuda_moe_combine_dev(hs[0], eo.data_ptr(), wgt.data_ptr(), shared.data_ptr(), s,
+                                       out.data_ptr(), None, st) == 0
+    torch.cuda.synchronize()
+    for h in hs:
+        L.apus_cuda_moe_destroy(h)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(whole["out"]))
