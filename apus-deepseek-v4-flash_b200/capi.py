@@ -129,6 +129,9 @@ def load(path=LIB_PATH):
         "apus_cuda_moe_destroy": (None, [vp]),
         "apus_cuda_moe_bytes": (C.c_uint64, [vp]),
         "apus_cuda_moe_set_hash_table": (ci, [vp, vp, i64]),
+        "apus_cuda_moe_get": (vp, [C.POINTER(MoeW)]),
+        "apus_cuda_moe_timing": (None, [vp, ci]),
+        "apus_cuda_moe_timing_read": (ci, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(ci)]),
         "apus_cuda_moe_route_dev": (ci, [vp, vp, vp, ci, vp, vp, vp, vp, vp]),
         "apus_cuda_moe_experts_dev": (ci, [vp, vp, ci, vp, vp, ci, vp, vp]),
         "apus_cuda_moe_combine_dev": (ci, [vp, vp, vp, vp, ci, vp, vp, vp]),

@@ -32,8 +32,24 @@ struct ApusCudaMoe {
     DevBuf b_logits, b_sp, b_biased, b_idx, b_wgt, b_xq, b_xs, b_routrow, b_spos, b_srow,
         b_g13, b_g2, b_ng, b_h, b_hq, b_hs, b_eo, b_shared, b_sh_h, b_sh_hq, b_sh_hs, b_ids,
         b_tab;
+    // optional per-kernel timing of the two expert GEMM launches
+    bool timing = false;
+    std::vector<cudaEvent_t> ev;
+    size_t ev_used = 0;
     int ensure(int s, int n_rout);
+    int mark(cudaStream_t st);
 };
+
+int ApusCudaMoe::mark(cudaStream_t st) {
+    if (!timing) return 0;
+    if (ev_used == ev.size()) {
+        cudaEvent_t e;
+        APUS_CUDA_OK(cudaEventCreate(&e));
+        ev.push_back(e);
+    }
+    APUS_CUDA_OK(cudaEventRecord(ev[ev_used++], st));
+    return 0;
+}
 
 int ApusCudaMoe::ensure(int s, int n_rout) {
     const size_t S = (size_t)(s > 0 ? s : 1), R = (size_t)(n_rout > 0 ? n_rout : 1);
@@ -92,7 +108,7 @@ static int experts_run(ApusCudaMoe *m, const float *xrows, int n_rows, const int
     a.acodes = m->b_xq.as<uint8_t>(); a.ascales = m->b_xs.as<float>();
     a.arow = m->b_srow.as<int>(); a.orow = nullptr; a.out = m->b_h.as<float>();
     a.zero_scale = m->zero_scale;
-    if (gemm_small(a, st)) return 1;
+    if (m->mark(st) || gemm_small(a, st) || m->mark(st)) return 1;
     // h rows are in sorted order; rows past the local routings are never read
     if (act_quant(m->b_h.as<float>(), nullptr, n_rout, inter, m->b_hq.as<uint8_t>(),
                   m->b_hs.as<float>(), nullptr, st))
@@ -104,7 +120,8 @@ static int experts_run(ApusCudaMoe *m, const float *xrows, int n_rows, const int
     b.acodes = m->b_hq.as<uint8_t>(); b.ascales = m->b_hs.as<float>();
     b.arow = nullptr; b.orow = m->b_spos.as<int>(); b.out = eo;
     b.zero_scale = m->zero_scale;
-    return gemm_small(b, st);
+    if (m->mark(st) || gemm_small(b, st) || m->mark(st)) return 1;
+    return 0;
 }
 
 static int shared_run(ApusCudaMoe *m, const float *x, int s, float *shared, cudaStream_t st) {
@@ -239,10 +256,47 @@ void apus_cuda_moe_destroy(ApusCudaMoe *m) {
                       &m->b_hq, &m->b_hs, &m->b_eo, &m->b_shared, &m->b_sh_h, &m->b_sh_hq,
                       &m->b_sh_hs, &m->b_ids, &m->b_tab};
     for (DevBuf *b : bufs) b->release();
+    for (cudaEvent_t e : m->ev) cudaEventDestroy(e);
     delete m;
 }
 
 uint64_t apus_cuda_moe_bytes(const ApusCudaMoe *m) { return m ? m->weight_bytes : 0; }
+
+ApusCudaMoe *apus_cuda_moe_get(const ApusMoeW *w) {
+    if (ensure_enabled()) return nullptr;
+    Ctx &c = ctx();
+    auto it = c.moes.find(w->gate_w);
+    if (it != c.moes.end()) return it->second;
+    ApusCudaMoe *m = apus_cuda_moe_create(w, 0, w->E);
+    if (m) c.moes[w->gate_w] = m;
+    return m;
+}
+
+void apus_cuda_moe_timing(ApusCudaMoe *m, int enable) {
+    if (!m) return;
+    m->timing = enable != 0;
+    m->ev_used = 0;
+}
+
+int apus_cuda_moe_timing_read(ApusCudaMoe *m, double *ms_gate_up, double *ms_down, int *launches) {
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    double a = 0, b = 0;
+    int n = 0;
+    for (size_t i = 0; i + 3 < m->ev_used; i += 4) {
+        float t;
+        APUS_CUDA_OK(cudaEventSynchronize(m->ev[i + 3]));
+        APUS_CUDA_OK(cudaEventElapsedTime(&t, m->ev[i], m->ev[i + 1]));
+        a += t;
+        APUS_CUDA_OK(cudaEventElapsedTime(&t, m->ev[i + 2], m->ev[i + 3]));
+        b += t;
+        n++;
+    }
+    if (ms_gate_up) *ms_gate_up = a;
+    if (ms_down) *ms_down = b;
+    if (launches) *launches = n;
+    m->ev_used = 0;
+    return 0;
+}
 
 int apus_cuda_moe_set_hash_table(ApusCudaMoe *m, const int64_t *tid2eid, int64_t vocab) {
     if (!m || !m->hash) { set_error("set_hash_table: not a hash-routed layer"); return 1; }
@@ -301,14 +355,7 @@ int apus_cuda_moe_last_routing(ApusCudaMoe *m, int s, int32_t *idx, float *wgt, 
 }
 
 // ---- host-pointer tier ----------------------------------------------------------------------------
-static ApusCudaMoe *moe_for(const ApusMoeW *w) {
-    Ctx &c = ctx();
-    auto it = c.moes.find(w->gate_w);
-    if (it != c.moes.end()) return it->second;
-    ApusCudaMoe *m = apus_cuda_moe_create(w, 0, w->E);
-    if (m) c.moes[w->gate_w] = m;
-    return m;
-}
+static ApusCudaMoe *moe_for(const ApusMoeW *w) { return apus_cuda_moe_get(w); }
 
 int apus_cuda_router_score(const ApusMoeW *w, const float *x, int s, float *sp, float *biased) {
     if (ensure_enabled()) return 1;

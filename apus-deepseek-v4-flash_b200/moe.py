@@ -1,0 +1,149 @@
+"""Host side of the MoE sublayer: the reference's operator interface
+(`apus_moe_forward`, c/moe.h:82) on HBM-resident weights, single-GPU and
+expert-parallel.
+
+Expert parallelism (one process per GPU): expert e lives on rank
+e // (E / world) — contiguous blocks, the rule of the vendored reference model
+(reference-0731/inference/model.py:623-626).  Gate, bias and the shared expert
+are replicated.  A step is
+
+    route (local) -> dispatch all-to-all (token rows + expert ids to the ranks
+    that own the experts) -> expert FFNs (local) -> combine all-to-all (expert
+    outputs back to the token's home rank) -> y[t] = sum_j w[t,j]*eo[t,j] in
+    slot order on the home rank + shared expert, BF16 round.
+
+The combine sums on the token's home rank in top-k slot order, so the result
+is bit-identical to the single-GPU run (the reference has no collective;
+its summation order is c/moe.h:148-158).  torch.distributed is only the
+plumbing: NCCL moves the rows, every arithmetic step is a kernel of
+libapus_b200.so.
+"""
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import capi, check, lib
+
+
+def owner_ranks(eids, n_experts, world):
+    """Rank that owns each expert id (contiguous partition)."""
+    return torch.div(eids, n_experts // world, rounding_mode="floor")
+
+
+def dispatch_plan(idx, n_experts, world):
+    """From routing indices idx [s, topk] build the dispatch permutation.
+
+    Returns (order, send_counts): `order` lists the flat routing positions
+    (t*topk + j) grouped by destination rank, stable within a rank; send_counts
+    [world] is how many go to each rank."""
+    flat = idx.reshape(-1)
+    dest = owner_ranks(flat, n_experts, world)
+    order = torch.argsort(dest, stable=True)
+    send_counts = torch.bincount(dest, minlength=world)
+    return order, send_counts
+
+
+def exchange_counts(send_counts, group=None):
+    """All ranks learn how many rows each peer sends them."""
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    return recv_counts
+
+
+class ExpertParallelMoe:
+    """One MoE sublayer sharded over the ranks of a process group.
+
+    `experts_fn(rows, eids) -> outs` computes the routed-expert FFN for each
+    (row, global expert id) pair whose expert is local; by default it is the
+    CUDA library's apus_cuda_moe_experts_dev.  Tests inject a CPU stand-in to
+    exercise the exchange logic over gloo."""
+
+    def __init__(self, n_experts, topk, dim, rank=0, world=1, group=None, handle=None,
+                 experts_fn=None, route_fn=None, shared_fn=None, combine_fn=None):
+        assert n_experts % world == 0, "experts must divide evenly over the ranks"
+        self.E, self.topk, self.dim = n_experts, topk, dim
+        self.rank, self.world, self.group = rank, world, group
+        self.handle = handle
+        self.e_lo = rank * (n_experts // world)
+        self.e_hi = self.e_lo + n_experts // world
+        self.experts_fn = experts_fn or self._experts_cuda
+        self.route_fn = route_fn or self._route_cuda
+        self.shared_fn = shared_fn or self._shared_cuda
+        self.combine_fn = combine_fn or self._combine_cuda
+
+    # ---- CUDA-library steps (device tensors, current stream) -----------------------
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def _route_cuda(self, x, ids):
+        s = x.shape[0]
+        idx = torch.empty(s, self.topk, dtype=torch.int32, device=x.device)
+        wgt = torch.empty(s, self.topk, dtype=torch.float32, device=x.device)
+        check(lib().apus_cuda_moe_route_dev(self.handle, x.data_ptr(),
+                                            ids.data_ptr() if ids is not None else None, s,
+                                            idx.data_ptr(), wgt.data_ptr(), None, None,
+                                            self._stream()), "moe_route_dev")
+        return idx, wgt
+
+    def _experts_cuda(self, rows, eids):
+        n = rows.shape[0]
+        out = torch.empty(max(n, 1), self.dim, dtype=torch.float32, device=rows.device)
+        if n:
+            rr = torch.arange(n, dtype=torch.int32, device=rows.device)
+            check(lib().apus_cuda_moe_experts_dev(self.handle, rows.data_ptr(), n, rr.data_ptr(),
+                                                  eids.data_ptr(), n, out.data_ptr(),
+                                                  self._stream()), "moe_experts_dev")
+        return out[:n]
+
+    def _shared_cuda(self, x):
+        out = torch.empty_like(x)
+        check(lib().apus_cuda_moe_shared_dev(self.handle, x.data_ptr(), x.shape[0], out.data_ptr(),
+                                             self._stream()), "moe_shared_dev")
+        return out
+
+    def _combine_cuda(self, eo, wgt, shared):
+        s = wgt.shape[0]
+        out = torch.empty(s, self.dim, dtype=torch.float32, device=eo.device)
+        check(lib().apus_cuda_moe_combine_dev(self.handle, eo.data_ptr(), wgt.data_ptr(),
+                                              shared.data_ptr(), s, out.data_ptr(), None,
+                                              self._stream()), "moe_combine_dev")
+        return out
+
+    # ---- one sublayer step -------------------------------------------------------------
+    def forward(self, x, ids=None):
+        """x [s, dim] f32 (BF16-valued) on this rank's device -> out [s, dim]."""
+        s = x.shape[0]
+        idx, wgt = self.route_fn(x, ids)
+        if self.world == 1:
+            rows = torch.arange(s, device=x.device).repeat_interleave(self.topk)
+            eo = self.experts_fn(x[rows].contiguous(), idx.reshape(-1).contiguous())
+            return self.combine_fn(eo.contiguous(), wgt, self.shared_fn(x))
+        order, send_counts = dispatch_plan(idx.long(), self.E, self.world)
+        recv_counts = exchange_counts(send_counts, self.group)
+        # the split sizes of a variable all-to-all live on the host
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        tok = torch.div(order, self.topk, rounding_mode="floor")
+        send_rows = x[tok].contiguous()
+        send_eids = idx.reshape(-1)[order].contiguous()
+        n_recv = sum(rc)
+        recv_rows = torch.empty(n_recv, self.dim, dtype=x.dtype, device=x.device)
+        recv_eids = torch.empty(n_recv, dtype=send_eids.dtype, device=x.device)
+        dist.all_to_all_single(recv_rows, send_rows, rc, sc, group=self.group)
+        dist.all_to_all_single(recv_eids, send_eids, rc, sc, group=self.group)
+        shared = self.shared_fn(x)                       # overlaps the exchange on the GPU queue
+        eo_recv = self.experts_fn(recv_rows, recv_eids).contiguous()
+        eo_back = torch.empty(order.numel(), self.dim, dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(eo_back, eo_recv, sc, rc, group=self.group)
+        eo = torch.empty_like(eo_back)
+        eo[order] = eo_back                              # back to (t, j) order
+        return self.combine_fn(eo, wgt, shared)
+
+
+def create_handle(moew, e_lo, e_hi):
+    """Upload the experts [e_lo, e_hi) of an ApusMoeW (plus gate/shared) to HBM."""
+    h = lib().apus_cuda_moe_create(C.byref(moew), e_lo, e_hi)
+    if not h:
+        check(1, "apus_cuda_moe_create")
+    return h

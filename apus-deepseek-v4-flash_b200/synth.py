@@ -82,22 +82,21 @@ def activations(rng, T, K, std=1.0):
 
 
 class MoeWeights:
-    """All tensors of one synthetic MoE sublayer (reference c/moe.h:37-63)."""
+    """All tensors of one synthetic MoE sublayer (reference c/moe.h:37-63).
+
+    Every expert is drawn from its own generator stream keyed by (seed, expert
+    id), so a rank of an expert-parallel job can materialise only its shard
+    [e_lo, e_hi) and still agree bit for bit with a full-size instance."""
 
     def __init__(self, seed=0, E=N_EXPERTS, dim=DIM, inter=INTER, topk=TOPK,
-                 hash_vocab=0, route_scale=ROUTE_SCALE, limit=SWIGLU_LIMIT):
-        rng = np.random.default_rng(seed)
+                 hash_vocab=0, route_scale=ROUTE_SCALE, limit=SWIGLU_LIMIT,
+                 e_lo=0, e_hi=None):
+        rng = np.random.default_rng([seed, 1 << 20])
         self.E, self.dim, self.inter, self.topk = E, dim, inter, topk
         self.route_scale, self.limit = route_scale, limit
+        self.e_lo, self.e_hi = e_lo, E if e_hi is None else e_hi
         self.gate_w = bf16_round((rng.standard_normal((E, dim)) * 0.01).astype(np.float32))
         self.gate_bias = (rng.standard_normal(E) * 0.01).astype(np.float32)
-        # expert-major contiguous storage: one slab per tensor kind
-        self.w1p = rng.integers(0, 256, size=(E, inter, dim // 2), dtype=np.uint8)
-        self.w1s = rng.integers(120, 127, size=(E, inter, dim // 32), dtype=np.uint8)
-        self.w3p = rng.integers(0, 256, size=(E, inter, dim // 2), dtype=np.uint8)
-        self.w3s = rng.integers(120, 127, size=(E, inter, dim // 32), dtype=np.uint8)
-        self.w2p = rng.integers(0, 256, size=(E, dim, inter // 2), dtype=np.uint8)
-        self.w2s = rng.integers(120, 127, size=(E, dim, inter // 32), dtype=np.uint8)
         self.sw1 = fp8_weight(rng, inter, dim)
         self.sw3 = fp8_weight(rng, inter, dim)
         self.sw2 = fp8_weight(rng, dim, inter)
@@ -105,22 +104,38 @@ class MoeWeights:
         if hash_vocab:
             self.tid2eid = np.stack([rng.permutation(E)[:topk] for _ in range(hash_vocab)]
                                     ).astype(np.int64)
+        # expert-major contiguous storage of the local shard, one slab per tensor
+        nl = self.e_hi - self.e_lo
+        self.w1p = np.empty((nl, inter, dim // 2), np.uint8)
+        self.w1s = np.empty((nl, inter, dim // 32), np.uint8)
+        self.w3p = np.empty((nl, inter, dim // 2), np.uint8)
+        self.w3s = np.empty((nl, inter, dim // 32), np.uint8)
+        self.w2p = np.empty((nl, dim, inter // 2), np.uint8)
+        self.w2s = np.empty((nl, dim, inter // 32), np.uint8)
+        for le in range(nl):
+            er = np.random.default_rng([seed, self.e_lo + le])
+            self.w1p[le], self.w1s[le] = fp4_weight(er, inter, dim)
+            self.w3p[le], self.w3s[le] = fp4_weight(er, inter, dim)
+            self.w2p[le], self.w2s[le] = fp4_weight(er, dim, inter)
 
     def expert_bytes(self):
         return (self.w1p[0].nbytes + self.w1s[0].nbytes + self.w3p[0].nbytes
                 + self.w3s[0].nbytes + self.w2p[0].nbytes + self.w2s[0].nbytes)
 
     def moew(self):
-        """Build the ApusMoeW view; keeps the expert arrays alive on self."""
+        """Build the ApusMoeW view; keeps the expert arrays alive on self.
+        Experts outside [e_lo, e_hi) get NULL views."""
+        import ctypes as C
         from . import capi
         E = self.E
         self._a1 = (capi.QW * E)()
         self._a2 = (capi.QW * E)()
         self._a3 = (capi.QW * E)()
-        for e in range(E):
-            self._a1[e] = capi.qw(self.w1p[e], self.w1s[e], self.inter, self.dim)
-            self._a3[e] = capi.qw(self.w3p[e], self.w3s[e], self.inter, self.dim)
-            self._a2[e] = capi.qw(self.w2p[e], self.w2s[e], self.dim, self.inter)
+        for e in range(self.e_lo, self.e_hi):
+            le = e - self.e_lo
+            self._a1[e] = capi.qw(self.w1p[le], self.w1s[le], self.inter, self.dim)
+            self._a3[e] = capi.qw(self.w3p[le], self.w3s[le], self.inter, self.dim)
+            self._a2[e] = capi.qw(self.w2p[le], self.w2s[le], self.dim, self.inter)
         w = capi.MoeW()
         w.E, w.topk, w.inter, w.dim = E, self.topk, self.inter, self.dim
         w.hash = 1 if self.tid2eid is not None else 0
@@ -128,7 +143,6 @@ class MoeWeights:
         w.gate_w = capi.ptr(self.gate_w)
         w.gate_bias = None if w.hash else capi.ptr(self.gate_bias)
         w.tid2eid = capi.ptr(self.tid2eid) if w.hash else None
-        import ctypes as C
         w.w1 = C.cast(self._a1, C.POINTER(capi.QW))
         w.w2 = C.cast(self._a2, C.POINTER(capi.QW))
         w.w3 = C.cast(self._a3, C.POINTER(capi.QW))

@@ -1,0 +1,328 @@
+#!/usr/bin/env python3
+"""Benchmark of the hot path: decode through one full MoE sublayer at
+DeepSeek-V4-Flash dimensions (hidden 4096, 256 MXFP4 routed experts of
+intermediate 2048, top-6, FP8 shared expert), `--tokens` decode tokens per GPU
+per step, synthetic seeded weights and activations.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository
+    python bench.py --impl reference --gpus N --steps K ...  # reference C code on the host cores
+
+One JSON line on stdout (rank 0).  `value` is whole-job decode tokens/s with
+inputs resident in HBM; `e2e` is the same metric through the host-pointer C ABI
+(apus_cuda_moe_forward: pinned host activations in, host result out, copies
+inside the timed region); `roofline` describes the dominant kernel (MXFP4
+gate/up expert GEMV with fused SwiGLU) from CUDA events recorded around its
+launches inside the timed region; `cpu_baseline` is the unmodified reference
+`apus_moe_forward` timed on the host cores in the same run.
+
+N > 1: experts are sharded expert-parallel (contiguous blocks), each rank brings
+its own `--tokens` tokens (weak scaling), dispatch and combine are NCCL
+all-to-alls.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+W13_BYTES = 2 * (2048 * 4096 // 2 + 2048 * 4096 // 32)   # gate+up codes and scales of one expert
+W2_BYTES = 4096 * 2048 // 2 + 4096 * 2048 // 32
+METRIC = "moe_layer_decode_tokens_per_s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=32, help="decode tokens per GPU per step")
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--batches", type=int, default=8, help="distinct activation batches cycled")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_config(a, n):
+    return {"workload": f"config2: one MoE sublayer at V4-Flash dims, decode T={a.tokens} per GPU",
+            "hidden": 4096, "moe_intermediate": 2048, "n_routed_experts": a.experts, "topk": 6,
+            "tokens_per_gpu": a.tokens, "global_tokens": a.tokens * n,
+            "parallelism": f"ep{n}" if n > 1 else "single",
+            "l2": "experts touched per step (>1 GB) exceed the 126 MB L2; activation batches cycle"}
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc:
+            self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1] or [r for _, r in self.rows[-3:]]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][1]), "reasons": reasons,
+                "samples": len(rows)}
+
+
+def peak_hbm():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- the reference's CPU implementation (cpu_baseline and --impl reference) ---------------
+def cpu_moe_runner(W, tokens):
+    """Returns (callable running one T-token apus_moe_forward on the host, kind, cores)."""
+    from _oracle import P, ora_moe, ref
+    from apus_b200 import capi
+    L = ref()
+    rng = np.random.default_rng(12345)
+    from apus_b200 import synth
+    x = synth.activations(rng, tokens, W.dim)
+    if L is not None:
+        w = W.moew()
+        out = np.empty((tokens, W.dim), np.float32)
+
+        def run():
+            L.apus_moe_forward(C.byref(w), P(x), None, tokens, P(out), None)
+        run.keep = (w, out)
+        return run, "reference", L.ref_pool_threads
+    return (lambda: ora_moe(W, x)), "port", (lambda: 1)
+
+
+def time_cpu(run, tokens, budget_s, min_steps=1, max_steps=10 ** 9):
+    run()                                   # warm-up (spawns the pool, faults pages in)
+    t0 = time.perf_counter()
+    n = 0
+    while n < min_steps or (time.perf_counter() - t0 < budget_s and n < max_steps):
+        run()
+        n += 1
+    dt = time.perf_counter() - t0
+    return tokens * n / dt, n, dt
+
+
+def reference_arm(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 32)))
+    from apus_b200 import synth
+    W = synth.MoeWeights(seed=a.seed, E=a.experts)
+    run, kind, cores = cpu_moe_runner(W, a.tokens)
+    for _ in range(max(a.warmup, 1) if kind == "reference" else 1):
+        run()
+    steps = a.steps if kind == "reference" else min(a.steps, 2)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = time.perf_counter() - t0
+    val = a.tokens * steps / dt
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": a.gpus,
+            "steps": steps, "warmup": a.warmup, "ms_per_step": dt / steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(a, a.gpus),
+            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores(), "kind": kind,
+                             "sample": f"{steps} steps of T={a.tokens} tokens through apus_moe_forward "
+                                       f"on the host ({'unmodified reference C, AVX2 rows' if kind == 'reference' else 'oracle port'})"},
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---- this repository's arm ---------------------------------------------------------------------
+def main():
+    a = parse()
+    if a.impl == "reference":
+        return reference_arm(a)
+    import torch
+    import torch.distributed as dist
+    import apus_b200
+    from apus_b200 import capi, synth
+    from apus_b200.moe import ExpertParallelMoe, create_handle
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    apus_b200.build()
+    L = apus_b200.lib()
+    err = C.create_string_buffer(512)
+    if L.apus_cuda_enable(err, 512):
+        raise RuntimeError(err.value.decode())
+
+    T, E, K, Wm = a.tokens, a.experts, a.steps, a.warmup
+    n_local = E // world
+    W = synth.MoeWeights(seed=a.seed, E=E, e_lo=rank * n_local, e_hi=(rank + 1) * n_local)
+    moew = W.moew()
+    if world == 1:
+        handle = L.apus_cuda_moe_get(C.byref(moew))
+        if not handle:
+            apus_b200.check(1, "apus_cuda_moe_get")
+    else:
+        handle = create_handle(moew, W.e_lo, W.e_hi)
+    ep = ExpertParallelMoe(E, W.topk, W.dim, rank, world, handle=handle)
+
+    rng = np.random.default_rng([a.seed, 777, rank])
+    host_x = [torch.from_numpy(synth.activations(rng, T, W.dim)).pin_memory() for _ in range(a.batches)]
+    dev_x = [h.to(dev) for h in host_x]
+    dev_out = torch.empty(T, W.dim, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step_dev(b):
+        if world == 1:
+            apus_b200.check(L.apus_cuda_moe_forward_dev(handle, dev_x[b].data_ptr(), None, T,
+                                                        dev_out.data_ptr(), stream), "moe_forward_dev")
+            return dev_out
+        return ep.forward(dev_x[b])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # unique local experts touched per batch (for the algorithmic bytes of the GEMV kernels)
+    uniq = []
+    for b in range(a.batches):
+        step_dev(b)
+        torch.cuda.synchronize()
+        if world == 1:
+            idx = np.empty((T, W.topk), np.int32)
+            wg = np.empty((T, W.topk), np.float32)
+            apus_b200.check(L.apus_cuda_moe_last_routing(handle, T, capi.ptr(idx), capi.ptr(wg), stream),
+                            "last_routing")
+            uniq.append(len(np.unique(idx)))
+        else:
+            idx, _ = ep.route_fn(dev_x[b], None)
+            allidx = [torch.empty_like(idx) for _ in range(world)]
+            dist.all_gather(allidx, idx)
+            flat = torch.cat(allidx).reshape(-1)
+            mine = flat[(flat >= W.e_lo) & (flat < W.e_hi)]
+            uniq.append(int(torch.unique(mine).numel()))
+    for i in range(Wm):
+        step_dev(i % a.batches)
+    barrier()
+
+    uuid = str(torch.cuda.get_device_properties(dev).uuid)
+    sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid) if rank == 0 else None
+    L.apus_cuda_moe_timing(handle, 1)
+    d0 = L.apus_cuda_dispatches()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_wall0 = time.time()
+    ev0.record()
+    for i in range(K):
+        step_dev(i % a.batches)
+    ev1.record()
+    barrier()
+    t_wall1 = time.time()
+    ms = ev0.elapsed_time(ev1)
+    launches = int(L.apus_cuda_dispatches() - d0)
+    g13, g2, nl = C.c_double(), C.c_double(), C.c_int()
+    apus_b200.check(L.apus_cuda_moe_timing_read(handle, C.byref(g13), C.byref(g2), C.byref(nl)), "timing")
+    L.apus_cuda_moe_timing(handle, 0)
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    value = world * T * K / (ms * 1e-3)
+
+    # ---- end to end through host buffers -------------------------------------------------
+    host_out = torch.empty(T, W.dim).pin_memory()
+
+    def step_e2e(b):
+        if world == 1:
+            apus_b200.check(L.apus_cuda_moe_forward(C.byref(moew), host_x[b].data_ptr(), None, T,
+                                                    host_out.data_ptr(), None), "moe_forward")
+        else:
+            x = host_x[b].to(dev, non_blocking=True)
+            host_out.copy_(ep.forward(x), non_blocking=True)
+            torch.cuda.synchronize()
+    for i in range(max(3, Wm)):
+        step_e2e(i % a.batches)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        step_e2e(i % a.batches)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        te = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_s = float(te.item())
+    e2e_val = world * T * K / e2e_s
+
+    if rank == 0:
+        peak, peak_kind = peak_hbm()
+        steps_uniq = [uniq[i % a.batches] for i in range(K)]
+        bytes13 = float(sum(steps_uniq)) * W13_BYTES
+        achieved = bytes13 / (g13.value * 1e-3) / 1e9 if g13.value > 0 else None
+        bytes2 = float(sum(steps_uniq)) * W2_BYTES
+        achieved2 = bytes2 / (g2.value * 1e-3) / 1e9 if g2.value > 0 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": Wm, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 accumulate over E2M1xE4M3 / E4M3xE4M3 tensor-core products",
+            "data": "synthetic", "config": workload_config(a, world), "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": world * T * W.dim * 4,
+                    "d2h_bytes_per_step": world * T * W.dim * 4},
+            "gpu_launches": launches,
+            "roofline": {"kernel": "gemm_small_kernel<MXFP4, pair> (expert gate/up GEMV + SwiGLU)",
+                         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,
+                         "traffic": None, "launches": nl.value,
+                         "avg_launch_us": g13.value / max(nl.value, 1) * 1e3,
+                         "avg_unique_experts": float(np.mean(steps_uniq)),
+                         "down_proj_kernel": {"achieved": achieved2, "frac": (achieved2 / peak) if achieved2 else None,
+                                              "avg_launch_us": g2.value / max(nl.value, 1) * 1e3}},
+        }
+        if world == 1 and not a.no_cpu_baseline:
+            os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 32)))
+            run, kind, cores = cpu_moe_runner(W, T)
+            v, n, dt = time_cpu(run, T, budget_s=12.0, min_steps=2, max_steps=40)
+            line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores(), "kind": kind,
+                                    "sample": f"{n} steps of T={T} tokens through apus_moe_forward on the host "
+                                              f"cores in {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

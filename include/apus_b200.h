@@ -231,6 +231,18 @@ ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi);
 void apus_cuda_moe_destroy(ApusCudaMoe *m);
 /* Bytes of expert + dense weights resident for this sublayer. */
 uint64_t apus_cuda_moe_bytes(const ApusCudaMoe *m);
+/* The backend-owned handle that apus_cuda_moe_forward uses for `w` (all experts
+ * local), created on first use and keyed by w->gate_w; freed by
+ * apus_cuda_disable / apus_cuda_forget(w->gate_w).  Lets a caller mix the
+ * host-pointer call with the *_dev calls on one resident copy of the weights. */
+ApusCudaMoe *apus_cuda_moe_get(const ApusMoeW *w);
+/* Per-kernel timing of the two expert GEMM launches (gate/up pair, down) with
+ * CUDA events on the launching stream — the counterpart of the reference's
+ * dispatch counters (c/backend_metal.h:93-97) for roofline reporting.
+ * _timing_read sums the elapsed milliseconds recorded since the last read. */
+void apus_cuda_moe_timing(ApusCudaMoe *m, int enable);
+int apus_cuda_moe_timing_read(ApusCudaMoe *m, double *ms_gate_up,
+                              double *ms_down, int *launches);
 /* Hash-routed layers (c/moe.h:42, 391-394): place the tid2eid table
  * [vocab, topk] in HBM so that apus_cuda_moe_route_dev / _forward_dev can look
  * token ids up on device.  (The host-pointer apus_cuda_moe_forward does not
