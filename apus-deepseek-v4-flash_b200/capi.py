@@ -123,6 +123,7 @@ def load(path=LIB_PATH):
         "apus_cuda_sparse_attn": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, i64, vp]),
         "apus_cuda_mhc_prepost": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, vp, vp, ci]),
         "apus_cuda_hc_pre": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, cf, vp, vp, vp, vp, ci]),
+        "apus_cuda_hc_pre_noalloc_dev": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, cf, vp, vp, vp, vp, ci, vp]),
         "apus_cuda_hc_post": (ci, [vp, vp, vp, vp, vp, sz, sz, ci]),
         "apus_cuda_hc_head": (ci, [vp, sz, sz, vp, cf, vp, cf, cf, vp, ci]),
         "apus_cuda_moe_create": (vp, [C.POINTER(MoeW), ci, ci]),

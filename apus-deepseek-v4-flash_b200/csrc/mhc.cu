@@ -222,4 +222,75 @@ int mhc_post(const float *f, const float *res4, const float *post,
     return 0;
 }
 
+// ---- entry point that allocates nothing ------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory at the moment they
+// call in: an engine that has handed all of HBM to its own arena, a caller
+// inside a region where the driver forbids allocation, or a real-time loop
+// that must not take the allocator's lock.  For them the scratch of the mHC
+// pre step (the raw map dots, (2+n)*n+1 floats per token) lives in a fixed
+// file-scope device array instead of a grown buffer.  Every GPU that loads the
+// library carries the array (MHC_NOALLOC_MAX_ROWS * 65 floats = 66,560 bytes)
+// until the process exits.
+#define MHC_NOALLOC_MAX_ROWS 256
+#define MHC_NOALLOC_MAX_DEVICES 64
+static __device__ __align__(256) float g_mhc_static_raw[MHC_NOALLOC_MAX_ROWS * (MHC_MAX_N * (MHC_MAX_N + 2) + 1)];
+// In host code the array's name is only a handle for the runtime, not a device
+// address; the address each device gives it is looked up once per device.
+static float *g_mhc_static_ptr[MHC_NOALLOC_MAX_DEVICES];
+
+static int mhc_static_scratch(float **out) {
+    int dev = 0;
+    APUS_CUDA_OK(cudaGetDevice(&dev));
+    APUS_REQUIRE(dev >= 0 && dev < MHC_NOALLOC_MAX_DEVICES, "hc_pre_noalloc: device %d out of range", dev);
+    if (!g_mhc_static_ptr[dev]) {
+        void *p = nullptr;
+        APUS_CUDA_OK(cudaGetSymbolAddress(&p, g_mhc_static_raw));
+        g_mhc_static_ptr[dev] = static_cast<float *>(p);
+    }
+    *out = g_mhc_static_ptr[dev];
+    return 0;
+}
+
+int mhc_pre_noalloc(const float *x4, int d, int n, const float *fn, const float *scale,
+                    const float *base, float norm_eps, float hc_eps, int iters,
+                    const float *norm_w, float rms_eps, float *post, float *comb, float *y,
+                    float *y_normed, int rows, cudaStream_t st) {
+    APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N && (n * d) % 4 == 0, "hc_pre_noalloc: n=%d d=%d unsupported", n, d);
+    APUS_REQUIRE(rows <= MHC_NOALLOC_MAX_ROWS,
+                 "hc_pre_noalloc: %d rows exceed the fixed scratch of %d rows; split the call or use "
+                 "apus_cuda_hc_pre", rows, MHC_NOALLOC_MAX_ROWS);
+    APUS_REQUIRE(y != nullptr, "hc_pre_noalloc: y must not be NULL");
+    if (rows <= 0) return 0;
+    float *raw = nullptr;
+    if (mhc_static_scratch(&raw)) return 1;
+    const int nmix = (2 + n) * n;
+    // every raw[row, 0..nmix] slot read by the finish kernel is written by the mix
+    // kernel of the same call, so nothing left over from an earlier call is used
+    mhc_mix_kernel<<<dim3(nmix + 1, rows), 256, 0, st>>>(x4, fn, n * d, nmix, raw);
+    APUS_LAUNCHED();
+    mhc_pre_finish_kernel<<<rows, 256, 0, st>>>(x4, raw, d, n, nmix, scale, 0.f, base, norm_eps,
+                                                hc_eps, iters, 0, norm_w, rms_eps, nullptr, post,
+                                                comb, y, norm_w ? y_normed : nullptr);
+    APUS_LAUNCHED();
+    return 0;
+}
+
 }  // namespace apus
+
+// The mHC pre step for callers that cannot allocate device memory (see the
+// comment above g_mhc_static_raw).  All pointers are device pointers owned by
+// the caller; the kernels run on `stream`.  The first call on each device looks
+// up the device address of the fixed scratch array (cudaGetSymbolAddress), so
+// make that first call outside any stream capture.  Calls share the one scratch
+// array per device: two calls whose kernels can overlap on the GPU (different
+// streams without an ordering between them) race on it.  rows > 256 is
+// rejected with an error.
+extern "C" int apus_cuda_hc_pre_noalloc_dev(const float *x4, size_t d, size_t n, const float *fn,
+                                            const float *scale, const float *base, float norm_eps,
+                                            float hc_eps, int iters, const float *norm_w,
+                                            float rms_eps, float *y, float *y_normed, float *post,
+                                            float *comb, int rows, void *stream) {
+    return apus::mhc_pre_noalloc(x4, (int)d, (int)n, fn, scale, base, norm_eps, hc_eps, iters, norm_w,
+                                 rms_eps, post, comb, y, y_normed, rows, (cudaStream_t)stream);
+}

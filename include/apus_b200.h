@@ -312,6 +312,23 @@ int apus_cuda_sparse_attn_dev(const float *q, const float *sink, int h, int d,
                               const uint16_t *kv_b, int64_t nb, float *o,
                               void *stream);
 
+/* No counterpart in the reference.  apus_cuda_hc_pre on device pointers for
+ * callers that must not allocate device memory while they run (an engine whose
+ * own arena already owns the HBM, a region where allocation is forbidden, a loop
+ * that must stay off the allocator's lock): the scratch between its two kernels
+ * is a fixed array inside the library, 66,560 bytes on every GPU that loads it,
+ * enough for rows <= 256; more rows are rejected with an error.  It calls no
+ * cudaMalloc/cudaFree.  The first call on a device resolves the array's device
+ * address: make it before any stream capture.  All calls on a device share the
+ * array; calls that may overlap on the GPU race on it. */
+int apus_cuda_hc_pre_noalloc_dev(const float *x4, size_t d, size_t n,
+                                 const float *fn, const float *scale,
+                                 const float *base, float norm_eps,
+                                 float hc_eps, int iters, const float *norm_w,
+                                 float rms_eps, float *y, float *y_normed,
+                                 float *post, float *comb, int rows,
+                                 void *stream);
+
 #ifdef __cplusplus
 }
 #endif
