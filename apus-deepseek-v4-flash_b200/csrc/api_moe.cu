@@ -98,7 +98,7 @@ static int experts_run(ApusCudaMoe *m, const float *xrows, int n_rows, const int
     const int max_groups = n_rout < n_local + n_rout / chunk + 1 ? n_rout : n_local + n_rout / chunk + 1;
     if (act_quant(xrows, nullptr, n_rows, dim, m->b_xq.as<uint8_t>(), m->b_xs.as<float>(), nullptr, st))
         return 1;
-    if (moe_group(rout_eid, rout_row, n_rout, m->sl, chunk, m->b_spos.as<int>(), m->b_srow.as<int>(),
+    if (moe_group(rout_eid, rout_row, m->topk, n_rout, m->sl, chunk, m->b_spos.as<int>(), m->b_srow.as<int>(),
                   m->b_g13.as<GemmGroup>(), m->b_g2.as<GemmGroup>(), m->b_ng.as<int>(), max_groups, st))
         return 1;
     GemmSmallArgs a = {};
@@ -144,11 +144,6 @@ static int route_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const i
                          m->route_scale, sp, biased, idx, wgt, st);
 }
 
-__global__ void iota_rows_kernel(int32_t *rout_row, int n, int topk) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) rout_row[i] = i / topk;
-}
-
 static int forward_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const int64_t *table,
                        int s, float *out, float *routed, cudaStream_t st) {
     const int R = s * m->topk;
@@ -158,9 +153,7 @@ static int forward_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const
                  m->e_lo, m->e_hi, m->E);
     if (route_run(m, x, ids, table, s, m->b_idx.as<int32_t>(), m->b_wgt.as<float>(), nullptr, nullptr, st))
         return 1;
-    iota_rows_kernel<<<ceil_div(R, 256), 256, 0, st>>>(m->b_routrow.as<int32_t>(), R, m->topk);
-    APUS_LAUNCHED();
-    if (experts_run(m, x, s, m->b_routrow.as<int32_t>(), m->b_idx.as<int32_t>(), R,
+    if (experts_run(m, x, s, nullptr, m->b_idx.as<int32_t>(), R,
                     m->b_eo.as<float>(), st))
         return 1;
     if (shared_run(m, x, s, m->b_shared.as<float>(), st)) return 1;

@@ -20,11 +20,17 @@
 // h = bf16(silu(clamp(gate)) * clamp(up)) (reference c/moe.h:113-126) so the
 // gate/up projections of an expert cost one pass over the activations.
 //
-// Launch: grid (ceil(O/128), work items), 256 threads; warp w of a CTA owns the
-// 16 output rows [blockIdx.x*128 + 16w, +16) for the whole K range and reads its
-// weight fragments straight from global memory in the tiled layout of
-// repack.cu (coalesced 16 bytes per lane); activation codes of the work item's
-// rows are staged once in shared memory.
+// Launch, MXFP4: grid (ceil(O/128), work items), 256 threads; warp w of a CTA owns
+// the 16 output rows [blockIdx.x*128 + 16w, +16) for the whole K range (the fold
+// over K blocks keeps the reference order) and reads its weight fragments
+// straight from global memory in the tiled layout of repack.cu (coalesced 16
+// bytes per lane); activation codes of the work item's rows are staged once in
+// shared memory.
+// Launch, FP8 (dense projections, shared expert: one matrix, few work items):
+// grid (O/16, work items); the 8 warps of a CTA share one 16-row group and split
+// K into eight contiguous ranges, their partial totals are added in warp order
+// through shared memory.  The split does not depend on the number of rows, so
+// a row's result is the same in any batch.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -85,8 +91,11 @@ gemm_small_kernel(const GemmSmallArgs a) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
-    const int rg = blockIdx.x * 8 + warp;
+    constexpr bool SPLITK = (FMT == 8);
+    const int rg = SPLITK ? (int)blockIdx.x : (int)blockIdx.x * 8 + warp;
     const bool active = rg * 16 < O;
+    const int kg_lo = SPLITK ? (KG * warp) / 8 : 0;
+    const int kg_hi = SPLITK ? (KG * (warp + 1)) / 8 : KG;
 
     // ---- weight stream pointers ------------------------------------------------
     const uint4 *pa = nullptr, *pb = nullptr;
@@ -126,7 +135,7 @@ gemm_small_kernel(const GemmSmallArgs a) {
             if (PAIR) yb.x = tb[kg];
         }
     };
-    if (active) load_group(0, wa, wb, sa, sb);      // in flight while activations stage
+    if (active && kg_lo < kg_hi) load_group(kg_lo, wa, wb, sa, sb);   // in flight while activations stage
 
     // ---- stage activation codes + scales of this work item ------------------------
     {
@@ -161,10 +170,10 @@ gemm_small_kernel(const GemmSmallArgs a) {
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
     const uint8_t *bbase = s_codes + (size_t)g * pitch + 8 * c;
 
-    for (int kg = 0; kg < KG; kg++) {
+    for (int kg = kg_lo; kg < kg_hi; kg++) {
         uint4 na[NW], nb[NW];
         uint2 nsa = make_uint2(0, 0), nsb = make_uint2(0, 0);
-        if (kg + 1 < KG) load_group(kg + 1, na, nb, nsa, nsb);
+        if (kg + 1 < kg_hi) load_group(kg + 1, na, nb, nsa, nsb);
 
         float2 as2[NT];
 #pragma unroll
@@ -236,11 +245,39 @@ gemm_small_kernel(const GemmSmallArgs a) {
                 }
             }
         }
-        if (kg + 1 < KG) {
+        if (kg + 1 < kg_hi) {
 #pragma unroll
             for (int i = 0; i < NW; i++) { wa[i] = na[i]; if (PAIR) wb[i] = nb[i]; }
             sa = nsa; sb = nsb;
         }
+    }
+
+    if (SPLITK) {
+        // add the eight K-range partials in warp order (the staging area is free now)
+        __syncthreads();
+        float *part = reinterpret_cast<float *>(smem);
+        constexpr int PER = NT * 4 * (PAIR ? 2 : 1);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                part[(warp * PER + nt * 4 + j) * 32 + lane] = totA[nt][j];
+                if (PAIR) part[(warp * PER + NT * 4 + nt * 4 + j) * 32 + lane] = totB[nt][j];
+            }
+        __syncthreads();
+        if (warp != 0) return;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float a0 = 0.f, b0 = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; w++) {
+                    a0 += part[(w * PER + nt * 4 + j) * 32 + lane];
+                    if (PAIR) b0 += part[(w * PER + NT * 4 + nt * 4 + j) * 32 + lane];
+                }
+                totA[nt][j] = a0; totB[nt][j] = b0;
+            }
     }
 
     // ---- epilogue ------------------------------------------------------------------
@@ -263,6 +300,10 @@ gemm_small_kernel(const GemmSmallArgs a) {
 template <int FMT, int NT, bool PAIR, bool ZS>
 static int launch(const GemmSmallArgs &a, cudaStream_t st) {
     size_t smem = (size_t)NT * 8 * (a.K + 32) + (size_t)(a.K / 128) * NT * 8 * sizeof(float);
+    if (FMT == 8) {                       // the split-K partials reuse the staging area
+        size_t part = (size_t)8 * NT * 4 * (PAIR ? 2 : 1) * 32 * sizeof(float);
+        if (part > smem) smem = part;
+    }
     auto kern = gemm_small_kernel<FMT, NT, PAIR, ZS>;
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -270,7 +311,7 @@ static int launch(const GemmSmallArgs &a, cudaStream_t st) {
                                           (int)smem));
         configured = smem;
     }
-    dim3 grid((unsigned)ceil_div(a.O, 128), (unsigned)a.n_groups);
+    dim3 grid((unsigned)(FMT == 8 ? a.O / 16 : ceil_div(a.O, 128)), (unsigned)a.n_groups);
     kern<<<grid, 256, smem, st>>>(a);
     APUS_LAUNCHED();
     return 0;

@@ -75,7 +75,8 @@ struct MoeSlab {            // where expert e's tiled tensors live
     size_t code_stride13, scale_stride13, code_stride2, scale_stride2;
     int e_lo, e_hi;
 };
-int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int n_rout,
+// rout_row == NULL: routing i belongs to row i / row_div (the (t, j) order).
+int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int row_div, int n_rout,
               const MoeSlab &slab, int chunk, int *sorted_pos, int *sorted_row,
               GemmGroup *g13, GemmGroup *g2, int *n_groups, int max_groups,
               cudaStream_t st);

@@ -101,50 +101,97 @@ int router_finish(const float *logits, const float *bias, const int64_t *tid2eid
 // ---- grouping -----------------------------------------------------------------------
 //
 // Stable counting sort of the routings by local expert (the reference's
-// counting sort, c/moe.h:465-474), done by one CTA with warp ballots so that
-// rows of one expert keep their (token, slot) order, followed by the work-item
-// table for the two GEMM passes: each expert's rows are cut into runs of at
-// most `chunk` rows.  Routings whose expert is not local are skipped.
+// counting sort, c/moe.h:465-474) by one CTA, followed by the work-item table
+// for the two GEMM passes: each expert's rows are cut into runs of at most
+// `chunk` rows.  Routings whose expert is not local are skipped.  Rows of one
+// expert keep their (token, slot) order: a routing's rank inside its expert is
+// the number of earlier routings with the same expert id.
+//   n <= GROUP_SMEM_N: ids staged in shared memory, one thread per routing
+//     counts its predecessors; otherwise one warp per expert sweeps the list
+//     with ballots.
+#define GROUP_SMEM_N 4096
 __global__ void __launch_bounds__(1024)
-moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ row, int n,
-                 MoeSlab slab, int chunk, int *__restrict__ sorted_pos,
+moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ row, int row_div,
+                 int n, MoeSlab slab, int chunk, int *__restrict__ sorted_pos,
                  int *__restrict__ sorted_row, GemmGroup *__restrict__ g13,
                  GemmGroup *__restrict__ g2, int *__restrict__ n_groups, int max_groups) {
     __shared__ int s_cnt[1024], s_off[1024], s_goff[1024];
+    __shared__ int s_eid[GROUP_SMEM_N];
+    __shared__ int s_wsum[32], s_wgsum[32];
     const int nE = slab.e_hi - slab.e_lo;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
-    for (int le = warp; le < nE; le += nwarp) {
-        int cnt = 0;
-        for (int base = 0; base < n; base += 32) {
-            int i = base + lane;
-            bool hit = i < n && eid[i] == slab.e_lo + le;
-            cnt += __popc(__ballot_sync(0xffffffffu, hit));
-        }
-        if (lane == 0) s_cnt[le] = cnt;
-    }
+    const bool small = n <= GROUP_SMEM_N;
+    for (int i = tid; i < nE; i += blockDim.x) s_cnt[i] = 0;
     __syncthreads();
-    if (tid == 0) {
-        int off = 0, goff = 0;
-        for (int le = 0; le < nE; le++) {
-            s_off[le] = off; s_goff[le] = goff;
-            off += s_cnt[le];
-            goff += (s_cnt[le] + chunk - 1) / chunk;
+    if (small) {
+        for (int i = tid; i < n; i += blockDim.x) {
+            int le = eid[i] - slab.e_lo;
+            s_eid[i] = (le >= 0 && le < nE) ? le : -1;
+            if (le >= 0 && le < nE) atomicAdd(&s_cnt[le], 1);
         }
-        *n_groups = goff < max_groups ? goff : max_groups;
-    }
-    __syncthreads();
-    for (int le = warp; le < nE; le += nwarp) {
-        int pos = s_off[le];
-        for (int base = 0; base < n; base += 32) {
-            int i = base + lane;
-            bool hit = i < n && eid[i] == slab.e_lo + le;
-            unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                int p = pos + __popc(m & ((1u << lane) - 1u));
-                sorted_pos[p] = i;
-                sorted_row[p] = row ? row[i] : i;
+    } else {
+        for (int le = warp; le < nE; le += nwarp) {
+            int cnt = 0;
+            for (int base = 0; base < n; base += 32) {
+                int i = base + lane;
+                bool hit = i < n && eid[i] == slab.e_lo + le;
+                cnt += __popc(__ballot_sync(0xffffffffu, hit));
             }
-            pos += __popc(m);
+            if (lane == 0) s_cnt[le] = cnt;
+        }
+    }
+    __syncthreads();
+    // exclusive scans of the counts and of the per-expert work-item counts
+    {
+        int c = tid < nE ? s_cnt[tid] : 0;
+        int g = (c + chunk - 1) / chunk;
+        int ic = c, ig = g;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int tc = __shfl_up_sync(0xffffffffu, ic, o), tg = __shfl_up_sync(0xffffffffu, ig, o);
+            if (lane >= o) { ic += tc; ig += tg; }
+        }
+        if (lane == 31) { s_wsum[warp] = ic; s_wgsum[warp] = ig; }
+        __syncthreads();
+        if (warp == 0) {
+            int wc = s_wsum[lane], wg = s_wgsum[lane];
+            int jc = wc, jg = wg;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int tc = __shfl_up_sync(0xffffffffu, jc, o), tg = __shfl_up_sync(0xffffffffu, jg, o);
+                if (lane >= o) { jc += tc; jg += tg; }
+            }
+            s_wsum[lane] = jc - wc; s_wgsum[lane] = jg - wg;
+            if (lane == 31) *n_groups = jg < max_groups ? jg : max_groups;
+        }
+        __syncthreads();
+        if (tid < nE) { s_off[tid] = s_wsum[warp] + ic - c; s_goff[tid] = s_wgsum[warp] + ig - g; }
+    }
+    __syncthreads();
+    if (small) {
+        for (int i = tid; i < n; i += blockDim.x) {
+            int le = s_eid[i];
+            if (le < 0) continue;
+            int rank = 0;
+            for (int j = 0; j < i; j++) rank += (s_eid[j] == le);
+            int p = s_off[le] + rank;
+            sorted_pos[p] = i;
+            sorted_row[p] = row ? row[i] : i / row_div;
+        }
+    } else {
+        for (int le = warp; le < nE; le += nwarp) {
+            int pos = s_off[le];
+            for (int base = 0; base < n; base += 32) {
+                int i = base + lane;
+                bool hit = i < n && eid[i] == slab.e_lo + le;
+                unsigned m = __ballot_sync(0xffffffffu, hit);
+                if (hit) {
+                    int p = pos + __popc(m & ((1u << lane) - 1u));
+                    sorted_pos[p] = i;
+                    sorted_row[p] = row ? row[i] : i / row_div;
+                }
+                pos += __popc(m);
+            }
         }
     }
     for (int le = tid; le < nE; le += blockDim.x) {
@@ -166,12 +213,13 @@ moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ ro
     }
 }
 
-int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int n_rout,
+int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int row_div, int n_rout,
               const MoeSlab &slab, int chunk, int *sorted_pos, int *sorted_row,
               GemmGroup *g13, GemmGroup *g2, int *n_groups, int max_groups,
               cudaStream_t st) {
     APUS_REQUIRE(slab.e_hi - slab.e_lo <= 1024, "moe_group: more than 1024 local experts");
-    moe_group_kernel<<<1, 1024, 0, st>>>(rout_eid, rout_row, n_rout, slab, chunk, sorted_pos,
+    APUS_REQUIRE(rout_row || row_div > 0, "moe_group: no row mapping");
+    moe_group_kernel<<<1, 1024, 0, st>>>(rout_eid, rout_row, row_div, n_rout, slab, chunk, sorted_pos,
                                          sorted_row, g13, g2, n_groups, max_groups);
     APUS_LAUNCHED();
     return 0;
