@@ -54,7 +54,7 @@ def build(force=False, verbose=False):
             raise RuntimeError(f"nvcc failed on {src.name}:\n{out}")
     if force or _stale(OUT, objs):
         cmd = [nvcc, "-shared", "-o", str(OUT)] + [str(o) for o in objs] + \
-            ["-gencode", "arch=compute_100a,code=sm_100a", "-lcuda"]
+            ["-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}")

@@ -107,12 +107,14 @@ def load(path=LIB_PATH):
         "apus_cuda_fill_hooks": (ci, [C.POINTER(Hooks), sz, sz]),
         "apus_cuda_last_error": (C.c_char_p, []),
         "apus_cuda_forget": (None, [vp]),
+        "apus_cuda_kernel_status": (ci, [ci]),
         "apus_cuda_fp8_linear": (ci, [C.POINTER(QW), vp, vp, ci, ci, ci]),
         "apus_cuda_fp4_linear": (ci, [C.POINTER(QW), vp, vp, ci, ci, ci]),
         "apus_cuda_f32_linear": (ci, [vp, vp, vp, ci, ci, ci, ci]),
         "apus_cuda_head_gemv_bf16": (ci, [vp, vp, vp, i64, i64]),
         "apus_cuda_fp8_gemm": (ci, [vp, vp, vp, vp, vp, ci, ci, ci]),
         "apus_cuda_fp4_gemm": (ci, [vp, vp, vp, vp, vp, ci, ci, ci]),
+        "apus_cuda_fp4_gemm_tc": (ci, [vp, vp, vp, vp, vp, ci, ci, ci]),
         "apus_cuda_fp4_gemm_grouped": (ci, [C.POINTER(Fp4GemmEnt), sz, vp, vp, sz, sz, sz]),
         "apus_cuda_fp8_act_quant": (ci, [vp, ci, ci, vp, vp]),
         "apus_cuda_rmsnorm": (ci, [vp, vp, cf, vp, i64, i64]),
@@ -131,6 +133,7 @@ def load(path=LIB_PATH):
         "apus_cuda_moe_bytes": (C.c_uint64, [vp]),
         "apus_cuda_moe_set_hash_table": (ci, [vp, vp, i64]),
         "apus_cuda_moe_get": (vp, [C.POINTER(MoeW)]),
+        "apus_cuda_moe_use_tc": (ci, [vp, ci]),
         "apus_cuda_moe_timing": (None, [vp, ci]),
         "apus_cuda_moe_timing_read": (ci, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(ci)]),
         "apus_cuda_moe_route_dev": (ci, [vp, vp, vp, ci, vp, vp, vp, vp, vp]),

@@ -375,6 +375,45 @@ int apus_cuda_fp4_gemm(const uint8_t *w, const uint8_t *ws, const uint8_t *acode
     return host_qgemm(4, w, ws, acodes, as, out, M, O, K);
 }
 
+// c/fp4.h:166 on the tcgen05 path: weights stay in the reference storage and are
+// unpacked by TMA; used by the kernel-level tests of gemm_tc.cu.
+int apus_cuda_fp4_gemm_tc(const uint8_t *w, const uint8_t *ws, const uint8_t *acodes, const float *as,
+                          float *out, int M, int O, int K) {
+    if (ensure_enabled()) return 1;
+    if (M <= 0) return 0;
+    APUS_REQUIRE(O % 128 == 0 && K % 512 == 0, "fp4_gemm_tc: O=%d must be a multiple of 128 and K=%d of 512", O, K);
+    Ctx &c = ctx();
+    const size_t cb = (size_t)O * K / 2, sb = (size_t)O * K / 32;
+    const int ng = ceil_div(M, 32);
+    void *dw, *ds, *dq, *das, *dout, *dg;
+    if (c.ws[8].get(cb, &dw) || c.ws[9].get(sb, &ds) || c.ws[1].get((size_t)M * K, &dq) ||
+        c.ws[2].get((size_t)M * (K / 128) * 4, &das) || c.ws[3].get((size_t)M * O * 4, &dout) ||
+        c.ws[4].get((size_t)ng * sizeof(TcGroup), &dg))
+        return 1;
+    std::vector<TcGroup> g(ng);
+    for (int i = 0; i < ng; i++) { g[i].a_row = 0; g[i].row0 = i * 32; g[i].nrows = M - i * 32 < 32 ? M - i * 32 : 32; g[i].pad = 0; }
+    APUS_CUDA_OK(cudaMemcpyAsync(dw, w, cb, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(ds, ws, sb, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dq, acodes, (size_t)M * K, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(das, as, (size_t)M * (K / 128) * 4, cudaMemcpyHostToDevice, c.stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(dg, g.data(), ng * sizeof(TcGroup), cudaMemcpyHostToDevice, c.stream));
+    alignas(64) unsigned char map_w[128], map_x[128];
+    if (tc_make_weight_map(map_w, dw, O, K) || tc_make_act_map(map_x, dq, M, K)) return 1;
+    TcArgs a = {};
+    a.map_a = map_w; a.map_b = map_w; a.map_x = map_x;
+    a.scales_a = (const uint8_t *)ds; a.ascales = (const float *)das;
+    a.groups = (const TcGroup *)dg; a.n_groups = ng; a.O = O; a.K = K; a.pair = 0; a.round_out = 0;
+    a.out = (float *)dout;
+    if (const char *e = getenv("APUS_TC_TX")) a.tx_bytes = atoi(e);
+    gemm_tc_status(1);
+    if (gemm_tc(a, c.stream)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)M * O * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "fp4_gemm_tc: a bounded wait expired inside the kernel (code %d)", stt);
+    return 0;
+}
+
 int apus_cuda_fp4_gemm_grouped(const ApusFp4GemmEnt *ents, size_t n_ent, const uint8_t *acodes,
                                const float *as, size_t rows, size_t O, size_t K) {
     if (ensure_enabled()) return 1;

@@ -9,6 +9,7 @@
 //   gate matmul -> router finish -> act quant(x) -> group routings by expert
 //   -> gate/up GEMM + SwiGLU -> act quant(h) -> down GEMM (scatter to (t,j))
 //   -> shared expert (3 FP8 GEMMs) -> ordered combine.
+#include <stdlib.h>
 #include <vector>
 
 #include "runtime.cuh"
@@ -27,6 +28,12 @@ struct ApusCudaMoe {
     int zero_scale = 0;
     DevQW sw1, sw2, sw3;                  // shared expert
     uint64_t weight_bytes = 0;
+    // tcgen05 path: the same experts in the reference storage + TMA tensor maps
+    bool use_tc = false;
+    uint8_t *raw = nullptr;
+    const uint8_t *rw1 = nullptr, *rw3 = nullptr, *rw2 = nullptr, *rs1 = nullptr, *rs3 = nullptr, *rs2 = nullptr;
+    alignas(64) unsigned char map_w1[128], map_w3[128], map_w2[128], map_xq[128], map_hq[128];
+    DevBuf b_t13, b_t2;
     // workspaces
     int cap_s = 0, cap_r = 0;
     DevBuf b_logits, b_sp, b_biased, b_idx, b_wgt, b_xq, b_xs, b_routrow, b_spos, b_srow,
@@ -73,7 +80,11 @@ int ApusCudaMoe::ensure(int s, int n_rout) {
             b_g13.get(max_groups * sizeof(GemmGroup), nullptr) ||
             b_g2.get(max_groups * sizeof(GemmGroup), nullptr) || b_ng.get(256, nullptr) ||
             b_h.get(R * inter * 4, nullptr) || b_hq.get(R * inter, nullptr) ||
-            b_hs.get(R * (inter / 128) * 4, nullptr) || b_eo.get(R * dim * 4, nullptr))
+            b_hs.get(R * (inter / 128) * 4, nullptr) || b_eo.get(R * dim * 4, nullptr) ||
+            b_t13.get(max_groups * sizeof(TcGroup), nullptr) || b_t2.get(max_groups * sizeof(TcGroup), nullptr))
+            return 1;
+        if (use_tc && (tc_make_act_map(map_xq, b_xq.p, (long long)(b_xq.cap / dim), dim) ||
+                       tc_make_act_map(map_hq, b_hq.p, (long long)(b_hq.cap / inter), inter)))
             return 1;
         cap_r = (int)XR;
     }
@@ -88,10 +99,45 @@ static int pick_chunk(int n_rout, int n_local) {
     return 32;
 }
 
+// Routed experts on the tcgen05 path: group first, quantise the token rows
+// straight into sorted order, then two block-scaled tensor-core GEMMs.
+static int experts_run_tc(ApusCudaMoe *m, const float *xrows, const int32_t *rout_row,
+                          const int32_t *rout_eid, int n_rout, float *eo, cudaStream_t st) {
+    const int dim = m->dim, inter = m->inter;
+    const int n_local = m->e_hi - m->e_lo;
+    const int chunk = 32;
+    const int max_groups = n_rout < n_local + n_rout / chunk + 1 ? n_rout : n_local + n_rout / chunk + 1;
+    int *ng = m->b_ng.as<int>();
+    if (moe_group(rout_eid, rout_row, m->topk, n_rout, m->sl, chunk, m->b_spos.as<int>(), m->b_srow.as<int>(),
+                  m->b_g13.as<GemmGroup>(), m->b_g2.as<GemmGroup>(), ng, max_groups, st,
+                  m->b_t13.as<TcGroup>(), m->b_t2.as<TcGroup>(), inter, dim))
+        return 1;
+    if (act_quant(xrows, m->b_srow.as<int>(), n_rout, dim, m->b_xq.as<uint8_t>(), m->b_xs.as<float>(),
+                  ng + 1, st))
+        return 1;
+    TcArgs a = {};
+    a.map_a = m->map_w1; a.map_b = m->map_w3; a.map_x = m->map_xq;
+    a.scales_a = m->rs1; a.scales_b = m->rs3; a.ascales = m->b_xs.as<float>();
+    a.groups = m->b_t13.as<TcGroup>(); a.n_groups_dev = ng; a.n_groups = max_groups;
+    a.O = inter; a.K = dim; a.pair = 1; a.limit = m->limit; a.out = m->b_h.as<float>();
+    if (m->mark(st) || gemm_tc(a, st) || m->mark(st)) return 1;
+    if (act_quant(m->b_h.as<float>(), nullptr, n_rout, inter, m->b_hq.as<uint8_t>(), m->b_hs.as<float>(),
+                  ng + 1, st))
+        return 1;
+    TcArgs b = {};
+    b.map_a = m->map_w2; b.map_b = m->map_w2; b.map_x = m->map_hq;
+    b.scales_a = m->rs2; b.ascales = m->b_hs.as<float>();
+    b.groups = m->b_t2.as<TcGroup>(); b.n_groups_dev = ng; b.n_groups = max_groups;
+    b.O = dim; b.K = inter; b.pair = 0; b.round_out = 1; b.orow = m->b_spos.as<int>(); b.out = eo;
+    if (m->mark(st) || gemm_tc(b, st) || m->mark(st)) return 1;
+    return 0;
+}
+
 // Routed experts for arbitrary local routings (device pointers).
 static int experts_run(ApusCudaMoe *m, const float *xrows, int n_rows, const int32_t *rout_row,
                        const int32_t *rout_eid, int n_rout, float *eo, cudaStream_t st) {
     if (n_rout <= 0) return 0;
+    if (m->use_tc) return experts_run_tc(m, xrows, rout_row, rout_eid, n_rout, eo, st);
     const int dim = m->dim, inter = m->inter;
     const int n_local = m->e_hi - m->e_lo;
     const int chunk = pick_chunk(n_rout, n_local);
@@ -220,6 +266,44 @@ ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi) {
         }
         m->zero_scale |= z1 | z2 | z3;
     }
+    // the same experts once more in the reference storage for the tcgen05 kernel
+    {
+        const char *env = getenv("APUS_MOE_TC");
+        m->use_tc = !(env && env[0] == '0') && w->inter % 512 == 0 && w->dim % 512 == 0 && nl > 0;
+    }
+    if (m->use_tc) {
+        if (cudaMalloc(&m->raw, total) != cudaSuccess) {
+            set_error("moe_create: device allocation of %zu bytes (tcgen05 copy) failed", total);
+            apus_cuda_moe_destroy(m); return nullptr;
+        }
+        uint8_t *q = m->raw;
+        uint8_t *d1 = q; q += (size_t)nl * c13;
+        uint8_t *d3 = q; q += (size_t)nl * c13;
+        uint8_t *d2 = q; q += (size_t)nl * c2;
+        uint8_t *e1 = q; q += (size_t)nl * s13;
+        uint8_t *e3 = q; q += (size_t)nl * s13;
+        uint8_t *e2 = q;
+        m->rw1 = d1; m->rw3 = d3; m->rw2 = d2; m->rs1 = e1; m->rs3 = e3; m->rs2 = e2;
+        for (int e = e_lo; e < e_hi; e++) {
+            ApusFp4W r1, r2, r3;
+            if (w->hook_resolve) w->hook_resolve(w->hook_ctx, w->layer_id, e, &r1, &r2, &r3);
+            else { r1 = w->w1[e]; r2 = w->w2[e]; r3 = w->w3[e]; }
+            const int le = e - e_lo;
+            bool ok2 = cudaMemcpy(d1 + le * c13, r1.packed, c13, cudaMemcpyHostToDevice) == cudaSuccess &&
+                       cudaMemcpy(d3 + le * c13, r3.packed, c13, cudaMemcpyHostToDevice) == cudaSuccess &&
+                       cudaMemcpy(d2 + le * c2, r2.packed, c2, cudaMemcpyHostToDevice) == cudaSuccess &&
+                       cudaMemcpy(e1 + le * s13, r1.scales, s13, cudaMemcpyHostToDevice) == cudaSuccess &&
+                       cudaMemcpy(e3 + le * s13, r3.scales, s13, cudaMemcpyHostToDevice) == cudaSuccess &&
+                       cudaMemcpy(e2 + le * s2, r2.scales, s2, cudaMemcpyHostToDevice) == cudaSuccess;
+            if (!ok2) { set_error("moe_create: upload of expert %d failed", e); apus_cuda_moe_destroy(m); return nullptr; }
+        }
+        if (tc_make_weight_map(m->map_w1, d1, (long long)nl * w->inter, w->dim) ||
+            tc_make_weight_map(m->map_w3, d3, (long long)nl * w->inter, w->dim) ||
+            tc_make_weight_map(m->map_w2, d2, (long long)nl * w->dim, w->inter)) {
+            apus_cuda_moe_destroy(m); return nullptr;
+        }
+        c.bytes_uploaded += total;
+    }
     // shared expert
     struct { DevQW *d; const ApusFp8W *h; int O, K; } sh[3] = {
         {&m->sw1, &w->sw1, w->inter, w->dim}, {&m->sw3, &w->sw3, w->inter, w->dim},
@@ -243,11 +327,12 @@ void apus_cuda_moe_destroy(ApusCudaMoe *m) {
     if (m->gate_bias) cudaFree(m->gate_bias);
     if (m->tid2eid) cudaFree(m->tid2eid);
     if (m->slab) cudaFree(m->slab);
+    if (m->raw) cudaFree(m->raw);
     m->sw1.release(); m->sw2.release(); m->sw3.release();
     DevBuf *bufs[] = {&m->b_logits, &m->b_sp, &m->b_biased, &m->b_idx, &m->b_wgt, &m->b_xq, &m->b_xs,
                       &m->b_routrow, &m->b_spos, &m->b_srow, &m->b_g13, &m->b_g2, &m->b_ng, &m->b_h,
                       &m->b_hq, &m->b_hs, &m->b_eo, &m->b_shared, &m->b_sh_h, &m->b_sh_hq,
-                      &m->b_sh_hs, &m->b_ids, &m->b_tab};
+                      &m->b_sh_hs, &m->b_ids, &m->b_tab, &m->b_t13, &m->b_t2};
     for (DevBuf *b : bufs) b->release();
     for (cudaEvent_t e : m->ev) cudaEventDestroy(e);
     delete m;
@@ -263,6 +348,17 @@ ApusCudaMoe *apus_cuda_moe_get(const ApusMoeW *w) {
     ApusCudaMoe *m = apus_cuda_moe_create(w, 0, w->E);
     if (m) c.moes[w->gate_w] = m;
     return m;
+}
+
+/* 1 = tcgen05 block-scaled kernel on the reference weight storage, 0 = the
+ * mma.sync kernel on the re-tiled copy.  Returns the setting now in force. */
+int apus_cuda_moe_use_tc(ApusCudaMoe *m, int enable) {
+    if (!m) return -1;
+    if (enable >= 0 && m->raw) {
+        bool on = enable != 0;
+        if (on != m->use_tc) { m->use_tc = on; m->cap_r = 0; }    // act maps are rebuilt by ensure()
+    }
+    return m->use_tc ? 1 : 0;
 }
 
 void apus_cuda_moe_timing(ApusCudaMoe *m, int enable) {
@@ -418,7 +514,13 @@ int apus_cuda_moe_forward(const ApusMoeW *w, const float *x, const int64_t *ids,
         if (interm->moe_shared) APUS_CUDA_OK(cudaMemcpyAsync(interm->moe_shared, m->b_shared.p, sd, cudaMemcpyDeviceToHost, c.stream));
     }
     APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    if (m->use_tc) {
+        int stt = gemm_tc_status(1);
+        APUS_REQUIRE(stt == 0, "moe_forward: a bounded wait expired inside the tcgen05 kernel (code %d)", stt);
+    }
     return 0;
 }
+
+int apus_cuda_kernel_status(int reset) { return gemm_tc_status(reset); }
 
 }  // extern "C"

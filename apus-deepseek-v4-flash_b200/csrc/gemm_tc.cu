@@ -1,0 +1,392 @@
+// MXFP4 expert GEMV/GEMM on the 5th-generation tensor cores (tcgen05).
+//
+// out[n, o] = sum over 32-wide K blocks of (dot32(E4M3 act codes, E2M1 weights)
+//             * act_scale[n, kb/4]) * 2^(wscale[o, kb] - 127)
+// (reference c/fp4.h:367-395) computed by `tcgen05.mma kind::mxf8f6f4
+// .block_scale`: the hardware expands the E2M1 codes, applies both UE8M0 scale
+// factors per 32-element block and accumulates in f32 in tensor memory, so no
+// CUDA-core work is spent per weight element.  Activation scales are powers
+// of two, so their f32 exponent byte is the UE8M0 scale.  The result differs
+// from the reference's sequential f32 fold only by summation order.
+//
+// Weights are read in the REFERENCE storage (packed nibbles [O, K/2], scales
+// [O, K/32]): a TMA tensor map of type 16U4_ALIGN16B unpacks 128x128-element
+// tiles into 128-byte swizzled shared-memory rows, 4.25 bits per weight cross
+// HBM.  Algorithmic bytes per 128-row tile and matrix: 128*K/2 + 128*K/32.
+//
+// One CTA = one 128-row output tile of one work item (a gate/up pair or a
+// single matrix) for up to 32 activation rows:
+//   warp 4      TMA producer: per 128-wide K chunk the weight tile(s) and the
+//               32 x 128 activation-code tile into a ring of shared-memory stages;
+//   warps 0-3   scale-factor loaders: per chunk, four UE8M0 bytes per weight row
+//               and per activation row, written to tensor memory in the layout
+//               the MMA expects (row 32*j + l in lane l, column j, replicated
+//               in the four 32-lane quadrants); afterwards the epilogue
+//               (TMEM -> registers -> BF16 round / SwiGLU -> global);
+//   warp 5      MMA issuer: four K=32 MMAs per chunk and matrix, scale-factor
+//               byte selected per MMA through the instruction descriptor.
+// mbarriers: full[s] (TMA bytes landed), sf_full[s] (scale factors stored),
+// empty[s] (MMAs of the stage retired, via tcgen05.commit), done.
+// Every wait is bounded; on expiry the CTA records a status word, drains and
+// frees its tensor memory instead of hanging.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace apus {
+
+namespace {
+
+constexpr int TC_THREADS = 192;
+constexpr int TC_N = 32;                 // activation rows per work item (MMA N)
+constexpr int TC_A_BYTES = 128 * 128;    // one weight tile in shared memory
+constexpr int TC_B_BYTES = TC_N * 128;
+constexpr int TC_TMEM_COLS = 128;
+constexpr int TC_COL_D0 = 0, TC_COL_D1 = 32, TC_COL_SF = 64, TC_SF_STRIDE = 12;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+
+__device__ int g_tc_status = 0;          // first failure code recorded by any CTA
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity; false on expiry or abort.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1,
+                                            uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+// K-major operand tile with 128-byte swizzled rows (8-row groups 1024 B apart).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (uint64_t)1 << 46;                            // descriptor version
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor, kind::mxf8f6f4 block-scaled: A = E2M1, B = E4M3, both
+// K-major, UE8M0 scales, M = 128, N = TC_N; sf ids pick the scale byte.
+__device__ __forceinline__ uint32_t umma_idesc(uint32_t a_sf, uint32_t b_sf) {
+    return (b_sf << 4) | (5u << 7) | (0u << 10) | ((uint32_t)(TC_N >> 3) << 17) | (1u << 23) |
+           ((uint32_t)(128 >> 4) << 24) | (a_sf << 29);
+}
+__device__ __forceinline__ void umma_mxf8f6f4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                              uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t a) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(a) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+          "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+          "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+          "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ float swiglu_tc(float gate, float up, float limit) {
+    float g = bf16_round(gate), u = bf16_round(up);
+    if (limit > 0.f) {
+        u = fminf(fmaxf(u, -limit), limit);
+        g = fminf(g, limit);
+    }
+    float sig = 1.0f / (1.0f + expf(-g));
+    return bf16_round(__fmul_rn(__fmul_rn(g, sig), u));
+}
+
+template <bool PAIR, int NS>
+__global__ void __launch_bounds__(TC_THREADS, 2)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int STAGE = TC_A_BYTES * (PAIR ? 2 : 1) + TC_B_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)NS * STAGE);
+    uint64_t *full = bars, *empty = bars + NS, *sf_full = bars + 2 * NS, *done = bars + 3 * NS;
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 3 * NS + 1);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
+
+    const int n_groups = a.n_groups_dev ? *a.n_groups_dev : a.n_groups;
+    if ((int)blockIdx.y >= n_groups) return;
+    const TcGroup grp = a.groups[blockIdx.y];
+    const int nrows = grp.nrows, row0 = grp.row0;
+    if (nrows <= 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = a.K, O = a.O, NC = K >> 7;
+    const int tile_row = grp.a_row + (int)blockIdx.x * 128;     // row in the weight slab
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 128); }
+        mbar_init(done, 1);
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {                                   // tensor-memory allocation (one warp)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(s_tmem)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *s_tmem;
+    int fail = 0;
+
+    if (warp == 4) {
+        // ---- TMA producer --------------------------------------------------------
+        if (lane == 0) {
+            for (int i = 0; i < NC && !fail; i++) {
+                const int s = i % NS;
+                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+                if (!mbar_wait(&empty[s], ph ^ 1u, s_abort)) { fail = 1; break; }
+                uint8_t *st = smem + (size_t)s * STAGE;
+                // the transaction count of a packed 4-bit tile is its global-memory size
+                // (64 B per row), not the 128 B per row it occupies in shared memory
+                mbar_expect_tx(&full[s], a.tx_bytes ? a.tx_bytes
+                                                    : (TC_A_BYTES / 2) * (PAIR ? 2 : 1) + TC_B_BYTES);
+                tma_load_2d(st, &tm_a, i * 128, tile_row, &full[s]);
+                if (PAIR) tma_load_2d(st + TC_A_BYTES, &tm_b, i * 128, tile_row, &full[s]);
+                tma_load_2d(st + TC_A_BYTES * (PAIR ? 2 : 1), &tm_x, i * 128, row0, &full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issuer -------------------------------------------------------------
+        if (lane == 0) {
+            for (int i = 0; i < NC && !fail; i++) {
+                const int s = i % NS;
+                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+                if (!mbar_wait(&full[s], ph, s_abort)) { fail = 2; break; }
+                if (!mbar_wait(&sf_full[s], ph, s_abort)) { fail = 5; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = smem_u32(smem + (size_t)s * STAGE);
+                const uint64_t da = umma_desc_sw128(sa);
+                const uint64_t db = umma_desc_sw128(sa + TC_A_BYTES);
+                const uint64_t dx = umma_desc_sw128(sa + TC_A_BYTES * (PAIR ? 2 : 1));
+                const uint32_t sf = tmem + TC_COL_SF + s * TC_SF_STRIDE;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t idesc = umma_idesc(j, j);
+                    const uint32_t acc = (i | j) ? 1u : 0u;
+                    umma_mxf8f6f4(tmem + TC_COL_D0, da + 2 * j, dx + 2 * j, idesc, sf, sf + 8, acc);
+                    if (PAIR) umma_mxf8f6f4(tmem + TC_COL_D1, db + 2 * j, dx + 2 * j, idesc, sf + 4, sf + 8, acc);
+                }
+                umma_commit(&empty[s]);
+            }
+            if (!fail) umma_commit(done);
+        }
+    } else {
+        // ---- scale-factor loaders (threads 0..127) -----------------------------------
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int nbk = K >> 5;                        // scale bytes per weight row
+        const uint8_t *sA = a.scales_a + (size_t)tile_row * nbk;
+        const uint8_t *sB = PAIR ? a.scales_b + (size_t)tile_row * nbk : nullptr;
+        const float *xs = a.ascales + (size_t)(row0 + lane) * NC;
+        const bool xrow_ok = lane < nrows;
+        // scale bytes are fetched four chunks (16 bytes per weight row) at a time and
+        // one batch ahead of their use, so that no global-memory latency sits
+        // between two stages
+        uint4 ca[4], cb[4], na[4], nb[4];
+        float4 cx = make_float4(0.f, 0.f, 0.f, 0.f), nx = cx;
+        auto load_batch = [&](int i4, uint4 (&ya)[4], uint4 (&yb)[4], float4 &yx) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                ya[j] = __ldg(reinterpret_cast<const uint4 *>(sA + (size_t)(32 * j + lane) * nbk) + i4);
+                if (PAIR) yb[j] = __ldg(reinterpret_cast<const uint4 *>(sB + (size_t)(32 * j + lane) * nbk) + i4);
+            }
+            if (xrow_ok) yx = __ldg(reinterpret_cast<const float4 *>(xs) + i4);
+        };
+        auto comp = [](const uint4 &v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; };
+        auto compf = [](const float4 &v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; };
+        const int NB4 = NC >> 2;                       // K is a multiple of 512 on this path
+        load_batch(0, ca, cb, cx);
+        for (int i4 = 0; i4 < NB4 && !fail; i4++) {
+            if (i4 + 1 < NB4) load_batch(i4 + 1, na, nb, nx);
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                const int i = i4 * 4 + cc;
+                const int s = i % NS;
+                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+                uint32_t xb = 0;
+                if (xrow_ok) xb = ((__float_as_uint(compf(cx, cc)) >> 23) & 0xffu) * 0x01010101u;
+                if (!mbar_wait(&empty[s], ph ^ 1u, s_abort)) { fail = 3; break; }
+                const uint32_t sf = tmem + lane_base + TC_COL_SF + s * TC_SF_STRIDE;
+                tmem_st4(sf, comp(ca[0], cc), comp(ca[1], cc), comp(ca[2], cc), comp(ca[3], cc));
+                if (PAIR) tmem_st4(sf + 4, comp(cb[0], cc), comp(cb[1], cc), comp(cb[2], cc), comp(cb[3], cc));
+                tmem_st1(sf + 8, xb);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&sf_full[s]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) { ca[j] = na[j]; if (PAIR) cb[j] = nb[j]; }
+            cx = nx;
+        }
+        // ---- epilogue ------------------------------------------------------------------
+        if (!fail && !mbar_wait(done, 0, s_abort)) fail = 4;
+        if (!fail) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t d0[32], d1[32];
+            tmem_ld32(tmem + lane_base + TC_COL_D0, d0);
+            if (PAIR) tmem_ld32(tmem + lane_base + TC_COL_D1, d1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const int o = (int)blockIdx.x * 128 + tid;
+            if (o < O) {
+#pragma unroll
+                for (int n = 0; n < TC_N; n++) {
+                    if (n >= nrows) break;
+                    const int dst = a.orow ? a.orow[row0 + n] : row0 + n;
+                    float v;
+                    if (PAIR) v = swiglu_tc(__uint_as_float(d0[n]), __uint_as_float(d1[n]), a.limit);
+                    else v = a.round_out ? bf16_round(__uint_as_float(d0[n])) : __uint_as_float(d0[n]);
+                    a.out[(size_t)dst * O + o] = v;
+                }
+            }
+        }
+    }
+    if (fail) {
+        *s_abort = 1;
+        atomicCAS(&g_tc_status, 0, fail);
+        // give copies already issued to this CTA's shared memory time to land
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS)
+                     : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+}  // namespace
+
+// Tensor map over packed E2M1 codes [rows, K/2] (K elements per row), 128x128 boxes.
+int tc_make_weight_map(void *out_map, const void *codes, long long rows, int K) {
+    EncodeTiledFn fn = encode_fn();
+    APUS_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from the driver");
+    APUS_REQUIRE(K % 128 == 0 && ((uintptr_t)codes & 31) == 0, "tensor map: K=%d / base alignment", K);
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    cuuint32_t box[2] = {128, 128}, estr[2] = {1, 1};
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(out_map), CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2,
+                    const_cast<void *>(codes), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    APUS_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(weights [%lld,%d]) failed: %d", rows, K, (int)r);
+    return 0;
+}
+
+// Tensor map over E4M3 activation codes [rows, K] bytes, 128 x 32 boxes.
+int tc_make_act_map(void *out_map, const void *codes, long long rows, int K) {
+    EncodeTiledFn fn = encode_fn();
+    APUS_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {128, TC_N}, estr[2] = {1, 1};
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(out_map), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                    const_cast<void *>(codes), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    APUS_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(acts [%lld,%d]) failed: %d", rows, K, (int)r);
+    return 0;
+}
+
+template <bool PAIR, int NS>
+static int launch_tc(const TcArgs &a, cudaStream_t st) {
+    constexpr int STAGE = TC_A_BYTES * (PAIR ? 2 : 1) + TC_B_BYTES;
+    const size_t smem = (size_t)NS * STAGE + 1024 + 256;
+    auto kern = gemm_tc_kernel<PAIR, NS>;
+    static bool configured = false;
+    if (!configured) {
+        APUS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    dim3 grid((unsigned)(a.O / 128), (unsigned)a.n_groups);
+    kern<<<grid, TC_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
+                                        *reinterpret_cast<const CUtensorMap *>(a.pair ? a.map_b : a.map_a),
+                                        *reinterpret_cast<const CUtensorMap *>(a.map_x), a);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+int gemm_tc(const TcArgs &a, cudaStream_t st) {
+    APUS_REQUIRE(a.K % 512 == 0 && a.O % 128 == 0, "gemm_tc: unsupported shape O=%d K=%d", a.O, a.K);
+    if (a.n_groups <= 0) return 0;
+    return a.pair ? launch_tc<true, 3>(a, st) : launch_tc<false, 5>(a, st);
+}
+
+// Status word of the bounded waits (0 = no failure since the last reset).
+int gemm_tc_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v) {
+        int z = 0;
+        cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace apus

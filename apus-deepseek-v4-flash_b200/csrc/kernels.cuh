@@ -58,6 +58,30 @@ struct GemmSmallArgs {
 };
 int gemm_small(const GemmSmallArgs &a, cudaStream_t st);
 
+// ---- tcgen05 MXFP4 GEMM on the reference weight storage (gemm_tc.cu) ---------------------
+struct TcGroup {
+    int a_row;                // first row of this work item's matrix in the weight slab
+    int row0, nrows;          // activation rows [row0, row0+nrows) in sorted order, nrows <= 32
+    int pad;
+};
+struct TcArgs {
+    const void *map_a, *map_b, *map_x;   // host pointers to CUtensorMap objects (weights A/B, act codes)
+    const uint8_t *scales_a, *scales_b;  // weight scale slabs, reference layout [rows, K/32]
+    const float *ascales;                // activation scales [*, K/128], rows in sorted order
+    const TcGroup *groups;
+    const int *n_groups_dev;
+    int n_groups;
+    int O, K, pair, round_out;
+    float limit;
+    const int *orow;                     // nullable: output row of sorted position p
+    float *out;
+    int tx_bytes;                        // 0 = default transaction bytes per stage
+};
+int gemm_tc(const TcArgs &a, cudaStream_t st);
+int gemm_tc_status(int reset);
+int tc_make_weight_map(void *out_map, const void *codes, long long rows, int K);
+int tc_make_act_map(void *out_map, const void *codes, long long rows, int K);
+
 // ---- dense f32 / bf16 linears (linear.cu) ------------------------------------------------
 // out[m,o] = sum_k x[m,k]*w[o,k]; flags as APUS_CUDA_R_IN/R_OUT/W_BF16.
 int f32_linear(const void *w, const float *x, float *out, int M, int K, int O,
@@ -79,7 +103,7 @@ struct MoeSlab {            // where expert e's tiled tensors live
 int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int row_div, int n_rout,
               const MoeSlab &slab, int chunk, int *sorted_pos, int *sorted_row,
               GemmGroup *g13, GemmGroup *g2, int *n_groups, int max_groups,
-              cudaStream_t st);
+              cudaStream_t st, TcGroup *t13 = nullptr, TcGroup *t2 = nullptr, int o13 = 0, int o2 = 0);
 // y[t] = sum_j wgt[t,j]*eo[t*topk+j] (j order) ; out = bf16(y + shared).
 int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
                 int topk, int dim, float *out, float *routed, cudaStream_t st);

@@ -114,7 +114,8 @@ __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ row, int row_div,
                  int n, MoeSlab slab, int chunk, int *__restrict__ sorted_pos,
                  int *__restrict__ sorted_row, GemmGroup *__restrict__ g13,
-                 GemmGroup *__restrict__ g2, int *__restrict__ n_groups, int max_groups) {
+                 GemmGroup *__restrict__ g2, int *__restrict__ n_groups, int max_groups,
+                 TcGroup *__restrict__ t13, TcGroup *__restrict__ t2, int o13, int o2) {
     __shared__ int s_cnt[1024], s_off[1024], s_goff[1024];
     __shared__ int s_eid[GROUP_SMEM_N];
     __shared__ int s_wsum[32], s_wgsum[32];
@@ -162,7 +163,10 @@ moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ ro
                 if (lane >= o) { jc += tc; jg += tg; }
             }
             s_wsum[lane] = jc - wc; s_wgsum[lane] = jg - wg;
-            if (lane == 31) *n_groups = jg < max_groups ? jg : max_groups;
+            if (lane == 31) {
+                n_groups[0] = jg < max_groups ? jg : max_groups;
+                n_groups[1] = jc;                  // routings that are local
+            }
         }
         __syncthreads();
         if (tid < nE) { s_off[tid] = s_wsum[warp] + ic - c; s_goff[tid] = s_wgsum[warp] + ig - g; }
@@ -209,6 +213,10 @@ moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ ro
             b.wb = nullptr; b.sb = nullptr;
             b.row0 = a.row0; b.nrows = a.nrows;
             g13[gi] = a; g2[gi] = b;
+            if (t13) {
+                TcGroup u = {le * o13, a.row0, a.nrows, 0}, v = {le * o2, a.row0, a.nrows, 0};
+                t13[gi] = u; t2[gi] = v;
+            }
         }
     }
 }
@@ -216,11 +224,11 @@ moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ ro
 int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int row_div, int n_rout,
               const MoeSlab &slab, int chunk, int *sorted_pos, int *sorted_row,
               GemmGroup *g13, GemmGroup *g2, int *n_groups, int max_groups,
-              cudaStream_t st) {
+              cudaStream_t st, TcGroup *t13, TcGroup *t2, int o13, int o2) {
     APUS_REQUIRE(slab.e_hi - slab.e_lo <= 1024, "moe_group: more than 1024 local experts");
     APUS_REQUIRE(rout_row || row_div > 0, "moe_group: no row mapping");
     moe_group_kernel<<<1, 1024, 0, st>>>(rout_eid, rout_row, row_div, n_rout, slab, chunk, sorted_pos,
-                                         sorted_row, g13, g2, n_groups, max_groups);
+                                         sorted_row, g13, g2, n_groups, max_groups, t13, t2, o13, o2);
     APUS_LAUNCHED();
     return 0;
 }

@@ -307,7 +307,9 @@ def main():
             "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": world * T * W.dim * 4,
                     "d2h_bytes_per_step": world * T * W.dim * 4},
             "gpu_launches": launches,
-            "roofline": {"kernel": "gemm_small_kernel<MXFP4, pair> (expert gate/up GEMV + SwiGLU)",
+            "roofline": {"kernel": ("gemm_tc_kernel<pair> (tcgen05 block-scaled MXFP4 expert gate/up GEMV + SwiGLU)"
+                                    if L.apus_cuda_moe_use_tc(handle, -1) == 1 else
+                                    "gemm_small_kernel<MXFP4, pair> (mma.sync expert gate/up GEMV + SwiGLU)"),
                          "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,
                          "traffic": None, "launches": nl.value,

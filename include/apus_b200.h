@@ -123,6 +123,11 @@ int  apus_cuda_fill_hooks(ApusCudaHooks *hooks, size_t struct_dtype_off,
                           size_t struct_data_off);
 /* Message of the most recent failure on the calling thread ("" if none). */
 const char *apus_cuda_last_error(void);
+/* Device-side waits (mbarriers of the TMA/tcgen05 pipeline) are bounded: when one
+ * expires the kernel records a code, frees its tensor memory and returns
+ * instead of hanging.  Returns the first code recorded since the last reset
+ * (0 = none); synchronises the device. */
+int apus_cuda_kernel_status(int reset);
 /* Forget the cached device copy of a weight buffer (the reference frees and
  * reuses host addresses between tests, tests/m7b/README.md:90-94). */
 void apus_cuda_forget(const void *host_ptr);
@@ -152,6 +157,12 @@ int apus_cuda_fp8_gemm(const uint8_t *w, const uint8_t *ws,
 int apus_cuda_fp4_gemm(const uint8_t *w, const uint8_t *ws,
                        const uint8_t *acodes, const float *as, float *out,
                        int M, int O, int K);
+/* c/fp4.h:166 apus_fp4_gemm_mt again, on the tcgen05 block-scaled tensor-core
+ * path: the weights stay in the reference storage ([O,K/2] nibbles, [O,K/32]
+ * scales) and are unpacked by TMA.  O and K multiples of 128. */
+int apus_cuda_fp4_gemm_tc(const uint8_t *w, const uint8_t *ws,
+                          const uint8_t *acodes, const float *as, float *out,
+                          int M, int O, int K);
 /* c/fp4.h:190 apus_fp4_gemm_mt_grouped: several same-(O,K) GEMMs sharing one
  * activation row space of `rows` rows (rows = max(m0+M) over the entries). */
 int apus_cuda_fp4_gemm_grouped(const ApusFp4GemmEnt *ents, size_t n_ent,
@@ -236,6 +247,12 @@ uint64_t apus_cuda_moe_bytes(const ApusCudaMoe *m);
  * apus_cuda_disable / apus_cuda_forget(w->gate_w).  Lets a caller mix the
  * host-pointer call with the *_dev calls on one resident copy of the weights. */
 ApusCudaMoe *apus_cuda_moe_get(const ApusMoeW *w);
+/* Selects the routed-expert kernel of this sublayer: 1 = tcgen05 block-scaled
+ * MMA with TMA-unpacked weights in the reference storage (default when the
+ * shapes are multiples of 128; APUS_MOE_TC=0 in the environment disables it at
+ * creation), 0 = the mma.sync kernel on the re-tiled copy; a negative value
+ * only queries.  Returns the setting in force.  Both compute c/moe.h:333-350. */
+int apus_cuda_moe_use_tc(ApusCudaMoe *m, int enable);
 /* Per-kernel timing of the two expert GEMM launches (gate/up pair, down) with
  * CUDA events on the launching stream — the counterpart of the reference's
  * dispatch counters (c/backend_metal.h:93-97) for roofline reporting.
