@@ -56,6 +56,47 @@ class MoeInterm(C.Structure):
                 ("moe_routed", C.c_void_p), ("moe_shared", C.c_void_p)]
 
 
+class AttnCfg(C.Structure):
+    """ApusAttnCfg (c/attn.h:114-122)."""
+    _fields_ = [(n, C.c_int) for n in ("dim", "n_heads", "head_dim", "rope_dim", "q_lora", "o_groups",
+                                        "o_lora", "window", "ratio", "has_indexer", "idx_heads",
+                                        "idx_dim", "idx_topk")] + [("eps", C.c_float), ("max_pos", C.c_int)]
+
+
+class CompW(C.Structure):
+    """ApusCompW (c/attn.h:126-130)."""
+    _fields_ = [("wkv", C.c_void_p), ("wgate", C.c_void_p), ("ape", C.c_void_p), ("norm", C.c_void_p),
+                ("ratio", C.c_int), ("overlap", C.c_int), ("d", C.c_int), ("rd", C.c_int),
+                ("rotate", C.c_int), ("eps", C.c_float)]
+
+
+class AttnW(C.Structure):
+    """ApusAttnW (c/attn.h:132-143)."""
+    _fields_ = [("wq_a", QW), ("wq_b", QW), ("wkv", QW), ("wo_b", QW), ("wo_a", C.c_void_p),
+                ("q_norm", C.c_void_p), ("kv_norm", C.c_void_p), ("sink", C.c_void_p),
+                ("comp", CompW), ("idx_comp", CompW), ("idx_wq_b", QW), ("idx_wproj", C.c_void_p)]
+
+
+class CompS(C.Structure):
+    """ApusCompS (c/attn.h:147-153)."""
+    _fields_ = [("rows", C.c_int), ("cols", C.c_int), ("kv", C.c_void_p), ("sc", C.c_void_p),
+                ("cache", C.c_void_p), ("nb", C.c_int), ("max_nb", C.c_int), ("d", C.c_int),
+                ("cap", C.c_int)]
+
+
+class AttnS(C.Structure):
+    """ApusAttnS (c/attn.h:155-160)."""
+    _fields_ = [("pos", C.c_int64), ("win", C.c_void_p), ("comp", CompS), ("idx_comp", CompS)]
+
+
+class AttnInterm(C.Structure):
+    """ApusAttnInterm (c/attn.h:168-173)."""
+    _fields_ = [("q", C.c_void_p), ("win_kv", C.c_void_p), ("comp_kv", C.c_void_p),
+                ("idx_comp_kv", C.c_void_p), ("idx_scores", C.c_void_p), ("idx_topk", C.c_void_p),
+                ("attn_out", C.c_void_p), ("o_out", C.c_void_p), ("comp_nb", C.c_int),
+                ("idx_nb", C.c_int), ("idx_k", C.c_int)]
+
+
 class Fp4GemmEnt(C.Structure):
     """ApusFp4GemmEnt (c/fp4.h:184-188)."""
     _fields_ = [("w", C.c_void_p), ("ws", C.c_void_p), ("out", C.c_void_p),
@@ -123,6 +164,12 @@ def load(path=LIB_PATH):
         "apus_cuda_router_score": (ci, [C.POINTER(MoeW), vp, ci, vp, vp]),
         "apus_cuda_moe_forward": (ci, [C.POINTER(MoeW), vp, vp, ci, vp, C.POINTER(MoeInterm)]),
         "apus_cuda_sparse_attn": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, i64, vp]),
+        "apus_cuda_attention": (ci, [C.POINTER(AttnCfg), C.POINTER(AttnW), C.POINTER(AttnS), vp, ci, i64,
+                                    vp, vp, vp, C.POINTER(AttnInterm)]),
+        "apus_cuda_apply_rope": (ci, [vp, vp, vp, ci, ci, ci, ci]),
+        "apus_cuda_hadamard": (ci, [vp, ci, ci]),
+        "apus_cuda_fp8_qat_sim": (ci, [vp, ci, ci, ci]),
+        "apus_cuda_fp4_qat_sim": (ci, [vp, ci, ci]),
         "apus_cuda_mhc_prepost": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, vp, vp, ci]),
         "apus_cuda_hc_pre": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, cf, vp, vp, vp, vp, ci]),
         "apus_cuda_hc_pre_noalloc_dev": (ci, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, cf, vp, vp, vp, vp, ci, vp]),

@@ -1,0 +1,330 @@
+// C ABI, part 3: the attention sublayer (include/apus_b200.h; reference
+// c/attn.h:1515-1740) and its row helpers.
+//
+// A token is one fixed sequence of kernels on the backend stream — low-rank q
+// path, window KV, (CSA) indexer with its own compressor and stable top-k,
+// ring write, attention compressor, index-gathered attention with sink,
+// inverse RoPE, grouped o-projection — in the reference's call order, because
+// the indexer and the two compressors mutate the sequence state.  The host
+// knows the position, so every data-independent decision (does this token
+// complete a compressed block, how many entries exist) is taken on the host
+// and no kernel result is read back inside a step.
+#include <math.h>
+#include <vector>
+
+#include "runtime.cuh"
+
+using namespace apus;
+
+namespace {
+
+struct CompDev {
+    const float *wkv = nullptr, *wgate = nullptr, *ape = nullptr, *norm = nullptr;
+    int ratio = 0, overlap = 0, d = 0, rd = 0, rotate = 0;
+    float eps = 0.f;
+};
+struct CompStateDev {
+    DevBuf kv, sc, cache;
+    int nb = 0;
+};
+struct AttnDev {
+    ApusAttnCfg cfg;
+    DevQW *wq_a, *wq_b, *wkv, *wo_b, *idx_wq_b;
+    const uint16_t *wo_a;
+    const float *q_norm, *kv_norm, *sink, *idx_wproj;
+    CompDev comp, idx_comp;
+};
+
+int comp_weights(const ApusCompW &h, int dim, CompDev *d) {
+    const int cd = (1 + h.overlap) * h.d;
+    d->ratio = h.ratio; d->overlap = h.overlap; d->d = h.d; d->rd = h.rd; d->rotate = h.rotate; d->eps = h.eps;
+    d->wkv = (const float *)cached_dense(h.wkv, (size_t)cd * dim * 4);
+    d->wgate = (const float *)cached_dense(h.wgate, (size_t)cd * dim * 4);
+    d->ape = (const float *)cached_dense(h.ape, (size_t)h.ratio * cd * 4);
+    d->norm = (const float *)cached_dense(h.norm, (size_t)h.d * 4);
+    return (d->wkv && d->wgate && d->ape && d->norm) ? 0 : 1;
+}
+
+int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A) {
+    const int hd = cfg->n_heads * cfg->head_dim, G = cfg->o_groups;
+    A->cfg = *cfg;
+    A->wq_a = cached_qw(8, w->wq_a.codes, w->wq_a.scales, cfg->q_lora, cfg->dim);
+    A->wq_b = cached_qw(8, w->wq_b.codes, w->wq_b.scales, hd, cfg->q_lora);
+    A->wkv = cached_qw(8, w->wkv.codes, w->wkv.scales, cfg->head_dim, cfg->dim);
+    A->wo_b = cached_qw(8, w->wo_b.codes, w->wo_b.scales, cfg->dim, G * cfg->o_lora);
+    if (!A->wq_a || !A->wq_b || !A->wkv || !A->wo_b) return 1;
+    A->wo_a = (const uint16_t *)cached_dense(w->wo_a, (size_t)G * cfg->o_lora * (hd / G) * 2);
+    A->q_norm = (const float *)cached_dense(w->q_norm, (size_t)cfg->q_lora * 4);
+    A->kv_norm = (const float *)cached_dense(w->kv_norm, (size_t)cfg->head_dim * 4);
+    A->sink = (const float *)cached_dense(w->sink, (size_t)cfg->n_heads * 4);
+    if (!A->wo_a || !A->q_norm || !A->kv_norm || !A->sink) return 1;
+    A->idx_wq_b = nullptr; A->idx_wproj = nullptr;
+    if (cfg->ratio && comp_weights(w->comp, cfg->dim, &A->comp)) return 1;
+    if (cfg->ratio && cfg->has_indexer) {
+        if (comp_weights(w->idx_comp, cfg->dim, &A->idx_comp)) return 1;
+        A->idx_wq_b = cached_qw(8, w->idx_wq_b.codes, w->idx_wq_b.scales, cfg->idx_heads * cfg->idx_dim,
+                                cfg->q_lora);
+        A->idx_wproj = (const float *)cached_dense(w->idx_wproj, (size_t)cfg->idx_heads * cfg->dim * 4);
+        if (!A->idx_wq_b || !A->idx_wproj) return 1;
+    }
+    return 0;
+}
+
+// Device mirror of one sequence's state (host-pointer tier: refreshed per call).
+struct StateDev {
+    DevBuf win;
+    CompStateDev comp, idx;
+};
+StateDev g_state;
+DevBuf g_ws[24];
+
+struct StepBufs {
+    float *qa, *qr, *q, *kva, *kv, *iq, *ckv, *csc, *pooled, *wt, *scores, *o, *y;
+    uint8_t *xq;
+    float *xs;
+    int32_t *sel, *idxs;
+};
+
+int step_bufs(const ApusAttnCfg &c, long long max_nb, StepBufs *b) {
+    const int hd = c.n_heads * c.head_dim;
+    int kmax = c.dim;
+    if (c.q_lora > kmax) kmax = c.q_lora;
+    if (c.o_groups * c.o_lora > kmax) kmax = c.o_groups * c.o_lora;
+    const size_t cdmax = 2 * (size_t)(c.head_dim > c.idx_dim ? c.head_dim : c.idx_dim);
+    const size_t idxw = (size_t)c.window + (size_t)(c.has_indexer ? c.idx_topk : max_nb) + 8;
+    void *p[17];
+    size_t sz[17] = {(size_t)c.q_lora * 4, (size_t)c.q_lora * 4, (size_t)hd * 4, (size_t)c.head_dim * 4,
+                     (size_t)c.head_dim * 4, (size_t)(c.idx_heads * c.idx_dim + 4) * 4, cdmax * 4, cdmax * 4,
+                     cdmax * 4, (size_t)(c.idx_heads + 4) * 4, (size_t)(max_nb + 8) * 4, (size_t)hd * 4,
+                     (size_t)c.o_groups * c.o_lora * 4, (size_t)kmax, (size_t)(kmax / 128 + 1) * 4,
+                     (size_t)(c.idx_topk + 8) * 4, idxw * 4};
+    for (int i = 0; i < 17; i++)
+        if (g_ws[i].get(sz[i], &p[i])) return 1;
+    b->qa = (float *)p[0]; b->qr = (float *)p[1]; b->q = (float *)p[2]; b->kva = (float *)p[3];
+    b->kv = (float *)p[4]; b->iq = (float *)p[5]; b->ckv = (float *)p[6]; b->csc = (float *)p[7];
+    b->pooled = (float *)p[8]; b->wt = (float *)p[9]; b->scores = (float *)p[10]; b->o = (float *)p[11];
+    b->y = (float *)p[12]; b->xq = (uint8_t *)p[13]; b->xs = (float *)p[14]; b->sel = (int32_t *)p[15];
+    b->idxs = (int32_t *)p[16];
+    return 0;
+}
+
+// One compressor decode step; appends a finished entry to the cache when the
+// block completes (reference c/attn.h:960-1008 + 797-819).
+int compressor_step(const CompDev &W, CompStateDev &S, const float *x, int dim, long long pos,
+                    const float *cs_rp, int half2, const StepBufs &b, cudaStream_t st) {
+    const int cd = (1 + W.overlap) * W.d;
+    if (f32_linear(W.wkv, x, b.ckv, 1, dim, cd, 0, st) || f32_linear(W.wgate, x, b.csc, 1, dim, cd, 0, st))
+        return 1;
+    const int slot = (int)(pos % W.ratio);
+    const int should = (pos + 1) % W.ratio == 0;
+    if (comp_step(S.kv.as<float>(), S.sc.as<float>(), 0, b.ckv, b.csc, cd, W.ape, W.ratio, W.overlap, W.d,
+                  slot, should, b.pooled, W.d, 1, st))
+        return 1;
+    if (should) {
+        int flags = ROW_BF16_IN | ROW_RMS_W | ROW_ROPE | ROW_BF16_OUT |
+                    (W.rotate ? (ROW_HADAMARD | ROW_FP4QAT) : ROW_FP8QAT);
+        if (row_ops(b.pooled, W.d, S.cache.as<float>() + (size_t)S.nb * W.d, W.d, 1, W.d, flags, W.norm,
+                    W.eps, W.rd, cs_rp, 1, half2, st))
+            return 1;
+        S.nb++;
+    }
+    return 0;
+}
+
+int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
+              const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st) {
+    const ApusAttnCfg &c = A.cfg;
+    const int h = c.n_heads, d = c.head_dim, rd = c.rope_dim, half2 = rd, win = c.window, ratio = c.ratio;
+    const int hd = h * d;
+    // q path (c/attn.h:1525-1548)
+    if (qlinear_dev(A.wq_a, x, b.qa, 1, b.xq, b.xs, true, st)) return 1;
+    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, 1, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st))
+        return 1;
+    if (qlinear_dev(A.wq_b, b.qr, b.q, 1, b.xq, b.xs, true, st)) return 1;
+    if (row_ops(b.q, d, b.q, d, h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, h, 0, st)) return 1;
+    // window KV (c/attn.h:1552-1569)
+    if (qlinear_dev(A.wkv, x, b.kva, 1, b.xq, b.xs, true, st)) return 1;
+    if (row_ops(b.kva, d, b.kv, d, 1, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd,
+                cs_pos, 1, 0, st))
+        return 1;
+    // compressed ids: the indexer runs BEFORE the ring write and the attention compressor
+    int compw = 0;
+    const int32_t *sel = nullptr;
+    if (ratio) {
+        const long long nbs = (pos + 1) / ratio;
+        if (c.has_indexer) {
+            const int ih = c.idx_heads, idm = c.idx_dim;
+            if (qlinear_dev(A.idx_wq_b, b.qr, b.iq, 1, b.xq, b.xs, true, st)) return 1;
+            if (row_ops(b.iq, idm, b.iq, idm, ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr,
+                        0.f, rd, cs_pos, ih, 0, st))
+                return 1;
+            if (compressor_step(A.idx_comp, S.idx, x, c.dim, pos, cs_rp, half2, b, st)) return 1;
+            if (f32_linear(A.idx_wproj, x, b.wt, 1, c.dim, ih, APUS_CUDA_R_IN | APUS_CUDA_R_OUT, st)) return 1;
+            const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
+            compw = (int)(c.idx_topk < nbs ? c.idx_topk : nbs);
+            if (compw > 0) {
+                if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), nbs, ih, idm, b.scores, st)) return 1;
+                if (topk_stable(b.scores, (int)nbs, compw, b.sel, 1, st)) return 1;
+                sel = b.sel;
+            }
+        } else {
+            compw = (int)nbs;
+        }
+    }
+    if (idx_k_out) *idx_k_out = compw;
+    // ring write, attention compressor (c/attn.h:1642-1665)
+    APUS_CUDA_OK(cudaMemcpyAsync(S.win.as<float>() + (size_t)(pos % win) * d, b.kv, (size_t)d * 4,
+                                 cudaMemcpyDeviceToDevice, st));
+    if (ratio && compressor_step(A.comp, S.comp, x, c.dim, pos, cs_rp, half2, b, st)) return 1;
+    // gathered attention over ring ++ compressed cache, inverse RoPE
+    if (build_idx(b.idxs, win, pos, sel, compw, st)) return 1;
+    const float scale = (float)pow((double)d, -0.5);
+    if (sparse_attn(b.q, A.sink, h, d, b.idxs, win + compw, 1, scale, S.win.p, win,
+                    ratio ? S.comp.cache.p : nullptr, ratio ? S.comp.nb : 0, 0, b.o, st))
+        return 1;
+    if (row_ops(b.o, d, b.o, d, h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs_pos, h, 0, st)) return 1;
+    // grouped low-rank o-projection (c/attn.h:1692-1737)
+    const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
+    if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, 1, sub, ol,
+                           APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT, st))
+        return 1;
+    return qlinear_dev(A.wo_b, b.y, out, 1, b.xq, b.xs, true, st);
+}
+
+int upload_comp(const ApusCompS &h, CompStateDev &d, int extra, cudaStream_t st) {
+    const size_t sb = (size_t)h.rows * h.cols * 4;
+    if (d.kv.get(sb, nullptr) || d.sc.get(sb, nullptr) || d.cache.get((size_t)(h.nb + extra + 1) * h.d * 4, nullptr))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(d.kv.p, h.kv, sb, cudaMemcpyHostToDevice, st));
+    APUS_CUDA_OK(cudaMemcpyAsync(d.sc.p, h.sc, sb, cudaMemcpyHostToDevice, st));
+    if (h.nb) APUS_CUDA_OK(cudaMemcpyAsync(d.cache.p, h.cache, (size_t)h.nb * h.d * 4, cudaMemcpyHostToDevice, st));
+    d.nb = h.nb;
+    return 0;
+}
+
+int download_comp(ApusCompS &h, const CompStateDev &d, cudaStream_t st) {
+    const size_t sb = (size_t)h.rows * h.cols * 4;
+    APUS_REQUIRE(d.nb <= h.cap, "attention: the host compressed cache holds %d entries but %d are needed", h.cap, d.nb);
+    APUS_CUDA_OK(cudaMemcpyAsync(h.kv, d.kv.p, sb, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaMemcpyAsync(h.sc, d.sc.p, sb, cudaMemcpyDeviceToHost, st));
+    if (d.nb > h.nb)
+        APUS_CUDA_OK(cudaMemcpyAsync(h.cache + (size_t)h.nb * h.d, (const float *)d.cache.p + (size_t)h.nb * h.d,
+                                     (size_t)(d.nb - h.nb) * h.d * 4, cudaMemcpyDeviceToHost, st));
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int apus_cuda_attention(const ApusAttnCfg *cfg, const ApusAttnW *w, ApusAttnS *st, const float *x, int s,
+                        int64_t start_pos, const float *cos, const float *sin, float *out,
+                        ApusAttnInterm *interm) {
+    if (ensure_enabled()) return 1;
+    if (s <= 0) return 0;
+    APUS_REQUIRE(cfg->head_dim <= 1024 && cfg->q_lora <= 1024 && cfg->head_dim % 32 == 0 && cfg->q_lora % 128 == 0 &&
+                 cfg->dim % 128 == 0 && (cfg->o_groups * cfg->o_lora) % 128 == 0 && cfg->rope_dim % 2 == 0,
+                 "attention: unsupported dimensions");
+    Ctx &c = ctx();
+    cudaStream_t sm = c.stream;
+    AttnDev A;
+    if (attn_weights(cfg, w, &A)) return 1;
+    const int d = cfg->head_dim, win = cfg->window, ratio = cfg->ratio, half = cfg->rope_dim / 2;
+    const int hd = cfg->n_heads * d;
+    const long long max_nb = ratio ? (start_pos + s) / ratio + 2 : 0;
+    StepBufs b;
+    if (step_bufs(*cfg, max_nb, &b)) return 1;
+    // state in
+    if (g_state.win.get((size_t)win * d * 4, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(g_state.win.p, st->win, (size_t)win * d * 4, cudaMemcpyHostToDevice, sm));
+    const int extra = ratio ? s / ratio + 2 : 0;
+    if (ratio && upload_comp(st->comp, g_state.comp, extra, sm)) return 1;
+    if (ratio && cfg->has_indexer && upload_comp(st->idx_comp, g_state.idx, extra, sm)) return 1;
+    // rope rows: per token [cos | sin] at its position and at the first position of the block it completes
+    std::vector<float> cs((size_t)s * 4 * half, 0.f);
+    for (int t = 0; t < s; t++) {
+        const int64_t pos = start_pos + t, rp = ratio ? pos + 1 - ratio : -1;
+        memcpy(&cs[(size_t)t * 4 * half], cos + pos * half, half * 4);
+        memcpy(&cs[(size_t)t * 4 * half + half], sin + pos * half, half * 4);
+        if (rp >= 0) {
+            memcpy(&cs[(size_t)t * 4 * half + 2 * half], cos + rp * half, half * 4);
+            memcpy(&cs[(size_t)t * 4 * half + 3 * half], sin + rp * half, half * 4);
+        }
+    }
+    void *dcs, *dx, *dout;
+    if (g_ws[17].get(cs.size() * 4, &dcs) || g_ws[18].get((size_t)s * cfg->dim * 4, &dx) ||
+        g_ws[19].get((size_t)s * cfg->dim * 4, &dout))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dcs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, sm));
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)s * cfg->dim * 4, cudaMemcpyHostToDevice, sm));
+    const int nb0 = ratio ? st->comp.nb : 0, inb0 = (ratio && cfg->has_indexer) ? st->idx_comp.nb : 0;
+    for (int t = 0; t < s; t++) {
+        const float *cs_pos = (const float *)dcs + (size_t)t * 4 * half;
+        int idx_k = 0;
+        if (attn_step(A, g_state, (const float *)dx + (size_t)t * cfg->dim, start_pos + t, cs_pos, cs_pos + 2 * half,
+                      (float *)dout + (size_t)t * cfg->dim, b, &idx_k, sm))
+            return 1;
+        if (interm) {
+            if (interm->q) APUS_CUDA_OK(cudaMemcpyAsync(interm->q + (size_t)t * hd, b.q, (size_t)hd * 4, cudaMemcpyDeviceToHost, sm));
+            if (interm->win_kv) APUS_CUDA_OK(cudaMemcpyAsync(interm->win_kv + (size_t)t * d, b.kv, (size_t)d * 4, cudaMemcpyDeviceToHost, sm));
+            if (interm->attn_out) APUS_CUDA_OK(cudaMemcpyAsync(interm->attn_out + (size_t)t * hd, b.o, (size_t)hd * 4, cudaMemcpyDeviceToHost, sm));
+            if (interm->idx_topk && idx_k && cfg->has_indexer)
+                APUS_CUDA_OK(cudaMemcpyAsync(interm->idx_topk + (size_t)t * cfg->idx_topk, b.idxs + win, (size_t)idx_k * 4,
+                                             cudaMemcpyDeviceToHost, sm));
+            interm->idx_k = idx_k;
+            // the step buffers are reused by the next token
+            if (interm->q || interm->win_kv || interm->attn_out || interm->idx_topk) APUS_CUDA_OK(cudaStreamSynchronize(sm));
+        }
+    }
+    APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)s * cfg->dim * 4, cudaMemcpyDeviceToHost, sm));
+    if (interm && interm->o_out)
+        APUS_CUDA_OK(cudaMemcpyAsync(interm->o_out, dout, (size_t)s * cfg->dim * 4, cudaMemcpyDeviceToHost, sm));
+    // state out
+    APUS_CUDA_OK(cudaMemcpyAsync(st->win, g_state.win.p, (size_t)win * d * 4, cudaMemcpyDeviceToHost, sm));
+    if (ratio) {
+        if (download_comp(st->comp, g_state.comp, sm)) return 1;
+        if (cfg->has_indexer && download_comp(st->idx_comp, g_state.idx, sm)) return 1;
+    }
+    APUS_CUDA_OK(cudaStreamSynchronize(sm));
+    if (ratio) {
+        st->comp.nb = g_state.comp.nb;
+        if (cfg->has_indexer) st->idx_comp.nb = g_state.idx.nb;
+        if (interm) { interm->comp_nb = st->comp.nb - nb0; interm->idx_nb = cfg->has_indexer ? st->idx_comp.nb - inb0 : 0; }
+    }
+    return 0;
+}
+
+// ---- row helpers (c/attn.h:76-90) -------------------------------------------------------------
+static int rows_host(float *x, int n, int rows, int flags, int rd, const float *cos, const float *sin) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    Ctx &c = ctx();
+    void *dx, *dcs = nullptr;
+    if (g_ws[20].get((size_t)rows * n * 4, &dx)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)rows * n * 4, cudaMemcpyHostToDevice, c.stream));
+    if (cos) {
+        const int half = rd / 2;
+        std::vector<float> cs((size_t)rd);
+        memcpy(cs.data(), cos, half * 4);
+        memcpy(cs.data() + half, sin, half * 4);
+        if (g_ws[21].get((size_t)rd * 4, &dcs)) return 1;
+        APUS_CUDA_OK(cudaMemcpyAsync(dcs, cs.data(), (size_t)rd * 4, cudaMemcpyHostToDevice, c.stream));
+        APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    }
+    if (row_ops((float *)dx, n, (float *)dx, n, rows, n, flags, nullptr, 0.f, rd, (const float *)dcs, rows, 0, c.stream))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(x, dx, (size_t)rows * n * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
+int apus_cuda_apply_rope(float *x, const float *cos, const float *sin, int n, int rd, int inverse, int rows) {
+    return rows_host(x, n, rows, inverse ? ROW_ROPE_INV : ROW_ROPE, rd, cos, sin);
+}
+int apus_cuda_hadamard(float *x, int n, int rows) { return rows_host(x, n, rows, ROW_HADAMARD, 0, nullptr, nullptr); }
+int apus_cuda_fp8_qat_sim(float *x, int n, int K, int rows) {
+    return rows_host(x, n, rows, ROW_FP8QAT, n - K, nullptr, nullptr);
+}
+int apus_cuda_fp4_qat_sim(float *x, int n, int rows) { return rows_host(x, n, rows, ROW_FP4QAT, 0, nullptr, nullptr); }
+
+}  // extern "C"

@@ -1,0 +1,264 @@
+// Row-wise numerics helpers of the attention sublayer and the compressor /
+// indexer steps.  Every kernel reproduces the reference's per-element
+// operation sequence (separately rounded multiply and add where the reference
+// is built without contraction, BF16 rounds at the same points); only the
+// sums of squares are tree reductions.
+//
+// Reference: c/attn.h:290-299 (RoPE), 301-311 (Hadamard), 325-369 (FP8 / FP4
+// quant-dequant), 371-378 (RMSNorm), 797-819 (compressor finish), 892-1011
+// (compressor decode step), 1027-1067 (indexer q prep and scores),
+// 1356-1388 (q norm + RoPE, window KV finish), 692-737 (index sets).
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace apus {
+
+// ---- one row per CTA: [bf16 in] -> [rms] -> [rope] -> [hadamard] -> [qat] -> [bf16 out] ----
+__device__ __forceinline__ float fp4_qat_value(float y) {
+    // E2M1 round-to-nearest-even of |y| <= 6 (reference c/attn.h:342-348)
+    float a = fabsf(y);
+    const float T[7] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.0f};
+    const float V[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+    int mag = 0;
+#pragma unroll
+    for (int j = 0; j < 7; j++) mag += (a > T[j]) || (a == T[j] && (j & 1));
+    float v = V[mag];
+    return (signbit(y) && mag) ? -v : v;      // the table entry of code 8 is +0
+}
+
+__global__ void __launch_bounds__(1024)
+row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y, int y_stride, int n,
+               int flags, const float *__restrict__ norm_w, float eps, int rd,
+               const float *__restrict__ cs, int rows_per_cs, int cs_stride) {
+    extern __shared__ float s_v[];            // [n] row, then [n/32 + 32] scratch
+    float *s_red = s_v + n;
+    const int row = blockIdx.x, i = threadIdx.x;
+    const bool on = i < n;
+    float v = on ? x[(size_t)row * x_stride + i] : 0.f;
+    if (flags & ROW_BF16_IN) v = bf16_round(v);
+    if (flags & (ROW_RMS_W | ROW_RMS_PLAIN)) {
+        float ss = warp_sum(on ? __fmul_rn(v, v) : 0.f);
+        if ((i & 31) == 0) s_red[i >> 5] = ss;
+        __syncthreads();
+        if (i < 32) {
+            float t = i < (int)(blockDim.x >> 5) ? s_red[i] : 0.f;
+            t = warp_sum(t);
+            if (i == 0) s_red[0] = t;
+        }
+        __syncthreads();
+        float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(s_red[0], (float)n), eps)));
+        if (flags & ROW_RMS_W) v = bf16_round(__fmul_rn(norm_w[on ? i : 0], __fmul_rn(v, inv)));
+        else v = bf16_round(__fmul_rn(v, inv));
+        __syncthreads();
+    }
+    s_v[on ? i : 0] = on ? v : s_v[0];
+    __syncthreads();
+    if (flags & (ROW_ROPE | ROW_ROPE_INV)) {
+        const int half = rd >> 1;
+        if (i < half) {
+            const float *c = cs + (size_t)(row / rows_per_cs) * cs_stride;
+            float co = c[i], si = c[half + i];
+            if (flags & ROW_ROPE_INV) si = -si;
+            float x1 = s_v[n - rd + 2 * i], x2 = s_v[n - rd + 2 * i + 1];
+            s_v[n - rd + 2 * i] = bf16_round(__fsub_rn(__fmul_rn(x1, co), __fmul_rn(x2, si)));
+            s_v[n - rd + 2 * i + 1] = bf16_round(__fadd_rn(__fmul_rn(x1, si), __fmul_rn(x2, co)));
+        }
+        __syncthreads();
+    }
+    if (flags & ROW_HADAMARD) {
+        for (int len = 1; len < n; len <<= 1) {
+            float a = 0.f, b = 0.f;
+            const bool lo = on && !(i & len);
+            if (lo) { a = s_v[i]; b = s_v[i + len]; }
+            __syncthreads();
+            if (lo) { s_v[i] = __fadd_rn(a, b); s_v[i + len] = __fsub_rn(a, b); }
+            __syncthreads();
+        }
+        const float inv = (float)pow((double)n, -0.5);
+        if (on) s_v[i] = bf16_round(__fmul_rn(s_v[i], inv));
+        __syncthreads();
+    }
+    v = on ? s_v[i] : 0.f;
+    if (flags & ROW_FP8QAT) {
+        // groups of 64 over the first n - rd elements
+        const int lim = n - rd;
+        unsigned *s_amax = reinterpret_cast<unsigned *>(s_red);
+        if (i < (lim + 63) / 64) s_amax[i] = 0u;
+        __syncthreads();
+        if (i < lim) atomicMax(&s_amax[i >> 6], __float_as_uint(fabsf(v)));
+        __syncthreads();
+        if (i < lim) {
+            float amax = fmaxf(__uint_as_float(s_amax[i >> 6]), 1e-4f);
+            float s = ceil_pow2(__fmul_rn(amax, 1.0f / 448.0f));
+            uint16_t c2 = e4m3x2_from_f32(__fdiv_rn(v, s), 0.f);
+            v = __fmul_rn(e4m3_to_f32(c2 & 0xffu), s);
+        }
+    }
+    if (flags & ROW_FP4QAT) {
+        float amax = warp_max(on ? fabsf(v) : 0.f);     // 32-element groups = warps
+        amax = fmaxf(amax, 7.05484372e-38f);
+        float s = ceil_pow2(__fmul_rn(amax, 1.0f / 6.0f));
+        float q = __fdiv_rn(v, s);
+        q = fminf(fmaxf(q, -6.0f), 6.0f);
+        v = __fmul_rn(fp4_qat_value(q), s);
+    }
+    if (flags & ROW_BF16_OUT) v = bf16_round(v);
+    if (on) y[(size_t)row * y_stride + i] = v;
+}
+
+int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
+            const float *norm_w, float eps, int rd, const float *cs, int rows_per_cs, int cs_stride,
+            cudaStream_t st) {
+    APUS_REQUIRE(n >= 32 && n <= 1024 && n % 32 == 0, "row_ops: n=%d unsupported", n);
+    APUS_REQUIRE(!(flags & ROW_HADAMARD) || (n & (n - 1)) == 0, "row_ops: Hadamard needs a power of two, n=%d", n);
+    if (rows <= 0) return 0;
+    size_t smem = (size_t)(n + 64) * sizeof(float);
+    row_ops_kernel<<<rows, n, smem, st>>>(x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
+                                          rows_per_cs > 0 ? rows_per_cs : 1, cs_stride);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// ---- compressor decode step (reference c/attn.h:960-1008) ---------------------------------
+// One CTA per sequence, one thread per state column (cd = coff*d).
+//   write: state row (overlap ? ratio + slot : slot) <- kv_new, score_new + ape[slot]
+//   pool (when the block completes): per channel c < d a softmax over the ne
+//     candidate rows (sequential, in row order), weighted sum -> pooled[c]
+//   shift (overlap only): rows [ratio, 2*ratio) -> [0, ratio)
+__global__ void __launch_bounds__(1024)
+comp_step_kernel(float *__restrict__ kv_state, float *__restrict__ sc_state, long long state_stride,
+                 const float *__restrict__ kv_new, const float *__restrict__ sc_new, int new_stride,
+                 const float *__restrict__ ape, int ratio, int overlap, int d, int slot, int should,
+                 float *__restrict__ pooled, int pooled_stride) {
+    const int seq = blockIdx.x, c = threadIdx.x;
+    const int cd = (1 + overlap) * d;
+    float *kvs = kv_state + (size_t)seq * state_stride;
+    float *scs = sc_state + (size_t)seq * state_stride;
+    const int wrow = overlap ? ratio + slot : slot;
+    if (c < cd) {
+        kvs[(size_t)wrow * cd + c] = kv_new[(size_t)seq * new_stride + c];
+        scs[(size_t)wrow * cd + c] = __fadd_rn(sc_new[(size_t)seq * new_stride + c], ape[(size_t)slot * cd + c]);
+    }
+    if (!should) return;
+    __syncthreads();
+    const int ne = overlap ? 2 * ratio : ratio;
+    if (c < d) {
+        float mx = -INFINITY;
+        for (int e = 0; e < ne; e++) {
+            float p = (overlap && e >= ratio) ? scs[(size_t)e * cd + d + c] : scs[(size_t)e * cd + c];
+            mx = fmaxf(mx, p);
+        }
+        float sum = 0.f;
+        for (int e = 0; e < ne; e++) {
+            float p = (overlap && e >= ratio) ? scs[(size_t)e * cd + d + c] : scs[(size_t)e * cd + c];
+            sum = __fadd_rn(sum, expf(__fsub_rn(p, mx)));
+        }
+        float acc = 0.f;
+        for (int e = 0; e < ne; e++) {
+            const size_t off = (overlap && e >= ratio) ? (size_t)e * cd + d + c : (size_t)e * cd + c;
+            float p = expf(__fsub_rn(scs[off], mx));
+            acc = __fadd_rn(acc, __fmul_rn(kvs[off], __fdiv_rn(p, sum)));
+        }
+        pooled[(size_t)seq * pooled_stride + c] = acc;
+    }
+    if (overlap) {
+        __syncthreads();
+        if (c < cd)
+            for (int e = 0; e < ratio; e++) {
+                kvs[(size_t)e * cd + c] = kvs[(size_t)(ratio + e) * cd + c];
+                scs[(size_t)e * cd + c] = scs[(size_t)(ratio + e) * cd + c];
+            }
+    }
+}
+
+int comp_step(float *kv_state, float *sc_state, long long state_stride, const float *kv_new,
+              const float *sc_new, int new_stride, const float *ape, int ratio, int overlap, int d,
+              int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st) {
+    const int cd = (1 + overlap) * d;
+    APUS_REQUIRE(cd <= 1024, "compressor: state width %d exceeds 1024", cd);
+    if (n_seq <= 0) return 0;
+    comp_step_kernel<<<n_seq, ((cd + 31) / 32) * 32, 0, st>>>(kv_state, sc_state, state_stride, kv_new,
+                                                              sc_new, new_stride, ape, ratio, overlap, d,
+                                                              slot, should, pooled, pooled_stride);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// ---- indexer scores (reference c/attn.h:1049-1067) ---------------------------------------------
+// score[b] = bf16( sum_h bf16( relu(bf16(q_h . k_b)) * w_h ) ), heads summed in order.
+// CTA = ih threads x IDX_B cache entries; each thread computes one (head, entry)
+// dot sequentially in k order with separately rounded multiply and add, then one
+// thread per entry adds the per-head terms in head order.
+#define IDX_B 4
+__global__ void __launch_bounds__(64 * IDX_B)
+idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, float wscale,
+                 const float *__restrict__ cache, long long nb, int ih, int idm, float *__restrict__ sc) {
+    extern __shared__ float sm[];             // q [ih*idm], k [IDX_B*idm], terms [IDX_B*ih]
+    float *s_q = sm, *s_k = sm + ih * idm, *s_t = s_k + IDX_B * idm;
+    const int hh = threadIdx.x % ih, bl = threadIdx.x / ih;
+    const long long b = (long long)blockIdx.x * IDX_B + bl;
+    for (int i = threadIdx.x; i < ih * idm; i += blockDim.x) s_q[i] = q[i];
+    for (int i = threadIdx.x; i < IDX_B * idm; i += blockDim.x) {
+        long long bb = (long long)blockIdx.x * IDX_B + i / idm;
+        s_k[i] = bb < nb ? cache[bb * idm + i % idm] : 0.f;
+    }
+    __syncthreads();
+    const float *qv = s_q + hh * idm, *kv = s_k + bl * idm;
+    float dot = 0.f;
+    for (int i = 0; i < idm; i++) dot = __fadd_rn(dot, __fmul_rn(qv[i], kv[i]));
+    dot = bf16_round(dot);
+    // head weight: bf16(bf16_linear(x) * idm^-0.5 * ih^-0.5) (reference c/attn.h:1133-1135)
+    const float w = bf16_round(__fmul_rn(wt_raw[hh], wscale));
+    float v = dot > 0.f ? __fmul_rn(dot, w) : 0.f;
+    s_t[bl * ih + hh] = bf16_round(v);
+    __syncthreads();
+    if (hh == 0 && b < nb) {
+        float acc = 0.f;
+        for (int h2 = 0; h2 < ih; h2++) acc = __fadd_rn(acc, s_t[bl * ih + h2]);
+        sc[b] = bf16_round(acc);
+    }
+}
+
+int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long nb,
+               int ih, int idm, float *sc, cudaStream_t st) {
+    APUS_REQUIRE(ih <= 64 && ih >= 1, "indexer: %d heads unsupported", ih);
+    if (nb <= 0) return 0;
+    size_t smem = ((size_t)ih * idm + IDX_B * idm + IDX_B * ih) * sizeof(float);
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        APUS_CUDA_OK(cudaFuncSetAttribute(idx_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    idx_score_kernel<<<(unsigned)((nb + IDX_B - 1) / IDX_B), ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, nb,
+                                                                                    ih, idm, sc);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// ---- index set of one decode step (reference c/attn.h:692-737) -------------------------------------
+// row = [window ids in ring order] ++ [compressed ids + win]; comp ids either the
+// indexer's top-k (sel != NULL) or the dense list 0..compw-1.
+__global__ void build_idx_kernel(int32_t *__restrict__ out, int win, long long pos,
+                                 const int32_t *__restrict__ sel, int compw) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < win) {
+        int v;
+        if (pos >= win - 1) {
+            int sp = (int)(pos % win);
+            v = j < win - 1 - sp ? sp + 1 + j : j - (win - 1 - sp);
+        } else {
+            v = j <= pos ? j : -1;
+        }
+        out[j] = v;
+    } else if (j < win + compw) {
+        out[j] = (sel ? sel[j - win] : j - win) + win;
+    }
+}
+
+int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, cudaStream_t st) {
+    build_idx_kernel<<<ceil_div(win + compw, 256), 256, 0, st>>>(out, win, pos, sel, compw);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+}  // namespace apus

@@ -86,6 +86,11 @@ int tc_make_act_map(void *out_map, const void *codes, long long rows, int K);
 // out[m,o] = sum_k x[m,k]*w[o,k]; flags as APUS_CUDA_R_IN/R_OUT/W_BF16.
 int f32_linear(const void *w, const float *x, float *out, int M, int K, int O,
                int flags, cudaStream_t st);
+// `batch` independent problems: problem b uses w + b*w_stride (elements of w's
+// type), x + b*x_stride with rows x_ld apart, out + b*out_stride with rows out_ld apart.
+int f32_linear_batched(const void *w, long long w_stride, const float *x, long long x_stride, int x_ld,
+                       float *out, long long out_stride, int out_ld, int batch, int M, int K, int O,
+                       int flags, cudaStream_t st);
 
 // ---- MoE glue (moe.cu) ---------------------------------------------------------------------
 // sqrtsoftplus of gate logits, bias, stable top-k or hash lookup, weights.
@@ -115,6 +120,29 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
                 int kv_bf16, float *o, cudaStream_t st);
+
+// ---- attention row helpers, compressor and indexer steps (attn_ops.cu) -----------------------
+enum {
+    ROW_BF16_IN = 1,      // BF16-round the input
+    ROW_RMS_W = 2,        // y = bf16(w * (x * rsqrt(mean x^2 + eps)))
+    ROW_RMS_PLAIN = 4,    // y = bf16(x * rsqrt(mean x^2 + eps))
+    ROW_ROPE = 8,         // interleaved-pair rotation of the last rd elements, BF16 out
+    ROW_ROPE_INV = 16,    // the conjugate rotation
+    ROW_HADAMARD = 32,    // Sylvester butterflies * n^-1/2, BF16 out
+    ROW_FP8QAT = 64,      // E4M3 quant-dequant per 64 on the first n - rd elements
+    ROW_FP4QAT = 128,     // E2M1 quant-dequant per 32
+    ROW_BF16_OUT = 256
+};
+// cs: per position [cos(half) | sin(half)]; row r uses cs + (r / rows_per_cs) * cs_stride.
+int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
+            const float *norm_w, float eps, int rd, const float *cs, int rows_per_cs, int cs_stride,
+            cudaStream_t st);
+int comp_step(float *kv_state, float *sc_state, long long state_stride, const float *kv_new,
+              const float *sc_new, int new_stride, const float *ape, int ratio, int overlap, int d,
+              int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st);
+int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long nb,
+               int ih, int idm, float *sc, cudaStream_t st);
+int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, cudaStream_t st);
 
 // ---- mHC (mhc.cu) -----------------------------------------------------------------------------------
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,

@@ -75,6 +75,56 @@ typedef struct {
 } ApusMoeInterm;
 #endif
 
+#ifndef APUS_ATTN_H
+/* c/attn.h:114-122 */
+typedef struct {
+    int dim, n_heads, head_dim, rope_dim, q_lora, o_groups, o_lora;
+    int window, ratio;              /* ratio == 0 => sliding window only */
+    int has_indexer;                /* ratio == 4 */
+    int idx_heads, idx_dim, idx_topk;
+    float eps;
+    int max_pos;
+} ApusAttnCfg;
+/* c/attn.h:126-130 — compressor weights: wkv/wgate [coff*d, dim] f32, ape
+ * [ratio, coff*d], norm [d]; coff = 1 + overlap. */
+typedef struct {
+    const float *wkv, *wgate, *ape, *norm;
+    int ratio, overlap, d, rd, rotate;
+    float eps;
+} ApusCompW;
+/* c/attn.h:132-143 */
+typedef struct {
+    ApusFp8W wq_a, wq_b, wkv, wo_b;
+    const uint16_t *wo_a;   /* [G*o_lora, h*d/G] BF16 bits */
+    const float *q_norm, *kv_norm, *sink;
+    ApusCompW comp, idx_comp;
+    ApusFp8W idx_wq_b;
+    const float *idx_wproj; /* [idx_heads, dim] */
+} ApusAttnW;
+/* c/attn.h:147-153 — compressor state: carries kv/sc [rows, cols] (sc starts at
+ * -inf), cache [cap, d] of finished entries, nb entries valid. */
+typedef struct {
+    int rows, cols;
+    float *kv, *sc;
+    float *cache;
+    int nb, max_nb, d;
+    int cap;
+} ApusCompS;
+/* c/attn.h:155-160 */
+typedef struct {
+    int64_t pos;
+    float *win;             /* [window, head_dim] ring */
+    ApusCompS comp, idx_comp;
+} ApusAttnS;
+/* c/attn.h:168-173 — optional named intermediates. */
+typedef struct {
+    float *q, *win_kv, *comp_kv, *idx_comp_kv, *idx_scores;
+    int32_t *idx_topk;
+    float *attn_out, *o_out;
+    int comp_nb, idx_nb, idx_k;
+} ApusAttnInterm;
+#endif
+
 #ifndef APUS_FP4_H
 /* c/fp4.h:184-188 — one entry of a grouped MXFP4 GEMM. */
 typedef struct {
@@ -204,6 +254,28 @@ int apus_cuda_sparse_attn(const float *q, const float *sink, int h, int d,
                           const int32_t *idxs, int idxw, int s, float scale,
                           const float *kv_a, int64_t na, const float *kv_b,
                           int64_t nb, float *o);
+/* c/attn.h:178 apus_attention: the attention sublayer for s tokens of ONE
+ * sequence starting at start_pos; x [s,dim], out [s,dim]; cos/sin are the
+ * layer's rope tables [>= start_pos+s, rope_dim/2]; `st` is the caller's host
+ * state, read at entry and updated at exit exactly as the reference mutates it
+ * (ring row(s), compressor carries, appended cache entries, nb; the caches
+ * must have room: cap >= nb + new entries).  Tokens are processed as
+ * consecutive decode steps, which the reference defines to be equal to its
+ * batched prefill (tests/m4c chunk invariance).  interm: q, win_kv, attn_out,
+ * o_out, comp_nb, idx_nb and (decode form: offsets relative to the ring)
+ * idx_topk / idx_k are filled when non-NULL; the other members are ignored. */
+int apus_cuda_attention(const ApusAttnCfg *cfg, const ApusAttnW *w,
+                        ApusAttnS *st, const float *x, int s,
+                        int64_t start_pos, const float *cos, const float *sin,
+                        float *out, ApusAttnInterm *interm);
+/* c/attn.h:76-90 row helpers on `rows` rows of n (stride n): apus_apply_rope
+ * on the last rd elements with one cos/sin row [rd/2] each, apus_hadamard,
+ * apus_fp8_qat_sim (per `group` = 64 on the first K elements), apus_fp4_qat_sim. */
+int apus_cuda_apply_rope(float *x, const float *cos, const float *sin, int n,
+                         int rd, int inverse, int rows);
+int apus_cuda_hadamard(float *x, int n, int rows);
+int apus_cuda_fp8_qat_sim(float *x, int n, int K, int rows);
+int apus_cuda_fp4_qat_sim(float *x, int n, int rows);
 /* c/mhc.h:103 apus_mhc_prepost_scalar for `rows` tokens (x4 [rows, n*d]). */
 int apus_cuda_mhc_prepost(const float *x4, size_t d, size_t n,
                           const float *fn, const float *scale,

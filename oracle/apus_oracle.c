@@ -46,7 +46,7 @@ float ora_ue8m0(uint8_t b) {
 
 /* c/fp4.h:204-207 — E2M1 value table, bit 3 is the sign. */
 static const float E2M1[16] = { 0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f,
-                                -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f };
+                                0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f };
 
 /* c/fp4.h:255-260 — E4M3 code to f32 (codes 0x7f/0xff give +-480). */
 float ora_e4m3_to_f32(uint8_t c) {
@@ -483,4 +483,63 @@ void ora_mhc_head(const float *x4, size_t d, size_t n, const float *fn,
     for (size_t j = 0; j < n; j++) pre[j] = sigm(pre[j] * scale + base[j]) + hc_eps;
     ora_mhc_collapse(x4, pre, y, d, n);
     free(pre);
+}
+
+/* ---- attention row helpers ------------------------------------------------------- */
+
+/* c/attn.h:290-299 — interleaved-pair rotation of rd floats, each output BF16-
+ * rounded; inverse = conjugate. Products and the sum are rounded separately. */
+void ora_apply_rope(float *x, const float *cos, const float *sin, int rd, int inverse) {
+    for (int j = 0; j < rd / 2; j++) {
+        float a = x[2 * j], b = x[2 * j + 1], c = cos[j], s = inverse ? -sin[j] : sin[j];
+        float ac = a * c, bs = b * s, as = a * s, bc = b * c;
+        x[2 * j] = ora_bf16_round(ac - bs);
+        x[2 * j + 1] = ora_bf16_round(as + bc);
+    }
+}
+
+/* c/attn.h:301-311 — Sylvester butterflies, then * n^-1/2 and BF16 round. */
+void ora_hadamard(float *x, int n) {
+    for (int len = 1; len < n; len *= 2)
+        for (int i = 0; i < n; i++)
+            if (!(i & len)) {
+                float a = x[i], b = x[i + len];
+                x[i] = a + b;
+                x[i + len] = a - b;
+            }
+    float inv = (float)pow((double)n, -0.5);
+    for (int i = 0; i < n; i++) x[i] = ora_bf16_round(x[i] * inv);
+}
+
+/* c/attn.h:325-339 — E4M3 quantise-dequantise per `group` with a power-of-two
+ * scale (amax floored at 1e-4). */
+void ora_fp8_qat_sim(float *x, size_t K, size_t group) {
+    for (size_t g0 = 0; g0 < K; g0 += group) {
+        size_t g1 = g0 + group < K ? g0 + group : K;
+        float amax = 0.0f;
+        for (size_t i = g0; i < g1; i++) if (fabsf(x[i]) > amax) amax = fabsf(x[i]);
+        if (amax < 1e-4f) amax = 1e-4f;
+        float s = ceil_pow2(amax * (1.0f / 448.0f));
+        for (size_t i = g0; i < g1; i++) x[i] = ora_e4m3_to_f32(ora_e4m3_from_f32(x[i] / s)) * s;
+    }
+}
+
+/* c/attn.h:342-369 — E2M1 quantise-dequantise per 32 (amax floor 6*2^-126,
+ * clamp +-6, ties to the even code). */
+void ora_fp4_qat_sim(float *x, size_t K) {
+    static const float cut[7] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.0f};
+    for (size_t g0 = 0; g0 < K; g0 += 32) {
+        float amax = 0.0f;
+        for (size_t i = g0; i < g0 + 32; i++) if (fabsf(x[i]) > amax) amax = fabsf(x[i]);
+        if (amax < 7.05484372e-38f) amax = 7.05484372e-38f;
+        float s = ceil_pow2(amax * (1.0f / 6.0f));
+        for (size_t i = g0; i < g0 + 32; i++) {
+            float y = x[i] / s;
+            y = y > 6.0f ? 6.0f : (y < -6.0f ? -6.0f : y);
+            float a = fabsf(y);
+            int mag = 0;
+            for (int j = 0; j < 7; j++) mag += (a > cut[j]) || (a == cut[j] && (j & 1));
+            x[i] = E2M1[signbit(y) ? (mag | 8) : mag] * s;
+        }
+    }
 }

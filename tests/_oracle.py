@@ -59,6 +59,10 @@ def ora():
             "ora_mhc_collapse": (None, [vp, vp, vp, sz, sz]),
             "ora_mhc_apply": (None, [vp, vp, vp, vp, vp, sz, sz]),
             "ora_mhc_head": (None, [vp, sz, sz, vp, cf, vp, cf, cf, vp]),
+            "ora_apply_rope": (None, [vp, vp, vp, ci, ci]),
+            "ora_hadamard": (None, [vp, ci]),
+            "ora_fp8_qat_sim": (None, [vp, sz, sz]),
+            "ora_fp4_qat_sim": (None, [vp, sz]),
         }
         for n, (r, a) in sig.items():
             f = getattr(L, n)
@@ -103,6 +107,10 @@ def ref():
             "ref_expert_swiglu": (None, [vp, vp, vp, sz, cf]),
             "ref_sparse_attn": (None, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, vp]),
             "apus_mhc_sinkhorn": (None, [vp, sz, ci, cf]),
+            "apus_apply_rope": (None, [vp, vp, vp, ci, ci]),
+            "apus_hadamard": (None, [vp, ci]),
+            "apus_fp8_qat_sim": (None, [vp, sz, sz]),
+            "apus_fp4_qat_sim": (None, [vp, sz]),
             "apus_mhc_prepost_scalar": (None, [vp, sz, sz, vp, vp, vp, cf, cf, ci, vp, vp, vp, vp]),
             "apus_mhc_collapse_scalar": (None, [vp, vp, vp, sz, sz]),
             "apus_mhc_apply_scalar": (None, [vp, vp, vp, vp, vp, sz, sz]),

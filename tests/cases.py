@@ -97,3 +97,103 @@ def mhc_case(seed, rows, d, n=4):
     f = synth.activations(rng, rows, d)
     norm_w = (1.0 + 0.05 * rng.standard_normal(d)).astype(np.float32)
     return dict(x4=x4, fn=fn, scale=scale, base=base, hfn=hfn, hbase=hbase, f=f, norm_w=norm_w)
+
+
+# ---- attention sublayer ------------------------------------------------------------------
+ATTN_DIMS = dict(dim=256, n_heads=4, head_dim=128, rope_dim=64, q_lora=128, o_groups=2, o_lora=128,
+                 window=8, idx_heads=4, idx_dim=128, idx_topk=4, max_pos=256)
+
+
+class AttnLayer:
+    """Synthetic weights + ctypes views of one attention sublayer (reference
+    c/attn.h:114-143).  kind: 'swa' (ratio 0), 'csa' (ratio 4 + indexer),
+    'hca' (dense compressed attention, ratio 8 here instead of 128 so that a
+    short sequence completes several blocks)."""
+
+    def __init__(self, seed, kind, dims=None):
+        from apus_b200 import capi
+        D = dict(ATTN_DIMS)
+        D.update(dims or {})
+        self.D, self.kind = D, kind
+        rng = np.random.default_rng(seed)
+        ratio = {"swa": 0, "csa": 4, "hca": 8}[kind]
+        self.ratio = ratio
+        dim, h, d, ql = D["dim"], D["n_heads"], D["head_dim"], D["q_lora"]
+        G, ol, ih, idm = D["o_groups"], D["o_lora"], D["idx_heads"], D["idx_dim"]
+        hd = h * d
+        f8 = lambda O, K, std: synth.fp8_weight(rng, O, K, std=std)
+        self.wq_a, self.wq_b = f8(ql, dim, 0.06), f8(hd, ql, 0.09)
+        self.wkv, self.wo_b = f8(d, dim, 0.06), f8(dim, G * ol, 0.06)
+        self.wo_a = synth.bf16_bits((rng.standard_normal((G * ol, hd // G)) * 0.04).astype(np.float32))
+        nrm = lambda n: (1 + 0.05 * rng.standard_normal(n)).astype(np.float32)
+        self.q_norm, self.kv_norm = nrm(ql), nrm(d)
+        self.sink = (rng.standard_normal(h) * 0.5).astype(np.float32)
+        bfw = lambda *s, std=0.05: synth.bf16_round((rng.standard_normal(s) * std).astype(np.float32))
+
+        def comp(dd, overlap):
+            cd = (1 + overlap) * dd
+            return dict(wkv=bfw(cd, dim), wgate=bfw(cd, dim), ape=(rng.standard_normal((max(ratio, 1), cd)) * 0.5
+                                                                ).astype(np.float32), norm=nrm(dd))
+        self.comp = comp(d, int(ratio == 4))
+        self.idx_comp = comp(idm, 1)
+        self.idx_wq_b = f8(ih * idm, ql, 0.09)
+        self.idx_wproj = bfw(ih, dim)
+        cfg = capi.AttnCfg(dim, h, d, D["rope_dim"], ql, G, ol, D["window"], ratio, int(kind == "csa"), ih, idm,
+                           D["idx_topk"], 1e-6, D["max_pos"])
+        w = capi.AttnW()
+        w.wq_a, w.wq_b = capi.qw(*self.wq_a, ql, dim), capi.qw(*self.wq_b, hd, ql)
+        w.wkv, w.wo_b = capi.qw(*self.wkv, d, dim), capi.qw(*self.wo_b, dim, G * ol)
+        w.wo_a, w.q_norm, w.kv_norm, w.sink = (capi.ptr(self.wo_a), capi.ptr(self.q_norm),
+                                               capi.ptr(self.kv_norm), capi.ptr(self.sink))
+
+        def cw(c, dd, overlap, rotate):
+            return capi.CompW(capi.ptr(c["wkv"]), capi.ptr(c["wgate"]), capi.ptr(c["ape"]), capi.ptr(c["norm"]),
+                              ratio, overlap, dd, D["rope_dim"], rotate, 1e-6)
+        w.comp = cw(self.comp, d, int(ratio == 4), 0)
+        w.idx_comp = cw(self.idx_comp, idm, 1, 1)
+        w.idx_wq_b = capi.qw(*self.idx_wq_b, ih * idm, ql)
+        w.idx_wproj = capi.ptr(self.idx_wproj)
+        self.cfg, self.w = cfg, w
+
+    def weight_ptrs(self):
+        """Host addresses the backend may have cached device copies for."""
+        arrs = [self.wq_a[0], self.wq_b[0], self.wkv[0], self.wo_b[0], self.wo_a, self.q_norm, self.kv_norm,
+                self.sink, self.idx_wq_b[0], self.idx_wproj]
+        for c in (self.comp, self.idx_comp):
+            arrs += [c["wkv"], c["wgate"], c["ape"], c["norm"]]
+        return arrs
+
+
+class AttnState:
+    """Host-side ApusAttnS built from numpy arrays (reference c/attn.h:747-760,
+    1494-1504)."""
+
+    def __init__(self, L):
+        from apus_b200 import capi
+        D, ratio = L.D, L.ratio
+        self.win = np.zeros((D["window"], D["head_dim"]), np.float32)
+        st = capi.AttnS()
+        st.pos = 0
+        st.win = capi.ptr(self.win)
+        self.keep = []
+
+        def comp(dd, overlap):
+            coff = 1 + overlap
+            rows, cols = coff * ratio, coff * dd
+            kv = np.zeros((rows, cols), np.float32)
+            sc = np.full((rows, cols), -np.inf, np.float32)
+            max_nb = D["max_pos"] // ratio + 2
+            cache = np.zeros((max_nb, dd), np.float32)
+            self.keep += [kv, sc, cache]
+            return capi.CompS(rows, cols, capi.ptr(kv), capi.ptr(sc), capi.ptr(cache), 0, max_nb, dd, max_nb), \
+                (kv, sc, cache)
+        if ratio:
+            st.comp, self.comp = comp(D["head_dim"], int(ratio == 4))
+            if L.kind == "csa":
+                st.idx_comp, self.idx = comp(D["idx_dim"], 1)
+        self.st = st
+
+
+def attn_inputs(seed, n_tokens, dim):
+    rng = np.random.default_rng(seed)
+    return synth.activations(rng, n_tokens, dim)

@@ -60,6 +60,50 @@ def ref_linear(L, fmt, c):
     return dict(out=out, acodes=codes, ascales=scales, raw=raw)
 
 
+def rope_tables(L, D, compressed):
+    """cos/sin [max_pos, rd/2] exactly as the reference's layers build them
+    (c/layer.h:147-149: plain theta 1e4 for sliding-window layers, YaRN factor 16
+    over 65536 with theta 1.6e5 for compressed ones)."""
+    half = D["rope_dim"] // 2
+    cos = np.empty((D["max_pos"], half), np.float32)
+    sin = np.empty((D["max_pos"], half), np.float32)
+    L.apus_rope_precompute.restype = None
+    L.apus_rope_precompute.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_double,
+                                       C.c_double, C.c_int, C.c_int]
+    if compressed:
+        L.apus_rope_precompute(P(cos), P(sin), D["rope_dim"], D["max_pos"], 65536, 160000.0, 16.0, 32, 1)
+    else:
+        L.apus_rope_precompute(P(cos), P(sin), D["rope_dim"], D["max_pos"], 0, 10000.0, 1.0, 32, 1)
+    return cos, sin
+
+
+def ref_attention(L, seed, kind, chunks):
+    """Runs the reference apus_attention over consecutive chunks of tokens
+    (first chunk = prefill at position 0, the rest single-token decodes or
+    mid-stream batches) and returns outputs + final state."""
+    Lyr = cases.AttnLayer(seed, kind)
+    S = cases.AttnState(Lyr)
+    D = Lyr.D
+    cos, sin = rope_tables(L, D, kind != "swa")
+    total = sum(chunks)
+    x = cases.attn_inputs(seed + 7, total, D["dim"])
+    out = np.empty((total, D["dim"]), np.float32)
+    L.apus_attention.restype = None
+    L.apus_attention.argtypes = [C.c_void_p] * 4 + [C.c_int, C.c_int64] + [C.c_void_p] * 4
+    pos = 0
+    for n in chunks:
+        L.apus_attention(C.byref(Lyr.cfg), C.byref(Lyr.w), C.byref(S.st), P(x[pos:pos + n]), n, pos, P(cos), P(sin),
+                         P(out[pos:pos + n]), None)
+        pos += n
+    r = dict(out=out, win=S.win.copy(), cos=cos, sin=sin)
+    if Lyr.ratio:
+        r.update(comp_kv=S.comp[0].copy(), comp_sc=S.comp[1].copy(),
+                 comp_cache=S.comp[2][:S.st.comp.nb].copy())
+        if kind == "csa":
+            r.update(idx_kv=S.idx[0].copy(), idx_sc=S.idx[1].copy(), idx_cache=S.idx[2][:S.st.idx_comp.nb].copy())
+    return r
+
+
 def main():
     L = ref()
     assert L is not None, "reference build not available"
@@ -132,6 +176,8 @@ def main():
             L.apus_rms_norm(P(yb[t]), P(c["norm_w"]), 1e-6, P(yn[t]), d)
         G.update({f"{tag}.pre": pre, f"{tag}.post": post, f"{tag}.comb": comb, f"{tag}.y": y,
                   f"{tag}.y4": y4, f"{tag}.yhead": yh, f"{tag}.ynorm": yn})
+    for tag, (seed, kind, chunks) in ATTN_LAYER_CASES.items():
+        G.update({f"{tag}.{k}": v for k, v in ref_attention(L, seed, kind, chunks).items()})
     np.savez_compressed(HERE / "ref_cases.npz", **G)
     print(f"wrote {len(G)} arrays; avx2 hits {L.ref_avx2_hits()}, threads {L.ref_pool_threads()}")
 
@@ -163,6 +209,13 @@ ATTN_CASES = {
     "attn_empty": (52, 2, 2, 64, 8, 8, 12, "empty"),
     "attn_dups": (53, 2, 3, 128, 0, 50, 33, "dups"),
     "attn_full": (54, 1, 2, 64, 128, 30, 140, "full"),
+}
+# tag -> (seed, layer kind, token chunks fed to apus_attention one call each)
+ATTN_LAYER_CASES = {
+    "attn_swa": (71, "swa", [11] + [1] * 9),
+    "attn_csa": (72, "csa", [13] + [1] * 14 + [3]),
+    "attn_hca": (73, "hca", [10] + [1] * 16),
+    "attn_csa_decode_only": (74, "csa", [1] * 26),
 }
 MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
 

@@ -273,3 +273,35 @@ def test_live_reference_linear(seed, fmt, M, O, K):
     (L.apus_fp4_linear if fmt == 4 else L.apus_fp8_linear)(C.byref(w), P(c["x"]), P(out), M, K, O)
     mine = ora_qlinear(0 if fmt == 4 else 1, c["codes"], c["scales"], c["x"], O)
     assert np.array_equal(mine.view(np.uint32), out.view(np.uint32))
+
+
+def row_helper_inputs():
+    rng = np.random.default_rng(99)
+    x = (rng.standard_normal((6, 128)) * rng.choice([1e-3, 1.0, 30.0], size=(6, 1))).astype(np.float32)
+    x[1, :32] = 0.0
+    x[2, 5] = -0.0
+    x[3, :8] = [6, -6, 0.25, 0.75, 1.25, 2.5, 3.5, 5.0]
+    cos = np.cos(rng.standard_normal(32)).astype(np.float32)
+    sin = np.sin(rng.standard_normal(32)).astype(np.float32)
+    return x, cos, sin
+
+
+@needs_ref
+def test_live_reference_row_helpers_bitwise():
+    L = ref()
+    x, cos, sin = row_helper_inputs()
+    for fn_o, fn_r, args in (("ora_hadamard", "apus_hadamard", (128,)),
+                             ("ora_fp8_qat_sim", "apus_fp8_qat_sim", (64, 64)),
+                             ("ora_fp8_qat_sim", "apus_fp8_qat_sim", (128, 64)),
+                             ("ora_fp4_qat_sim", "apus_fp4_qat_sim", (128,))):
+        a, b = x.copy(), x.copy()
+        for r in range(x.shape[0]):
+            getattr(ora(), fn_o)(P(a[r]), *args)
+            getattr(L, fn_r)(P(b[r]), *args)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), fn_o
+    for inv in (0, 1):
+        a, b = x.copy(), x.copy()
+        for r in range(x.shape[0]):
+            ora().ora_apply_rope(P(a[r, 64:]), P(cos), P(sin), 64, inv)
+            L.apus_apply_rope(P(b[r, 64:]), P(cos), P(sin), 64, inv)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
