@@ -97,6 +97,24 @@ class AttnInterm(C.Structure):
                 ("idx_nb", C.c_int), ("idx_k", C.c_int)]
 
 
+class LayerDesc(C.Structure):
+    """ApusCudaLayerDesc: what apus_block_forward reads of ApusLayer (c/layer.h:45-71)."""
+    _fields_ = [("acfg", AttnCfg), ("aw", AttnW), ("mw", MoeW),
+                ("attn_norm_w", C.c_void_p), ("ffn_norm_w", C.c_void_p),
+                ("hc_attn_fn", C.c_void_p), ("hc_attn_base", C.c_void_p), ("hc_attn_scale", C.c_void_p),
+                ("hc_ffn_fn", C.c_void_p), ("hc_ffn_base", C.c_void_p), ("hc_ffn_scale", C.c_void_p),
+                ("cos", C.c_void_p), ("sin", C.c_void_p), ("rope_rows", C.c_int)]
+
+
+class ModelDesc(C.Structure):
+    """ApusCudaModelDesc: top-level tensors and sizes (c/model.h:58-84)."""
+    _fields_ = [("n_layers", C.c_int), ("dim", C.c_int), ("hc_mult", C.c_int), ("hc_sinkhorn_iters", C.c_int),
+                ("vocab", C.c_int), ("hc_eps", C.c_float), ("norm_eps", C.c_float),
+                ("layers", C.POINTER(LayerDesc)), ("embed", C.c_void_p), ("embed_bf16", C.c_int),
+                ("head", C.c_void_p), ("head_bf16", C.c_int), ("norm_w", C.c_void_p),
+                ("hc_head_fn", C.c_void_p), ("hc_head_base", C.c_void_p), ("hc_head_scale", C.c_float)]
+
+
 class Fp4GemmEnt(C.Structure):
     """ApusFp4GemmEnt (c/fp4.h:184-188)."""
     _fields_ = [("w", C.c_void_p), ("ws", C.c_void_p), ("out", C.c_void_p),
@@ -166,6 +184,14 @@ def load(path=LIB_PATH):
         "apus_cuda_sparse_attn": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, i64, vp]),
         "apus_cuda_attention": (ci, [C.POINTER(AttnCfg), C.POINTER(AttnW), C.POINTER(AttnS), vp, ci, i64,
                                     vp, vp, vp, C.POINTER(AttnInterm)]),
+        "apus_cuda_set_sum_order": (ci, [ci]),
+        "apus_cuda_block_forward": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64]),
+        "apus_cuda_model_create": (vp, [C.POINTER(ModelDesc), ci, ci]),
+        "apus_cuda_model_destroy": (None, [vp]),
+        "apus_cuda_model_reset": (ci, [vp]),
+        "apus_cuda_model_pos": (i64, [vp]),
+        "apus_cuda_model_forward": (ci, [vp, vp, ci, vp, vp]),
+        "apus_cuda_model_generate": (ci, [vp, vp, ci, ci, vp, C.POINTER(cf), C.POINTER(cf)]),
         "apus_cuda_apply_rope": (ci, [vp, vp, vp, ci, ci, ci, ci]),
         "apus_cuda_hadamard": (ci, [vp, ci, ci]),
         "apus_cuda_fp8_qat_sim": (ci, [vp, ci, ci, ci]),

@@ -214,6 +214,22 @@ int expert_dev(DevQW *w1, DevQW *w2, DevQW *w3, float limit, const float *x, int
 using namespace apus;
 
 // =====================================================================================
+namespace apus {
+static std::vector<std::pair<void (*)(), void (*)(const void *)>> &release_hooks() {
+    static std::vector<std::pair<void (*)(), void (*)(const void *)>> v;
+    return v;
+}
+void on_disable(void (*release_all)(), void (*forget_one)(const void *)) {
+    release_hooks().push_back({release_all, forget_one});
+}
+}  // namespace apus
+
+namespace apus {
+static int g_sum_order = getenv("APUS_SUM_ORDER") && atoi(getenv("APUS_SUM_ORDER")) == 1 ? APUS_CUDA_SUM_TREE
+                                                                                         : APUS_CUDA_SUM_REFERENCE;
+int sum_order() { return g_sum_order; }
+}  // namespace apus
+
 extern "C" {
 
 int apus_cuda_enable(char *err, size_t errcap) {
@@ -226,10 +242,16 @@ int apus_cuda_enable(char *err, size_t errcap) {
 
 void apus_cuda_moe_destroy(ApusCudaMoe *m);
 
+int apus_cuda_set_sum_order(int order) {
+    if (order == APUS_CUDA_SUM_REFERENCE || order == APUS_CUDA_SUM_TREE) apus::g_sum_order = order;
+    return apus::g_sum_order;
+}
+
 void apus_cuda_disable(void) {
     Ctx &c = ctx();
     if (!c.enabled) return;
     cudaDeviceSynchronize();
+    for (auto &h : apus::release_hooks()) if (h.first) h.first();
     for (auto &kv : c.qcache) { kv.second->release(); delete kv.second; }
     c.qcache.clear();
     for (auto &kv : c.dcache) { kv.second->release(); delete kv.second; }
@@ -256,6 +278,7 @@ void apus_cuda_forget(const void *host_ptr) {
     if (d != c.dcache.end()) { cudaDeviceSynchronize(); d->second->release(); delete d->second; c.dcache.erase(d); }
     auto m = c.moes.find(host_ptr);
     if (m != c.moes.end()) { cudaDeviceSynchronize(); apus_cuda_moe_destroy(m->second); c.moes.erase(m); }
+    for (auto &h : apus::release_hooks()) if (h.second) h.second(host_ptr);
 }
 
 // ---- hook table ----------------------------------------------------------------------

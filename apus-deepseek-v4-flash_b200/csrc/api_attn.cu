@@ -12,30 +12,13 @@
 #include <math.h>
 #include <vector>
 
-#include "runtime.cuh"
+#include "attn_engine.cuh"
 
 using namespace apus;
 
-namespace {
+namespace apus {
 
-struct CompDev {
-    const float *wkv = nullptr, *wgate = nullptr, *ape = nullptr, *norm = nullptr;
-    int ratio = 0, overlap = 0, d = 0, rd = 0, rotate = 0;
-    float eps = 0.f;
-};
-struct CompStateDev {
-    DevBuf kv, sc, cache;
-    int nb = 0;
-};
-struct AttnDev {
-    ApusAttnCfg cfg;
-    DevQW *wq_a, *wq_b, *wkv, *wo_b, *idx_wq_b;
-    const uint16_t *wo_a;
-    const float *q_norm, *kv_norm, *sink, *idx_wproj;
-    CompDev comp, idx_comp;
-};
-
-int comp_weights(const ApusCompW &h, int dim, CompDev *d) {
+static int comp_weights(const ApusCompW &h, int dim, CompDev *d) {
     const int cd = (1 + h.overlap) * h.d;
     d->ratio = h.ratio; d->overlap = h.overlap; d->d = h.d; d->rd = h.rd; d->rotate = h.rotate; d->eps = h.eps;
     d->wkv = (const float *)cached_dense(h.wkv, (size_t)cd * dim * 4);
@@ -70,22 +53,46 @@ int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A) {
     return 0;
 }
 
-// Device mirror of one sequence's state (host-pointer tier: refreshed per call).
-struct StateDev {
-    DevBuf win;
-    CompStateDev comp, idx;
-};
-StateDev g_state;
-DevBuf g_ws[24];
+void StateDev::release() {
+    win.release();
+    comp.kv.release(); comp.sc.release(); comp.cache.release();
+    idx.kv.release(); idx.sc.release(); idx.cache.release();
+}
 
-struct StepBufs {
-    float *qa, *qr, *q, *kva, *kv, *iq, *ckv, *csc, *pooled, *wt, *scores, *o, *y;
-    uint8_t *xq;
-    float *xs;
-    int32_t *sel, *idxs;
-};
+__global__ void fill_kernel(float *p, size_t n, float v) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
 
-int step_bufs(const ApusAttnCfg &c, long long max_nb, StepBufs *b) {
+static int comp_state_alloc(CompStateDev &S, int B, int ratio, int overlap, int d, int cap) {
+    const int coff = 1 + overlap;
+    S.carry = (size_t)coff * ratio * coff * d;
+    S.cap = cap; S.nb = 0;
+    if (S.kv.get(S.carry * B * 4, nullptr) || S.sc.get(S.carry * B * 4, nullptr) ||
+        S.cache.get((size_t)B * cap * d * 4 + 16, nullptr))
+        return 1;
+    return 0;
+}
+
+int attn_state_init(const ApusAttnCfg &c, StateDev &S, int B, int cap) {
+    Ctx &cx = ctx();
+    S.B = B;
+    if (S.win.get((size_t)B * c.window * c.head_dim * 4, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemsetAsync(S.win.p, 0, (size_t)B * c.window * c.head_dim * 4, cx.stream));
+    if (c.ratio) {
+        if (comp_state_alloc(S.comp, B, c.ratio, c.ratio == 4, c.head_dim, cap)) return 1;
+        APUS_CUDA_OK(cudaMemsetAsync(S.comp.kv.p, 0, S.comp.carry * B * 4, cx.stream));
+        fill_kernel<<<ceil_div(S.comp.carry * B, 256), 256, 0, cx.stream>>>(S.comp.sc.as<float>(), S.comp.carry * B, -INFINITY);
+        if (c.has_indexer) {
+            if (comp_state_alloc(S.idx, B, c.ratio, 1, c.idx_dim, cap)) return 1;
+            APUS_CUDA_OK(cudaMemsetAsync(S.idx.kv.p, 0, S.idx.carry * B * 4, cx.stream));
+            fill_kernel<<<ceil_div(S.idx.carry * B, 256), 256, 0, cx.stream>>>(S.idx.sc.as<float>(), S.idx.carry * B, -INFINITY);
+        }
+    }
+    return 0;
+}
+
+int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, StepBufs *b) {
     const int hd = c.n_heads * c.head_dim;
     int kmax = c.dim;
     if (c.q_lora > kmax) kmax = c.q_lora;
@@ -99,7 +106,7 @@ int step_bufs(const ApusAttnCfg &c, long long max_nb, StepBufs *b) {
                      (size_t)c.o_groups * c.o_lora * 4, (size_t)kmax, (size_t)(kmax / 128 + 1) * 4,
                      (size_t)(c.idx_topk + 8) * 4, idxw * 4};
     for (int i = 0; i < 17; i++)
-        if (g_ws[i].get(sz[i], &p[i])) return 1;
+        if (ws[i].get(sz[i] * B, &p[i])) return 1;
     b->qa = (float *)p[0]; b->qr = (float *)p[1]; b->q = (float *)p[2]; b->kva = (float *)p[3];
     b->kv = (float *)p[4]; b->iq = (float *)p[5]; b->ckv = (float *)p[6]; b->csc = (float *)p[7];
     b->pooled = (float *)p[8]; b->wt = (float *)p[9]; b->scores = (float *)p[10]; b->o = (float *)p[11];
@@ -108,23 +115,24 @@ int step_bufs(const ApusAttnCfg &c, long long max_nb, StepBufs *b) {
     return 0;
 }
 
-// One compressor decode step; appends a finished entry to the cache when the
-// block completes (reference c/attn.h:960-1008 + 797-819).
-int compressor_step(const CompDev &W, CompStateDev &S, const float *x, int dim, long long pos,
-                    const float *cs_rp, int half2, const StepBufs &b, cudaStream_t st) {
+// One compressor decode step of B sequences; appends a finished entry to every
+// cache when the block completes (reference c/attn.h:960-1008 + 797-819).
+static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, int B, int dim, long long pos,
+                           const float *cs_rp, const StepBufs &b, cudaStream_t st) {
     const int cd = (1 + W.overlap) * W.d;
-    if (f32_linear(W.wkv, x, b.ckv, 1, dim, cd, 0, st) || f32_linear(W.wgate, x, b.csc, 1, dim, cd, 0, st))
+    if (f32_linear(W.wkv, x, b.ckv, B, dim, cd, 0, st) || f32_linear(W.wgate, x, b.csc, B, dim, cd, 0, st))
         return 1;
     const int slot = (int)(pos % W.ratio);
     const int should = (pos + 1) % W.ratio == 0;
-    if (comp_step(S.kv.as<float>(), S.sc.as<float>(), 0, b.ckv, b.csc, cd, W.ape, W.ratio, W.overlap, W.d,
-                  slot, should, b.pooled, W.d, 1, st))
+    if (comp_step(S.kv.as<float>(), S.sc.as<float>(), (long long)S.carry, b.ckv, b.csc, cd, W.ape, W.ratio,
+                  W.overlap, W.d, slot, should, b.pooled, W.d, B, st))
         return 1;
     if (should) {
+        APUS_REQUIRE(S.nb < S.cap, "compressed cache is full (%d entries)", S.cap);
         int flags = ROW_BF16_IN | ROW_RMS_W | ROW_ROPE | ROW_BF16_OUT |
                     (W.rotate ? (ROW_HADAMARD | ROW_FP4QAT) : ROW_FP8QAT);
-        if (row_ops(b.pooled, W.d, S.cache.as<float>() + (size_t)S.nb * W.d, W.d, 1, W.d, flags, W.norm,
-                    W.eps, W.rd, cs_rp, 1, half2, st))
+        if (row_ops(b.pooled, W.d, S.cache.as<float>() + (size_t)S.nb * W.d, S.cap * W.d, B, W.d, flags, W.norm,
+                    W.eps, W.rd, cs_rp, B, 0, st))
             return 1;
         S.nb++;
     }
@@ -134,18 +142,19 @@ int compressor_step(const CompDev &W, CompStateDev &S, const float *x, int dim, 
 int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
               const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st) {
     const ApusAttnCfg &c = A.cfg;
-    const int h = c.n_heads, d = c.head_dim, rd = c.rope_dim, half2 = rd, win = c.window, ratio = c.ratio;
+    const int B = S.B;
+    const int h = c.n_heads, d = c.head_dim, rd = c.rope_dim, win = c.window, ratio = c.ratio;
     const int hd = h * d;
     // q path (c/attn.h:1525-1548)
-    if (qlinear_dev(A.wq_a, x, b.qa, 1, b.xq, b.xs, true, st)) return 1;
-    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, 1, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st))
+    if (qlinear_dev(A.wq_a, x, b.qa, B, b.xq, b.xs, true, st)) return 1;
+    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st))
         return 1;
-    if (qlinear_dev(A.wq_b, b.qr, b.q, 1, b.xq, b.xs, true, st)) return 1;
-    if (row_ops(b.q, d, b.q, d, h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, h, 0, st)) return 1;
+    if (qlinear_dev(A.wq_b, b.qr, b.q, B, b.xq, b.xs, true, st)) return 1;
+    if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, B * h, 0, st)) return 1;
     // window KV (c/attn.h:1552-1569)
-    if (qlinear_dev(A.wkv, x, b.kva, 1, b.xq, b.xs, true, st)) return 1;
-    if (row_ops(b.kva, d, b.kv, d, 1, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd,
-                cs_pos, 1, 0, st))
+    if (qlinear_dev(A.wkv, x, b.kva, B, b.xq, b.xs, true, st)) return 1;
+    if (row_ops(b.kva, d, b.kv, d, B, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd,
+                cs_pos, B, 0, st))
         return 1;
     // compressed ids: the indexer runs BEFORE the ring write and the attention compressor
     int compw = 0;
@@ -154,17 +163,19 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
         const long long nbs = (pos + 1) / ratio;
         if (c.has_indexer) {
             const int ih = c.idx_heads, idm = c.idx_dim;
-            if (qlinear_dev(A.idx_wq_b, b.qr, b.iq, 1, b.xq, b.xs, true, st)) return 1;
-            if (row_ops(b.iq, idm, b.iq, idm, ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr,
-                        0.f, rd, cs_pos, ih, 0, st))
+            if (qlinear_dev(A.idx_wq_b, b.qr, b.iq, B, b.xq, b.xs, true, st)) return 1;
+            if (row_ops(b.iq, idm, b.iq, idm, B * ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr,
+                        0.f, rd, cs_pos, B * ih, 0, st))
                 return 1;
-            if (compressor_step(A.idx_comp, S.idx, x, c.dim, pos, cs_rp, half2, b, st)) return 1;
-            if (f32_linear(A.idx_wproj, x, b.wt, 1, c.dim, ih, APUS_CUDA_R_IN | APUS_CUDA_R_OUT, st)) return 1;
+            if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, st)) return 1;
+            if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, ih, APUS_CUDA_R_IN | APUS_CUDA_R_OUT, st)) return 1;
             const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
             compw = (int)(c.idx_topk < nbs ? c.idx_topk : nbs);
             if (compw > 0) {
-                if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), nbs, ih, idm, b.scores, st)) return 1;
-                if (topk_stable(b.scores, (int)nbs, compw, b.sel, 1, st)) return 1;
+                if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), (long long)S.idx.cap * idm, nbs, ih, idm,
+                               b.scores, B, st))
+                    return 1;
+                if (topk_stable(b.scores, (int)nbs, compw, b.sel, B, st)) return 1;
                 sel = b.sel;
             }
         } else {
@@ -173,27 +184,29 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     }
     if (idx_k_out) *idx_k_out = compw;
     // ring write, attention compressor (c/attn.h:1642-1665)
-    APUS_CUDA_OK(cudaMemcpyAsync(S.win.as<float>() + (size_t)(pos % win) * d, b.kv, (size_t)d * 4,
-                                 cudaMemcpyDeviceToDevice, st));
-    if (ratio && compressor_step(A.comp, S.comp, x, c.dim, pos, cs_rp, half2, b, st)) return 1;
+    if (scatter_rows(S.win.as<float>() + (size_t)(pos % win) * d, (long long)win * d, b.kv, d, B, st)) return 1;
+    if (ratio && compressor_step(A.comp, S.comp, x, B, c.dim, pos, cs_rp, b, st)) return 1;
     // gathered attention over ring ++ compressed cache, inverse RoPE
-    if (build_idx(b.idxs, win, pos, sel, compw, st)) return 1;
+    if (build_idx(b.idxs, win, pos, sel, compw, B, st)) return 1;
     const float scale = (float)pow((double)d, -0.5);
-    if (sparse_attn(b.q, A.sink, h, d, b.idxs, win + compw, 1, scale, S.win.p, win,
-                    ratio ? S.comp.cache.p : nullptr, ratio ? S.comp.nb : 0, 0, b.o, st))
+    if (sparse_attn(b.q, A.sink, h, d, b.idxs, win + compw, B, scale, S.win.p, win,
+                    ratio ? S.comp.cache.p : nullptr, ratio ? S.comp.nb : 0, 0, b.o, st, (long long)win * d,
+                    ratio ? (long long)S.comp.cap * d : 0))
         return 1;
-    if (row_ops(b.o, d, b.o, d, h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs_pos, h, 0, st)) return 1;
+    if (row_ops(b.o, d, b.o, d, B * h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs_pos, B * h, 0, st)) return 1;
     // grouped low-rank o-projection (c/attn.h:1692-1737)
     const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
-    if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, 1, sub, ol,
+    if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, B, sub, ol,
                            APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT, st))
         return 1;
-    return qlinear_dev(A.wo_b, b.y, out, 1, b.xq, b.xs, true, st);
+    return qlinear_dev(A.wo_b, b.y, out, B, b.xq, b.xs, true, st);
 }
 
-int upload_comp(const ApusCompS &h, CompStateDev &d, int extra, cudaStream_t st) {
+static int upload_comp(const ApusCompS &h, CompStateDev &d, int extra, cudaStream_t st) {
     const size_t sb = (size_t)h.rows * h.cols * 4;
-    if (d.kv.get(sb, nullptr) || d.sc.get(sb, nullptr) || d.cache.get((size_t)(h.nb + extra + 1) * h.d * 4, nullptr))
+    d.carry = (size_t)h.rows * h.cols;
+    d.cap = h.nb + extra + 1;
+    if (d.kv.get(sb, nullptr) || d.sc.get(sb, nullptr) || d.cache.get((size_t)d.cap * h.d * 4, nullptr))
         return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(d.kv.p, h.kv, sb, cudaMemcpyHostToDevice, st));
     APUS_CUDA_OK(cudaMemcpyAsync(d.sc.p, h.sc, sb, cudaMemcpyHostToDevice, st));
@@ -202,7 +215,7 @@ int upload_comp(const ApusCompS &h, CompStateDev &d, int extra, cudaStream_t st)
     return 0;
 }
 
-int download_comp(ApusCompS &h, const CompStateDev &d, cudaStream_t st) {
+static int download_comp(ApusCompS &h, const CompStateDev &d, cudaStream_t st) {
     const size_t sb = (size_t)h.rows * h.cols * 4;
     APUS_REQUIRE(d.nb <= h.cap, "attention: the host compressed cache holds %d entries but %d are needed", h.cap, d.nb);
     APUS_CUDA_OK(cudaMemcpyAsync(h.kv, d.kv.p, sb, cudaMemcpyDeviceToHost, st));
@@ -212,6 +225,47 @@ int download_comp(ApusCompS &h, const CompStateDev &d, cudaStream_t st) {
                                      (size_t)(d.nb - h.nb) * h.d * 4, cudaMemcpyDeviceToHost, st));
     return 0;
 }
+
+
+int attn_state_upload(const ApusAttnCfg &c, const ApusAttnS *st, StateDev &S, int extra, cudaStream_t sm) {
+    S.B = 1;
+    if (S.win.get((size_t)c.window * c.head_dim * 4, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(S.win.p, st->win, (size_t)c.window * c.head_dim * 4, cudaMemcpyHostToDevice, sm));
+    if (c.ratio && upload_comp(st->comp, S.comp, extra, sm)) return 1;
+    if (c.ratio && c.has_indexer && upload_comp(st->idx_comp, S.idx, extra, sm)) return 1;
+    return 0;
+}
+
+// Copies ring, carries and the appended cache entries back; the caller updates
+// the host entry counts with attn_state_commit after synchronising.
+int attn_state_download(const ApusAttnCfg &c, ApusAttnS *st, const StateDev &S, cudaStream_t sm) {
+    APUS_CUDA_OK(cudaMemcpyAsync(st->win, S.win.p, (size_t)c.window * c.head_dim * 4, cudaMemcpyDeviceToHost, sm));
+    if (c.ratio) {
+        if (download_comp(st->comp, S.comp, sm)) return 1;
+        if (c.has_indexer && download_comp(st->idx_comp, S.idx, sm)) return 1;
+    }
+    return 0;
+}
+
+void attn_state_commit(const ApusAttnCfg &c, ApusAttnS *st, const StateDev &S) {
+    if (c.ratio) {
+        st->comp.nb = S.comp.nb;
+        if (c.has_indexer) st->idx_comp.nb = S.idx.nb;
+    }
+}
+
+}  // namespace apus
+
+namespace {
+
+StateDev g_state;
+DevBuf g_ws[24];
+
+void attn_release_all() {
+    g_state.release();
+    for (auto &b : g_ws) b.release();
+}
+struct AttnReg { AttnReg() { apus::on_disable(attn_release_all, nullptr); } } g_attn_reg;
 
 }  // namespace
 
@@ -233,13 +287,11 @@ int apus_cuda_attention(const ApusAttnCfg *cfg, const ApusAttnW *w, ApusAttnS *s
     const int hd = cfg->n_heads * d;
     const long long max_nb = ratio ? (start_pos + s) / ratio + 2 : 0;
     StepBufs b;
-    if (step_bufs(*cfg, max_nb, &b)) return 1;
+    if (attn_step_bufs(*cfg, max_nb, 1, g_ws, &b)) return 1;
+    g_state.B = 1;
     // state in
-    if (g_state.win.get((size_t)win * d * 4, nullptr)) return 1;
-    APUS_CUDA_OK(cudaMemcpyAsync(g_state.win.p, st->win, (size_t)win * d * 4, cudaMemcpyHostToDevice, sm));
     const int extra = ratio ? s / ratio + 2 : 0;
-    if (ratio && upload_comp(st->comp, g_state.comp, extra, sm)) return 1;
-    if (ratio && cfg->has_indexer && upload_comp(st->idx_comp, g_state.idx, extra, sm)) return 1;
+    if (attn_state_upload(*cfg, st, g_state, extra, sm)) return 1;
     // rope rows: per token [cos | sin] at its position and at the first position of the block it completes
     std::vector<float> cs((size_t)s * 4 * half, 0.f);
     for (int t = 0; t < s; t++) {
@@ -280,15 +332,10 @@ int apus_cuda_attention(const ApusAttnCfg *cfg, const ApusAttnW *w, ApusAttnS *s
     if (interm && interm->o_out)
         APUS_CUDA_OK(cudaMemcpyAsync(interm->o_out, dout, (size_t)s * cfg->dim * 4, cudaMemcpyDeviceToHost, sm));
     // state out
-    APUS_CUDA_OK(cudaMemcpyAsync(st->win, g_state.win.p, (size_t)win * d * 4, cudaMemcpyDeviceToHost, sm));
-    if (ratio) {
-        if (download_comp(st->comp, g_state.comp, sm)) return 1;
-        if (cfg->has_indexer && download_comp(st->idx_comp, g_state.idx, sm)) return 1;
-    }
+    if (attn_state_download(*cfg, st, g_state, sm)) return 1;
     APUS_CUDA_OK(cudaStreamSynchronize(sm));
+    attn_state_commit(*cfg, st, g_state);
     if (ratio) {
-        st->comp.nb = g_state.comp.nb;
-        if (cfg->has_indexer) st->idx_comp.nb = g_state.idx.nb;
         if (interm) { interm->comp_nb = st->comp.nb - nb0; interm->idx_nb = cfg->has_indexer ? st->idx_comp.nb - inb0 : 0; }
     }
     return 0;

@@ -1,0 +1,355 @@
+// C ABI, part 4: block wiring and the device-resident token loop
+// (include/apus_b200.h; reference c/layer.h:495-545, c/model.h:651-720,
+// c/apus.c:895-944).
+//
+// ApusCudaModel keeps every weight and the state of `batch` sequences in HBM.
+// One decode step of all sequences (they advance in lockstep) is a fixed
+// sequence of kernel launches: embed x hc -> per layer [mHC pre + RMSNorm,
+// attention, mHC post, mHC pre + RMSNorm, MoE, mHC post] -> mHC head ->
+// RMSNorm -> LM-head GEMV -> greedy argmax, whose token feeds the next step on
+// the device.  Nothing is read back until the caller asks for logits or
+// tokens.  A prompt is consumed as consecutive steps; the reference defines
+// its batched prefill to be equal to that (tests/m4c chunk invariance).
+#include <math.h>
+#include <vector>
+
+#include "attn_engine.cuh"
+
+using namespace apus;
+
+namespace {
+
+struct LayerDev {
+    AttnDev attn;
+    ApusCudaMoe *moe = nullptr;
+    const float *attn_norm_w, *ffn_norm_w;
+    const float *hc_attn_fn, *hc_attn_base, *hc_attn_scale, *hc_ffn_fn, *hc_ffn_base, *hc_ffn_scale;
+    const float *cs = nullptr;        // device rope rows [rope_rows][cos(half) | sin(half)]
+    int rope_rows = 0;
+};
+
+struct BlockBufs {
+    float *x, *y, *sub, *post, *comb, *hn;
+};
+
+// One token of B sequences through one block (reference c/layer.h:495-545).
+int block_step(const LayerDev &L, StateDev &S, float **h, float **hn, const int64_t *ids, int B, long long pos,
+               int hc, int iters, float hc_eps, float norm_eps, const BlockBufs &bb, const StepBufs &sb,
+               cudaStream_t st) {
+    const int dim = L.attn.cfg.dim, half2 = L.attn.cfg.rope_dim, ratio = L.attn.cfg.ratio;
+    APUS_REQUIRE(pos < L.rope_rows, "position %lld is beyond the rope table (%d rows)", pos, L.rope_rows);
+    const float *cs_pos = L.cs + (size_t)pos * half2;
+    const long long rp = ratio ? pos + 1 - ratio : -1;
+    const float *cs_rp = rp >= 0 ? L.cs + (size_t)rp * half2 : cs_pos;
+    // attention half
+    if (mhc_pre(*h, dim, hc, L.hc_attn_fn, L.hc_attn_scale, L.hc_attn_base, norm_eps, hc_eps, iters,
+                L.attn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st))
+        return 1;
+    if (attn_step(L.attn, S, bb.x, pos, cs_pos, cs_rp, bb.sub, sb, nullptr, st)) return 1;
+    if (mhc_post(bb.sub, *h, bb.post, bb.comb, *hn, dim, hc, B, st)) return 1;
+    { float *t = *h; *h = *hn; *hn = t; }
+    // ffn half
+    if (mhc_pre(*h, dim, hc, L.hc_ffn_fn, L.hc_ffn_scale, L.hc_ffn_base, norm_eps, hc_eps, iters,
+                L.ffn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st))
+        return 1;
+    if (apus_cuda_moe_forward_dev(L.moe, bb.x, ids, B, bb.sub, st)) return 1;
+    if (mhc_post(bb.sub, *h, bb.post, bb.comb, *hn, dim, hc, B, st)) return 1;
+    { float *t = *h; *h = *hn; *hn = t; }
+    return 0;
+}
+
+int layer_weights(const ApusCudaLayerDesc &d, int hc, int vocab, LayerDev *L) {
+    const int dim = d.acfg.dim;
+    const size_t nmix = (size_t)(2 + hc) * hc, nx = (size_t)hc * dim;
+    if (attn_weights(&d.acfg, &d.aw, &L->attn)) return 1;
+    L->moe = apus_cuda_moe_get(&d.mw);
+    if (!L->moe) return 1;
+    if (d.mw.hash && vocab < (1 << 30) && apus_cuda_moe_set_hash_table(L->moe, d.mw.tid2eid, vocab)) return 1;
+    L->attn_norm_w = (const float *)cached_dense(d.attn_norm_w, (size_t)dim * 4);
+    L->ffn_norm_w = (const float *)cached_dense(d.ffn_norm_w, (size_t)dim * 4);
+    L->hc_attn_fn = (const float *)cached_dense(d.hc_attn_fn, nmix * nx * 4);
+    L->hc_attn_base = (const float *)cached_dense(d.hc_attn_base, nmix * 4);
+    L->hc_attn_scale = (const float *)cached_dense(d.hc_attn_scale, 3 * 4);
+    L->hc_ffn_fn = (const float *)cached_dense(d.hc_ffn_fn, nmix * nx * 4);
+    L->hc_ffn_base = (const float *)cached_dense(d.hc_ffn_base, nmix * 4);
+    L->hc_ffn_scale = (const float *)cached_dense(d.hc_ffn_scale, 3 * 4);
+    if (!L->attn_norm_w || !L->ffn_norm_w || !L->hc_attn_fn || !L->hc_attn_base || !L->hc_attn_scale ||
+        !L->hc_ffn_fn || !L->hc_ffn_base || !L->hc_ffn_scale)
+        return 1;
+    return 0;
+}
+
+// rope rows as [cos(half) | sin(half)] per position, cached by the host cos pointer
+std::map<const void *, DevBuf *> g_rope;
+const float *rope_rows_dev(const float *cos, const float *sin, int rows, int half) {
+    auto it = g_rope.find(cos);
+    if (it != g_rope.end() && it->second->cap >= (size_t)rows * 2 * half * 4) return it->second->as<float>();
+    std::vector<float> cs((size_t)rows * 2 * half);
+    for (int t = 0; t < rows; t++) {
+        memcpy(&cs[(size_t)t * 2 * half], cos + (size_t)t * half, half * 4);
+        memcpy(&cs[(size_t)t * 2 * half + half], sin + (size_t)t * half, half * 4);
+    }
+    DevBuf *b = it != g_rope.end() ? it->second : new DevBuf();
+    if (b->get(cs.size() * 4, nullptr)) return nullptr;
+    if (cudaMemcpy(b->p, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+    g_rope[cos] = b;
+    return b->as<float>();
+}
+
+StateDev g_block_state;
+DevBuf g_block_ws[20], g_block_hb[10];
+
+void model_release_all() {
+    for (auto &kv : g_rope) { kv.second->release(); delete kv.second; }
+    g_rope.clear();
+    g_block_state.release();
+    for (auto &b : g_block_ws) b.release();
+    for (auto &b : g_block_hb) b.release();
+}
+void model_forget(const void *host) {
+    auto it = g_rope.find(host);
+    if (it == g_rope.end()) return;
+    cudaDeviceSynchronize();
+    it->second->release();
+    delete it->second;
+    g_rope.erase(it);
+}
+struct ModelReg { ModelReg() { apus::on_disable(model_release_all, model_forget); } } g_model_reg;
+
+__global__ void next_ids_kernel(const int32_t *tok, int64_t *ids, int32_t *hist, int B, int step, int n_steps) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) {
+        ids[b] = tok[b];
+        if (hist) hist[(size_t)b * n_steps + step] = tok[b];
+    }
+}
+
+}  // namespace
+
+struct ApusCudaModel {
+    int n_layers = 0, dim = 0, hc = 0, iters = 0, vocab = 0, B = 0, max_pos = 0;
+    float hc_eps = 0.f, norm_eps = 0.f, hc_head_scale = 0.f;
+    std::vector<LayerDev> layers;
+    std::vector<StateDev> states;
+    const void *embed = nullptr, *head = nullptr;
+    int embed_bf16 = 0, head_bf16 = 0;
+    const float *norm_w = nullptr, *hc_head_fn = nullptr, *hc_head_base = nullptr;
+    long long pos = 0;
+    DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, ws[20];
+    StepBufs sb;
+};
+
+static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
+    const int B = m->B, dim = m->dim, hc = m->hc;
+    float *h = m->h0.as<float>(), *hn = m->h1.as<float>();
+    if (embed_rows(m->embed, m->embed_bf16, m->ids.as<int64_t>(), B, hc, dim, h, st)) return 1;
+    BlockBufs bb = {m->x.as<float>(), m->y.as<float>(), m->sub.as<float>(), m->post.as<float>(),
+                    m->comb.as<float>(), nullptr};
+    for (int i = 0; i < m->n_layers; i++)
+        if (block_step(m->layers[i], m->states[i], &h, &hn, m->ids.as<int64_t>(), B, m->pos, hc, m->iters,
+                       m->hc_eps, m->norm_eps, bb, m->sb, st))
+            return 1;
+    m->pos++;
+    if (!want_logits) return 0;
+    // head: hc_head collapse -> BF16 -> RMSNorm -> LM-head GEMV (reference c/model.h:706-718)
+    if (mhc_head(h, dim, hc, m->hc_head_fn, m->hc_head_scale, m->hc_head_base, m->norm_eps, m->hc_eps,
+                 m->yh.as<float>(), B, st))
+        return 1;
+    if (rms_norm(m->yh.as<float>(), m->norm_w, m->norm_eps, m->yn.as<float>(), dim, B, st)) return 1;
+    if (f32_linear(m->head, m->yn.as<float>(), m->logits.as<float>(), B, dim, m->vocab,
+                   m->head_bf16 ? APUS_CUDA_W_BF16 : 0, st))
+        return 1;
+    return argmax_rows(m->logits.as<float>(), m->vocab, B, m->tok.as<int32_t>(), st);
+}
+
+extern "C" {
+
+void apus_cuda_model_destroy(ApusCudaModel *m) {
+    if (!m) return;
+    cudaDeviceSynchronize();
+    for (auto &s : m->states) s.release();
+    DevBuf *bufs[] = {&m->h0, &m->h1, &m->x, &m->y, &m->sub, &m->post, &m->comb, &m->yh, &m->yn, &m->logits,
+                      &m->tok, &m->ids, &m->hist};
+    for (DevBuf *b : bufs) b->release();
+    for (auto &b : m->ws) b.release();
+    delete m;
+}
+
+int apus_cuda_model_reset(ApusCudaModel *m) {
+    if (!m) { set_error("NULL model"); return 1; }
+    for (int i = 0; i < m->n_layers; i++) {
+        const ApusAttnCfg &c = m->layers[i].attn.cfg;
+        const int cap = c.ratio ? m->max_pos / c.ratio + 2 : 0;
+        if (attn_state_init(c, m->states[i], m->B, cap)) return 1;
+    }
+    m->pos = 0;
+    return 0;
+}
+
+ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch, int max_pos) {
+    if (ensure_enabled()) return nullptr;
+    if (!d || batch < 1 || batch > 32 || d->n_layers < 1) { set_error("model_create: bad arguments (batch 1..32)"); return nullptr; }
+    ApusCudaModel *m = new ApusCudaModel();
+    m->n_layers = d->n_layers; m->dim = d->dim; m->hc = d->hc_mult; m->iters = d->hc_sinkhorn_iters;
+    m->vocab = d->vocab; m->B = batch; m->max_pos = max_pos;
+    m->hc_eps = d->hc_eps; m->norm_eps = d->norm_eps; m->hc_head_scale = d->hc_head_scale;
+    m->layers.resize(d->n_layers);
+    m->states.resize(d->n_layers);
+    long long max_nb = 8;
+    bool ok = true;
+    for (int i = 0; i < d->n_layers && ok; i++) {
+        const ApusCudaLayerDesc &ld = d->layers[i];
+        ok = layer_weights(ld, d->hc_mult, d->vocab, &m->layers[i]) == 0;
+        if (!ok) break;
+        const int half = ld.acfg.rope_dim / 2;
+        m->layers[i].cs = rope_rows_dev(ld.cos, ld.sin, ld.rope_rows, half);
+        m->layers[i].rope_rows = ld.rope_rows;
+        ok = m->layers[i].cs != nullptr && ld.rope_rows >= max_pos;
+        if (!ok) set_error("model_create: layer %d rope table has %d rows, %d needed", i, ld.rope_rows, max_pos);
+        if (ld.acfg.ratio && max_pos / ld.acfg.ratio + 2 > max_nb) max_nb = max_pos / ld.acfg.ratio + 2;
+    }
+    const size_t B = batch, dim = d->dim, hc = d->hc_mult;
+    const size_t esz_e = d->embed_bf16 ? 2 : 4, esz_h = d->head_bf16 ? 2 : 4;
+    if (ok) {
+        m->embed = cached_dense(d->embed, (size_t)d->vocab * dim * esz_e);
+        m->head = cached_dense(d->head, (size_t)d->vocab * dim * esz_h);
+        m->embed_bf16 = d->embed_bf16; m->head_bf16 = d->head_bf16;
+        m->norm_w = (const float *)cached_dense(d->norm_w, dim * 4);
+        m->hc_head_fn = (const float *)cached_dense(d->hc_head_fn, hc * hc * dim * 4);
+        m->hc_head_base = (const float *)cached_dense(d->hc_head_base, hc * 4);
+        ok = m->embed && m->head && m->norm_w && m->hc_head_fn && m->hc_head_base;
+    }
+    if (ok)
+        ok = !(m->h0.get(B * hc * dim * 4, nullptr) || m->h1.get(B * hc * dim * 4, nullptr) ||
+               m->x.get(B * dim * 4, nullptr) || m->y.get(B * dim * 4, nullptr) || m->sub.get(B * dim * 4, nullptr) ||
+               m->post.get(B * hc * 4, nullptr) || m->comb.get(B * hc * hc * 4, nullptr) ||
+               m->yh.get(B * dim * 4, nullptr) || m->yn.get(B * dim * 4, nullptr) ||
+               m->logits.get(B * (size_t)d->vocab * 4, nullptr) || m->tok.get(B * 4, nullptr) ||
+               m->ids.get(B * 8, nullptr));
+    if (ok) {
+        // step buffers sized for the widest layer configuration
+        ApusAttnCfg widest = d->layers[0].acfg;
+        for (int i = 1; i < d->n_layers; i++) {
+            const ApusAttnCfg &c = d->layers[i].acfg;
+            if (c.has_indexer) { widest.has_indexer = 1; widest.idx_heads = c.idx_heads; widest.idx_dim = c.idx_dim; widest.idx_topk = c.idx_topk; }
+        }
+        widest.has_indexer = 0;                      // size the index row for the dense (largest) case
+        ok = attn_step_bufs(widest, max_nb > widest.idx_topk ? max_nb : widest.idx_topk, batch, m->ws, &m->sb) == 0;
+    }
+    if (ok) ok = apus_cuda_model_reset(m) == 0;
+    if (!ok) { apus_cuda_model_destroy(m); return nullptr; }
+    return m;
+}
+
+int apus_cuda_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float hc_eps, float norm_eps,
+                            ApusAttnS *st, float *h, const int64_t *ids, int s, int64_t start_pos) {
+    if (ensure_enabled()) return 1;
+    if (s <= 0) return 0;
+    cudaStream_t sm = ctx().stream;
+    const ApusAttnCfg &c = d->acfg;
+    const int dim = c.dim, half = c.rope_dim / 2;
+    APUS_REQUIRE(start_pos + s <= d->rope_rows, "block_forward: rope table too short");
+    LayerDev L;
+    if (layer_weights(*d, hc, 1 << 30, &L)) return 1;
+    if (d->mw.hash) {
+        set_error("block_forward: hash-routed layers need the model entry points (vocab size unknown here)");
+        return 1;
+    }
+    L.cs = rope_rows_dev(d->cos, d->sin, d->rope_rows, half);
+    L.rope_rows = d->rope_rows;
+    if (!L.cs) return 1;
+    StateDev &S = g_block_state;
+    DevBuf *ws = g_block_ws, *hb = g_block_hb;
+    StepBufs sb;
+    const long long max_nb = c.ratio ? (start_pos + s) / c.ratio + 2 : 0;
+    if (attn_step_bufs(c, max_nb, 1, ws, &sb)) return 1;
+    if (attn_state_upload(c, st, S, c.ratio ? s / c.ratio + 2 : 0, sm)) return 1;
+    void *p[8];
+    size_t sz[8] = {(size_t)s * hc * dim * 4, (size_t)hc * dim * 4, (size_t)dim * 4, (size_t)dim * 4, (size_t)dim * 4,
+                    (size_t)hc * 4, (size_t)hc * hc * 4, (size_t)s * 8};
+    for (int i = 0; i < 8; i++) if (hb[i].get(sz[i], &p[i])) return 1;
+    float *hall = (float *)p[0];
+    APUS_CUDA_OK(cudaMemcpyAsync(hall, h, sz[0], cudaMemcpyHostToDevice, sm));
+    if (ids) APUS_CUDA_OK(cudaMemcpyAsync(p[7], ids, (size_t)s * 8, cudaMemcpyHostToDevice, sm));
+    BlockBufs bb = {(float *)p[2], (float *)p[3], (float *)p[4], (float *)p[5], (float *)p[6], nullptr};
+    for (int t = 0; t < s; t++) {
+        float *ht = hall + (size_t)t * hc * dim, *hn = (float *)p[1];
+        float *cur = ht, *alt = hn;
+        if (block_step(L, S, &cur, &alt, ids ? (const int64_t *)p[7] + t : nullptr, 1, start_pos + t, hc, iters,
+                       hc_eps, norm_eps, bb, sb, sm))
+            return 1;
+        if (cur != ht) APUS_CUDA_OK(cudaMemcpyAsync(ht, cur, (size_t)hc * dim * 4, cudaMemcpyDeviceToDevice, sm));
+    }
+    APUS_CUDA_OK(cudaMemcpyAsync(h, hall, sz[0], cudaMemcpyDeviceToHost, sm));
+    if (attn_state_download(c, st, S, sm)) return 1;
+    APUS_CUDA_OK(cudaStreamSynchronize(sm));
+    attn_state_commit(c, st, S);
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "block_forward: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
+int64_t apus_cuda_model_pos(const ApusCudaModel *m) { return m ? m->pos : -1; }
+
+int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int32_t *next) {
+    if (!m) { set_error("NULL model"); return 1; }
+    if (s <= 0) return 0;
+    APUS_REQUIRE(m->pos + s <= m->max_pos, "model_forward: position %lld + %d exceeds max_pos %d", m->pos, s, m->max_pos);
+    cudaStream_t st = ctx().stream;
+    std::vector<int64_t> col((size_t)m->B);
+    for (int t = 0; t < s; t++) {
+        for (int b = 0; b < m->B; b++) col[b] = ids[(size_t)b * s + t];
+        APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, col.data(), (size_t)m->B * 8, cudaMemcpyHostToDevice, st));
+        APUS_CUDA_OK(cudaStreamSynchronize(st));      // `col` is reused by the next position
+        if (model_step(m, t == s - 1, st)) return 1;
+    }
+    if (logits) APUS_CUDA_OK(cudaMemcpyAsync(logits, m->logits.p, (size_t)m->B * m->vocab * 4, cudaMemcpyDeviceToHost, st));
+    if (next) APUS_CUDA_OK(cudaMemcpyAsync(next, m->tok.p, (size_t)m->B * 4, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "model_forward: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
+int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt, int n_prompt, int n_gen, int32_t *out_tokens,
+                             float *ms_prefill, float *ms_decode) {
+    if (!m) { set_error("NULL model"); return 1; }
+    APUS_REQUIRE(n_prompt >= 1 && n_gen >= 1, "model_generate: needs a prompt and at least one token to generate");
+    APUS_REQUIRE(m->pos + n_prompt + n_gen - 1 <= m->max_pos, "model_generate: %d + %d tokens exceed max_pos %d",
+                 n_prompt, n_gen, m->max_pos);
+    cudaStream_t st = ctx().stream;
+    cudaEvent_t e0, e1, e2;
+    APUS_CUDA_OK(cudaEventCreate(&e0)); APUS_CUDA_OK(cudaEventCreate(&e1)); APUS_CUDA_OK(cudaEventCreate(&e2));
+    if (m->hist.get((size_t)m->B * n_gen * 4, nullptr)) return 1;
+    // the prompt columns are staged on the device first so the loop has no host copies
+    std::vector<int64_t> cols((size_t)n_prompt * m->B);
+    for (int t = 0; t < n_prompt; t++)
+        for (int b = 0; b < m->B; b++) cols[(size_t)t * m->B + b] = prompt[(size_t)b * n_prompt + t];
+    void *dcols;
+    if (m->ws[18].get(cols.size() * 8, &dcols)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dcols, cols.data(), cols.size() * 8, cudaMemcpyHostToDevice, st));
+    APUS_CUDA_OK(cudaEventRecord(e0, st));
+    for (int t = 0; t < n_prompt; t++) {
+        APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, (const int64_t *)dcols + (size_t)t * m->B, (size_t)m->B * 8,
+                                     cudaMemcpyDeviceToDevice, st));
+        if (model_step(m, t == n_prompt - 1, st)) return 1;
+    }
+    APUS_CUDA_OK(cudaEventRecord(e1, st));
+    for (int g = 0; g < n_gen; g++) {
+        next_ids_kernel<<<1, 32, 0, st>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), m->hist.as<int32_t>(), m->B, g, n_gen);
+        if (g + 1 < n_gen && model_step(m, true, st)) return 1;
+    }
+    APUS_CUDA_OK(cudaEventRecord(e2, st));
+    APUS_CUDA_OK(cudaMemcpyAsync(out_tokens, m->hist.p, (size_t)m->B * n_gen * 4, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    float a = 0, b = 0;
+    cudaEventElapsedTime(&a, e0, e1); cudaEventElapsedTime(&b, e1, e2);
+    if (ms_prefill) *ms_prefill = a;
+    if (ms_decode) *ms_decode = b;
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "model_generate: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
+}  // extern "C"

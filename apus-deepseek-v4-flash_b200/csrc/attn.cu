@@ -153,9 +153,12 @@ template <bool BF16>
 __global__ void __launch_bounds__(SA_IDS * SA_HEADS)
 sparse_scores_kernel(const float *__restrict__ q, int h, int d, const int32_t *__restrict__ ids,
                      const int *__restrict__ ns, int idxw, float scale, const void *kv_a,
-                     int64_t na, const void *kv_b, float *__restrict__ sc) {
+                     int64_t na, const void *kv_b, float *__restrict__ sc, size_t a_stride,
+                     size_t b_stride) {
     extern __shared__ float sm[];
     const int t = blockIdx.z, hb = blockIdx.y, tile = blockIdx.x;
+    kv_a = reinterpret_cast<const char *>(kv_a) + (size_t)t * a_stride;
+    kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)t * b_stride;
     const int n = ns[t];
     if (tile * SA_IDS >= n) return;
     const int pitch = d + 1;
@@ -195,11 +198,14 @@ template <bool BF16>
 __global__ void __launch_bounds__(256)
 sparse_pv_kernel(const float *__restrict__ sc, const float *__restrict__ sink, int h, int d,
                  const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw,
-                 const void *kv_a, int64_t na, const void *kv_b, float *__restrict__ o) {
+                 const void *kv_a, int64_t na, const void *kv_b, float *__restrict__ o, size_t a_stride,
+                 size_t b_stride) {
     extern __shared__ float s_p[];             // [idxw]
     __shared__ float red[32];
     __shared__ float s_mx, s_sum;
     const int t = blockIdx.y, head = blockIdx.x, tid = threadIdx.x;
+    kv_a = reinterpret_cast<const char *>(kv_a) + (size_t)t * a_stride;
+    kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)t * b_stride;
     const int n = ns[t];
     float *ov = o + ((size_t)t * h + head) * d;
     if (n == 0) {
@@ -219,7 +225,7 @@ sparse_pv_kernel(const float *__restrict__ sc, const float *__restrict__ sink, i
     }
     __syncthreads();
     mx = s_mx;
-    for (int j = tid; j < n; j += blockDim.x) s_p[j] = bf16_round(expf(__fsub_rn(sr[j], mx)));
+    for (int j = tid; j < n; j += blockDim.x) s_p[j] = bf16_round(exp_rn(__fsub_rn(sr[j], mx)));
     __syncthreads();
     if (tid == 0) {
         float sum = 0.f;
@@ -239,7 +245,7 @@ sparse_pv_kernel(const float *__restrict__ sc, const float *__restrict__ sink, i
         }
     }
     __syncthreads();
-    const float den = __fadd_rn(s_sum, expf(__fsub_rn(sink[head], mx)));
+    const float den = __fadd_rn(s_sum, exp_rn(__fsub_rn(sink[head], mx)));
     const int32_t *idr = ids + (size_t)t * idxw;
     for (int k2 = tid; k2 < d / 2; k2 += blockDim.x) {
         float a0 = 0.f, a1 = 0.f;
@@ -298,8 +304,10 @@ static int ensure_scratch(size_t bytes) {
 int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
-                int kv_bf16, float *o, cudaStream_t st) {
+                int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride, long long kv_b_stride) {
     (void)nb;
+    const size_t esz = kv_bf16 ? 2 : 4;
+    const size_t sa = (size_t)kv_a_stride * esz, sb = (size_t)kv_b_stride * esz;
     APUS_REQUIRE(d % 2 == 0 && d <= 1024, "sparse_attn: d=%d unsupported", d);
     APUS_REQUIRE((size_t)idxw * sizeof(float) <= 160 * 1024, "sparse_attn: idxw=%d too wide", idxw);
     if (s <= 0 || idxw <= 0) return 0;
@@ -322,9 +330,9 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<true>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
         sparse_scores_kernel<true><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
-                                                                       kv_a, na, kv_b, sc);
+                                                                       kv_a, na, kv_b, sc, sa, sb);
         APUS_LAUNCHED();
-        sparse_pv_kernel<true><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o);
+        sparse_pv_kernel<true><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb);
         APUS_LAUNCHED();
     } else {
         APUS_CUDA_OK(cudaFuncSetAttribute(sparse_scores_kernel<false>,
@@ -332,9 +340,9 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<false>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
         sparse_scores_kernel<false><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
-                                                                        kv_a, na, kv_b, sc);
+                                                                        kv_a, na, kv_b, sc, sa, sb);
         APUS_LAUNCHED();
-        sparse_pv_kernel<false><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o);
+        sparse_pv_kernel<false><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb);
         APUS_LAUNCHED();
     }
     return 0;

@@ -1,0 +1,54 @@
+// Device-side attention engine shared by the host-pointer attention entry
+// point and the device-resident model (api_attn.cu, api_model.cu).
+#pragma once
+#include "runtime.cuh"
+
+namespace apus {
+
+struct CompDev {
+    const float *wkv = nullptr, *wgate = nullptr, *ape = nullptr, *norm = nullptr;
+    int ratio = 0, overlap = 0, d = 0, rd = 0, rotate = 0;
+    float eps = 0.f;
+};
+// Compressor state of B sequences in lockstep: carries [B][rows*cols], cache
+// [B][cap][d]; nb entries valid in every sequence.
+struct CompStateDev {
+    DevBuf kv, sc, cache;
+    int nb = 0, cap = 0;
+    size_t carry = 0;         // rows*cols
+};
+struct AttnDev {
+    ApusAttnCfg cfg;
+    DevQW *wq_a, *wq_b, *wkv, *wo_b, *idx_wq_b;
+    const uint16_t *wo_a;
+    const float *q_norm, *kv_norm, *sink, *idx_wproj;
+    CompDev comp, idx_comp;
+};
+struct StateDev {
+    DevBuf win;               // [B][window][head_dim]
+    CompStateDev comp, idx;
+    int B = 1;
+    void release();
+};
+struct StepBufs {
+    float *qa, *qr, *q, *kva, *kv, *iq, *ckv, *csc, *pooled, *wt, *scores, *o, *y;
+    uint8_t *xq;
+    float *xs;
+    int32_t *sel, *idxs;
+};
+
+int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A);
+// Allocates (grows) and initialises the state of B sequences: zero ring and
+// carries, score carries at -inf, caches of `cap` entries.
+int attn_state_init(const ApusAttnCfg &c, StateDev &S, int B, int cap);
+int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, StepBufs *b);
+// One token of B sequences in lockstep at position pos. x [B, dim] -> out [B, dim].
+int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
+              const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st);
+
+// Host-state exchange of the host-pointer tier (one sequence).
+int attn_state_upload(const ApusAttnCfg &c, const ApusAttnS *st, StateDev &S, int extra, cudaStream_t sm);
+int attn_state_download(const ApusAttnCfg &c, ApusAttnS *st, const StateDev &S, cudaStream_t sm);
+void attn_state_commit(const ApusAttnCfg &c, ApusAttnS *st, const StateDev &S);
+
+}  // namespace apus

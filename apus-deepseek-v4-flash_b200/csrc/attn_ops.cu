@@ -1,8 +1,8 @@
 // Row-wise numerics helpers of the attention sublayer and the compressor /
 // indexer steps.  Every kernel reproduces the reference's per-element
 // operation sequence (separately rounded multiply and add where the reference
-// is built without contraction, BF16 rounds at the same points); only the
-// sums of squares are tree reductions.
+// is built without contraction, BF16 rounds at the same points); the sums of
+// squares follow the reference's loop order unless the tree order is selected.
 //
 // Reference: c/attn.h:290-299 (RoPE), 301-311 (Hadamard), 325-369 (FP8 / FP4
 // quant-dequant), 371-378 (RMSNorm), 797-819 (compressor finish), 892-1011
@@ -37,13 +37,24 @@ row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y,
     float v = on ? x[(size_t)row * x_stride + i] : 0.f;
     if (flags & ROW_BF16_IN) v = bf16_round(v);
     if (flags & (ROW_RMS_W | ROW_RMS_PLAIN)) {
-        float ss = warp_sum(on ? __fmul_rn(v, v) : 0.f);
-        if ((i & 31) == 0) s_red[i >> 5] = ss;
-        __syncthreads();
-        if (i < 32) {
-            float t = i < (int)(blockDim.x >> 5) ? s_red[i] : 0.f;
-            t = warp_sum(t);
-            if (i == 0) s_red[0] = t;
+        if (flags & ROW_SEQ_SUM) {             // the reference's loop order: one accumulator, index ascending
+            if (on) s_v[i] = __fmul_rn(v, v);
+            __syncthreads();
+            if (i == 0) {
+                float a = 0.f;
+#pragma unroll 8
+                for (int k = 0; k < n; k++) a = __fadd_rn(a, s_v[k]);
+                s_red[0] = a;
+            }
+        } else {
+            float ss = warp_sum(on ? __fmul_rn(v, v) : 0.f);
+            if ((i & 31) == 0) s_red[i >> 5] = ss;
+            __syncthreads();
+            if (i < 32) {
+                float t = i < (int)(blockDim.x >> 5) ? s_red[i] : 0.f;
+                t = warp_sum(t);
+                if (i == 0) s_red[0] = t;
+            }
         }
         __syncthreads();
         float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(s_red[0], (float)n), eps)));
@@ -113,6 +124,7 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
     APUS_REQUIRE(!(flags & ROW_HADAMARD) || (n & (n - 1)) == 0, "row_ops: Hadamard needs a power of two, n=%d", n);
     if (rows <= 0) return 0;
     size_t smem = (size_t)(n + 64) * sizeof(float);
+    if (sum_order() != APUS_CUDA_SUM_TREE) flags |= ROW_SEQ_SUM;
     row_ops_kernel<<<rows, n, smem, st>>>(x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
                                           rows_per_cs > 0 ? rows_per_cs : 1, cs_stride);
     APUS_LAUNCHED();
@@ -151,12 +163,12 @@ comp_step_kernel(float *__restrict__ kv_state, float *__restrict__ sc_state, lon
         float sum = 0.f;
         for (int e = 0; e < ne; e++) {
             float p = (overlap && e >= ratio) ? scs[(size_t)e * cd + d + c] : scs[(size_t)e * cd + c];
-            sum = __fadd_rn(sum, expf(__fsub_rn(p, mx)));
+            sum = __fadd_rn(sum, exp_rn(__fsub_rn(p, mx)));
         }
         float acc = 0.f;
         for (int e = 0; e < ne; e++) {
             const size_t off = (overlap && e >= ratio) ? (size_t)e * cd + d + c : (size_t)e * cd + c;
-            float p = expf(__fsub_rn(scs[off], mx));
+            float p = exp_rn(__fsub_rn(scs[off], mx));
             acc = __fadd_rn(acc, __fmul_rn(kvs[off], __fdiv_rn(p, sum)));
         }
         pooled[(size_t)seq * pooled_stride + c] = acc;
@@ -192,8 +204,13 @@ int comp_step(float *kv_state, float *sc_state, long long state_stride, const fl
 #define IDX_B 4
 __global__ void __launch_bounds__(64 * IDX_B)
 idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, float wscale,
-                 const float *__restrict__ cache, long long nb, int ih, int idm, float *__restrict__ sc) {
+                 const float *__restrict__ cache, long long cache_stride, long long nb, int ih, int idm,
+                 float *__restrict__ sc) {
     extern __shared__ float sm[];             // q [ih*idm], k [IDX_B*idm], terms [IDX_B*ih]
+    q += (size_t)blockIdx.y * ih * idm;
+    wt_raw += (size_t)blockIdx.y * ih;
+    cache += (size_t)blockIdx.y * cache_stride;
+    sc += (size_t)blockIdx.y * nb;
     float *s_q = sm, *s_k = sm + ih * idm, *s_t = s_k + IDX_B * idm;
     const int hh = threadIdx.x % ih, bl = threadIdx.x / ih;
     const long long b = (long long)blockIdx.x * IDX_B + bl;
@@ -219,18 +236,18 @@ idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, 
     }
 }
 
-int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long nb,
-               int ih, int idm, float *sc, cudaStream_t st) {
+int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long cache_stride,
+               long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st) {
     APUS_REQUIRE(ih <= 64 && ih >= 1, "indexer: %d heads unsupported", ih);
-    if (nb <= 0) return 0;
+    if (nb <= 0 || n_seq <= 0) return 0;
     size_t smem = ((size_t)ih * idm + IDX_B * idm + IDX_B * ih) * sizeof(float);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
         APUS_CUDA_OK(cudaFuncSetAttribute(idx_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    idx_score_kernel<<<(unsigned)((nb + IDX_B - 1) / IDX_B), ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, nb,
-                                                                                    ih, idm, sc);
+    dim3 grid((unsigned)((nb + IDX_B - 1) / IDX_B), (unsigned)n_seq);
+    idx_score_kernel<<<grid, ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc);
     APUS_LAUNCHED();
     return 0;
 }
@@ -241,6 +258,8 @@ int idx_scores(const float *q, const float *wt_raw, float wscale, const float *c
 __global__ void build_idx_kernel(int32_t *__restrict__ out, int win, long long pos,
                                  const int32_t *__restrict__ sel, int compw) {
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    out += (size_t)blockIdx.y * (win + compw);
+    if (sel) sel += (size_t)blockIdx.y * compw;
     if (j < win) {
         int v;
         if (pos >= win - 1) {
@@ -255,8 +274,80 @@ __global__ void build_idx_kernel(int32_t *__restrict__ out, int win, long long p
     }
 }
 
-int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, cudaStream_t st) {
-    build_idx_kernel<<<ceil_div(win + compw, 256), 256, 0, st>>>(out, win, pos, sel, compw);
+int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st) {
+    if (n_seq <= 0) return 0;
+    build_idx_kernel<<<dim3(ceil_div(win + compw, 256), n_seq), 256, 0, st>>>(out, win, pos, sel, compw);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+__global__ void scatter_rows_kernel(float *__restrict__ dst, long long dst_stride,
+                                    const float *__restrict__ src, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[(size_t)blockIdx.y * dst_stride + i] = src[(size_t)blockIdx.y * n + i];
+}
+
+int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    scatter_rows_kernel<<<dim3(ceil_div(n, 256), rows), 256, 0, st>>>(dst, dst_stride, src, n);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// First index of the maximum: strict greater-than scan order (reference c/sample.h:76-81).
+__global__ void __launch_bounds__(1024)
+argmax_rows_kernel(const float *__restrict__ x, int n, int32_t *__restrict__ out) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const float *r = x + (size_t)blockIdx.x * n;
+    float v = -INFINITY;
+    int vi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float t = r[i];
+        if (t > v || (t == v && i < vi)) { v = t; vi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, vi, o);
+        if (ov > v || (ov == v && oi < vi)) { v = ov; vi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = v; s_i[threadIdx.x >> 5] = vi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        v = threadIdx.x < (blockDim.x >> 5) ? s_v[threadIdx.x] : -INFINITY;
+        vi = threadIdx.x < (blockDim.x >> 5) ? s_i[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            int oi = __shfl_xor_sync(0xffffffffu, vi, o);
+            if (ov > v || (ov == v && oi < vi)) { v = ov; vi = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = vi == 0x7fffffff ? 0 : vi;
+    }
+}
+
+int argmax_rows(const float *x, int n, int rows, int32_t *out, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    argmax_rows_kernel<<<rows, 1024, 0, st>>>(x, n, out);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+__global__ void embed_rows_kernel(const void *__restrict__ table, int bf16, const int64_t *__restrict__ ids,
+                                  int hc, int dim, float *__restrict__ out) {
+    const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dim) return;
+    const int64_t id = ids[r];
+    float v = bf16 ? __uint_as_float((uint32_t)reinterpret_cast<const uint16_t *>(table)[id * dim + i] << 16)
+                   : reinterpret_cast<const float *>(table)[id * dim + i];
+    for (int j = 0; j < hc; j++) out[((size_t)r * hc + j) * dim + i] = v;
+}
+
+int embed_rows(const void *table, int bf16, const int64_t *ids, int rows, int hc, int dim, float *out,
+               cudaStream_t st) {
+    if (rows <= 0) return 0;
+    embed_rows_kernel<<<dim3(ceil_div(dim, 256), rows), 256, 0, st>>>(table, bf16, ids, hc, dim, out);
     APUS_LAUNCHED();
     return 0;
 }

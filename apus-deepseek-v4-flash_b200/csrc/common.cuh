@@ -11,6 +11,12 @@ namespace apus {
 // ---- error plumbing ---------------------------------------------------------
 void set_error(const char *fmt, ...);          // api.cu
 extern unsigned long long g_dispatches;        // api.cu: kernels launched
+// Order of the long f32 sums (public: apus_cuda_set_sum_order).
+#ifndef APUS_CUDA_SUM_REFERENCE
+#define APUS_CUDA_SUM_REFERENCE 0
+#define APUS_CUDA_SUM_TREE 1
+#endif
+int sum_order();                               // api.cu
 
 #define APUS_CUDA_OK(expr)                                                     \
     do {                                                                       \
@@ -41,7 +47,15 @@ extern unsigned long long g_dispatches;        // api.cu: kernels launched
 // ---- scalar format helpers (device + host) -------------------------------------
 
 // Round-to-nearest-even to BF16, kept in an f32 (reference c/fp4.h:262-270).
-__host__ __device__ __forceinline__ float bf16_round(float x) {
+__host__ // e^x and log(1+x) evaluated in double and rounded once to f32.  The reference
+// calls the host libm's expf/log1pf; a correctly rounded result agrees with any
+// good libm (glibc's expf stays under 0.502 ulp) on all but a vanishing share
+// of inputs, while the device's f32 expf may be 2 ulp off and would flip a
+// BF16 step downstream far more often.
+__device__ __forceinline__ float exp_rn(float x) { return (float)exp((double)x); }
+__device__ __forceinline__ float log1p_rn(float x) { return (float)log1p((double)x); }
+
+__device__ __forceinline__ float bf16_round(float x) {
 #ifdef __CUDA_ARCH__
     uint32_t u = __float_as_uint(x);
 #else

@@ -138,7 +138,7 @@ __device__ __forceinline__ float swiglu_tc(float gate, float up, float limit) {
         u = fminf(fmaxf(u, -limit), limit);
         g = fminf(g, limit);
     }
-    float sig = 1.0f / (1.0f + expf(-g));
+    float sig = 1.0f / (1.0f + exp_rn(-g));
     return bf16_round(__fmul_rn(__fmul_rn(g, sig), u));
 }
 

@@ -119,7 +119,8 @@ int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
 int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
-                int kv_bf16, float *o, cudaStream_t st);
+                int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride = 0,
+                long long kv_b_stride = 0);   // strides (elements) between the tokens' own caches; 0 = shared
 
 // ---- attention row helpers, compressor and indexer steps (attn_ops.cu) -----------------------
 enum {
@@ -131,7 +132,8 @@ enum {
     ROW_HADAMARD = 32,    // Sylvester butterflies * n^-1/2, BF16 out
     ROW_FP8QAT = 64,      // E4M3 quant-dequant per 64 on the first n - rd elements
     ROW_FP4QAT = 128,     // E2M1 quant-dequant per 32
-    ROW_BF16_OUT = 256
+    ROW_BF16_OUT = 256,
+    ROW_SEQ_SUM = 512     // set by the launcher: sums of squares in the reference's loop order
 };
 // cs: per position [cos(half) | sin(half)]; row r uses cs + (r / rows_per_cs) * cs_stride.
 int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
@@ -140,9 +142,19 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
 int comp_step(float *kv_state, float *sc_state, long long state_stride, const float *kv_new,
               const float *sc_new, int new_stride, const float *ape, int ratio, int overlap, int d,
               int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st);
-int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long nb,
-               int ih, int idm, float *sc, cudaStream_t st);
-int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, cudaStream_t st);
+// n_seq sequences in lockstep: q [n_seq, ih*idm], wt_raw [n_seq, ih], caches cache_stride floats
+// apart, sc [n_seq, nb].
+int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long cache_stride,
+               long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st);
+// out [n_seq, win + compw]; sel [n_seq, compw] or NULL for the dense list.
+int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st);
+// dst[b * dst_stride + i] = src[b * n + i] for b < rows (ring / cache row scatter).
+int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st);
+// First index of the row maximum (reference c/sample.h:76-81), rows of n.
+int argmax_rows(const float *x, int n, int rows, int32_t *out, cudaStream_t st);
+// Embedding rows replicated hc times (reference c/model.h:512-517): out [rows, hc, dim].
+int embed_rows(const void *table, int bf16, const int64_t *ids, int rows, int hc, int dim, float *out,
+               cudaStream_t st);
 
 // ---- mHC (mhc.cu) -----------------------------------------------------------------------------------
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,

@@ -60,14 +60,73 @@ mhc_mix_kernel(const float *__restrict__ x4, const float *__restrict__ fn, int n
     if (threadIdx.x == 0) raw[(size_t)row * (nmix + 1) + j] = tot;
 }
 
-__device__ __forceinline__ float sigm(float x) { return __fdiv_rn(1.0f, 1.0f + expf(-x)); }
+// The same dots in the reference's summation order (c/mhc.h:159-176: one f32
+// accumulator per dot, products rounded before each add, index ascending).
+// That order is a chain of n*d dependent adds per dot, so the kernel is bound
+// by add latency, not bandwidth: 256 producer threads stage rounded products
+// of a tile in shared memory while one lane per dot (the consumer warps) walks
+// the previous tile.  One CTA per token; chain c < nmix is fn_c . x, chain
+// nmix is sum x^2.
+__global__ void __launch_bounds__(320)
+mhc_mix_seq_kernel(const float *__restrict__ x4, const float *__restrict__ fn, int nx, int nmix,
+                   int MIX_TI, float *__restrict__ raw) {
+    extern __shared__ __align__(16) float s_prod[];
+    const int C = nmix + 1, stride = MIX_TI + 4, tid = threadIdx.x;
+    const int row = blockIdx.x, nt = (nx + MIX_TI - 1) / MIX_TI;
+    const float *x = x4 + (size_t)row * nx;
+    const bool consumer = tid >= 256;
+    float acc0 = 0.f, acc1 = 0.f;             // a consumer lane owns chains c0 and c0 + 64
+    const int c0 = tid - 256;
+    auto produce = [&](int t) {
+        float *dst = s_prod + (size_t)(t & 1) * C * stride;
+        const int q = MIX_TI / 4;
+        for (int idx = tid; idx < C * q; idx += 256) {
+            const int c = idx / q, i4 = idx - c * q, gi = t * MIX_TI + 4 * i4;
+            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), fv;
+            if (gi < nx) xv = *reinterpret_cast<const float4 *>(x + gi);
+            fv = xv;
+            if (c < nmix && gi < nx) fv = __ldg(reinterpret_cast<const float4 *>(fn + (size_t)c * nx + gi));
+            float4 p = make_float4(__fmul_rn(fv.x, xv.x), __fmul_rn(fv.y, xv.y), __fmul_rn(fv.z, xv.z),
+                                   __fmul_rn(fv.w, xv.w));
+            *reinterpret_cast<float4 *>(dst + (size_t)c * stride + 4 * i4) = p;
+        }
+    };
+    auto chain = [&](const float *src, float acc) {
+        const float4 *p = reinterpret_cast<const float4 *>(src);
+#pragma unroll 8
+        for (int i4 = 0; i4 < MIX_TI / 4; i4++) {
+            float4 v = p[i4];
+            acc = __fadd_rn(acc, v.x); acc = __fadd_rn(acc, v.y);
+            acc = __fadd_rn(acc, v.z); acc = __fadd_rn(acc, v.w);
+        }
+        return acc;
+    };
+    if (!consumer) produce(0);
+    __syncthreads();
+    for (int t = 0; t < nt; t++) {
+        if (!consumer) {
+            if (t + 1 < nt) produce(t + 1);
+        } else {
+            const float *src = s_prod + (size_t)(t & 1) * C * stride;
+            if (c0 < C) acc0 = chain(src + (size_t)c0 * stride, acc0);
+            if (c0 + 64 < C) acc1 = chain(src + (size_t)(c0 + 64) * stride, acc1);
+        }
+        __syncthreads();
+    }
+    if (consumer) {
+        if (c0 < C) raw[(size_t)row * C + c0] = acc0;
+        if (c0 + 64 < C) raw[(size_t)row * C + c0 + 64] = acc1;
+    }
+}
+
+__device__ __forceinline__ float sigm(float x) { return __fdiv_rn(1.0f, 1.0f + exp_rn(-x)); }
 
 // Sinkhorn on an n x n matrix held by one thread (reference c/mhc.h:181-218).
 __device__ void sinkhorn(float *c, int n, int iters, float eps) {
     for (int j = 0; j < n; j++) {
         float *r = c + j * n, mx = r[0], sum = 0.f;
         for (int k = 1; k < n; k++) mx = fmaxf(mx, r[k]);
-        for (int k = 0; k < n; k++) { r[k] = expf(r[k] - mx); sum = __fadd_rn(sum, r[k]); }
+        for (int k = 0; k < n; k++) { r[k] = exp_rn(r[k] - mx); sum = __fadd_rn(sum, r[k]); }
         for (int k = 0; k < n; k++) r[k] = __fadd_rn(__fdiv_rn(r[k], sum), eps);
     }
     for (int it = 0; it < iters; it++) {
@@ -96,7 +155,8 @@ mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ ra
                       int head_mode, const float *__restrict__ norm_w, float rms_eps,
                       float *__restrict__ pre_out, float *__restrict__ post_out,
                       float *__restrict__ comb_out, float *__restrict__ y,
-                      float *__restrict__ y_normed) {
+                      float *__restrict__ y_normed, int seq) {
+    extern __shared__ float s_sq[];           // seq: d squares of the collapsed row
     __shared__ float s_pre[MHC_MAX_N];
     __shared__ float red[32];
     const int row = blockIdx.x;
@@ -138,10 +198,24 @@ mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ ra
         for (int j = 0; j < n; j++) acc = __fadd_rn(acc, __fmul_rn(s_pre[j], x[(size_t)j * d + i]));
         acc = bf16_round(acc);
         y[(size_t)row * d + i] = acc;
-        ss = fmaf(acc, acc, ss);
+        if (seq) s_sq[i] = __fmul_rn(acc, acc);
+        else ss = fmaf(acc, acc, ss);
     }
     if (!y_normed) return;
-    float tot = block_sum(ss, red);
+    float tot;
+    if (seq) {                                // reference order: one accumulator, index ascending
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float a = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < d; i++) a = __fadd_rn(a, s_sq[i]);
+            red[0] = a;
+        }
+        __syncthreads();
+        tot = red[0];
+    } else {
+        tot = block_sum(ss, red);
+    }
     float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)d), rms_eps)));
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = y[(size_t)row * d + i];
@@ -180,6 +254,29 @@ static int ensure_raw(size_t floats) {
     return 0;
 }
 
+// raw[row, 0..nmix] for `rows` tokens in the sum order now in force.
+static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float *raw, int rows,
+                      cudaStream_t st) {
+    if (sum_order() == APUS_CUDA_SUM_TREE) {
+        mhc_mix_kernel<<<dim3(nmix + 1, rows), 256, 0, st>>>(x4, fn, nx, nmix, raw);
+        APUS_LAUNCHED();
+        return 0;
+    }
+    const int C = nmix + 1, ti = C <= 48 ? 512 : 128;
+    const size_t smem = (size_t)2 * C * (ti + 4) * sizeof(float);
+    static bool attr_set = false;
+    if (!attr_set) {
+        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_pre_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+        attr_set = true;
+    }
+    mhc_mix_seq_kernel<<<rows, 320, smem, st>>>(x4, fn, nx, nmix, ti, raw);
+    APUS_LAUNCHED();
+    return 0;
+}
+static inline int finish_seq() { return sum_order() == APUS_CUDA_SUM_TREE ? 0 : 1; }
+static inline size_t finish_smem(int d) { return finish_seq() ? (size_t)d * sizeof(float) : 0; }
+
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
             const float *base, float norm_eps, float hc_eps, int iters,
             const float *norm_w, float rms_eps, float *pre, float *post,
@@ -188,11 +285,10 @@ int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
     if (rows <= 0) return 0;
     int nmix = (2 + n) * n;
     if (ensure_raw((size_t)rows * (nmix + 1))) return 1;
-    mhc_mix_kernel<<<dim3(nmix + 1, rows), 256, 0, st>>>(x4, fn, n * d, nmix, g_raw);
-    APUS_LAUNCHED();
-    mhc_pre_finish_kernel<<<rows, 256, 0, st>>>(x4, g_raw, d, n, nmix, scale, 0.f, base,
+    if (launch_mix(x4, fn, n * d, nmix, g_raw, rows, st)) return 1;
+    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, g_raw, d, n, nmix, scale, 0.f, base,
                                                 norm_eps, hc_eps, iters, 0, norm_w, rms_eps,
-                                                pre, post, comb, y, norm_w ? y_normed : nullptr);
+                                                pre, post, comb, y, norm_w ? y_normed : nullptr, finish_seq());
     APUS_LAUNCHED();
     return 0;
 }
@@ -203,11 +299,10 @@ int mhc_head(const float *x4, int d, int n, const float *fn, float scale,
     APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N && (n * d) % 4 == 0, "mhc: n=%d d=%d unsupported", n, d);
     if (rows <= 0) return 0;
     if (ensure_raw((size_t)rows * (n + 1))) return 1;
-    mhc_mix_kernel<<<dim3(n + 1, rows), 256, 0, st>>>(x4, fn, n * d, n, g_raw);
-    APUS_LAUNCHED();
-    mhc_pre_finish_kernel<<<rows, 256, 0, st>>>(x4, g_raw, d, n, n, nullptr, scale, base,
+    if (launch_mix(x4, fn, n * d, n, g_raw, rows, st)) return 1;
+    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, g_raw, d, n, n, nullptr, scale, base,
                                                 norm_eps, hc_eps, 0, 1, nullptr, 0.f,
-                                                nullptr, nullptr, nullptr, y, nullptr);
+                                                nullptr, nullptr, nullptr, y, nullptr, finish_seq());
     APUS_LAUNCHED();
     return 0;
 }
@@ -267,11 +362,10 @@ int mhc_pre_noalloc(const float *x4, int d, int n, const float *fn, const float 
     const int nmix = (2 + n) * n;
     // every raw[row, 0..nmix] slot read by the finish kernel is written by the mix
     // kernel of the same call, so nothing left over from an earlier call is used
-    mhc_mix_kernel<<<dim3(nmix + 1, rows), 256, 0, st>>>(x4, fn, n * d, nmix, raw);
-    APUS_LAUNCHED();
-    mhc_pre_finish_kernel<<<rows, 256, 0, st>>>(x4, raw, d, n, nmix, scale, 0.f, base, norm_eps,
+    if (launch_mix(x4, fn, n * d, nmix, raw, rows, st)) return 1;
+    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, 0.f, base, norm_eps,
                                                 hc_eps, iters, 0, norm_w, rms_eps, nullptr, post,
-                                                comb, y, norm_w ? y_normed : nullptr);
+                                                comb, y, norm_w ? y_normed : nullptr, finish_seq());
     APUS_LAUNCHED();
     return 0;
 }

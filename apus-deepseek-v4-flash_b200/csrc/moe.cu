@@ -29,7 +29,7 @@ __global__ void router_finish_kernel(const float *__restrict__ logits,
     float sp = 0.f, key = -INFINITY;
     if (e < E) {
         float z = logits[(size_t)t * E + e];
-        float soft = z > 20.0f ? z : log1pf(expf(z));
+        float soft = z > 20.0f ? z : log1p_rn(exp_rn(z));
         sp = sqrtf(soft);
         s_sp[e] = sp;
         if (sp_out) sp_out[(size_t)t * E + e] = sp;

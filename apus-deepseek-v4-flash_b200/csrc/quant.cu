@@ -44,33 +44,57 @@ int act_quant(const float *x, const int *arow, int M, int K, uint8_t *codes,
 }
 
 // One CTA per row: y = bf16(w * (x * 1/sqrt(mean(x^2)+eps))) (reference
-// c/attn.h:371-378; the sum of squares is a tree reduction here).
+// c/attn.h:371-378).  seq: the sum of squares walks the row in index order with
+// one accumulator and rounded squares, as the reference's loop does; otherwise
+// it is a tree reduction.
 __global__ void rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ w,
-                                float eps, float *__restrict__ y, int64_t n) {
+                                float eps, float *__restrict__ y, int64_t n, int seq) {
+    extern __shared__ float s_sq[];
     const float *xr = x + (size_t)blockIdx.x * n;
     float *yr = y + (size_t)blockIdx.x * n;
-    float ss = 0.f;
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
     __shared__ float red[32];
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
-        v = warp_sum(v);
-        if (threadIdx.x == 0) red[0] = v;
+    if (seq) {
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s_sq[i] = __fmul_rn(xr[i], xr[i]);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float a = 0.f;
+#pragma unroll 8
+            for (int64_t i = 0; i < n; i++) a = __fadd_rn(a, s_sq[i]);
+            red[0] = a;
+        }
+    } else {
+        float ss = 0.f;
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+            v = warp_sum(v);
+            if (threadIdx.x == 0) red[0] = v;
+        }
     }
     __syncthreads();
-    float inv = 1.0f / sqrtf(red[0] / (float)n + eps);
+    float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(red[0], (float)n), eps)));
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
-        yr[i] = bf16_round(w[i] * (xr[i] * inv));
+        yr[i] = bf16_round(__fmul_rn(w[i], __fmul_rn(xr[i], inv)));
 }
 
 int rms_norm(const float *x, const float *w, float eps, float *y, int64_t n,
              int64_t rows, cudaStream_t st) {
     if (rows <= 0) return 0;
     int threads = n >= 1024 ? 256 : 128;
-    rms_norm_kernel<<<(unsigned)rows, threads, 0, st>>>(x, w, eps, y, n);
+    const int seq = sum_order() == APUS_CUDA_SUM_TREE ? 0 : 1;
+    const size_t smem = seq ? (size_t)n * sizeof(float) : 0;
+    APUS_REQUIRE(smem <= 200 * 1024, "rms_norm: row of %lld elements exceeds the staging buffer", (long long)n);
+    if (smem > 48 * 1024) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            APUS_CUDA_OK(cudaFuncSetAttribute(rms_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            attr_set = true;
+        }
+    }
+    rms_norm_kernel<<<(unsigned)rows, threads, smem, st>>>(x, w, eps, y, n, seq);
     APUS_LAUNCHED();
     return 0;
 }

@@ -59,6 +59,10 @@ struct Ctx {
 };
 Ctx &ctx();
 int ensure_enabled();
+// Files that keep device buffers outside Ctx register a release function
+// (run by apus_cuda_disable) and optionally a per-host-pointer one (run by
+// apus_cuda_forget).
+void on_disable(void (*release_all)(), void (*forget_one)(const void *));
 
 // Upload + re-tile one quantised matrix (host pointers in `codes`/`scales`).
 int upload_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K,

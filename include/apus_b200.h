@@ -178,6 +178,21 @@ const char *apus_cuda_last_error(void);
  * instead of hanging.  Returns the first code recorded since the last reset
  * (0 = none); synchronises the device. */
 int apus_cuda_kernel_status(int reset);
+/* Order of the long f32 sums whose result the reference defines by its loop
+ * order: the mHC map dots and sum of squares (c/mhc.h:159-176), the RMSNorm
+ * sum of squares (c/attn.h:371-378).
+ *   APUS_CUDA_SUM_REFERENCE (default): one accumulator, index ascending, products
+ *     rounded before each add -- the bits of the CPU path; the sums become
+ *     chains of dependent adds (about 35 us per mHC map at hc_mult 4 x dim 4096).
+ *   APUS_CUDA_SUM_TREE: pairwise tree sums with FMA; faster and closer to the exact
+ *     sum, but off the reference by ~1e-5 relative, which flips a BF16 step in a
+ *     fraction of a percent of the sublayer inputs (the reference's own NEON
+ *     variants differ from its scalar code by as much, c/mhc.h:296-330).
+ * order < 0 only queries.  Returns the order now in force.  Environment
+ * APUS_SUM_ORDER=1 selects the tree order at load time. */
+#define APUS_CUDA_SUM_REFERENCE 0
+#define APUS_CUDA_SUM_TREE 1
+int apus_cuda_set_sum_order(int order);
 /* Forget the cached device copy of a weight buffer (the reference frees and
  * reuses host addresses between tests, tests/m7b/README.md:90-94). */
 void apus_cuda_forget(const void *host_ptr);
@@ -400,6 +415,67 @@ int apus_cuda_sparse_attn_dev(const float *q, const float *sink, int h, int d,
                               float scale, const uint16_t *kv_a, int64_t na,
                               const uint16_t *kv_b, int64_t nb, float *o,
                               void *stream);
+
+/* ---- block and model (c/layer.h, c/model.h) --------------------------------- */
+
+/* The fields of the reference's ApusLayer (c/layer.h:45-71) that
+ * apus_block_forward reads, gathered in one plain descriptor (the integrator
+ * fills it from its ApusLayer).  cos/sin are the rope
+ * tables of this layer's theta class, [rope_rows, rope_dim/2]. */
+typedef struct {
+    ApusAttnCfg acfg;
+    ApusAttnW aw;
+    ApusMoeW mw;
+    const float *attn_norm_w, *ffn_norm_w;                        /* [dim] */
+    const float *hc_attn_fn, *hc_attn_base, *hc_attn_scale;       /* [(2+hc)*hc, hc*dim], [(2+hc)*hc], [3] */
+    const float *hc_ffn_fn, *hc_ffn_base, *hc_ffn_scale;
+    const float *cos, *sin;
+    int rope_rows;
+} ApusCudaLayerDesc;
+
+/* The top-level tensors and sizes of the reference's ApusModel / ApusCfg
+ * (c/model.h:58-84, c/layer.h:32-43). embed/head are [vocab, dim], BF16 bits or f32. */
+typedef struct {
+    int n_layers, dim, hc_mult, hc_sinkhorn_iters, vocab;
+    float hc_eps, norm_eps;
+    const ApusCudaLayerDesc *layers;
+    const void *embed; int embed_bf16;
+    const void *head;  int head_bf16;
+    const float *norm_w, *hc_head_fn, *hc_head_base;
+    float hc_head_scale;
+} ApusCudaModelDesc;
+
+typedef struct ApusCudaModel ApusCudaModel;
+
+/* c/layer.h:110 apus_block_forward: one block for s tokens of one sequence,
+ * h [s, hc_mult, dim] in/out, host state `st` read and updated like
+ * apus_cuda_attention does. */
+int apus_cuda_block_forward(const ApusCudaLayerDesc *L, int hc_mult,
+                            int hc_sinkhorn_iters, float hc_eps,
+                            float norm_eps, ApusAttnS *st, float *h,
+                            const int64_t *ids, int s, int64_t start_pos);
+/* c/model.h:396 + 485 apus_model_load / apus_model_state_init replaced by HBM
+ * residency: uploads every weight, allocates the state of `batch` sequences
+ * (1..32, advancing in lockstep) for positions < max_pos. */
+ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch,
+                                      int max_pos);
+void apus_cuda_model_destroy(ApusCudaModel *m);
+/* c/model.h:485: back to position 0 with empty caches. */
+int apus_cuda_model_reset(ApusCudaModel *m);
+int64_t apus_cuda_model_pos(const ApusCudaModel *m);
+/* c/model.h:722 apus_model_forward for every sequence: ids [batch, s] host,
+ * consumes s positions; logits [batch, vocab] of the last position and/or the
+ * greedy next token [batch] (c/sample.h:76-81, lowest index on ties) are
+ * copied back when non-NULL. */
+int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s,
+                            float *logits, int32_t *next);
+/* c/apus.c:895-944, greedy: prompt [batch, n_prompt] then n_gen tokens per
+ * sequence, the sampled token fed back on the device; out_tokens [batch,
+ * n_gen].  ms_prefill / ms_decode (nullable) receive the CUDA-event times of
+ * the prompt steps and of the n_gen - 1 decode steps. */
+int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt,
+                             int n_prompt, int n_gen, int32_t *out_tokens,
+                             float *ms_prefill, float *ms_decode);
 
 /* No counterpart in the reference.  apus_cuda_hc_pre on device pointers for
  * callers that must not allocate device memory while they run (an engine whose

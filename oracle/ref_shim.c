@@ -23,6 +23,8 @@
 #define APUS_ST_IMPLEMENTATION
 #define APUS_ATTN_IMPLEMENTATION
 #define APUS_MOE_IMPLEMENTATION
+#define APUS_LAYER_IMPLEMENTATION
+#define APUS_MODEL_IMPLEMENTATION
 
 #include <math.h>
 #include <stdio.h>
@@ -31,6 +33,11 @@
 
 #include "moe.h"
 #include "mhc.h"
+#include "model.h"
+/* after the reference headers: their include guards make this header skip its
+ * layout-identical copies of the reference types and only add the plain
+ * descriptors ApusCudaLayerDesc / ApusCudaModelDesc used below */
+#include "../include/apus_b200.h"
 
 /* c/moe.h:333 (static apus_expert). kind 0 = MXFP4, 1 = FP8. */
 void ref_expert(const void *w1, const void *w2, const void *w3, int kind,
@@ -74,3 +81,82 @@ uint64_t ref_avx2_hits(void) { return apus_x86_avx2_hits(); }
 
 /* c/pool.h — lanes the pool was configured with (APUS_THREADS or nproc). */
 int ref_pool_threads(void) { return apus_pool_threads(); }
+
+/* c/layer.h:495 apus_block_forward on an ApusLayer assembled from a descriptor. */
+static void shim_fill_layer(ApusLayer *L, ApusRopeTab *tab, const ApusCudaLayerDesc *d,
+                            int hc, int iters, float hc_eps, float norm_eps) {
+    memset(L, 0, sizeof *L);
+    L->cfg.dim = d->acfg.dim;
+    L->cfg.hc_mult = hc;
+    L->cfg.hc_sinkhorn_iters = iters;
+    L->cfg.hc_eps = hc_eps;
+    L->cfg.norm_eps = norm_eps;
+    L->cfg.n_activated_experts = d->mw.topk;
+    L->ratio = d->acfg.ratio;
+    L->hash = d->mw.hash;
+    L->attn_norm_w = (float *)d->attn_norm_w;
+    L->ffn_norm_w = (float *)d->ffn_norm_w;
+    L->hc_attn_fn = (float *)d->hc_attn_fn; L->hc_attn_base = (float *)d->hc_attn_base;
+    L->hc_attn_scale = (float *)d->hc_attn_scale;
+    L->hc_ffn_fn = (float *)d->hc_ffn_fn; L->hc_ffn_base = (float *)d->hc_ffn_base;
+    L->hc_ffn_scale = (float *)d->hc_ffn_scale;
+    L->acfg = d->acfg; L->aw = d->aw; L->mw = d->mw;
+    memset(tab, 0, sizeof *tab);
+    tab->rd = d->acfg.rope_dim;
+    tab->cap = d->rope_rows;              /* fully built: apus_rope_tab_ensure never grows it */
+    tab->cos = (float *)d->cos; tab->sin = (float *)d->sin;
+    L->rope = tab;
+}
+
+/* `interm` (nullable) is the reference's ApusInterm (c/layer.h:88-104). */
+void ref_block_forward_interm(const ApusCudaLayerDesc *d, int hc, int iters, float hc_eps, float norm_eps,
+                              ApusAttnS *st, float *h, const int64_t *ids, int s, int64_t start_pos,
+                              void *interm) {
+    ApusLayer L;
+    ApusRopeTab tab;
+    ApusLayerState ls;
+    shim_fill_layer(&L, &tab, d, hc, iters, hc_eps, norm_eps);
+    ls.attn = *st;
+    apus_block_forward(&L, &ls, h, ids, s, start_pos, (ApusInterm *)interm);
+    *st = ls.attn;
+}
+
+void ref_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float hc_eps, float norm_eps,
+                       ApusAttnS *st, float *h, const int64_t *ids, int s, int64_t start_pos) {
+    ref_block_forward_interm(d, hc, iters, hc_eps, norm_eps, st, h, ids, s, start_pos, NULL);
+}
+
+/* c/model.h:722 apus_model_forward on an ApusModel assembled from a descriptor.
+ * states[i] is layer i's attention state; *pos is advanced by s. */
+void ref_model_forward(const ApusCudaModelDesc *d, ApusAttnS *states, int64_t *pos,
+                       const int64_t *ids, int s, float *logits, int logits_all) {
+    ApusModel m;
+    memset(&m, 0, sizeof m);
+    m.n_layers = d->n_layers;
+    m.cfg.dim = d->dim; m.cfg.hc_mult = d->hc_mult; m.cfg.vocab_size = d->vocab;
+    m.cfg.hc_eps = d->hc_eps; m.cfg.norm_eps = d->norm_eps; m.cfg.hc_sinkhorn_iters = d->hc_sinkhorn_iters;
+    m.cfg.n_activated_experts = d->layers[0].mw.topk;
+    ApusLayer *Ls = calloc((size_t)d->n_layers, sizeof *Ls);
+    ApusRopeTab *tabs = calloc((size_t)d->n_layers, sizeof *tabs);
+    ApusLayerState *lst = calloc((size_t)d->n_layers, sizeof *lst);
+    for (int i = 0; i < d->n_layers; i++) {
+        shim_fill_layer(&Ls[i], &tabs[i], &d->layers[i], d->hc_mult, d->hc_sinkhorn_iters, d->hc_eps, d->norm_eps);
+        Ls[i].cfg.vocab_size = d->vocab;
+        lst[i].attn = states[i];
+    }
+    m.layers = Ls;
+    ApusStTensor te, th;
+    memset(&te, 0, sizeof te); memset(&th, 0, sizeof th);
+    te.dtype = d->embed_bf16 ? APUS_ST_BF16 : APUS_ST_F32; te.data = d->embed;
+    th.dtype = d->head_bf16 ? APUS_ST_BF16 : APUS_ST_F32; th.data = d->head;
+    m.embed = &te; m.head = &th;
+    m.norm_w = (float *)d->norm_w;
+    m.hc_head_fn = (float *)d->hc_head_fn; m.hc_head_base = (float *)d->hc_head_base;
+    m.hc_head_scale = d->hc_head_scale;
+    ApusModelState st;
+    st.layers = lst; st.pos = *pos;
+    apus_model_forward(&m, &st, ids, s, logits, logits_all);
+    *pos = st.pos;
+    for (int i = 0; i < d->n_layers; i++) states[i] = lst[i].attn;
+    free(Ls); free(tabs); free(lst);
+}

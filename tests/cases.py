@@ -197,3 +197,94 @@ class AttnState:
 def attn_inputs(seed, n_tokens, dim):
     rng = np.random.default_rng(seed)
     return synth.activations(rng, n_tokens, dim)
+
+
+# ---- block / model ------------------------------------------------------------------------
+MODEL_DIMS = dict(hc=4, iters=20, hc_eps=1e-6, norm_eps=1e-6, vocab=384, E=8, topk=2, inter=128)
+
+
+class BlockLayer:
+    """One full block (reference c/layer.h:45-71): attention sublayer, MoE
+    sublayer, the two RMSNorm weights and the two sets of mHC mixing
+    parameters, plus the ApusCudaLayerDesc that points at them.  cos/sin are
+    the reference's rope tables for this layer kind (read from the committed
+    golden file; the reference builds them in c/layer.h:167-190)."""
+
+    def __init__(self, seed, kind, cos, sin, hash_vocab=0, dims=None):
+        from apus_b200 import capi
+        M = dict(MODEL_DIMS)
+        M.update(dims or {})
+        self.M = M
+        self.attn = AttnLayer(seed, kind)
+        dim, hc = self.attn.D["dim"], M["hc"]
+        self.moe = synth.MoeWeights(seed=seed + 500, E=M["E"], dim=dim, inter=M["inter"], topk=M["topk"],
+                                    hash_vocab=hash_vocab)
+        rng = np.random.default_rng(seed + 900)
+        nmix = (2 + hc) * hc
+        nrm = lambda n: (1 + 0.05 * rng.standard_normal(n)).astype(np.float32)
+        self.attn_norm_w, self.ffn_norm_w = nrm(dim), nrm(dim)
+        mk = lambda: ((rng.standard_normal((nmix, hc * dim)) * 0.05).astype(np.float32),
+                      (rng.standard_normal(nmix) * 0.5).astype(np.float32),
+                      (np.array([0.7, 1.3, 0.9], np.float32) * (1 + 0.1 * rng.standard_normal(3))).astype(np.float32))
+        self.hc_attn, self.hc_ffn = mk(), mk()
+        self.cos, self.sin = np.ascontiguousarray(cos), np.ascontiguousarray(sin)
+        d = capi.LayerDesc()
+        d.acfg, d.aw, d.mw = self.attn.cfg, self.attn.w, self.moe.moew()
+        d.attn_norm_w, d.ffn_norm_w = capi.ptr(self.attn_norm_w), capi.ptr(self.ffn_norm_w)
+        d.hc_attn_fn, d.hc_attn_base, d.hc_attn_scale = (capi.ptr(a) for a in self.hc_attn)
+        d.hc_ffn_fn, d.hc_ffn_base, d.hc_ffn_scale = (capi.ptr(a) for a in self.hc_ffn)
+        d.cos, d.sin, d.rope_rows = capi.ptr(self.cos), capi.ptr(self.sin), self.cos.shape[0]
+        self.desc = d
+
+
+class TinyModel:
+    """A few blocks + embedding, final norm, mHC head and BF16 vocabulary head
+    (reference c/model.h:58-84) at toy sizes: layer 0 sliding-window with hash
+    routing, then compressed-sparse (indexer) and dense-compressed layers,
+    i.e. every layer kind of the real model once."""
+
+    KINDS = ("swa", "csa", "hca", "swa")
+
+    def __init__(self, seed, rope, n_layers=3):
+        from apus_b200 import capi
+        M = dict(MODEL_DIMS)
+        self.M = M
+        dim, hc, V = ATTN_DIMS["dim"], M["hc"], M["vocab"]
+        self.layers = []
+        for i in range(n_layers):
+            kind = self.KINDS[i % len(self.KINDS)]
+            cos, sin = rope["plain" if kind == "swa" else "yarn"]
+            self.layers.append(BlockLayer(seed + 10 * i, kind, cos, sin, hash_vocab=V if i == 0 else 0))
+        rng = np.random.default_rng(seed + 77)
+        self.embed = synth.bf16_bits(rng.standard_normal((V, dim)).astype(np.float32))
+        self.head = synth.bf16_bits((rng.standard_normal((V, dim)) * 0.05).astype(np.float32))
+        self.norm_w = (1 + 0.05 * rng.standard_normal(dim)).astype(np.float32)
+        self.hc_head_fn = (rng.standard_normal((hc, hc * dim)) * 0.05).astype(np.float32)
+        self.hc_head_base = (rng.standard_normal(hc) * 0.5).astype(np.float32)
+        self._descs = (capi.LayerDesc * n_layers)(*[L.desc for L in self.layers])
+        d = capi.ModelDesc()
+        d.n_layers, d.dim, d.hc_mult, d.hc_sinkhorn_iters, d.vocab = n_layers, dim, hc, M["iters"], V
+        d.hc_eps, d.norm_eps = M["hc_eps"], M["norm_eps"]
+        import ctypes as C
+        d.layers = C.cast(self._descs, C.POINTER(capi.LayerDesc))
+        d.embed, d.embed_bf16, d.head, d.head_bf16 = capi.ptr(self.embed), 1, capi.ptr(self.head), 1
+        d.norm_w, d.hc_head_fn, d.hc_head_base = capi.ptr(self.norm_w), capi.ptr(self.hc_head_fn), \
+            capi.ptr(self.hc_head_base)
+        d.hc_head_scale = 0.8
+        self.desc = d
+
+    def states(self):
+        """Fresh host attention states, one per layer, as a contiguous ApusAttnS array."""
+        from apus_b200 import capi
+        S = [AttnState(L.attn) for L in self.layers]
+        arr = (capi.AttnS * len(S))(*[s.st for s in S])
+        return S, arr
+
+
+def block_inputs(seed, n_tokens, hc, dim):
+    rng = np.random.default_rng(seed)
+    return synth.activations(rng, n_tokens, hc * dim, std=1.2).reshape(n_tokens, hc, dim)
+
+
+def prompt_ids(seed, batch, n, vocab):
+    return np.random.default_rng(seed).integers(0, vocab, size=(batch, n)).astype(np.int64)

@@ -104,6 +104,79 @@ def ref_attention(L, seed, kind, chunks):
     return r
 
 
+def rope_pair(L):
+    D = cases.ATTN_DIMS
+    return {"plain": rope_tables(L, D, False), "yarn": rope_tables(L, D, True)}
+
+
+class RefInterm(C.Structure):
+    """The reference's ApusInterm (c/layer.h:88-104)."""
+    _fields_ = [("attn_hc_pre", C.c_void_p), ("attn_hc_post", C.c_void_p), ("attn_hc_comb", C.c_void_p),
+                ("attn_norm_out", C.c_void_p), ("attn", capi.AttnInterm), ("post_attn_h", C.c_void_p),
+                ("ffn_hc_pre", C.c_void_p), ("ffn_hc_post", C.c_void_p), ("ffn_hc_comb", C.c_void_p),
+                ("ffn_norm_out", C.c_void_p), ("moe", capi.MoeInterm), ("moe_out", C.c_void_p)]
+
+
+def ref_block(L, seed, kind, chunks):
+    """The reference's apus_block_forward over consecutive chunks (prefill at
+    position 0, then decodes) through the shim's descriptor adapter, with the
+    stage outputs its ApusInterm exposes."""
+    rope = rope_pair(L)
+    cos, sin = rope["plain" if kind == "swa" else "yarn"]
+    B = cases.BlockLayer(seed, kind, cos, sin)
+    S = cases.AttnState(B.attn)
+    M, dim = B.M, B.attn.D["dim"]
+    hc = M["hc"]
+    total = sum(chunks)
+    h = cases.block_inputs(seed + 3, total, hc, dim)
+    out = h.copy()
+    ids = np.zeros(total, np.int64)
+    A = {k: np.zeros((total,) + sh, np.float32) for k, sh in dict(
+        attn_hc_post=(hc,), attn_hc_comb=(hc, hc), attn_norm_out=(dim,), o_out=(dim,), post_attn_h=(hc, dim),
+        ffn_hc_post=(hc,), ffn_hc_comb=(hc, hc), ffn_norm_out=(dim,), moe_out=(dim,)).items()}
+    L.ref_block_forward_interm.restype = None
+    L.ref_block_forward_interm.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_void_p,
+                                           C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]
+    pos = 0
+    for n in chunks:
+        it = RefInterm()
+        for k, a in A.items():
+            if k == "o_out":
+                it.attn.o_out = P(a[pos:pos + n])
+            else:
+                setattr(it, k, P(a[pos:pos + n]))
+        L.ref_block_forward_interm(C.byref(B.desc), hc, M["iters"], M["hc_eps"], M["norm_eps"], C.byref(S.st),
+                                   P(out[pos:pos + n]), P(ids[pos:pos + n]), n, pos, C.byref(it))
+        pos += n
+    return dict(out=out, win=S.win.copy(), **A)
+
+
+def ref_generate(L, seed, n_layers, batch, n_prompt, n_gen):
+    """Greedy token loop on the reference's apus_model_forward (c/apus.c:895-944
+    with temperature 0: argmax, lowest index on ties), one sequence at a time."""
+    Mdl = cases.TinyModel(seed, rope_pair(L), n_layers)
+    V = Mdl.M["vocab"]
+    prompts = cases.prompt_ids(seed + 5, batch, n_prompt, V)
+    L.ref_model_forward.restype = None
+    L.ref_model_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+    toks = np.zeros((batch, n_gen), np.int32)
+    logits = np.zeros((batch, n_gen, V), np.float32)
+    for b in range(batch):
+        keep, st = Mdl.states()
+        pos = C.c_int64(0)
+        lg = np.empty(V, np.float32)
+        ids = np.ascontiguousarray(prompts[b])
+        L.ref_model_forward(C.byref(Mdl.desc), st, C.byref(pos), P(ids), n_prompt, P(lg), 0)
+        for g in range(n_gen):
+            logits[b, g] = lg
+            toks[b, g] = int(np.argmax(lg))
+            if g + 1 < n_gen:
+                nxt = np.array([toks[b, g]], np.int64)
+                L.ref_model_forward(C.byref(Mdl.desc), st, C.byref(pos), P(nxt), 1, P(lg), 0)
+        assert pos.value == n_prompt + n_gen - 1
+    return dict(tokens=toks, logits=logits)
+
+
 def main():
     L = ref()
     assert L is not None, "reference build not available"
@@ -178,6 +251,12 @@ def main():
                   f"{tag}.y4": y4, f"{tag}.yhead": yh, f"{tag}.ynorm": yn})
     for tag, (seed, kind, chunks) in ATTN_LAYER_CASES.items():
         G.update({f"{tag}.{k}": v for k, v in ref_attention(L, seed, kind, chunks).items()})
+    for name, (cos, sin) in rope_pair(L).items():
+        G[f"rope.{name}.cos"], G[f"rope.{name}.sin"] = cos, sin
+    for tag, (seed, kind, chunks) in BLOCK_CASES.items():
+        G.update({f"{tag}.{k}": v for k, v in ref_block(L, seed, kind, chunks).items()})
+    for tag, args in MODEL_CASES.items():
+        G.update({f"{tag}.{k}": v for k, v in ref_generate(L, *args).items()})
     np.savez_compressed(HERE / "ref_cases.npz", **G)
     print(f"wrote {len(G)} arrays; avx2 hits {L.ref_avx2_hits()}, threads {L.ref_pool_threads()}")
 
@@ -216,6 +295,17 @@ ATTN_LAYER_CASES = {
     "attn_csa": (72, "csa", [13] + [1] * 14 + [3]),
     "attn_hca": (73, "hca", [10] + [1] * 16),
     "attn_csa_decode_only": (74, "csa", [1] * 26),
+}
+# tag -> (seed, layer kind, token chunks fed to apus_block_forward one call each)
+BLOCK_CASES = {
+    "block_swa": (81, "swa", [6] + [1] * 6),
+    "block_csa": (82, "csa", [9] + [1] * 12),
+    "block_hca": (83, "hca", [10] + [1] * 10),
+}
+# tag -> (seed, layers, sequences, prompt tokens, generated tokens)
+MODEL_CASES = {
+    "model_one": (91, 3, 1, 9, 14),
+    "model_batch": (92, 4, 3, 7, 12),
 }
 MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
 
