@@ -109,9 +109,11 @@ int upload_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K
     const size_t off_s = (cb + 255) & ~(size_t)255;
     if (c.stage.get(off_s + sb + 256, &stg)) return 1;
     uint8_t *sc = (uint8_t *)stg, *ss = sc + off_s;
-    APUS_CUDA_OK(cudaMemcpyAsync(sc, codes, cb, cudaMemcpyHostToDevice, c.stream));
+    // the source may be host memory or (for weights generated or already resident
+    // on the device) device memory; the copy kind is inferred from the pointer
+    APUS_CUDA_OK(cudaMemcpyAsync(sc, codes, cb, cudaMemcpyDefault, c.stream));
     if (fmt == 4) {
-        APUS_CUDA_OK(cudaMemcpyAsync(ss, scales, sb, cudaMemcpyHostToDevice, c.stream));
+        APUS_CUDA_OK(cudaMemcpyAsync(ss, scales, sb, cudaMemcpyDefault, c.stream));
         int *flag = nullptr;
         void *fp = nullptr;
         if (c.ws[15].get(256, &fp)) return 1;
@@ -124,7 +126,7 @@ int upload_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K
         if (zero_scale) *zero_scale = hz;
     } else {
         if (repack_fp8(sc, O, K, dst_codes, c.stream)) return 1;
-        APUS_CUDA_OK(cudaMemcpyAsync(dst_scales, scales, sb, cudaMemcpyHostToDevice, c.stream));
+        APUS_CUDA_OK(cudaMemcpyAsync(dst_scales, scales, sb, cudaMemcpyDefault, c.stream));
         APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
         if (zero_scale) *zero_scale = 0;
     }
@@ -165,7 +167,16 @@ DevQW *cached_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, in
     return w;
 }
 
+bool is_device_ptr(const void *p) {
+    cudaPointerAttributes a;
+    if (!p || cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeDevice;
+}
+
+// Dense weights: a host buffer is uploaded once and cached by its address; a
+// device buffer is used in place (the caller keeps it alive).
 const void *cached_dense(const void *host, size_t bytes) {
+    if (is_device_ptr(host)) return host;
     Ctx &c = ctx();
     auto it = c.dcache.find(host);
     if (it != c.dcache.end() && it->second->cap >= bytes) return it->second->p;

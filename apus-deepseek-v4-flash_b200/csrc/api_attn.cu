@@ -18,36 +18,64 @@ using namespace apus;
 
 namespace apus {
 
-static int comp_weights(const ApusCompW &h, int dim, CompDev *d) {
+void WeightOwner::release() {
+    for (DevQW *q : qws) { q->release(); delete q; }
+    for (DevBuf *b : bufs) { b->release(); delete b; }
+    qws.clear(); bufs.clear();
+}
+
+// Weights of the global cache (own == NULL: the host-pointer tier, keyed by
+// host address) or owned by `own` (a model: freed with it).
+DevQW *get_qw(WeightOwner *own, int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K) {
+    if (!own) return cached_qw(fmt, codes, scales, O, K);
+    DevQW *q = new_qw(fmt, codes, scales, O, K);
+    if (q) own->qws.push_back(q);
+    return q;
+}
+const void *get_dense(WeightOwner *own, const void *src, size_t bytes) {
+    if (!own) return cached_dense(src, bytes);
+    if (is_device_ptr(src)) return src;           // used in place; the caller keeps it alive
+    DevBuf *b = new DevBuf();
+    if (b->get(bytes, nullptr) || cudaMemcpy(b->p, src, bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+        set_error("upload of %zu dense weight bytes failed", bytes);
+        b->release(); delete b;
+        return nullptr;
+    }
+    ctx().bytes_uploaded += bytes;
+    own->bufs.push_back(b);
+    return b->p;
+}
+
+static int comp_weights(const ApusCompW &h, int dim, CompDev *d, WeightOwner *own) {
     const int cd = (1 + h.overlap) * h.d;
     d->ratio = h.ratio; d->overlap = h.overlap; d->d = h.d; d->rd = h.rd; d->rotate = h.rotate; d->eps = h.eps;
-    d->wkv = (const float *)cached_dense(h.wkv, (size_t)cd * dim * 4);
-    d->wgate = (const float *)cached_dense(h.wgate, (size_t)cd * dim * 4);
-    d->ape = (const float *)cached_dense(h.ape, (size_t)h.ratio * cd * 4);
-    d->norm = (const float *)cached_dense(h.norm, (size_t)h.d * 4);
+    d->wkv = (const float *)get_dense(own, h.wkv, (size_t)cd * dim * 4);
+    d->wgate = (const float *)get_dense(own, h.wgate, (size_t)cd * dim * 4);
+    d->ape = (const float *)get_dense(own, h.ape, (size_t)h.ratio * cd * 4);
+    d->norm = (const float *)get_dense(own, h.norm, (size_t)h.d * 4);
     return (d->wkv && d->wgate && d->ape && d->norm) ? 0 : 1;
 }
 
-int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A) {
+int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A, WeightOwner *own) {
     const int hd = cfg->n_heads * cfg->head_dim, G = cfg->o_groups;
     A->cfg = *cfg;
-    A->wq_a = cached_qw(8, w->wq_a.codes, w->wq_a.scales, cfg->q_lora, cfg->dim);
-    A->wq_b = cached_qw(8, w->wq_b.codes, w->wq_b.scales, hd, cfg->q_lora);
-    A->wkv = cached_qw(8, w->wkv.codes, w->wkv.scales, cfg->head_dim, cfg->dim);
-    A->wo_b = cached_qw(8, w->wo_b.codes, w->wo_b.scales, cfg->dim, G * cfg->o_lora);
+    A->wq_a = get_qw(own, 8, w->wq_a.codes, w->wq_a.scales, cfg->q_lora, cfg->dim);
+    A->wq_b = get_qw(own, 8, w->wq_b.codes, w->wq_b.scales, hd, cfg->q_lora);
+    A->wkv = get_qw(own, 8, w->wkv.codes, w->wkv.scales, cfg->head_dim, cfg->dim);
+    A->wo_b = get_qw(own, 8, w->wo_b.codes, w->wo_b.scales, cfg->dim, G * cfg->o_lora);
     if (!A->wq_a || !A->wq_b || !A->wkv || !A->wo_b) return 1;
-    A->wo_a = (const uint16_t *)cached_dense(w->wo_a, (size_t)G * cfg->o_lora * (hd / G) * 2);
-    A->q_norm = (const float *)cached_dense(w->q_norm, (size_t)cfg->q_lora * 4);
-    A->kv_norm = (const float *)cached_dense(w->kv_norm, (size_t)cfg->head_dim * 4);
-    A->sink = (const float *)cached_dense(w->sink, (size_t)cfg->n_heads * 4);
+    A->wo_a = (const uint16_t *)get_dense(own, w->wo_a, (size_t)G * cfg->o_lora * (hd / G) * 2);
+    A->q_norm = (const float *)get_dense(own, w->q_norm, (size_t)cfg->q_lora * 4);
+    A->kv_norm = (const float *)get_dense(own, w->kv_norm, (size_t)cfg->head_dim * 4);
+    A->sink = (const float *)get_dense(own, w->sink, (size_t)cfg->n_heads * 4);
     if (!A->wo_a || !A->q_norm || !A->kv_norm || !A->sink) return 1;
     A->idx_wq_b = nullptr; A->idx_wproj = nullptr;
-    if (cfg->ratio && comp_weights(w->comp, cfg->dim, &A->comp)) return 1;
+    if (cfg->ratio && comp_weights(w->comp, cfg->dim, &A->comp, own)) return 1;
     if (cfg->ratio && cfg->has_indexer) {
-        if (comp_weights(w->idx_comp, cfg->dim, &A->idx_comp)) return 1;
-        A->idx_wq_b = cached_qw(8, w->idx_wq_b.codes, w->idx_wq_b.scales, cfg->idx_heads * cfg->idx_dim,
+        if (comp_weights(w->idx_comp, cfg->dim, &A->idx_comp, own)) return 1;
+        A->idx_wq_b = get_qw(own, 8, w->idx_wq_b.codes, w->idx_wq_b.scales, cfg->idx_heads * cfg->idx_dim,
                                 cfg->q_lora);
-        A->idx_wproj = (const float *)cached_dense(w->idx_wproj, (size_t)cfg->idx_heads * cfg->dim * 4);
+        A->idx_wproj = (const float *)get_dense(own, w->idx_wproj, (size_t)cfg->idx_heads * cfg->dim * 4);
         if (!A->idx_wq_b || !A->idx_wproj) return 1;
     }
     return 0;

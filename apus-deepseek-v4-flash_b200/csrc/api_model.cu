@@ -58,21 +58,23 @@ int block_step(const LayerDev &L, StateDev &S, float **h, float **hn, const int6
     return 0;
 }
 
-int layer_weights(const ApusCudaLayerDesc &d, int hc, int vocab, LayerDev *L) {
+// own == NULL: weights of the global cache (host-pointer tier); otherwise they
+// belong to `own` and the MoE object to the caller.
+int layer_weights(const ApusCudaLayerDesc &d, int hc, int vocab, LayerDev *L, WeightOwner *own) {
     const int dim = d.acfg.dim;
     const size_t nmix = (size_t)(2 + hc) * hc, nx = (size_t)hc * dim;
-    if (attn_weights(&d.acfg, &d.aw, &L->attn)) return 1;
-    L->moe = apus_cuda_moe_get(&d.mw);
+    if (attn_weights(&d.acfg, &d.aw, &L->attn, own)) return 1;
+    L->moe = own ? apus_cuda_moe_create(&d.mw, 0, d.mw.E) : apus_cuda_moe_get(&d.mw);
     if (!L->moe) return 1;
     if (d.mw.hash && vocab < (1 << 30) && apus_cuda_moe_set_hash_table(L->moe, d.mw.tid2eid, vocab)) return 1;
-    L->attn_norm_w = (const float *)cached_dense(d.attn_norm_w, (size_t)dim * 4);
-    L->ffn_norm_w = (const float *)cached_dense(d.ffn_norm_w, (size_t)dim * 4);
-    L->hc_attn_fn = (const float *)cached_dense(d.hc_attn_fn, nmix * nx * 4);
-    L->hc_attn_base = (const float *)cached_dense(d.hc_attn_base, nmix * 4);
-    L->hc_attn_scale = (const float *)cached_dense(d.hc_attn_scale, 3 * 4);
-    L->hc_ffn_fn = (const float *)cached_dense(d.hc_ffn_fn, nmix * nx * 4);
-    L->hc_ffn_base = (const float *)cached_dense(d.hc_ffn_base, nmix * 4);
-    L->hc_ffn_scale = (const float *)cached_dense(d.hc_ffn_scale, 3 * 4);
+    L->attn_norm_w = (const float *)get_dense(own, d.attn_norm_w, (size_t)dim * 4);
+    L->ffn_norm_w = (const float *)get_dense(own, d.ffn_norm_w, (size_t)dim * 4);
+    L->hc_attn_fn = (const float *)get_dense(own, d.hc_attn_fn, nmix * nx * 4);
+    L->hc_attn_base = (const float *)get_dense(own, d.hc_attn_base, nmix * 4);
+    L->hc_attn_scale = (const float *)get_dense(own, d.hc_attn_scale, 3 * 4);
+    L->hc_ffn_fn = (const float *)get_dense(own, d.hc_ffn_fn, nmix * nx * 4);
+    L->hc_ffn_base = (const float *)get_dense(own, d.hc_ffn_base, nmix * 4);
+    L->hc_ffn_scale = (const float *)get_dense(own, d.hc_ffn_scale, 3 * 4);
     if (!L->attn_norm_w || !L->ffn_norm_w || !L->hc_attn_fn || !L->hc_attn_base || !L->hc_attn_scale ||
         !L->hc_ffn_fn || !L->hc_ffn_base || !L->hc_ffn_scale)
         return 1;
@@ -81,18 +83,19 @@ int layer_weights(const ApusCudaLayerDesc &d, int hc, int vocab, LayerDev *L) {
 
 // rope rows as [cos(half) | sin(half)] per position, cached by the host cos pointer
 std::map<const void *, DevBuf *> g_rope;
-const float *rope_rows_dev(const float *cos, const float *sin, int rows, int half) {
-    auto it = g_rope.find(cos);
-    if (it != g_rope.end() && it->second->cap >= (size_t)rows * 2 * half * 4) return it->second->as<float>();
+const float *rope_rows_dev(const float *cos, const float *sin, int rows, int half,
+                           std::map<const void *, DevBuf *> &cache = g_rope) {
+    auto it = cache.find(cos);
+    if (it != cache.end() && it->second->cap >= (size_t)rows * 2 * half * 4) return it->second->as<float>();
     std::vector<float> cs((size_t)rows * 2 * half);
     for (int t = 0; t < rows; t++) {
         memcpy(&cs[(size_t)t * 2 * half], cos + (size_t)t * half, half * 4);
         memcpy(&cs[(size_t)t * 2 * half + half], sin + (size_t)t * half, half * 4);
     }
-    DevBuf *b = it != g_rope.end() ? it->second : new DevBuf();
+    DevBuf *b = it != cache.end() ? it->second : new DevBuf();
     if (b->get(cs.size() * 4, nullptr)) return nullptr;
     if (cudaMemcpy(b->p, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
-    g_rope[cos] = b;
+    cache[cos] = b;
     return b->as<float>();
 }
 
@@ -135,6 +138,8 @@ struct ApusCudaModel {
     int embed_bf16 = 0, head_bf16 = 0;
     const float *norm_w = nullptr, *hc_head_fn = nullptr, *hc_head_base = nullptr;
     long long pos = 0;
+    WeightOwner own;                       // every weight copy made for this model
+    std::map<const void *, DevBuf *> rope; // rope rows by host table (layers of a kind share one)
     DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, ws[20];
     StepBufs sb;
 };
@@ -168,6 +173,9 @@ void apus_cuda_model_destroy(ApusCudaModel *m) {
     if (!m) return;
     cudaDeviceSynchronize();
     for (auto &s : m->states) s.release();
+    for (auto &L : m->layers) if (L.moe) apus_cuda_moe_destroy(L.moe);
+    m->own.release();
+    for (auto &kv : m->rope) { kv.second->release(); delete kv.second; }
     DevBuf *bufs[] = {&m->h0, &m->h1, &m->x, &m->y, &m->sub, &m->post, &m->comb, &m->yh, &m->yn, &m->logits,
                       &m->tok, &m->ids, &m->hist};
     for (DevBuf *b : bufs) b->release();
@@ -199,10 +207,10 @@ ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch, int
     bool ok = true;
     for (int i = 0; i < d->n_layers && ok; i++) {
         const ApusCudaLayerDesc &ld = d->layers[i];
-        ok = layer_weights(ld, d->hc_mult, d->vocab, &m->layers[i]) == 0;
+        ok = layer_weights(ld, d->hc_mult, d->vocab, &m->layers[i], &m->own) == 0;
         if (!ok) break;
         const int half = ld.acfg.rope_dim / 2;
-        m->layers[i].cs = rope_rows_dev(ld.cos, ld.sin, ld.rope_rows, half);
+        m->layers[i].cs = rope_rows_dev(ld.cos, ld.sin, ld.rope_rows, half, m->rope);
         m->layers[i].rope_rows = ld.rope_rows;
         ok = m->layers[i].cs != nullptr && ld.rope_rows >= max_pos;
         if (!ok) set_error("model_create: layer %d rope table has %d rows, %d needed", i, ld.rope_rows, max_pos);
@@ -211,12 +219,13 @@ ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch, int
     const size_t B = batch, dim = d->dim, hc = d->hc_mult;
     const size_t esz_e = d->embed_bf16 ? 2 : 4, esz_h = d->head_bf16 ? 2 : 4;
     if (ok) {
-        m->embed = cached_dense(d->embed, (size_t)d->vocab * dim * esz_e);
-        m->head = cached_dense(d->head, (size_t)d->vocab * dim * esz_h);
+        m->embed = get_dense(&m->own, d->embed, (size_t)d->vocab * dim * esz_e);
+        m->head = d->head == d->embed && esz_e == esz_h ? m->embed
+                                                         : get_dense(&m->own, d->head, (size_t)d->vocab * dim * esz_h);
         m->embed_bf16 = d->embed_bf16; m->head_bf16 = d->head_bf16;
-        m->norm_w = (const float *)cached_dense(d->norm_w, dim * 4);
-        m->hc_head_fn = (const float *)cached_dense(d->hc_head_fn, hc * hc * dim * 4);
-        m->hc_head_base = (const float *)cached_dense(d->hc_head_base, hc * 4);
+        m->norm_w = (const float *)get_dense(&m->own, d->norm_w, dim * 4);
+        m->hc_head_fn = (const float *)get_dense(&m->own, d->hc_head_fn, hc * hc * dim * 4);
+        m->hc_head_base = (const float *)get_dense(&m->own, d->hc_head_base, hc * 4);
         ok = m->embed && m->head && m->norm_w && m->hc_head_fn && m->hc_head_base;
     }
     if (ok)
@@ -250,7 +259,7 @@ int apus_cuda_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float
     const int dim = c.dim, half = c.rope_dim / 2;
     APUS_REQUIRE(start_pos + s <= d->rope_rows, "block_forward: rope table too short");
     LayerDev L;
-    if (layer_weights(*d, hc, 1 << 30, &L)) return 1;
+    if (layer_weights(*d, hc, 1 << 30, &L, nullptr)) return 1;
     if (d->mw.hash) {
         set_error("block_forward: hash-routed layers need the model entry points (vocab size unknown here)");
         return 1;

@@ -29,8 +29,8 @@ struct ApusCudaMoe {
     DevQW sw1, sw2, sw3;                  // shared expert
     uint64_t weight_bytes = 0;
     // tcgen05 path: the same experts in the reference storage + TMA tensor maps
-    bool use_tc = false;
-    uint8_t *raw = nullptr;
+    bool use_tc = false, can_tc = false;
+    uint8_t *raw = nullptr;               // owned copy of the reference storage (NULL when adopted)
     const uint8_t *rw1 = nullptr, *rw3 = nullptr, *rw2 = nullptr, *rs1 = nullptr, *rs3 = nullptr, *rs2 = nullptr;
     alignas(64) unsigned char map_w1[128], map_w3[128], map_w2[128], map_xq[128], map_hq[128];
     DevBuf b_t13, b_t2;
@@ -207,6 +207,59 @@ static int forward_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const
                        m->topk, m->dim, out, routed, st);
 }
 
+// One expert's three matrices as the descriptor gives them (directly or through
+// the resolve hook, reference c/moe.h:57-62).
+static int resolve_expert(const ApusMoeW *w, int e, ApusFp4W *r1, ApusFp4W *r2, ApusFp4W *r3) {
+    if (w->hook_resolve) {
+        if (w->hook_resolve(w->hook_ctx, w->layer_id, e, r1, r2, r3)) {
+            set_error("moe_create: hook_resolve failed for expert %d", e);
+            return 1;
+        }
+    } else { *r1 = w->w1[e]; *r2 = w->w2[e]; *r3 = w->w3[e]; }
+    if (r1->O != w->inter || r1->K != w->dim || r3->O != w->inter || r3->K != w->dim ||
+        r2->O != w->dim || r2->K != w->inter) {
+        set_error("moe_create: expert %d has unexpected shapes", e);
+        return 1;
+    }
+    return 0;
+}
+
+// The re-tiled copy of the local experts for the mma.sync kernel, built from
+// the reference-storage copy already in HBM.
+static int build_tiled(ApusCudaMoe *m) {
+    if (m->slab) return 0;
+    const int nl = m->e_hi - m->e_lo;
+    const size_t c13 = (size_t)m->inter * m->dim / 2, s13 = (size_t)m->inter * m->dim / 32;
+    const size_t c2 = c13, s2 = s13;
+    const size_t total = (size_t)nl * (2 * (c13 + s13) + c2 + s2);
+    if (!total) return 0;
+    APUS_REQUIRE(m->rw1 != nullptr, "moe: no expert storage to re-tile from");
+    if (cudaMalloc(&m->slab, total) != cudaSuccess) {
+        set_error("moe: device allocation of %zu bytes (re-tiled experts) failed", total);
+        m->slab = nullptr;
+        return 1;
+    }
+    uint8_t *p = m->slab;
+    m->sl.w1 = p; p += (size_t)nl * c13;
+    m->sl.w3 = p; p += (size_t)nl * c13;
+    m->sl.w2 = p; p += (size_t)nl * c2;
+    m->sl.s1 = p; p += (size_t)nl * s13;
+    m->sl.s3 = p; p += (size_t)nl * s13;
+    m->sl.s2 = p;
+    for (int le = 0; le < nl; le++) {
+        int z1 = 0, z2 = 0, z3 = 0;
+        if (upload_qw(4, m->rw1 + le * c13, m->rs1 + le * s13, m->inter, m->dim, (uint8_t *)m->sl.w1 + le * c13,
+                      (uint8_t *)m->sl.s1 + le * s13, &z1) ||
+            upload_qw(4, m->rw3 + le * c13, m->rs3 + le * s13, m->inter, m->dim, (uint8_t *)m->sl.w3 + le * c13,
+                      (uint8_t *)m->sl.s3 + le * s13, &z3) ||
+            upload_qw(4, m->rw2 + le * c2, m->rs2 + le * s2, m->dim, m->inter, (uint8_t *)m->sl.w2 + le * c2,
+                      (uint8_t *)m->sl.s2 + le * s2, &z2))
+            return 1;
+        m->zero_scale |= z1 | z2 | z3;
+    }
+    return 0;
+}
+
 extern "C" {
 
 ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi) {
@@ -224,56 +277,40 @@ ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi) {
     const size_t total = (size_t)nl * (2 * (c13 + s13) + c2 + s2);
     bool ok = true;
     ok = ok && cudaMalloc(&m->gate_w, (size_t)w->E * w->dim * 4) == cudaSuccess;
-    ok = ok && cudaMemcpy(m->gate_w, w->gate_w, (size_t)w->E * w->dim * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+    ok = ok && cudaMemcpy(m->gate_w, w->gate_w, (size_t)w->E * w->dim * 4, cudaMemcpyDefault) == cudaSuccess;
     if (ok && !w->hash) {
         ok = ok && cudaMalloc(&m->gate_bias, (size_t)w->E * 4) == cudaSuccess;
-        ok = ok && cudaMemcpy(m->gate_bias, w->gate_bias, (size_t)w->E * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+        ok = ok && cudaMemcpy(m->gate_bias, w->gate_bias, (size_t)w->E * 4, cudaMemcpyDefault) == cudaSuccess;
     }
-    if (ok && total) ok = cudaMalloc(&m->slab, total) == cudaSuccess;
-    if (!ok) { set_error("moe_create: device allocation of %zu bytes failed", total); apus_cuda_moe_destroy(m); return nullptr; }
-    uint8_t *p = m->slab;
-    m->sl.w1 = p; p += (size_t)nl * c13;
-    m->sl.w3 = p; p += (size_t)nl * c13;
-    m->sl.w2 = p; p += (size_t)nl * c2;
-    m->sl.s1 = p; p += (size_t)nl * s13;
-    m->sl.s3 = p; p += (size_t)nl * s13;
-    m->sl.s2 = p;
+    if (!ok) { set_error("moe_create: upload of the gate failed"); apus_cuda_moe_destroy(m); return nullptr; }
     m->sl.code_stride13 = c13; m->sl.scale_stride13 = s13;
     m->sl.code_stride2 = c2; m->sl.scale_stride2 = s2;
     m->sl.e_lo = e_lo; m->sl.e_hi = e_hi;
-    for (int e = e_lo; e < e_hi; e++) {
-        ApusFp4W r1, r2, r3;
-        if (w->hook_resolve) {
-            if (w->hook_resolve(w->hook_ctx, w->layer_id, e, &r1, &r2, &r3)) {
-                set_error("moe_create: hook_resolve failed for expert %d", e);
-                apus_cuda_moe_destroy(m); return nullptr;
-            }
-        } else { r1 = w->w1[e]; r2 = w->w2[e]; r3 = w->w3[e]; }
-        const int le = e - e_lo;
-        int z1 = 0, z2 = 0, z3 = 0;
-        if (r1.O != w->inter || r1.K != w->dim || r3.O != w->inter || r3.K != w->dim ||
-            r2.O != w->dim || r2.K != w->inter) {
-            set_error("moe_create: expert %d has unexpected shapes", e);
-            apus_cuda_moe_destroy(m); return nullptr;
-        }
-        if (upload_qw(4, r1.packed, r1.scales, w->inter, w->dim, (uint8_t *)m->sl.w1 + le * c13,
-                      (uint8_t *)m->sl.s1 + le * s13, &z1) ||
-            upload_qw(4, r3.packed, r3.scales, w->inter, w->dim, (uint8_t *)m->sl.w3 + le * c13,
-                      (uint8_t *)m->sl.s3 + le * s13, &z3) ||
-            upload_qw(4, r2.packed, r2.scales, w->dim, w->inter, (uint8_t *)m->sl.w2 + le * c2,
-                      (uint8_t *)m->sl.s2 + le * s2, &z2)) {
-            apus_cuda_moe_destroy(m); return nullptr;
-        }
-        m->zero_scale |= z1 | z2 | z3;
-    }
-    // the same experts once more in the reference storage for the tcgen05 kernel
-    {
-        const char *env = getenv("APUS_MOE_TC");
-        m->use_tc = !(env && env[0] == '0') && w->inter % 512 == 0 && w->dim % 512 == 0 && nl > 0;
-    }
-    if (m->use_tc) {
+    // The local experts in the reference storage (packed nibbles [O, K/2], scale
+    // bytes [O, K/32]) as six expert-major slabs.  Device pointers that already
+    // form such slabs are used in place (the caller keeps them alive, like the
+    // stable host pointers of the reference's views); anything else is copied.
+    std::vector<ApusFp4W> r1(nl), r2(nl), r3(nl);
+    for (int le = 0; le < nl; le++)
+        if (resolve_expert(w, e_lo + le, &r1[le], &r2[le], &r3[le])) { apus_cuda_moe_destroy(m); return nullptr; }
+    bool adopt = nl > 0;
+    for (int le = 0; le < nl && adopt; le++)
+        adopt = r1[le].packed == r1[0].packed + le * c13 && r3[le].packed == r3[0].packed + le * c13 &&
+                r2[le].packed == r2[0].packed + le * c2 && r1[le].scales == r1[0].scales + le * s13 &&
+                r3[le].scales == r3[0].scales + le * s13 && r2[le].scales == r2[0].scales + le * s2;
+    if (adopt)
+        adopt = is_device_ptr(r1[0].packed) && is_device_ptr(r3[0].packed) && is_device_ptr(r2[0].packed) &&
+                is_device_ptr(r1[0].scales) && is_device_ptr(r3[0].scales) && is_device_ptr(r2[0].scales) &&
+                ((uintptr_t)r1[0].packed % 128 == 0) && ((uintptr_t)r3[0].packed % 128 == 0) &&
+                ((uintptr_t)r2[0].packed % 128 == 0) && ((uintptr_t)r1[0].scales % 16 == 0) &&
+                ((uintptr_t)r3[0].scales % 16 == 0) && ((uintptr_t)r2[0].scales % 16 == 0);
+    if (adopt) {
+        m->rw1 = r1[0].packed; m->rw3 = r3[0].packed; m->rw2 = r2[0].packed;
+        m->rs1 = r1[0].scales; m->rs3 = r3[0].scales; m->rs2 = r2[0].scales;
+    } else if (nl > 0) {
         if (cudaMalloc(&m->raw, total) != cudaSuccess) {
-            set_error("moe_create: device allocation of %zu bytes (tcgen05 copy) failed", total);
+            set_error("moe_create: device allocation of %zu bytes failed", total);
+            m->raw = nullptr;
             apus_cuda_moe_destroy(m); return nullptr;
         }
         uint8_t *q = m->raw;
@@ -284,25 +321,32 @@ ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi) {
         uint8_t *e3 = q; q += (size_t)nl * s13;
         uint8_t *e2 = q;
         m->rw1 = d1; m->rw3 = d3; m->rw2 = d2; m->rs1 = e1; m->rs3 = e3; m->rs2 = e2;
-        for (int e = e_lo; e < e_hi; e++) {
-            ApusFp4W r1, r2, r3;
-            if (w->hook_resolve) w->hook_resolve(w->hook_ctx, w->layer_id, e, &r1, &r2, &r3);
-            else { r1 = w->w1[e]; r2 = w->w2[e]; r3 = w->w3[e]; }
-            const int le = e - e_lo;
-            bool ok2 = cudaMemcpy(d1 + le * c13, r1.packed, c13, cudaMemcpyHostToDevice) == cudaSuccess &&
-                       cudaMemcpy(d3 + le * c13, r3.packed, c13, cudaMemcpyHostToDevice) == cudaSuccess &&
-                       cudaMemcpy(d2 + le * c2, r2.packed, c2, cudaMemcpyHostToDevice) == cudaSuccess &&
-                       cudaMemcpy(e1 + le * s13, r1.scales, s13, cudaMemcpyHostToDevice) == cudaSuccess &&
-                       cudaMemcpy(e3 + le * s13, r3.scales, s13, cudaMemcpyHostToDevice) == cudaSuccess &&
-                       cudaMemcpy(e2 + le * s2, r2.scales, s2, cudaMemcpyHostToDevice) == cudaSuccess;
-            if (!ok2) { set_error("moe_create: upload of expert %d failed", e); apus_cuda_moe_destroy(m); return nullptr; }
-        }
-        if (tc_make_weight_map(m->map_w1, d1, (long long)nl * w->inter, w->dim) ||
-            tc_make_weight_map(m->map_w3, d3, (long long)nl * w->inter, w->dim) ||
-            tc_make_weight_map(m->map_w2, d2, (long long)nl * w->dim, w->inter)) {
-            apus_cuda_moe_destroy(m); return nullptr;
+        for (int le = 0; le < nl; le++) {
+            bool ok2 = cudaMemcpy(d1 + le * c13, r1[le].packed, c13, cudaMemcpyDefault) == cudaSuccess &&
+                       cudaMemcpy(d3 + le * c13, r3[le].packed, c13, cudaMemcpyDefault) == cudaSuccess &&
+                       cudaMemcpy(d2 + le * c2, r2[le].packed, c2, cudaMemcpyDefault) == cudaSuccess &&
+                       cudaMemcpy(e1 + le * s13, r1[le].scales, s13, cudaMemcpyDefault) == cudaSuccess &&
+                       cudaMemcpy(e3 + le * s13, r3[le].scales, s13, cudaMemcpyDefault) == cudaSuccess &&
+                       cudaMemcpy(e2 + le * s2, r2[le].scales, s2, cudaMemcpyDefault) == cudaSuccess;
+            if (!ok2) { set_error("moe_create: upload of expert %d failed", e_lo + le); apus_cuda_moe_destroy(m); return nullptr; }
         }
         c.bytes_uploaded += total;
+    }
+    // tcgen05 kernel on that storage when the shapes allow; otherwise (or on
+    // request, apus_cuda_moe_use_tc) the mma.sync kernel on a re-tiled copy
+    {
+        const char *env = getenv("APUS_MOE_TC");
+        m->use_tc = !(env && env[0] == '0') && w->inter % 512 == 0 && w->dim % 512 == 0 && nl > 0;
+    }
+    if (m->use_tc) {
+        if (tc_make_weight_map(m->map_w1, m->rw1, (long long)nl * w->inter, w->dim) ||
+            tc_make_weight_map(m->map_w3, m->rw3, (long long)nl * w->inter, w->dim) ||
+            tc_make_weight_map(m->map_w2, m->rw2, (long long)nl * w->dim, w->inter)) {
+            apus_cuda_moe_destroy(m); return nullptr;
+        }
+        m->can_tc = true;
+    } else if (build_tiled(m)) {
+        apus_cuda_moe_destroy(m); return nullptr;
     }
     // shared expert
     struct { DevQW *d; const ApusFp8W *h; int O, K; } sh[3] = {
@@ -316,7 +360,6 @@ ApusCudaMoe *apus_cuda_moe_create(const ApusMoeW *w, int e_lo, int e_hi) {
     }
     m->weight_bytes = total + m->sw1.bytes() + m->sw2.bytes() + m->sw3.bytes() +
                       (size_t)w->E * w->dim * 4 + (w->hash ? 0 : (size_t)w->E * 4);
-    (void)c;
     return m;
 }
 
@@ -354,8 +397,9 @@ ApusCudaMoe *apus_cuda_moe_get(const ApusMoeW *w) {
  * mma.sync kernel on the re-tiled copy.  Returns the setting now in force. */
 int apus_cuda_moe_use_tc(ApusCudaMoe *m, int enable) {
     if (!m) return -1;
-    if (enable >= 0 && m->raw) {
+    if (enable >= 0 && m->can_tc) {
         bool on = enable != 0;
+        if (!on && build_tiled(m)) return -1;
         if (on != m->use_tc) { m->use_tc = on; m->cap_r = 0; }    // act maps are rebuilt by ensure()
     }
     return m->use_tc ? 1 : 0;
@@ -392,7 +436,7 @@ int apus_cuda_moe_set_hash_table(ApusCudaMoe *m, const int64_t *tid2eid, int64_t
     if (m->tid2eid) { cudaDeviceSynchronize(); cudaFree(m->tid2eid); m->tid2eid = nullptr; }
     size_t bytes = (size_t)vocab * m->topk * 8;
     APUS_CUDA_OK(cudaMalloc(&m->tid2eid, bytes));
-    APUS_CUDA_OK(cudaMemcpy(m->tid2eid, tid2eid, bytes, cudaMemcpyHostToDevice));
+    APUS_CUDA_OK(cudaMemcpy(m->tid2eid, tid2eid, bytes, cudaMemcpyDefault));
     m->vocab = vocab;
     return 0;
 }

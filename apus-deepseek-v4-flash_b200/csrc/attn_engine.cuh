@@ -37,7 +37,15 @@ struct StepBufs {
     int32_t *sel, *idxs;
 };
 
-int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A);
+// Device copies that belong to one object (a model) instead of the global cache.
+struct WeightOwner {
+    std::vector<DevQW *> qws;
+    std::vector<DevBuf *> bufs;
+    void release();
+};
+DevQW *get_qw(WeightOwner *own, int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K);
+const void *get_dense(WeightOwner *own, const void *src, size_t bytes);
+int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A, WeightOwner *own = nullptr);
 // Allocates (grows) and initialises the state of B sequences: zero ring and
 // carries, score carries at -inf, caches of `cap` entries.
 int attn_state_init(const ApusAttnCfg &c, StateDev &S, int B, int cap);

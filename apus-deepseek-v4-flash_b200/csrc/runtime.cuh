@@ -70,6 +70,7 @@ int upload_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K
 DevQW *new_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K);
 DevQW *cached_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K);
 const void *cached_dense(const void *host, size_t bytes);
+bool is_device_ptr(const void *p);
 
 // Quantised linear on device rows: act quant + block-scaled GEMM (+ BF16 round).
 // `xq`/`xs` are caller workspaces of M*K bytes and M*K/128 floats.

@@ -116,7 +116,7 @@ class AttnLayer:
         D.update(dims or {})
         self.D, self.kind = D, kind
         rng = np.random.default_rng(seed)
-        ratio = {"swa": 0, "csa": 4, "hca": 8}[kind]
+        ratio = {"swa": 0, "csa": 4, "hca": 8, "hca128": 128}[kind]
         self.ratio = ratio
         dim, h, d, ql = D["dim"], D["n_heads"], D["head_dim"], D["q_lora"]
         G, ol, ih, idm = D["o_groups"], D["o_lora"], D["idx_heads"], D["idx_dim"]
@@ -201,6 +201,10 @@ def attn_inputs(seed, n_tokens, dim):
 
 # ---- block / model ------------------------------------------------------------------------
 MODEL_DIMS = dict(hc=4, iters=20, hc_eps=1e-6, norm_eps=1e-6, vocab=384, E=8, topk=2, inter=128)
+# one block at the real model's sizes (reference-0731/config.json) with 8 routed experts
+FLASH_ATTN_DIMS = dict(dim=4096, n_heads=64, head_dim=512, rope_dim=64, q_lora=1024, o_groups=8, o_lora=1024,
+                       window=128, idx_heads=64, idx_dim=128, idx_topk=512, max_pos=256)
+FLASH_MOE_DIMS = dict(E=8, topk=6, inter=2048)
 
 
 class BlockLayer:
@@ -210,12 +214,12 @@ class BlockLayer:
     the reference's rope tables for this layer kind (read from the committed
     golden file; the reference builds them in c/layer.h:167-190)."""
 
-    def __init__(self, seed, kind, cos, sin, hash_vocab=0, dims=None):
+    def __init__(self, seed, kind, cos, sin, hash_vocab=0, dims=None, attn_dims=None):
         from apus_b200 import capi
         M = dict(MODEL_DIMS)
         M.update(dims or {})
         self.M = M
-        self.attn = AttnLayer(seed, kind)
+        self.attn = AttnLayer(seed, kind, attn_dims)
         dim, hc = self.attn.D["dim"], M["hc"]
         self.moe = synth.MoeWeights(seed=seed + 500, E=M["E"], dim=dim, inter=M["inter"], topk=M["topk"],
                                     hash_vocab=hash_vocab)

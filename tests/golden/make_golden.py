@@ -117,13 +117,14 @@ class RefInterm(C.Structure):
                 ("ffn_norm_out", C.c_void_p), ("moe", capi.MoeInterm), ("moe_out", C.c_void_p)]
 
 
-def ref_block(L, seed, kind, chunks):
+def ref_block(L, seed, kind, chunks, flash=False):
     """The reference's apus_block_forward over consecutive chunks (prefill at
     position 0, then decodes) through the shim's descriptor adapter, with the
     stage outputs its ApusInterm exposes."""
     rope = rope_pair(L)
     cos, sin = rope["plain" if kind == "swa" else "yarn"]
-    B = cases.BlockLayer(seed, kind, cos, sin)
+    B = cases.BlockLayer(seed, kind, cos, sin, dims=cases.FLASH_MOE_DIMS, attn_dims=cases.FLASH_ATTN_DIMS) \
+        if flash else cases.BlockLayer(seed, kind, cos, sin)
     S = cases.AttnState(B.attn)
     M, dim = B.M, B.attn.D["dim"]
     hc = M["hc"]
@@ -148,6 +149,11 @@ def ref_block(L, seed, kind, chunks):
         L.ref_block_forward_interm(C.byref(B.desc), hc, M["iters"], M["hc_eps"], M["norm_eps"], C.byref(S.st),
                                    P(out[pos:pos + n]), P(ids[pos:pos + n]), n, pos, C.byref(it))
         pos += n
+    if flash:          # real sizes: keep the hidden states of the listed tokens only, as BF16 bits
+        from apus_b200.synth import bf16_bits
+        keep = FLASH_KEEP[kind]
+        return dict(out_bits=bf16_bits(out[keep]), o_bits=bf16_bits(A["o_out"][keep]),
+                    moe_bits=bf16_bits(A["moe_out"][keep]))
     return dict(out=out, win=S.win.copy(), **A)
 
 
@@ -255,6 +261,9 @@ def main():
         G[f"rope.{name}.cos"], G[f"rope.{name}.sin"] = cos, sin
     for tag, (seed, kind, chunks) in BLOCK_CASES.items():
         G.update({f"{tag}.{k}": v for k, v in ref_block(L, seed, kind, chunks).items()})
+    for tag, (seed, kind, chunks) in BLOCK_FLASH_CASES.items():
+        G.update({f"{tag}.{k}": v for k, v in ref_block(L, seed, kind, chunks, flash=True).items()})
+        print(tag, "done", flush=True)
     for tag, args in MODEL_CASES.items():
         G.update({f"{tag}.{k}": v for k, v in ref_generate(L, *args).items()})
     np.savez_compressed(HERE / "ref_cases.npz", **G)
@@ -302,6 +311,13 @@ BLOCK_CASES = {
     "block_csa": (82, "csa", [9] + [1] * 12),
     "block_hca": (83, "hca", [10] + [1] * 10),
 }
+# one block at the real model's sizes; hca128 completes its first compressed entry at token 127
+BLOCK_FLASH_CASES = {
+    "flash_swa": (101, "swa", [3] + [1] * 4),
+    "flash_csa": (102, "csa", [6] + [1] * 7),
+    "flash_hca": (103, "hca128", [2] + [1] * 130),
+}
+FLASH_KEEP = {"swa": list(range(7)), "csa": list(range(13)), "hca128": [0, 1, 2, 64, 126, 127, 128, 129, 130, 131]}
 # tag -> (seed, layers, sequences, prompt tokens, generated tokens)
 MODEL_CASES = {
     "model_one": (91, 3, 1, 9, 14),

@@ -26,7 +26,7 @@ import pytest
 import cases
 from _gpu import bf16_ulps, bits, lib
 from _oracle import P, rel_l2
-from golden.make_golden import BLOCK_CASES, MODEL_CASES
+from golden.make_golden import BLOCK_CASES, BLOCK_FLASH_CASES, FLASH_KEEP, MODEL_CASES
 
 pytestmark = pytest.mark.gpu
 G = np.load(Path(__file__).resolve().parent / "golden" / "ref_cases.npz")
@@ -46,10 +46,11 @@ def fresh_caches():
     lib().apus_cuda_disable()
 
 
-def run_block(L, tag):
-    seed, kind, chunks = BLOCK_CASES[tag]
+def run_block(L, tag, flash=False):
+    seed, kind, chunks = (BLOCK_FLASH_CASES if flash else BLOCK_CASES)[tag]
     cos, sin = rope()["plain" if kind == "swa" else "yarn"]
-    B = cases.BlockLayer(seed, kind, cos, sin)
+    B = cases.BlockLayer(seed, kind, cos, sin, dims=cases.FLASH_MOE_DIMS, attn_dims=cases.FLASH_ATTN_DIMS) \
+        if flash else cases.BlockLayer(seed, kind, cos, sin)
     S = cases.AttnState(B.attn)
     M, dim = B.M, B.attn.D["dim"]
     total = sum(chunks)
@@ -74,6 +75,26 @@ def test_block_vs_reference(tag):
     assert rel_l2(out, want) <= 5e-3
     assert max(per_tok) <= 2e-2
     assert rel_l2(S.win, G[f"{tag}.win"]) <= 5e-3
+
+
+@pytest.mark.parametrize("tag", list(BLOCK_FLASH_CASES))
+def test_block_at_model_sizes(tag):
+    """One block with the real model's attention and expert shapes (hidden 4096,
+    64 heads x 512, q_lora 1024, window 128, indexer 64 x 128 top-512, experts
+    2048 x 4096 on the tcgen05 kernel, compression ratios 4 and 128) against the
+    reference's hidden states of selected tokens, kept as BF16 bits."""
+    out, S, total = run_block(lib(), tag, flash=True)
+    kind = BLOCK_FLASH_CASES[tag][1]
+    keep = FLASH_KEEP[kind]
+    want = (G[f"{tag}.out_bits"].astype(np.uint32) << 16).view(np.float32)
+    got = out[keep]
+    assert np.isfinite(out).all()
+    u = bf16_ulps(got, want)
+    per_tok = [rel_l2(got[i], want[i]) for i in range(len(keep))]
+    print(tag, "elements off:", int((u > 0).sum()), "of", u.size, "rel-L2", rel_l2(got, want), "max per-token",
+          max(per_tok))
+    assert rel_l2(got, want) <= 5e-3
+    assert max(per_tok) <= 2e-2
 
 
 @pytest.mark.parametrize("tag", list(BLOCK_CASES))
