@@ -42,6 +42,7 @@ void DevQW::release() {
     for (auto &kv : tables) cudaFree(kv.second);
     tables.clear();
     if (owned) { if (codes) cudaFree(codes); if (scales) cudaFree(scales); }
+    else if (tc && scales) cudaFree(scales);        // adopted codes, own scale copy
     codes = scales = nullptr;
 }
 
@@ -144,6 +145,28 @@ DevQW *new_qw(int fmt, const uint8_t *codes, const uint8_t *scales, int O, int K
     w->fmt = fmt; w->O = O; w->K = K;
     size_t cb = fmt == 4 ? (size_t)O * K / 2 : (size_t)O * K;
     size_t sb = fmt == 4 ? (size_t)O * K / 32 : (size_t)((O + 127) / 128) * (K / 128);
+    static const bool fp8_tc = !(getenv("APUS_FP8_TC") && getenv("APUS_FP8_TC")[0] == '0');
+    if (fmt == 8 && fp8_tc && O % 128 == 0 && K <= 16384) {
+        // tcgen05 kernel: no re-tiling; a device buffer of the caller is used in place
+        const bool adopt = is_device_ptr(codes) && ((uintptr_t)codes & 15) == 0;
+        bool ok = cudaMalloc(&w->scales, sb) == cudaSuccess &&
+                  cudaMemcpy(w->scales, scales, sb, cudaMemcpyDefault) == cudaSuccess;
+        if (ok && adopt) { w->codes = const_cast<uint8_t *>(codes); w->owned = false; }
+        else if (ok) {
+            ok = cudaMalloc(&w->codes, cb) == cudaSuccess &&
+                 cudaMemcpy(w->codes, codes, cb, cudaMemcpyDefault) == cudaSuccess;
+            if (ok) ctx().bytes_uploaded += cb + sb;
+        }
+        if (!ok) set_error("upload of %zu FP8 weight bytes failed", cb + sb);
+        if (ok) ok = tc8_make_weight_map(w->map, w->codes, O, K) == 0;
+        if (!ok) {
+            if (!w->owned) { w->codes = nullptr; if (w->scales) cudaFree(w->scales); w->scales = nullptr; }
+            w->release(); delete w;
+            return nullptr;
+        }
+        w->tc = true;
+        return w;
+    }
     if (cudaMalloc(&w->codes, cb) != cudaSuccess || cudaMalloc(&w->scales, sb) != cudaSuccess) {
         set_error("cudaMalloc of %zu weight bytes failed", cb + sb);
         w->release(); delete w;
@@ -192,16 +215,37 @@ const void *cached_dense(const void *host, size_t bytes) {
 }
 
 // ---- composite device ops ----------------------------------------------------------------------
+// Block-scaled GEMM of pre-quantised activation rows against one matrix, or a
+// gate/up pair with SwiGLU (`other` != NULL): the tcgen05 FP8 kernel when the
+// matrix is held in the reference storage, else the mma.sync kernel.
+int qgemm_dev(DevQW *w, DevQW *other, const uint8_t *acodes, const float *ascales, int M, float *out,
+              bool round_out, float limit, cudaStream_t st) {
+    if (M <= 0) return 0;
+    if (w->tc && (!other || other->tc)) {
+        alignas(64) unsigned char map_x[128];
+        if (tc_make_act_map(map_x, acodes, M, w->K)) return 1;
+        Tc8Args t = {};
+        t.map_a = w->map; t.map_b = other ? other->map : w->map; t.map_x = map_x;
+        t.scales_a = w->scales; t.scales_b = other ? other->scales : nullptr; t.ascales = ascales;
+        t.M = M; t.O = w->O; t.K = w->K; t.pair = other ? 1 : 0; t.round_out = round_out; t.limit = limit;
+        t.out = out;
+        return gemm_tc8(t, st);
+    }
+    APUS_REQUIRE(!w->tc && (!other || !other->tc), "qgemm: gate and up matrices are held in different layouts");
+    GemmSmallArgs a = {};
+    a.fmt = w->fmt; a.pair = other ? 1 : 0; a.round_out = round_out; a.limit = limit; a.O = w->O; a.K = w->K;
+    if (w->table_for(M, other != nullptr, other, const_cast<GemmGroup **>(&a.groups), &a.n_groups)) return 1;
+    a.max_rows = M < 32 ? M : 32;
+    a.acodes = acodes; a.ascales = ascales; a.out = out;
+    a.zero_scale = w->zero_scale | (other ? other->zero_scale : 0);
+    return gemm_small(a, st);
+}
+
 int qlinear_dev(DevQW *w, const float *x, float *out, int M, uint8_t *xq, float *xs,
                 bool round_out, cudaStream_t st) {
     if (M <= 0) return 0;
     if (act_quant(x, nullptr, M, w->K, xq, xs, nullptr, st)) return 1;
-    GemmSmallArgs a = {};
-    a.fmt = w->fmt; a.pair = 0; a.round_out = round_out; a.O = w->O; a.K = w->K;
-    if (w->table_for(M, false, nullptr, const_cast<GemmGroup **>(&a.groups), &a.n_groups)) return 1;
-    a.max_rows = M < 32 ? M : 32;
-    a.acodes = xq; a.ascales = xs; a.out = out; a.zero_scale = w->zero_scale;
-    return gemm_small(a, st);
+    return qgemm_dev(w, nullptr, xq, xs, M, out, round_out, 0.f, st);
 }
 
 int expert_dev(DevQW *w1, DevQW *w2, DevQW *w3, float limit, const float *x, int rows,
@@ -210,13 +254,7 @@ int expert_dev(DevQW *w1, DevQW *w2, DevQW *w3, float limit, const float *x, int
     APUS_REQUIRE(w1->fmt == w3->fmt && w1->fmt == w2->fmt && w1->O == w3->O && w1->K == w3->K &&
                  w2->K == w1->O && w2->O == w1->K, "expert: inconsistent weight shapes");
     if (act_quant(x, nullptr, rows, w1->K, ws.xq, ws.xs, nullptr, st)) return 1;
-    GemmSmallArgs a = {};
-    a.fmt = w1->fmt; a.pair = 1; a.limit = limit; a.O = w1->O; a.K = w1->K;
-    if (w1->table_for(rows, true, w3, const_cast<GemmGroup **>(&a.groups), &a.n_groups)) return 1;
-    a.max_rows = rows < 32 ? rows : 32;
-    a.acodes = ws.xq; a.ascales = ws.xs; a.out = ws.h;
-    a.zero_scale = w1->zero_scale | w3->zero_scale;
-    if (gemm_small(a, st)) return 1;
+    if (qgemm_dev(w1, w3, ws.xq, ws.xs, rows, ws.h, false, limit, st)) return 1;
     return qlinear_dev(w2, ws.h, out, rows, ws.hq, ws.hs, true, st);
 }
 
@@ -342,6 +380,10 @@ static int host_qlinear(int fmt, const uint8_t *codes, const uint8_t *scales, in
         return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)M * O * 4, cudaMemcpyDeviceToHost, c.stream));
     APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    if (w->tc) {
+        int stt = gemm_tc_status(1);
+        APUS_REQUIRE(stt == 0, "a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    }
     return 0;
 }
 
@@ -388,15 +430,11 @@ static int host_qgemm(int fmt, const uint8_t *w, const uint8_t *ws, const uint8_
         return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(dq, acodes, (size_t)M * K, cudaMemcpyHostToDevice, c.stream));
     APUS_CUDA_OK(cudaMemcpyAsync(ds, as, (size_t)M * (K / 128) * 4, cudaMemcpyHostToDevice, c.stream));
-    GemmSmallArgs a = {};
-    a.fmt = fmt; a.O = O; a.K = K; a.round_out = 0;
-    if (dw->table_for(M, false, nullptr, const_cast<GemmGroup **>(&a.groups), &a.n_groups)) return 1;
-    a.max_rows = M < 32 ? M : 32;
-    a.acodes = (uint8_t *)dq; a.ascales = (float *)ds; a.out = (float *)dout;
-    a.zero_scale = dw->zero_scale;
-    if (gemm_small(a, c.stream)) return 1;
+    if (qgemm_dev(dw, nullptr, (uint8_t *)dq, (float *)ds, M, (float *)dout, false, 0.f, c.stream)) return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)M * O * 4, cudaMemcpyDeviceToHost, c.stream));
     APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
     return 0;
 }
 

@@ -366,6 +366,8 @@ int apus_cuda_attention(const ApusAttnCfg *cfg, const ApusAttnW *w, ApusAttnS *s
     if (ratio) {
         if (interm) { interm->comp_nb = st->comp.nb - nb0; interm->idx_nb = cfg->has_indexer ? st->idx_comp.nb - inb0 : 0; }
     }
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "attention: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
     return 0;
 }
 

@@ -29,12 +29,12 @@
 // empty[s] (MMAs of the stage retired, via tcgen05.commit), done.
 // Every wait is bounded; on expiry the CTA records a status word, drains and
 // frees its tensor memory instead of hanging.
-#include <cuda.h>
-
-#include "common.cuh"
 #include "kernels.cuh"
+#include "tc_common.cuh"
 
 namespace apus {
+
+__device__ int g_tc_status = 0;
 
 namespace {
 
@@ -44,54 +44,6 @@ constexpr int TC_A_BYTES = 128 * 128;    // one weight tile in shared memory
 constexpr int TC_B_BYTES = TC_N * 128;
 constexpr int TC_TMEM_COLS = 128;
 constexpr int TC_COL_D0 = 0, TC_COL_D1 = 32, TC_COL_SF = 64, TC_SF_STRIDE = 12;
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
-
-__device__ int g_tc_status = 0;          // first failure code recorded by any CTA
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait for the phase with the given parity; false on expiry or abort.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((it & 1023u) == 1023u && *abort_flag) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1,
-                                            uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
-}
-// K-major operand tile with 128-byte swizzled rows (8-row groups 1024 B apart).
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (uint64_t)1 << 46;                            // descriptor version
-    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
-    return d;
-}
 // Instruction descriptor, kind::mxf8f6f4 block-scaled: A = E2M1, B = E4M3, both
 // K-major, UE8M0 scales, M = 128, N = TC_N; sf ids pick the scale byte.
 __device__ __forceinline__ uint32_t umma_idesc(uint32_t a_sf, uint32_t b_sf) {
@@ -108,30 +60,6 @@ __device__ __forceinline__ void umma_mxf8f6f4(uint32_t d_tmem, uint64_t adesc, u
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
-                 ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t a) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(a) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-          "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-          "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-          "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-}
-
 __device__ __forceinline__ float swiglu_tc(float gate, float up, float limit) {
     float g = bf16_round(gate), u = bf16_round(up);
     if (limit > 0.f) {
@@ -304,12 +232,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                      : "memory");
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
+}  // namespace
 
-EncodeTiledFn encode_fn() {
+EncodeTiledFn tc_encode_fn() {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
         void *p = nullptr;
@@ -321,11 +246,9 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-}  // namespace
-
 // Tensor map over packed E2M1 codes [rows, K/2] (K elements per row), 128x128 boxes.
 int tc_make_weight_map(void *out_map, const void *codes, long long rows, int K) {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = tc_encode_fn();
     APUS_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from the driver");
     APUS_REQUIRE(K % 128 == 0 && ((uintptr_t)codes & 31) == 0, "tensor map: K=%d / base alignment", K);
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -341,7 +264,7 @@ int tc_make_weight_map(void *out_map, const void *codes, long long rows, int K) 
 
 // Tensor map over E4M3 activation codes [rows, K] bytes, 128 x 32 boxes.
 int tc_make_act_map(void *out_map, const void *codes, long long rows, int K) {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = tc_encode_fn();
     APUS_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K};
@@ -386,7 +309,8 @@ int gemm_tc_status(int reset) {
         int z = 0;
         cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int));
     }
-    return v;
+    const int v8 = gemm_tc8_status(reset);          // the FP8 kernel keeps its own word (codes 11..15)
+    return v ? v : v8;
 }
 
 }  // namespace apus

@@ -82,6 +82,19 @@ int gemm_tc_status(int reset);
 int tc_make_weight_map(void *out_map, const void *codes, long long rows, int K);
 int tc_make_act_map(void *out_map, const void *codes, long long rows, int K);
 
+// ---- tcgen05 FP8 GEMM on the reference weight storage (gemm_tc8.cu) -----------------------
+struct Tc8Args {
+    const void *map_a, *map_b, *map_x;   // host pointers to CUtensorMap objects (weights A/B, act codes)
+    const uint8_t *scales_a, *scales_b;  // weight tile scales [O/128, K/128]
+    const float *ascales;                // activation scales [M, K/128]
+    int M, O, K, pair, round_out;        // activation rows 32*y .. of CTA row y
+    float limit;
+    float *out;                          // [M, O]
+};
+int gemm_tc8(const Tc8Args &a, cudaStream_t st);
+int gemm_tc8_status(int reset);
+int tc8_make_weight_map(void *out_map, const void *codes, long long rows, int K);
+
 // ---- dense f32 / bf16 linears (linear.cu) ------------------------------------------------
 // out[m,o] = sum_k x[m,k]*w[o,k]; flags as APUS_CUDA_R_IN/R_OUT/W_BF16.
 int f32_linear(const void *w, const float *x, float *out, int M, int K, int O,

@@ -33,6 +33,11 @@ struct DevQW {
     uint8_t *scales = nullptr;// MXFP4: tiled scales; FP8: [O/128, K/128] bytes
     int zero_scale = 0;       // MXFP4 only
     bool owned = true;        // false when the storage belongs to a slab
+    // FP8 on the tcgen05 kernel: codes stay in the reference storage [O, K]
+    // (`codes` then points at it; owned == false when a device buffer of the
+    // caller is used in place) and are read through this TMA tensor map
+    bool tc = false;
+    alignas(64) unsigned char map[128];
     std::map<int, GemmGroup *> tables;   // device work-item tables keyed by M
     size_t bytes() const;
     int table_for(int M, bool pair, const DevQW *other, GemmGroup **out, int *n_groups);
