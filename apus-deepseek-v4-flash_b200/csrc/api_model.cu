@@ -300,6 +300,11 @@ int apus_cuda_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float
 
 int64_t apus_cuda_model_pos(const ApusCudaModel *m) { return m ? m->pos : -1; }
 
+ApusCudaMoe *apus_cuda_model_moe(ApusCudaModel *m, int layer) {
+    if (!m || layer < 0 || layer >= m->n_layers) return nullptr;
+    return m->layers[layer].moe;
+}
+
 int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int32_t *next) {
     if (!m) { set_error("NULL model"); return 1; }
     if (s <= 0) return 0;

@@ -83,6 +83,7 @@ int ApusCudaMoe::ensure(int s, int n_rout) {
             b_hs.get(R * (inter / 128) * 4, nullptr) || b_eo.get(R * dim * 4, nullptr) ||
             b_t13.get(max_groups * sizeof(TcGroup), nullptr) || b_t2.get(max_groups * sizeof(TcGroup), nullptr))
             return 1;
+        APUS_CUDA_OK(cudaMemset(b_ng.p, 0, 256));
         if (use_tc && (tc_make_act_map(map_xq, b_xq.p, (long long)(b_xq.cap / dim), dim) ||
                        tc_make_act_map(map_hq, b_hq.p, (long long)(b_hq.cap / inter), inter)))
             return 1;
@@ -429,6 +430,20 @@ int apus_cuda_moe_timing_read(ApusCudaMoe *m, double *ms_gate_up, double *ms_dow
     if (launches) *launches = n;
     m->ev_used = 0;
     return 0;
+}
+
+/* Work items (expert x up to 32 rows) launched since the last reset: at decode
+ * sizes one per distinct expert touched, i.e. the number of expert weight sets
+ * the GEMV kernels streamed. */
+long long apus_cuda_moe_work_items(ApusCudaMoe *m, int reset) {
+    if (!m || !m->b_ng.p) return 0;
+    int v[4] = {0, 0, 0, 0};
+    cudaStream_t st = ctx().stream;
+    if (cudaMemcpyAsync(v, m->b_ng.p, sizeof v, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+        return -1;
+    if (reset) { cudaMemsetAsync(m->b_ng.as<int>() + 2, 0, sizeof(int), st); cudaStreamSynchronize(st); }
+    return v[2];
 }
 
 int apus_cuda_moe_set_hash_table(ApusCudaMoe *m, const int64_t *tid2eid, int64_t vocab) {

@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(1024)
 row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y, int y_stride, int n,
                int flags, const float *__restrict__ norm_w, float eps, int rd,
                const float *__restrict__ cs, int rows_per_cs, int cs_stride) {
-    extern __shared__ float s_v[];            // [n] row, then [n/32 + 32] scratch
+    extern __shared__ __align__(16) float s_v[];   // [n] row, then [n/32 + 32] scratch
     float *s_red = s_v + n;
     const int row = blockIdx.x, i = threadIdx.x;
     const bool on = i < n;
@@ -40,12 +40,7 @@ row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y,
         if (flags & ROW_SEQ_SUM) {             // the reference's loop order: one accumulator, index ascending
             if (on) s_v[i] = __fmul_rn(v, v);
             __syncthreads();
-            if (i == 0) {
-                float a = 0.f;
-#pragma unroll 8
-                for (int k = 0; k < n; k++) a = __fadd_rn(a, s_v[k]);
-                s_red[0] = a;
-            }
+            if (i == 0) s_red[0] = seq_sum_smem(s_v, n, 0.f);
         } else {
             float ss = warp_sum(on ? __fmul_rn(v, v) : 0.f);
             if ((i & 31) == 0) s_red[i >> 5] = ss;

@@ -46,8 +46,36 @@ int sum_order();                               // api.cu
 
 // ---- scalar format helpers (device + host) -------------------------------------
 
-// Round-to-nearest-even to BF16, kept in an f32 (reference c/fp4.h:262-270).
-__host__ // e^x and log(1+x) evaluated in double and rounded once to f32.  The reference
+// acc + s[0] + s[1] + ... + s[n-1], one accumulator, index ascending, every add
+// rounded: the order of the reference's scalar loops.  `s` is shared memory,
+// 16-byte aligned.  The adds form one dependent chain (about four cycles each),
+// so the loads are issued a batch of sixteen values ahead of the adds that
+// consume them; left to itself the compiler keeps each load next to its add
+// and the chain then pays the shared-memory latency per element.
+__device__ __forceinline__ float seq_add4(float acc, const float4 &v) {
+    acc = __fadd_rn(acc, v.x); acc = __fadd_rn(acc, v.y);
+    acc = __fadd_rn(acc, v.z); acc = __fadd_rn(acc, v.w);
+    return acc;
+}
+__device__ __forceinline__ float seq_sum_smem(const float *s, int n, float acc) {
+    const float4 *p = reinterpret_cast<const float4 *>(s);
+    const int n4 = n >> 2;
+    int i = 0;
+    float4 c0, c1, c2, c3;
+    c0 = c1 = c2 = c3 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (n4 >= 4) { c0 = p[0]; c1 = p[1]; c2 = p[2]; c3 = p[3]; }
+    for (; i + 4 <= n4; i += 4) {
+        const float4 d0 = c0, d1 = c1, d2 = c2, d3 = c3;
+        if (i + 8 <= n4) { c0 = p[i + 4]; c1 = p[i + 5]; c2 = p[i + 6]; c3 = p[i + 7]; }
+        acc = seq_add4(acc, d0); acc = seq_add4(acc, d1);
+        acc = seq_add4(acc, d2); acc = seq_add4(acc, d3);
+    }
+    for (; i < n4; i++) acc = seq_add4(acc, p[i]);
+    for (int k = n4 * 4; k < n; k++) acc = __fadd_rn(acc, s[k]);
+    return acc;
+}
+
+// e^x and log(1+x) evaluated in double and rounded once to f32.  The reference
 // calls the host libm's expf/log1pf; a correctly rounded result agrees with any
 // good libm (glibc's expf stays under 0.502 ulp) on all but a vanishing share
 // of inputs, while the device's f32 expf may be 2 ulp off and would flip a
@@ -55,7 +83,8 @@ __host__ // e^x and log(1+x) evaluated in double and rounded once to f32.  The r
 __device__ __forceinline__ float exp_rn(float x) { return (float)exp((double)x); }
 __device__ __forceinline__ float log1p_rn(float x) { return (float)log1p((double)x); }
 
-__device__ __forceinline__ float bf16_round(float x) {
+// Round-to-nearest-even to BF16, kept in an f32 (reference c/fp4.h:262-270).
+__host__ __device__ __forceinline__ float bf16_round(float x) {
 #ifdef __CUDA_ARCH__
     uint32_t u = __float_as_uint(x);
 #else

@@ -256,7 +256,11 @@ int gemm_tc8(const Tc8Args &a, cudaStream_t st) {
     APUS_REQUIRE(a.K % 128 == 0 && a.K <= 128 * T8_MAX_NC && a.O % 128 == 0,
                  "gemm_tc8: unsupported shape O=%d K=%d", a.O, a.K);
     if (a.M <= 0) return 0;
-    return a.pair ? launch_tc8<true, 3>(a, st) : launch_tc8<false, 4>(a, st);
+    // few CTAs (small O): one CTA per SM with a deep ring, so that each CTA keeps
+    // ~200 KB of weight tiles in flight; many CTAs: two per SM with a short ring
+    const long long ctas = (long long)(a.O / 128) * ((a.M + T8_N - 1) / T8_N);
+    if (a.pair) return ctas <= 148 ? launch_tc8<true, 5>(a, st) : launch_tc8<true, 3>(a, st);
+    return ctas <= 148 ? launch_tc8<false, 10>(a, st) : launch_tc8<false, 4>(a, st);
 }
 
 int gemm_tc8_status(int reset) {

@@ -63,83 +63,143 @@ mhc_mix_kernel(const float *__restrict__ x4, const float *__restrict__ fn, int n
 // The same dots in the reference's summation order (c/mhc.h:159-176: one f32
 // accumulator per dot, products rounded before each add, index ascending).
 // That order is a chain of n*d dependent adds per dot, so the kernel is bound
-// by add latency, not bandwidth: 256 producer threads stage rounded products
-// of a tile in shared memory while one lane per dot (the consumer warps) walks
-// the previous tile.  One CTA per token; chain c < nmix is fn_c . x, chain
-// nmix is sum x^2.
-__global__ void __launch_bounds__(320)
+// by add latency (about 35 us at 4 x 4096), not bandwidth: 256 producer threads
+// stage rounded products of a tile in shared memory while one lane per dot (the
+// consumer warp) walks the previous tile.  One CTA per (token, group of
+// MIX_CPG chains): the chains of a token are independent, so spreading them
+// over CTAs divides the producers' load without lengthening any chain.
+// Chain c < nmix is fn_c . x, chain nmix is sum x^2.
+#define MIX_CPG 4
+// TOK tokens share one CTA (and one read of the fn tile): consumer lane
+// l = token * MIX_CPG + chain, TOK * MIX_CPG <= 32.
+template <int TOK>
+__global__ void __launch_bounds__(288)
 mhc_mix_seq_kernel(const float *__restrict__ x4, const float *__restrict__ fn, int nx, int nmix,
-                   int MIX_TI, float *__restrict__ raw) {
+                   int MIX_TI, int rows, float *__restrict__ raw) {
     extern __shared__ __align__(16) float s_prod[];
     const int C = nmix + 1, stride = MIX_TI + 4, tid = threadIdx.x;
-    const int row = blockIdx.x, nt = (nx + MIX_TI - 1) / MIX_TI;
-    const float *x = x4 + (size_t)row * nx;
+    const int row0 = blockIdx.x * TOK, c_lo = blockIdx.y * MIX_CPG, Cl = min(MIX_CPG, C - c_lo);
+    const int ntok = min(TOK, rows - row0);
+    const int nt = (nx + MIX_TI - 1) / MIX_TI;
     const bool consumer = tid >= 256;
-    float acc0 = 0.f, acc1 = 0.f;             // a consumer lane owns chains c0 and c0 + 64
-    const int c0 = tid - 256;
+    float acc = 0.f;
+    const int cl = tid - 256;                 // consumer lane
+    const int my_tok = cl / MIX_CPG, my_c = cl - my_tok * MIX_CPG;
+    const bool live = consumer && my_tok < ntok && my_c < Cl;
+    // Producer thread p owns the 16-byte word p of every tile when a tile has at
+    // most 256 words per chain group (TOK > 1: MIX_TI = 256), and keeps the fn
+    // word of the NEXT tile it will multiply in a register, loaded one whole
+    // iteration ahead; with a single token per CTA (large tiles) it loops.
+    const int q = MIX_TI / 4, total = Cl * q;
+    const bool one_word = TOK > 1;
+    const int pc = tid / q, pi4 = tid - pc * q;          // one_word: this thread's (chain, word)
+    const bool p_on = one_word && !consumer && tid < total;
+    const bool p_sq = c_lo + pc >= nmix;
+    float4 f_next = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto fetch_fn = [&](int t) {
+        const int gi = t * MIX_TI + 4 * pi4;
+        f_next = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p_on && !p_sq && t < nt && gi < nx)
+            f_next = __ldg(reinterpret_cast<const float4 *>(fn + (size_t)(c_lo + pc) * nx + gi));
+    };
     auto produce = [&](int t) {
-        float *dst = s_prod + (size_t)(t & 1) * C * stride;
-        const int q = MIX_TI / 4;
-        for (int idx = tid; idx < C * q; idx += 256) {
-            const int c = idx / q, i4 = idx - c * q, gi = t * MIX_TI + 4 * i4;
-            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), fv;
-            if (gi < nx) xv = *reinterpret_cast<const float4 *>(x + gi);
-            fv = xv;
-            if (c < nmix && gi < nx) fv = __ldg(reinterpret_cast<const float4 *>(fn + (size_t)c * nx + gi));
-            float4 p = make_float4(__fmul_rn(fv.x, xv.x), __fmul_rn(fv.y, xv.y), __fmul_rn(fv.z, xv.z),
-                                   __fmul_rn(fv.w, xv.w));
-            *reinterpret_cast<float4 *>(dst + (size_t)c * stride + 4 * i4) = p;
+        float *dst = s_prod + (size_t)(t & 1) * (TOK * MIX_CPG) * stride;
+        if (one_word) {
+            const float4 fcur = f_next;
+            fetch_fn(t + 1);                              // lands while tile t is multiplied and t - 1 consumed
+            if (!p_on) return;
+            const int gi = t * MIX_TI + 4 * pi4;
+            float4 xv[TOK];
+#pragma unroll
+            for (int tk = 0; tk < TOK; tk++) {
+                xv[tk] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (tk < ntok && gi < nx) xv[tk] = *reinterpret_cast<const float4 *>(x4 + (size_t)(row0 + tk) * nx + gi);
+            }
+#pragma unroll
+            for (int tk = 0; tk < TOK; tk++) {
+                const float4 f = p_sq ? xv[tk] : fcur;
+                *reinterpret_cast<float4 *>(dst + (size_t)(tk * MIX_CPG + pc) * stride + 4 * pi4) =
+                    make_float4(__fmul_rn(f.x, xv[tk].x), __fmul_rn(f.y, xv[tk].y), __fmul_rn(f.z, xv[tk].z),
+                                __fmul_rn(f.w, xv[tk].w));
+            }
+            return;
+        }
+        // eight 16-byte loads of fn (and the matching x words) in flight per thread
+        const float *x = x4 + (size_t)row0 * nx;
+        for (int base = tid; base < total; base += 256 * 8) {
+            float4 fv[8], xv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int idx = base + u * 256;
+                const int c = idx / q, i4 = idx - c * q, gi = t * MIX_TI + 4 * i4;
+                const bool ok = idx < total && gi < nx;
+                xv[u] = ok ? *reinterpret_cast<const float4 *>(x + gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+                fv[u] = (ok && c_lo + c < nmix) ? __ldg(reinterpret_cast<const float4 *>(fn + (size_t)(c_lo + c) * nx + gi))
+                                                : xv[u];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int idx = base + u * 256;
+                if (idx >= total) continue;
+                const int c = idx / q, i4 = idx - c * q;
+                *reinterpret_cast<float4 *>(dst + (size_t)c * stride + 4 * i4) =
+                    make_float4(__fmul_rn(fv[u].x, xv[u].x), __fmul_rn(fv[u].y, xv[u].y),
+                                __fmul_rn(fv[u].z, xv[u].z), __fmul_rn(fv[u].w, xv[u].w));
+            }
         }
     };
-    auto chain = [&](const float *src, float acc) {
-        const float4 *p = reinterpret_cast<const float4 *>(src);
-#pragma unroll 8
-        for (int i4 = 0; i4 < MIX_TI / 4; i4++) {
-            float4 v = p[i4];
-            acc = __fadd_rn(acc, v.x); acc = __fadd_rn(acc, v.y);
-            acc = __fadd_rn(acc, v.z); acc = __fadd_rn(acc, v.w);
-        }
-        return acc;
-    };
+    if (one_word) fetch_fn(0);
     if (!consumer) produce(0);
     __syncthreads();
     for (int t = 0; t < nt; t++) {
         if (!consumer) {
             if (t + 1 < nt) produce(t + 1);
-        } else {
-            const float *src = s_prod + (size_t)(t & 1) * C * stride;
-            if (c0 < C) acc0 = chain(src + (size_t)c0 * stride, acc0);
-            if (c0 + 64 < C) acc1 = chain(src + (size_t)(c0 + 64) * stride, acc1);
+        } else if (live) {
+            acc = seq_sum_smem(s_prod + (size_t)(t & 1) * (TOK * MIX_CPG) * stride + (size_t)cl * stride, MIX_TI, acc);
         }
         __syncthreads();
     }
-    if (consumer) {
-        if (c0 < C) raw[(size_t)row * C + c0] = acc0;
-        if (c0 + 64 < C) raw[(size_t)row * C + c0 + 64] = acc1;
-    }
+    if (live) raw[(size_t)(row0 + my_tok) * C + c_lo + my_c] = acc;
 }
 
 __device__ __forceinline__ float sigm(float x) { return __fdiv_rn(1.0f, 1.0f + exp_rn(-x)); }
 
 // Sinkhorn on an n x n matrix held by one thread (reference c/mhc.h:181-218).
-__device__ void sinkhorn(float *c, int n, int iters, float eps) {
+// N > 0 fixes the size at compile time so that the matrix stays in registers
+// and the loops unroll (N = 4 is the model's hc_mult); N = 0 is the generic
+// form on a local array.
+template <int N>
+__device__ __forceinline__ void sinkhorn(float *c, int n_rt, int iters, float eps) {
+    const int n = N ? N : n_rt;
+#pragma unroll
     for (int j = 0; j < n; j++) {
         float *r = c + j * n, mx = r[0], sum = 0.f;
+#pragma unroll
         for (int k = 1; k < n; k++) mx = fmaxf(mx, r[k]);
+#pragma unroll
         for (int k = 0; k < n; k++) { r[k] = exp_rn(r[k] - mx); sum = __fadd_rn(sum, r[k]); }
+#pragma unroll
         for (int k = 0; k < n; k++) r[k] = __fadd_rn(__fdiv_rn(r[k], sum), eps);
     }
     for (int it = 0; it < iters; it++) {
-        if (it) for (int j = 0; j < n; j++) {
-            float sum = 0.f;
-            for (int k = 0; k < n; k++) sum = __fadd_rn(sum, c[j * n + k]);
-            float den = __fadd_rn(sum, eps);
-            for (int k = 0; k < n; k++) c[j * n + k] = __fdiv_rn(c[j * n + k], den);
+        if (it) {
+#pragma unroll
+            for (int j = 0; j < n; j++) {
+                float sum = 0.f;
+#pragma unroll
+                for (int k = 0; k < n; k++) sum = __fadd_rn(sum, c[j * n + k]);
+                float den = __fadd_rn(sum, eps);
+#pragma unroll
+                for (int k = 0; k < n; k++) c[j * n + k] = __fdiv_rn(c[j * n + k], den);
+            }
         }
+#pragma unroll
         for (int k = 0; k < n; k++) {
             float sum = 0.f;
+#pragma unroll
             for (int j = 0; j < n; j++) sum = __fadd_rn(sum, c[j * n + k]);
             float den = __fadd_rn(sum, eps);
+#pragma unroll
             for (int j = 0; j < n; j++) c[j * n + k] = __fdiv_rn(c[j * n + k], den);
         }
     }
@@ -156,61 +216,89 @@ mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ ra
                       float *__restrict__ pre_out, float *__restrict__ post_out,
                       float *__restrict__ comb_out, float *__restrict__ y,
                       float *__restrict__ y_normed, int seq) {
-    extern __shared__ float s_sq[];           // seq: d squares of the collapsed row
+    extern __shared__ __align__(16) float s_sq[];   // seq: d squares of the collapsed row
     __shared__ float s_pre[MHC_MAX_N];
     __shared__ float red[32];
     const int row = blockIdx.x;
     const float *rw = raw + (size_t)row * (nmix + 1);
+    const float mean = __fdiv_rn(rw[nmix], (float)(n * d));
+    const float r = __fdiv_rn(1.0f, sqrtf(__fadd_rn(mean, norm_eps)));
+    // the gates that the collapse needs first (thread 0); post / comb / Sinkhorn,
+    // which nothing in this kernel waits for, run on another warp's lane while
+    // thread 0 walks the sum of squares
     if (threadIdx.x == 0) {
-        float mean = __fdiv_rn(rw[nmix], (float)(n * d));
-        float r = __fdiv_rn(1.0f, sqrtf(__fadd_rn(mean, norm_eps)));
-        if (head_mode) {
-            for (int j = 0; j < n; j++) {
-                float m = __fmul_rn(rw[j], r);
-                s_pre[j] = __fadd_rn(sigm(__fadd_rn(__fmul_rn(m, head_scale), base[j])), hc_eps);
+        for (int j = 0; j < n; j++) {
+            float m = __fmul_rn(rw[j], r);
+            float sc = head_mode ? head_scale : scale[0];
+            s_pre[j] = __fadd_rn(sigm(__fadd_rn(__fmul_rn(m, sc), base[j])), hc_eps);
+            if (pre_out) pre_out[(size_t)row * n + j] = s_pre[j];
+        }
+    }
+    __syncthreads();
+    const float *x = x4 + (size_t)row * n * d;
+    float ss = 0.f;
+    if (y) {
+        // collapse: y[i] = sum_j pre[j] * X[j,i], j ascending, mul then add; BF16 round
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float acc = 0.f;
+            for (int j = 0; j < n; j++) acc = __fadd_rn(acc, __fmul_rn(s_pre[j], x[(size_t)j * d + i]));
+            acc = bf16_round(acc);
+            y[(size_t)row * d + i] = acc;
+            if (seq) s_sq[i] = __fmul_rn(acc, acc);
+            else ss = fmaf(acc, acc, ss);
+        }
+    }
+    __syncthreads();
+    if ((threadIdx.x >> 5) == 1 && !head_mode && n * n <= 32) {
+        // warp 1: lane l < n holds post[l]; lane l < n*n holds comb[l / n][l % n].  Every
+        // lane gathers the n values of its row (column) with shuffles and adds them in
+        // index order, so each sum is the reference's, computed n*n times in parallel.
+        const int l = threadIdx.x & 31;
+        if (l < n) {
+            float m2 = __fmul_rn(rw[n + l], r);
+            float po = __fmul_rn(2.0f, sigm(__fadd_rn(__fmul_rn(m2, scale[1]), base[n + l])));
+            if (post_out) post_out[(size_t)row * n + l] = po;
+        }
+        const bool on = l < n * n;
+        const int j = on ? l / n : 0, k = on ? l - j * n : 0;
+        float c = on ? __fadd_rn(__fmul_rn(__fmul_rn(rw[2 * n + l], r), scale[2]), base[2 * n + l]) : 0.f;
+        // row softmax with eps added per element (reference c/mhc.h:181-190)
+        float mx = __shfl_sync(0xffffffffu, c, j * n);
+        for (int q = 1; q < n; q++) mx = fmaxf(mx, __shfl_sync(0xffffffffu, c, j * n + q));
+        c = exp_rn(c - mx);
+        float sum = 0.f;
+        for (int q = 0; q < n; q++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, c, j * n + q));
+        c = __fadd_rn(__fdiv_rn(c, sum), hc_eps);
+        for (int it = 0; it < iters; it++) {
+            if (it) {
+                float s2 = 0.f;
+                for (int q = 0; q < n; q++) s2 = __fadd_rn(s2, __shfl_sync(0xffffffffu, c, j * n + q));
+                c = __fdiv_rn(c, __fadd_rn(s2, hc_eps));
             }
-        } else {
+            float s3 = 0.f;
+            for (int q = 0; q < n; q++) s3 = __fadd_rn(s3, __shfl_sync(0xffffffffu, c, q * n + k));
+            c = __fdiv_rn(c, __fadd_rn(s3, hc_eps));
+        }
+        if (on && comb_out) comb_out[(size_t)row * n * n + l] = c;
+    } else if (threadIdx.x == 32 && !head_mode) {
+        for (int j = 0; j < n; j++) {
+            float m2 = __fmul_rn(rw[n + j], r);
+            float po = __fmul_rn(2.0f, sigm(__fadd_rn(__fmul_rn(m2, scale[1]), base[n + j])));
+            if (post_out) post_out[(size_t)row * n + j] = po;
+        }
+        {
             float comb[MHC_MAX_N * MHC_MAX_N];
-            for (int j = 0; j < n; j++) {
-                float m = __fmul_rn(rw[j], r);
-                s_pre[j] = __fadd_rn(sigm(__fadd_rn(__fmul_rn(m, scale[0]), base[j])), hc_eps);
-                float m2 = __fmul_rn(rw[n + j], r);
-                float po = __fmul_rn(2.0f, sigm(__fadd_rn(__fmul_rn(m2, scale[1]), base[n + j])));
-                if (post_out) post_out[(size_t)row * n + j] = po;
-            }
-            for (int i = 0; i < n * n; i++) {
-                float m = __fmul_rn(rw[2 * n + i], r);
-                comb[i] = __fadd_rn(__fmul_rn(m, scale[2]), base[2 * n + i]);
-            }
-            sinkhorn(comb, n, iters, hc_eps);
+            for (int i = 0; i < n * n; i++)
+                comb[i] = __fadd_rn(__fmul_rn(__fmul_rn(rw[2 * n + i], r), scale[2]), base[2 * n + i]);
+            sinkhorn<0>(comb, n, iters, hc_eps);
             if (comb_out)
                 for (int i = 0; i < n * n; i++) comb_out[(size_t)row * n * n + i] = comb[i];
         }
-        if (pre_out) for (int j = 0; j < n; j++) pre_out[(size_t)row * n + j] = s_pre[j];
     }
-    __syncthreads();
-    if (!y) return;
-    // collapse: y[i] = sum_j pre[j] * X[j,i], j ascending, mul then add; BF16 round
-    const float *x = x4 + (size_t)row * n * d;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < n; j++) acc = __fadd_rn(acc, __fmul_rn(s_pre[j], x[(size_t)j * d + i]));
-        acc = bf16_round(acc);
-        y[(size_t)row * d + i] = acc;
-        if (seq) s_sq[i] = __fmul_rn(acc, acc);
-        else ss = fmaf(acc, acc, ss);
-    }
-    if (!y_normed) return;
+    if (!y || !y_normed) return;
     float tot;
     if (seq) {                                // reference order: one accumulator, index ascending
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float a = 0.f;
-#pragma unroll 8
-            for (int i = 0; i < d; i++) a = __fadd_rn(a, s_sq[i]);
-            red[0] = a;
-        }
+        if (threadIdx.x == 0) red[0] = seq_sum_smem(s_sq, d, 0.f);
         __syncthreads();
         tot = red[0];
     } else {
@@ -262,15 +350,24 @@ static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float 
         APUS_LAUNCHED();
         return 0;
     }
-    const int C = nmix + 1, ti = C <= 48 ? 512 : 128;
-    const size_t smem = (size_t)2 * C * (ti + 4) * sizeof(float);
+    const int C = nmix + 1;
     static bool attr_set = false;
     if (!attr_set) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
         APUS_CUDA_OK(cudaFuncSetAttribute(mhc_pre_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
         attr_set = true;
     }
-    mhc_mix_seq_kernel<<<rows, 320, smem, st>>>(x4, fn, nx, nmix, ti, raw);
+    const unsigned gy = (unsigned)((C + MIX_CPG - 1) / MIX_CPG);
+    if (rows >= 4) {                          // eight tokens share a CTA and its read of fn
+        const int ti = 256;
+        const size_t smem = (size_t)2 * 8 * MIX_CPG * (ti + 4) * sizeof(float);
+        mhc_mix_seq_kernel<8><<<dim3((unsigned)((rows + 7) / 8), gy), 288, smem, st>>>(x4, fn, nx, nmix, ti, rows, raw);
+    } else {
+        const int ti = 1024;
+        const size_t smem = (size_t)2 * MIX_CPG * (ti + 4) * sizeof(float);
+        mhc_mix_seq_kernel<1><<<dim3((unsigned)rows, gy), 288, smem, st>>>(x4, fn, nx, nmix, ti, rows, raw);
+    }
     APUS_LAUNCHED();
     return 0;
 }

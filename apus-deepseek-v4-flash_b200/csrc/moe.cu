@@ -166,6 +166,7 @@ moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ ro
             if (lane == 31) {
                 n_groups[0] = jg < max_groups ? jg : max_groups;
                 n_groups[1] = jc;                  // routings that are local
+                n_groups[2] += n_groups[0];        // running total of work items (read by the timing interface)
             }
         }
         __syncthreads();

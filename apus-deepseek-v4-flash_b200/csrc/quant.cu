@@ -49,19 +49,14 @@ int act_quant(const float *x, const int *arow, int M, int K, uint8_t *codes,
 // it is a tree reduction.
 __global__ void rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ w,
                                 float eps, float *__restrict__ y, int64_t n, int seq) {
-    extern __shared__ float s_sq[];
+    extern __shared__ __align__(16) float s_sq[];
     const float *xr = x + (size_t)blockIdx.x * n;
     float *yr = y + (size_t)blockIdx.x * n;
     __shared__ float red[32];
     if (seq) {
         for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s_sq[i] = __fmul_rn(xr[i], xr[i]);
         __syncthreads();
-        if (threadIdx.x == 0) {
-            float a = 0.f;
-#pragma unroll 8
-            for (int64_t i = 0; i < n; i++) a = __fadd_rn(a, s_sq[i]);
-            red[0] = a;
-        }
+        if (threadIdx.x == 0) red[0] = seq_sum_smem(s_sq, (int)n, 0.f);
     } else {
         float ss = 0.f;
         for (int64_t i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];

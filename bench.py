@@ -51,7 +51,17 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--batches", type=int, default=8, help="distinct activation batches cycled")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    return ap.parse_args()
+    ap.add_argument("--workload", default=None, choices=["model", "moe_layer"],
+                    help="model: full 43-layer token loop (default on 1 GPU); moe_layer: one MoE sublayer")
+    ap.add_argument("--batch", type=int, default=32, help="model workload: sequences decoded in lockstep")
+    ap.add_argument("--prompt", type=int, default=512, help="model workload: prompt tokens per sequence")
+    ap.add_argument("--layers", type=int, default=43, help="model workload: layers (43 = the real model)")
+    a = ap.parse_args()
+    if a.workload is None:
+        a.workload = "model" if a.gpus == 1 else "moe_layer"
+    if a.workload == "model" and a.steps == 400 and a.warmup == 20:
+        a.steps, a.warmup = 64, 4          # defaults of the token-loop workload
+    return a
 
 
 def workload_config(a, n):
@@ -161,9 +171,247 @@ def reference_arm(a):
     print(json.dumps(line), flush=True)
 
 
-# ---- this repository's arm ---------------------------------------------------------------------
+# ---- full-model token loop (config 4 of the baseline; the headline metric) ------------------
+MODEL_METRIC = "decode_tokens_per_s"
+
+
+def model_config(a, n, cfg):
+    kinds = cfg.layer_kinds()
+    return {"workload": f"config4: full DeepSeek-V4-Flash token loop, random-init weights generated on the device, "
+                        f"{a.prompt}-token prompt then greedy decode at batch {a.batch}",
+            "layers": cfg.n_layers, "layer_kinds": {"swa": kinds.count(0), "csa": kinds.count(4), "hca": kinds.count(128)},
+            "hidden": cfg.dim, "n_routed_experts": cfg.n_experts, "topk": cfg.topk, "vocab": cfg.vocab,
+            "batch": a.batch, "prompt_tokens": a.prompt, "parallelism": f"ep{n}" if n > 1 else "single",
+            "sum_order": "reference",
+            "l2": "each step streams the touched experts and all dense weights (>20 GB at batch 32), far above the 126 MB L2"}
+
+
+def flash_config(a):
+    from apus_b200.flash import FlashConfig
+    cfg = FlashConfig()
+    if a.layers != cfg.n_layers:
+        cfg.n_layers = a.layers
+    if a.experts != cfg.n_experts:
+        cfg.n_experts = a.experts
+    return cfg
+
+
+def cpu_model_baseline(cfg, seed, budget_s):
+    """The reference's decode step composed from its own apus_block_forward timed
+    on one layer of each kind at full size (E experts, one token at position 8
+    after an 8-token prefill) plus the head: t = sum_kinds n_kind * t_kind + t_head."""
+    import cases
+    from _oracle import P, ref
+    from apus_b200 import capi, synth
+    from apus_b200.flash import rope_tables
+    L = ref()
+    if L is None:
+        return None
+    rng = np.random.default_rng(seed)
+    dims = dict(dim=cfg.dim, n_heads=cfg.n_heads, head_dim=cfg.head_dim, rope_dim=cfg.rope_dim, q_lora=cfg.q_lora,
+                o_groups=cfg.o_groups, o_lora=cfg.o_lora, window=cfg.window, idx_heads=cfg.idx_heads,
+                idx_dim=cfg.idx_dim, idx_topk=cfg.idx_topk, max_pos=256)
+    mdims = dict(E=cfg.n_experts, topk=cfg.topk, inter=cfg.inter)
+    L.ref_block_forward.restype = None
+    L.ref_block_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p,
+                                    C.c_void_p, C.c_int, C.c_int64]
+    kinds = cfg.layer_kinds()
+    t_kind, moe = {}, None
+    for ratio, kind in ((0, "swa"), (4, "csa"), (128, "hca128")):
+        if ratio not in kinds:
+            continue
+        cos, sin = rope_tables(cfg, ratio != 0, 256)
+        B = cases.BlockLayer(seed + ratio, kind, cos, sin, dims=mdims, attn_dims=dims)
+        if moe is None:
+            moe = B.moe                                  # 3.4 GB of experts: generated once, shared by the kinds
+        else:
+            B.moe = moe
+            B.desc.mw = moe.moew()
+        S = cases.AttnState(B.attn)
+        h = cases.block_inputs(seed + 3, 9, cfg.hc_mult, cfg.dim)
+        ids = np.zeros(9, np.int64)
+        L.ref_block_forward(C.byref(B.desc), cfg.hc_mult, cfg.hc_iters, cfg.hc_eps, cfg.norm_eps, C.byref(S.st),
+                            P(h[:8]), P(ids[:8]), 8, 0)
+        n, t0 = 0, time.perf_counter()
+        while n < 3 or (time.perf_counter() - t0 < budget_s / 3 and n < 40):
+            hh = h[8:9].copy()
+            L.ref_block_forward(C.byref(B.desc), cfg.hc_mult, cfg.hc_iters, cfg.hc_eps, cfg.norm_eps, C.byref(S.st),
+                                P(hh), P(ids[8:9]), 1, 8 + n)
+            n += 1
+        t_kind[ratio] = (time.perf_counter() - t0) / n
+    # head: BF16 [vocab, dim] GEMV
+    head = synth.bf16_bits((rng.standard_normal((cfg.vocab, cfg.dim)) * 0.02).astype(np.float32))
+    x = synth.activations(rng, 1, cfg.dim)
+    out = np.empty(cfg.vocab, np.float32)
+    L.ref_head_gemv.restype = None
+    L.ref_head_gemv.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]
+    L.ref_head_gemv(P(head), P(x), P(out), cfg.vocab, cfg.dim)
+    t0 = time.perf_counter()
+    n = 0
+    while n < 3:
+        L.ref_head_gemv(P(head), P(x), P(out), cfg.vocab, cfg.dim)     # c/model.h:638-647
+        n += 1
+    t_head = (time.perf_counter() - t0) / n
+    t_step = sum(t_kind[r] for r in kinds) + t_head
+    return {"value": 1.0 / t_step, "unit": "tok/s", "cores": L.ref_pool_threads(), "kind": "reference",
+            "sample": "one decode token (position 8+) through the unmodified apus_block_forward at full sizes, "
+                      "one layer of each kind with 256 experts ("
+                      + ", ".join(f"{k}: {v * 1e3:.0f} ms" for k, v in t_kind.items())
+                      + f"), head GEMV {t_head * 1e3:.0f} ms; step = sum over the {cfg.n_layers} layers + head; "
+                        "the reference decodes sequences one at a time, so its tok/s does not grow with the batch"}
+
+
+def model_reference_arm(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 32)))
+    cfg = flash_config(a)
+    cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0)
+    if cb is None:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference build (oracle/_ref) is not present"}))
+        return
+    line = {"impl": "reference", "metric": MODEL_METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": a.gpus,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": model_config(a, a.gpus, cfg), "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def model_main(a):
+    import torch
+    import apus_b200
+    from apus_b200 import capi
+    from apus_b200.flash import RandomFlashModel
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == 1 and a.gpus == 1, "the full-model workload runs on one GPU (use --workload moe_layer for N > 1)"
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    apus_b200.build()
+    L = apus_b200.lib()
+    err = C.create_string_buffer(512)
+    if L.apus_cuda_enable(err, 512):
+        raise RuntimeError(err.value.decode())
+    cfg = flash_config(a)
+    B, K, Wm = a.batch, a.steps, a.warmup
+    max_pos = a.prompt + 2 * (K + Wm) + 72
+    t0 = time.time()
+    W = RandomFlashModel(cfg, a.seed, dev, max_pos=max_pos)
+    torch.cuda.synchronize()
+    t_gen = time.time() - t0
+    torch.cuda.empty_cache()
+
+    def create(batch):
+        h = L.apus_cuda_model_create(C.byref(W.desc), batch, max_pos)
+        if not h:
+            apus_b200.check(1, "apus_cuda_model_create")
+        return h
+    rng = np.random.default_rng([a.seed, 4242])
+    uuid = str(torch.cuda.get_device_properties(dev).uuid)
+    sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+
+    def run(batch, timed_moe):
+        """Prompt, warm-up decode steps, K timed decode steps with the sampled
+        token fed back on the device; returns (ms of the K steps, prefill ms, launches, tokens)."""
+        h = create(batch)
+        prompt = rng.integers(0, cfg.vocab, size=(batch, a.prompt)).astype(np.int64)
+        toks = np.empty((batch, Wm + 1), np.int32)
+        ms_pre, ms_dec = C.c_float(0), C.c_float(0)
+        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(prompt), a.prompt, Wm + 1, capi.ptr(toks),
+                                                   C.byref(ms_pre), C.byref(ms_dec)), "generate (prompt + warm-up)")
+        prefill_ms = ms_pre.value
+        moes = [L.apus_cuda_model_moe(h, i) for i in range(cfg.n_layers)]
+        if timed_moe:
+            for m in moes:
+                L.apus_cuda_moe_timing(m, 1)
+                L.apus_cuda_moe_work_items(m, 1)
+        last = np.ascontiguousarray(toks[:, -1:].astype(np.int64))
+        out = np.empty((batch, K + 1), np.int32)
+        d0 = L.apus_cuda_dispatches()
+        torch.cuda.synchronize()
+        w0 = time.time()
+        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(last), 1, K + 1, capi.ptr(out), C.byref(ms_pre),
+                                                   C.byref(ms_dec)), "generate (timed)")
+        torch.cuda.synchronize()
+        w1 = time.time()
+        launches = int(L.apus_cuda_dispatches() - d0)
+        stats = None
+        if timed_moe:
+            g13 = g2 = 0.0
+            nl = items = 0
+            for m in moes:
+                x, y, n = C.c_double(), C.c_double(), C.c_int()
+                apus_b200.check(L.apus_cuda_moe_timing_read(m, C.byref(x), C.byref(y), C.byref(n)), "timing")
+                L.apus_cuda_moe_timing(m, 0)
+                g13 += x.value; g2 += y.value; nl += n.value
+                items += L.apus_cuda_moe_work_items(m, 0)
+            stats = (g13, g2, nl, items)
+        return h, ms_dec.value, prefill_ms, launches, out, (w0, w1), stats
+
+    h32, ms, prefill_ms, launches, out, wall, stats = run(B, True)
+    clocks = sampler.stop(*wall)
+    value = B * K / (ms * 1e-3)
+
+    # ---- end to end: ids from the host every step, sampled ids back to the host -----------------
+    ids = np.ascontiguousarray(out[:, -1:].astype(np.int64))
+    nxt = np.empty(B, np.int32)
+    ne = max(8, K // 4)
+    for _ in range(3):
+        apus_b200.check(L.apus_cuda_model_forward(h32, capi.ptr(ids), 1, None, capi.ptr(nxt)), "model_forward")
+        ids[:, 0] = nxt
+    t0 = time.perf_counter()
+    for _ in range(ne):
+        apus_b200.check(L.apus_cuda_model_forward(h32, capi.ptr(ids), 1, None, capi.ptr(nxt)), "model_forward")
+        ids[:, 0] = nxt
+    e2e_val = B * ne / (time.perf_counter() - t0)
+    L.apus_cuda_model_destroy(h32)
+
+    # ---- batch 1 ------------------------------------------------------------------------------
+    h1, ms1, prefill1, launches1, out1, _, _ = run(1, False)
+    L.apus_cuda_model_destroy(h1)
+
+    peak, peak_kind = peak_hbm()
+    g13, g2, nl, items = stats
+    achieved = items * W13_BYTES / (g13 * 1e-3) / 1e9 if g13 > 0 else None
+    achieved2 = items * W2_BYTES / (g2 * 1e-3) / 1e9 if g2 > 0 else None
+    line = {
+        "metric": MODEL_METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 accumulate over E2M1xE4M3 / E4M3xE4M3 tensor-core products; BF16-valued activations",
+        "data": "synthetic", "config": model_config(a, 1, cfg), "clocks": clocks,
+        "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 4,
+                "steps": ne},
+        "gpu_launches": launches,
+        "batch1": {"value": 1 * K / (ms1 * 1e-3), "unit": "tok/s", "ms_per_step": ms1 / K,
+                   "gpu_launches": launches1, "prefill_ms": prefill1},
+        "prefill": {"tokens": B * a.prompt, "ms": prefill_ms, "tok_s": B * a.prompt / (prefill_ms * 1e-3),
+                    "note": "prompt consumed as consecutive decode steps (no batched prefill kernel yet)"},
+        "weights": {"bytes": W.bytes, "generate_s": t_gen},
+        "roofline": {"kernel": "gemm_tc_kernel<pair> (tcgen05 block-scaled MXFP4 expert gate/up GEMV + SwiGLU), "
+                               "all layers of the timed steps",
+                     "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind, "traffic": None,
+                     "launches": nl, "avg_launch_us": g13 / max(nl, 1) * 1e3,
+                     "avg_unique_experts": items / max(nl, 1),
+                     "share_of_step": g13 / ms if ms > 0 else None,
+                     "down_proj_kernel": {"achieved": achieved2, "frac": (achieved2 / peak) if achieved2 else None,
+                                          "avg_launch_us": g2 / max(nl, 1) * 1e3, "share_of_step": g2 / ms}},
+    }
+    if not a.no_cpu_baseline:
+        os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 32)))
+        cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0)
+        if cb:
+            line["cpu_baseline"] = cb
+    print(json.dumps(line), flush=True)
+
+
+# ---- this repository's arm (one MoE sublayer) --------------------------------------------------
 def main():
     a = parse()
+    if a.workload == "model":
+        return model_reference_arm(a) if a.impl == "reference" else model_main(a)
     if a.impl == "reference":
         return reference_arm(a)
     import torch

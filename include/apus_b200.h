@@ -347,6 +347,10 @@ int apus_cuda_moe_use_tc(ApusCudaMoe *m, int enable);
 void apus_cuda_moe_timing(ApusCudaMoe *m, int enable);
 int apus_cuda_moe_timing_read(ApusCudaMoe *m, double *ms_gate_up,
                               double *ms_down, int *launches);
+/* Work items (one expert x up to 32 rows each) the expert kernels were launched
+ * for since the last reset; at decode sizes that is the number of distinct
+ * experts whose weights were streamed.  Synchronises the library stream. */
+long long apus_cuda_moe_work_items(ApusCudaMoe *m, int reset);
 /* Hash-routed layers (c/moe.h:42, 391-394): place the tid2eid table
  * [vocab, topk] in HBM so that apus_cuda_moe_route_dev / _forward_dev can look
  * token ids up on device.  (The host-pointer apus_cuda_moe_forward does not
@@ -463,6 +467,9 @@ void apus_cuda_model_destroy(ApusCudaModel *m);
 /* c/model.h:485: back to position 0 with empty caches. */
 int apus_cuda_model_reset(ApusCudaModel *m);
 int64_t apus_cuda_model_pos(const ApusCudaModel *m);
+/* The MoE sublayer object of one layer (owned by the model), e.g. for
+ * apus_cuda_moe_timing / apus_cuda_moe_use_tc. */
+ApusCudaMoe *apus_cuda_model_moe(ApusCudaModel *m, int layer);
 /* c/model.h:722 apus_model_forward for every sequence: ids [batch, s] host,
  * consumes s positions; logits [batch, vocab] of the last position and/or the
  * greedy next token [batch] (c/sample.h:76-81, lowest index on ties) are

@@ -160,3 +160,12 @@ void ref_model_forward(const ApusCudaModelDesc *d, ApusAttnS *states, int64_t *p
     for (int i = 0; i < d->n_layers; i++) states[i] = lst[i].attn;
     free(Ls); free(tabs); free(lst);
 }
+
+/* c/model.h:638-647 (static apus_head_gemv) on a BF16 [O, K] matrix. */
+void ref_head_gemv(const void *w_bf16, const float *x, float *out, int64_t O, int64_t K) {
+    ApusStTensor t;
+    memset(&t, 0, sizeof t);
+    t.dtype = APUS_ST_BF16;
+    t.data = w_bf16;
+    apus_head_gemv(&t, x, out, O, K);
+}

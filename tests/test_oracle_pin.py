@@ -305,3 +305,18 @@ def test_live_reference_row_helpers_bitwise():
             ora().ora_apply_rope(P(a[r, 64:]), P(cos), P(sin), 64, inv)
             L.apus_apply_rope(P(b[r, 64:]), P(cos), P(sin), 64, inv)
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_rope_tables_match_the_reference():
+    """apus_b200.flash.rope_tables restates c/attn.h:247-281; the committed tables
+    were written by the reference's apus_rope_precompute (plain theta 1e4 and the
+    YaRN-scaled compressed-layer table).  powf/cosf/sinf come from different
+    math libraries (a frequency one ulp off moves the f32 angle at position 200
+    by a few 1e-6), hence an absolute bar of 2e-5 instead of bit equality."""
+    from apus_b200.flash import FlashConfig, rope_tables
+    G = np.load(Path(__file__).resolve().parent / "golden" / "ref_cases.npz")
+    cfg = FlashConfig()
+    for name, compressed in (("plain", False), ("yarn", True)):
+        cos, sin = rope_tables(cfg, compressed, 256)
+        assert np.abs(cos - G[f"rope.{name}.cos"]).max() <= 2e-5
+        assert np.abs(sin - G[f"rope.{name}.sin"]).max() <= 2e-5
