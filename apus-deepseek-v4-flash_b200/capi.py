@@ -187,6 +187,16 @@ def load(path=LIB_PATH):
         "apus_cuda_set_sum_order": (ci, [ci]),
         "apus_cuda_block_forward": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64]),
         "apus_cuda_model_create": (vp, [C.POINTER(ModelDesc), ci, ci]),
+        "apus_cuda_model_create_ep": (vp, [C.POINTER(ModelDesc), ci, ci, ci, ci]),
+        "apus_cuda_use_stream": (ci, [vp, ci]),
+        "apus_cuda_model_set_ids": (ci, [vp, vp]),
+        "apus_cuda_model_begin_step": (ci, [vp]),
+        "apus_cuda_model_attn_half": (ci, [vp, ci]),
+        "apus_cuda_model_ffn_input": (vp, [vp, ci]),
+        "apus_cuda_model_ffn_output": (ci, [vp, ci, vp]),
+        "apus_cuda_model_end_step": (ci, [vp, ci, ci]),
+        "apus_cuda_model_ids": (vp, [vp]),
+        "apus_cuda_model_read": (ci, [vp, vp, vp]),
         "apus_cuda_model_destroy": (None, [vp]),
         "apus_cuda_model_reset": (ci, [vp]),
         "apus_cuda_model_pos": (i64, [vp]),

@@ -95,7 +95,8 @@ int ensure_enabled() {
                   prop.major, prop.minor);
         return 1;
     }
-    APUS_CUDA_OK(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    APUS_CUDA_OK(cudaStreamCreateWithFlags(&c.own_stream, cudaStreamNonBlocking));
+    c.stream = c.own_stream;
     c.enabled = true;
     return 0;
 }
@@ -291,6 +292,14 @@ int apus_cuda_enable(char *err, size_t errcap) {
 
 void apus_cuda_moe_destroy(ApusCudaMoe *m);
 
+int apus_cuda_use_stream(void *stream, int use_own) {
+    if (ensure_enabled()) return 1;
+    Ctx &c = ctx();
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    c.stream = use_own ? c.own_stream : (cudaStream_t)stream;
+    return 0;
+}
+
 int apus_cuda_set_sum_order(int order) {
     if (order == APUS_CUDA_SUM_REFERENCE || order == APUS_CUDA_SUM_TREE) apus::g_sum_order = order;
     return apus::g_sum_order;
@@ -309,8 +318,8 @@ void apus_cuda_disable(void) {
     c.moes.clear();
     for (auto &b : c.ws) b.release();
     c.stage.release();
-    if (c.stream) cudaStreamDestroy(c.stream);
-    c.stream = nullptr;
+    if (c.own_stream) cudaStreamDestroy(c.own_stream);
+    c.stream = c.own_stream = nullptr;
     c.enabled = false;
 }
 

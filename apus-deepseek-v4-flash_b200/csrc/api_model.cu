@@ -32,39 +32,54 @@ struct BlockBufs {
     float *x, *y, *sub, *post, *comb, *hn;
 };
 
-// One token of B sequences through one block (reference c/layer.h:495-545).
-int block_step(const LayerDev &L, StateDev &S, float **h, float **hn, const int64_t *ids, int B, long long pos,
-               int hc, int iters, float hc_eps, float norm_eps, const BlockBufs &bb, const StepBufs &sb,
-               cudaStream_t st) {
+// One token of B sequences through one block (reference c/layer.h:495-545), in
+// three pieces so that an expert-parallel caller can run the MoE sublayer
+// itself between the second and the third.
+int block_attn_half(const LayerDev &L, StateDev &S, float **h, float **hn, int B, long long pos, int hc,
+                    int iters, float hc_eps, float norm_eps, const BlockBufs &bb, const StepBufs &sb,
+                    cudaStream_t st) {
     const int dim = L.attn.cfg.dim, half2 = L.attn.cfg.rope_dim, ratio = L.attn.cfg.ratio;
     APUS_REQUIRE(pos < L.rope_rows, "position %lld is beyond the rope table (%d rows)", pos, L.rope_rows);
     const float *cs_pos = L.cs + (size_t)pos * half2;
     const long long rp = ratio ? pos + 1 - ratio : -1;
     const float *cs_rp = rp >= 0 ? L.cs + (size_t)rp * half2 : cs_pos;
-    // attention half
     if (mhc_pre(*h, dim, hc, L.hc_attn_fn, L.hc_attn_scale, L.hc_attn_base, norm_eps, hc_eps, iters,
                 L.attn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st))
         return 1;
     if (attn_step(L.attn, S, bb.x, pos, cs_pos, cs_rp, bb.sub, sb, nullptr, st)) return 1;
     if (mhc_post(bb.sub, *h, bb.post, bb.comb, *hn, dim, hc, B, st)) return 1;
     { float *t = *h; *h = *hn; *hn = t; }
-    // ffn half
-    if (mhc_pre(*h, dim, hc, L.hc_ffn_fn, L.hc_ffn_scale, L.hc_ffn_base, norm_eps, hc_eps, iters,
-                L.ffn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st))
-        return 1;
-    if (apus_cuda_moe_forward_dev(L.moe, bb.x, ids, B, bb.sub, st)) return 1;
-    if (mhc_post(bb.sub, *h, bb.post, bb.comb, *hn, dim, hc, B, st)) return 1;
+    return 0;
+}
+// mHC pre + RMSNorm of the ffn half: leaves the sublayer input in bb.x
+int block_ffn_pre(const LayerDev &L, float *h, int B, int hc, int iters, float hc_eps, float norm_eps,
+                  const BlockBufs &bb, cudaStream_t st) {
+    return mhc_pre(h, L.attn.cfg.dim, hc, L.hc_ffn_fn, L.hc_ffn_scale, L.hc_ffn_base, norm_eps, hc_eps, iters,
+                   L.ffn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st);
+}
+int block_ffn_post(const LayerDev &L, const float *sub, float **h, float **hn, int B, int hc, const BlockBufs &bb,
+                   cudaStream_t st) {
+    if (mhc_post(sub, *h, bb.post, bb.comb, *hn, L.attn.cfg.dim, hc, B, st)) return 1;
     { float *t = *h; *h = *hn; *hn = t; }
     return 0;
+}
+int block_step(const LayerDev &L, StateDev &S, float **h, float **hn, const int64_t *ids, int B, long long pos,
+               int hc, int iters, float hc_eps, float norm_eps, const BlockBufs &bb, const StepBufs &sb,
+               cudaStream_t st) {
+    if (block_attn_half(L, S, h, hn, B, pos, hc, iters, hc_eps, norm_eps, bb, sb, st)) return 1;
+    if (block_ffn_pre(L, *h, B, hc, iters, hc_eps, norm_eps, bb, st)) return 1;
+    if (apus_cuda_moe_forward_dev(L.moe, bb.x, ids, B, bb.sub, st)) return 1;
+    return block_ffn_post(L, bb.sub, h, hn, B, hc, bb, st);
 }
 
 // own == NULL: weights of the global cache (host-pointer tier); otherwise they
 // belong to `own` and the MoE object to the caller.
-int layer_weights(const ApusCudaLayerDesc &d, int hc, int vocab, LayerDev *L, WeightOwner *own) {
+int layer_weights(const ApusCudaLayerDesc &d, int hc, int vocab, LayerDev *L, WeightOwner *own, int e_lo = 0,
+                  int e_hi = -1) {
     const int dim = d.acfg.dim;
     const size_t nmix = (size_t)(2 + hc) * hc, nx = (size_t)hc * dim;
     if (attn_weights(&d.acfg, &d.aw, &L->attn, own)) return 1;
-    L->moe = own ? apus_cuda_moe_create(&d.mw, 0, d.mw.E) : apus_cuda_moe_get(&d.mw);
+    L->moe = own ? apus_cuda_moe_create(&d.mw, e_lo, e_hi < 0 ? d.mw.E : e_hi) : apus_cuda_moe_get(&d.mw);
     if (!L->moe) return 1;
     if (d.mw.hash && vocab < (1 << 30) && apus_cuda_moe_set_hash_table(L->moe, d.mw.tid2eid, vocab)) return 1;
     L->attn_norm_w = (const float *)get_dense(own, d.attn_norm_w, (size_t)dim * 4);
@@ -130,7 +145,7 @@ __global__ void next_ids_kernel(const int32_t *tok, int64_t *ids, int32_t *hist,
 }  // namespace
 
 struct ApusCudaModel {
-    int n_layers = 0, dim = 0, hc = 0, iters = 0, vocab = 0, B = 0, max_pos = 0;
+    int n_layers = 0, dim = 0, hc = 0, iters = 0, vocab = 0, B = 0, max_pos = 0, n_experts = 0;
     float hc_eps = 0.f, norm_eps = 0.f, hc_head_scale = 0.f;
     std::vector<LayerDev> layers;
     std::vector<StateDev> states;
@@ -138,26 +153,25 @@ struct ApusCudaModel {
     int embed_bf16 = 0, head_bf16 = 0;
     const float *norm_w = nullptr, *hc_head_fn = nullptr, *hc_head_base = nullptr;
     long long pos = 0;
+    int e_lo = 0, e_hi = 0;                // routed experts resident here (expert parallelism)
+    float *h_cur = nullptr, *h_alt = nullptr;   // hidden state between the pieces of a step
     WeightOwner own;                       // every weight copy made for this model
     std::map<const void *, DevBuf *> rope; // rope rows by host table (layers of a kind share one)
     DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, ws[20];
     StepBufs sb;
 };
 
-static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
-    const int B = m->B, dim = m->dim, hc = m->hc;
-    float *h = m->h0.as<float>(), *hn = m->h1.as<float>();
-    if (embed_rows(m->embed, m->embed_bf16, m->ids.as<int64_t>(), B, hc, dim, h, st)) return 1;
-    BlockBufs bb = {m->x.as<float>(), m->y.as<float>(), m->sub.as<float>(), m->post.as<float>(),
-                    m->comb.as<float>(), nullptr};
-    for (int i = 0; i < m->n_layers; i++)
-        if (block_step(m->layers[i], m->states[i], &h, &hn, m->ids.as<int64_t>(), B, m->pos, hc, m->iters,
-                       m->hc_eps, m->norm_eps, bb, m->sb, st))
-            return 1;
-    m->pos++;
-    if (!want_logits) return 0;
-    // head: hc_head collapse -> BF16 -> RMSNorm -> LM-head GEMV (reference c/model.h:706-718)
-    if (mhc_head(h, dim, hc, m->hc_head_fn, m->hc_head_scale, m->hc_head_base, m->norm_eps, m->hc_eps,
+static BlockBufs model_bufs(ApusCudaModel *m) {
+    return {m->x.as<float>(), m->y.as<float>(), m->sub.as<float>(), m->post.as<float>(), m->comb.as<float>(), nullptr};
+}
+static int model_embed(ApusCudaModel *m, cudaStream_t st) {
+    m->h_cur = m->h0.as<float>(); m->h_alt = m->h1.as<float>();
+    return embed_rows(m->embed, m->embed_bf16, m->ids.as<int64_t>(), m->B, m->hc, m->dim, m->h_cur, st);
+}
+// head: hc_head collapse -> BF16 -> RMSNorm -> LM-head GEMV (reference c/model.h:706-718) -> greedy pick
+static int model_head(ApusCudaModel *m, cudaStream_t st) {
+    const int B = m->B, dim = m->dim;
+    if (mhc_head(m->h_cur, dim, m->hc, m->hc_head_fn, m->hc_head_scale, m->hc_head_base, m->norm_eps, m->hc_eps,
                  m->yh.as<float>(), B, st))
         return 1;
     if (rms_norm(m->yh.as<float>(), m->norm_w, m->norm_eps, m->yn.as<float>(), dim, B, st)) return 1;
@@ -165,6 +179,20 @@ static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
                    m->head_bf16 ? APUS_CUDA_W_BF16 : 0, st))
         return 1;
     return argmax_rows(m->logits.as<float>(), m->vocab, B, m->tok.as<int32_t>(), st);
+}
+static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
+    APUS_REQUIRE(m->e_lo == 0 && m->e_hi == m->n_experts,
+                 "this model holds experts [%d,%d) of %d: drive it layer by layer (apus_cuda_model_attn_half ...)",
+                 m->e_lo, m->e_hi, m->n_experts);
+    if (model_embed(m, st)) return 1;
+    BlockBufs bb = model_bufs(m);
+    for (int i = 0; i < m->n_layers; i++)
+        if (block_step(m->layers[i], m->states[i], &m->h_cur, &m->h_alt, m->ids.as<int64_t>(), m->B, m->pos, m->hc,
+                       m->iters, m->hc_eps, m->norm_eps, bb, m->sb, st))
+            return 1;
+    m->pos++;
+    if (!want_logits) return 0;
+    return model_head(m, st);
 }
 
 extern "C" {
@@ -195,9 +223,17 @@ int apus_cuda_model_reset(ApusCudaModel *m) {
 }
 
 ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch, int max_pos) {
+    return apus_cuda_model_create_ep(d, batch, max_pos, 0, -1);
+}
+
+ApusCudaModel *apus_cuda_model_create_ep(const ApusCudaModelDesc *d, int batch, int max_pos, int e_lo, int e_hi) {
     if (ensure_enabled()) return nullptr;
     if (!d || batch < 1 || batch > 32 || d->n_layers < 1) { set_error("model_create: bad arguments (batch 1..32)"); return nullptr; }
+    const int E = d->layers[0].mw.E;
+    if (e_hi < 0) e_hi = E;
+    if (e_lo < 0 || e_lo > e_hi || e_hi > E) { set_error("model_create: bad expert range [%d,%d) of %d", e_lo, e_hi, E); return nullptr; }
     ApusCudaModel *m = new ApusCudaModel();
+    m->n_experts = E; m->e_lo = e_lo; m->e_hi = e_hi;
     m->n_layers = d->n_layers; m->dim = d->dim; m->hc = d->hc_mult; m->iters = d->hc_sinkhorn_iters;
     m->vocab = d->vocab; m->B = batch; m->max_pos = max_pos;
     m->hc_eps = d->hc_eps; m->norm_eps = d->norm_eps; m->hc_head_scale = d->hc_head_scale;
@@ -207,7 +243,7 @@ ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch, int
     bool ok = true;
     for (int i = 0; i < d->n_layers && ok; i++) {
         const ApusCudaLayerDesc &ld = d->layers[i];
-        ok = layer_weights(ld, d->hc_mult, d->vocab, &m->layers[i], &m->own) == 0;
+        ok = layer_weights(ld, d->hc_mult, d->vocab, &m->layers[i], &m->own, e_lo, e_hi) == 0;
         if (!ok) break;
         const int half = ld.acfg.rope_dim / 2;
         m->layers[i].cs = rope_rows_dev(ld.cos, ld.sin, ld.rope_rows, half, m->rope);
@@ -363,6 +399,54 @@ int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt, int n_prom
     cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
     int stt = gemm_tc_status(1);
     APUS_REQUIRE(stt == 0, "model_generate: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
+// ---- one step in pieces (expert parallelism: the caller runs the MoE sublayer) ----------------
+int apus_cuda_model_set_ids(ApusCudaModel *m, const int64_t *ids) {
+    if (!m) { set_error("NULL model"); return 1; }
+    APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, ids, (size_t)m->B * 8, cudaMemcpyDefault, ctx().stream));
+    return 0;
+}
+int apus_cuda_model_begin_step(ApusCudaModel *m) {
+    if (!m) { set_error("NULL model"); return 1; }
+    APUS_REQUIRE(m->pos < m->max_pos, "model step: position %lld reaches max_pos %d", m->pos, m->max_pos);
+    return model_embed(m, ctx().stream);
+}
+int apus_cuda_model_attn_half(ApusCudaModel *m, int layer) {
+    if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_attn_half: bad layer"); return 1; }
+    return block_attn_half(m->layers[layer], m->states[layer], &m->h_cur, &m->h_alt, m->B, m->pos, m->hc, m->iters,
+                           m->hc_eps, m->norm_eps, model_bufs(m), m->sb, ctx().stream);
+}
+const float *apus_cuda_model_ffn_input(ApusCudaModel *m, int layer) {
+    if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_ffn_input: bad layer"); return nullptr; }
+    if (block_ffn_pre(m->layers[layer], m->h_cur, m->B, m->hc, m->iters, m->hc_eps, m->norm_eps, model_bufs(m),
+                      ctx().stream))
+        return nullptr;
+    return m->x.as<float>();
+}
+int apus_cuda_model_ffn_output(ApusCudaModel *m, int layer, const float *sub) {
+    if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_ffn_output: bad layer"); return 1; }
+    return block_ffn_post(m->layers[layer], sub, &m->h_cur, &m->h_alt, m->B, m->hc, model_bufs(m), ctx().stream);
+}
+int apus_cuda_model_end_step(ApusCudaModel *m, int want_logits, int feed_back) {
+    if (!m) { set_error("NULL model"); return 1; }
+    m->pos++;
+    if (!want_logits) return 0;
+    if (model_head(m, ctx().stream)) return 1;
+    if (feed_back)
+        next_ids_kernel<<<1, 32, 0, ctx().stream>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), nullptr, m->B, 0, 1);
+    return 0;
+}
+const int64_t *apus_cuda_model_ids(ApusCudaModel *m) { return m ? m->ids.as<int64_t>() : nullptr; }
+int apus_cuda_model_read(ApusCudaModel *m, float *logits, int32_t *next) {
+    if (!m) { set_error("NULL model"); return 1; }
+    cudaStream_t st = ctx().stream;
+    if (logits) APUS_CUDA_OK(cudaMemcpyAsync(logits, m->logits.p, (size_t)m->B * m->vocab * 4, cudaMemcpyDeviceToHost, st));
+    if (next) APUS_CUDA_OK(cudaMemcpyAsync(next, m->tok.p, (size_t)m->B * 4, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "model: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
     return 0;
 }
 

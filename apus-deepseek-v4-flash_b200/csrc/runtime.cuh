@@ -54,7 +54,8 @@ namespace apus {
 struct Ctx {
     bool enabled = false;
     int device = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;          // the stream every entry point without a stream argument uses
+    cudaStream_t own_stream = nullptr;      // the one the library created (stream may be the caller's)
     uint64_t bytes_uploaded = 0;
     std::unordered_map<const void *, DevQW *> qcache;      // quantised weights by host codes ptr
     std::unordered_map<const void *, DevBuf *> dcache;     // dense weights by host ptr

@@ -90,13 +90,18 @@ class RandomFlashModel:
         self.e_lo, self.e_hi = e_lo, cfg.n_experts if e_hi is None else e_hi
         self.keep = []
         self.bytes = 0
-        g = torch.Generator(device=device)
-        g.manual_seed(seed)
-        self.g = g
+        # replicated tensors come from one generator stream per layer and every
+        # expert from its own stream keyed by (seed, layer, expert), so that the
+        # ranks of an expert-parallel job hold the same model
+        self.seed = seed
+        self.g = torch.Generator(device=device)
+        self.g.manual_seed(seed)
+        self.ge = torch.Generator(device=device)
         self.torch = torch
         self.rope = {c: rope_tables(cfg, c, max_pos) for c in (False, True)}
         descs = [self._layer(i, r) for i, r in enumerate(cfg.layer_kinds())]
         self._descs = (capi.LayerDesc * cfg.n_layers)(*descs)
+        self.g.manual_seed(self.seed * 1000003 + 999983)
         d = capi.ModelDesc()
         d.n_layers, d.dim, d.hc_mult, d.hc_sinkhorn_iters, d.vocab = (cfg.n_layers, cfg.dim, cfg.hc_mult,
                                                                       cfg.hc_iters, cfg.vocab)
@@ -143,13 +148,23 @@ class RandomFlashModel:
                                dtype=torch.uint8)
         return capi.QW(self._hold(codes), self._hold(scales), O, K)
 
-    def _fp4_slab(self, n, O, K):
-        """n MXFP4 matrices, expert-major: uniform nibbles, scale bytes uniform in [120, 126]."""
-        return self._bytes((n, O, K // 2), 0, 256), self._bytes((n, O, K // 32), 120, 127)
+    def _fp4_slab(self, layer, which, O, K):
+        """The local experts' MXFP4 matrices, expert-major: uniform nibbles, scale
+        bytes uniform in [120, 126]; expert e is drawn from its own stream."""
+        torch = self.torch
+        n = self.e_hi - self.e_lo
+        codes = torch.empty((n, O, K // 2), device=self.device, dtype=torch.uint8)
+        scales = torch.empty((n, O, K // 32), device=self.device, dtype=torch.uint8)
+        for le in range(n):
+            self.ge.manual_seed(((self.seed * 64 + layer) * 1024 + self.e_lo + le) * 4 + which)
+            codes[le].random_(0, 256, generator=self.ge)
+            scales[le].random_(120, 127, generator=self.ge)
+        return self._hold(codes), self._hold(scales)
 
     # ---- one layer ----------------------------------------------------------------------------
     def _layer(self, i, ratio):
         cfg, torch = self.cfg, self.torch
+        self.g.manual_seed(self.seed * 1000003 + i)
         dim, h, hd = cfg.dim, cfg.n_heads, cfg.head_dim
         G, ol, ql = cfg.o_groups, cfg.o_lora, cfg.q_lora
         csa = ratio == 4
@@ -185,9 +200,9 @@ class RandomFlashModel:
             mw.tid2eid = self._hold(t.to(torch.int64).contiguous())
         else:
             mw.gate_bias = self._f32((E,), 0.01)
-        p1, s1 = self._fp4_slab(nl, inter, dim)
-        p3, s3 = self._fp4_slab(nl, inter, dim)
-        p2, s2 = self._fp4_slab(nl, dim, inter)
+        p1, s1 = self._fp4_slab(i, 0, inter, dim)
+        p3, s3 = self._fp4_slab(i, 1, inter, dim)
+        p2, s2 = self._fp4_slab(i, 2, dim, inter)
         a1, a2, a3 = (capi.QW * E)(), (capi.QW * E)(), (capi.QW * E)()
         c13, z13 = inter * dim // 2, inter * dim // 32
         for e in range(self.e_lo, self.e_hi):

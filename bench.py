@@ -58,7 +58,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=43, help="model workload: layers (43 = the real model)")
     a = ap.parse_args()
     if a.workload is None:
-        a.workload = "model" if a.gpus == 1 else "moe_layer"
+        a.workload = "model"
     if a.workload == "model" and a.steps == 400 and a.warmup == 20:
         a.steps, a.warmup = 64, 4          # defaults of the token-loop workload
     return a
@@ -280,13 +280,107 @@ def model_reference_arm(a):
     print(json.dumps(line), flush=True)
 
 
+def model_main_ep(a):
+    """N > 1: every rank decodes its own batch; the routed experts are sharded over
+    the ranks and token rows travel by NCCL all-to-all inside every layer."""
+    import datetime
+    import torch
+    import torch.distributed as dist
+    import apus_b200
+    from apus_b200.ep_model import EpModel
+    from apus_b200.flash import RandomFlashModel
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    apus_b200.build()
+    L = apus_b200.lib()
+    err = C.create_string_buffer(512)
+    if L.apus_cuda_enable(err, 512):
+        raise RuntimeError(err.value.decode())
+    cfg = flash_config(a)
+    B, K, Wm = a.batch, a.steps, a.warmup
+    per = cfg.n_experts // world
+    max_pos = a.prompt + 2 * (K + Wm) + 72
+    W = RandomFlashModel(cfg, a.seed, dev, e_lo=rank * per, e_hi=(rank + 1) * per, max_pos=max_pos)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    ep = EpModel(W.desc, cfg.n_layers, cfg.n_experts, cfg.topk, cfg.dim, B, max_pos, rank, world, device=dev)
+    rng = np.random.default_rng([a.seed, 4242, rank])
+    prompt = rng.integers(0, cfg.vocab, size=(B, a.prompt)).astype(np.int64)
+    uuid = str(torch.cuda.get_device_properties(dev).uuid)
+    sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid) if rank == 0 else None
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    ep.prefill(prompt)
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    for _ in range(Wm):
+        ep.step()
+    d0 = L.apus_cuda_dispatches()
+    barrier()
+    w0 = time.time()
+    e0.record()
+    for _ in range(K):
+        ep.step()
+    e1.record()
+    barrier()
+    w1 = time.time()
+    launches = int(L.apus_cuda_dispatches() - d0)
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    clocks = sampler.stop(w0, w1) if sampler else None
+    # end to end: ids from the host, sampled ids back to the host, every step
+    nxt = np.empty(B, np.int32)
+    ep.read(tokens=nxt)
+    ne = max(8, K // 4)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(ne):
+        ep.set_ids(nxt.astype(np.int64))
+        ep.step(feed_back=False)
+        ep.read(tokens=nxt)
+    barrier()
+    te = torch.tensor([time.perf_counter() - t0], device=dev)
+    dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_val = world * B * ne / float(te.item())
+    ep.close()
+    if rank == 0:
+        line = {
+            "metric": MODEL_METRIC, "value": world * B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": K, "warmup": Wm, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f32 accumulate over E2M1xE4M3 / E4M3xE4M3 tensor-core products; BF16-valued activations",
+            "data": "synthetic", "config": model_config(a, world, cfg), "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": world * B * 8,
+                    "d2h_bytes_per_step": world * B * 4, "steps": ne},
+            "gpu_launches": launches,
+            "prefill": {"tokens": world * B * a.prompt, "ms": prefill_ms,
+                        "note": "prompt consumed as consecutive decode steps"},
+            "roofline": None, "weights": {"bytes_per_rank": W.bytes},
+            "note": "expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine per layer; "
+                    "the per-kernel roofline is reported by the 1-GPU run"}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def model_main(a):
+    if a.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return model_main_ep(a)
     import torch
     import apus_b200
     from apus_b200 import capi
     from apus_b200.flash import RandomFlashModel
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    assert world == 1 and a.gpus == 1, "the full-model workload runs on one GPU (use --workload moe_layer for N > 1)"
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     apus_b200.build()

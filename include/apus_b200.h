@@ -190,6 +190,11 @@ int apus_cuda_kernel_status(int reset);
  *     variants differ from its scalar code by as much, c/mhc.h:296-330).
  * order < 0 only queries.  Returns the order now in force.  Environment
  * APUS_SUM_ORDER=1 selects the tree order at load time. */
+/* Run the entry points that take no stream argument (host-pointer tier, model
+ * loop) on the caller's stream instead of the library's own, e.g. to order them
+ * with the caller's collectives without events; use_own != 0 switches back.
+ * The previous stream is synchronised first. */
+int apus_cuda_use_stream(void *stream, int use_own);
 #define APUS_CUDA_SUM_REFERENCE 0
 #define APUS_CUDA_SUM_TREE 1
 int apus_cuda_set_sum_order(int order);
@@ -463,6 +468,11 @@ int apus_cuda_block_forward(const ApusCudaLayerDesc *L, int hc_mult,
  * (1..32, advancing in lockstep) for positions < max_pos. */
 ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch,
                                       int max_pos);
+/* The same with only the routed experts [e_lo, e_hi) of every layer resident
+ * (expert parallelism: rank r of N holds [r*E/N, (r+1)*E/N); descriptors of the
+ * other experts are not read).  Such a model is driven layer by layer, below. */
+ApusCudaModel *apus_cuda_model_create_ep(const ApusCudaModelDesc *d, int batch,
+                                         int max_pos, int e_lo, int e_hi);
 void apus_cuda_model_destroy(ApusCudaModel *m);
 /* c/model.h:485: back to position 0 with empty caches. */
 int apus_cuda_model_reset(ApusCudaModel *m);
@@ -483,6 +493,25 @@ int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s,
 int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt,
                              int n_prompt, int n_gen, int32_t *out_tokens,
                              float *ms_prefill, float *ms_decode);
+
+/* One decode step of all sequences in pieces, on the library stream, for callers
+ * that run the MoE sublayer themselves (expert parallelism: route, exchange
+ * rows with the expert owners, apus_cuda_moe_experts_dev, exchange back,
+ * combine -- apus_b200/ep_model.py).  Per step: set_ids (host or device
+ * pointer, [batch]) or the fed-back token; begin_step (embedding); per layer
+ * attn_half, then ffn_input returns the device pointer of the normed sublayer
+ * input [batch, dim] and ffn_output takes the sublayer result [batch, dim];
+ * end_step advances the position and, if asked, computes logits, the greedy
+ * token and feeds it back as the next step's ids.  read copies logits / tokens
+ * to the host and synchronises. */
+int apus_cuda_model_set_ids(ApusCudaModel *m, const int64_t *ids);
+int apus_cuda_model_begin_step(ApusCudaModel *m);
+int apus_cuda_model_attn_half(ApusCudaModel *m, int layer);
+const float *apus_cuda_model_ffn_input(ApusCudaModel *m, int layer);
+int apus_cuda_model_ffn_output(ApusCudaModel *m, int layer, const float *sub);
+int apus_cuda_model_end_step(ApusCudaModel *m, int want_logits, int feed_back);
+const int64_t *apus_cuda_model_ids(ApusCudaModel *m);
+int apus_cuda_model_read(ApusCudaModel *m, float *logits, int32_t *next);
 
 /* No counterpart in the reference.  apus_cuda_hc_pre on device pointers for
  * callers that must not allocate device memory while they run (an engine whose

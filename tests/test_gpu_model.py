@@ -287,3 +287,35 @@ def test_model_rejects_bad_arguments():
     finally:
         L.apus_cuda_model_destroy(h)
     assert not L.apus_cuda_model_create(C.byref(Mdl.desc), 33, 64)                  # batch 1..32
+
+
+def test_piecewise_loop_equals_generate():
+    """The layer-by-layer interface the expert-parallel loop uses (attention half,
+    MoE sublayer run by the caller through route / experts / shared / combine,
+    mHC post) reproduces apus_cuda_model_generate bit for bit."""
+    import torch
+    from apus_b200.ep_model import EpModel
+    L = lib()
+    tag = "model_batch"
+    _, n_layers, B, n_prompt, n_gen = MODEL_CASES[tag]
+    Mdl, prompts, h = make_model(L, tag, B)
+    toks = np.empty((B, n_gen), np.int32)
+    try:
+        assert L.apus_cuda_model_generate(h, P(prompts), n_prompt, n_gen, P(toks), None, None) == 0
+    finally:
+        L.apus_cuda_model_destroy(h)
+    M = Mdl.M
+    ep = EpModel(Mdl.desc, n_layers, M["E"], M["topk"], cases.ATTN_DIMS["dim"], B, 64, device=torch.device("cuda", 0))
+    try:
+        got = np.empty((B, n_gen), np.int32)
+        nxt = np.empty(B, np.int32)
+        ep.prefill(prompts)
+        for g in range(n_gen):
+            ep.read(tokens=nxt)
+            got[:, g] = nxt
+            if g + 1 < n_gen:
+                ep.step()
+    finally:
+        ep.close()
+        L.apus_cuda_use_stream(None, 1)
+    assert np.array_equal(got, toks)
