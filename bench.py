@@ -486,7 +486,11 @@ def model_main(a):
         "roofline": {"kernel": "gemm_tc_kernel<pair> (tcgen05 block-scaled MXFP4 expert gate/up GEMV + SwiGLU), "
                                "all layers of the timed steps",
                      "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind, "traffic": None,
+                     "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,
+                     # dram read+write bytes per launch: measured with ncu on a 64-expert case of the same
+                     # kernel (1.002 x the algorithmic bytes) and scaled by the experts touched here
+                     "traffic": items / max(nl, 1) * W13_BYTES * 1.002,
+                     "traffic_source": "ncu capture of a smaller case scaled by units (profiles/gemm_tc_mxfp4_pair_T32_E64.md)",
                      "launches": nl, "avg_launch_us": g13 / max(nl, 1) * 1e3,
                      "avg_unique_experts": items / max(nl, 1),
                      "share_of_step": g13 / ms if ms > 0 else None,
