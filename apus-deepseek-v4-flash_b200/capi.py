@@ -201,6 +201,8 @@ def load(path=LIB_PATH):
         "apus_cuda_model_reset": (ci, [vp]),
         "apus_cuda_model_pos": (i64, [vp]),
         "apus_cuda_model_moe": (vp, [vp, ci]),
+        "apus_cuda_model_use_graph": (ci, [vp, ci]),
+        "apus_cuda_moe_timing_enabled": (ci, [vp]),
         "apus_cuda_moe_work_items": (C.c_longlong, [vp, ci]),
         "apus_cuda_model_forward": (ci, [vp, vp, ci, vp, vp]),
         "apus_cuda_model_generate": (ci, [vp, vp, ci, ci, vp, C.POINTER(cf), C.POINTER(cf)]),

@@ -146,15 +146,25 @@ int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, St
 // One compressor decode step of B sequences; appends a finished entry to every
 // cache when the block completes (reference c/attn.h:960-1008 + 797-819).
 static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, int B, int dim, long long pos,
-                           const float *cs_rp, const StepBufs &b, cudaStream_t st) {
+                           const float *cs_rp, const StepBufs &b, cudaStream_t st, const long long *pos_dev,
+                           const float *cs_table) {
     const int cd = (1 + W.overlap) * W.d;
     if (f32_linear(W.wkv, x, b.ckv, B, dim, cd, 0, st) || f32_linear(W.wgate, x, b.csc, B, dim, cd, 0, st))
         return 1;
     const int slot = (int)(pos % W.ratio);
     const int should = (pos + 1) % W.ratio == 0;
     if (comp_step(S.kv.as<float>(), S.sc.as<float>(), (long long)S.carry, b.ckv, b.csc, cd, W.ape, W.ratio,
-                  W.overlap, W.d, slot, should, b.pooled, W.d, B, st))
+                  W.overlap, W.d, slot, should, b.pooled, W.d, B, st, pos_dev))
         return 1;
+    if (pos_dev) {
+        // position on the device: the append is always launched and gates itself; the
+        // entry index and the rope row follow from the position; the caller keeps S.nb
+        int flags = ROW_BF16_IN | ROW_RMS_W | ROW_ROPE | ROW_BF16_OUT |
+                    (W.rotate ? (ROW_HADAMARD | ROW_FP4QAT) : ROW_FP8QAT);
+        const RowDyn dyn = {pos_dev, 1 - W.ratio, W.ratio, (long long)W.d};
+        return row_ops(b.pooled, W.d, S.cache.as<float>(), S.cap * W.d, B, W.d, flags, W.norm, W.eps, W.rd, cs_table,
+                       B, 0, st, &dyn);
+    }
     if (should) {
         APUS_REQUIRE(S.nb < S.cap, "compressed cache is full (%d entries)", S.cap);
         int flags = ROW_BF16_IN | ROW_RMS_W | ROW_ROPE | ROW_BF16_OUT |
@@ -168,9 +178,15 @@ static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, in
 }
 
 int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
-              const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st) {
+              const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st,
+              const long long *pos_dev, const float *cs_table) {
     const ApusAttnCfg &c = A.cfg;
     const int B = S.B;
+    // pos_dev != NULL: every position-dependent value is read on the device from
+    // *pos_dev (rope rows from cs_table), so the launches are the same at every position
+    const RowDyn dyn_pos = {pos_dev, 0, 0, 0};
+    const RowDyn *dp = pos_dev ? &dyn_pos : nullptr;
+    if (pos_dev) cs_pos = cs_table;
     const int h = c.n_heads, d = c.head_dim, rd = c.rope_dim, win = c.window, ratio = c.ratio;
     const int hd = h * d;
     // q path (c/attn.h:1525-1548)
@@ -178,11 +194,11 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st))
         return 1;
     if (qlinear_dev(A.wq_b, b.qr, b.q, B, b.xq, b.xs, true, st)) return 1;
-    if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, B * h, 0, st)) return 1;
+    if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, B * h, 0, st, dp)) return 1;
     // window KV (c/attn.h:1552-1569)
     if (qlinear_dev(A.wkv, x, b.kva, B, b.xq, b.xs, true, st)) return 1;
     if (row_ops(b.kva, d, b.kv, d, B, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd,
-                cs_pos, B, 0, st))
+                cs_pos, B, 0, st, dp))
         return 1;
     // compressed ids: the indexer runs BEFORE the ring write and the attention compressor
     int compw = 0;
@@ -193,13 +209,20 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
             const int ih = c.idx_heads, idm = c.idx_dim;
             if (qlinear_dev(A.idx_wq_b, b.qr, b.iq, B, b.xq, b.xs, true, st)) return 1;
             if (row_ops(b.iq, idm, b.iq, idm, B * ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr,
-                        0.f, rd, cs_pos, B * ih, 0, st))
+                        0.f, rd, cs_pos, B * ih, 0, st, dp))
                 return 1;
-            if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, st)) return 1;
+            if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, st, pos_dev, cs_table)) return 1;
             if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, ih, APUS_CUDA_R_IN | APUS_CUDA_R_OUT, st)) return 1;
             const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
             compw = (int)(c.idx_topk < nbs ? c.idx_topk : nbs);
-            if (compw > 0) {
+            if (pos_dev) {                         // capacities; the live counts are derived on the device
+                compw = c.idx_topk < S.idx.cap ? c.idx_topk : S.idx.cap;
+                if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), (long long)S.idx.cap * idm, S.idx.cap, ih,
+                               idm, b.scores, B, st, pos_dev, ratio))
+                    return 1;
+                if (topk_stable(b.scores, S.idx.cap, compw, b.sel, B, st, pos_dev, ratio)) return 1;
+                sel = b.sel;
+            } else if (compw > 0) {
                 if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), (long long)S.idx.cap * idm, nbs, ih, idm,
                                b.scores, B, st))
                     return 1;
@@ -207,21 +230,23 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
                 sel = b.sel;
             }
         } else {
-            compw = (int)nbs;
+            compw = pos_dev ? S.comp.cap : (int)nbs;
         }
     }
     if (idx_k_out) *idx_k_out = compw;
     // ring write, attention compressor (c/attn.h:1642-1665)
-    if (scatter_rows(S.win.as<float>() + (size_t)(pos % win) * d, (long long)win * d, b.kv, d, B, st)) return 1;
-    if (ratio && compressor_step(A.comp, S.comp, x, B, c.dim, pos, cs_rp, b, st)) return 1;
+    if (scatter_rows(S.win.as<float>() + (pos_dev ? 0 : (size_t)(pos % win) * d), (long long)win * d, b.kv, d, B, st,
+                     pos_dev, win))
+        return 1;
+    if (ratio && compressor_step(A.comp, S.comp, x, B, c.dim, pos, cs_rp, b, st, pos_dev, cs_table)) return 1;
     // gathered attention over ring ++ compressed cache, inverse RoPE
-    if (build_idx(b.idxs, win, pos, sel, compw, B, st)) return 1;
+    if (build_idx(b.idxs, win, pos, sel, compw, B, st, pos_dev, ratio)) return 1;
     const float scale = (float)pow((double)d, -0.5);
     if (sparse_attn(b.q, A.sink, h, d, b.idxs, win + compw, B, scale, S.win.p, win,
                     ratio ? S.comp.cache.p : nullptr, ratio ? S.comp.nb : 0, 0, b.o, st, (long long)win * d,
                     ratio ? (long long)S.comp.cap * d : 0))
         return 1;
-    if (row_ops(b.o, d, b.o, d, B * h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs_pos, B * h, 0, st)) return 1;
+    if (row_ops(b.o, d, b.o, d, B * h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs_pos, B * h, 0, st, dp)) return 1;
     // grouped low-rank o-projection (c/attn.h:1692-1737)
     const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
     if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, B, sub, ol,

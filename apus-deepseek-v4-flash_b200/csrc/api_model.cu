@@ -37,7 +37,7 @@ struct BlockBufs {
 // itself between the second and the third.
 int block_attn_half(const LayerDev &L, StateDev &S, float **h, float **hn, int B, long long pos, int hc,
                     int iters, float hc_eps, float norm_eps, const BlockBufs &bb, const StepBufs &sb,
-                    cudaStream_t st) {
+                    cudaStream_t st, const long long *pos_dev = nullptr) {
     const int dim = L.attn.cfg.dim, half2 = L.attn.cfg.rope_dim, ratio = L.attn.cfg.ratio;
     APUS_REQUIRE(pos < L.rope_rows, "position %lld is beyond the rope table (%d rows)", pos, L.rope_rows);
     const float *cs_pos = L.cs + (size_t)pos * half2;
@@ -46,7 +46,7 @@ int block_attn_half(const LayerDev &L, StateDev &S, float **h, float **hn, int B
     if (mhc_pre(*h, dim, hc, L.hc_attn_fn, L.hc_attn_scale, L.hc_attn_base, norm_eps, hc_eps, iters,
                 L.attn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st))
         return 1;
-    if (attn_step(L.attn, S, bb.x, pos, cs_pos, cs_rp, bb.sub, sb, nullptr, st)) return 1;
+    if (attn_step(L.attn, S, bb.x, pos, cs_pos, cs_rp, bb.sub, sb, nullptr, st, pos_dev, L.cs)) return 1;
     if (mhc_post(bb.sub, *h, bb.post, bb.comb, *hn, dim, hc, B, st)) return 1;
     { float *t = *h; *h = *hn; *hn = t; }
     return 0;
@@ -65,8 +65,8 @@ int block_ffn_post(const LayerDev &L, const float *sub, float **h, float **hn, i
 }
 int block_step(const LayerDev &L, StateDev &S, float **h, float **hn, const int64_t *ids, int B, long long pos,
                int hc, int iters, float hc_eps, float norm_eps, const BlockBufs &bb, const StepBufs &sb,
-               cudaStream_t st) {
-    if (block_attn_half(L, S, h, hn, B, pos, hc, iters, hc_eps, norm_eps, bb, sb, st)) return 1;
+               cudaStream_t st, const long long *pos_dev = nullptr) {
+    if (block_attn_half(L, S, h, hn, B, pos, hc, iters, hc_eps, norm_eps, bb, sb, st, pos_dev)) return 1;
     if (block_ffn_pre(L, *h, B, hc, iters, hc_eps, norm_eps, bb, st)) return 1;
     if (apus_cuda_moe_forward_dev(L.moe, bb.x, ids, B, bb.sub, st)) return 1;
     return block_ffn_post(L, bb.sub, h, hn, B, hc, bb, st);
@@ -155,6 +155,13 @@ struct ApusCudaModel {
     long long pos = 0;
     int e_lo = 0, e_hi = 0;                // routed experts resident here (expert parallelism)
     float *h_cur = nullptr, *h_alt = nullptr;   // hidden state between the pieces of a step
+    // the position also lives on the device: the kernels of a step read it there, so
+    // a step is the same launch sequence at every position and is replayed from a
+    // CUDA graph (one with the head, one without) after the first step ran eagerly
+    DevBuf pos_dev;
+    cudaGraphExec_t gexec[2] = {nullptr, nullptr};
+    bool use_graph = true;
+    long long steps_run = 0;
     WeightOwner own;                       // every weight copy made for this model
     std::map<const void *, DevBuf *> rope; // rope rows by host table (layers of a kind share one)
     DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, ws[20];
@@ -180,19 +187,78 @@ static int model_head(ApusCudaModel *m, cudaStream_t st) {
         return 1;
     return argmax_rows(m->logits.as<float>(), m->vocab, B, m->tok.as<int32_t>(), st);
 }
+__global__ void advance_pos_kernel(long long *pos) { *pos += 1; }
+
+// host mirror of what a step does to the sequence state: entry counts follow the position
+static int model_host_advance(ApusCudaModel *m) {
+    for (int i = 0; i < m->n_layers; i++) {
+        const ApusAttnCfg &c = m->layers[i].attn.cfg;
+        if (c.ratio && (m->pos + 1) % c.ratio == 0) {
+            m->states[i].comp.nb++;
+            if (c.has_indexer) m->states[i].idx.nb++;
+        }
+    }
+    m->pos++;
+    m->steps_run++;
+    return 0;
+}
+
+// every launch of one position of all sequences, position read on the device
+static int model_step_enqueue(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
+    if (model_embed(m, st)) return 1;
+    BlockBufs bb = model_bufs(m);
+    const long long *pd = m->pos_dev.as<long long>();
+    for (int i = 0; i < m->n_layers; i++)
+        if (block_step(m->layers[i], m->states[i], &m->h_cur, &m->h_alt, m->ids.as<int64_t>(), m->B, m->pos, m->hc,
+                       m->iters, m->hc_eps, m->norm_eps, bb, m->sb, st, pd))
+            return 1;
+    if (want_logits && model_head(m, st)) return 1;
+    advance_pos_kernel<<<1, 1, 0, st>>>(m->pos_dev.as<long long>());
+    APUS_LAUNCHED();
+    return 0;
+}
+
+int apus_cuda_moe_timing_enabled(const ApusCudaMoe *m);      // api_moe.cu
+static bool model_timing_on(ApusCudaModel *m) {
+    for (auto &L : m->layers) if (L.moe && apus_cuda_moe_timing_enabled(L.moe)) return true;
+    return false;
+}
+
 static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
     APUS_REQUIRE(m->e_lo == 0 && m->e_hi == m->n_experts,
                  "this model holds experts [%d,%d) of %d: drive it layer by layer (apus_cuda_model_attn_half ...)",
                  m->e_lo, m->e_hi, m->n_experts);
-    if (model_embed(m, st)) return 1;
-    BlockBufs bb = model_bufs(m);
-    for (int i = 0; i < m->n_layers; i++)
-        if (block_step(m->layers[i], m->states[i], &m->h_cur, &m->h_alt, m->ids.as<int64_t>(), m->B, m->pos, m->hc,
-                       m->iters, m->hc_eps, m->norm_eps, bb, m->sb, st))
-            return 1;
-    m->pos++;
-    if (!want_logits) return 0;
-    return model_head(m, st);
+    APUS_REQUIRE(m->pos < m->max_pos, "model step: position %lld reaches max_pos %d", m->pos, m->max_pos);
+    for (int i = 0; i < m->n_layers; i++) {
+        const ApusAttnCfg &c = m->layers[i].attn.cfg;
+        if (c.ratio && (m->pos + 1) % c.ratio == 0)
+            APUS_REQUIRE(m->states[i].comp.nb < m->states[i].comp.cap, "layer %d: compressed cache is full", i);
+    }
+    const int gi = want_logits ? 1 : 0;
+    if (m->use_graph && m->steps_run >= 1 && !model_timing_on(m)) {
+        if (!m->gexec[gi]) {
+            // capture the launches of one step; nothing in here allocates or synchronises
+            // because the first step already ran eagerly with the same shapes
+            cudaGraph_t graph = nullptr;
+            bool ok = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+            const int rc = ok ? model_step_enqueue(m, want_logits, st) : 1;
+            if (ok) ok = cudaStreamEndCapture(st, &graph) == cudaSuccess && rc == 0 && graph;
+            if (ok) ok = cudaGraphInstantiate(&m->gexec[gi], graph, 0) == cudaSuccess;
+            if (graph) cudaGraphDestroy(graph);
+            if (!ok) {                         // fall back to plain launches for good
+                cudaGetLastError();
+                m->gexec[gi] = nullptr;
+                m->use_graph = false;
+            }
+        }
+        if (m->gexec[gi]) {
+            APUS_CUDA_OK(cudaGraphLaunch(m->gexec[gi], st));
+            g_dispatches++;
+            return model_host_advance(m);
+        }
+    }
+    if (model_step_enqueue(m, want_logits, st)) return 1;
+    return model_host_advance(m);
 }
 
 extern "C" {
@@ -201,6 +267,8 @@ void apus_cuda_model_destroy(ApusCudaModel *m) {
     if (!m) return;
     cudaDeviceSynchronize();
     for (auto &s : m->states) s.release();
+    for (int i = 0; i < 2; i++) if (m->gexec[i]) cudaGraphExecDestroy(m->gexec[i]);
+    m->pos_dev.release();
     for (auto &L : m->layers) if (L.moe) apus_cuda_moe_destroy(L.moe);
     m->own.release();
     for (auto &kv : m->rope) { kv.second->release(); delete kv.second; }
@@ -218,6 +286,9 @@ int apus_cuda_model_reset(ApusCudaModel *m) {
         const int cap = c.ratio ? m->max_pos / c.ratio + 2 : 0;
         if (attn_state_init(c, m->states[i], m->B, cap)) return 1;
     }
+    if (m->pos_dev.get(256, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemsetAsync(m->pos_dev.p, 0, 256, ctx().stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(ctx().stream));
     m->pos = 0;
     return 0;
 }
@@ -335,6 +406,12 @@ int apus_cuda_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float
 }
 
 int64_t apus_cuda_model_pos(const ApusCudaModel *m) { return m ? m->pos : -1; }
+
+int apus_cuda_model_use_graph(ApusCudaModel *m, int enable) {
+    if (!m) return -1;
+    if (enable >= 0) m->use_graph = enable != 0;
+    return m->use_graph ? 1 : 0;
+}
 
 ApusCudaMoe *apus_cuda_model_moe(ApusCudaModel *m, int layer) {
     if (!m || layer < 0 || layer >= m->n_layers) return nullptr;

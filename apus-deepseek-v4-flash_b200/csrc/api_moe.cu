@@ -406,6 +406,8 @@ int apus_cuda_moe_use_tc(ApusCudaMoe *m, int enable) {
     return m->use_tc ? 1 : 0;
 }
 
+int apus_cuda_moe_timing_enabled(const ApusCudaMoe *m) { return m && m->timing ? 1 : 0; }
+
 void apus_cuda_moe_timing(ApusCudaMoe *m, int enable) {
     if (!m) return;
     m->timing = enable != 0;

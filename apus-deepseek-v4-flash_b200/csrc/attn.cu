@@ -25,12 +25,19 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 #define TOPK_MAX_K 2048
 
 __global__ void __launch_bounds__(TOPK_THREADS)
-topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__restrict__ idx_out) {
+topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__restrict__ idx_out,
+                   const long long *__restrict__ dyn_pos, int ratio) {
     __shared__ unsigned hist[256];
     __shared__ unsigned s_prefix, s_need, s_greater, s_taken, s_base;
     __shared__ unsigned long long sel[TOPK_MAX_K];
-    const float *row = scores + (size_t)blockIdx.x * n;
+    const float *row = scores + (size_t)blockIdx.x * n;     // n, k as given are the row strides
     int32_t *out = idx_out + (size_t)blockIdx.x * k;
+    if (dyn_pos) {                                          // live sizes from the position on the device
+        const long long nbs = (*dyn_pos + 1) / ratio;
+        n = (int)(nbs < n ? nbs : n);
+        k = k < n ? k : n;
+        if (k <= 0) return;
+    }
     const int tid = threadIdx.x;
 
     // radix select: after the loop `prefix` is the key of the k-th largest score
@@ -115,10 +122,10 @@ topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__re
 }
 
 int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
-                cudaStream_t st) {
-    APUS_REQUIRE(k >= 1 && k <= n && k <= TOPK_MAX_K, "topk: n=%d k=%d unsupported", n, k);
+                cudaStream_t st, const long long *dyn_pos, int ratio) {
+    APUS_REQUIRE(k >= 1 && (k <= n || dyn_pos) && k <= TOPK_MAX_K, "topk: n=%d k=%d unsupported", n, k);
     if (rows <= 0) return 0;
-    topk_stable_kernel<<<rows, TOPK_THREADS, 0, st>>>(scores, n, k, idx);
+    topk_stable_kernel<<<rows, TOPK_THREADS, 0, st>>>(scores, n, k, idx, dyn_pos, ratio);
     APUS_LAUNCHED();
     return 0;
 }
@@ -324,21 +331,30 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
     dim3 g1((unsigned)ceil_div(idxw, SA_IDS), (unsigned)ceil_div(h, SA_HEADS), (unsigned)s);
     size_t sm2 = (size_t)idxw * sizeof(float);
     dim3 g2((unsigned)h, (unsigned)s);
+    static size_t cfg1[2] = {0, 0}, cfg2[2] = {0, 0};        // largest sizes configured so far (f32 / BF16 KV)
+    const int kb = kv_bf16 ? 1 : 0;
+    if (sm1 > cfg1[kb] || sm2 > cfg2[kb]) {
+        if (kv_bf16) {
+            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_scores_kernel<true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1));
+            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)(sm2 > cfg2[kb] ? sm2 : cfg2[kb])));
+        } else {
+            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_scores_kernel<false>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1));
+            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)(sm2 > cfg2[kb] ? sm2 : cfg2[kb])));
+        }
+        if (sm1 > cfg1[kb]) cfg1[kb] = sm1;
+        if (sm2 > cfg2[kb]) cfg2[kb] = sm2;
+    }
     if (kv_bf16) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(sparse_scores_kernel<true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1));
-        APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
         sparse_scores_kernel<true><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
                                                                        kv_a, na, kv_b, sc, sa, sb);
         APUS_LAUNCHED();
         sparse_pv_kernel<true><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb);
         APUS_LAUNCHED();
     } else {
-        APUS_CUDA_OK(cudaFuncSetAttribute(sparse_scores_kernel<false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1));
-        APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
         sparse_scores_kernel<false><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
                                                                         kv_a, na, kv_b, sc, sa, sb);
         APUS_LAUNCHED();

@@ -51,8 +51,12 @@ int attn_weights(const ApusAttnCfg *cfg, const ApusAttnW *w, AttnDev *A, WeightO
 int attn_state_init(const ApusAttnCfg &c, StateDev &S, int B, int cap);
 int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, StepBufs *b);
 // One token of B sequences in lockstep at position pos. x [B, dim] -> out [B, dim].
+// pos_dev != NULL: the position is read on the device from *pos_dev and the rope
+// rows from cs_table ([pos][cos | sin]); the launch sequence is then the same at
+// every position, and the entry counts S.*.nb are left to the caller.
 int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
-              const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st);
+              const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st,
+              const long long *pos_dev = nullptr, const float *cs_table = nullptr);
 
 // Host-state exchange of the host-pointer tier (one sequence).
 int attn_state_upload(const ApusAttnCfg &c, const ApusAttnS *st, StateDev &S, int extra, cudaStream_t sm);

@@ -29,7 +29,18 @@ __device__ __forceinline__ float fp4_qat_value(float y) {
 __global__ void __launch_bounds__(1024)
 row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y, int y_stride, int n,
                int flags, const float *__restrict__ norm_w, float eps, int rd,
-               const float *__restrict__ cs, int rows_per_cs, int cs_stride) {
+               const float *__restrict__ cs, int rows_per_cs, int cs_stride, const RowDyn dyn) {
+    if (dyn.pos) {                             // position read on the device (see RowDyn)
+        const long long p = *dyn.pos;
+        if (dyn.gate_ratio > 0) {
+            if ((p + 1) % dyn.gate_ratio != 0) return;
+            y += ((p + 1) / dyn.gate_ratio - 1) * dyn.y_step;
+        }
+        if (cs) {
+            long long r = p + dyn.cs_bias;
+            cs += (r > 0 ? r : 0) * rd;
+        }
+    }
     extern __shared__ __align__(16) float s_v[];   // [n] row, then [n/32 + 32] scratch
     float *s_red = s_v + n;
     const int row = blockIdx.x, i = threadIdx.x;
@@ -114,14 +125,15 @@ row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y,
 
 int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
             const float *norm_w, float eps, int rd, const float *cs, int rows_per_cs, int cs_stride,
-            cudaStream_t st) {
+            cudaStream_t st, const RowDyn *dyn) {
     APUS_REQUIRE(n >= 32 && n <= 1024 && n % 32 == 0, "row_ops: n=%d unsupported", n);
     APUS_REQUIRE(!(flags & ROW_HADAMARD) || (n & (n - 1)) == 0, "row_ops: Hadamard needs a power of two, n=%d", n);
     if (rows <= 0) return 0;
     size_t smem = (size_t)(n + 64) * sizeof(float);
     if (sum_order() != APUS_CUDA_SUM_TREE) flags |= ROW_SEQ_SUM;
+    const RowDyn none = {nullptr, 0, 0, 0};
     row_ops_kernel<<<rows, n, smem, st>>>(x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
-                                          rows_per_cs > 0 ? rows_per_cs : 1, cs_stride);
+                                          rows_per_cs > 0 ? rows_per_cs : 1, cs_stride, dyn ? *dyn : none);
     APUS_LAUNCHED();
     return 0;
 }
@@ -136,7 +148,12 @@ __global__ void __launch_bounds__(1024)
 comp_step_kernel(float *__restrict__ kv_state, float *__restrict__ sc_state, long long state_stride,
                  const float *__restrict__ kv_new, const float *__restrict__ sc_new, int new_stride,
                  const float *__restrict__ ape, int ratio, int overlap, int d, int slot, int should,
-                 float *__restrict__ pooled, int pooled_stride) {
+                 float *__restrict__ pooled, int pooled_stride, const long long *__restrict__ dyn_pos) {
+    if (dyn_pos) {
+        const long long p = *dyn_pos;
+        slot = (int)(p % ratio);
+        should = (p + 1) % ratio == 0;
+    }
     const int seq = blockIdx.x, c = threadIdx.x;
     const int cd = (1 + overlap) * d;
     float *kvs = kv_state + (size_t)seq * state_stride;
@@ -180,13 +197,14 @@ comp_step_kernel(float *__restrict__ kv_state, float *__restrict__ sc_state, lon
 
 int comp_step(float *kv_state, float *sc_state, long long state_stride, const float *kv_new,
               const float *sc_new, int new_stride, const float *ape, int ratio, int overlap, int d,
-              int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st) {
+              int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st,
+              const long long *dyn_pos) {
     const int cd = (1 + overlap) * d;
     APUS_REQUIRE(cd <= 1024, "compressor: state width %d exceeds 1024", cd);
     if (n_seq <= 0) return 0;
     comp_step_kernel<<<n_seq, ((cd + 31) / 32) * 32, 0, st>>>(kv_state, sc_state, state_stride, kv_new,
                                                               sc_new, new_stride, ape, ratio, overlap, d,
-                                                              slot, should, pooled, pooled_stride);
+                                                              slot, should, pooled, pooled_stride, dyn_pos);
     APUS_LAUNCHED();
     return 0;
 }
@@ -200,12 +218,16 @@ int comp_step(float *kv_state, float *sc_state, long long state_stride, const fl
 __global__ void __launch_bounds__(64 * IDX_B)
 idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, float wscale,
                  const float *__restrict__ cache, long long cache_stride, long long nb, int ih, int idm,
-                 float *__restrict__ sc) {
+                 float *__restrict__ sc, const long long *__restrict__ dyn_pos, int ratio) {
     extern __shared__ float sm[];             // q [ih*idm], k [IDX_B*idm], terms [IDX_B*ih]
     q += (size_t)blockIdx.y * ih * idm;
     wt_raw += (size_t)blockIdx.y * ih;
     cache += (size_t)blockIdx.y * cache_stride;
-    sc += (size_t)blockIdx.y * nb;
+    sc += (size_t)blockIdx.y * nb;             // row stride: the capacity when the count is read on the device
+    if (dyn_pos) {
+        nb = (*dyn_pos + 1) / ratio;
+        if ((long long)blockIdx.x * IDX_B >= nb) return;
+    }
     float *s_q = sm, *s_k = sm + ih * idm, *s_t = s_k + IDX_B * idm;
     const int hh = threadIdx.x % ih, bl = threadIdx.x / ih;
     const long long b = (long long)blockIdx.x * IDX_B + bl;
@@ -232,7 +254,8 @@ idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, 
 }
 
 int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long cache_stride,
-               long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st) {
+               long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st, const long long *dyn_pos,
+               int ratio) {
     APUS_REQUIRE(ih <= 64 && ih >= 1, "indexer: %d heads unsupported", ih);
     if (nb <= 0 || n_seq <= 0) return 0;
     size_t smem = ((size_t)ih * idm + IDX_B * idm + IDX_B * ih) * sizeof(float);
@@ -242,7 +265,8 @@ int idx_scores(const float *q, const float *wt_raw, float wscale, const float *c
         configured = smem;
     }
     dim3 grid((unsigned)((nb + IDX_B - 1) / IDX_B), (unsigned)n_seq);
-    idx_score_kernel<<<grid, ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc);
+    idx_score_kernel<<<grid, ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc,
+                                                     dyn_pos, ratio);
     APUS_LAUNCHED();
     return 0;
 }
@@ -251,10 +275,18 @@ int idx_scores(const float *q, const float *wt_raw, float wscale, const float *c
 // row = [window ids in ring order] ++ [compressed ids + win]; comp ids either the
 // indexer's top-k (sel != NULL) or the dense list 0..compw-1.
 __global__ void build_idx_kernel(int32_t *__restrict__ out, int win, long long pos,
-                                 const int32_t *__restrict__ sel, int compw) {
+                                 const int32_t *__restrict__ sel, int compw,
+                                 const long long *__restrict__ dyn_pos, int ratio) {
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     out += (size_t)blockIdx.y * (win + compw);
     if (sel) sel += (size_t)blockIdx.y * compw;
+    if (dyn_pos) {                             // compw so far = capacity; the rest of the row is padding
+        const int cap = compw;
+        pos = *dyn_pos;
+        const long long nbs = ratio ? (pos + 1) / ratio : 0;
+        compw = (int)(nbs < cap ? nbs : cap);
+        if (j >= win + compw && j < win + cap) { out[j] = -1; return; }
+    }
     if (j < win) {
         int v;
         if (pos >= win - 1) {
@@ -269,22 +301,27 @@ __global__ void build_idx_kernel(int32_t *__restrict__ out, int win, long long p
     }
 }
 
-int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st) {
+int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st,
+              const long long *dyn_pos, int ratio) {
     if (n_seq <= 0) return 0;
-    build_idx_kernel<<<dim3(ceil_div(win + compw, 256), n_seq), 256, 0, st>>>(out, win, pos, sel, compw);
+    build_idx_kernel<<<dim3(ceil_div(win + compw, 256), n_seq), 256, 0, st>>>(out, win, pos, sel, compw, dyn_pos,
+                                                                              ratio);
     APUS_LAUNCHED();
     return 0;
 }
 
 __global__ void scatter_rows_kernel(float *__restrict__ dst, long long dst_stride,
-                                    const float *__restrict__ src, int n) {
+                                    const float *__restrict__ src, int n,
+                                    const long long *__restrict__ dyn_pos, int win) {
+    if (dyn_pos) dst += (size_t)(*dyn_pos % win) * n;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[(size_t)blockIdx.y * dst_stride + i] = src[(size_t)blockIdx.y * n + i];
 }
 
-int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st) {
+int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st,
+                 const long long *dyn_pos, int win) {
     if (rows <= 0) return 0;
-    scatter_rows_kernel<<<dim3(ceil_div(n, 256), rows), 256, 0, st>>>(dst, dst_stride, src, n);
+    scatter_rows_kernel<<<dim3(ceil_div(n, 256), rows), 256, 0, st>>>(dst, dst_stride, src, n, dyn_pos, win);
     APUS_LAUNCHED();
     return 0;
 }

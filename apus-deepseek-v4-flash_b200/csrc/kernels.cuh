@@ -128,7 +128,8 @@ int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
 
 // ---- selection + attention (attn.cu) ----------------------------------------------------------
 int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
-                cudaStream_t st);
+                cudaStream_t st, const long long *dyn_pos = nullptr, int ratio = 0);
+// dyn_pos: n and k are capacities (row strides); live n = (*dyn_pos + 1) / ratio, live k = min(k, n)
 int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
@@ -149,20 +150,36 @@ enum {
     ROW_SEQ_SUM = 512     // set by the launcher: sums of squares in the reference's loop order
 };
 // cs: per position [cos(half) | sin(half)]; row r uses cs + (r / rows_per_cs) * cs_stride.
+// Position-dependent arguments read on the device, so that the launch sequence
+// of a decode step is the same at every position (a step can then be replayed
+// from a CUDA graph).  pos == NULL: the host arguments are used as given.
+struct RowDyn {
+    const long long *pos;     // device scalar: position of the step
+    int cs_bias;              // `cs` is the table base; the row of position pos + cs_bias (>= 0) is used
+    int gate_ratio;           // > 0: run only when (pos + 1) % gate_ratio == 0 ...
+    long long y_step;         // ... and write to y + ((pos + 1) / gate_ratio - 1) * y_step
+};
 int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
             const float *norm_w, float eps, int rd, const float *cs, int rows_per_cs, int cs_stride,
-            cudaStream_t st);
+            cudaStream_t st, const RowDyn *dyn = nullptr);
 int comp_step(float *kv_state, float *sc_state, long long state_stride, const float *kv_new,
               const float *sc_new, int new_stride, const float *ape, int ratio, int overlap, int d,
-              int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st);
+              int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st,
+              const long long *dyn_pos = nullptr);    // dyn_pos: slot and should derived from *dyn_pos
 // n_seq sequences in lockstep: q [n_seq, ih*idm], wt_raw [n_seq, ih], caches cache_stride floats
 // apart, sc [n_seq, nb].
 int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long cache_stride,
-               long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st);
+               long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st,
+               const long long *dyn_pos = nullptr, int ratio = 0);
+// dyn_pos: nb is the capacity (grid size and row stride of sc); the live count is (*dyn_pos + 1) / ratio
 // out [n_seq, win + compw]; sel [n_seq, compw] or NULL for the dense list.
-int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st);
+int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st,
+              const long long *dyn_pos = nullptr, int ratio = 0);
+// dyn_pos: compw is the row capacity (row stride win + compw, unused tail -1, sel stride compw); the live
+// width is min(compw, (*dyn_pos + 1) / ratio)
 // dst[b * dst_stride + i] = src[b * n + i] for b < rows (ring / cache row scatter).
-int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st);
+int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st,
+                 const long long *dyn_pos = nullptr, int win = 0);   // dyn_pos: dst += (*dyn_pos % win) * n
 // First index of the row maximum (reference c/sample.h:76-81), rows of n.
 int argmax_rows(const float *x, int n, int rows, int32_t *out, cudaStream_t st);
 // Embedding rows replicated hc times (reference c/model.h:512-517): out [rows, hc, dim].

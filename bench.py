@@ -407,8 +407,10 @@ def model_main(a):
     sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
 
     def run(batch, timed_moe):
-        """Prompt, warm-up decode steps, K timed decode steps with the sampled
-        token fed back on the device; returns (ms of the K steps, prefill ms, launches, tokens)."""
+        """Prompt, warm-up decode steps, K timed decode steps with the sampled token fed
+        back on the device (each step replayed from a CUDA graph); then, when asked, a
+        short pass with plain launches and CUDA events around the expert kernels.
+        Returns (handle, ms of the K steps, prefill ms, kernels per step, tokens, wall, stats)."""
         h = create(batch)
         prompt = rng.integers(0, cfg.vocab, size=(batch, a.prompt)).astype(np.int64)
         toks = np.empty((batch, Wm + 1), np.int32)
@@ -416,33 +418,38 @@ def model_main(a):
         apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(prompt), a.prompt, Wm + 1, capi.ptr(toks),
                                                    C.byref(ms_pre), C.byref(ms_dec)), "generate (prompt + warm-up)")
         prefill_ms = ms_pre.value
-        moes = [L.apus_cuda_model_moe(h, i) for i in range(cfg.n_layers)]
-        if timed_moe:
-            for m in moes:
-                L.apus_cuda_moe_timing(m, 1)
-                L.apus_cuda_moe_work_items(m, 1)
         last = np.ascontiguousarray(toks[:, -1:].astype(np.int64))
         out = np.empty((batch, K + 1), np.int32)
-        d0 = L.apus_cuda_dispatches()
         torch.cuda.synchronize()
         w0 = time.time()
         apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(last), 1, K + 1, capi.ptr(out), C.byref(ms_pre),
                                                    C.byref(ms_dec)), "generate (timed)")
         torch.cuda.synchronize()
         w1 = time.time()
-        launches = int(L.apus_cuda_dispatches() - d0)
-        stats = None
-        if timed_moe:
-            g13 = g2 = 0.0
-            nl = items = 0
-            for m in moes:
-                x, y, n = C.c_double(), C.c_double(), C.c_int()
-                apus_b200.check(L.apus_cuda_moe_timing_read(m, C.byref(x), C.byref(y), C.byref(n)), "timing")
-                L.apus_cuda_moe_timing(m, 0)
-                g13 += x.value; g2 += y.value; nl += n.value
-                items += L.apus_cuda_moe_work_items(m, 0)
-            stats = (g13, g2, nl, items)
-        return h, ms_dec.value, prefill_ms, launches, out, (w0, w1), stats
+        ms = ms_dec.value
+        # plain-launch pass: kernels per step, and events around the expert GEMVs
+        moes = [L.apus_cuda_model_moe(h, i) for i in range(cfg.n_layers)]
+        kt = min(K, 16)
+        for m in moes:
+            L.apus_cuda_moe_timing(m, 1)
+            L.apus_cuda_moe_work_items(m, 1)
+        last = np.ascontiguousarray(out[:, -1:].astype(np.int64))
+        out2 = np.empty((batch, kt + 1), np.int32)
+        d0 = L.apus_cuda_dispatches()
+        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(last), 1, kt + 1, capi.ptr(out2), C.byref(ms_pre),
+                                                   C.byref(ms_dec)), "generate (event pass)")
+        per_step = (int(L.apus_cuda_dispatches() - d0)) // (kt + 1)
+        ms_plain = ms_dec.value / kt
+        g13 = g2 = 0.0
+        nl = items = 0
+        for m in moes:
+            x, y, n = C.c_double(), C.c_double(), C.c_int()
+            apus_b200.check(L.apus_cuda_moe_timing_read(m, C.byref(x), C.byref(y), C.byref(n)), "timing")
+            L.apus_cuda_moe_timing(m, 0)
+            g13 += x.value; g2 += y.value; nl += n.value
+            items += L.apus_cuda_moe_work_items(m, 0)
+        stats = (g13, g2, nl, items, kt, ms_plain)
+        return h, ms, prefill_ms, per_step * K, out2, (w0, w1), stats
 
     h32, ms, prefill_ms, launches, out, wall, stats = run(B, True)
     clocks = sampler.stop(*wall)
@@ -463,11 +470,12 @@ def model_main(a):
     L.apus_cuda_model_destroy(h32)
 
     # ---- batch 1 ------------------------------------------------------------------------------
-    h1, ms1, prefill1, launches1, out1, _, _ = run(1, False)
+    h1, ms1, prefill1, launches1, out1, _, st1 = run(1, False)
     L.apus_cuda_model_destroy(h1)
 
     peak, peak_kind = peak_hbm()
-    g13, g2, nl, items = stats
+    g13, g2, nl, items, kt, ms_plain = stats
+    ms_ev = ms_plain * (kt + 1)                  # time of the event pass, for the kernels' share of a step
     achieved = items * W13_BYTES / (g13 * 1e-3) / 1e9 if g13 > 0 else None
     achieved2 = items * W2_BYTES / (g2 * 1e-3) / 1e9 if g2 > 0 else None
     line = {
@@ -479,7 +487,7 @@ def model_main(a):
                 "steps": ne},
         "gpu_launches": launches,
         "batch1": {"value": 1 * K / (ms1 * 1e-3), "unit": "tok/s", "ms_per_step": ms1 / K,
-                   "gpu_launches": launches1, "prefill_ms": prefill1},
+                   "gpu_launches": launches1, "prefill_ms": prefill1, "ms_per_step_plain_launches": st1[5]},
         "prefill": {"tokens": B * a.prompt, "ms": prefill_ms, "tok_s": B * a.prompt / (prefill_ms * 1e-3),
                     "note": "prompt consumed as consecutive decode steps (no batched prefill kernel yet)"},
         "weights": {"bytes": W.bytes, "generate_s": t_gen},
@@ -493,9 +501,12 @@ def model_main(a):
                      "traffic_source": "ncu capture of a smaller case scaled by units (profiles/gemm_tc_mxfp4_pair_T32_E64.md)",
                      "launches": nl, "avg_launch_us": g13 / max(nl, 1) * 1e3,
                      "avg_unique_experts": items / max(nl, 1),
-                     "share_of_step": g13 / ms if ms > 0 else None,
+                     "share_of_step": g13 / ms_ev if ms_ev > 0 else None,
+                     "events": f"CUDA events around every launch in a pass of {kt} plain-launch steps right after the "
+                               "timed region (a replayed graph cannot carry readable events)",
                      "down_proj_kernel": {"achieved": achieved2, "frac": (achieved2 / peak) if achieved2 else None,
-                                          "avg_launch_us": g2 / max(nl, 1) * 1e3, "share_of_step": g2 / ms}},
+                                          "avg_launch_us": g2 / max(nl, 1) * 1e3, "share_of_step": g2 / ms_ev}},
+        "cuda_graph": {"replayed_steps": K, "ms_per_step_plain_launches": ms_plain},
     }
     if not a.no_cpu_baseline:
         os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 32)))

@@ -350,6 +350,7 @@ int apus_cuda_moe_use_tc(ApusCudaMoe *m, int enable);
  * dispatch counters (c/backend_metal.h:93-97) for roofline reporting.
  * _timing_read sums the elapsed milliseconds recorded since the last read. */
 void apus_cuda_moe_timing(ApusCudaMoe *m, int enable);
+int apus_cuda_moe_timing_enabled(const ApusCudaMoe *m);
 int apus_cuda_moe_timing_read(ApusCudaMoe *m, double *ms_gate_up,
                               double *ms_down, int *launches);
 /* Work items (one expert x up to 32 rows each) the expert kernels were launched
@@ -477,6 +478,12 @@ void apus_cuda_model_destroy(ApusCudaModel *m);
 /* c/model.h:485: back to position 0 with empty caches. */
 int apus_cuda_model_reset(ApusCudaModel *m);
 int64_t apus_cuda_model_pos(const ApusCudaModel *m);
+/* A decode step is the same sequence of launches at every position (the kernels
+ * read the position on the device), so apus_cuda_model_forward / _generate
+ * replay it from a CUDA graph after the first step (default on; it is bypassed
+ * while apus_cuda_moe_timing is enabled on a layer).  enable < 0 only queries.
+ * Returns the setting in force. */
+int apus_cuda_model_use_graph(ApusCudaModel *m, int enable);
 /* The MoE sublayer object of one layer (owned by the model), e.g. for
  * apus_cuda_moe_timing / apus_cuda_moe_use_tc. */
 ApusCudaMoe *apus_cuda_model_moe(ApusCudaModel *m, int layer);
