@@ -97,7 +97,31 @@ int ensure_enabled() {
     }
     APUS_CUDA_OK(cudaStreamCreateWithFlags(&c.own_stream, cudaStreamNonBlocking));
     c.stream = c.own_stream;
+    for (int i = 0; i < Ctx::N_AUX; i++) {
+        APUS_CUDA_OK(cudaStreamCreateWithFlags(&c.aux[i], cudaStreamNonBlocking));
+        APUS_CUDA_OK(cudaEventCreateWithFlags(&c.ev_fork[i], cudaEventDisableTiming));
+        APUS_CUDA_OK(cudaEventCreateWithFlags(&c.ev_join[i], cudaEventDisableTiming));
+    }
     c.enabled = true;
+    return 0;
+}
+
+cudaStream_t branch_begin(cudaStream_t main, int i) {
+    Ctx &c = ctx();
+    static const bool off = getenv("APUS_NO_BRANCH") && getenv("APUS_NO_BRANCH")[0] == '1';
+    if (off || i < 0 || i >= Ctx::N_AUX) return main;
+    if (cudaEventRecord(c.ev_fork[i], main) != cudaSuccess || cudaStreamWaitEvent(c.aux[i], c.ev_fork[i], 0) != cudaSuccess) {
+        cudaGetLastError();
+        return main;                            // no side stream: the chain simply runs in line
+    }
+    return c.aux[i];
+}
+int branch_end(int i, cudaStream_t main) {
+    Ctx &c = ctx();
+    static const bool off = getenv("APUS_NO_BRANCH") && getenv("APUS_NO_BRANCH")[0] == '1';
+    if (off || i < 0 || i >= Ctx::N_AUX) return 0;
+    APUS_CUDA_OK(cudaEventRecord(c.ev_join[i], c.aux[i]));
+    APUS_CUDA_OK(cudaStreamWaitEvent(main, c.ev_join[i], 0));
     return 0;
 }
 
@@ -320,6 +344,12 @@ void apus_cuda_disable(void) {
     c.stage.release();
     if (c.own_stream) cudaStreamDestroy(c.own_stream);
     c.stream = c.own_stream = nullptr;
+    for (int i = 0; i < Ctx::N_AUX; i++) {
+        if (c.aux[i]) cudaStreamDestroy(c.aux[i]);
+        if (c.ev_fork[i]) cudaEventDestroy(c.ev_fork[i]);
+        if (c.ev_join[i]) cudaEventDestroy(c.ev_join[i]);
+        c.aux[i] = nullptr; c.ev_fork[i] = c.ev_join[i] = nullptr;
+    }
     c.enabled = false;
 }
 

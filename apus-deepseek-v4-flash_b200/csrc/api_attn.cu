@@ -127,14 +127,17 @@ int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, St
     if (c.o_groups * c.o_lora > kmax) kmax = c.o_groups * c.o_lora;
     const size_t cdmax = 2 * (size_t)(c.head_dim > c.idx_dim ? c.head_dim : c.idx_dim);
     const size_t idxw = (size_t)c.window + (size_t)(c.has_indexer ? c.idx_topk : max_nb) + 8;
-    void *p[17];
-    size_t sz[17] = {(size_t)c.q_lora * 4, (size_t)c.q_lora * 4, (size_t)hd * 4, (size_t)c.head_dim * 4,
+    void *p[22];
+    size_t sz[22] = {(size_t)c.q_lora * 4, (size_t)c.q_lora * 4, (size_t)hd * 4, (size_t)c.head_dim * 4,
                      (size_t)c.head_dim * 4, (size_t)(c.idx_heads * c.idx_dim + 4) * 4, cdmax * 4, cdmax * 4,
                      cdmax * 4, (size_t)(c.idx_heads + 4) * 4, (size_t)(max_nb + 8) * 4, (size_t)hd * 4,
                      (size_t)c.o_groups * c.o_lora * 4, (size_t)kmax, (size_t)(kmax / 128 + 1) * 4,
-                     (size_t)(c.idx_topk + 8) * 4, idxw * 4};
-    for (int i = 0; i < 17; i++)
+                     (size_t)(c.idx_topk + 8) * 4, idxw * 4,
+                     (size_t)kmax, (size_t)(kmax / 128 + 1) * 4, cdmax * 4, cdmax * 4, cdmax * 4};
+    for (int i = 0; i < 22; i++)
         if (ws[i].get(sz[i] * B, &p[i])) return 1;
+    b->xq2 = (uint8_t *)p[17]; b->xs2 = (float *)p[18]; b->ckv2 = (float *)p[19]; b->csc2 = (float *)p[20];
+    b->pooled2 = (float *)p[21];
     b->qa = (float *)p[0]; b->qr = (float *)p[1]; b->q = (float *)p[2]; b->kva = (float *)p[3];
     b->kv = (float *)p[4]; b->iq = (float *)p[5]; b->ckv = (float *)p[6]; b->csc = (float *)p[7];
     b->pooled = (float *)p[8]; b->wt = (float *)p[9]; b->scores = (float *)p[10]; b->o = (float *)p[11];
@@ -146,8 +149,10 @@ int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, St
 // One compressor decode step of B sequences; appends a finished entry to every
 // cache when the block completes (reference c/attn.h:960-1008 + 797-819).
 static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, int B, int dim, long long pos,
-                           const float *cs_rp, const StepBufs &b, cudaStream_t st, const long long *pos_dev,
-                           const float *cs_table) {
+                           const float *cs_rp, const StepBufs &b0, cudaStream_t st, const long long *pos_dev,
+                           const float *cs_table, bool second_set = false) {
+    StepBufs b = b0;
+    if (second_set) { b.ckv = b0.ckv2; b.csc = b0.csc2; b.pooled = b0.pooled2; }
     const int cd = (1 + W.overlap) * W.d;
     if (f32_linear(W.wkv, x, b.ckv, B, dim, cd, 0, st) || f32_linear(W.wgate, x, b.csc, B, dim, cd, 0, st))
         return 1;
@@ -189,56 +194,74 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     if (pos_dev) cs_pos = cs_table;
     const int h = c.n_heads, d = c.head_dim, rd = c.rope_dim, win = c.window, ratio = c.ratio;
     const int hd = h * d;
+    // Independent chains of the step run on side streams and are joined before the
+    // gathered attention: (a) window KV, (b) the attention compressor, (c) the
+    // indexer with its own compressor; the q path stays on `st`.  Each chain has
+    // its own scratch.  The reference's order (indexer, ring write, compressor,
+    // attention; c/attn.h:1572-1665) only matters through the data each step
+    // reads, which the joins preserve.
+    if (act_quant(x, nullptr, B, c.dim, b.xq, b.xs, nullptr, st)) return 1;            // x codes: wq_a and wkv
+    cudaStream_t sa = branch_begin(st, 0);
+    if (qgemm_dev(A.wkv, nullptr, b.xq, b.xs, B, b.kva, true, 0.f, sa)) return 1;       // (a) c/attn.h:1552-1569
+    if (row_ops(b.kva, d, b.kv, d, B, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd,
+                cs_pos, B, 0, sa, dp))
+        return 1;
+    cudaStream_t sb = st;
+    if (ratio) {                                                                         // (b) c/attn.h:1660-1665
+        sb = branch_begin(st, 1);
+        if (compressor_step(A.comp, S.comp, x, B, c.dim, pos, cs_rp, b, sb, pos_dev, cs_table)) return 1;
+    }
     // q path (c/attn.h:1525-1548)
-    if (qlinear_dev(A.wq_a, x, b.qa, B, b.xq, b.xs, true, st)) return 1;
+    if (qgemm_dev(A.wq_a, nullptr, b.xq, b.xs, B, b.qa, true, 0.f, st)) return 1;
     if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st))
         return 1;
-    if (qlinear_dev(A.wq_b, b.qr, b.q, B, b.xq, b.xs, true, st)) return 1;
-    if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, B * h, 0, st, dp)) return 1;
-    // window KV (c/attn.h:1552-1569)
-    if (qlinear_dev(A.wkv, x, b.kva, B, b.xq, b.xs, true, st)) return 1;
-    if (row_ops(b.kva, d, b.kv, d, B, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd,
-                cs_pos, B, 0, st, dp))
-        return 1;
-    // compressed ids: the indexer runs BEFORE the ring write and the attention compressor
+    if (act_quant(b.qr, nullptr, B, c.q_lora, b.xq2, b.xs2, nullptr, st)) return 1;     // qr codes: wq_b and idx_wq_b
+    // compressed ids (c): the indexer
     int compw = 0;
     const int32_t *sel = nullptr;
+    cudaStream_t sc = st;
     if (ratio) {
         const long long nbs = (pos + 1) / ratio;
         if (c.has_indexer) {
             const int ih = c.idx_heads, idm = c.idx_dim;
-            if (qlinear_dev(A.idx_wq_b, b.qr, b.iq, B, b.xq, b.xs, true, st)) return 1;
+            sc = branch_begin(st, 2);
+            if (qgemm_dev(A.idx_wq_b, nullptr, b.xq2, b.xs2, B, b.iq, true, 0.f, sc)) return 1;
             if (row_ops(b.iq, idm, b.iq, idm, B * ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr,
-                        0.f, rd, cs_pos, B * ih, 0, st, dp))
+                        0.f, rd, cs_pos, B * ih, 0, sc, dp))
                 return 1;
-            if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, st, pos_dev, cs_table)) return 1;
-            if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, ih, APUS_CUDA_R_IN | APUS_CUDA_R_OUT, st)) return 1;
+            if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, sc, pos_dev, cs_table, true)) return 1;
+            if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, ih, APUS_CUDA_R_IN | APUS_CUDA_R_OUT, sc)) return 1;
             const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
             compw = (int)(c.idx_topk < nbs ? c.idx_topk : nbs);
             if (pos_dev) {                         // capacities; the live counts are derived on the device
                 compw = c.idx_topk < S.idx.cap ? c.idx_topk : S.idx.cap;
                 if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), (long long)S.idx.cap * idm, S.idx.cap, ih,
-                               idm, b.scores, B, st, pos_dev, ratio))
+                               idm, b.scores, B, sc, pos_dev, ratio))
                     return 1;
-                if (topk_stable(b.scores, S.idx.cap, compw, b.sel, B, st, pos_dev, ratio)) return 1;
+                if (topk_stable(b.scores, S.idx.cap, compw, b.sel, B, sc, pos_dev, ratio)) return 1;
                 sel = b.sel;
             } else if (compw > 0) {
                 if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), (long long)S.idx.cap * idm, nbs, ih, idm,
-                               b.scores, B, st))
+                               b.scores, B, sc))
                     return 1;
-                if (topk_stable(b.scores, (int)nbs, compw, b.sel, B, st)) return 1;
+                if (topk_stable(b.scores, (int)nbs, compw, b.sel, B, sc)) return 1;
                 sel = b.sel;
             }
         } else {
             compw = pos_dev ? S.comp.cap : (int)nbs;
         }
     }
+    if (qgemm_dev(A.wq_b, nullptr, b.xq2, b.xs2, B, b.q, true, 0.f, st)) return 1;
+    if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, B * h, 0, st, dp)) return 1;
+    // join the side chains: everything below reads what they produced
+    if (sa != st && branch_end(0, st)) return 1;
+    if (sb != st && branch_end(1, st)) return 1;
+    if (sc != st && branch_end(2, st)) return 1;
     if (idx_k_out) *idx_k_out = compw;
-    // ring write, attention compressor (c/attn.h:1642-1665)
+    // ring write (c/attn.h:1642-1658)
     if (scatter_rows(S.win.as<float>() + (pos_dev ? 0 : (size_t)(pos % win) * d), (long long)win * d, b.kv, d, B, st,
                      pos_dev, win))
         return 1;
-    if (ratio && compressor_step(A.comp, S.comp, x, B, c.dim, pos, cs_rp, b, st, pos_dev, cs_table)) return 1;
     // gathered attention over ring ++ compressed cache, inverse RoPE
     if (build_idx(b.idxs, win, pos, sel, compw, B, st, pos_dev, ratio)) return 1;
     const float scale = (float)pow((double)d, -0.5);
@@ -312,7 +335,7 @@ void attn_state_commit(const ApusAttnCfg &c, ApusAttnS *st, const StateDev &S) {
 namespace {
 
 StateDev g_state;
-DevBuf g_ws[24];
+DevBuf g_ws[30];
 
 void attn_release_all() {
     g_state.release();
@@ -357,8 +380,8 @@ int apus_cuda_attention(const ApusAttnCfg *cfg, const ApusAttnW *w, ApusAttnS *s
         }
     }
     void *dcs, *dx, *dout;
-    if (g_ws[17].get(cs.size() * 4, &dcs) || g_ws[18].get((size_t)s * cfg->dim * 4, &dx) ||
-        g_ws[19].get((size_t)s * cfg->dim * 4, &dout))
+    if (g_ws[22].get(cs.size() * 4, &dcs) || g_ws[23].get((size_t)s * cfg->dim * 4, &dx) ||
+        g_ws[24].get((size_t)s * cfg->dim * 4, &dout))
         return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(dcs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, sm));
     APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)s * cfg->dim * 4, cudaMemcpyHostToDevice, sm));
@@ -402,14 +425,14 @@ static int rows_host(float *x, int n, int rows, int flags, int rd, const float *
     if (rows <= 0) return 0;
     Ctx &c = ctx();
     void *dx, *dcs = nullptr;
-    if (g_ws[20].get((size_t)rows * n * 4, &dx)) return 1;
+    if (g_ws[25].get((size_t)rows * n * 4, &dx)) return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)rows * n * 4, cudaMemcpyHostToDevice, c.stream));
     if (cos) {
         const int half = rd / 2;
         std::vector<float> cs((size_t)rd);
         memcpy(cs.data(), cos, half * 4);
         memcpy(cs.data() + half, sin, half * 4);
-        if (g_ws[21].get((size_t)rd * 4, &dcs)) return 1;
+        if (g_ws[26].get((size_t)rd * 4, &dcs)) return 1;
         APUS_CUDA_OK(cudaMemcpyAsync(dcs, cs.data(), (size_t)rd * 4, cudaMemcpyHostToDevice, c.stream));
         APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
     }

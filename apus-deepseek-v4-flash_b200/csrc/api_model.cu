@@ -115,7 +115,7 @@ const float *rope_rows_dev(const float *cos, const float *sin, int rows, int hal
 }
 
 StateDev g_block_state;
-DevBuf g_block_ws[20], g_block_hb[10];
+DevBuf g_block_ws[24], g_block_hb[10];
 
 void model_release_all() {
     for (auto &kv : g_rope) { kv.second->release(); delete kv.second; }
@@ -164,7 +164,7 @@ struct ApusCudaModel {
     long long steps_run = 0;
     WeightOwner own;                       // every weight copy made for this model
     std::map<const void *, DevBuf *> rope; // rope rows by host table (layers of a kind share one)
-    DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, ws[20];
+    DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, ws[24];
     StepBufs sb;
 };
 
@@ -453,7 +453,7 @@ int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt, int n_prom
     for (int t = 0; t < n_prompt; t++)
         for (int b = 0; b < m->B; b++) cols[(size_t)t * m->B + b] = prompt[(size_t)b * n_prompt + t];
     void *dcols;
-    if (m->ws[18].get(cols.size() * 8, &dcols)) return 1;
+    if (m->ws[23].get(cols.size() * 8, &dcols)) return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(dcols, cols.data(), cols.size() * 8, cudaMemcpyHostToDevice, st));
     APUS_CUDA_OK(cudaEventRecord(e0, st));
     for (int t = 0; t < n_prompt; t++) {

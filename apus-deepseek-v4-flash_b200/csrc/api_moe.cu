@@ -38,7 +38,7 @@ struct ApusCudaMoe {
     int cap_s = 0, cap_r = 0;
     DevBuf b_logits, b_sp, b_biased, b_idx, b_wgt, b_xq, b_xs, b_routrow, b_spos, b_srow,
         b_g13, b_g2, b_ng, b_h, b_hq, b_hs, b_eo, b_shared, b_sh_h, b_sh_hq, b_sh_hs, b_ids,
-        b_tab;
+        b_tab, b_sh_xq, b_sh_xs;
     // optional per-kernel timing of the two expert GEMM launches
     bool timing = false;
     std::vector<cudaEvent_t> ev;
@@ -66,6 +66,7 @@ int ApusCudaMoe::ensure(int s, int n_rout) {
             b_wgt.get(S * topk * 4, nullptr) || b_shared.get(S * dim * 4, nullptr) ||
             b_sh_h.get(S * inter * 4, nullptr) || b_sh_hq.get(S * inter, nullptr) ||
             b_sh_hs.get(S * (inter / 128) * 4, nullptr) || b_ids.get(S * 8, nullptr) ||
+            b_sh_xq.get(S * dim, nullptr) || b_sh_xs.get(S * (dim / 128) * 4, nullptr) ||
             b_tab.get(S * topk * 8, nullptr))
             return 1;
         cap_s = s;
@@ -172,8 +173,9 @@ static int experts_run(ApusCudaMoe *m, const float *xrows, int n_rows, const int
 }
 
 static int shared_run(ApusCudaMoe *m, const float *x, int s, float *shared, cudaStream_t st) {
-    ExpertWs ws = {m->b_sh_h.as<float>(), m->b_xq.as<uint8_t>(), m->b_sh_hq.as<uint8_t>(),
-                   m->b_xs.as<float>(), m->b_sh_hs.as<float>()};
+    // own activation-code buffers: the shared expert may run beside the routed experts
+    ExpertWs ws = {m->b_sh_h.as<float>(), m->b_sh_xq.as<uint8_t>(), m->b_sh_hq.as<uint8_t>(),
+                   m->b_sh_xs.as<float>(), m->b_sh_hs.as<float>()};
     return expert_dev(&m->sw1, &m->sw2, &m->sw3, m->limit, x, s, shared, ws, st);
 }
 
@@ -198,12 +200,16 @@ static int forward_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const
     APUS_REQUIRE(m->e_lo == 0 && m->e_hi == m->E,
                  "moe_forward_dev needs all experts local (this handle holds [%d,%d) of %d)",
                  m->e_lo, m->e_hi, m->E);
+    // the shared expert depends only on x: it runs on a side stream beside the
+    // router and the routed experts and is joined before the combine
+    cudaStream_t ss = branch_begin(st, 0);
+    if (shared_run(m, x, s, m->b_shared.as<float>(), ss)) return 1;
     if (route_run(m, x, ids, table, s, m->b_idx.as<int32_t>(), m->b_wgt.as<float>(), nullptr, nullptr, st))
         return 1;
     if (experts_run(m, x, s, nullptr, m->b_idx.as<int32_t>(), R,
                     m->b_eo.as<float>(), st))
         return 1;
-    if (shared_run(m, x, s, m->b_shared.as<float>(), st)) return 1;
+    if (ss != st && branch_end(0, st)) return 1;
     return moe_combine(m->b_eo.as<float>(), m->b_wgt.as<float>(), m->b_shared.as<float>(), s,
                        m->topk, m->dim, out, routed, st);
 }
@@ -376,7 +382,7 @@ void apus_cuda_moe_destroy(ApusCudaMoe *m) {
     DevBuf *bufs[] = {&m->b_logits, &m->b_sp, &m->b_biased, &m->b_idx, &m->b_wgt, &m->b_xq, &m->b_xs,
                       &m->b_routrow, &m->b_spos, &m->b_srow, &m->b_g13, &m->b_g2, &m->b_ng, &m->b_h,
                       &m->b_hq, &m->b_hs, &m->b_eo, &m->b_shared, &m->b_sh_h, &m->b_sh_hq,
-                      &m->b_sh_hs, &m->b_ids, &m->b_tab, &m->b_t13, &m->b_t2};
+                      &m->b_sh_hs, &m->b_ids, &m->b_tab, &m->b_t13, &m->b_t2, &m->b_sh_xq, &m->b_sh_xs};
     for (DevBuf *b : bufs) b->release();
     for (cudaEvent_t e : m->ev) cudaEventDestroy(e);
     delete m;

@@ -35,6 +35,9 @@ struct StepBufs {
     uint8_t *xq;
     float *xs;
     int32_t *sel, *idxs;
+    // second set for the chains that run beside the main one (see attn_step)
+    uint8_t *xq2;
+    float *xs2, *ckv2, *csc2, *pooled2;
 };
 
 // Device copies that belong to one object (a model) instead of the global cache.

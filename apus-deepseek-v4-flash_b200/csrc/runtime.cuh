@@ -56,6 +56,11 @@ struct Ctx {
     int device = 0;
     cudaStream_t stream = nullptr;          // the stream every entry point without a stream argument uses
     cudaStream_t own_stream = nullptr;      // the one the library created (stream may be the caller's)
+    // side streams for independent kernel chains inside a step (joined back before
+    // the step goes on); each has an event for the fork and one for the join
+    static const int N_AUX = 3;
+    cudaStream_t aux[N_AUX] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_fork[N_AUX] = {nullptr, nullptr, nullptr}, ev_join[N_AUX] = {nullptr, nullptr, nullptr};
     uint64_t bytes_uploaded = 0;
     std::unordered_map<const void *, DevQW *> qcache;      // quantised weights by host codes ptr
     std::unordered_map<const void *, DevBuf *> dcache;     // dense weights by host ptr
@@ -65,6 +70,11 @@ struct Ctx {
 };
 Ctx &ctx();
 int ensure_enabled();
+// aux stream i starts after everything enqueued on `main` so far / `main` waits for
+// aux stream i.  Plain event dependencies, so they also work while `main` is
+// being captured into a graph (the side chain becomes a parallel branch).
+cudaStream_t branch_begin(cudaStream_t main, int i);
+int branch_end(int i, cudaStream_t main);
 // Files that keep device buffers outside Ctx register a release function
 // (run by apus_cuda_disable) and optionally a per-host-pointer one (run by
 // apus_cuda_forget).
@@ -82,6 +92,10 @@ bool is_device_ptr(const void *p);
 // `xq`/`xs` are caller workspaces of M*K bytes and M*K/128 floats.
 int qlinear_dev(DevQW *w, const float *x, float *out, int M, uint8_t *xq, float *xs,
                 bool round_out, cudaStream_t st);
+// Block-scaled GEMM of pre-quantised rows against one matrix, or a gate/up pair
+// with SwiGLU (`other` != NULL).
+int qgemm_dev(DevQW *w, DevQW *other, const uint8_t *acodes, const float *ascales, int M, float *out,
+              bool round_out, float limit, cudaStream_t st);
 // SwiGLU expert on device rows (MXFP4 or FP8 by the handles' fmt).
 struct ExpertWs { float *h; uint8_t *xq, *hq; float *xs, *hs; };
 int expert_dev(DevQW *w1, DevQW *w2, DevQW *w3, float limit, const float *x, int rows,
