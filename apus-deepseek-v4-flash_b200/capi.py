@@ -195,6 +195,8 @@ def load(path=LIB_PATH):
         "apus_cuda_model_ffn_input": (vp, [vp, ci]),
         "apus_cuda_model_ffn_output": (ci, [vp, ci, vp]),
         "apus_cuda_model_end_step": (ci, [vp, ci, ci]),
+        "apus_cuda_model_capturing": (ci, [vp, ci]),
+        "apus_cuda_model_note_step": (ci, [vp]),
         "apus_cuda_model_ids": (vp, [vp]),
         "apus_cuda_model_read": (ci, [vp, vp, vp]),
         "apus_cuda_model_destroy": (None, [vp]),

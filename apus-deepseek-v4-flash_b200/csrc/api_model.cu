@@ -161,6 +161,7 @@ struct ApusCudaModel {
     DevBuf pos_dev;
     cudaGraphExec_t gexec[2] = {nullptr, nullptr};
     bool use_graph = true;
+    bool capturing = false;               // the caller is recording a step into its own graph
     long long steps_run = 0;
     WeightOwner own;                       // every weight copy made for this model
     std::map<const void *, DevBuf *> rope; // rope rows by host table (layers of a kind share one)
@@ -493,7 +494,7 @@ int apus_cuda_model_begin_step(ApusCudaModel *m) {
 int apus_cuda_model_attn_half(ApusCudaModel *m, int layer) {
     if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_attn_half: bad layer"); return 1; }
     return block_attn_half(m->layers[layer], m->states[layer], &m->h_cur, &m->h_alt, m->B, m->pos, m->hc, m->iters,
-                           m->hc_eps, m->norm_eps, model_bufs(m), m->sb, ctx().stream);
+                           m->hc_eps, m->norm_eps, model_bufs(m), m->sb, ctx().stream, m->pos_dev.as<long long>());
 }
 const float *apus_cuda_model_ffn_input(ApusCudaModel *m, int layer) {
     if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_ffn_input: bad layer"); return nullptr; }
@@ -508,12 +509,30 @@ int apus_cuda_model_ffn_output(ApusCudaModel *m, int layer, const float *sub) {
 }
 int apus_cuda_model_end_step(ApusCudaModel *m, int want_logits, int feed_back) {
     if (!m) { set_error("NULL model"); return 1; }
-    m->pos++;
-    if (!want_logits) return 0;
-    if (model_head(m, ctx().stream)) return 1;
-    if (feed_back)
-        next_ids_kernel<<<1, 32, 0, ctx().stream>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), nullptr, m->B, 0, 1);
+    cudaStream_t st = ctx().stream;
+    if (want_logits) {
+        if (model_head(m, st)) return 1;
+        if (feed_back)
+            next_ids_kernel<<<1, 32, 0, st>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), nullptr, m->B, 0, 1);
+    }
+    advance_pos_kernel<<<1, 1, 0, st>>>(m->pos_dev.as<long long>());
+    APUS_LAUNCHED();
+    return m->capturing ? 0 : model_host_advance(m);
+}
+/* While the caller records a step into a CUDA graph of its own (stream capture on
+ * the stream given to apus_cuda_use_stream), the host-side position must not move:
+ * capturing(1) before, capturing(0) after; then, after every replay of that graph,
+ * note_step() moves the host-side position and entry counts like the step did on
+ * the device. */
+int apus_cuda_model_capturing(ApusCudaModel *m, int on) {
+    if (!m) return 1;
+    m->capturing = on != 0;
     return 0;
+}
+int apus_cuda_model_note_step(ApusCudaModel *m) {
+    if (!m) { set_error("NULL model"); return 1; }
+    APUS_REQUIRE(m->pos < m->max_pos, "model step: position %lld reaches max_pos %d", m->pos, m->max_pos);
+    return model_host_advance(m);
 }
 const int64_t *apus_cuda_model_ids(ApusCudaModel *m) { return m ? m->ids.as<int64_t>() : nullptr; }
 int apus_cuda_model_read(ApusCudaModel *m, float *logits, int32_t *next) {

@@ -96,25 +96,31 @@ mhc_mix_seq_kernel(const float *__restrict__ x4, const float *__restrict__ fn, i
     const bool p_on = one_word && !consumer && tid < total;
     const bool p_sq = c_lo + pc >= nmix;
     float4 f_next = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 x_next[TOK];
+#pragma unroll
+    for (int tk = 0; tk < TOK; tk++) x_next[tk] = make_float4(0.f, 0.f, 0.f, 0.f);
+    // the words of tile t: fn (one per thread) and the tokens' x, issued a whole
+    // iteration before they are multiplied
     auto fetch_fn = [&](int t) {
         const int gi = t * MIX_TI + 4 * pi4;
         f_next = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p_on && !p_sq && t < nt && gi < nx)
-            f_next = __ldg(reinterpret_cast<const float4 *>(fn + (size_t)(c_lo + pc) * nx + gi));
+        const bool in = p_on && t < nt && gi < nx;
+        if (in && !p_sq) f_next = __ldg(reinterpret_cast<const float4 *>(fn + (size_t)(c_lo + pc) * nx + gi));
+#pragma unroll
+        for (int tk = 0; tk < TOK; tk++) {
+            x_next[tk] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (in && tk < ntok) x_next[tk] = *reinterpret_cast<const float4 *>(x4 + (size_t)(row0 + tk) * nx + gi);
+        }
     };
     auto produce = [&](int t) {
         float *dst = s_prod + (size_t)(t & 1) * (TOK * MIX_CPG) * stride;
         if (one_word) {
             const float4 fcur = f_next;
-            fetch_fn(t + 1);                              // lands while tile t is multiplied and t - 1 consumed
-            if (!p_on) return;
-            const int gi = t * MIX_TI + 4 * pi4;
             float4 xv[TOK];
 #pragma unroll
-            for (int tk = 0; tk < TOK; tk++) {
-                xv[tk] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (tk < ntok && gi < nx) xv[tk] = *reinterpret_cast<const float4 *>(x4 + (size_t)(row0 + tk) * nx + gi);
-            }
+            for (int tk = 0; tk < TOK; tk++) xv[tk] = x_next[tk];
+            fetch_fn(t + 1);                              // lands while tile t is multiplied and t - 1 consumed
+            if (!p_on) return;
 #pragma unroll
             for (int tk = 0; tk < TOK; tk++) {
                 const float4 f = p_sq ? xv[tk] : fcur;

@@ -42,19 +42,48 @@ class EpModel:
         if not self.h:
             check(1, "apus_cuda_model_create_ep")
         self.moes = [ExpertParallelMoe(n_experts, topk, dim, rank, world, group,
-                                       handle=L.apus_cuda_model_moe(self.h, i)) for i in range(n_layers)]
+                                       handle=L.apus_cuda_model_moe(self.h, i), padded=True)
+                     for i in range(n_layers)]
         self.ids = dev_tensor(L.apus_cuda_model_ids(self.h), (batch,), torch.int64, device)
+        self.graph = None
 
     def close(self):
         if self.h:
             self.L.apus_cuda_model_destroy(self.h)
             self.h = None
 
+    def capture(self):
+        """Records one step (logits + feed-back) into a CUDA graph: the library's
+        kernels read the position on the device and the padded exchange has fixed
+        shapes, so the same graph serves every position.  Call after at least one
+        plain step (workspaces are allocated by then)."""
+        L, h = self.L, self.h
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        check(L.apus_cuda_use_stream(side.cuda_stream, 0), "use_stream")      # synchronises outside the capture
+        g = torch.cuda.CUDAGraph()
+        check(L.apus_cuda_model_capturing(h, 1), "capturing")
+        try:
+            with torch.cuda.graph(g, stream=side):
+                self._enqueue(True, True)
+        finally:
+            L.apus_cuda_model_capturing(h, 0)
+            torch.cuda.current_stream().wait_stream(side)
+            check(L.apus_cuda_use_stream(torch.cuda.current_stream().cuda_stream, 0), "use_stream")
+        self.graph = g
+
     def step(self, want_logits=True, feed_back=True):
         """One position of every sequence.  The ids of the step are whatever
         set_ids / the previous step's feed-back left on the device."""
+        if self.graph is not None and want_logits and feed_back:
+            self.graph.replay()
+            check(self.L.apus_cuda_model_note_step(self.h), "note_step")
+            return
+        check(self.L.apus_cuda_use_stream(torch.cuda.current_stream().cuda_stream, 0), "use_stream")
+        self._enqueue(want_logits, feed_back)
+
+    def _enqueue(self, want_logits, feed_back):
         L, h = self.L, self.h
-        check(L.apus_cuda_use_stream(torch.cuda.current_stream().cuda_stream, 0), "use_stream")
         check(L.apus_cuda_model_begin_step(h), "begin_step")
         for i in range(self.n_layers):
             check(L.apus_cuda_model_attn_half(h, i), "attn_half")

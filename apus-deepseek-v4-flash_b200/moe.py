@@ -60,11 +60,12 @@ class ExpertParallelMoe:
     exercise the exchange logic over gloo."""
 
     def __init__(self, n_experts, topk, dim, rank=0, world=1, group=None, handle=None,
-                 experts_fn=None, route_fn=None, shared_fn=None, combine_fn=None):
+                 experts_fn=None, route_fn=None, shared_fn=None, combine_fn=None, padded=False):
         assert n_experts % world == 0, "experts must divide evenly over the ranks"
         self.E, self.topk, self.dim = n_experts, topk, dim
         self.rank, self.world, self.group = rank, world, group
         self.handle = handle
+        self.padded = padded
         self.e_lo = rank * (n_experts // world)
         self.e_hi = self.e_lo + n_experts // world
         self.experts_fn = experts_fn or self._experts_cuda
@@ -115,6 +116,8 @@ class ExpertParallelMoe:
     def forward(self, x, ids=None):
         """x [s, dim] f32 (BF16-valued) on this rank's device -> out [s, dim]."""
         s = x.shape[0]
+        if self.padded and (self.world > 1 or dist.is_initialized()):
+            return self.forward_padded(x, ids)
         idx, wgt = self.route_fn(x, ids)
         if self.world == 1:
             rows = torch.arange(s, device=x.device).repeat_interleave(self.topk)
@@ -138,6 +141,41 @@ class ExpertParallelMoe:
         dist.all_to_all_single(eo_back, eo_recv, sc, rc, group=self.group)
         eo = torch.empty_like(eo_back)
         eo[order] = eo_back                              # back to (t, j) order
+        return self.combine_fn(eo, wgt, shared)
+
+
+    def forward_padded(self, x, ids=None):
+        """The same exchange with fixed shapes and no host synchronisation: every
+        (source, destination) pair carries `s * topk` row slots (the worst case),
+        unused slots hold expert id -1, which the expert kernels skip.  All ranks
+        must bring the same number of tokens.  Nothing here depends on device
+        values on the host, so a whole step can be captured into a CUDA graph."""
+        s, W, dim = x.shape[0], self.world, self.dim
+        idx, wgt = self.route_fn(x, ids)
+        R = s * self.topk
+        C = R                                            # slots per destination
+        flat = idx.reshape(-1).long()
+        dest = owner_ranks(flat, self.E, W)
+        order = torch.argsort(dest, stable=True)
+        dest_s = dest[order]
+        ranks = torch.arange(W, device=x.device)
+        counts = (dest_s[:, None] == ranks[None, :]).sum(0)
+        starts = torch.cumsum(counts, 0) - counts
+        slot = dest_s * C + (torch.arange(R, device=x.device) - starts[dest_s])
+        send_rows = torch.zeros(W * C, dim, dtype=x.dtype, device=x.device)
+        send_eids = torch.full((W * C,), -1, dtype=idx.dtype, device=x.device)
+        send_rows[slot] = x[torch.div(order, self.topk, rounding_mode="floor")]
+        send_eids[slot] = idx.reshape(-1)[order]
+        recv_rows = torch.empty_like(send_rows)
+        recv_eids = torch.empty_like(send_eids)
+        dist.all_to_all_single(recv_rows, send_rows, group=self.group)
+        dist.all_to_all_single(recv_eids, send_eids, group=self.group)
+        shared = self.shared_fn(x)
+        eo_recv = self.experts_fn(recv_rows, recv_eids).contiguous()
+        eo_back = torch.empty_like(eo_recv)
+        dist.all_to_all_single(eo_back, eo_recv, group=self.group)
+        eo = torch.empty(R, dim, dtype=x.dtype, device=x.device)
+        eo[order] = eo_back[slot]                        # back to (t, j) order
         return self.combine_fn(eo, wgt, shared)
 
 

@@ -295,7 +295,9 @@ def model_main_ep(a):
     assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    if "MASTER_ADDR" not in os.environ:                   # single process (one-rank test of this loop)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", RANK="0", WORLD_SIZE="1")
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
     apus_b200.build()
     L = apus_b200.lib()
     err = C.create_string_buffer(512)
@@ -304,7 +306,7 @@ def model_main_ep(a):
     cfg = flash_config(a)
     B, K, Wm = a.batch, a.steps, a.warmup
     per = cfg.n_experts // world
-    max_pos = a.prompt + 2 * (K + Wm) + 72
+    max_pos = a.prompt + 2 * (K + Wm) + 80
     W = RandomFlashModel(cfg, a.seed, dev, e_lo=rank * per, e_hi=(rank + 1) * per, max_pos=max_pos)
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
@@ -317,17 +319,38 @@ def model_main_ep(a):
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
+    def mark(msg):
+        if os.environ.get("APUS_BENCH_TRACE"):
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    mark("prefill")
     e0.record()
     ep.prefill(prompt)
     e1.record()
     torch.cuda.synchronize()
     prefill_ms = e0.elapsed_time(e1)
+    mark("warm-up steps")
     for _ in range(Wm):
         ep.step()
+    torch.cuda.synchronize()
+    mark("warm-up done")
     d0 = L.apus_cuda_dispatches()
+    ep.step()
+    per_step = int(L.apus_cuda_dispatches() - d0)       # kernels of one step, counted on plain launches
+    graph_note = "each step replayed from one CUDA graph (library kernels + NCCL all-to-alls)"
+    if os.environ.get("APUS_EP_GRAPH", "1") != "0":
+        try:
+            ep.capture()
+        except Exception as e:                          # keep going on plain launches
+            graph_note = f"plain launches (graph capture failed: {type(e).__name__}: {e})"
+            torch.cuda.synchronize()
+    else:
+        graph_note = "plain launches"
+    mark(graph_note)
+    ep.step()
     barrier()
+    mark("timed region")
     w0 = time.time()
     e0.record()
     for _ in range(K):
@@ -335,7 +358,7 @@ def model_main_ep(a):
     e1.record()
     barrier()
     w1 = time.time()
-    launches = int(L.apus_cuda_dispatches() - d0)
+    launches = per_step * K
     tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(tms, op=dist.ReduceOp.MAX)
     ms = float(tms.item())
@@ -367,15 +390,22 @@ def model_main_ep(a):
             "gpu_launches": launches,
             "prefill": {"tokens": world * B * a.prompt, "ms": prefill_ms,
                         "note": "prompt consumed as consecutive decode steps"},
-            "roofline": None, "weights": {"bytes_per_rank": W.bytes},
+            "roofline": None, "weights": {"bytes_per_rank": W.bytes}, "cuda_graph": graph_note,
             "note": "expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine per layer; "
                     "the per-kernel roofline is reported by the 1-GPU run"}
         print(json.dumps(line), flush=True)
-    dist.destroy_process_group()
+    # a captured graph holds NCCL work; release it and leave without tearing the
+    # communicator down (destroying the group with such graphs alive can block)
+    ep.graph = None
+    barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def model_main(a):
-    if a.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    # APUS_EP_TEST=1: run the expert-parallel loop (padded exchange, graph capture) with one rank
+    if a.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1 or os.environ.get("APUS_EP_TEST") == "1":
         return model_main_ep(a)
     import torch
     import apus_b200

@@ -517,6 +517,14 @@ int apus_cuda_model_attn_half(ApusCudaModel *m, int layer);
 const float *apus_cuda_model_ffn_input(ApusCudaModel *m, int layer);
 int apus_cuda_model_ffn_output(ApusCudaModel *m, int layer, const float *sub);
 int apus_cuda_model_end_step(ApusCudaModel *m, int want_logits, int feed_back);
+/* The pieces read the position on the device, so a caller may record one whole
+ * step (its own collectives included) into a CUDA graph by stream capture on the
+ * stream given to apus_cuda_use_stream: capturing(1) before the recording,
+ * capturing(0) after it (the recorded calls must not move the host-side
+ * position), and note_step() after every replay, which moves the host-side
+ * position and entry counts like the replayed step did on the device. */
+int apus_cuda_model_capturing(ApusCudaModel *m, int on);
+int apus_cuda_model_note_step(ApusCudaModel *m);
 const int64_t *apus_cuda_model_ids(ApusCudaModel *m);
 int apus_cuda_model_read(ApusCudaModel *m, float *logits, int32_t *next);
 

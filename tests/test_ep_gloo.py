@@ -38,15 +38,16 @@ def fake_combine(eo, wgt, shared):
     return y + shared
 
 
-def make(rank, world, check_local=None):
+def make(rank, world, check_local=None, padded=False):
     lo, hi = rank * (E // world), (rank + 1) * (E // world)
 
     def experts(rows, eids):
         if check_local is not None:
-            assert bool(((eids >= lo) & (eids < hi)).all()), "routing reached the wrong rank"
+            live = eids >= 0                   # -1 = unused slot of the padded exchange
+            assert bool(((eids[live] >= lo) & (eids[live] < hi)).all()), "routing reached the wrong rank"
         return fake_expert(rows, eids)
     return ExpertParallelMoe(E, TOPK, DIM, rank, world, experts_fn=experts, route_fn=fake_route,
-                             shared_fn=lambda x: x * 0.5, combine_fn=fake_combine)
+                             shared_fn=lambda x: x * 0.5, combine_fn=fake_combine, padded=padded)
 
 
 def worker(rank, world, port, q):
@@ -61,6 +62,10 @@ def worker(rank, world, port, q):
     x0 = torch.randn(0 if rank == 1 else 3, DIM)
     out0 = make(rank, world).forward(x0)
     q.put((rank, out0.shape[0] == x0.shape[0]))
+    # fixed-shape exchange (equal batches): same result as a single rank, bit for bit
+    xp = torch.randn(6, DIM)
+    outp = make(rank, world, check_local=True, padded=True).forward(xp)
+    q.put((rank, bool(torch.equal(outp, make(0, 1).forward(xp)))))
     dist.destroy_process_group()
 
 
@@ -86,5 +91,5 @@ def test_expert_parallel_exchange_world2():
     for p in procs:
         p.join(timeout=180)
         assert p.exitcode == 0
-    res = [q.get(timeout=10) for _ in range(4)]
+    res = [q.get(timeout=10) for _ in range(6)]
     assert all(ok for _, ok in res), res
