@@ -9,7 +9,7 @@
 // `tcgen05.mma kind::f8f6f4` (K = 32) accumulating in tensor memory; the
 // finished 128 x 32 block is read back (`tcgen05.ld`) by the epilogue warps and
 // folded into f32 registers with that block's scales while the tensor core
-// works on the next block in the other of two accumulators.  The fold order is
+// works on the next blocks in the other accumulators of a ring of four.  The fold order is
 // therefore the reference's, for any K, with no split along K.
 //
 // Weights are read in the reference storage ([O, K] bytes, scales
@@ -22,7 +22,7 @@
 //   warp 5      MMA issuer; owns the tensor-memory allocation
 //   warps 0-3   per block: TMEM -> registers, fold with the scales; final epilogue
 // mbarriers: full[s] / empty[s] for the shared-memory ring, acc_full[b] /
-// acc_empty[b] for the two accumulators.  Every wait is bounded; on expiry
+// acc_empty[b] for the ring of four accumulators.  Every wait is bounded; on expiry
 // the CTA records a status word, drains and frees its tensor memory.
 #include "kernels.cuh"
 #include "tc_common.cuh"
@@ -69,11 +69,14 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int STAGE = T8_A_BYTES * (PAIR ? 2 : 1) + T8_B_BYTES;
-    constexpr int NACC = PAIR ? 4 : 2;               // accumulators of 32 columns each
-    constexpr int TMEM_COLS = PAIR ? 128 : 64;
+    // ring of NACC accumulators (32 columns each; a pair uses two rings): the
+    // MMA -> fold -> MMA round trip through the barriers takes longer than one
+    // block's MMAs, so two accumulators leave the tensor core waiting
+    constexpr int NACC = 4;
+    constexpr int TMEM_COLS = PAIR ? 256 : 128;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)NS * STAGE);
-    uint64_t *full = bars, *empty = bars + NS, *acc_full = bars + 2 * NS, *acc_empty = bars + 2 * NS + 2;
-    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 2 * NS + 4);
+    uint64_t *full = bars, *empty = bars + NS, *acc_full = bars + 2 * NS, *acc_empty = bars + 2 * NS + NACC;
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 2 * NS + 2 * NACC);
     volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
     float *s_as = reinterpret_cast<float *>(s_tmem + 4);          // [NC][T8_N] activation scales
     const int K = a.K, O = a.O, NC = K >> 7, M = a.M;
@@ -86,7 +89,7 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 
     if (tid == 0) {
         for (int s = 0; s < NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        for (int b = 0; b < NACC; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -128,12 +131,12 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             }
         }
     } else if (warp == 5) {
-        // ---- MMA issuer: block i accumulates into accumulator i & 1 ---------------------
+        // ---- MMA issuer: block i accumulates into accumulator i % NACC -------------------
         if (lane == 0) {
             const uint32_t idesc = idesc_f8();
             for (int i = 0; i < NC && !fail; i++) {
-                const int s = i % NS, b = i & 1;
-                const uint32_t ph = (uint32_t)(i / NS) & 1u, pb = (uint32_t)(i >> 1) & 1u;
+                const int s = i % NS, b = i % NACC;
+                const uint32_t ph = (uint32_t)(i / NS) & 1u, pb = (uint32_t)(i / NACC) & 1u;
                 if (!mbar_wait(&acc_empty[b], pb ^ 1u, s_abort)) { fail = 12; break; }
                 if (!mbar_wait(&full[s], ph, s_abort)) { fail = 13; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -144,7 +147,7 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     umma_f8(tmem + b * 32, da + 2 * j, dx + 2 * j, idesc, j ? 1u : 0u);
-                    if (PAIR) umma_f8(tmem + 64 + b * 32, db + 2 * j, dx + 2 * j, idesc, j ? 1u : 0u);
+                    if (PAIR) umma_f8(tmem + NACC * 32 + b * 32, db + 2 * j, dx + 2 * j, idesc, j ? 1u : 0u);
                 }
                 umma_commit(&empty[s]);                // the stage may be refilled once these MMAs retire
                 umma_commit(&acc_full[b]);             // ... and the block is ready for the fold
@@ -161,13 +164,13 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             for (int n = 0; n < T8_N; n++) accB[n] = 0.f;
         }
         for (int i = 0; i < NC && !fail; i++) {
-            const int b = i & 1;
-            const uint32_t pb = (uint32_t)(i >> 1) & 1u;
+            const int b = i % NACC;
+            const uint32_t pb = (uint32_t)(i / NACC) & 1u;
             if (!mbar_wait(&acc_full[b], pb, s_abort)) { fail = 14; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t d0[32], d1[32];
             tmem_ld32(tmem + lane_base + b * 32, d0);
-            if (PAIR) tmem_ld32(tmem + lane_base + 64 + b * 32, d1);
+            if (PAIR) tmem_ld32(tmem + lane_base + NACC * 32 + b * 32, d1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&acc_empty[b]);                // the tensor core may overwrite this accumulator

@@ -12,6 +12,8 @@
 //      collapsed row in the same kernel (reference c/attn.h:371-378).
 // Bytes per token: fn (nmix*n*d*4, L2-resident across tokens) + 2 reads of the
 // n*d state.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -365,7 +367,8 @@ static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float 
         attr_set = true;
     }
     const unsigned gy = (unsigned)((C + MIX_CPG - 1) / MIX_CPG);
-    if (rows >= 4) {                          // eight tokens share a CTA and its read of fn
+    static const int force_single = getenv("APUS_MIX_SINGLE") ? atoi(getenv("APUS_MIX_SINGLE")) : 0;
+    if (rows >= 4 && !force_single) {         // eight tokens share a CTA and its read of fn
         const int ti = 256;
         const size_t smem = (size_t)2 * 8 * MIX_CPG * (ti + 4) * sizeof(float);
         mhc_mix_seq_kernel<8><<<dim3((unsigned)((rows + 7) / 8), gy), 288, smem, st>>>(x4, fn, nx, nmix, ti, rows, raw);

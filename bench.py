@@ -51,8 +51,9 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--batches", type=int, default=8, help="distinct activation batches cycled")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default=None, choices=["model", "moe_layer"],
-                    help="model: full 43-layer token loop (default on 1 GPU); moe_layer: one MoE sublayer")
+    ap.add_argument("--workload", default=None, choices=["model", "moe_layer", "fp8_gemm"],
+                    help="model: full 43-layer token loop (default); moe_layer: one MoE sublayer (config 2); "
+                         "fp8_gemm: the FP8 dense GEMM of config 1 (W [4096,4096], M = 1, 32, 512, 4096)")
     ap.add_argument("--batch", type=int, default=32, help="model workload: sequences decoded in lockstep")
     ap.add_argument("--prompt", type=int, default=512, help="model workload: prompt tokens per sequence")
     ap.add_argument("--layers", type=int, default=43, help="model workload: layers (43 = the real model)")
@@ -546,9 +547,60 @@ def model_main(a):
     print(json.dumps(line), flush=True)
 
 
+# ---- config 1: FP8 E4M3 block-scaled dense GEMM ------------------------------------------------
+def fp8_gemm_main(a):
+    """W [4096, 4096] E4M3 with 128x128 UE8M0 tile scales, activations [M, 4096] quantised per
+    token per 128 (act quant + tcgen05 kernel + BF16 round = apus_fp8_linear), device resident."""
+    import torch
+    import apus_b200
+    from apus_b200 import capi, synth
+    torch.cuda.set_device(0)
+    apus_b200.build()
+    L = apus_b200.lib()
+    err = C.create_string_buffer(512)
+    if L.apus_cuda_enable(err, 512):
+        raise RuntimeError(err.value.decode())
+    O = K = 4096
+    rng = np.random.default_rng(a.seed)
+    codes, scales = synth.fp8_weight(rng, O, K)
+    qw = capi.qw(codes, scales, O, K)
+    h = L.apus_cuda_fp8_upload(C.byref(qw))
+    if not h:
+        apus_b200.check(1, "fp8_upload")
+    peak, peak_kind = peak_hbm()
+    res = {}
+    stream = torch.cuda.current_stream().cuda_stream
+    for M in (1, 32, 512, 4096):
+        x = torch.from_numpy(synth.activations(rng, M, K)).cuda()
+        out = torch.empty(M, O, device="cuda")
+        for _ in range(max(a.warmup, 3)):
+            apus_b200.check(L.apus_cuda_fp8_linear_dev(h, x.data_ptr(), out.data_ptr(), M, stream), "fp8_linear_dev")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        tot = 0.0
+        n = min(a.steps, 50)
+        for _ in range(n):
+            flush.zero_()                                  # 256 MB write: evicts the 126 MB L2
+            e0.record()
+            apus_b200.check(L.apus_cuda_fp8_linear_dev(h, x.data_ptr(), out.data_ptr(), M, stream), "fp8_linear_dev")
+            e1.record()
+            e1.synchronize()
+            tot += e0.elapsed_time(e1)
+        us = tot / n * 1e3
+        res[str(M)] = {"us": us, "weight_GBs": (O * K + (O // 128) * (K // 128)) / us / 1e3,
+                       "TFLOPs": 2.0 * M * O * K / us / 1e6}
+    line = {"metric": "fp8_dense_gemm_us", "workload": "config1: FP8 E4M3 block-scaled GEMM, W [4096,4096]",
+            "n_gpus": 1, "results_by_M": res, "hbm_peak_GBs": peak, "peak_kind": peak_kind,
+            "note": "act quant + gemm_tc8_kernel + BF16 round per call; L2 flushed between timed calls; "
+                    "M > 32 runs as 32-row work items (weights re-read from L2)"}
+    print(json.dumps(line), flush=True)
+
+
 # ---- this repository's arm (one MoE sublayer) --------------------------------------------------
 def main():
     a = parse()
+    if a.workload == "fp8_gemm":
+        return fp8_gemm_main(a)
     if a.workload == "model":
         return model_reference_arm(a) if a.impl == "reference" else model_main(a)
     if a.impl == "reference":
