@@ -12,8 +12,6 @@
 //      collapsed row in the same kernel (reference c/attn.h:371-378).
 // Bytes per token: fn (nmix*n*d*4, L2-resident across tokens) + 2 reads of the
 // n*d state.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -362,16 +360,19 @@ static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float 
     static bool attr_set = false;
     if (!attr_set) {
         APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
         APUS_CUDA_OK(cudaFuncSetAttribute(mhc_pre_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
         attr_set = true;
     }
     const unsigned gy = (unsigned)((C + MIX_CPG - 1) / MIX_CPG);
-    static const int force_single = getenv("APUS_MIX_SINGLE") ? atoi(getenv("APUS_MIX_SINGLE")) : 0;
-    if (rows >= 4 && !force_single) {         // eight tokens share a CTA and its read of fn
-        const int ti = 256;
-        const size_t smem = (size_t)2 * 8 * MIX_CPG * (ti + 4) * sizeof(float);
-        mhc_mix_seq_kernel<8><<<dim3((unsigned)((rows + 7) / 8), gy), 288, smem, st>>>(x4, fn, nx, nmix, ti, rows, raw);
+    if (rows >= 2) {
+        // two tokens share a CTA and its read of fn (measured at batch 32: 2 tokens per CTA
+        // beat 1, 4 and 8 by a few percent -- more tokens per CTA load the shared-memory
+        // pipe with products and slow every chain down)
+        const int tok = 2, ti = 256;
+        const size_t smem = (size_t)2 * tok * MIX_CPG * (ti + 4) * sizeof(float);
+        const dim3 grid((unsigned)((rows + tok - 1) / tok), gy);
+        mhc_mix_seq_kernel<2><<<grid, 288, smem, st>>>(x4, fn, nx, nmix, ti, rows, raw);
     } else {
         const int ti = 1024;
         const size_t smem = (size_t)2 * MIX_CPG * (ti + 4) * sizeof(float);
