@@ -204,6 +204,8 @@ def load(path=LIB_PATH):
         "apus_cuda_model_pos": (i64, [vp]),
         "apus_cuda_model_moe": (vp, [vp, ci]),
         "apus_cuda_model_use_graph": (ci, [vp, ci]),
+        "apus_cuda_model_set_sampling": (ci, [vp, cf, cf, C.c_uint64]),
+        "apus_cuda_sample_logits_u": (ci, [vp, C.c_size_t, cf, cf, vp, vp, ci]),
         "apus_cuda_moe_timing_enabled": (ci, [vp]),
         "apus_cuda_moe_work_items": (C.c_longlong, [vp, ci]),
         "apus_cuda_model_forward": (ci, [vp, vp, ci, vp, vp]),

@@ -324,6 +324,27 @@ int apus_cuda_use_stream(void *stream, int use_own) {
     return 0;
 }
 
+int apus_cuda_sample_logits_u(const float *logits, size_t n, float temp, float top_p, const double *u,
+                              int32_t *tokens, int rows) {
+    if (ensure_enabled()) return 1;
+    if (rows <= 0) return 0;
+    Ctx &c = ctx();
+    void *dl, *dp, *du, *dt;
+    if (c.ws[0].get((size_t)rows * n * 4, &dl) || c.ws[1].get((size_t)rows * n * 4, &dp) ||
+        c.ws[2].get((size_t)rows * 8, &du) || c.ws[3].get((size_t)rows * 4, &dt))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dl, logits, (size_t)rows * n * 4, cudaMemcpyHostToDevice, c.stream));
+    if (temp > 0.f) {
+        APUS_REQUIRE(u != nullptr, "sample_logits_u: no uniforms given");
+        APUS_CUDA_OK(cudaMemcpyAsync(du, u, (size_t)rows * 8, cudaMemcpyHostToDevice, c.stream));
+    }
+    if (sample_rows((float *)dl, (int)n, rows, temp, top_p, (double *)du, nullptr, (float *)dp, (int32_t *)dt, c.stream))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(tokens, dt, (size_t)rows * 4, cudaMemcpyDeviceToHost, c.stream));
+    APUS_CUDA_OK(cudaStreamSynchronize(c.stream));
+    return 0;
+}
+
 int apus_cuda_set_sum_order(int order) {
     if (order == APUS_CUDA_SUM_REFERENCE || order == APUS_CUDA_SUM_TREE) apus::g_sum_order = order;
     return apus::g_sum_order;

@@ -160,6 +160,10 @@ struct ApusCudaModel {
     // CUDA graph (one with the head, one without) after the first step ran eagerly
     DevBuf pos_dev;
     cudaGraphExec_t gexec[2] = {nullptr, nullptr};
+    // sampling (temp <= 0: greedy argmax): per-sequence splitmix64 states and the
+    // probability scratch live on the device
+    float temp = 0.f, top_p = 1.f;
+    DevBuf rng, probs;
     bool use_graph = true;
     bool capturing = false;               // the caller is recording a step into its own graph
     long long steps_run = 0;
@@ -186,6 +190,9 @@ static int model_head(ApusCudaModel *m, cudaStream_t st) {
     if (f32_linear(m->head, m->yn.as<float>(), m->logits.as<float>(), B, dim, m->vocab,
                    m->head_bf16 ? APUS_CUDA_W_BF16 : 0, st))
         return 1;
+    if (m->temp > 0.f)                                   // c/sample.h:173-178; greedy otherwise (c/sample.h:76-81)
+        return sample_rows(m->logits.as<float>(), m->vocab, B, m->temp, m->top_p, nullptr,
+                           m->rng.as<unsigned long long>(), m->probs.as<float>(), m->tok.as<int32_t>(), st);
     return argmax_rows(m->logits.as<float>(), m->vocab, B, m->tok.as<int32_t>(), st);
 }
 __global__ void advance_pos_kernel(long long *pos) { *pos += 1; }
@@ -270,6 +277,7 @@ void apus_cuda_model_destroy(ApusCudaModel *m) {
     for (auto &s : m->states) s.release();
     for (int i = 0; i < 2; i++) if (m->gexec[i]) cudaGraphExecDestroy(m->gexec[i]);
     m->pos_dev.release();
+    m->rng.release(); m->probs.release();
     for (auto &L : m->layers) if (L.moe) apus_cuda_moe_destroy(L.moe);
     m->own.release();
     for (auto &kv : m->rope) { kv.second->release(); delete kv.second; }
@@ -407,6 +415,22 @@ int apus_cuda_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float
 }
 
 int64_t apus_cuda_model_pos(const ApusCudaModel *m) { return m ? m->pos : -1; }
+
+int apus_cuda_model_set_sampling(ApusCudaModel *m, float temp, float top_p, uint64_t seed) {
+    if (!m) { set_error("NULL model"); return 1; }
+    cudaStream_t st = ctx().stream;
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    for (int i = 0; i < 2; i++)                       // the head of a recorded step changes
+        if (m->gexec[i]) { cudaGraphExecDestroy(m->gexec[i]); m->gexec[i] = nullptr; }
+    m->temp = temp; m->top_p = top_p;
+    if (temp <= 0.f) return 0;
+    if (m->rng.get((size_t)m->B * 8, nullptr) || m->probs.get((size_t)m->B * m->vocab * 4, nullptr)) return 1;
+    std::vector<unsigned long long> s((size_t)m->B);
+    for (int b = 0; b < m->B; b++) s[b] = seed + (unsigned long long)b;
+    APUS_CUDA_OK(cudaMemcpyAsync(m->rng.p, s.data(), s.size() * 8, cudaMemcpyHostToDevice, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    return 0;
+}
 
 int apus_cuda_model_use_graph(ApusCudaModel *m, int enable) {
     if (!m) return -1;

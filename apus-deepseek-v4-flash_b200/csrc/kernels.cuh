@@ -95,6 +95,10 @@ int gemm_tc8(const Tc8Args &a, cudaStream_t st);
 int gemm_tc8_status(int reset);
 int tc8_make_weight_map(void *out_map, const void *codes, long long rows, int K);
 
+// ---- temperature / top-p sampling (sample.cu; reference c/sample.h) ------------------------
+int sample_rows(const float *logits, int n, int rows, float temp, float top_p, const double *u,
+                unsigned long long *rng, float *probs, int32_t *out, cudaStream_t st);
+
 // ---- dense f32 / bf16 linears (linear.cu) ------------------------------------------------
 // out[m,o] = sum_k x[m,k]*w[o,k]; flags as APUS_CUDA_R_IN/R_OUT/W_BF16.
 int f32_linear(const void *w, const float *x, float *out, int M, int K, int O,

@@ -204,6 +204,13 @@ void apus_cuda_forget(const void *host_ptr);
 
 /* ---- host-pointer tier: kernel-level entry points ------------------------- */
 
+/* c/sample.h:66-67 apus_sample_logits_u for `rows` rows: logits [rows, n], one
+ * explicit uniform u[row] in [0, 1) per row (unused when temp <= 0: greedy),
+ * tokens [rows].  The nucleus walk over the sorted probabilities is a weighted
+ * selection on the device (no sort); see csrc/sample.cu. */
+int apus_cuda_sample_logits_u(const float *logits, size_t n, float temp, float top_p,
+                              const double *u, int32_t *tokens, int rows);
+
 /* c/backend_metal.h:102 apus_metal_fp8_linear == c/attn.h:408 apus_fp8_linear:
  * BF16-round x, per-128 act quant, block-scaled FP8 GEMM, BF16-rounded out. */
 int apus_cuda_fp8_linear(const ApusFp8W *w, const float *x, float *out,
@@ -478,6 +485,11 @@ void apus_cuda_model_destroy(ApusCudaModel *m);
 /* c/model.h:485: back to position 0 with empty caches. */
 int apus_cuda_model_reset(ApusCudaModel *m);
 int64_t apus_cuda_model_pos(const ApusCudaModel *m);
+/* c/sample.h:44-71 for the loop above: temp <= 0 keeps the greedy pick; otherwise
+ * every step draws with temperature and nucleus (top-p) sampling, one uniform
+ * per sequence and step from a splitmix64 stream kept on the device; sequence b
+ * uses the stream seeded with seed + b (sequence 0 = the reference CLI's --seed). */
+int apus_cuda_model_set_sampling(ApusCudaModel *m, float temp, float top_p, uint64_t seed);
 /* A decode step is the same sequence of launches at every position (the kernels
  * read the position on the device), so apus_cuda_model_forward / _generate
  * replay it from a CUDA graph after the first step (default on; it is bypassed

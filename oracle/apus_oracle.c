@@ -543,3 +543,69 @@ void ora_fp4_qat_sim(float *x, size_t K) {
         }
     }
 }
+
+/* ---- sampling (c/sample.h:76-180) ------------------------------------------------- */
+/* greedy: strict >, lowest index on ties (c/sample.h:76-81) */
+int ora_sample_argmax(const float *logits, size_t n) {
+    size_t best = 0;
+    for (size_t i = 1; i < n; i++) if (logits[i] > logits[best]) best = i;
+    return (int)best;
+}
+
+/* splitmix64 and the 53-bit uniform (c/sample.h:160-171) */
+uint64_t ora_rng_next(uint64_t *state) {
+    uint64_t z = (*state += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+double ora_rng_uniform(uint64_t *state) { return (double)(ora_rng_next(state) >> 11) * 0x1.0p-53; }
+
+/* temperature softmax + nucleus draw with an explicit uniform (c/sample.h:91-158).
+ * The reference sorts the probabilities (descending, lower index first on ties)
+ * and walks the sorted list twice; this restatement does the same with an
+ * insertion-free O(n log n) merge sort on (prob desc, index asc), which yields
+ * the identical order.  ord: scratch of n int32, p: scratch of n floats. */
+static void ora_merge_sort(int32_t *ord, int32_t *tmp, const float *p, size_t n) {
+    for (size_t w = 1; w < n; w *= 2) {
+        for (size_t lo = 0; lo < n; lo += 2 * w) {
+            size_t mid = lo + w < n ? lo + w : n, hi = lo + 2 * w < n ? lo + 2 * w : n;
+            size_t a = lo, b = mid, o = lo;
+            while (a < mid && b < hi) {
+                int32_t x = ord[a], y = ord[b];
+                /* take from the left run unless the right element sorts strictly before it */
+                int right_first = p[y] > p[x] || (p[y] == p[x] && y < x);
+                tmp[o++] = right_first ? ord[b++] : ord[a++];
+            }
+            while (a < mid) tmp[o++] = ord[a++];
+            while (b < hi) tmp[o++] = ord[b++];
+        }
+        for (size_t i = 0; i < n; i++) ord[i] = tmp[i];
+    }
+}
+
+int ora_sample_logits_u(const float *logits, size_t n, float temp, float top_p, double u,
+                        float *p, int32_t *ord, int32_t *tmp) {
+    if (temp <= 0.0f) return ora_sample_argmax(logits, n);
+    float mx = logits[0];
+    for (size_t i = 1; i < n; i++) if (logits[i] > mx) mx = logits[i];
+    double sum = 0.0;
+    for (size_t i = 0; i < n; i++) { p[i] = expf((logits[i] - mx) / temp); sum += p[i]; }
+    for (size_t i = 0; i < n; i++) p[i] = (float)(p[i] / sum);
+    for (size_t i = 0; i < n; i++) ord[i] = (int32_t)i;
+    ora_merge_sort(ord, tmp, p, n);
+    /* nucleus: keep token i iff the mass before it is <= top_p; always the top token */
+    double cum = 0.0, kept = 0.0;
+    size_t nk = 0;
+    for (size_t i = 0; i < n; i++) {
+        if (cum <= (double)top_p) { cum += p[ord[i]]; kept = cum; nk = i + 1; }
+        else break;
+    }
+    if (nk == 0) { nk = 1; kept = p[ord[0]]; }
+    double c = 0.0;
+    for (size_t i = 0; i < nk; i++) {
+        c += (double)p[ord[i]] / kept;
+        if (u < c) return ord[i];
+    }
+    return ord[nk - 1];
+}

@@ -25,6 +25,7 @@
 #define APUS_MOE_IMPLEMENTATION
 #define APUS_LAYER_IMPLEMENTATION
 #define APUS_MODEL_IMPLEMENTATION
+#define APUS_SAMPLE_IMPLEMENTATION
 
 #include <math.h>
 #include <stdio.h>
@@ -34,6 +35,7 @@
 #include "moe.h"
 #include "mhc.h"
 #include "model.h"
+#include "sample.h"
 /* after the reference headers: their include guards make this header skip its
  * layout-identical copies of the reference types and only add the plain
  * descriptors ApusCudaLayerDesc / ApusCudaModelDesc used below */

@@ -50,6 +50,9 @@ def ora():
             "ora_swiglu": (None, [vp, vp, vp, sz, cf]),
             "ora_expert": (None, [q, q, q, ci, cf, vp, ci, ci, ci, vp]),
             "ora_topk_stable": (None, [vp, ci, ci, vp]),
+            "ora_sample_logits_u": (ci, [vp, C.c_size_t, C.c_float, C.c_float, C.c_double, vp, vp, vp]),
+            "ora_sample_argmax": (ci, [vp, C.c_size_t]),
+            "ora_rng_uniform": (C.c_double, [vp]),
             "ora_router_score": (None, [vp, vp, ci, ci, vp, ci, vp, vp]),
             "ora_moe_forward": (None, [ci, ci, ci, ci, ci, cf, cf, vp, vp, vp, vp, vp, vp,
                                        q, q, q, vp, vp, ci, vp, vp, vp, vp, vp]),

@@ -292,3 +292,20 @@ def block_inputs(seed, n_tokens, hc, dim):
 
 def prompt_ids(seed, batch, n, vocab):
     return np.random.default_rng(seed).integers(0, vocab, size=(batch, n)).astype(np.int64)
+
+
+# ---- sampling -------------------------------------------------------------------------
+def sample_case(seed, rows, n, kind):
+    """Logit rows + one uniform per row.  kind: 'peaked' (a few dominant tokens),
+    'flat' (near-uniform, the nucleus reaches deep into the tail), 'ties'
+    (BF16-rounded logits: many exactly equal probabilities)."""
+    rng = np.random.default_rng(seed)
+    if kind == "peaked":
+        lg = (rng.standard_normal((rows, n)) * 4.0).astype(np.float32)
+    elif kind == "flat":
+        lg = (rng.standard_normal((rows, n)) * 0.05).astype(np.float32)
+    else:
+        lg = synth.bf16_round((rng.standard_normal((rows, n)) * 0.5).astype(np.float32))
+        lg = (np.round(lg * 8) / 8).astype(np.float32)
+    u = rng.random(rows)
+    return lg, u

@@ -157,7 +157,7 @@ def ref_block(L, seed, kind, chunks, flash=False):
     return dict(out=out, win=S.win.copy(), **A)
 
 
-def ref_generate(L, seed, n_layers, batch, n_prompt, n_gen):
+def ref_generate(L, seed, n_layers, batch, n_prompt, n_gen, temp=0.0, top_p=1.0, rng_seed=0):
     """Greedy token loop on the reference's apus_model_forward (c/apus.c:895-944
     with temperature 0: argmax, lowest index on ties), one sequence at a time."""
     Mdl = cases.TinyModel(seed, rope_pair(L), n_layers)
@@ -167,7 +167,12 @@ def ref_generate(L, seed, n_layers, batch, n_prompt, n_gen):
     L.ref_model_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int]
     toks = np.zeros((batch, n_gen), np.int32)
     logits = np.zeros((batch, n_gen, V), np.float32)
+    L.apus_sample_logits_u.restype = C.c_int
+    L.apus_sample_logits_u.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_float, C.c_double, C.c_void_p]
+    L.apus_rng_uniform.restype = C.c_double
+    scratch = np.empty(2 * V, np.float32)
     for b in range(batch):
+        rng_state = C.c_uint64(rng_seed + b)             # sequence b draws from the stream seeded seed + b
         keep, st = Mdl.states()
         pos = C.c_int64(0)
         lg = np.empty(V, np.float32)
@@ -175,7 +180,11 @@ def ref_generate(L, seed, n_layers, batch, n_prompt, n_gen):
         L.ref_model_forward(C.byref(Mdl.desc), st, C.byref(pos), P(ids), n_prompt, P(lg), 0)
         for g in range(n_gen):
             logits[b, g] = lg
-            toks[b, g] = int(np.argmax(lg))
+            if temp > 0:                                  # c/sample.h:173-178 apus_sample
+                toks[b, g] = L.apus_sample_logits_u(P(lg), V, temp, top_p, L.apus_rng_uniform(C.byref(rng_state)),
+                                                    P(scratch))
+            else:
+                toks[b, g] = int(np.argmax(lg))
             if g + 1 < n_gen:
                 nxt = np.array([toks[b, g]], np.int64)
                 L.ref_model_forward(C.byref(Mdl.desc), st, C.byref(pos), P(nxt), 1, P(lg), 0)
@@ -266,6 +275,18 @@ def main():
         print(tag, "done", flush=True)
     for tag, args in MODEL_CASES.items():
         G.update({f"{tag}.{k}": v for k, v in ref_generate(L, *args).items()})
+    for tag, args in MODEL_SAMPLED_CASES.items():
+        G.update({f"{tag}.{k}": v for k, v in ref_generate(L, *args).items()})
+    L.apus_sample_logits_u.restype = C.c_int
+    L.apus_sample_logits_u.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_float, C.c_double, C.c_void_p]
+    for tag, (seed, rows, n, kind, temp, top_p) in SAMPLE_CASES.items():
+        lg, u = cases.sample_case(seed, rows, n, kind)
+        scratch = np.empty(2 * n, np.float32)
+        G[f"{tag}.tokens"] = np.array([L.apus_sample_logits_u(P(lg[r]), n, temp, top_p, float(u[r]), P(scratch))
+                                       for r in range(rows)], np.int32)
+    st = C.c_uint64(20260729)
+    L.apus_rng_uniform.restype = C.c_double
+    G["rng.uniforms"] = np.array([L.apus_rng_uniform(C.byref(st)) for _ in range(16)], np.float64)
     np.savez_compressed(HERE / "ref_cases.npz", **G)
     print(f"wrote {len(G)} arrays; avx2 hits {L.ref_avx2_hits()}, threads {L.ref_pool_threads()}")
 
@@ -322,6 +343,21 @@ FLASH_KEEP = {"swa": list(range(7)), "csa": list(range(13)), "hca128": [0, 1, 2,
 MODEL_CASES = {
     "model_one": (91, 3, 1, 9, 14),
     "model_batch": (92, 4, 3, 7, 12),
+}
+# the same plus (temperature, top_p, generator seed): sampled continuation (c/apus.c:895-944 with --temp)
+MODEL_SAMPLED_CASES = {
+    "model_sampled": (93, 3, 2, 6, 12, 0.8, 0.9, 1234),
+}
+# tag -> (seed, rows, vocabulary, logit pattern, temperature, top_p); c/sample.h
+SAMPLE_CASES = {
+    "sample_peaked": (111, 24, 4096, "peaked", 0.8, 0.95),
+    "sample_flat": (112, 24, 4096, "flat", 1.0, 0.9),
+    "sample_all": (113, 16, 3000, "flat", 1.0, 1.0),
+    "sample_ties": (114, 24, 2048, "ties", 0.7, 0.5),
+    "sample_top1": (115, 8, 1000, "peaked", 1.0, 0.0),
+    "sample_vocab": (116, 6, 129280, "peaked", 0.8, 0.95),
+    "sample_vocab_flat": (117, 4, 129280, "flat", 1.0, 1.0),
+    "sample_greedy": (118, 8, 5000, "ties", 0.0, 0.9),
 }
 MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
 

@@ -26,7 +26,8 @@ import pytest
 import cases
 from _gpu import bf16_ulps, bits, lib
 from _oracle import P, rel_l2
-from golden.make_golden import BLOCK_CASES, BLOCK_FLASH_CASES, FLASH_KEEP, MODEL_CASES
+from golden.make_golden import (BLOCK_CASES, BLOCK_FLASH_CASES, FLASH_KEEP, MODEL_CASES, MODEL_SAMPLED_CASES,
+                                SAMPLE_CASES)
 
 pytestmark = pytest.mark.gpu
 G = np.load(Path(__file__).resolve().parent / "golden" / "ref_cases.npz")
@@ -319,3 +320,36 @@ def test_piecewise_loop_equals_generate():
         ep.close()
         L.apus_cuda_use_stream(None, 1)
     assert np.array_equal(got, toks)
+
+
+@pytest.mark.parametrize("tag", list(SAMPLE_CASES))
+def test_sampler_vs_reference(tag):
+    """apus_cuda_sample_logits_u (weighted selection instead of the reference's sort)
+    picks the reference's token for every row: peaked, flat, tie-ridden rows, the
+    whole vocabulary, top_p 0 / 1, greedy."""
+    L = lib()
+    seed, rows, n, kind, temp, top_p = SAMPLE_CASES[tag]
+    lg, u = cases.sample_case(seed, rows, n, kind)
+    tok = np.empty(rows, np.int32)
+    assert L.apus_cuda_sample_logits_u(P(lg), n, temp, top_p, P(u), P(tok), rows) == 0, L.apus_cuda_last_error()
+    assert tok.tolist() == G[f"{tag}.tokens"].tolist()
+
+
+def test_sampled_generation_vs_reference():
+    """The token loop with temperature / top-p sampling and the per-sequence
+    splitmix64 streams on the device against the reference loop."""
+    L = lib()
+    tag = "model_sampled"
+    seed, n_layers, B, n_prompt, n_gen, temp, top_p, rng_seed = MODEL_SAMPLED_CASES[tag]
+    Mdl = cases.TinyModel(seed, rope(), n_layers)
+    prompts = cases.prompt_ids(seed + 5, B, n_prompt, Mdl.M["vocab"])
+    h = L.apus_cuda_model_create(C.byref(Mdl.desc), B, 64)
+    assert h, L.apus_cuda_last_error()
+    toks = np.empty((B, n_gen), np.int32)
+    try:
+        assert L.apus_cuda_model_set_sampling(h, temp, top_p, rng_seed) == 0
+        assert L.apus_cuda_model_generate(h, P(prompts), n_prompt, n_gen, P(toks), None, None) == 0, \
+            L.apus_cuda_last_error()
+    finally:
+        L.apus_cuda_model_destroy(h)
+    assert np.array_equal(toks, G[f"{tag}.tokens"]), (toks, G[f"{tag}.tokens"])

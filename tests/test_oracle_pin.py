@@ -320,3 +320,18 @@ def test_rope_tables_match_the_reference():
         cos, sin = rope_tables(cfg, compressed, 256)
         assert np.abs(cos - G[f"rope.{name}.cos"]).max() <= 2e-5
         assert np.abs(sin - G[f"rope.{name}.sin"]).max() <= 2e-5
+
+
+def test_sampler_matches_the_reference():
+    """Temperature + nucleus sampling and the splitmix64 stream (c/sample.h) against
+    tokens and uniforms produced by the unmodified reference."""
+    from golden.make_golden import SAMPLE_CASES
+    G = np.load(Path(__file__).resolve().parent / "golden" / "ref_cases.npz")
+    O = ora()
+    for tag, (seed, rows, n, kind, temp, top_p) in SAMPLE_CASES.items():
+        lg, u = cases.sample_case(seed, rows, n, kind)
+        p, ordr, tmp = np.empty(n, np.float32), np.empty(n, np.int32), np.empty(n, np.int32)
+        got = [O.ora_sample_logits_u(P(lg[r]), n, temp, top_p, float(u[r]), P(p), P(ordr), P(tmp)) for r in range(rows)]
+        assert got == G[f"{tag}.tokens"].tolist(), tag
+    st = C.c_uint64(20260729)
+    assert [O.ora_rng_uniform(C.byref(st)) for _ in range(16)] == G["rng.uniforms"].tolist()
