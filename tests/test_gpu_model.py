@@ -353,3 +353,92 @@ def test_sampled_generation_vs_reference():
     finally:
         L.apus_cuda_model_destroy(h)
     assert np.array_equal(toks, G[f"{tag}.tokens"]), (toks, G[f"{tag}.tokens"])
+
+
+def test_block_chunk_invariance():
+    """One call over 12 tokens equals 12 single-token calls bit for bit (the
+    reference's chunk invariance, tests/m4c): hidden states and the ring."""
+    L = lib()
+    tag = "block_csa"
+    seed, kind, chunks = BLOCK_CASES[tag]
+    cos, sin = rope()["yarn"]
+    total = 12
+
+    def run(parts):
+        B = cases.BlockLayer(seed, kind, cos, sin)
+        S = cases.AttnState(B.attn)
+        M, dim = B.M, B.attn.D["dim"]
+        out = cases.block_inputs(seed + 3, total, M["hc"], dim).copy()
+        ids = np.zeros(total, np.int64)
+        pos = 0
+        for n in parts:
+            assert L.apus_cuda_block_forward(C.byref(B.desc), M["hc"], M["iters"], M["hc_eps"], M["norm_eps"],
+                                             C.byref(S.st), P(out[pos:pos + n]), P(ids[pos:pos + n]), n, pos) == 0
+            pos += n
+        L.apus_cuda_disable()
+        return out, S.win.copy()
+    a, wa = run([total])
+    b, wb = run([1] * total)
+    c, wc = run([5, 1, 4, 2])
+    assert np.array_equal(bits(a), bits(b)) and np.array_equal(bits(a), bits(c))
+    assert np.array_equal(bits(wa), bits(wb)) and np.array_equal(bits(wa), bits(wc))
+
+
+def test_graph_replay_equals_plain_launches():
+    """The step replayed from a CUDA graph gives the logits and tokens of the
+    same steps issued as plain launches."""
+    L = lib()
+    tag = "model_batch"
+    _, _, B, n_prompt, n_gen = MODEL_CASES[tag]
+    res = []
+    for graph in (1, 0):
+        Mdl, prompts, h = make_model(L, tag, B)
+        try:
+            assert L.apus_cuda_model_use_graph(h, graph) == graph
+            toks = np.empty((B, n_gen), np.int32)
+            lg = np.empty((B, Mdl.M["vocab"]), np.float32)
+            assert L.apus_cuda_model_generate(h, P(prompts), n_prompt, n_gen, P(toks), None, None) == 0
+            nxt = np.ascontiguousarray(toks[:, -1:].astype(np.int64))
+            assert L.apus_cuda_model_forward(h, P(nxt), 1, P(lg), None) == 0
+            res.append((toks, lg.copy()))
+        finally:
+            L.apus_cuda_model_destroy(h)
+    assert np.array_equal(res[0][0], res[1][0])
+    assert np.array_equal(bits(res[0][1]), bits(res[1][1]))
+
+
+def test_caller_side_graph_capture():
+    """The layer-by-layer interface recorded into the caller's CUDA graph
+    (EpModel.capture) and replayed gives the tokens of apus_cuda_model_generate."""
+    import torch
+    from apus_b200.ep_model import EpModel
+    L = lib()
+    tag = "model_batch"
+    _, n_layers, B, n_prompt, n_gen = MODEL_CASES[tag]
+    Mdl, prompts, h = make_model(L, tag, B)
+    toks = np.empty((B, n_gen), np.int32)
+    try:
+        assert L.apus_cuda_model_generate(h, P(prompts), n_prompt, n_gen, P(toks), None, None) == 0
+    finally:
+        L.apus_cuda_model_destroy(h)
+    M = Mdl.M
+    ep = EpModel(Mdl.desc, n_layers, M["E"], M["topk"], cases.ATTN_DIMS["dim"], B, 64, device=torch.device("cuda", 0))
+    try:
+        got = np.empty((B, n_gen), np.int32)
+        nxt = np.empty(B, np.int32)
+        ep.prefill(prompts)
+        ep.read(tokens=nxt)
+        got[:, 0] = nxt
+        ep.step()                              # one plain step, then record and replay
+        ep.read(tokens=nxt)
+        got[:, 1] = nxt
+        ep.capture()
+        for g in range(2, n_gen):
+            ep.step()
+            ep.read(tokens=nxt)
+            got[:, g] = nxt
+    finally:
+        ep.graph = None
+        ep.close()
+        L.apus_cuda_use_stream(None, 1)
+    assert np.array_equal(got, toks)
