@@ -246,6 +246,16 @@ const void *cached_dense(const void *host, size_t bytes) {
 int qgemm_dev(DevQW *w, DevQW *other, const uint8_t *acodes, const float *ascales, int M, float *out,
               bool round_out, float limit, cudaStream_t st) {
     if (M <= 0) return 0;
+    static const bool wide_ok = !(getenv("APUS_FP8_WIDE") && getenv("APUS_FP8_WIDE")[0] == '0');
+    if (w->tc && !other && M >= 64 && w->K <= 8192 && wide_ok) {       // many rows: 128 per CTA
+        alignas(64) unsigned char map_x[128];
+        if (tc8_make_act_map_wide(map_x, acodes, M, w->K)) return 1;
+        Tc8Args t = {};
+        t.map_a = w->map; t.map_b = w->map; t.map_x = map_x;
+        t.scales_a = w->scales; t.ascales = ascales;
+        t.M = M; t.O = w->O; t.K = w->K; t.pair = 0; t.round_out = round_out; t.out = out;
+        return gemm_tc8_wide(t, st);
+    }
     if (w->tc && (!other || other->tc)) {
         alignas(64) unsigned char map_x[128];
         if (tc_make_act_map(map_x, acodes, M, w->K)) return 1;

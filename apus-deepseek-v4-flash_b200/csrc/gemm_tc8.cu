@@ -218,6 +218,148 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                      : "memory");
 }
 
+// ---- many activation rows (prefill / large batches): 128 rows per CTA -----------------------
+// Same structure with MMA N = 128: one weight tile is read once per 128
+// activation rows instead of once per 32, two accumulators of 128 TMEM columns,
+// and every fold thread keeps 128 running sums (its output row against the
+// CTA's 128 activation rows).  The fold (3 CUDA-core operations per element per
+// block: scale product, multiply, add -- the reference's order) costs more issue
+// slots than the block's MMAs, so this kernel is bound by the FP32 pipe at about
+// two thirds of the tensor peak; the per-block promotion is what keeps the
+// result equal to the reference's block-ordered f32 fold.
+constexpr int T8W_N = 128, T8W_NS = 5, T8W_NACC = 2;
+
+__device__ __forceinline__ uint32_t idesc_f8_wide() {
+    return (1u << 4) | ((uint32_t)(T8W_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(T8_THREADS, 1)
+gemm_tc8_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_x,
+                     const Tc8Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int B_BYTES = T8W_N * 128, STAGE = T8_A_BYTES + B_BYTES, NS = T8W_NS, NACC = T8W_NACC;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)NS * STAGE);
+    uint64_t *full = bars, *empty = bars + NS, *acc_full = bars + 2 * NS, *acc_empty = bars + 2 * NS + NACC;
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 2 * NS + 2 * NACC);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
+    float *s_as = reinterpret_cast<float *>(s_tmem + 4);          // [NC][128] activation scales
+    const int K = a.K, O = a.O, NC = K >> 7, M = a.M;
+    float *s_ws = s_as + (size_t)NC * T8W_N;                       // [NC] weight tile scales
+    const int row0 = (int)blockIdx.y * T8W_N;
+    const int nrows = min(T8W_N, M - row0);
+    if (nrows <= 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile_row = (int)blockIdx.x * 128;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < NACC; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(s_tmem)), "r"(NACC * T8W_N) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid < 128) {
+        for (int i = tid; i < NC * T8W_N; i += 128) {
+            const int kb = i / T8W_N, n = i - kb * T8W_N;
+            s_as[i] = n < nrows ? a.ascales[(size_t)(row0 + n) * NC + kb] : 0.f;
+        }
+        const uint8_t *wsa = a.scales_a + (size_t)blockIdx.x * NC;
+        for (int i = tid; i < NC; i += 128) s_ws[i] = ue8m0_f32(wsa[i]);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *s_tmem;
+    int fail = 0;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            for (int i = 0; i < NC && !fail; i++) {
+                const int s = i % NS;
+                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+                if (!mbar_wait(&empty[s], ph ^ 1u, s_abort)) { fail = 11; break; }
+                uint8_t *st = smem + (size_t)s * STAGE;
+                mbar_expect_tx(&full[s], STAGE);
+                tma_load_2d(st, &tm_a, i * 128, tile_row, &full[s]);
+                tma_load_2d(st + T8_A_BYTES, &tm_x, i * 128, row0, &full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            const uint32_t idesc = idesc_f8_wide();
+            for (int i = 0; i < NC && !fail; i++) {
+                const int s = i % NS, b = i % NACC;
+                const uint32_t ph = (uint32_t)(i / NS) & 1u, pb = (uint32_t)(i / NACC) & 1u;
+                if (!mbar_wait(&acc_empty[b], pb ^ 1u, s_abort)) { fail = 12; break; }
+                if (!mbar_wait(&full[s], ph, s_abort)) { fail = 13; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = smem_u32(smem + (size_t)s * STAGE);
+                const uint64_t da = umma_desc_sw128(sa), dx = umma_desc_sw128(sa + T8_A_BYTES);
+#pragma unroll
+                for (int j = 0; j < 4; j++) umma_f8(tmem + b * T8W_N, da + 2 * j, dx + 2 * j, idesc, j ? 1u : 0u);
+                umma_commit(&empty[s]);
+                umma_commit(&acc_full[b]);
+            }
+        }
+    } else {
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float acc[T8W_N];
+#pragma unroll
+        for (int n = 0; n < T8W_N; n++) acc[n] = 0.f;
+        for (int i = 0; i < NC && !fail; i++) {
+            const int b = i % NACC;
+            const uint32_t pb = (uint32_t)(i / NACC) & 1u;
+            if (!mbar_wait(&acc_full[b], pb, s_abort)) { fail = 14; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float ws = s_ws[i];
+            const float4 *as4 = reinterpret_cast<const float4 *>(s_as + (size_t)i * T8W_N);
+#pragma unroll
+            for (int qd = 0; qd < T8W_N / 32; qd++) {
+                uint32_t d[32];
+                tmem_ld32(tmem + lane_base + b * T8W_N + qd * 32, d);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (qd == T8W_N / 32 - 1) {              // the accumulator has been read completely
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&acc_empty[b]);
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const float4 s4 = as4[qd * 8 + q];
+                    const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const int n = qd * 32 + 4 * q + r;
+                        acc[n] = __fadd_rn(acc[n], __fmul_rn(__uint_as_float(d[4 * q + r]), __fmul_rn(sv[r], ws)));
+                    }
+                }
+            }
+        }
+        if (!fail) {
+            const int o = tile_row + tid;
+            if (o < O) {
+#pragma unroll
+                for (int n = 0; n < T8W_N; n++)
+                    if (n < nrows) a.out[(size_t)(row0 + n) * O + o] = a.round_out ? bf16_round(acc[n]) : acc[n];
+            }
+        }
+    }
+    if (fail) {
+        *s_abort = 1;
+        atomicCAS(&g_tc8_status, 0, fail);
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NACC * T8W_N)
+                     : "memory");
+}
+
 template <bool PAIR, int NS>
 int launch_tc8(const Tc8Args &a, cudaStream_t st) {
     constexpr int STAGE = T8_A_BYTES * (PAIR ? 2 : 1) + T8_B_BYTES;
@@ -253,6 +395,30 @@ int tc8_make_weight_map(void *out_map, const void *codes, long long rows, int K)
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     APUS_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(fp8 weights [%lld,%d]) failed: %d", rows, K, (int)r);
     return 0;
+}
+
+// a.map_x must be a map with 128-row boxes (tc8_make_act_map_wide)
+int gemm_tc8_wide(const Tc8Args &a, cudaStream_t st) {
+    APUS_REQUIRE(a.K % 128 == 0 && a.K <= 128 * 64 && a.O % 128 == 0 && !a.pair,
+                 "gemm_tc8_wide: unsupported shape O=%d K=%d", a.O, a.K);
+    if (a.M <= 0) return 0;
+    const int NC = a.K >> 7;
+    const size_t smem = (size_t)T8W_NS * (T8_A_BYTES + T8W_N * 128) + 1024 + 256 + (size_t)NC * T8W_N * 4 + (size_t)NC * 4;
+    static bool configured = false;
+    if (!configured) {
+        APUS_CUDA_OK(cudaFuncSetAttribute(gemm_tc8_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        configured = true;
+    }
+    dim3 grid((unsigned)(a.O / 128), (unsigned)((a.M + T8W_N - 1) / T8W_N));
+    gemm_tc8_wide_kernel<<<grid, T8_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
+                                                         *reinterpret_cast<const CUtensorMap *>(a.map_x), a);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// Tensor map over E4M3 activation codes [rows, K] bytes with 128 x 128 boxes.
+int tc8_make_act_map_wide(void *out_map, const void *codes, long long rows, int K) {
+    return tc8_make_weight_map(out_map, codes, rows, K);
 }
 
 int gemm_tc8(const Tc8Args &a, cudaStream_t st) {

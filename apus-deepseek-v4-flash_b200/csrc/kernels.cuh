@@ -92,6 +92,8 @@ struct Tc8Args {
     float *out;                          // [M, O]
 };
 int gemm_tc8(const Tc8Args &a, cudaStream_t st);
+int gemm_tc8_wide(const Tc8Args &a, cudaStream_t st);      // 128 activation rows per CTA; map_x from tc8_make_act_map_wide
+int tc8_make_act_map_wide(void *out_map, const void *codes, long long rows, int K);
 int gemm_tc8_status(int reset);
 int tc8_make_weight_map(void *out_map, const void *codes, long long rows, int K);
 

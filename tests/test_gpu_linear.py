@@ -110,7 +110,8 @@ def test_linear_vs_reference_outputs(tag):
 
 @pytest.mark.parametrize("fmt,M,O,K", [(4, 1, 2048, 4096), (4, 8, 2048, 4096), (4, 5, 4096, 2048),
                                        (4, 17, 256, 512), (4, 40, 128, 1024), (8, 1, 2048, 4096),
-                                       (8, 7, 4096, 2048), (8, 32, 1024, 4096), (8, 70, 256, 1024)])
+                                       (8, 7, 4096, 2048), (8, 32, 1024, 4096), (8, 70, 256, 1024),
+                                       (8, 300, 512, 2048), (8, 128, 256, 8192)])
 def test_linear_vs_oracle_model_shapes(fmt, M, O, K):
     c = cases.linear_case(1000 + M + O + K + fmt, fmt, M, O, K)
     want = ora_qlinear(0 if fmt == 4 else 1, c["codes"], c["scales"], c["x"], O)
@@ -131,6 +132,16 @@ def test_linear_m_independence():
     for m in (0, 5, 10):
         one = cuda_qlinear(4, c["codes"], c["scales"], c["x"][m:m + 1].copy(), 512)
         assert np.array_equal(bits(one[0]), bits(full[m]))
+
+
+def test_fp8_many_rows_equal_single_rows():
+    """The 128-rows-per-CTA FP8 kernel (M >= 64) returns for every row the bits of
+    the M = 1 call (32-row kernel): same block dots, same block-ordered fold."""
+    c = cases.linear_case(78, 8, 200, 384, 1024)
+    full = cuda_qlinear(8, c["codes"], c["scales"], c["x"], 384)
+    for m in (0, 63, 127, 128, 199):
+        one = cuda_qlinear(8, c["codes"], c["scales"], c["x"][m:m + 1].copy(), 384)
+        assert np.array_equal(bits(one[0]), bits(full[m])), m
 
 
 @pytest.mark.parametrize("tag", list(EXPERT_CASES))
