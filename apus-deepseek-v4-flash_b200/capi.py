@@ -127,6 +127,21 @@ class Hooks(C.Structure):
                 ("head_gemv", C.c_void_p)]
 
 
+class CkptCfg(C.Structure):
+    """ApusCudaCkptCfg: the reference's ApusCfg (c/layer.h:32-41) + what its config parser returns beside it."""
+    _fields_ = [(n, C.c_int) for n in (
+        "dim", "n_heads", "head_dim", "rope_head_dim", "q_lora_rank", "o_groups", "o_lora_rank", "window_size",
+        "moe_inter_dim", "n_routed_experts", "n_activated_experts", "index_n_heads", "index_head_dim",
+        "index_topk", "hc_mult", "hc_sinkhorn_iters", "original_seq_len", "beta_fast", "beta_slow",
+        "vocab_size", "max_pos")] + \
+        [(n, C.c_float) for n in ("route_scale", "swiglu_limit", "hc_eps", "norm_eps")] + \
+        [(n, C.c_double) for n in ("rope_theta", "compress_rope_theta", "rope_factor")] + \
+        [(n, C.c_int) for n in ("n_layers", "bos_id", "eos_id", "n_mtp", "mtp_ratio", "mtp_hash", "dspark")]
+
+
+ST_DTYPES = ("I8", "U8", "F8_E8M0", "F8_E4M3", "BF16", "F16", "F32", "I32", "I64", "OTHER")
+
+
 def ptr(a):
     """Address of a numpy array's (or torch tensor's) first element."""
     if a is None:
@@ -188,6 +203,19 @@ def load(path=LIB_PATH):
         "apus_cuda_block_forward": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64]),
         "apus_cuda_model_create": (vp, [C.POINTER(ModelDesc), ci, ci]),
         "apus_cuda_model_create_ep": (vp, [C.POINTER(ModelDesc), ci, ci, ci, ci]),
+        "apus_cuda_model_load": (vp, [C.c_char_p, ci, ci, ci, ci]),
+        "apus_cuda_ckpt_open": (vp, [C.c_char_p, C.c_char_p, sz]),
+        "apus_cuda_ckpt_close": (None, [vp]),
+        "apus_cuda_ckpt_cfg": (C.POINTER(CkptCfg), [vp]),
+        "apus_cuda_ckpt_layer_kind": (ci, [vp, ci, C.POINTER(ci), C.POINTER(ci)]),
+        "apus_cuda_ckpt_tensor": (ci, [vp, C.c_char_p, C.POINTER(ci), C.POINTER(ci), i64p, C.POINTER(C.c_uint64)]),
+        "apus_cuda_ckpt_read": (ci, [vp, C.c_char_p, vp, C.c_uint64]),
+        "apus_cuda_ckpt_read_f32": (ci, [vp, C.c_char_p, vp, C.c_uint64]),
+        "apus_cuda_ckpt_wo_a": (ci, [vp, ci, vp, C.c_uint64]),
+        "apus_cuda_ckpt_rope": (ci, [vp, ci, i64, vp, vp]),
+        "apus_cuda_ckpt_expert": (ci, [vp, ci, ci, vp, C.c_uint64, C.POINTER(QW), C.POINTER(QW), C.POINTER(QW)]),
+        "apus_cuda_ckpt_read_count": (C.c_uint64, [vp]),
+        "apus_cuda_ckpt_read_bytes": (C.c_uint64, [vp]),
         "apus_cuda_use_stream": (ci, [vp, ci]),
         "apus_cuda_model_set_ids": (ci, [vp, vp]),
         "apus_cuda_model_begin_step": (ci, [vp]),

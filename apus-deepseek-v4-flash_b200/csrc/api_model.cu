@@ -11,9 +11,11 @@
 // tokens.  A prompt is consumed as consecutive steps; the reference defines
 // its batched prefill to be equal to that (tests/m4c chunk invariance).
 #include <math.h>
+#include <string>
 #include <vector>
 
 #include "attn_engine.cuh"
+#include "ckpt.cuh"
 
 using namespace apus;
 
@@ -146,6 +148,7 @@ __global__ void next_ids_kernel(const int32_t *tok, int64_t *ids, int32_t *hist,
 
 struct ApusCudaModel {
     int n_layers = 0, dim = 0, hc = 0, iters = 0, vocab = 0, B = 0, max_pos = 0, n_experts = 0;
+    long long max_nb = 8;                  // most compressed entries any layer can hold
     float hc_eps = 0.f, norm_eps = 0.f, hc_head_scale = 0.f;
     std::vector<LayerDev> layers;
     std::vector<StateDev> states;
@@ -306,62 +309,143 @@ ApusCudaModel *apus_cuda_model_create(const ApusCudaModelDesc *d, int batch, int
     return apus_cuda_model_create_ep(d, batch, max_pos, 0, -1);
 }
 
-ApusCudaModel *apus_cuda_model_create_ep(const ApusCudaModelDesc *d, int batch, int max_pos, int e_lo, int e_hi) {
+// A model is put together in three steps so that a loader can hand over one layer
+// at a time (its host copy is no longer needed once model_add_layer returned:
+// uploads are synchronous): sizes, the layers in order, the top-level tensors.
+static ApusCudaModel *model_begin(const ApusCudaModelDesc &d, int E, int batch, int max_pos, int e_lo, int e_hi) {
     if (ensure_enabled()) return nullptr;
-    if (!d || batch < 1 || batch > 32 || d->n_layers < 1) { set_error("model_create: bad arguments (batch 1..32)"); return nullptr; }
-    const int E = d->layers[0].mw.E;
+    if (batch < 1 || batch > 32 || d.n_layers < 1) { set_error("model_create: bad arguments (batch 1..32)"); return nullptr; }
     if (e_hi < 0) e_hi = E;
     if (e_lo < 0 || e_lo > e_hi || e_hi > E) { set_error("model_create: bad expert range [%d,%d) of %d", e_lo, e_hi, E); return nullptr; }
     ApusCudaModel *m = new ApusCudaModel();
     m->n_experts = E; m->e_lo = e_lo; m->e_hi = e_hi;
-    m->n_layers = d->n_layers; m->dim = d->dim; m->hc = d->hc_mult; m->iters = d->hc_sinkhorn_iters;
-    m->vocab = d->vocab; m->B = batch; m->max_pos = max_pos;
-    m->hc_eps = d->hc_eps; m->norm_eps = d->norm_eps; m->hc_head_scale = d->hc_head_scale;
-    m->layers.resize(d->n_layers);
-    m->states.resize(d->n_layers);
-    long long max_nb = 8;
+    m->n_layers = d.n_layers; m->dim = d.dim; m->hc = d.hc_mult; m->iters = d.hc_sinkhorn_iters;
+    m->vocab = d.vocab; m->B = batch; m->max_pos = max_pos;
+    m->hc_eps = d.hc_eps; m->norm_eps = d.norm_eps; m->hc_head_scale = d.hc_head_scale;
+    m->layers.resize(d.n_layers);
+    m->states.resize(d.n_layers);
+    return m;
+}
+
+static int model_add_layer(ApusCudaModel *m, int i, const ApusCudaLayerDesc &ld) {
+    if (layer_weights(ld, m->hc, m->vocab, &m->layers[i], &m->own, m->e_lo, m->e_hi)) return 1;
+    const int half = ld.acfg.rope_dim / 2;
+    m->layers[i].cs = rope_rows_dev(ld.cos, ld.sin, ld.rope_rows, half, m->rope);
+    m->layers[i].rope_rows = ld.rope_rows;
+    if (!m->layers[i].cs || ld.rope_rows < m->max_pos) {
+        set_error("model_create: layer %d rope table has %d rows, %d needed", i, ld.rope_rows, m->max_pos);
+        return 1;
+    }
+    if (ld.acfg.ratio && m->max_pos / ld.acfg.ratio + 2 > m->max_nb) m->max_nb = m->max_pos / ld.acfg.ratio + 2;
+    return 0;
+}
+
+static int model_finish(ApusCudaModel *m, const ApusCudaModelDesc &d) {
+    const size_t B = m->B, dim = d.dim, hc = d.hc_mult;
+    const size_t esz_e = d.embed_bf16 ? 2 : 4, esz_h = d.head_bf16 ? 2 : 4;
+    m->embed = get_dense(&m->own, d.embed, (size_t)d.vocab * dim * esz_e);
+    m->head = d.head == d.embed && esz_e == esz_h ? m->embed : get_dense(&m->own, d.head, (size_t)d.vocab * dim * esz_h);
+    m->embed_bf16 = d.embed_bf16; m->head_bf16 = d.head_bf16;
+    m->norm_w = (const float *)get_dense(&m->own, d.norm_w, dim * 4);
+    m->hc_head_fn = (const float *)get_dense(&m->own, d.hc_head_fn, hc * hc * dim * 4);
+    m->hc_head_base = (const float *)get_dense(&m->own, d.hc_head_base, hc * 4);
+    if (!(m->embed && m->head && m->norm_w && m->hc_head_fn && m->hc_head_base)) return 1;
+    if (m->h0.get(B * hc * dim * 4, nullptr) || m->h1.get(B * hc * dim * 4, nullptr) ||
+        m->x.get(B * dim * 4, nullptr) || m->y.get(B * dim * 4, nullptr) || m->sub.get(B * dim * 4, nullptr) ||
+        m->post.get(B * hc * 4, nullptr) || m->comb.get(B * hc * hc * 4, nullptr) ||
+        m->yh.get(B * dim * 4, nullptr) || m->yn.get(B * dim * 4, nullptr) ||
+        m->logits.get(B * (size_t)d.vocab * 4, nullptr) || m->tok.get(B * 4, nullptr) || m->ids.get(B * 8, nullptr))
+        return 1;
+    // step buffers sized for the widest layer configuration
+    ApusAttnCfg widest = m->layers[0].attn.cfg;
+    for (int i = 1; i < m->n_layers; i++) {
+        const ApusAttnCfg &c = m->layers[i].attn.cfg;
+        if (c.has_indexer) { widest.has_indexer = 1; widest.idx_heads = c.idx_heads; widest.idx_dim = c.idx_dim; widest.idx_topk = c.idx_topk; }
+    }
+    widest.has_indexer = 0;                      // size the index row for the dense (largest) case
+    if (attn_step_bufs(widest, m->max_nb > widest.idx_topk ? m->max_nb : widest.idx_topk, m->B, m->ws, &m->sb)) return 1;
+    return apus_cuda_model_reset(m);
+}
+
+ApusCudaModel *apus_cuda_model_create_ep(const ApusCudaModelDesc *d, int batch, int max_pos, int e_lo, int e_hi) {
+    if (!d || d->n_layers < 1 || !d->layers) { set_error("model_create: bad arguments (batch 1..32)"); return nullptr; }
+    ApusCudaModel *m = model_begin(*d, d->layers[0].mw.E, batch, max_pos, e_lo, e_hi);
+    if (!m) return nullptr;
     bool ok = true;
-    for (int i = 0; i < d->n_layers && ok; i++) {
-        const ApusCudaLayerDesc &ld = d->layers[i];
-        ok = layer_weights(ld, d->hc_mult, d->vocab, &m->layers[i], &m->own, e_lo, e_hi) == 0;
-        if (!ok) break;
-        const int half = ld.acfg.rope_dim / 2;
-        m->layers[i].cs = rope_rows_dev(ld.cos, ld.sin, ld.rope_rows, half, m->rope);
-        m->layers[i].rope_rows = ld.rope_rows;
-        ok = m->layers[i].cs != nullptr && ld.rope_rows >= max_pos;
-        if (!ok) set_error("model_create: layer %d rope table has %d rows, %d needed", i, ld.rope_rows, max_pos);
-        if (ld.acfg.ratio && max_pos / ld.acfg.ratio + 2 > max_nb) max_nb = max_pos / ld.acfg.ratio + 2;
-    }
-    const size_t B = batch, dim = d->dim, hc = d->hc_mult;
-    const size_t esz_e = d->embed_bf16 ? 2 : 4, esz_h = d->head_bf16 ? 2 : 4;
-    if (ok) {
-        m->embed = get_dense(&m->own, d->embed, (size_t)d->vocab * dim * esz_e);
-        m->head = d->head == d->embed && esz_e == esz_h ? m->embed
-                                                         : get_dense(&m->own, d->head, (size_t)d->vocab * dim * esz_h);
-        m->embed_bf16 = d->embed_bf16; m->head_bf16 = d->head_bf16;
-        m->norm_w = (const float *)get_dense(&m->own, d->norm_w, dim * 4);
-        m->hc_head_fn = (const float *)get_dense(&m->own, d->hc_head_fn, hc * hc * dim * 4);
-        m->hc_head_base = (const float *)get_dense(&m->own, d->hc_head_base, hc * 4);
-        ok = m->embed && m->head && m->norm_w && m->hc_head_fn && m->hc_head_base;
-    }
-    if (ok)
-        ok = !(m->h0.get(B * hc * dim * 4, nullptr) || m->h1.get(B * hc * dim * 4, nullptr) ||
-               m->x.get(B * dim * 4, nullptr) || m->y.get(B * dim * 4, nullptr) || m->sub.get(B * dim * 4, nullptr) ||
-               m->post.get(B * hc * 4, nullptr) || m->comb.get(B * hc * hc * 4, nullptr) ||
-               m->yh.get(B * dim * 4, nullptr) || m->yn.get(B * dim * 4, nullptr) ||
-               m->logits.get(B * (size_t)d->vocab * 4, nullptr) || m->tok.get(B * 4, nullptr) ||
-               m->ids.get(B * 8, nullptr));
-    if (ok) {
-        // step buffers sized for the widest layer configuration
-        ApusAttnCfg widest = d->layers[0].acfg;
-        for (int i = 1; i < d->n_layers; i++) {
-            const ApusAttnCfg &c = d->layers[i].acfg;
-            if (c.has_indexer) { widest.has_indexer = 1; widest.idx_heads = c.idx_heads; widest.idx_dim = c.idx_dim; widest.idx_topk = c.idx_topk; }
+    for (int i = 0; i < d->n_layers && ok; i++) ok = model_add_layer(m, i, d->layers[i]) == 0;
+    if (ok) ok = model_finish(m, *d) == 0;
+    if (!ok) { apus_cuda_model_destroy(m); return nullptr; }
+    return m;
+}
+
+// c/model.h:396-470 with HBM as the destination: one layer in host memory at a time.
+ApusCudaModel *apus_cuda_model_load(const char *dir, int batch, int max_pos, int e_lo, int e_hi) {
+    char err[512] = "";
+    ApusCudaCkpt *c = apus_cuda_ckpt_open(dir, err, sizeof err);
+    if (!c) return nullptr;                           // message already recorded
+    const ApusCudaCkptCfg &cfg = c->cfg;
+    if (max_pos <= 0 || max_pos > cfg.max_pos) max_pos = cfg.max_pos;
+    ApusCudaModelDesc top;
+    memset(&top, 0, sizeof top);
+    top.n_layers = cfg.n_layers; top.dim = cfg.dim; top.hc_mult = cfg.hc_mult;
+    top.hc_sinkhorn_iters = cfg.hc_sinkhorn_iters; top.vocab = cfg.vocab_size;
+    top.hc_eps = cfg.hc_eps; top.norm_eps = cfg.norm_eps;
+    ApusCudaModel *m = model_begin(top, cfg.n_routed_experts, batch, max_pos, e_lo, e_hi);
+    if (!m) { apus_cuda_ckpt_close(c); return nullptr; }
+    // one rope table per theta class (c/layer.h:145-166), shared by the layers of the class
+    const size_t half = cfg.rope_head_dim / 2;
+    std::vector<float> rope[2][2];                    // [class][cos | sin]
+    bool ok = true;
+    std::string why;
+    for (int i = 0; i < cfg.n_layers && ok; i++) {
+        CkLayerHost L;
+        if (ckpt_load_layer(c, i, m->e_lo, m->e_hi, &L, &why)) { set_error("%s", why.c_str()); ok = false; break; }
+        const int cls = c->ratios[i] ? 1 : 0;
+        if (rope[cls][0].empty()) {
+            rope[cls][0].resize((size_t)max_pos * half); rope[cls][1].resize((size_t)max_pos * half);
+            ckpt_rope(cfg, c->ratios[i], max_pos, rope[cls][0].data(), rope[cls][1].data());
         }
-        widest.has_indexer = 0;                      // size the index row for the dense (largest) case
-        ok = attn_step_bufs(widest, max_nb > widest.idx_topk ? max_nb : widest.idx_topk, batch, m->ws, &m->sb) == 0;
+        L.desc.cos = rope[cls][0].data(); L.desc.sin = rope[cls][1].data(); L.desc.rope_rows = max_pos;
+        L.desc.acfg.max_pos = max_pos;
+        ok = model_add_layer(m, i, L.desc) == 0;
     }
-    if (ok) ok = apus_cuda_model_reset(m) == 0;
+    if (ok) {
+        // c/model.h:432-467: embed/head [vocab, dim] BF16 or F32, norm, hc_head_*
+        const size_t V = cfg.vocab_size, dim = cfg.dim, hc = cfg.hc_mult;
+        std::vector<uint8_t> embed, head;
+        std::vector<float> norm_w(dim), hfn(hc * hc * dim), hbase(hc);
+        auto mat = [&](const char *name, std::vector<uint8_t> *buf, int *bf16) -> bool {
+            const CkTensor *t = c->find(name, &why);
+            if (!t || (t->dtype != APUS_CUDA_ST_BF16 && t->dtype != APUS_CUDA_ST_F32) || t->ndim != 2 ||
+                t->shape[0] != (int64_t)V || t->shape[1] != (int64_t)dim) {
+                set_error("model: bad tensor %s", name);
+                return false;
+            }
+            buf->resize(t->nbytes);
+            *bf16 = t->dtype == APUS_CUDA_ST_BF16;
+            if (c->read(*t, buf->data(), &why)) { set_error("%s", why.c_str()); return false; }
+            return true;
+        };
+        auto vec = [&](const char *name, float *out, size_t n, bool f32_only) -> bool {
+            const CkTensor *t = c->find(name, &why);
+            if (!t || t->nelem() != n || (f32_only && t->dtype != APUS_CUDA_ST_F32) ||
+                apus_cuda_ckpt_read_f32(c, name, out, n)) {
+                set_error("model: bad tensor %s", name);
+                return false;
+            }
+            return true;
+        };
+        ok = mat("embed.weight", &embed, &top.embed_bf16) && mat("head.weight", &head, &top.head_bf16) &&
+             vec("norm.weight", norm_w.data(), dim, false) && vec("hc_head_fn", hfn.data(), hc * hc * dim, true) &&
+             vec("hc_head_base", hbase.data(), hc, false) && vec("hc_head_scale", &top.hc_head_scale, 1, false);
+        if (ok) {
+            top.embed = embed.data(); top.head = head.data();
+            top.norm_w = norm_w.data(); top.hc_head_fn = hfn.data(); top.hc_head_base = hbase.data();
+            m->hc_head_scale = top.hc_head_scale;
+            ok = model_finish(m, top) == 0;
+        }
+    }
+    apus_cuda_ckpt_close(c);
     if (!ok) { apus_cuda_model_destroy(m); return nullptr; }
     return m;
 }

@@ -112,6 +112,17 @@ f32_linear_kernel(const void *__restrict__ wv, const float *__restrict__ x,
 // in flight with 16-byte asynchronous copies while the compute warps walk the
 // current tile, so the weight stream is read once per CTA.  FP32-pipe bound at batch 32
 // (2*O*K*M separately rounded operations), HBM-bound at batch 1.
+//
+// One fused multiply-add per term where that is the same number: when x and w both
+// carry BF16 values (8 significant bits each) the product has at most 16 significant
+// bits, so the f32 multiply is exact and round(acc + x*w) is what the separate add
+// returns.  That also needs the product to be a normal number or an exact zero, so a
+// tile takes the fused walk only if every operand in it is +-0 or a BF16 value with
+// 2^-60 <= |v| < 2^60 (checked while the tile is staged; the whole CTA agrees on it);
+// any other tile -- true f32 operands, subnormals, huge values, NaN -- takes the
+// two-instruction walk.  BF16 weights with BF16 activations (o-projection, LM head,
+// router, compressor projections) therefore run at half the instruction count with
+// bit-identical sums.
 constexpr int SQ_KT = 128;
 constexpr int SQ_WP_F32 = (SQ_KT + 4) * 4;               // bytes per staged weight row, f32 (+16 B: conflict-free 16-byte reads)
 constexpr int SQ_WP_BF16 = (SQ_KT + 8) * 2;              // ... BF16 rows stay BF16 in shared memory
@@ -120,6 +131,59 @@ __device__ __forceinline__ void cp_async16(void *dst, const void *src, bool vali
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
     const int bytes = valid ? 16 : 0;                    // 0 source bytes = zero fill
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+// +-0, or a BF16 value with 67 <= biased exponent < 187
+__device__ __forceinline__ bool fma_ok_f32(float v) {
+    const uint32_t u = __float_as_uint(v), a = u & 0x7fffffffu;
+    return a == 0u || ((u & 0xffffu) == 0u && a - (67u << 23) < (120u << 23));
+}
+__device__ __forceinline__ bool fma_ok_bf16x2(uint32_t p) {
+    const uint32_t lo = p & 0x7fffu, hi = (p >> 16) & 0x7fffu;
+    return (lo == 0u || lo - (67u << 7) < (120u << 7)) && (hi == 0u || hi - (67u << 7) < (120u << 7));
+}
+
+// Eight consecutive k of one output row against MTT token rows: acc[j] = acc[j] + x*w,
+// k ascending.  FUSED: one FMA per term (only for tiles whose products are exact).
+template <int MTT, bool FUSED>
+__device__ __forceinline__ void seq_walk8(float (&acc)[MTT], const float4 &wa, const float4 &wb4,
+                                          const float4 *xrow, int k8) {
+#pragma unroll
+    for (int j = 0; j < MTT; j++) {
+        const float4 xa = xrow[j * (SQ_KT / 4) + 2 * k8], xb = xrow[j * (SQ_KT / 4) + 2 * k8 + 1];
+        float a = acc[j];
+        if (FUSED) {
+            a = __fmaf_rn(xa.x, wa.x, a); a = __fmaf_rn(xa.y, wa.y, a);
+            a = __fmaf_rn(xa.z, wa.z, a); a = __fmaf_rn(xa.w, wa.w, a);
+            a = __fmaf_rn(xb.x, wb4.x, a); a = __fmaf_rn(xb.y, wb4.y, a);
+            a = __fmaf_rn(xb.z, wb4.z, a); a = __fmaf_rn(xb.w, wb4.w, a);
+        } else {
+            a = __fadd_rn(a, __fmul_rn(xa.x, wa.x)); a = __fadd_rn(a, __fmul_rn(xa.y, wa.y));
+            a = __fadd_rn(a, __fmul_rn(xa.z, wa.z)); a = __fadd_rn(a, __fmul_rn(xa.w, wa.w));
+            a = __fadd_rn(a, __fmul_rn(xb.x, wb4.x)); a = __fadd_rn(a, __fmul_rn(xb.y, wb4.y));
+            a = __fadd_rn(a, __fmul_rn(xb.z, wb4.z)); a = __fadd_rn(a, __fmul_rn(xb.w, wb4.w));
+        }
+        acc[j] = a;
+    }
+}
+
+template <bool WBF16, int MTT, bool FUSED>
+__device__ __forceinline__ void seq_walk_tile(float (&acc)[MTT], const unsigned char *wrow, const float4 *xrow) {
+#pragma unroll 2
+    for (int k8 = 0; k8 < SQ_KT / 8; k8++) {
+        float4 wa, wb4;                                   // eight consecutive k of this lane's row
+        if (WBF16) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(wrow + k8 * 16);
+            wa = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                             __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+            wb4 = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
+                              __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
+        } else {
+            wa = *reinterpret_cast<const float4 *>(wrow + k8 * 32);
+            wb4 = *reinterpret_cast<const float4 *>(wrow + k8 * 32 + 16);
+        }
+        seq_walk8<MTT, FUSED>(acc, wa, wb4, xrow, k8);
+    }
 }
 
 template <bool WBF16, int MTT, int MG, int SQ_NST>
@@ -174,41 +238,33 @@ f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, 
         __syncthreads();                                  // tile t of every thread has landed
         unsigned char *st = sq_smem + (size_t)(t % SQ_NST) * STAGE;
         float *xs = reinterpret_cast<float *>(st + W_BYTES);
-        if (rin) {                                        // bf16_linear: round the input once per tile
-            for (int idx = tid; idx < TPC * SQ_KT; idx += 256) xs[idx] = bf16_round(xs[idx]);
-            __syncthreads();
+        // one pass over the staged tile: round the input (bf16_linear) and decide whether
+        // every product of this tile is exact (see the head of this section)
+        bool exact = true;
+        for (int idx = tid; idx < TPC * SQ_KT; idx += 256) {
+            float v = xs[idx];
+            if (rin) { v = bf16_round(v); xs[idx] = v; }
+            exact &= fma_ok_f32(v);
         }
+        if (WBF16) {
+            for (int idx = tid; idx < 32 * (SQ_KT / 8); idx += 256) {
+                const int r = idx / (SQ_KT / 8), c = idx - r * (SQ_KT / 8);
+                const uint4 raw = *reinterpret_cast<const uint4 *>(st + (size_t)r * WP + c * 16);
+                exact &= fma_ok_bf16x2(raw.x) && fma_ok_bf16x2(raw.y) && fma_ok_bf16x2(raw.z) && fma_ok_bf16x2(raw.w);
+            }
+        } else {
+            for (int idx = tid; idx < 32 * (SQ_KT / 4); idx += 256) {
+                const int r = idx / (SQ_KT / 4), c = idx - r * (SQ_KT / 4);
+                const float4 v = *reinterpret_cast<const float4 *>(st + (size_t)r * WP + c * 16);
+                exact &= fma_ok_f32(v.x) && fma_ok_f32(v.y) && fma_ok_f32(v.z) && fma_ok_f32(v.w);
+            }
+        }
+        const bool fused = __syncthreads_and(exact);
         if (warp < MG) {
             const unsigned char *wrow = st + (size_t)lane * WP;
             const float4 *xrow = reinterpret_cast<const float4 *>(xs + (size_t)warp * MTT * SQ_KT);
-#pragma unroll 2
-            for (int k8 = 0; k8 < SQ_KT / 8; k8++) {
-                float4 wa, wb4;                           // eight consecutive k of this lane's row
-                if (WBF16) {
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(wrow + k8 * 16);
-                    wa = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                                     __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-                    wb4 = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
-                                      __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
-                } else {
-                    wa = *reinterpret_cast<const float4 *>(wrow + k8 * 32);
-                    wb4 = *reinterpret_cast<const float4 *>(wrow + k8 * 32 + 16);
-                }
-#pragma unroll
-                for (int j = 0; j < MTT; j++) {
-                    const float4 xa = xrow[j * (SQ_KT / 4) + 2 * k8], xb = xrow[j * (SQ_KT / 4) + 2 * k8 + 1];
-                    float a = acc[j];
-                    a = __fadd_rn(a, __fmul_rn(xa.x, wa.x));
-                    a = __fadd_rn(a, __fmul_rn(xa.y, wa.y));
-                    a = __fadd_rn(a, __fmul_rn(xa.z, wa.z));
-                    a = __fadd_rn(a, __fmul_rn(xa.w, wa.w));
-                    a = __fadd_rn(a, __fmul_rn(xb.x, wb4.x));
-                    a = __fadd_rn(a, __fmul_rn(xb.y, wb4.y));
-                    a = __fadd_rn(a, __fmul_rn(xb.z, wb4.z));
-                    a = __fadd_rn(a, __fmul_rn(xb.w, wb4.w));
-                    acc[j] = a;
-                }
-            }
+            if (fused) seq_walk_tile<WBF16, MTT, true>(acc, wrow, xrow);
+            else seq_walk_tile<WBF16, MTT, false>(acc, wrow, xrow);
         }
         __syncthreads();                                  // stage t % SQ_NST may be refilled
     }

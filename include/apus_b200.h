@@ -540,6 +540,74 @@ int apus_cuda_model_note_step(ApusCudaModel *m);
 const int64_t *apus_cuda_model_ids(ApusCudaModel *m);
 int apus_cuda_model_read(ApusCudaModel *m, float *logits, int32_t *next);
 
+/* ---- checkpoint directory -> HBM (c/st.h, c/model.h:195-470, c/layer.h:193-330) ----
+ * The reference loads <dir>/config.json and the safetensors shards named by
+ * <dir>/model.safetensors.index.json (else <dir>/weights/...), c/model.h:396-423.
+ * The reader below is host code (no GPU needed): it parses the same two config
+ * schemas, resolves tensors by the same names and dtypes and fails with the same
+ * messages; apus_cuda_model_load streams layer after layer into HBM, so host
+ * memory holds one layer at a time.  A shard is 8 bytes of little-endian header
+ * length, a JSON header {name: {dtype, shape, data_offsets}}, then the payloads
+ * (c/st.h:5-9). */
+typedef enum {                       /* c/st.h:42-46 */
+    APUS_CUDA_ST_I8, APUS_CUDA_ST_U8, APUS_CUDA_ST_F8_E8M0, APUS_CUDA_ST_F8_E4M3,
+    APUS_CUDA_ST_BF16, APUS_CUDA_ST_F16, APUS_CUDA_ST_F32, APUS_CUDA_ST_I32,
+    APUS_CUDA_ST_I64, APUS_CUDA_ST_OTHER
+} ApusCudaStDtype;
+/* The reference's ApusCfg (c/layer.h:32-41) followed by what
+ * apus_model_parse_config returns beside it (c/model.h:195-376). */
+typedef struct {
+    int dim, n_heads, head_dim, rope_head_dim, q_lora_rank;
+    int o_groups, o_lora_rank, window_size;
+    int moe_inter_dim, n_routed_experts, n_activated_experts;
+    int index_n_heads, index_head_dim, index_topk;
+    int hc_mult, hc_sinkhorn_iters;
+    int original_seq_len, beta_fast, beta_slow, vocab_size, max_pos;
+    float route_scale, swiglu_limit, hc_eps, norm_eps;
+    double rope_theta, compress_rope_theta, rope_factor;
+    int n_layers, bos_id, eos_id, n_mtp, mtp_ratio, mtp_hash, dspark;
+} ApusCudaCkptCfg;
+typedef struct ApusCudaCkpt ApusCudaCkpt;
+
+/* c/model.h:396-423: config + shard index; shard headers are parsed when a
+ * tensor of theirs is first asked for.  NULL + err on failure. */
+ApusCudaCkpt *apus_cuda_ckpt_open(const char *dir, char *err, size_t errcap);
+void apus_cuda_ckpt_close(ApusCudaCkpt *c);
+const ApusCudaCkptCfg *apus_cuda_ckpt_cfg(const ApusCudaCkpt *c);
+/* compress ratio (0 sliding window, 4 compressed sparse, 128 heavily compressed)
+ * and hash routing of a layer. */
+int apus_cuda_ckpt_layer_kind(const ApusCudaCkpt *c, int layer, int *ratio, int *hash);
+/* c/st.h:85 apus_st_set_get: 0 and the tensor's dtype / shape [8] / size, or 1. */
+int apus_cuda_ckpt_tensor(ApusCudaCkpt *c, const char *name, int *dtype, int *ndim,
+                          int64_t *shape, uint64_t *nbytes);
+/* The raw payload (nbytes must match). */
+int apus_cuda_ckpt_read(ApusCudaCkpt *c, const char *name, void *dst, uint64_t nbytes);
+/* c/st.h:73 apus_st_f32: F32 or BF16 (widened exactly) -> f32 [n]. */
+int apus_cuda_ckpt_read_f32(ApusCudaCkpt *c, const char *name, float *out, uint64_t n);
+/* c/layer.h:226-247: layers.<i>.attn.wo_a, FP8 on disk, as the BF16 bits the
+ * attention uses (dequantise, round to BF16); out [G*o_lora, n_heads*head_dim/G]. */
+int apus_cuda_ckpt_wo_a(ApusCudaCkpt *c, int layer, uint16_t *out, uint64_t n);
+/* c/layer.h:145-178 + c/attn.h:247-281: rows [0, rows) of the rope table of the
+ * layer class (ratio == 0: plain theta; else the compress theta with YaRN),
+ * cos/sin [rows, rope_head_dim/2], computed with the host's cosf/sinf like the
+ * reference does. */
+int apus_cuda_ckpt_rope(const ApusCudaCkpt *c, int ratio, int64_t rows, float *cos, float *sin);
+/* The six tensors of one routed expert (w1/w2/w3 weight + scale) into `slab`
+ * (cap >= the sum of their sizes) and views into it.  When the container keeps
+ * them adjacent (tools/convert.py's coalesced layout, c/cache.h:8-15) this is ONE
+ * positional read, otherwise six. */
+int apus_cuda_ckpt_expert(ApusCudaCkpt *c, int layer, int expert, void *slab, uint64_t cap,
+                          ApusFp4W *w1, ApusFp4W *w2, ApusFp4W *w3);
+/* c/st.h:143-144: positional reads issued so far and the bytes they returned. */
+uint64_t apus_cuda_ckpt_read_count(const ApusCudaCkpt *c);
+uint64_t apus_cuda_ckpt_read_bytes(const ApusCudaCkpt *c);
+/* c/model.h:392 apus_model_load + c/model.h:485 apus_model_state_init for HBM
+ * residency: every layer read, converted like the reference's loader does and
+ * uploaded, rope tables built for positions < max_pos (clamped to the config's
+ * max_pos), routed experts [e_lo, e_hi) only (e_hi < 0: all).  NULL on failure,
+ * message in apus_cuda_last_error(). */
+ApusCudaModel *apus_cuda_model_load(const char *dir, int batch, int max_pos, int e_lo, int e_hi);
+
 /* No counterpart in the reference.  apus_cuda_hc_pre on device pointers for
  * callers that must not allocate device memory while they run (an engine whose
  * own arena already owns the HBM, a region where allocation is forbidden, a loop

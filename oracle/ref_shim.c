@@ -171,3 +171,75 @@ void ref_head_gemv(const void *w_bf16, const float *x, float *out, int64_t O, in
     t.data = w_bf16;
     apus_head_gemv(&t, x, out, O, K);
 }
+
+/* c/model.h:392 apus_model_load on a checkpoint directory, then the greedy loop
+ * of c/apus.c:895-944 on the loaded model: what the reference's own loader makes
+ * of the files.  cfg_out receives the parsed ApusCfg followed by n_layers, bos,
+ * eos, n_mtp, mtp_ratio, mtp_hash, dspark (the layout of ApusCudaCkptCfg);
+ * ratios/hash [n_layers]; wo_a0 = layer 0's BF16 wo_a; rope rows [0, rope_rows)
+ * of the two table classes.  Returns 0, or -1 with err filled. */
+int ref_ckpt_run(const char *dir, const int64_t *prompt, int n_prompt, int n_gen,
+                 int32_t *tokens, float *logits, void *cfg_out, int *ratios, int *hash,
+                 uint16_t *wo_a0, size_t n_wo, int rope_rows, float *cos_plain,
+                 float *sin_plain, float *cos_yarn, float *sin_yarn, char *err, size_t errcap) {
+    ApusModel m;
+    if (apus_model_load(&m, dir, err, errcap)) return -1;
+    if (cfg_out) {
+        ApusCudaCkptCfg *o = cfg_out;
+        memcpy(o, &m.cfg, sizeof m.cfg);
+        o->n_layers = m.n_layers; o->bos_id = m.bos_id; o->eos_id = m.eos_id;
+        o->n_mtp = m.n_mtp; o->mtp_ratio = m.mtp_ratio; o->mtp_hash = m.mtp_hash; o->dspark = m.dspark;
+    }
+    for (int i = 0; i < m.n_layers; i++) {
+        if (ratios) ratios[i] = m.layers[i].ratio;
+        if (hash) hash[i] = m.layers[i].hash;
+    }
+    if (wo_a0) memcpy(wo_a0, m.layers[0].wo_a, n_wo * sizeof(uint16_t));
+    int half = m.cfg.rope_head_dim / 2;
+    for (int cls = 0; cls < 2 && rope_rows > 0; cls++) {
+        ApusRopeTab *t = apus_rope_tab_get(&m.cfg, cls ? 4 : 0);
+        apus_rope_tab_ensure(t, rope_rows);
+        memcpy(cls ? cos_yarn : cos_plain, t->cos, (size_t)rope_rows * half * sizeof(float));
+        memcpy(cls ? sin_yarn : sin_plain, t->sin, (size_t)rope_rows * half * sizeof(float));
+    }
+    if (n_gen > 0) {
+        int V = m.cfg.vocab_size;
+        ApusModelState st;
+        apus_model_state_init(&st, &m);
+        float *lg = malloc((size_t)V * sizeof(float));
+        apus_model_forward(&m, &st, prompt, n_prompt, lg, 0);
+        for (int g = 0; g < n_gen; g++) {
+            int tok = apus_sample_argmax(lg, (size_t)V);
+            tokens[g] = tok;
+            if (logits) memcpy(logits + (size_t)g * V, lg, (size_t)V * sizeof(float));
+            if (g + 1 < n_gen) {
+                int64_t id = tok;
+                apus_model_forward(&m, &st, &id, 1, lg, 0);
+            }
+        }
+        free(lg);
+        apus_model_state_free(&st, &m);
+    }
+    apus_model_free(&m);
+    return 0;
+}
+
+/* c/model.h:195 (static apus_model_parse_config) alone: cfg_out as in ref_ckpt_run,
+ * ratios/hash up to cap entries.  Returns 0, or -1 with err filled. */
+int ref_parse_config(const char *path, void *cfg_out, int *ratios, int *hash, int cap,
+                     char *err, size_t errcap) {
+    ApusCfg c;
+    ApusDsparkCfg dsc;
+    int n_layers = 0, *r = NULL, *h = NULL, bos, eos, n_mtp, mtp_ratio, mtp_hash, dspark;
+    if (apus_model_parse_config(&c, &n_layers, &r, &h, &bos, &eos, &n_mtp, &mtp_ratio,
+                                &mtp_hash, &dspark, &dsc, path, err, errcap))
+        return -1;
+    ApusCudaCkptCfg *o = cfg_out;
+    memset(o, 0, sizeof *o);
+    memcpy(o, &c, sizeof c);
+    o->n_layers = n_layers; o->bos_id = bos; o->eos_id = eos;
+    o->n_mtp = n_mtp; o->mtp_ratio = mtp_ratio; o->mtp_hash = mtp_hash; o->dspark = dspark;
+    for (int i = 0; i < n_layers && i < cap; i++) { ratios[i] = r[i]; hash[i] = h[i]; }
+    free(r); free(h);
+    return 0;
+}

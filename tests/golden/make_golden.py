@@ -192,6 +192,45 @@ def ref_generate(L, seed, n_layers, batch, n_prompt, n_gen, temp=0.0, top_p=1.0,
     return dict(tokens=toks, logits=logits)
 
 
+def ref_checkpoint(L, seed, n_layers, n_prompt, n_gen):
+    """The model of tests/ckpt_util.py written as a checkpoint directory, loaded
+    by the reference's own apus_model_load and run through its greedy loop
+    (oracle/ref_shim.c ref_ckpt_run): what the reference makes of the files."""
+    import tempfile
+    import ckpt_util
+    tm = cases.TinyModel(seed, rope_pair(L), n_layers)
+    V, D = tm.M["vocab"], cases.ATTN_DIMS
+    prompt = cases.prompt_ids(seed + 5, 1, n_prompt, V)[0]
+    toks = np.zeros(n_gen, np.int32)
+    logits = np.zeros((n_gen, V), np.float32)
+    cfg = capi.CkptCfg()
+    ratios, hash_ = np.zeros(n_layers, np.int32), np.zeros(n_layers, np.int32)
+    wo = np.zeros_like(tm.layers[0].attn.wo_a)
+    rows, half = D["max_pos"], D["rope_dim"] // 2
+    rope = [np.zeros((rows, half), np.float32) for _ in range(4)]
+    err = C.create_string_buffer(256)
+    with tempfile.TemporaryDirectory() as d:
+        ckpt_util.write_checkpoint(d, tm, seed=seed)
+        L.ref_ckpt_run.restype = C.c_int
+        L.ref_ckpt_run.argtypes = [C.c_char_p, C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 6 + \
+            [C.c_size_t, C.c_int] + [C.c_void_p] * 4 + [C.c_char_p, C.c_size_t]
+        rc = L.ref_ckpt_run(d.encode(), P(prompt), n_prompt, n_gen, P(toks), P(logits), C.addressof(cfg),
+                            P(ratios), P(hash_), P(wo), wo.size, rows, P(rope[0]), P(rope[1]), P(rope[2]),
+                            P(rope[3]), err, 256)
+        assert rc == 0, err.value
+    assert np.array_equal(wo, tm.layers[0].attn.wo_a)
+    return dict(tokens=toks, logits=logits, cfg=np.frombuffer(bytes(cfg), np.uint8).copy(), ratios=ratios,
+                hash=hash_, wo_a0=wo, cos_plain=rope[0], sin_plain=rope[1], cos_yarn=rope[2], sin_yarn=rope[3])
+
+
+def main_ckpt():
+    L = ref()
+    assert L is not None, "reference build not available"
+    G = ref_checkpoint(L, **CKPT_CASE)
+    np.savez_compressed(HERE / "ckpt_case.npz", **G)
+    print("wrote ckpt_case.npz:", {k: v.shape for k, v in G.items()})
+
+
 def main():
     L = ref()
     assert L is not None, "reference build not available"
@@ -291,6 +330,8 @@ def main():
     print(f"wrote {len(G)} arrays; avx2 hits {L.ref_avx2_hits()}, threads {L.ref_pool_threads()}")
 
 
+# the checkpoint-directory case (tests/ckpt_util.py)
+CKPT_CASE = dict(seed=91, n_layers=3, n_prompt=6, n_gen=8)
 # tag -> arguments of the case builders in tests/cases.py
 LINEAR_CASES = {
     "fp4_small": (11, 4, 3, 64, 256, True),
@@ -362,4 +403,9 @@ SAMPLE_CASES = {
 MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
 
 if __name__ == "__main__":
-    main()
+    import sys
+    if sys.argv[1:] == ["ckpt"]:      # only the checkpoint case (its own file)
+        main_ckpt()
+    else:
+        main()
+        main_ckpt()

@@ -202,6 +202,33 @@ def test_f32_linear(M, K, O, flags):
     assert rel_l2(out, want) <= 1e-5 if not flags & 2 else rel_l2(out, want) <= 1e-3
 
 
+@pytest.mark.parametrize("M", [1, 5, 32])
+@pytest.mark.parametrize("flags", [0, 1, 4, 5, 7])
+def test_f32_linear_bitwise_reference_order(M, flags):
+    """Reference sum order, bit for bit, over tiles that take the fused walk (BF16
+    operands: one FMA per term is the same number) and tiles that must not (true f32
+    inputs, products in the subnormal range, huge values)."""
+    rng = np.random.default_rng(100 * M + flags)
+    K, O = 1024, 96
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    if flags & 1 or flags == 4:
+        x = synth.bf16_round(x)                       # BF16 values: fused tiles
+    else:
+        x[:, :256] = synth.bf16_round(x[:, :256])     # mixed: tiles 0,1 fused, the rest not
+    wf = synth.bf16_round((rng.standard_normal((O, K)) * 0.02).astype(np.float32))
+    wf[:, 5] = 0.0; x[:, 7] = 0.0; x[0, 9] = -0.0
+    # subnormal-range products and operands outside the exact window in tiles 4 and 5
+    x[:, 520] = np.float32(1.5e-22); wf[:, 520] = synth.bf16_round(np.float32(1.3e-20).reshape(1))[0]
+    x[:, 650] = synth.bf16_round(np.float32(3e25).reshape(1))[0]
+    x[-1, 651] = np.float32(1e-41)                    # a subnormal input
+    w = synth.bf16_bits(wf) if flags & 4 else wf
+    out = np.empty((M, O), np.float32); want = np.empty((M, O), np.float32)
+    assert lib().apus_cuda_f32_linear(P(w), P(x), P(out), M, K, O, flags) == 0
+    ora().ora_f32_linear(P(w), P(x), P(want), M, K, O, flags)
+    lib().apus_cuda_forget(P(w))
+    assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+
+
 def test_head_gemv_bf16_and_hook_table():
     rng = np.random.default_rng(9)
     O, K = 12928, 4096                         # a tenth of the 129280-row LM head

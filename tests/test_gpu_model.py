@@ -442,3 +442,60 @@ def test_caller_side_graph_capture():
         ep.close()
         L.apus_cuda_use_stream(None, 1)
     assert np.array_equal(got, toks)
+
+
+def test_model_load_from_checkpoint_directory(tmp_path):
+    """apus_cuda_model_load on a checkpoint directory (tests/ckpt_util.py): the
+    same tokens and logits as the reference's own loader + greedy loop produced
+    from the same files (tests/golden/ckpt_case.npz), and bit for bit what the
+    model built from the in-memory tensors produces."""
+    import ckpt_util
+    from golden.make_golden import CKPT_CASE
+    K = np.load(Path(__file__).resolve().parent / "golden" / "ckpt_case.npz")
+    L = lib()
+    seed, n_layers, n_prompt, n_gen = (CKPT_CASE[k] for k in ("seed", "n_layers", "n_prompt", "n_gen"))
+    tm = cases.TinyModel(seed, rope(), n_layers)
+    ckpt_util.write_checkpoint(tmp_path, tm, seed=seed)       # also sets tm's wo_a to the loader's conversion
+    V = tm.M["vocab"]
+    prompt = cases.prompt_ids(seed + 5, 1, n_prompt, V)
+
+    def run(h, teacher=None):
+        lg, nxt = np.empty((1, V), np.float32), np.empty(1, np.int32)
+        toks, lgs = np.empty(n_gen, np.int32), np.empty((n_gen, V), np.float32)
+        assert L.apus_cuda_model_forward(h, P(prompt), n_prompt, P(lg), P(nxt)) == 0, L.apus_cuda_last_error()
+        for g in range(n_gen):
+            toks[g], lgs[g] = nxt[0], lg[0]
+            if g + 1 < n_gen:
+                feed = np.array([[toks[g] if teacher is None else teacher[g]]], np.int64)
+                assert L.apus_cuda_model_forward(h, P(feed), 1, P(lg), P(nxt)) == 0, L.apus_cuda_last_error()
+        return toks, lgs
+    h = L.apus_cuda_model_load(str(tmp_path).encode(), 1, 64, 0, -1)
+    assert h, L.apus_cuda_last_error()
+    try:
+        toks, lgs = run(h, teacher=K["tokens"])               # fed the reference's tokens
+        worst = max(rel_l2(lgs[g], K["logits"][g]) for g in range(n_gen))
+        assert worst <= 5e-3, worst
+        srt = np.sort(K["logits"], axis=1)
+        clear = srt[:, -1] - srt[:, -2] > MARGIN
+        assert np.array_equal(toks[clear], K["tokens"][clear]) and clear.sum() >= 3
+        assert L.apus_cuda_model_reset(h) == 0
+        free_toks, free_lgs = run(h)
+    finally:
+        L.apus_cuda_model_destroy(h)
+    h2 = L.apus_cuda_model_create(C.byref(tm.desc), 1, 64)
+    assert h2, L.apus_cuda_last_error()
+    try:
+        mem_toks, mem_lgs = run(h2)
+    finally:
+        L.apus_cuda_model_destroy(h2)
+    assert np.array_equal(free_toks, mem_toks) and np.array_equal(bits(free_lgs), bits(mem_lgs))
+    # expert-parallel placement reads only the local experts; a bad directory fails loudly
+    h3 = L.apus_cuda_model_load(str(tmp_path).encode(), 2, 64, 2, 6)
+    assert h3, L.apus_cuda_last_error()
+    L.apus_cuda_model_destroy(h3)
+    assert not L.apus_cuda_model_load(str(tmp_path / "missing").encode(), 1, 64, 0, -1)
+    assert b"cannot open" in L.apus_cuda_last_error()
+    (tmp_path / "apus-00001.safetensors").write_bytes(b"\0" * 4)
+    assert not L.apus_cuda_model_load(str(tmp_path).encode(), 1, 64, 0, -1)
+    assert b"layers.1: fp8 attn weights" in L.apus_cuda_last_error()     # the reference's message for it
+    print("checkpoint model: worst logits rel-L2 vs the reference's loaded model", worst)
