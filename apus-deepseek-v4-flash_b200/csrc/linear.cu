@@ -105,13 +105,15 @@ f32_linear_kernel(const void *__restrict__ wv, const float *__restrict__ x,
 // add rounded to f32, k ascending (reference c/attn.h:460-465, 621-666,
 // 1439-1492; c/model.h:585-636) -- bit for bit what the CPU path computes.
 // Each output is a chain of K dependent adds, so the kernel is organised
-// around the chains: one warp owns 32 output rows, a lane keeps MTT
-// accumulators (tokens) of its row; MG such warps per CTA cover MG*MTT
-// tokens.  All 256 threads of the CTA keep a three-deep ring of K tiles (32
-// rows x 128 of w, BF16 kept as BF16 and widened exactly at use; the tokens' x)
-// in flight with 16-byte asynchronous copies while the compute warps walk the
-// current tile, so the weight stream is read once per CTA.  FP32-pipe bound at batch 32
-// (2*O*K*M separately rounded operations), HBM-bound at batch 1.
+// around the chains: a lane owns R output rows (rows lane, lane + 32, ...) and
+// MTT tokens, i.e. R*MTT accumulators; MG such warps per CTA cover MG*MTT
+// tokens of the same 32*R rows.  All 256 threads keep a ring of K tiles (the
+// rows' weights as stored and the tokens' x) in flight with 16-byte
+// asynchronous copies, so the weight stream is read once per CTA.  BF16
+// weights are widened to f32 once per CTA and tile (into a second buffer) and
+// not once per warp; the walk then reads f32 rows for either storage.
+// Issue-bound at batch 32 (one multiply-add per term and the shared-memory reads
+// that feed it), add-latency bound for small grids, HBM-bound at batch 1.
 //
 // One fused multiply-add per term where that is the same number: when x and w both
 // carry BF16 values (8 significant bits each) the product has at most 16 significant
@@ -124,8 +126,20 @@ f32_linear_kernel(const void *__restrict__ wv, const float *__restrict__ x,
 // router, compressor projections) therefore run at half the instruction count with
 // bit-identical sums.
 constexpr int SQ_KT = 128;
-constexpr int SQ_WP_F32 = (SQ_KT + 4) * 4;               // bytes per staged weight row, f32 (+16 B: conflict-free 16-byte reads)
-constexpr int SQ_WP_BF16 = (SQ_KT + 8) * 2;              // ... BF16 rows stay BF16 in shared memory
+constexpr int SQ_WP = (SQ_KT + 4) * 4;                   // f32 weight row pitch, bytes (+16 B: conflict-free 16-byte reads)
+
+template <bool WBF16, int R, int MTT, int MG, int NST>
+struct SeqCfg {
+    static constexpr int ROWS = 32 * R;                  // output rows per CTA
+    static constexpr int TPC = MTT * MG;                 // tokens per CTA
+    static constexpr int ESZ = WBF16 ? 2 : 4;
+    static constexpr int WP_RAW = SQ_KT * ESZ + 16;      // pitch of a staged weight row as stored (272 / 528 bytes)
+    static constexpr int W_RAW = ROWS * WP_RAW;
+    static constexpr int X_BYTES = TPC * SQ_KT * 4;
+    static constexpr int STAGE = W_RAW + X_BYTES;
+    static constexpr int WIDE = WBF16 ? ROWS * SQ_WP : 0;  // the widened copy of the current tile
+    static constexpr int SMEM = NST * STAGE + WIDE;
+};
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src, bool valid) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -138,161 +152,196 @@ __device__ __forceinline__ bool fma_ok_f32(float v) {
     const uint32_t u = __float_as_uint(v), a = u & 0x7fffffffu;
     return a == 0u || ((u & 0xffffu) == 0u && a - (67u << 23) < (120u << 23));
 }
-__device__ __forceinline__ bool fma_ok_bf16x2(uint32_t p) {
-    const uint32_t lo = p & 0x7fffu, hi = (p >> 16) & 0x7fffu;
-    return (lo == 0u || lo - (67u << 7) < (120u << 7)) && (hi == 0u || hi - (67u << 7) < (120u << 7));
+// The same test on two BF16 values at once, per 16-bit half h = |value| bits: with
+// bit 15 set first no subtraction borrows across the halves, and bit 15 of
+// (h | 0x8000) - c then says h >= c.  Returns bit 15 / 31 set for a half that is
+// neither zero nor inside the window.
+__device__ __forceinline__ uint32_t fma_bad_bf16x2(uint32_t p) {
+    const uint32_t a = (p & 0x7fff7fffu) | 0x80008000u;
+    const uint32_t ge_lo = a - 0x21802180u;              // 67 << 7
+    const uint32_t ge_hi = a - 0x5d805d80u;              // 187 << 7
+    const uint32_t nz = a - 0x00010001u;
+    return nz & ~(ge_lo & ~ge_hi);
 }
 
-// Eight consecutive k of one output row against MTT token rows: acc[j] = acc[j] + x*w,
-// k ascending.  FUSED: one FMA per term (only for tiles whose products are exact).
-template <int MTT, bool FUSED>
-__device__ __forceinline__ void seq_walk8(float (&acc)[MTT], const float4 &wa, const float4 &wb4,
-                                          const float4 *xrow, int k8) {
+// Eight consecutive k of one output row against one token: acc = acc + x*w, k ascending.
+template <bool FUSED>
+__device__ __forceinline__ float seq_walk8(float a, const float4 &wa, const float4 &wb, const float4 &xa,
+                                           const float4 &xb) {
+    if (FUSED) {
+        a = __fmaf_rn(xa.x, wa.x, a); a = __fmaf_rn(xa.y, wa.y, a);
+        a = __fmaf_rn(xa.z, wa.z, a); a = __fmaf_rn(xa.w, wa.w, a);
+        a = __fmaf_rn(xb.x, wb.x, a); a = __fmaf_rn(xb.y, wb.y, a);
+        a = __fmaf_rn(xb.z, wb.z, a); a = __fmaf_rn(xb.w, wb.w, a);
+    } else {
+        a = __fadd_rn(a, __fmul_rn(xa.x, wa.x)); a = __fadd_rn(a, __fmul_rn(xa.y, wa.y));
+        a = __fadd_rn(a, __fmul_rn(xa.z, wa.z)); a = __fadd_rn(a, __fmul_rn(xa.w, wa.w));
+        a = __fadd_rn(a, __fmul_rn(xb.x, wb.x)); a = __fadd_rn(a, __fmul_rn(xb.y, wb.y));
+        a = __fadd_rn(a, __fmul_rn(xb.z, wb.z)); a = __fadd_rn(a, __fmul_rn(xb.w, wb.w));
+    }
+    return a;
+}
+
+// The operands of one step of eight k: R weight rows and MTT token rows.
+template <int R, int MTT>
+struct SeqOps {
+    float4 wa[R], wb[R], xa[MTT], xb[MTT];
+    __device__ __forceinline__ void load(const unsigned char *wrow, const float4 *xrow, int k8) {
 #pragma unroll
-    for (int j = 0; j < MTT; j++) {
-        const float4 xa = xrow[j * (SQ_KT / 4) + 2 * k8], xb = xrow[j * (SQ_KT / 4) + 2 * k8 + 1];
-        float a = acc[j];
-        if (FUSED) {
-            a = __fmaf_rn(xa.x, wa.x, a); a = __fmaf_rn(xa.y, wa.y, a);
-            a = __fmaf_rn(xa.z, wa.z, a); a = __fmaf_rn(xa.w, wa.w, a);
-            a = __fmaf_rn(xb.x, wb4.x, a); a = __fmaf_rn(xb.y, wb4.y, a);
-            a = __fmaf_rn(xb.z, wb4.z, a); a = __fmaf_rn(xb.w, wb4.w, a);
-        } else {
-            a = __fadd_rn(a, __fmul_rn(xa.x, wa.x)); a = __fadd_rn(a, __fmul_rn(xa.y, wa.y));
-            a = __fadd_rn(a, __fmul_rn(xa.z, wa.z)); a = __fadd_rn(a, __fmul_rn(xa.w, wa.w));
-            a = __fadd_rn(a, __fmul_rn(xb.x, wb4.x)); a = __fadd_rn(a, __fmul_rn(xb.y, wb4.y));
-            a = __fadd_rn(a, __fmul_rn(xb.z, wb4.z)); a = __fadd_rn(a, __fmul_rn(xb.w, wb4.w));
+        for (int r = 0; r < R; r++) {
+            const float4 *p = reinterpret_cast<const float4 *>(wrow + (size_t)r * 32 * SQ_WP) + 2 * k8;
+            wa[r] = p[0]; wb[r] = p[1];
         }
-        acc[j] = a;
+#pragma unroll
+        for (int j = 0; j < MTT; j++) {
+            xa[j] = xrow[j * (SQ_KT / 4) + 2 * k8]; xb[j] = xrow[j * (SQ_KT / 4) + 2 * k8 + 1];
+        }
+    }
+    template <bool FUSED>
+    __device__ __forceinline__ void walk(float (&acc)[R][MTT]) const {
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int j = 0; j < MTT; j++) acc[r][j] = seq_walk8<FUSED>(acc[r][j], wa[r], wb[r], xa[j], xb[j]);
+    }
+};
+
+// One K tile: the operands of the next step are read from shared memory while the
+// current step's chain runs (two register sets, alternating), so the chains do not
+// wait for the loads.
+template <int R, int MTT, bool FUSED>
+__device__ __forceinline__ void seq_walk_tile(float (&acc)[R][MTT], const unsigned char *wrow, const float4 *xrow) {
+    SeqOps<R, MTT> A, B;
+    A.load(wrow, xrow, 0);
+#pragma unroll 1
+    for (int k8 = 0; k8 < SQ_KT / 8; k8 += 2) {
+        B.load(wrow, xrow, k8 + 1);
+        A.template walk<FUSED>(acc);
+        if (k8 + 2 < SQ_KT / 8) A.load(wrow, xrow, k8 + 2);
+        B.template walk<FUSED>(acc);
     }
 }
 
-template <bool WBF16, int MTT, bool FUSED>
-__device__ __forceinline__ void seq_walk_tile(float (&acc)[MTT], const unsigned char *wrow, const float4 *xrow) {
-#pragma unroll 2
-    for (int k8 = 0; k8 < SQ_KT / 8; k8++) {
-        float4 wa, wb4;                                   // eight consecutive k of this lane's row
-        if (WBF16) {
-            const uint4 raw = *reinterpret_cast<const uint4 *>(wrow + k8 * 16);
-            wa = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                             __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-            wb4 = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
-                              __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
-        } else {
-            wa = *reinterpret_cast<const float4 *>(wrow + k8 * 32);
-            wb4 = *reinterpret_cast<const float4 *>(wrow + k8 * 32 + 16);
-        }
-        seq_walk8<MTT, FUSED>(acc, wa, wb4, xrow, k8);
-    }
-}
-
-template <bool WBF16, int MTT, int MG, int SQ_NST>
-__global__ void __launch_bounds__(256)
+template <bool WBF16, int R, int MTT, int MG, int NST>
+__global__ void __launch_bounds__(256, R == 2 ? 2 : 1)
 f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, float *__restrict__ out,
                       int M, int K, int O, int flags, long long w_stride, long long x_stride, int x_ld,
                       long long out_stride, int out_ld) {
-    constexpr int TPC = MTT * MG;                        // tokens per CTA
-    constexpr int WP = WBF16 ? SQ_WP_BF16 : SQ_WP_F32;   // weight row pitch, bytes
-    constexpr int W_BYTES = 32 * WP, X_BYTES = TPC * SQ_KT * 4, STAGE = W_BYTES + X_BYTES;
+    using Cf = SeqCfg<WBF16, R, MTT, MG, NST>;
+    constexpr int ROWS = Cf::ROWS, TPC = Cf::TPC, ESZ = Cf::ESZ, WP_RAW = Cf::WP_RAW, STAGE = Cf::STAGE;
     extern __shared__ __align__(16) unsigned char sq_smem[];
+    unsigned char *wide = sq_smem + (size_t)NST * STAGE;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int o0 = blockIdx.x * 32, m0 = blockIdx.y * TPC;
-    const unsigned char *wbase = reinterpret_cast<const unsigned char *>(wv) +
-                                 (size_t)blockIdx.z * w_stride * (WBF16 ? 2 : 4);
+    const int o0 = blockIdx.x * ROWS, m0 = blockIdx.y * TPC;
+    const unsigned char *wbase = reinterpret_cast<const unsigned char *>(wv) + (size_t)blockIdx.z * w_stride * ESZ;
     x += blockIdx.z * x_stride;
     out += blockIdx.z * out_stride;
     const bool rin = flags & APUS_CUDA_R_IN;
     const int nt = (K + SQ_KT - 1) / SQ_KT;
-    constexpr int ESZ = WBF16 ? 2 : 4, W_CH = SQ_KT * ESZ / 16;      // 16-byte chunks per weight row of a tile
+    constexpr int W_CH = SQ_KT * ESZ / 16;               // 16-byte chunks per stored weight row of a tile
 
-    // all 256 threads issue the asynchronous 16-byte copies of tile t into stage t % SQ_NST
+    // all 256 threads issue the asynchronous 16-byte copies of tile t into stage t % NST
     auto issue = [&](int t) {
-        unsigned char *st = sq_smem + (size_t)(t % SQ_NST) * STAGE;
+        unsigned char *st = sq_smem + (size_t)(t % NST) * STAGE;
         const int k0 = t * SQ_KT;
-        for (int idx = tid; idx < 32 * W_CH; idx += 256) {
+        for (int idx = tid; idx < ROWS * W_CH; idx += 256) {
             const int r = idx / W_CH, c = idx - r * W_CH, k = k0 + c * (16 / ESZ);
             const bool ok = o0 + r < O && k < K;
             const unsigned char *src = wbase + ((size_t)(ok ? o0 + r : 0) * K + (ok ? k : 0)) * ESZ;
-            cp_async16(st + (size_t)r * WP + c * 16, src, ok);
+            cp_async16(st + (size_t)r * WP_RAW + c * 16, src, ok);
         }
         for (int idx = tid; idx < TPC * (SQ_KT / 4); idx += 256) {
             const int r = idx / (SQ_KT / 4), c = idx - r * (SQ_KT / 4), k = k0 + c * 4;
             const bool ok = m0 + r < M && k < K;
             const float *src = x + (size_t)(ok ? m0 + r : 0) * x_ld + (ok ? k : 0);
-            cp_async16(st + W_BYTES + ((size_t)r * SQ_KT + c * 4) * 4, src, ok);
+            cp_async16(st + Cf::W_RAW + ((size_t)r * SQ_KT + c * 4) * 4, src, ok);
         }
     };
 
-    float acc[MTT];
+    float acc[R][MTT];
 #pragma unroll
-    for (int j = 0; j < MTT; j++) acc[j] = 0.f;
+    for (int r = 0; r < R; r++)
 #pragma unroll
-    for (int t = 0; t < SQ_NST - 1; t++) {
+        for (int j = 0; j < MTT; j++) acc[r][j] = 0.f;
+#pragma unroll
+    for (int t = 0; t < NST - 1; t++) {
         if (t < nt) issue(t);
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     for (int t = 0; t < nt; t++) {
-        if (t + SQ_NST - 1 < nt) issue(t + SQ_NST - 1);   // into the stage consumed at t - 1 (all passed its barrier)
+        if (t + NST - 1 < nt) issue(t + NST - 1);         // into the stage consumed at t - 1 (all passed its barrier)
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group %0;" ::"n"(SQ_NST - 1) : "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
         __syncthreads();                                  // tile t of every thread has landed
-        unsigned char *st = sq_smem + (size_t)(t % SQ_NST) * STAGE;
-        float *xs = reinterpret_cast<float *>(st + W_BYTES);
-        // one pass over the staged tile: round the input (bf16_linear) and decide whether
-        // every product of this tile is exact (see the head of this section)
+        unsigned char *st = sq_smem + (size_t)(t % NST) * STAGE;
+        float *xs = reinterpret_cast<float *>(st + Cf::W_RAW);
+        // one pass over the staged tile: round the input (bf16_linear), widen BF16 weights,
+        // and decide whether every product of this tile is exact (see the head of this section)
         bool exact = true;
-        for (int idx = tid; idx < TPC * SQ_KT; idx += 256) {
-            float v = xs[idx];
-            if (rin) { v = bf16_round(v); xs[idx] = v; }
-            exact &= fma_ok_f32(v);
+        for (int idx = tid; idx < TPC * (SQ_KT / 4); idx += 256) {
+            float4 v = reinterpret_cast<float4 *>(xs)[idx];
+            if (rin) {
+                v.x = bf16_round(v.x); v.y = bf16_round(v.y); v.z = bf16_round(v.z); v.w = bf16_round(v.w);
+                reinterpret_cast<float4 *>(xs)[idx] = v;
+            }
+            exact &= fma_ok_f32(v.x) && fma_ok_f32(v.y) && fma_ok_f32(v.z) && fma_ok_f32(v.w);
         }
         if (WBF16) {
-            for (int idx = tid; idx < 32 * (SQ_KT / 8); idx += 256) {
-                const int r = idx / (SQ_KT / 8), c = idx - r * (SQ_KT / 8);
-                const uint4 raw = *reinterpret_cast<const uint4 *>(st + (size_t)r * WP + c * 16);
-                exact &= fma_ok_bf16x2(raw.x) && fma_ok_bf16x2(raw.y) && fma_ok_bf16x2(raw.z) && fma_ok_bf16x2(raw.w);
+            uint32_t bad = 0;
+            for (int idx = tid; idx < ROWS * W_CH; idx += 256) {
+                const int r = idx / W_CH, c = idx - r * W_CH;
+                const uint4 raw = *reinterpret_cast<const uint4 *>(st + (size_t)r * WP_RAW + c * 16);
+                bad |= fma_bad_bf16x2(raw.x) | fma_bad_bf16x2(raw.y) | fma_bad_bf16x2(raw.z) | fma_bad_bf16x2(raw.w);
+                float4 *dst = reinterpret_cast<float4 *>(wide + (size_t)r * SQ_WP + c * 32);
+                dst[0] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                     __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                dst[1] = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
+                                     __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
             }
+            exact &= (bad & 0x80008000u) == 0u;
         } else {
-            for (int idx = tid; idx < 32 * (SQ_KT / 4); idx += 256) {
-                const int r = idx / (SQ_KT / 4), c = idx - r * (SQ_KT / 4);
-                const float4 v = *reinterpret_cast<const float4 *>(st + (size_t)r * WP + c * 16);
+            for (int idx = tid; idx < ROWS * W_CH; idx += 256) {
+                const int r = idx / W_CH, c = idx - r * W_CH;
+                const float4 v = *reinterpret_cast<const float4 *>(st + (size_t)r * WP_RAW + c * 16);
                 exact &= fma_ok_f32(v.x) && fma_ok_f32(v.y) && fma_ok_f32(v.z) && fma_ok_f32(v.w);
             }
         }
         const bool fused = __syncthreads_and(exact);
         if (warp < MG) {
-            const unsigned char *wrow = st + (size_t)lane * WP;
+            const unsigned char *wrow = (WBF16 ? wide : st) + (size_t)lane * SQ_WP;
             const float4 *xrow = reinterpret_cast<const float4 *>(xs + (size_t)warp * MTT * SQ_KT);
-            if (fused) seq_walk_tile<WBF16, MTT, true>(acc, wrow, xrow);
-            else seq_walk_tile<WBF16, MTT, false>(acc, wrow, xrow);
+            if (fused) seq_walk_tile<R, MTT, true>(acc, wrow, xrow);
+            else seq_walk_tile<R, MTT, false>(acc, wrow, xrow);
         }
-        __syncthreads();                                  // stage t % SQ_NST may be refilled
+        __syncthreads();                                  // stage t % NST and the widened tile may be rewritten
     }
-    if (warp < MG && o0 + lane < O) {
+    if (warp < MG) {
 #pragma unroll
-        for (int j = 0; j < MTT; j++) {
-            const int m = m0 + warp * MTT + j;
-            if (m < M) out[(size_t)m * out_ld + o0 + lane] = (flags & APUS_CUDA_R_OUT) ? bf16_round(acc[j]) : acc[j];
+        for (int r = 0; r < R; r++) {
+            const int o = o0 + lane + 32 * r;
+#pragma unroll
+            for (int j = 0; j < MTT; j++) {
+                const int m = m0 + warp * MTT + j;
+                if (o < O && m < M)
+                    out[(size_t)m * out_ld + o] = (flags & APUS_CUDA_R_OUT) ? bf16_round(acc[r][j]) : acc[r][j];
+            }
         }
     }
 }
 
-template <bool WBF16, int MTT, int MG>
-static cudaError_t seq_launch(dim3 grid, cudaStream_t st, const void *w, const float *x, float *out, int M, int K,
+template <bool WBF16, int R, int MTT, int MG, int NST>
+static cudaError_t seq_launch(cudaStream_t st, int batch, const void *w, const float *x, float *out, int M, int K,
                               int O, int flags, long long ws, long long xs, int x_ld, long long os, int out_ld) {
-    constexpr int WP = WBF16 ? SQ_WP_BF16 : SQ_WP_F32;
-    // ring depth: few tokens per CTA leave shared memory for a deeper ring, which a
-    // CTA that is alone on its SM (small O) needs to cover the memory latency
-    constexpr int SQ_NST = MTT * MG <= 8 ? 6 : 3;
-    constexpr int smem = SQ_NST * (32 * WP + MTT * MG * SQ_KT * 4);
-    auto kern = f32_linear_seq_kernel<WBF16, MTT, MG, SQ_NST>;
+    using Cf = SeqCfg<WBF16, R, MTT, MG, NST>;
+    auto kern = f32_linear_seq_kernel<WBF16, R, MTT, MG, NST>;
     static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (!configured && Cf::SMEM > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::SMEM);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    kern<<<grid, 256, smem, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
+    const dim3 grid((unsigned)ceil_div(O, Cf::ROWS), (unsigned)ceil_div(M, Cf::TPC), (unsigned)batch);
+    kern<<<grid, 256, Cf::SMEM, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
     return cudaSuccess;
 }
 
@@ -300,18 +349,20 @@ template <bool WBF16>
 static int launch_linear_seq(const void *w, long long ws, const float *x, long long xs, int x_ld, float *out,
                              long long os, int out_ld, int batch, int M, int K, int O, int flags,
                              cudaStream_t st) {
-    const unsigned gx = (unsigned)ceil_div(O, 32);
-#define SEQ_LAUNCH(MTT, MG)                                                                              \
-    APUS_CUDA_OK((seq_launch<WBF16, MTT, MG>(dim3(gx, (unsigned)ceil_div(M, (MTT) * (MG)), (unsigned)batch), st, w, x, \
-                                              out, M, K, O, flags, ws, xs, x_ld, os, out_ld)))
-    // tokens per CTA: as many as keep enough CTAs in flight, at most 32
-    const long long ctas32 = (long long)gx * batch * ceil_div(M, 32);
-    if (M == 1) SEQ_LAUNCH(1, 1);
-    else if (M <= 2) SEQ_LAUNCH(1, 2);
-    else if (M <= 4) SEQ_LAUNCH(1, 4);
-    else if (M <= 8 || ctas32 < 64) SEQ_LAUNCH(1, 8);          // 8 tokens per CTA, one per warp
-    else if (M <= 16 || ctas32 < 148) SEQ_LAUNCH(2, 8);        // 16 tokens per CTA
-    else SEQ_LAUNCH(4, 8);                                     // 32 tokens per CTA
+#define SEQ_LAUNCH(R, MTT, MG, NST)                                                                          \
+    APUS_CUDA_OK((seq_launch<WBF16, R, MTT, MG, NST>(st, batch, w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld)))
+    // Tokens per CTA: as many as keep enough CTAs in flight, at most 32.  Few tokens per
+    // CTA leave shared memory for a deep ring, which a CTA that is alone on its SM (small
+    // O) needs to cover the memory latency; the 64-row tile (R = 2) halves the staging and
+    // the x reads per term once there are CTAs enough to fill the GPU with it.
+    const long long ctas32 = (long long)ceil_div(O, 32) * batch * ceil_div(M, 32);
+    if (M == 1) SEQ_LAUNCH(1, 1, 1, 6);
+    else if (M <= 2) SEQ_LAUNCH(1, 1, 2, 6);
+    else if (M <= 4) SEQ_LAUNCH(1, 1, 4, 6);
+    else if (M <= 8 || ctas32 < 64) SEQ_LAUNCH(1, 1, 8, 6);     // 8 tokens per CTA, one per warp
+    else if (M <= 16 || ctas32 < 148) SEQ_LAUNCH(1, 2, 8, 3);   // 16 tokens per CTA
+    else if (WBF16) SEQ_LAUNCH(2, 4, 8, 2);                     // 32 tokens x 64 rows per CTA
+    else SEQ_LAUNCH(1, 4, 8, 3);                                // 32 tokens per CTA
 #undef SEQ_LAUNCH
     return 0;
 }

@@ -183,7 +183,7 @@ def model_config(a, n, cfg):
             "layers": cfg.n_layers, "layer_kinds": {"swa": kinds.count(0), "csa": kinds.count(4), "hca": kinds.count(128)},
             "hidden": cfg.dim, "n_routed_experts": cfg.n_experts, "topk": cfg.topk, "vocab": cfg.vocab,
             "batch": a.batch, "prompt_tokens": a.prompt, "parallelism": f"ep{n}" if n > 1 else "single",
-            "sum_order": "reference",
+            "sum_order": "tree" if os.environ.get("APUS_SUM_ORDER", "0") == "1" else "reference",
             "l2": "each step streams the touched experts and all dense weights (>20 GB at batch 32), far above the 126 MB L2"}
 
 
