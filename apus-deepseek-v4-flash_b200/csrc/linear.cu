@@ -107,8 +107,8 @@ f32_linear_kernel(const void *__restrict__ wv, const float *__restrict__ x,
 // Each output is a chain of K dependent adds, so the kernel is organised
 // around the chains: a lane owns R output rows (rows lane, lane + 32, ...) and
 // MTT tokens, i.e. R*MTT accumulators; MG such warps per CTA cover MG*MTT
-// tokens of the same 32*R rows.  All 256 threads keep a ring of K tiles (the
-// rows' weights as stored and the tokens' x) in flight with 16-byte
+// tokens of the same 32*R rows.  A second set of warps keeps a ring of K tiles
+// (the rows' weights as stored and the tokens' x) in flight with 16-byte
 // asynchronous copies, so the weight stream is read once per CTA.  BF16
 // weights are widened to f32 once per CTA and tile (into a second buffer) and
 // not once per warp; the walk then reads f32 rows for either storage.
@@ -138,7 +138,7 @@ struct SeqCfg {
     static constexpr int X_BYTES = TPC * SQ_KT * 4;
     static constexpr int STAGE = W_RAW + X_BYTES;
     static constexpr int WIDE = WBF16 ? ROWS * SQ_WP : 0;  // the widened copy of the current tile
-    static constexpr int SMEM = NST * STAGE + WIDE;
+    static constexpr int SMEM = NST * STAGE + 2 * WIDE + 16;   // ring, two widened halves, the tiles' exactness flags
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src, bool valid) {
@@ -222,77 +222,100 @@ __device__ __forceinline__ void seq_walk_tile(float (&acc)[R][MTT], const unsign
     }
 }
 
+// 512 threads: warps 0..7 walk the chains (warp w < MG owns MTT tokens), warps 8..15
+// stage.  While the chain warps walk tile t, the staging warps issue the copies of
+// tile t + NST - 1, wait for tile t + 1 and make their pass over it (round the input,
+// widen BF16 weights into the other half of the widened buffer, decide exactness), so
+// the chain warps execute nothing but the walk; one __syncthreads per tile hands tile
+// t + 1 over.  Every thread runs the same number of loop iterations and barriers.
+constexpr int SQ_THREADS = 512, SQ_STAGERS = 256;
+
 template <bool WBF16, int R, int MTT, int MG, int NST>
-__global__ void __launch_bounds__(256, R == 2 ? 2 : 1)
+__global__ void __launch_bounds__(SQ_THREADS, 1)
 f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, float *__restrict__ out,
                       int M, int K, int O, int flags, long long w_stride, long long x_stride, int x_ld,
                       long long out_stride, int out_ld) {
     using Cf = SeqCfg<WBF16, R, MTT, MG, NST>;
     constexpr int ROWS = Cf::ROWS, TPC = Cf::TPC, ESZ = Cf::ESZ, WP_RAW = Cf::WP_RAW, STAGE = Cf::STAGE;
+    constexpr int W_CH = SQ_KT * ESZ / 16;               // 16-byte chunks per stored weight row of a tile
+    constexpr int NWC = ROWS * W_CH / SQ_STAGERS;        // weight chunks per staging thread and tile
+    constexpr int NXC = (TPC * (SQ_KT / 4) + SQ_STAGERS - 1) / SQ_STAGERS;
+    static_assert(ROWS * W_CH % SQ_STAGERS == 0, "weight chunks must divide among the staging threads");
     extern __shared__ __align__(16) unsigned char sq_smem[];
-    unsigned char *wide = sq_smem + (size_t)NST * STAGE;
+    unsigned char *wide = sq_smem + (size_t)NST * STAGE; // [2][ROWS * SQ_WP] when WBF16
+    int *s_bad = reinterpret_cast<int *>(sq_smem + (size_t)NST * STAGE + 2 * Cf::WIDE);   // [2]: tile parity
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool stager = tid >= SQ_THREADS - SQ_STAGERS;
+    const int sid = tid - (SQ_THREADS - SQ_STAGERS);
     const int o0 = blockIdx.x * ROWS, m0 = blockIdx.y * TPC;
     const unsigned char *wbase = reinterpret_cast<const unsigned char *>(wv) + (size_t)blockIdx.z * w_stride * ESZ;
     x += blockIdx.z * x_stride;
     out += blockIdx.z * out_stride;
     const bool rin = flags & APUS_CUDA_R_IN;
     const int nt = (K + SQ_KT - 1) / SQ_KT;
-    constexpr int W_CH = SQ_KT * ESZ / 16;               // 16-byte chunks per stored weight row of a tile
 
-    // all 256 threads issue the asynchronous 16-byte copies of tile t into stage t % NST
-    auto issue = [&](int t) {
+    // a staging thread copies the same chunks of every tile: their sources are kept as
+    // pointers that only advance by a tile per iteration
+    const unsigned char *wsrc[NWC];
+    const float *xsrc[NXC];
+    unsigned row_ok = 0;                                  // bit j: weight chunk j, bit 16 + j: x chunk j
+    if (stager) {
+#pragma unroll
+        for (int j = 0; j < NWC; j++) {
+            const int id = sid + SQ_STAGERS * j, r = id / W_CH, c = id - r * W_CH;
+            const bool ok = o0 + r < O;
+            wsrc[j] = wbase + ((size_t)(ok ? o0 + r : 0) * K) * ESZ + c * 16;
+            row_ok |= ok ? 1u << j : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < NXC; j++) {
+            const int id = sid + SQ_STAGERS * j, r = id / (SQ_KT / 4), c = id - r * (SQ_KT / 4);
+            const bool ok = id < TPC * (SQ_KT / 4) && m0 + r < M;
+            xsrc[j] = x + (size_t)(ok ? m0 + r : 0) * x_ld + c * 4;
+            row_ok |= ok ? 1u << (16 + j) : 0u;
+        }
+    }
+    auto issue = [&](int t) {                             // staging threads: tile t into stage t % NST
         unsigned char *st = sq_smem + (size_t)(t % NST) * STAGE;
         const int k0 = t * SQ_KT;
-        for (int idx = tid; idx < ROWS * W_CH; idx += 256) {
-            const int r = idx / W_CH, c = idx - r * W_CH, k = k0 + c * (16 / ESZ);
-            const bool ok = o0 + r < O && k < K;
-            const unsigned char *src = wbase + ((size_t)(ok ? o0 + r : 0) * K + (ok ? k : 0)) * ESZ;
-            cp_async16(st + (size_t)r * WP_RAW + c * 16, src, ok);
+#pragma unroll
+        for (int j = 0; j < NWC; j++) {
+            const int id = sid + SQ_STAGERS * j, r = id / W_CH, c = id - r * W_CH;
+            const bool ok = (row_ok >> j & 1u) && k0 + c * (16 / ESZ) < K;
+            cp_async16(st + (size_t)r * WP_RAW + c * 16, ok ? wsrc[j] + (size_t)k0 * ESZ : wbase, ok);
         }
-        for (int idx = tid; idx < TPC * (SQ_KT / 4); idx += 256) {
-            const int r = idx / (SQ_KT / 4), c = idx - r * (SQ_KT / 4), k = k0 + c * 4;
-            const bool ok = m0 + r < M && k < K;
-            const float *src = x + (size_t)(ok ? m0 + r : 0) * x_ld + (ok ? k : 0);
-            cp_async16(st + Cf::W_RAW + ((size_t)r * SQ_KT + c * 4) * 4, src, ok);
+#pragma unroll
+        for (int j = 0; j < NXC; j++) {
+            const int id = sid + SQ_STAGERS * j, r = id / (SQ_KT / 4), c = id - r * (SQ_KT / 4);
+            if (id < TPC * (SQ_KT / 4)) {
+                const bool ok = (row_ok >> (16 + j) & 1u) && k0 + c * 4 < K;
+                cp_async16(st + Cf::W_RAW + ((size_t)r * SQ_KT + c * 4) * 4, ok ? xsrc[j] + k0 : x, ok);
+            }
         }
     };
-
-    float acc[R][MTT];
-#pragma unroll
-    for (int r = 0; r < R; r++)
-#pragma unroll
-        for (int j = 0; j < MTT; j++) acc[r][j] = 0.f;
-#pragma unroll
-    for (int t = 0; t < NST - 1; t++) {
-        if (t < nt) issue(t);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    for (int t = 0; t < nt; t++) {
-        if (t + NST - 1 < nt) issue(t + NST - 1);         // into the stage consumed at t - 1 (all passed its barrier)
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
-        __syncthreads();                                  // tile t of every thread has landed
+    // staging threads: round the input of tile t (bf16_linear), widen its BF16 weights into
+    // half t & 1 of the widened buffer, and note whether every product of the tile is exact
+    auto pass = [&](int t) {
         unsigned char *st = sq_smem + (size_t)(t % NST) * STAGE;
-        float *xs = reinterpret_cast<float *>(st + Cf::W_RAW);
-        // one pass over the staged tile: round the input (bf16_linear), widen BF16 weights,
-        // and decide whether every product of this tile is exact (see the head of this section)
+        float4 *xs4 = reinterpret_cast<float4 *>(st + Cf::W_RAW);
         bool exact = true;
-        for (int idx = tid; idx < TPC * (SQ_KT / 4); idx += 256) {
-            float4 v = reinterpret_cast<float4 *>(xs)[idx];
+        for (int idx = sid; idx < TPC * (SQ_KT / 4); idx += SQ_STAGERS) {
+            float4 v = xs4[idx];
             if (rin) {
                 v.x = bf16_round(v.x); v.y = bf16_round(v.y); v.z = bf16_round(v.z); v.w = bf16_round(v.w);
-                reinterpret_cast<float4 *>(xs)[idx] = v;
+                xs4[idx] = v;
             }
             exact &= fma_ok_f32(v.x) && fma_ok_f32(v.y) && fma_ok_f32(v.z) && fma_ok_f32(v.w);
         }
         if (WBF16) {
+            unsigned char *wd = wide + (size_t)(t & 1) * Cf::WIDE;
             uint32_t bad = 0;
-            for (int idx = tid; idx < ROWS * W_CH; idx += 256) {
-                const int r = idx / W_CH, c = idx - r * W_CH;
+#pragma unroll
+            for (int j = 0; j < NWC; j++) {
+                const int id = sid + SQ_STAGERS * j, r = id / W_CH, c = id - r * W_CH;
                 const uint4 raw = *reinterpret_cast<const uint4 *>(st + (size_t)r * WP_RAW + c * 16);
                 bad |= fma_bad_bf16x2(raw.x) | fma_bad_bf16x2(raw.y) | fma_bad_bf16x2(raw.z) | fma_bad_bf16x2(raw.w);
-                float4 *dst = reinterpret_cast<float4 *>(wide + (size_t)r * SQ_WP + c * 32);
+                float4 *dst = reinterpret_cast<float4 *>(wd + (size_t)r * SQ_WP + c * 32);
                 dst[0] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
                                      __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
                 dst[1] = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
@@ -300,22 +323,55 @@ f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, 
             }
             exact &= (bad & 0x80008000u) == 0u;
         } else {
-            for (int idx = tid; idx < ROWS * W_CH; idx += 256) {
-                const int r = idx / W_CH, c = idx - r * W_CH;
+#pragma unroll
+            for (int j = 0; j < NWC; j++) {
+                const int id = sid + SQ_STAGERS * j, r = id / W_CH, c = id - r * W_CH;
                 const float4 v = *reinterpret_cast<const float4 *>(st + (size_t)r * WP_RAW + c * 16);
                 exact &= fma_ok_f32(v.x) && fma_ok_f32(v.y) && fma_ok_f32(v.z) && fma_ok_f32(v.w);
             }
         }
-        const bool fused = __syncthreads_and(exact);
-        if (warp < MG) {
-            const unsigned char *wrow = (WBF16 ? wide : st) + (size_t)lane * SQ_WP;
-            const float4 *xrow = reinterpret_cast<const float4 *>(xs + (size_t)warp * MTT * SQ_KT);
-            if (fused) seq_walk_tile<R, MTT, true>(acc, wrow, xrow);
-            else seq_walk_tile<R, MTT, false>(acc, wrow, xrow);
+        if (!exact) s_bad[t & 1] = 1;                     // every writer stores the same value
+    };
+    // the staging threads' own barrier (hardware barrier 1; barrier 0 is __syncthreads)
+    auto stagers_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(SQ_STAGERS) : "memory"); };
+
+    float acc[R][MTT];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int j = 0; j < MTT; j++) acc[r][j] = 0.f;
+    if (tid < 2) s_bad[tid] = 0;
+    __syncthreads();
+    if (stager) {
+#pragma unroll
+        for (int t = 0; t < NST - 1; t++) {
+            if (t < nt) issue(t);
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        __syncthreads();                                  // stage t % NST and the widened tile may be rewritten
+        asm volatile("cp.async.wait_group %0;" ::"n"(NST - 2) : "memory");
+        stagers_sync();                                   // tile 0 of every staging thread has landed
+        pass(0);
     }
-    if (warp < MG) {
+    __syncthreads();                                      // tile 0 is staged
+    for (int t = 0; t < nt; t++) {
+        if (stager) {
+            // stage (t - 1) % NST was walked in the last iteration and is free again
+            if (t + NST - 1 < nt) issue(t + NST - 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (sid == 0) s_bad[(t + 1) & 1] = 0;         // read last at tile t - 1
+            asm volatile("cp.async.wait_group %0;" ::"n"(NST - 2) : "memory");
+            stagers_sync();                               // tile t + 1 of every staging thread has landed
+            if (t + 1 < nt) pass(t + 1);
+        } else if (warp < MG) {
+            const unsigned char *stg = sq_smem + (size_t)(t % NST) * STAGE;
+            const unsigned char *wrow = (WBF16 ? wide + (size_t)(t & 1) * Cf::WIDE : stg) + (size_t)lane * SQ_WP;
+            const float4 *xrow = reinterpret_cast<const float4 *>(stg + Cf::W_RAW) + (size_t)warp * MTT * (SQ_KT / 4);
+            if (s_bad[t & 1]) seq_walk_tile<R, MTT, false>(acc, wrow, xrow);
+            else seq_walk_tile<R, MTT, true>(acc, wrow, xrow);
+        }
+        __syncthreads();                                  // tile t + 1 is staged; tile t's buffers are free
+    }
+    if (!stager && warp < MG) {
 #pragma unroll
         for (int r = 0; r < R; r++) {
             const int o = o0 + lane + 32 * r;
@@ -341,7 +397,7 @@ static cudaError_t seq_launch(cudaStream_t st, int batch, const void *w, const f
         configured = true;
     }
     const dim3 grid((unsigned)ceil_div(O, Cf::ROWS), (unsigned)ceil_div(M, Cf::TPC), (unsigned)batch);
-    kern<<<grid, 256, Cf::SMEM, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
+    kern<<<grid, SQ_THREADS, Cf::SMEM, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
     return cudaSuccess;
 }
 
@@ -361,7 +417,7 @@ static int launch_linear_seq(const void *w, long long ws, const float *x, long l
     else if (M <= 4) SEQ_LAUNCH(1, 1, 4, 6);
     else if (M <= 8 || ctas32 < 64) SEQ_LAUNCH(1, 1, 8, 6);     // 8 tokens per CTA, one per warp
     else if (M <= 16 || ctas32 < 148) SEQ_LAUNCH(1, 2, 8, 3);   // 16 tokens per CTA
-    else if (WBF16) SEQ_LAUNCH(2, 4, 8, 2);                     // 32 tokens x 64 rows per CTA
+    else if constexpr (WBF16) SEQ_LAUNCH(2, 4, 8, 3);           // 32 tokens x 64 rows per CTA
     else SEQ_LAUNCH(1, 4, 8, 3);                                // 32 tokens per CTA
 #undef SEQ_LAUNCH
     return 0;
