@@ -267,7 +267,7 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     const float scale = (float)pow((double)d, -0.5);
     if (sparse_attn(b.q, A.sink, h, d, b.idxs, win + compw, B, scale, S.win.p, win,
                     ratio ? S.comp.cache.p : nullptr, ratio ? S.comp.nb : 0, 0, b.o, st, (long long)win * d,
-                    ratio ? (long long)S.comp.cap * d : 0))
+                    ratio ? (long long)S.comp.cap * d : 0, b.sa, b.sa_cap))
         return 1;
     if (row_ops(b.o, d, b.o, d, B * h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs_pos, B * h, 0, st, dp)) return 1;
     // grouped low-rank o-projection (c/attn.h:1692-1737)

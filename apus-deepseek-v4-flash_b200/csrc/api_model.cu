@@ -31,7 +31,7 @@ struct LayerDev {
 };
 
 struct BlockBufs {
-    float *x, *y, *sub, *post, *comb, *hn;
+    float *x, *y, *sub, *post, *comb, *raw;   // raw: mHC scratch of the owner (NULL: the library's)
 };
 
 // One token of B sequences through one block (reference c/layer.h:495-545), in
@@ -46,7 +46,7 @@ int block_attn_half(const LayerDev &L, StateDev &S, float **h, float **hn, int B
     const long long rp = ratio ? pos + 1 - ratio : -1;
     const float *cs_rp = rp >= 0 ? L.cs + (size_t)rp * half2 : cs_pos;
     if (mhc_pre(*h, dim, hc, L.hc_attn_fn, L.hc_attn_scale, L.hc_attn_base, norm_eps, hc_eps, iters,
-                L.attn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st))
+                L.attn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st, bb.raw))
         return 1;
     if (attn_step(L.attn, S, bb.x, pos, cs_pos, cs_rp, bb.sub, sb, nullptr, st, pos_dev, L.cs)) return 1;
     if (mhc_post(bb.sub, *h, bb.post, bb.comb, *hn, dim, hc, B, st)) return 1;
@@ -57,7 +57,7 @@ int block_attn_half(const LayerDev &L, StateDev &S, float **h, float **hn, int B
 int block_ffn_pre(const LayerDev &L, float *h, int B, int hc, int iters, float hc_eps, float norm_eps,
                   const BlockBufs &bb, cudaStream_t st) {
     return mhc_pre(h, L.attn.cfg.dim, hc, L.hc_ffn_fn, L.hc_ffn_scale, L.hc_ffn_base, norm_eps, hc_eps, iters,
-                   L.ffn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st);
+                   L.ffn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st, bb.raw);
 }
 int block_ffn_post(const LayerDev &L, const float *sub, float **h, float **hn, int B, int hc, const BlockBufs &bb,
                    cudaStream_t st) {
@@ -156,6 +156,9 @@ struct ApusCudaModel {
     int embed_bf16 = 0, head_bf16 = 0;
     const float *norm_w = nullptr, *hc_head_fn = nullptr, *hc_head_base = nullptr;
     long long pos = 0;
+    // the stream this model's work is enqueued on: the library stream unless the model was
+    // given one of its own (models that step side by side, apus_cuda_model_set_stream)
+    cudaStream_t stream = nullptr, own_stream = nullptr;
     int e_lo = 0, e_hi = 0;                // routed experts resident here (expert parallelism)
     float *h_cur = nullptr, *h_alt = nullptr;   // hidden state between the pieces of a step
     // the position also lives on the device: the kernels of a step read it there, so
@@ -172,12 +175,14 @@ struct ApusCudaModel {
     long long steps_run = 0;
     WeightOwner own;                       // every weight copy made for this model
     std::map<const void *, DevBuf *> rope; // rope rows by host table (layers of a kind share one)
-    DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, ws[24];
+    DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, raw, sa, ws[24];
     StepBufs sb;
 };
 
+static inline cudaStream_t mstream(const ApusCudaModel *m) { return m->stream ? m->stream : ctx().stream; }
 static BlockBufs model_bufs(ApusCudaModel *m) {
-    return {m->x.as<float>(), m->y.as<float>(), m->sub.as<float>(), m->post.as<float>(), m->comb.as<float>(), nullptr};
+    return {m->x.as<float>(), m->y.as<float>(), m->sub.as<float>(), m->post.as<float>(), m->comb.as<float>(),
+            m->raw.as<float>()};
 }
 static int model_embed(ApusCudaModel *m, cudaStream_t st) {
     m->h_cur = m->h0.as<float>(); m->h_alt = m->h1.as<float>();
@@ -187,7 +192,7 @@ static int model_embed(ApusCudaModel *m, cudaStream_t st) {
 static int model_head(ApusCudaModel *m, cudaStream_t st) {
     const int B = m->B, dim = m->dim;
     if (mhc_head(m->h_cur, dim, m->hc, m->hc_head_fn, m->hc_head_scale, m->hc_head_base, m->norm_eps, m->hc_eps,
-                 m->yh.as<float>(), B, st))
+                 m->yh.as<float>(), B, st, m->raw.as<float>()))
         return 1;
     if (rms_norm(m->yh.as<float>(), m->norm_w, m->norm_eps, m->yn.as<float>(), dim, B, st)) return 1;
     if (f32_linear(m->head, m->yn.as<float>(), m->logits.as<float>(), B, dim, m->vocab,
@@ -279,13 +284,14 @@ void apus_cuda_model_destroy(ApusCudaModel *m) {
     cudaDeviceSynchronize();
     for (auto &s : m->states) s.release();
     for (int i = 0; i < 2; i++) if (m->gexec[i]) cudaGraphExecDestroy(m->gexec[i]);
+    if (m->own_stream) cudaStreamDestroy(m->own_stream);
     m->pos_dev.release();
     m->rng.release(); m->probs.release();
     for (auto &L : m->layers) if (L.moe) apus_cuda_moe_destroy(L.moe);
     m->own.release();
     for (auto &kv : m->rope) { kv.second->release(); delete kv.second; }
     DevBuf *bufs[] = {&m->h0, &m->h1, &m->x, &m->y, &m->sub, &m->post, &m->comb, &m->yh, &m->yn, &m->logits,
-                      &m->tok, &m->ids, &m->hist};
+                      &m->tok, &m->ids, &m->hist, &m->raw, &m->sa};
     for (DevBuf *b : bufs) b->release();
     for (auto &b : m->ws) b.release();
     delete m;
@@ -299,8 +305,8 @@ int apus_cuda_model_reset(ApusCudaModel *m) {
         if (attn_state_init(c, m->states[i], m->B, cap)) return 1;
     }
     if (m->pos_dev.get(256, nullptr)) return 1;
-    APUS_CUDA_OK(cudaMemsetAsync(m->pos_dev.p, 0, 256, ctx().stream));
-    APUS_CUDA_OK(cudaStreamSynchronize(ctx().stream));
+    APUS_CUDA_OK(cudaMemsetAsync(m->pos_dev.p, 0, 256, mstream(m)));
+    APUS_CUDA_OK(cudaStreamSynchronize(mstream(m)));
     m->pos = 0;
     return 0;
 }
@@ -354,7 +360,8 @@ static int model_finish(ApusCudaModel *m, const ApusCudaModelDesc &d) {
         m->x.get(B * dim * 4, nullptr) || m->y.get(B * dim * 4, nullptr) || m->sub.get(B * dim * 4, nullptr) ||
         m->post.get(B * hc * 4, nullptr) || m->comb.get(B * hc * hc * 4, nullptr) ||
         m->yh.get(B * dim * 4, nullptr) || m->yn.get(B * dim * 4, nullptr) ||
-        m->logits.get(B * (size_t)d.vocab * 4, nullptr) || m->tok.get(B * 4, nullptr) || m->ids.get(B * 8, nullptr))
+        m->logits.get(B * (size_t)d.vocab * 4, nullptr) || m->tok.get(B * 4, nullptr) || m->ids.get(B * 8, nullptr) ||
+        m->raw.get(B * ((2 + hc) * hc + 1) * 4, nullptr))
         return 1;
     // step buffers sized for the widest layer configuration
     ApusAttnCfg widest = m->layers[0].attn.cfg;
@@ -363,7 +370,10 @@ static int model_finish(ApusCudaModel *m, const ApusCudaModelDesc &d) {
         if (c.has_indexer) { widest.has_indexer = 1; widest.idx_heads = c.idx_heads; widest.idx_dim = c.idx_dim; widest.idx_topk = c.idx_topk; }
     }
     widest.has_indexer = 0;                      // size the index row for the dense (largest) case
-    if (attn_step_bufs(widest, m->max_nb > widest.idx_topk ? m->max_nb : widest.idx_topk, m->B, m->ws, &m->sb)) return 1;
+    const long long wide_nb = m->max_nb > widest.idx_topk ? m->max_nb : widest.idx_topk;
+    if (attn_step_bufs(widest, wide_nb, m->B, m->ws, &m->sb)) return 1;
+    m->sb.sa_cap = sparse_attn_scratch(widest.n_heads, (int)(widest.window + wide_nb + 8), m->B);
+    if (m->sa.get(m->sb.sa_cap, &m->sb.sa)) return 1;
     return apus_cuda_model_reset(m);
 }
 
@@ -502,7 +512,7 @@ int64_t apus_cuda_model_pos(const ApusCudaModel *m) { return m ? m->pos : -1; }
 
 int apus_cuda_model_set_sampling(ApusCudaModel *m, float temp, float top_p, uint64_t seed) {
     if (!m) { set_error("NULL model"); return 1; }
-    cudaStream_t st = ctx().stream;
+    cudaStream_t st = mstream(m);
     APUS_CUDA_OK(cudaStreamSynchronize(st));
     for (int i = 0; i < 2; i++)                       // the head of a recorded step changes
         if (m->gexec[i]) { cudaGraphExecDestroy(m->gexec[i]); m->gexec[i] = nullptr; }
@@ -527,97 +537,176 @@ ApusCudaMoe *apus_cuda_model_moe(ApusCudaModel *m, int layer) {
     return m->layers[layer].moe;
 }
 
-int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int32_t *next) {
+int apus_cuda_model_set_stream(ApusCudaModel *m, void *stream, int create) {
     if (!m) { set_error("NULL model"); return 1; }
-    if (s <= 0) return 0;
-    APUS_REQUIRE(m->pos + s <= m->max_pos, "model_forward: position %lld + %d exceeds max_pos %d", m->pos, s, m->max_pos);
-    cudaStream_t st = ctx().stream;
-    std::vector<int64_t> col((size_t)m->B);
-    for (int t = 0; t < s; t++) {
-        for (int b = 0; b < m->B; b++) col[b] = ids[(size_t)b * s + t];
-        APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, col.data(), (size_t)m->B * 8, cudaMemcpyHostToDevice, st));
-        APUS_CUDA_OK(cudaStreamSynchronize(st));      // `col` is reused by the next position
-        if (model_step(m, t == s - 1, st)) return 1;
+    APUS_CUDA_OK(cudaStreamSynchronize(mstream(m)));
+    for (int i = 0; i < 2; i++)                       // a recorded step belongs to the stream it was recorded on
+        if (m->gexec[i]) { cudaGraphExecDestroy(m->gexec[i]); m->gexec[i] = nullptr; }
+    if (create) {
+        if (!m->own_stream) APUS_CUDA_OK(cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking));
+        m->stream = m->own_stream;
+    } else {
+        m->stream = (cudaStream_t)stream;
     }
-    if (logits) APUS_CUDA_OK(cudaMemcpyAsync(logits, m->logits.p, (size_t)m->B * m->vocab * 4, cudaMemcpyDeviceToHost, st));
-    if (next) APUS_CUDA_OK(cudaMemcpyAsync(next, m->tok.p, (size_t)m->B * 4, cudaMemcpyDeviceToHost, st));
-    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    m->steps_run = 0;                                 // the next step runs eagerly on the new stream first
+    return 0;
+}
+
+// Every stream of the group waits for what the others have enqueued so far, then
+// `ev` is recorded on the first one: a time stamp all of the group's work lies
+// before (or after) without stopping the host.
+static int group_mark(ApusCudaModel *const *ms, int n, cudaEvent_t *tmp, cudaEvent_t ev) {
+    cudaStream_t s0 = mstream(ms[0]);
+    for (int i = 1; i < n; i++) {
+        APUS_CUDA_OK(cudaEventRecord(tmp[i], mstream(ms[i])));
+        APUS_CUDA_OK(cudaStreamWaitEvent(s0, tmp[i], 0));
+    }
+    APUS_CUDA_OK(cudaEventRecord(ev, s0));
+    for (int i = 1; i < n; i++) APUS_CUDA_OK(cudaStreamWaitEvent(mstream(ms[i]), ev, 0));
+    return 0;
+}
+static int group_sync(ApusCudaModel *const *ms, int n) {
+    for (int i = 0; i < n; i++) APUS_CUDA_OK(cudaStreamSynchronize(mstream(ms[i])));
+    return 0;
+}
+static int group_check(ApusCudaModel *const *ms, int n, const char *who) {
+    APUS_REQUIRE(ms && n >= 1 && n <= 16, "%s: 1..16 models", who);
+    for (int i = 0; i < n; i++) {
+        APUS_REQUIRE(ms[i], "%s: NULL model", who);
+        for (int j = 0; j < i; j++)
+            APUS_REQUIRE(mstream(ms[i]) != mstream(ms[j]) || n == 1,
+                         "%s: models %d and %d share a stream (apus_cuda_model_set_stream)", who, j, i);
+    }
+    return 0;
+}
+
+int apus_cuda_model_forward_group(ApusCudaModel *const *ms, int n, const int64_t *const *ids, int s,
+                                  float *const *logits, int32_t *const *next) {
+    if (group_check(ms, n, "model_forward")) return 1;
+    if (s <= 0) return 0;
+    for (int i = 0; i < n; i++)
+        APUS_REQUIRE(ms[i]->pos + s <= ms[i]->max_pos, "model_forward: position %lld + %d exceeds max_pos %d",
+                     ms[i]->pos, s, ms[i]->max_pos);
+    std::vector<std::vector<int64_t>> col((size_t)n);
+    for (int t = 0; t < s; t++) {
+        for (int i = 0; i < n; i++) {
+            ApusCudaModel *m = ms[i];
+            col[i].resize((size_t)m->B);
+            for (int b = 0; b < m->B; b++) col[i][b] = ids[i][(size_t)b * s + t];
+            APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, col[i].data(), (size_t)m->B * 8, cudaMemcpyHostToDevice, mstream(m)));
+        }
+        if (s > 1 && group_sync(ms, n)) return 1;         // `col` is reused by the next position
+        for (int i = 0; i < n; i++)
+            if (model_step(ms[i], t == s - 1, mstream(ms[i]))) return 1;
+    }
+    for (int i = 0; i < n; i++) {
+        ApusCudaModel *m = ms[i];
+        if (logits && logits[i])
+            APUS_CUDA_OK(cudaMemcpyAsync(logits[i], m->logits.p, (size_t)m->B * m->vocab * 4, cudaMemcpyDeviceToHost, mstream(m)));
+        if (next && next[i])
+            APUS_CUDA_OK(cudaMemcpyAsync(next[i], m->tok.p, (size_t)m->B * 4, cudaMemcpyDeviceToHost, mstream(m)));
+    }
+    if (group_sync(ms, n)) return 1;
     int stt = gemm_tc_status(1);
     APUS_REQUIRE(stt == 0, "model_forward: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
+int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int32_t *next) {
+    if (!m) { set_error("NULL model"); return 1; }
+    return apus_cuda_model_forward_group(&m, 1, &ids, s, &logits, &next);
+}
+
+int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n, const int64_t *const *prompts, int n_prompt,
+                                   int n_gen, int32_t *const *out_tokens, float *ms_prefill, float *ms_decode) {
+    if (group_check(ms, n, "model_generate")) return 1;
+    APUS_REQUIRE(n_prompt >= 1 && n_gen >= 1, "model_generate: needs a prompt and at least one token to generate");
+    for (int i = 0; i < n; i++)
+        APUS_REQUIRE(ms[i]->pos + n_prompt + n_gen - 1 <= ms[i]->max_pos, "model_generate: %d + %d tokens exceed max_pos %d",
+                     n_prompt, n_gen, ms[i]->max_pos);
+    cudaEvent_t e0, e1, e2, tmp[16];
+    APUS_CUDA_OK(cudaEventCreate(&e0)); APUS_CUDA_OK(cudaEventCreate(&e1)); APUS_CUDA_OK(cudaEventCreate(&e2));
+    for (int i = 0; i < n; i++) APUS_CUDA_OK(cudaEventCreateWithFlags(&tmp[i], cudaEventDisableTiming));
+    // the prompt columns are staged on the device first so the loop has no host copies
+    std::vector<std::vector<int64_t>> cols((size_t)n);
+    std::vector<void *> dcols((size_t)n);
+    for (int i = 0; i < n; i++) {
+        ApusCudaModel *m = ms[i];
+        if (m->hist.get((size_t)m->B * n_gen * 4, nullptr)) return 1;
+        cols[i].resize((size_t)n_prompt * m->B);
+        for (int t = 0; t < n_prompt; t++)
+            for (int b = 0; b < m->B; b++) cols[i][(size_t)t * m->B + b] = prompts[i][(size_t)b * n_prompt + t];
+        if (m->ws[23].get(cols[i].size() * 8, &dcols[i])) return 1;
+        APUS_CUDA_OK(cudaMemcpyAsync(dcols[i], cols[i].data(), cols[i].size() * 8, cudaMemcpyHostToDevice, mstream(m)));
+    }
+    if (group_mark(ms, n, tmp, e0)) return 1;
+    for (int t = 0; t < n_prompt; t++)
+        for (int i = 0; i < n; i++) {
+            ApusCudaModel *m = ms[i];
+            APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, (const int64_t *)dcols[i] + (size_t)t * m->B, (size_t)m->B * 8,
+                                         cudaMemcpyDeviceToDevice, mstream(m)));
+            if (model_step(m, t == n_prompt - 1, mstream(m))) return 1;
+        }
+    if (group_mark(ms, n, tmp, e1)) return 1;
+    for (int g = 0; g < n_gen; g++)
+        for (int i = 0; i < n; i++) {                     // the models' steps alternate, each on its own stream
+            ApusCudaModel *m = ms[i];
+            next_ids_kernel<<<1, 32, 0, mstream(m)>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), m->hist.as<int32_t>(),
+                                                     m->B, g, n_gen);
+            if (g + 1 < n_gen && model_step(m, true, mstream(m))) return 1;
+        }
+    if (group_mark(ms, n, tmp, e2)) return 1;
+    for (int i = 0; i < n; i++)
+        APUS_CUDA_OK(cudaMemcpyAsync(out_tokens[i], ms[i]->hist.p, (size_t)ms[i]->B * n_gen * 4, cudaMemcpyDeviceToHost,
+                                     mstream(ms[i])));
+    if (group_sync(ms, n)) return 1;
+    float a = 0, b = 0;
+    cudaEventElapsedTime(&a, e0, e1); cudaEventElapsedTime(&b, e1, e2);
+    if (ms_prefill) *ms_prefill = a;
+    if (ms_decode) *ms_decode = b;
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    for (int i = 0; i < n; i++) cudaEventDestroy(tmp[i]);
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "model_generate: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
     return 0;
 }
 
 int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt, int n_prompt, int n_gen, int32_t *out_tokens,
                              float *ms_prefill, float *ms_decode) {
     if (!m) { set_error("NULL model"); return 1; }
-    APUS_REQUIRE(n_prompt >= 1 && n_gen >= 1, "model_generate: needs a prompt and at least one token to generate");
-    APUS_REQUIRE(m->pos + n_prompt + n_gen - 1 <= m->max_pos, "model_generate: %d + %d tokens exceed max_pos %d",
-                 n_prompt, n_gen, m->max_pos);
-    cudaStream_t st = ctx().stream;
-    cudaEvent_t e0, e1, e2;
-    APUS_CUDA_OK(cudaEventCreate(&e0)); APUS_CUDA_OK(cudaEventCreate(&e1)); APUS_CUDA_OK(cudaEventCreate(&e2));
-    if (m->hist.get((size_t)m->B * n_gen * 4, nullptr)) return 1;
-    // the prompt columns are staged on the device first so the loop has no host copies
-    std::vector<int64_t> cols((size_t)n_prompt * m->B);
-    for (int t = 0; t < n_prompt; t++)
-        for (int b = 0; b < m->B; b++) cols[(size_t)t * m->B + b] = prompt[(size_t)b * n_prompt + t];
-    void *dcols;
-    if (m->ws[23].get(cols.size() * 8, &dcols)) return 1;
-    APUS_CUDA_OK(cudaMemcpyAsync(dcols, cols.data(), cols.size() * 8, cudaMemcpyHostToDevice, st));
-    APUS_CUDA_OK(cudaEventRecord(e0, st));
-    for (int t = 0; t < n_prompt; t++) {
-        APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, (const int64_t *)dcols + (size_t)t * m->B, (size_t)m->B * 8,
-                                     cudaMemcpyDeviceToDevice, st));
-        if (model_step(m, t == n_prompt - 1, st)) return 1;
-    }
-    APUS_CUDA_OK(cudaEventRecord(e1, st));
-    for (int g = 0; g < n_gen; g++) {
-        next_ids_kernel<<<1, 32, 0, st>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), m->hist.as<int32_t>(), m->B, g, n_gen);
-        if (g + 1 < n_gen && model_step(m, true, st)) return 1;
-    }
-    APUS_CUDA_OK(cudaEventRecord(e2, st));
-    APUS_CUDA_OK(cudaMemcpyAsync(out_tokens, m->hist.p, (size_t)m->B * n_gen * 4, cudaMemcpyDeviceToHost, st));
-    APUS_CUDA_OK(cudaStreamSynchronize(st));
-    float a = 0, b = 0;
-    cudaEventElapsedTime(&a, e0, e1); cudaEventElapsedTime(&b, e1, e2);
-    if (ms_prefill) *ms_prefill = a;
-    if (ms_decode) *ms_decode = b;
-    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
-    int stt = gemm_tc_status(1);
-    APUS_REQUIRE(stt == 0, "model_generate: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
-    return 0;
+    return apus_cuda_model_generate_group(&m, 1, &prompt, n_prompt, n_gen, &out_tokens, ms_prefill, ms_decode);
 }
 
 // ---- one step in pieces (expert parallelism: the caller runs the MoE sublayer) ----------------
 int apus_cuda_model_set_ids(ApusCudaModel *m, const int64_t *ids) {
     if (!m) { set_error("NULL model"); return 1; }
-    APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, ids, (size_t)m->B * 8, cudaMemcpyDefault, ctx().stream));
+    APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, ids, (size_t)m->B * 8, cudaMemcpyDefault, mstream(m)));
     return 0;
 }
 int apus_cuda_model_begin_step(ApusCudaModel *m) {
     if (!m) { set_error("NULL model"); return 1; }
     APUS_REQUIRE(m->pos < m->max_pos, "model step: position %lld reaches max_pos %d", m->pos, m->max_pos);
-    return model_embed(m, ctx().stream);
+    return model_embed(m, mstream(m));
 }
 int apus_cuda_model_attn_half(ApusCudaModel *m, int layer) {
     if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_attn_half: bad layer"); return 1; }
     return block_attn_half(m->layers[layer], m->states[layer], &m->h_cur, &m->h_alt, m->B, m->pos, m->hc, m->iters,
-                           m->hc_eps, m->norm_eps, model_bufs(m), m->sb, ctx().stream, m->pos_dev.as<long long>());
+                           m->hc_eps, m->norm_eps, model_bufs(m), m->sb, mstream(m), m->pos_dev.as<long long>());
 }
 const float *apus_cuda_model_ffn_input(ApusCudaModel *m, int layer) {
     if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_ffn_input: bad layer"); return nullptr; }
     if (block_ffn_pre(m->layers[layer], m->h_cur, m->B, m->hc, m->iters, m->hc_eps, m->norm_eps, model_bufs(m),
-                      ctx().stream))
+                      mstream(m)))
         return nullptr;
     return m->x.as<float>();
 }
 int apus_cuda_model_ffn_output(ApusCudaModel *m, int layer, const float *sub) {
     if (!m || layer < 0 || layer >= m->n_layers) { set_error("model_ffn_output: bad layer"); return 1; }
-    return block_ffn_post(m->layers[layer], sub, &m->h_cur, &m->h_alt, m->B, m->hc, model_bufs(m), ctx().stream);
+    return block_ffn_post(m->layers[layer], sub, &m->h_cur, &m->h_alt, m->B, m->hc, model_bufs(m), mstream(m));
 }
 int apus_cuda_model_end_step(ApusCudaModel *m, int want_logits, int feed_back) {
     if (!m) { set_error("NULL model"); return 1; }
-    cudaStream_t st = ctx().stream;
+    cudaStream_t st = mstream(m);
     if (want_logits) {
         if (model_head(m, st)) return 1;
         if (feed_back)
@@ -645,7 +734,7 @@ int apus_cuda_model_note_step(ApusCudaModel *m) {
 const int64_t *apus_cuda_model_ids(ApusCudaModel *m) { return m ? m->ids.as<int64_t>() : nullptr; }
 int apus_cuda_model_read(ApusCudaModel *m, float *logits, int32_t *next) {
     if (!m) { set_error("NULL model"); return 1; }
-    cudaStream_t st = ctx().stream;
+    cudaStream_t st = mstream(m);
     if (logits) APUS_CUDA_OK(cudaMemcpyAsync(logits, m->logits.p, (size_t)m->B * m->vocab * 4, cudaMemcpyDeviceToHost, st));
     if (next) APUS_CUDA_OK(cudaMemcpyAsync(next, m->tok.p, (size_t)m->B * 4, cudaMemcpyDeviceToHost, st));
     APUS_CUDA_OK(cudaStreamSynchronize(st));

@@ -1,4 +1,5 @@
 // Stable top-k selection and index-gathered sparse attention.
+#include <map>
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -297,21 +298,32 @@ __global__ void compact_ids_kernel(const int32_t *__restrict__ idxs, int idxw,
     if (tid == 0) ns[t] = s_base;
 }
 
+// Scores / compacted ids between the kernels of a call: the caller's scratch (a model
+// object keeps its own), else one buffer of the library, which only grows.
 static void *g_scratch = nullptr;
 static size_t g_scratch_cap = 0;
-static int ensure_scratch(size_t bytes) {
-    if (bytes <= g_scratch_cap) return 0;
-    if (g_scratch) cudaFree(g_scratch);
+static void *ensure_scratch(size_t bytes) {
+    if (bytes <= g_scratch_cap) return g_scratch;
+    if (g_scratch) { cudaDeviceSynchronize(); cudaFree(g_scratch); }
     g_scratch = nullptr; g_scratch_cap = 0;
-    APUS_CUDA_OK(cudaMalloc(&g_scratch, bytes));
+    if (cudaMalloc(&g_scratch, bytes) != cudaSuccess) {
+        set_error("sparse_attn: scratch of %zu bytes", bytes);
+        g_scratch = nullptr;
+        return nullptr;
+    }
     g_scratch_cap = bytes;
-    return 0;
+    return g_scratch;
+}
+size_t sparse_attn_scratch(int h, int idxw, int s) {
+    const size_t sc_bytes = (size_t)s * h * idxw * sizeof(float), ids_bytes = (size_t)s * idxw * sizeof(int32_t);
+    return ((sc_bytes + ids_bytes + 255) & ~(size_t)255) + (size_t)s * sizeof(int);
 }
 
 int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
-                int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride, long long kv_b_stride) {
+                int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride, long long kv_b_stride,
+                void *callers, size_t callers_cap) {
     (void)nb;
     const size_t esz = kv_bf16 ? 2 : 4;
     const size_t sa = (size_t)kv_a_stride * esz, sb = (size_t)kv_b_stride * esz;
@@ -321,10 +333,13 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
     size_t sc_bytes = (size_t)s * h * idxw * sizeof(float);
     size_t ids_bytes = (size_t)s * idxw * sizeof(int32_t);
     size_t ns_off = (sc_bytes + ids_bytes + 255) & ~(size_t)255;
-    if (ensure_scratch(ns_off + (size_t)s * sizeof(int))) return 1;
-    float *sc = (float *)g_scratch;
-    int32_t *ids = (int32_t *)((char *)g_scratch + sc_bytes);
-    int *ns = (int *)((char *)g_scratch + ns_off);
+    const size_t need = ns_off + (size_t)s * sizeof(int);
+    APUS_REQUIRE(!callers || need <= callers_cap, "sparse_attn: scratch of %zu bytes given, %zu needed", callers_cap, need);
+    void *scratch = callers ? callers : ensure_scratch(need);
+    if (!scratch) return 1;
+    float *sc = (float *)scratch;
+    int32_t *ids = (int32_t *)((char *)scratch + sc_bytes);
+    int *ns = (int *)((char *)scratch + ns_off);
     compact_ids_kernel<<<s, 256, 0, st>>>(idxs, idxw, ids, ns);
     APUS_LAUNCHED();
     size_t sm1 = ((size_t)SA_IDS * (d + 1) + (size_t)SA_HEADS * d) * sizeof(float);

@@ -38,6 +38,9 @@ struct StepBufs {
     // second set for the chains that run beside the main one (see attn_step)
     uint8_t *xq2;
     float *xs2, *ckv2, *csc2, *pooled2;
+    // sparse-attention scratch of the owner (NULL: the library's shared one)
+    void *sa = nullptr;
+    size_t sa_cap = 0;
 };
 
 // Device copies that belong to one object (a model) instead of the global cache.

@@ -140,7 +140,9 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
                 int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride = 0,
-                long long kv_b_stride = 0);   // strides (elements) between the tokens' own caches; 0 = shared
+                long long kv_b_stride = 0,    // strides (elements) between the tokens' own caches; 0 = shared
+                void *scratch = nullptr, size_t scratch_cap = 0);   // caller's scratch (sparse_attn_scratch bytes) or the shared one
+size_t sparse_attn_scratch(int h, int idxw, int s);
 
 // ---- attention row helpers, compressor and indexer steps (attn_ops.cu) -----------------------
 enum {
@@ -196,12 +198,13 @@ int embed_rows(const void *table, int bf16, const int64_t *ids, int rows, int hc
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
             const float *base, float norm_eps, float hc_eps, int iters,
             const float *norm_w, float rms_eps, float *pre, float *post,
-            float *comb, float *y, float *y_normed, int rows, cudaStream_t st);
+            float *comb, float *y, float *y_normed, int rows, cudaStream_t st,
+            float *raw = nullptr);            // caller's scratch of rows * ((2+n)*n + 1) floats, or the shared one
 int mhc_post(const float *f, const float *res4, const float *post,
              const float *comb, float *y4, int d, int n, int rows,
              cudaStream_t st);
 int mhc_head(const float *x4, int d, int n, const float *fn, float scale,
              const float *base, float norm_eps, float hc_eps, float *y,
-             int rows, cudaStream_t st);
+             int rows, cudaStream_t st, float *raw = nullptr);
 
 }  // namespace apus

@@ -12,6 +12,7 @@
 //      collapsed row in the same kernel (reference c/attn.h:371-378).
 // Bytes per token: fn (nmix*n*d*4, L2-resident across tokens) + 2 reads of the
 // n*d state.
+#include <map>
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -337,15 +338,23 @@ __global__ void mhc_post_kernel(const float *__restrict__ f, const float *__rest
     }
 }
 
+// Scratch between the two kernels of a call: the caller's (a model object keeps its
+// own, so that models stepping side by side on different streams do not share one),
+// else one buffer of the library, which only grows.
 static float *g_raw = nullptr;
 static size_t g_raw_cap = 0;
-static int ensure_raw(size_t floats) {
-    if (floats <= g_raw_cap) return 0;
-    if (g_raw) cudaFree(g_raw);
+static float *ensure_raw(size_t floats, float *callers) {
+    if (callers) return callers;
+    if (floats <= g_raw_cap) return g_raw;
+    if (g_raw) { cudaDeviceSynchronize(); cudaFree(g_raw); }
     g_raw = nullptr; g_raw_cap = 0;
-    APUS_CUDA_OK(cudaMalloc(&g_raw, floats * sizeof(float)));
+    if (cudaMalloc(&g_raw, floats * sizeof(float)) != cudaSuccess) {
+        set_error("mhc: scratch of %zu floats", floats);
+        g_raw = nullptr;
+        return nullptr;
+    }
     g_raw_cap = floats;
-    return 0;
+    return g_raw;
 }
 
 // raw[row, 0..nmix] for `rows` tokens in the sum order now in force.
@@ -387,13 +396,14 @@ static inline size_t finish_smem(int d) { return finish_seq() ? (size_t)d * size
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
             const float *base, float norm_eps, float hc_eps, int iters,
             const float *norm_w, float rms_eps, float *pre, float *post,
-            float *comb, float *y, float *y_normed, int rows, cudaStream_t st) {
+            float *comb, float *y, float *y_normed, int rows, cudaStream_t st, float *raw_in) {
     APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N && (n * d) % 4 == 0, "mhc: n=%d d=%d unsupported", n, d);
     if (rows <= 0) return 0;
     int nmix = (2 + n) * n;
-    if (ensure_raw((size_t)rows * (nmix + 1))) return 1;
-    if (launch_mix(x4, fn, n * d, nmix, g_raw, rows, st)) return 1;
-    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, g_raw, d, n, nmix, scale, 0.f, base,
+    float *raw = ensure_raw((size_t)rows * (nmix + 1), raw_in);
+    if (!raw) return 1;
+    if (launch_mix(x4, fn, n * d, nmix, raw, rows, st)) return 1;
+    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, 0.f, base,
                                                 norm_eps, hc_eps, iters, 0, norm_w, rms_eps,
                                                 pre, post, comb, y, norm_w ? y_normed : nullptr, finish_seq());
     APUS_LAUNCHED();
@@ -402,12 +412,13 @@ int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
 
 int mhc_head(const float *x4, int d, int n, const float *fn, float scale,
              const float *base, float norm_eps, float hc_eps, float *y,
-             int rows, cudaStream_t st) {
+             int rows, cudaStream_t st, float *raw_in) {
     APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N && (n * d) % 4 == 0, "mhc: n=%d d=%d unsupported", n, d);
     if (rows <= 0) return 0;
-    if (ensure_raw((size_t)rows * (n + 1))) return 1;
-    if (launch_mix(x4, fn, n * d, n, g_raw, rows, st)) return 1;
-    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, g_raw, d, n, n, nullptr, scale, base,
+    float *raw = ensure_raw((size_t)rows * (n + 1), raw_in);
+    if (!raw) return 1;
+    if (launch_mix(x4, fn, n * d, n, raw, rows, st)) return 1;
+    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, n, nullptr, scale, base,
                                                 norm_eps, hc_eps, 0, 1, nullptr, 0.f,
                                                 nullptr, nullptr, nullptr, y, nullptr, finish_seq());
     APUS_LAUNCHED();

@@ -57,6 +57,9 @@ def parse():
     ap.add_argument("--batch", type=int, default=32, help="model workload: sequences decoded in lockstep")
     ap.add_argument("--prompt", type=int, default=512, help="model workload: prompt tokens per sequence")
     ap.add_argument("--layers", type=int, default=43, help="model workload: layers (43 = the real model)")
+    ap.add_argument("--microbatches", type=int, default=1,
+                    help="model workload, 1 GPU: model objects the batch is split over; they share the weights "
+                         "and step side by side on streams of their own")
     a = ap.parse_args()
     if a.workload is None:
         a.workload = "model"
@@ -183,6 +186,7 @@ def model_config(a, n, cfg):
             "layers": cfg.n_layers, "layer_kinds": {"swa": kinds.count(0), "csa": kinds.count(4), "hca": kinds.count(128)},
             "hidden": cfg.dim, "n_routed_experts": cfg.n_experts, "topk": cfg.topk, "vocab": cfg.vocab,
             "batch": a.batch, "prompt_tokens": a.prompt, "parallelism": f"ep{n}" if n > 1 else "single",
+            "microbatches": 1 if n > 1 else max(1, a.microbatches),
             "sum_order": "tree" if os.environ.get("APUS_SUM_ORDER", "0") == "1" else "reference",
             "l2": "each step streams the touched experts and all dense weights (>20 GB at batch 32), far above the 126 MB L2"}
 
@@ -437,37 +441,51 @@ def model_main(a):
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
 
-    def run(batch, timed_moe):
-        """Prompt, warm-up decode steps, K timed decode steps with the sampled token fed
-        back on the device (each step replayed from a CUDA graph); then, when asked, a
-        short pass with plain launches and CUDA events around the expert kernels.
-        Returns (handle, ms of the K steps, prefill ms, kernels per step, tokens, wall, stats)."""
-        h = create(batch)
-        prompt = rng.integers(0, cfg.vocab, size=(batch, a.prompt)).astype(np.int64)
-        toks = np.empty((batch, Wm + 1), np.int32)
+    def parr(arrays):
+        return (C.c_void_p * len(arrays))(*[capi.ptr(x) for x in arrays])
+
+    def run(batch, groups):
+        """`batch` sequences held by `groups` model objects (batch / groups each) that share
+        the device-resident weights and step side by side, each on its own stream.
+        Prompt, warm-up decode steps, K timed decode steps with the sampled token fed back
+        on the device (each model's step replayed from its CUDA graph); then a short pass
+        of the first model alone with plain launches and CUDA events around the expert
+        kernels.  Returns (handles, ms of the K steps, prefill ms, kernels in the timed
+        region, last tokens per model, wall, stats)."""
+        per = batch // groups
+        hs = [create(per) for _ in range(groups)]
+        if groups > 1:
+            for h in hs:
+                apus_b200.check(L.apus_cuda_model_set_stream(h, None, 1), "model_set_stream")
+        harr = (C.c_void_p * groups)(*hs)
+        prompts = [np.ascontiguousarray(rng.integers(0, cfg.vocab, size=(per, a.prompt)).astype(np.int64))
+                   for _ in range(groups)]
+        toks = [np.empty((per, Wm + 1), np.int32) for _ in range(groups)]
         ms_pre, ms_dec = C.c_float(0), C.c_float(0)
-        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(prompt), a.prompt, Wm + 1, capi.ptr(toks),
-                                                   C.byref(ms_pre), C.byref(ms_dec)), "generate (prompt + warm-up)")
+        apus_b200.check(L.apus_cuda_model_generate_group(harr, groups, parr(prompts), a.prompt, Wm + 1, parr(toks),
+                                                         C.byref(ms_pre), C.byref(ms_dec)),
+                        "generate (prompt + warm-up)")
         prefill_ms = ms_pre.value
-        last = np.ascontiguousarray(toks[:, -1:].astype(np.int64))
-        out = np.empty((batch, K + 1), np.int32)
+        last = [np.ascontiguousarray(t[:, -1:].astype(np.int64)) for t in toks]
+        out = [np.empty((per, K + 1), np.int32) for _ in range(groups)]
         torch.cuda.synchronize()
         w0 = time.time()
-        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(last), 1, K + 1, capi.ptr(out), C.byref(ms_pre),
-                                                   C.byref(ms_dec)), "generate (timed)")
+        apus_b200.check(L.apus_cuda_model_generate_group(harr, groups, parr(last), 1, K + 1, parr(out),
+                                                         C.byref(ms_pre), C.byref(ms_dec)), "generate (timed)")
         torch.cuda.synchronize()
         w1 = time.time()
         ms = ms_dec.value
-        # plain-launch pass: kernels per step, and events around the expert GEMVs
+        # plain-launch pass of the first model alone: kernels per step, and events around the expert GEMVs
+        h = hs[0]
         moes = [L.apus_cuda_model_moe(h, i) for i in range(cfg.n_layers)]
         kt = min(K, 16)
         for m in moes:
             L.apus_cuda_moe_timing(m, 1)
             L.apus_cuda_moe_work_items(m, 1)
-        last = np.ascontiguousarray(out[:, -1:].astype(np.int64))
-        out2 = np.empty((batch, kt + 1), np.int32)
+        last0 = np.ascontiguousarray(out[0][:, -1:].astype(np.int64))
+        out2 = np.empty((per, kt + 1), np.int32)
         d0 = L.apus_cuda_dispatches()
-        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(last), 1, kt + 1, capi.ptr(out2), C.byref(ms_pre),
+        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(last0), 1, kt + 1, capi.ptr(out2), C.byref(ms_pre),
                                                    C.byref(ms_dec)), "generate (event pass)")
         per_step = (int(L.apus_cuda_dispatches() - d0)) // (kt + 1)
         ms_plain = ms_dec.value / kt
@@ -480,29 +498,46 @@ def model_main(a):
             g13 += x.value; g2 += y.value; nl += n.value
             items += L.apus_cuda_moe_work_items(m, 0)
         stats = (g13, g2, nl, items, kt, ms_plain)
-        return h, ms, prefill_ms, per_step * K, out2, (w0, w1), stats
+        # the other models catch up with the first one's event pass (same position for the e2e loop)
+        for g in range(1, groups):
+            lg = np.ascontiguousarray(out[g][:, -1:].astype(np.int64))
+            o2 = np.empty((per, kt + 1), np.int32)
+            apus_b200.check(L.apus_cuda_model_generate(hs[g], capi.ptr(lg), 1, kt + 1, capi.ptr(o2), None, None),
+                            "generate (catch up)")
+            out[g] = o2
+        out[0] = out2
+        return hs, ms, prefill_ms, per_step * K * groups, out, (w0, w1), stats
 
-    h32, ms, prefill_ms, launches, out, wall, stats = run(B, True)
+    G = max(1, a.microbatches)
+    if B % G:
+        raise SystemExit(f"--batch {B} is not a multiple of --microbatches {G}")
+    hs, ms, prefill_ms, launches, out, wall, stats = run(B, G)
     clocks = sampler.stop(*wall)
     value = B * K / (ms * 1e-3)
 
     # ---- end to end: ids from the host every step, sampled ids back to the host -----------------
-    ids = np.ascontiguousarray(out[:, -1:].astype(np.int64))
-    nxt = np.empty(B, np.int32)
+    per = B // G
+    harr = (C.c_void_p * G)(*hs)
+    ids = [np.ascontiguousarray(o[:, -1:].astype(np.int64)) for o in out]
+    nxt = [np.empty(per, np.int32) for _ in range(G)]
     ne = max(8, K // 4)
+
+    def e2e_step():
+        apus_b200.check(L.apus_cuda_model_forward_group(harr, G, parr(ids), 1, None, parr(nxt)), "model_forward")
+        for g in range(G):
+            ids[g][:, 0] = nxt[g]
     for _ in range(3):
-        apus_b200.check(L.apus_cuda_model_forward(h32, capi.ptr(ids), 1, None, capi.ptr(nxt)), "model_forward")
-        ids[:, 0] = nxt
+        e2e_step()
     t0 = time.perf_counter()
     for _ in range(ne):
-        apus_b200.check(L.apus_cuda_model_forward(h32, capi.ptr(ids), 1, None, capi.ptr(nxt)), "model_forward")
-        ids[:, 0] = nxt
+        e2e_step()
     e2e_val = B * ne / (time.perf_counter() - t0)
-    L.apus_cuda_model_destroy(h32)
+    for h in hs:
+        L.apus_cuda_model_destroy(h)
 
     # ---- batch 1 ------------------------------------------------------------------------------
-    h1, ms1, prefill1, launches1, out1, _, st1 = run(1, False)
-    L.apus_cuda_model_destroy(h1)
+    h1, ms1, prefill1, launches1, out1, _, st1 = run(1, 1)
+    L.apus_cuda_model_destroy(h1[0])
 
     peak, peak_kind = peak_hbm()
     g13, g2, nl, items, kt, ms_plain = stats

@@ -513,6 +513,27 @@ int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt,
                              int n_prompt, int n_gen, int32_t *out_tokens,
                              float *ms_prefill, float *ms_decode);
 
+/* Models that step side by side.  A decode step at batch 32 is mostly a chain of
+ * short kernels that leave the GPU idle between them; sequences are independent,
+ * so a batch can be split over several model objects (created from the same
+ * descriptor with device-resident weights they share without copying them),
+ * each enqueuing on a stream of its own, and their steps overlap on the GPU.
+ * Every sequence computes exactly what it computes alone.
+ * set_stream: `create` != 0 gives the model a stream made by the library,
+ * otherwise `stream` (a cudaStream_t; NULL = back to the library stream); the next
+ * step runs eagerly on the new stream before steps are recorded again.
+ * forward_group / generate_group are apus_cuda_model_forward / _generate for n
+ * models at once (arrays of n prompts / outputs, batch of model i rows each);
+ * the models must be on different streams; the times cover the whole group. */
+int apus_cuda_model_set_stream(ApusCudaModel *m, void *stream, int create);
+int apus_cuda_model_forward_group(ApusCudaModel *const *ms, int n,
+                                  const int64_t *const *ids, int s,
+                                  float *const *logits, int32_t *const *next);
+int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n,
+                                   const int64_t *const *prompts, int n_prompt,
+                                   int n_gen, int32_t *const *out_tokens,
+                                   float *ms_prefill, float *ms_decode);
+
 /* One decode step of all sequences in pieces, on the library stream, for callers
  * that run the MoE sublayer themselves (expert parallelism: route, exchange
  * rows with the expert owners, apus_cuda_moe_experts_dev, exchange back,

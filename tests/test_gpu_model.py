@@ -499,3 +499,62 @@ def test_model_load_from_checkpoint_directory(tmp_path):
     assert not L.apus_cuda_model_load(str(tmp_path).encode(), 1, 64, 0, -1)
     assert b"layers.1: fp8 attn weights" in L.apus_cuda_last_error()     # the reference's message for it
     print("checkpoint model: worst logits rel-L2 vs the reference's loaded model", worst)
+
+
+def test_models_side_by_side_equal_one_batch():
+    """Two models holding half of the sequences each, stepping side by side on
+    streams of their own (apus_cuda_model_generate_group / _forward_group),
+    produce bit for bit what one model holding all sequences produces."""
+    L = lib()
+    tag = "model_batch"
+    _, _, B, n_prompt, n_gen = MODEL_CASES[tag]
+    Mdl, prompts, h = make_model(L, tag, B)
+    V = Mdl.M["vocab"]
+    want = np.empty((B, n_gen), np.int32)
+    want_lg = np.empty((B, V), np.float32)
+    try:
+        assert L.apus_cuda_model_generate(h, P(prompts), n_prompt, n_gen, P(want), None, None) == 0
+        feed = np.ascontiguousarray(want[:, -1:].astype(np.int64))
+        assert L.apus_cuda_model_forward(h, P(feed), 1, P(want_lg), None) == 0
+    finally:
+        L.apus_cuda_model_destroy(h)
+    sizes = [B - B // 2, B // 2]
+    lo = [0, sizes[0]]
+    half = sizes[0]
+    hs = [L.apus_cuda_model_create(C.byref(Mdl.desc), n, 64) for n in sizes]
+    assert all(hs), L.apus_cuda_last_error()
+    try:
+        arr = (C.c_void_p * 2)(*hs)
+        # both on the library stream: refused (their work would not overlap and the group's
+        # time stamps assume one stream per model)
+        pr = [np.ascontiguousarray(prompts[lo[i]:lo[i] + sizes[i]]) for i in range(2)]
+        got = [np.empty((n, n_gen), np.int32) for n in sizes]
+        pp = (C.c_void_p * 2)(*[P(a) for a in pr])
+        gp = (C.c_void_p * 2)(*[P(a) for a in got])
+        assert L.apus_cuda_model_generate_group(arr, 2, pp, n_prompt, n_gen, gp, None, None) != 0
+        assert b"share a stream" in L.apus_cuda_last_error()
+        for hh in hs:
+            assert L.apus_cuda_model_set_stream(hh, None, 1) == 0
+        ms_pre, ms_dec = C.c_float(0), C.c_float(0)
+        rc = L.apus_cuda_model_generate_group(arr, 2, pp, n_prompt, n_gen, gp, C.byref(ms_pre), C.byref(ms_dec))
+        assert rc == 0, L.apus_cuda_last_error()
+        assert ms_pre.value > 0 and ms_dec.value > 0
+        assert np.array_equal(np.concatenate(got), want)
+        feeds = [np.ascontiguousarray(g[:, -1:].astype(np.int64)) for g in got]
+        lgs = [np.empty((n, V), np.float32) for n in sizes]
+        nx = [np.empty(n, np.int32) for n in sizes]
+        fp = (C.c_void_p * 2)(*[P(a) for a in feeds])
+        lp = (C.c_void_p * 2)(*[P(a) for a in lgs])
+        npp = (C.c_void_p * 2)(*[P(a) for a in nx])
+        assert L.apus_cuda_model_forward_group(arr, 2, fp, 1, lp, npp) == 0, L.apus_cuda_last_error()
+        assert np.array_equal(bits(np.concatenate(lgs)), bits(want_lg))
+        assert np.array_equal(np.concatenate(nx), np.argmax(want_lg, axis=1))
+        # back on the library stream a model still works alone
+        assert L.apus_cuda_model_set_stream(hs[0], None, 0) == 0
+        assert L.apus_cuda_model_reset(hs[0]) == 0
+        alone = np.empty((half, n_gen), np.int32)
+        assert L.apus_cuda_model_generate(hs[0], P(pr[0]), n_prompt, n_gen, P(alone), None, None) == 0
+        assert np.array_equal(alone, want[:half])
+    finally:
+        for hh in hs:
+            L.apus_cuda_model_destroy(hh)
