@@ -122,9 +122,9 @@ f32_linear_kernel(const void *__restrict__ wv, const float *__restrict__ x,
 // tile takes the fused walk only if every operand in it is +-0 or a BF16 value with
 // 2^-60 <= |v| < 2^60 (checked while the tile is staged; the whole CTA agrees on it);
 // any other tile -- true f32 operands, subnormals, huge values, NaN -- takes the
-// two-instruction walk.  BF16 weights with BF16 activations (o-projection, LM head,
-// router, compressor projections) therefore run at half the instruction count with
-// bit-identical sums.
+// two-instruction walk.  BF16-stored weights with BF16 activations (o-projection, LM
+// head) therefore run at half the instruction count with bit-identical sums; f32-stored
+// weights always take the two-instruction walk (those projections are latency bound).
 constexpr int SQ_KT = 128;
 constexpr int SQ_WP = (SQ_KT + 4) * 4;                   // f32 weight row pitch, bytes (+16 B: conflict-free 16-byte reads)
 
@@ -299,6 +299,18 @@ f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, 
         unsigned char *st = sq_smem + (size_t)(t % NST) * STAGE;
         float4 *xs4 = reinterpret_cast<float4 *>(st + Cf::W_RAW);
         bool exact = true;
+        if (!WBF16) {
+            // f32 weight storage: these are the small, add-latency bound projections (router,
+            // compressors); the chain is as long either way, so the tile is not examined and
+            // takes the two-instruction walk -- the staging warps then only copy (and round)
+            if (rin)
+                for (int idx = sid; idx < TPC * (SQ_KT / 4); idx += SQ_STAGERS) {
+                    float4 v = xs4[idx];
+                    v.x = bf16_round(v.x); v.y = bf16_round(v.y); v.z = bf16_round(v.z); v.w = bf16_round(v.w);
+                    xs4[idx] = v;
+                }
+            return;
+        }
         for (int idx = sid; idx < TPC * (SQ_KT / 4); idx += SQ_STAGERS) {
             float4 v = xs4[idx];
             if (rin) {
@@ -322,13 +334,6 @@ f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, 
                                      __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
             }
             exact &= (bad & 0x80008000u) == 0u;
-        } else {
-#pragma unroll
-            for (int j = 0; j < NWC; j++) {
-                const int id = sid + SQ_STAGERS * j, r = id / W_CH, c = id - r * W_CH;
-                const float4 v = *reinterpret_cast<const float4 *>(st + (size_t)r * WP_RAW + c * 16);
-                exact &= fma_ok_f32(v.x) && fma_ok_f32(v.y) && fma_ok_f32(v.z) && fma_ok_f32(v.w);
-            }
         }
         if (!exact) s_bad[t & 1] = 1;                     // every writer stores the same value
     };
@@ -366,7 +371,7 @@ f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, 
             const unsigned char *stg = sq_smem + (size_t)(t % NST) * STAGE;
             const unsigned char *wrow = (WBF16 ? wide + (size_t)(t & 1) * Cf::WIDE : stg) + (size_t)lane * SQ_WP;
             const float4 *xrow = reinterpret_cast<const float4 *>(stg + Cf::W_RAW) + (size_t)warp * MTT * (SQ_KT / 4);
-            if (s_bad[t & 1]) seq_walk_tile<R, MTT, false>(acc, wrow, xrow);
+            if (!WBF16 || s_bad[t & 1]) seq_walk_tile<R, MTT, false>(acc, wrow, xrow);
             else seq_walk_tile<R, MTT, true>(acc, wrow, xrow);
         }
         __syncthreads();                                  // tile t + 1 is staged; tile t's buffers are free
