@@ -172,7 +172,7 @@ def reference_arm(a):
                                        f"on the host ({'unmodified reference C, AVX2 rows' if kind == 'reference' else 'oracle port'})"},
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---- full-model token loop (config 4 of the baseline; the headline metric) ------------------
@@ -274,7 +274,7 @@ def model_reference_arm(a):
     cfg = flash_config(a)
     cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0)
     if cb is None:
-        print(json.dumps({"impl": "reference", "unavailable": "the reference build (oracle/_ref) is not present"}))
+        emit({"impl": "reference", "unavailable": "the reference build (oracle/_ref) is not present"})
         return
     line = {"impl": "reference", "metric": MODEL_METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": a.gpus,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
@@ -282,7 +282,7 @@ def model_reference_arm(a):
             "config": model_config(a, a.gpus, cfg), "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def model_main_ep(a):
@@ -398,7 +398,7 @@ def model_main_ep(a):
             "roofline": None, "weights": {"bytes_per_rank": W.bytes}, "cuda_graph": graph_note,
             "note": "expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine per layer; "
                     "the per-kernel roofline is reported by the 1-GPU run"}
-        print(json.dumps(line), flush=True)
+        emit(line)
     # a captured graph holds NCCL work; release it and leave without tearing the
     # communicator down (destroying the group with such graphs alive can block)
     ep.graph = None
@@ -579,7 +579,7 @@ def model_main(a):
         cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0)
         if cb:
             line["cpu_baseline"] = cb
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---- config 1: FP8 E4M3 block-scaled dense GEMM ------------------------------------------------
@@ -628,12 +628,29 @@ def fp8_gemm_main(a):
             "n_gpus": 1, "results_by_M": res, "hbm_peak_GBs": peak, "peak_kind": peak_kind,
             "note": "act quant + gemm_tc8_kernel + BF16 round per call; L2 flushed between timed calls; "
                     "M > 32 runs as 32-row work items (weights re-read from L2)"}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---- this repository's arm (one MoE sublayer) --------------------------------------------------
+_RESULT_OUT = None
+
+
+def emit(line):
+    """The one JSON line of a run, on the process's original stdout."""
+    out = _RESULT_OUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
+    # stdout carries exactly one JSON line: keep the original descriptor for it and point
+    # descriptor 1 at stderr, so that whatever a library prints (NCCL's version banner,
+    # compiler notes) cannot land in front of the result
+    global _RESULT_OUT
     a = parse()
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if a.workload == "fp8_gemm":
         return fp8_gemm_main(a)
     if a.workload == "model":
@@ -799,7 +816,7 @@ def main():
             line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores(), "kind": kind,
                                     "sample": f"{n} steps of T={T} tokens through apus_moe_forward on the host "
                                               f"cores in {dt:.1f} s"}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
