@@ -78,6 +78,16 @@ class ExpertParallelMoe:
     def _stream():
         return torch.cuda.current_stream().cuda_stream
 
+    _side = {}
+
+    @classmethod
+    def _side_stream(cls, device):
+        """One side stream per device, shared by the sublayers (they run one after another)."""
+        key = str(device)
+        if key not in cls._side:
+            cls._side[key] = torch.cuda.Stream(device=device)
+        return cls._side[key]
+
     def _route_cuda(self, x, ids):
         s = x.shape[0]
         idx = torch.empty(s, self.topk, dtype=torch.int32, device=x.device)
@@ -151,6 +161,16 @@ class ExpertParallelMoe:
         must bring the same number of tokens.  Nothing here depends on device
         values on the host, so a whole step can be captured into a CUDA graph."""
         s, W, dim = x.shape[0], self.world, self.dim
+        # the shared expert needs nothing from the exchange: on the GPU it runs on a side
+        # stream beside routing, the all-to-alls and the routed experts (a parallel branch
+        # when the step is being captured into a graph)
+        side = cur = None
+        if x.is_cuda:
+            cur = torch.cuda.current_stream()
+            side = self._side_stream(x.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                shared = self.shared_fn(x)
         idx, wgt = self.route_fn(x, ids)
         R = s * self.topk
         C = R                                            # slots per destination
@@ -170,12 +190,16 @@ class ExpertParallelMoe:
         recv_eids = torch.empty_like(send_eids)
         dist.all_to_all_single(recv_rows, send_rows, group=self.group)
         dist.all_to_all_single(recv_eids, send_eids, group=self.group)
-        shared = self.shared_fn(x)
+        if side is None:
+            shared = self.shared_fn(x)
         eo_recv = self.experts_fn(recv_rows, recv_eids).contiguous()
         eo_back = torch.empty_like(eo_recv)
         dist.all_to_all_single(eo_back, eo_recv, group=self.group)
         eo = torch.empty(R, dim, dtype=x.dtype, device=x.device)
         eo[order] = eo_back[slot]                        # back to (t, j) order
+        if side is not None:
+            cur.wait_stream(side)
+            shared.record_stream(cur)
         return self.combine_fn(eo, wgt, shared)
 
 
