@@ -417,10 +417,13 @@ static int launch_linear_seq(const void *w, long long ws, const float *x, long l
     // O) needs to cover the memory latency; the 64-row tile (R = 2) halves the staging and
     // the x reads per term once there are CTAs enough to fill the GPU with it.
     const long long ctas32 = (long long)ceil_div(O, 32) * batch * ceil_div(M, 32);
+    // Every chain warp reads the whole weight tile from shared memory, so two tokens per
+    // warp (half as many warps re-reading it) keep the small shapes off the shared-memory
+    // pipe: with one token per warp the 8-token CTA spent 3/4 of a tile's time on it.
     if (M == 1) SEQ_LAUNCH(1, 1, 1, 6);
-    else if (M <= 2) SEQ_LAUNCH(1, 1, 2, 6);
-    else if (M <= 4) SEQ_LAUNCH(1, 1, 4, 6);
-    else if (M <= 8 || ctas32 < 64) SEQ_LAUNCH(1, 1, 8, 6);     // 8 tokens per CTA, one per warp
+    else if (M <= 2) SEQ_LAUNCH(1, 2, 1, 6);
+    else if (M <= 4) SEQ_LAUNCH(1, 2, 2, 6);
+    else if (M <= 8 || ctas32 < 64) SEQ_LAUNCH(1, 2, 4, 6);     // 8 tokens per CTA, two per warp
     else if (M <= 16 || ctas32 < 148) SEQ_LAUNCH(1, 2, 8, 3);   // 16 tokens per CTA
     else if constexpr (WBF16) SEQ_LAUNCH(2, 4, 8, 3);           // 32 tokens x 64 rows per CTA
     else SEQ_LAUNCH(1, 4, 8, 3);                                // 32 tokens per CTA
