@@ -494,6 +494,20 @@ int apus_cuda_moe_combine_dev(const ApusCudaMoe *m, const float *eo, const float
     return moe_combine(eo, wgt, shared, s, m->topk, m->dim, out, routed, (cudaStream_t)stream);
 }
 
+int apus_cuda_moe_ep_plan_dev(const int32_t *idx, int n_rout, int n_experts, int world, int slots,
+                              int32_t *send_eids, int32_t *slot_of, void *stream) {
+    if (n_rout <= 0) return 0;
+    APUS_REQUIRE(world >= 1 && n_experts % world == 0 && slots >= n_rout && n_rout <= 8192,
+                 "moe_ep_plan: %d routings, %d experts over %d ranks, %d slots per rank", n_rout, n_experts, world, slots);
+    return ep_plan(idx, n_rout, n_experts / world, world, slots, send_eids, slot_of, (cudaStream_t)stream);
+}
+int apus_cuda_moe_ep_rows_dev(const float *src, int dim, const int32_t *slot_of, int n_rout, int topk, int gather,
+                              float *dst, void *stream) {
+    if (n_rout <= 0) return 0;
+    APUS_REQUIRE(dim % 4 == 0 && topk >= 1, "moe_ep_rows: dim %d, topk %d", dim, topk);
+    return ep_rows(src, dim, slot_of, n_rout, topk, gather, dst, (cudaStream_t)stream);
+}
+
 int apus_cuda_moe_forward_dev(ApusCudaMoe *m, const float *x, const int64_t *ids, int s, float *out,
                               void *stream) {
     if (!m) { set_error("NULL moe handle"); return 1; }

@@ -194,6 +194,12 @@ int argmax_rows(const float *x, int n, int rows, int32_t *out, cudaStream_t st);
 int embed_rows(const void *table, int bf16, const int64_t *ids, int rows, int hc, int dim, float *out,
                cudaStream_t st);
 
+// expert-parallel exchange helpers (moe.cu)
+int ep_plan(const int32_t *idx, int n_rout, int per_rank, int world, int slots, int32_t *send_eids,
+            int32_t *slot_of, cudaStream_t st);
+int ep_rows(const float *src, int dim, const int32_t *slot_of, int n_rout, int topk, int gather, float *dst,
+            cudaStream_t st);
+
 // ---- mHC (mhc.cu) -----------------------------------------------------------------------------------
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
             const float *base, float norm_eps, float hc_eps, int iters,

@@ -277,4 +277,49 @@ int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
     return 0;
 }
 
+// ---- expert-parallel exchange helpers ---------------------------------------------------------------
+// The slots of the fixed-shape exchange: routing p = t * topk + j goes to the rank
+// that owns its expert, into that rank's block of `slots` row slots, in the order of
+// p (a stable grouping by destination).  One CTA: a routing counts the earlier
+// routings with its destination.  Unused slots keep expert id -1.
+__global__ void __launch_bounds__(1024)
+ep_plan_kernel(const int32_t *__restrict__ idx, int n_rout, int per_rank, int world, int slots,
+               int32_t *__restrict__ send_eids, int32_t *__restrict__ slot_of) {
+    extern __shared__ int s_dest[];
+    for (int i = threadIdx.x; i < world * slots; i += blockDim.x) send_eids[i] = -1;
+    for (int p = threadIdx.x; p < n_rout; p += blockDim.x) s_dest[p] = idx[p] / per_rank;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_rout; p += blockDim.x) {
+        const int d = s_dest[p];
+        int before = 0;
+        for (int q = 0; q < p; q++) before += s_dest[q] == d;
+        const int slot = d * slots + before;
+        slot_of[p] = slot;
+        send_eids[slot] = idx[p];
+    }
+}
+// gather == 0: dst[slot_of[p]] = src[p / topk]  (token rows into their slots)
+// gather == 1: dst[p] = src[slot_of[p]]         (expert outputs back to (t, j) order)
+__global__ void __launch_bounds__(256)
+ep_rows_kernel(const float *__restrict__ src, int dim, const int32_t *__restrict__ slot_of, int topk, int gather,
+               float *__restrict__ dst) {
+    const int p = blockIdx.x, slot = slot_of[p];
+    const float4 *s4 = reinterpret_cast<const float4 *>(src + (size_t)(gather ? slot : p / topk) * dim);
+    float4 *d4 = reinterpret_cast<float4 *>(dst + (size_t)(gather ? p : slot) * dim);
+    for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) d4[i] = s4[i];
+}
+
+int ep_plan(const int32_t *idx, int n_rout, int per_rank, int world, int slots, int32_t *send_eids,
+            int32_t *slot_of, cudaStream_t st) {
+    ep_plan_kernel<<<1, 1024, (size_t)n_rout * sizeof(int), st>>>(idx, n_rout, per_rank, world, slots, send_eids, slot_of);
+    APUS_LAUNCHED();
+    return 0;
+}
+int ep_rows(const float *src, int dim, const int32_t *slot_of, int n_rout, int topk, int gather, float *dst,
+            cudaStream_t st) {
+    ep_rows_kernel<<<n_rout, 256, 0, st>>>(src, dim, slot_of, topk, gather, dst);
+    APUS_LAUNCHED();
+    return 0;
+}
+
 }  // namespace apus

@@ -174,33 +174,65 @@ class ExpertParallelMoe:
         idx, wgt = self.route_fn(x, ids)
         R = s * self.topk
         C = R                                            # slots per destination
-        flat = idx.reshape(-1).long()
-        dest = owner_ranks(flat, self.E, W)
-        order = torch.argsort(dest, stable=True)
-        dest_s = dest[order]
-        ranks = torch.arange(W, device=x.device)
-        counts = (dest_s[:, None] == ranks[None, :]).sum(0)
-        starts = torch.cumsum(counts, 0) - counts
-        slot = dest_s * C + (torch.arange(R, device=x.device) - starts[dest_s])
-        send_rows = torch.zeros(W * C, dim, dtype=x.dtype, device=x.device)
-        send_eids = torch.full((W * C,), -1, dtype=idx.dtype, device=x.device)
-        send_rows[slot] = x[torch.div(order, self.topk, rounding_mode="floor")]
-        send_eids[slot] = idx.reshape(-1)[order]
-        recv_rows = torch.empty_like(send_rows)
-        recv_eids = torch.empty_like(send_eids)
+        fused = x.is_cuda and idx.dtype == torch.int32 and x.dtype == torch.float32
+        if fused:
+            # three library kernels instead of a dozen tensor ops: slots + expert ids, rows in
+            send_rows, send_eids, recv_rows, recv_eids, eo_back, eo, slot = self._exchange_bufs(x.device, W * C, R)
+            st = self._stream()
+            check(lib().apus_cuda_moe_ep_plan_dev(idx.data_ptr(), R, self.E, W, C, send_eids.data_ptr(),
+                                                  slot.data_ptr(), st), "moe_ep_plan_dev")
+            check(lib().apus_cuda_moe_ep_rows_dev(x.data_ptr(), dim, slot.data_ptr(), R, self.topk, 0,
+                                                  send_rows.data_ptr(), st), "moe_ep_rows_dev")
+        else:
+            flat = idx.reshape(-1).long()
+            dest = owner_ranks(flat, self.E, W)
+            order = torch.argsort(dest, stable=True)
+            dest_s = dest[order]
+            ranks = torch.arange(W, device=x.device)
+            counts = (dest_s[:, None] == ranks[None, :]).sum(0)
+            starts = torch.cumsum(counts, 0) - counts
+            slot = dest_s * C + (torch.arange(R, device=x.device) - starts[dest_s])
+            send_rows = torch.zeros(W * C, dim, dtype=x.dtype, device=x.device)
+            send_eids = torch.full((W * C,), -1, dtype=idx.dtype, device=x.device)
+            send_rows[slot] = x[torch.div(order, self.topk, rounding_mode="floor")]
+            send_eids[slot] = idx.reshape(-1)[order]
+            recv_rows = torch.empty_like(send_rows)
+            recv_eids = torch.empty_like(send_eids)
         dist.all_to_all_single(recv_rows, send_rows, group=self.group)
         dist.all_to_all_single(recv_eids, send_eids, group=self.group)
         if side is None:
             shared = self.shared_fn(x)
         eo_recv = self.experts_fn(recv_rows, recv_eids).contiguous()
-        eo_back = torch.empty_like(eo_recv)
-        dist.all_to_all_single(eo_back, eo_recv, group=self.group)
-        eo = torch.empty(R, dim, dtype=x.dtype, device=x.device)
-        eo[order] = eo_back[slot]                        # back to (t, j) order
+        if fused:
+            dist.all_to_all_single(eo_back, eo_recv, group=self.group)
+            check(lib().apus_cuda_moe_ep_rows_dev(eo_back.data_ptr(), dim, slot.data_ptr(), R, self.topk, 1,
+                                                  eo.data_ptr(), self._stream()), "moe_ep_rows_dev")
+        else:
+            eo_back = torch.empty_like(eo_recv)
+            dist.all_to_all_single(eo_back, eo_recv, group=self.group)
+            eo = torch.empty(R, dim, dtype=x.dtype, device=x.device)
+            eo[order] = eo_back[slot]                    # back to (t, j) order
         if side is not None:
             cur.wait_stream(side)
             shared.record_stream(cur)
         return self.combine_fn(eo, wgt, shared)
+
+    _bufs = {}
+
+    def _exchange_bufs(self, device, n_slots, n_rout):
+        """Exchange buffers, kept per (device, shape) and shared by the sublayers, which run
+        one after another on one stream.  Unused row slots are never read by the expert
+        kernels (their expert id is -1), so the rows are not cleared between uses."""
+        key = (str(device), n_slots, n_rout, self.dim)
+        b = ExpertParallelMoe._bufs.get(key)
+        if b is None:
+            f = dict(dtype=torch.float32, device=device)
+            i = dict(dtype=torch.int32, device=device)
+            b = (torch.zeros(n_slots, self.dim, **f), torch.empty(n_slots, **i), torch.empty(n_slots, self.dim, **f),
+                 torch.empty(n_slots, **i), torch.empty(n_slots, self.dim, **f), torch.empty(n_rout, self.dim, **f),
+                 torch.empty(n_rout, **i))
+            ExpertParallelMoe._bufs[key] = b
+        return b
 
 
 def create_handle(moew, e_lo, e_hi):

@@ -395,6 +395,21 @@ int apus_cuda_moe_experts_dev(ApusCudaMoe *m, const float *xrows, int n_rows,
 int apus_cuda_moe_combine_dev(const ApusCudaMoe *m, const float *eo,
                               const float *wgt, const float *shared, int s,
                               float *out, float *routed, void *stream);
+/* The fixed-shape exchange of an expert-parallel sublayer (no counterpart in the
+ * reference): every (source, destination) pair of ranks carries `slots` row slots.
+ * plan: routing p = t*topk + j (idx [n_rout], global expert ids) goes to rank
+ * idx[p] / (n_experts / world), into the next free slot of that rank's block in
+ * the order of p; slot_of [n_rout] receives destination * slots + position,
+ * send_eids [world * slots] the expert ids by slot with -1 in unused slots (the
+ * expert kernels skip those).  rows: gather == 0 copies token row p / topk of src
+ * [s, dim] to dst[slot_of[p]]; gather == 1 copies src[slot_of[p]] (expert outputs
+ * as they came back) to dst[p], i.e. back to (t, j) order. */
+int apus_cuda_moe_ep_plan_dev(const int32_t *idx, int n_rout, int n_experts,
+                              int world, int slots, int32_t *send_eids,
+                              int32_t *slot_of, void *stream);
+int apus_cuda_moe_ep_rows_dev(const float *src, int dim, const int32_t *slot_of,
+                              int n_rout, int topk, int gather, float *dst,
+                              void *stream);
 /* c/moe.h:570-581 on device: the FP8 shared expert for s tokens. */
 int apus_cuda_moe_shared_dev(ApusCudaMoe *m, const float *x, int s,
                              float *shared, void *stream);

@@ -1,4 +1,4 @@
-"""Expert-parallel dispatch/combine host logic over gloo, world size 2, on CPU.
+"""Expert-parallel dispatch/combine host logic over gloo, world sizes 2 and 4, on CPU.
 
 The expert FFN is replaced by a deterministic CPU stand-in so that the test
 checks what the exchange must guarantee: every (token, slot) routing reaches
@@ -78,18 +78,28 @@ def test_dispatch_plan_groups_by_owner():
     assert order.tolist() == [0, 3, 5, 1, 2, 4]          # stable within a destination
 
 
-def test_expert_parallel_exchange_world2():
+def run_world(world):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(timeout=180)
         assert p.exitcode == 0
-    res = [q.get(timeout=10) for _ in range(6)]
+    res = [q.get(timeout=10) for _ in range(3 * world)]
     assert all(ok for _, ok in res), res
+
+
+def test_expert_parallel_exchange_world2():
+    run_world(2)
+
+
+def test_expert_parallel_exchange_world4():
+    """Four ranks of two experts each: the partition, the padded slots and the way back
+    are the same code at 4 and 8 ranks as at 2."""
+    run_world(4)
