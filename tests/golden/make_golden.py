@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Regenerates the committed golden vectors from the reference itself.
 
-Run in a container where the reference checkout is mounted (default
-/root/reference):
+Run in a container where the reference checkout is mounted (its location: the
+APUS_REFERENCE environment variable, else the default below):
 
   1. m3/ and m4a/: the reference's OWN golden generators
      (tests/m3/gen_golden.py, tests/m4a/gen_golden.py; seed 20260729) are

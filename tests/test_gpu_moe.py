@@ -131,3 +131,49 @@ def test_expert_parallel_split_equals_whole():
     for h in hs:
         L.apus_cuda_moe_destroy(h)
     assert np.array_equal(bits(out.cpu().numpy()), bits(whole["out"]))
+
+
+@pytest.mark.parametrize("world,s,topk,E", [(1, 5, 3, 8), (2, 32, 6, 256), (4, 7, 2, 16), (8, 32, 6, 256)])
+def test_exchange_plan_and_row_moves(world, s, topk, E):
+    """The slot planning and row moves of the fixed-shape expert-parallel exchange
+    against the same logic written with tensor ops (the path the gloo tests run)."""
+    import torch
+    from apus_b200.moe import owner_ranks
+    L = lib()
+    g = torch.Generator().manual_seed(world * 100 + s)
+    dim, R = 64, s * topk
+    Cs = R                                                   # slots per destination
+    idx = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(s)]).to(torch.int32)
+    if world > 1:
+        idx[0, :] = 0                                        # a token whose routings all go to rank 0
+    x = torch.randn(s, dim, generator=g)
+    # tensor-op statement (apus_b200/moe.py, CPU path)
+    flat = idx.reshape(-1).long()
+    dest = owner_ranks(flat, E, world)
+    order = torch.argsort(dest, stable=True)
+    dest_s = dest[order]
+    counts = torch.bincount(dest, minlength=world)
+    starts = torch.cumsum(counts, 0) - counts
+    slot_sorted = dest_s * Cs + (torch.arange(R) - starts[dest_s])
+    want_slot = torch.empty(R, dtype=torch.long)
+    want_slot[order] = slot_sorted
+    want_eids = torch.full((world * Cs,), -1, dtype=torch.int32)
+    want_eids[want_slot] = idx.reshape(-1)
+    dev = torch.device("cuda", 0)
+    st = torch.cuda.current_stream().cuda_stream
+    d_idx, d_x = idx.to(dev), x.to(dev)
+    eids = torch.zeros(world * Cs, dtype=torch.int32, device=dev)
+    slot = torch.zeros(R, dtype=torch.int32, device=dev)
+    assert L.apus_cuda_moe_ep_plan_dev(d_idx.data_ptr(), R, E, world, Cs, eids.data_ptr(), slot.data_ptr(), st) == 0
+    assert torch.equal(slot.cpu().long(), want_slot) and torch.equal(eids.cpu(), want_eids)
+    rows = torch.full((world * Cs, dim), -7.0, device=dev)
+    assert L.apus_cuda_moe_ep_rows_dev(d_x.data_ptr(), dim, slot.data_ptr(), R, topk, 0, rows.data_ptr(), st) == 0
+    got = rows.cpu()
+    assert torch.equal(got[want_slot], x[torch.arange(R) // topk])
+    unused = torch.ones(world * Cs, dtype=torch.bool); unused[want_slot] = False
+    assert bool((got[unused] == -7.0).all())                 # unused slots are not touched
+    back = torch.empty(R, dim, device=dev)
+    assert L.apus_cuda_moe_ep_rows_dev(rows.data_ptr(), dim, slot.data_ptr(), R, topk, 1, back.data_ptr(), st) == 0
+    assert torch.equal(back.cpu(), x[torch.arange(R) // topk])
+    assert L.apus_cuda_moe_ep_plan_dev(d_idx.data_ptr(), R, E, world, R - 1, eids.data_ptr(), slot.data_ptr(), st) != 0
+    assert b"slots per rank" in L.apus_cuda_last_error()
