@@ -627,7 +627,7 @@ def fp8_gemm_main(a):
     line = {"metric": "fp8_dense_gemm_us", "workload": "config1: FP8 E4M3 block-scaled GEMM, W [4096,4096]",
             "n_gpus": 1, "results_by_M": res, "hbm_peak_GBs": peak, "peak_kind": peak_kind,
             "note": "act quant + gemm_tc8_kernel + BF16 round per call; L2 flushed between timed calls; "
-                    "M > 32 runs as 32-row work items (weights re-read from L2)"}
+                    "M <= 63 runs as 32-row work items, M >= 64 on the 128-rows-per-CTA kernel"}
     emit(line)
 
 
