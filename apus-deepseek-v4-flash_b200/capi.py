@@ -205,6 +205,9 @@ def load(path=LIB_PATH):
         "apus_cuda_model_create_ep": (vp, [C.POINTER(ModelDesc), ci, ci, ci, ci]),
         "apus_cuda_model_load": (vp, [C.c_char_p, ci, ci, ci, ci]),
         "apus_cuda_model_set_stream": (ci, [vp, vp, ci]),
+        "apus_cuda_model_snapshot": (vp, [vp, vp]),
+        "apus_cuda_model_restore": (ci, [vp, vp]),
+        "apus_cuda_snap_free": (None, [vp]),
         "apus_cuda_model_forward_group": (ci, [vp, ci, vp, ci, vp, vp]),
         "apus_cuda_model_generate_group": (ci, [vp, ci, vp, ci, ci, vp, C.POINTER(cf), C.POINTER(cf)]),
         "apus_cuda_ckpt_open": (vp, [C.c_char_p, C.c_char_p, sz]),

@@ -179,6 +179,19 @@ struct ApusCudaModel {
     StepBufs sb;
 };
 
+// What a rollback needs (reference c/mtp.h:113-138, 398-439): per layer the ring, the
+// compressor carries and the entry counts -- cache entries past a restored count are
+// dead capacity, so rollback is a copy plus truncation -- and the position; here also
+// the device-side position, the fed-back token and the sampler streams.
+struct ApusCudaSnap {
+    struct Layer { DevBuf win, ckv, csc, ikv, isc; int comp_nb = 0, idx_nb = 0; };
+    std::vector<Layer> layers;
+    int B = 0;
+    long long pos = 0;
+    DevBuf pos_dev, tok, ids, rng;
+    bool has_rng = false;
+};
+
 static inline cudaStream_t mstream(const ApusCudaModel *m) { return m->stream ? m->stream : ctx().stream; }
 static BlockBufs model_bufs(ApusCudaModel *m) {
     return {m->x.as<float>(), m->y.as<float>(), m->sub.as<float>(), m->post.as<float>(), m->comb.as<float>(),
@@ -306,6 +319,7 @@ int apus_cuda_model_reset(ApusCudaModel *m) {
     }
     if (m->pos_dev.get(256, nullptr)) return 1;
     APUS_CUDA_OK(cudaMemsetAsync(m->pos_dev.p, 0, 256, mstream(m)));
+    APUS_CUDA_OK(cudaStreamSynchronize(ctx().stream));   // the state was cleared on the library stream
     APUS_CUDA_OK(cudaStreamSynchronize(mstream(m)));
     m->pos = 0;
     return 0;
@@ -675,6 +689,74 @@ int apus_cuda_model_generate(ApusCudaModel *m, const int64_t *prompt, int n_prom
                              float *ms_prefill, float *ms_decode) {
     if (!m) { set_error("NULL model"); return 1; }
     return apus_cuda_model_generate_group(&m, 1, &prompt, n_prompt, n_gen, &out_tokens, ms_prefill, ms_decode);
+}
+
+// ---- snapshots (c/mtp.h:113-138, 398-439) -------------------------------------------------------
+static int snap_copy(DevBuf &dst, const DevBuf &src, size_t bytes, bool to_snap, cudaStream_t st) {
+    if (!bytes) return 0;
+    if (to_snap && dst.get(bytes, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dst.p, src.p, bytes, cudaMemcpyDeviceToDevice, st));
+    return 0;
+}
+static int snap_move(ApusCudaModel *m, ApusCudaSnap *sn, bool take) {
+    cudaStream_t st = mstream(m);
+    const size_t B = m->B;
+    for (int i = 0; i < m->n_layers; i++) {
+        const ApusAttnCfg &c = m->layers[i].attn.cfg;
+        StateDev &S = m->states[i];
+        ApusCudaSnap::Layer &L = sn->layers[i];
+        const size_t wb = B * c.window * c.head_dim * 4, cb = S.comp.carry * B * 4, ib = S.idx.carry * B * 4;
+        DevBuf *pairs[5][2] = {{&L.win, &S.win}, {&L.ckv, &S.comp.kv}, {&L.csc, &S.comp.sc}, {&L.ikv, &S.idx.kv},
+                               {&L.isc, &S.idx.sc}};
+        const size_t bytes[5] = {wb, c.ratio ? cb : 0, c.ratio ? cb : 0, c.ratio && c.has_indexer ? ib : 0,
+                                 c.ratio && c.has_indexer ? ib : 0};
+        for (int k = 0; k < 5; k++)
+            if (take ? snap_copy(*pairs[k][0], *pairs[k][1], bytes[k], true, st)
+                     : snap_copy(*pairs[k][1], *pairs[k][0], bytes[k], false, st))
+                return 1;
+        if (take) { L.comp_nb = S.comp.nb; L.idx_nb = S.idx.nb; }
+        else { S.comp.nb = L.comp_nb; S.idx.nb = L.idx_nb; }
+    }
+    DevBuf *top[3][2] = {{&sn->pos_dev, &m->pos_dev}, {&sn->tok, &m->tok}, {&sn->ids, &m->ids}};
+    const size_t tb[3] = {256, B * 4, B * 8};
+    for (int k = 0; k < 3; k++)
+        if (take ? snap_copy(*top[k][0], *top[k][1], tb[k], true, st) : snap_copy(*top[k][1], *top[k][0], tb[k], false, st))
+            return 1;
+    if (take) sn->has_rng = m->temp > 0.f && m->rng.p;
+    if (sn->has_rng && m->rng.p &&
+        (take ? snap_copy(sn->rng, m->rng, B * 8, true, st) : snap_copy(m->rng, sn->rng, B * 8, false, st)))
+        return 1;
+    if (take) sn->pos = m->pos; else m->pos = sn->pos;
+    return 0;
+}
+
+ApusCudaSnap *apus_cuda_model_snapshot(ApusCudaModel *m, ApusCudaSnap *reuse) {
+    if (!m) { set_error("NULL model"); return nullptr; }
+    if (reuse && ((int)reuse->layers.size() != m->n_layers || reuse->B != m->B)) {
+        set_error("model_snapshot: the snapshot to reuse belongs to another model shape");
+        return nullptr;
+    }
+    ApusCudaSnap *sn = reuse ? reuse : new ApusCudaSnap();
+    if (!reuse) { sn->layers.resize(m->n_layers); sn->B = m->B; }
+    if (snap_move(m, sn, true)) {
+        if (!reuse) apus_cuda_snap_free(sn);
+        return nullptr;
+    }
+    return sn;
+}
+
+int apus_cuda_model_restore(ApusCudaModel *m, const ApusCudaSnap *sn) {
+    if (!m || !sn) { set_error("model_restore: NULL argument"); return 1; }
+    APUS_REQUIRE((int)sn->layers.size() == m->n_layers && sn->B == m->B, "model_restore: snapshot of another model shape");
+    return snap_move(m, const_cast<ApusCudaSnap *>(sn), false);
+}
+
+void apus_cuda_snap_free(ApusCudaSnap *sn) {
+    if (!sn) return;
+    cudaDeviceSynchronize();
+    for (auto &L : sn->layers) { L.win.release(); L.ckv.release(); L.csc.release(); L.ikv.release(); L.isc.release(); }
+    sn->pos_dev.release(); sn->tok.release(); sn->ids.release(); sn->rng.release();
+    delete sn;
 }
 
 // ---- one step in pieces (expert parallelism: the caller runs the MoE sublayer) ----------------

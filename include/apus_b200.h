@@ -549,6 +549,20 @@ int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n,
                                    int n_gen, int32_t *const *out_tokens,
                                    float *ms_prefill, float *ms_decode);
 
+/* c/mtp.h:113-138, 398-439 apus_snap_take / apus_snap_restore on the device (the
+ * rollback of speculative decoding: draft and verify a few positions, keep the
+ * accepted prefix).  A snapshot holds, per layer, the sliding-window ring, the
+ * compressor carries and the entry counts -- cache entries past a restored
+ * count are dead capacity, so rollback is a copy plus truncation -- and the
+ * position, the token fed back for the next step and the sampler streams.
+ * Copies are device-to-device on the model's stream, nothing waits on the host.
+ * snapshot: `reuse` (nullable) is an earlier snapshot of the same model to
+ * overwrite instead of allocating. */
+typedef struct ApusCudaSnap ApusCudaSnap;
+ApusCudaSnap *apus_cuda_model_snapshot(ApusCudaModel *m, ApusCudaSnap *reuse);
+int apus_cuda_model_restore(ApusCudaModel *m, const ApusCudaSnap *snap);
+void apus_cuda_snap_free(ApusCudaSnap *snap);
+
 /* One decode step of all sequences in pieces, on the library stream, for callers
  * that run the MoE sublayer themselves (expert parallelism: route, exchange
  * rows with the expert owners, apus_cuda_moe_experts_dev, exchange back,

@@ -558,3 +558,63 @@ def test_models_side_by_side_equal_one_batch():
     finally:
         for hh in hs:
             L.apus_cuda_model_destroy(hh)
+
+
+def test_snapshot_restore_rolls_back():
+    """apus_cuda_model_snapshot / _restore (reference c/mtp.h:113-138, 398-439): after a
+    rollback the model repeats bit for bit what it did the first time, across compressor
+    block boundaries and ring wrap-around, also when only a prefix of the drafted tokens
+    is replayed (the accept step of speculative decoding)."""
+    L = lib()
+    tag = "model_batch"
+    _, _, B, n_prompt, _ = MODEL_CASES[tag]
+    Mdl, prompts, h = make_model(L, tag, B)
+    V = Mdl.M["vocab"]
+    n = 13                                     # crosses ratio-4 and ratio-8 blocks and the 8-entry ring
+    lg, nxt = np.empty((B, V), np.float32), np.empty(B, np.int32)
+
+    def run(first, steps):
+        toks, lgs = [], []
+        feed = first
+        for _ in range(steps):
+            ids = np.ascontiguousarray(feed.astype(np.int64).reshape(B, 1))
+            assert L.apus_cuda_model_forward(h, P(ids), 1, P(lg), P(nxt)) == 0, L.apus_cuda_last_error()
+            toks.append(nxt.copy()); lgs.append(lg.copy())
+            feed = nxt.copy()
+        return np.stack(toks, 1), np.stack(lgs, 1)
+    snap = other = None
+    try:
+        assert L.apus_cuda_model_forward(h, P(prompts), n_prompt, P(lg), P(nxt)) == 0
+        first = nxt.copy()
+        snap = L.apus_cuda_model_snapshot(h, None)
+        assert snap, L.apus_cuda_last_error()
+        a_tok, a_lg = run(first, n)
+        assert L.apus_cuda_model_pos(h) == n_prompt + n
+        assert L.apus_cuda_model_restore(h, snap) == 0
+        assert L.apus_cuda_model_pos(h) == n_prompt
+        b_tok, b_lg = run(first, n)
+        assert np.array_equal(a_tok, b_tok) and np.array_equal(bits(a_lg), bits(b_lg))
+        # accept 3 drafted tokens: roll back, replay them in one call, go on from there
+        assert L.apus_cuda_model_restore(h, snap) == 0
+        acc = np.ascontiguousarray(np.concatenate([first[:, None], a_tok[:, :2]], 1).astype(np.int64))
+        assert L.apus_cuda_model_forward(h, P(acc), 3, P(lg), P(nxt)) == 0
+        assert np.array_equal(nxt, a_tok[:, 2]) and np.array_equal(bits(lg), bits(a_lg[:, 2]))
+        c_tok, c_lg = run(nxt.copy(), n - 3)
+        assert np.array_equal(c_tok, a_tok[:, 3:]) and np.array_equal(bits(c_lg), bits(a_lg[:, 3:]))
+        # the snapshot object can be overwritten in place; one of another shape is refused
+        assert L.apus_cuda_model_snapshot(h, snap) == snap
+        d_tok, _ = run(c_tok[:, -1], 2)
+        assert L.apus_cuda_model_restore(h, snap) == 0
+        e_tok, _ = run(c_tok[:, -1], 2)
+        assert np.array_equal(d_tok, e_tok)
+        h1 = L.apus_cuda_model_create(C.byref(Mdl.desc), 1, 64)
+        other = L.apus_cuda_model_snapshot(h1, None)
+        assert other and L.apus_cuda_model_restore(h, other) != 0
+        assert not L.apus_cuda_model_snapshot(h, other)
+        L.apus_cuda_model_destroy(h1)
+    finally:
+        if snap:
+            L.apus_cuda_snap_free(snap)
+        if other:
+            L.apus_cuda_snap_free(other)
+        L.apus_cuda_model_destroy(h)
