@@ -243,6 +243,7 @@ def load(path=LIB_PATH):
         "apus_cuda_moe_timing_enabled": (ci, [vp]),
         "apus_cuda_moe_work_items": (C.c_longlong, [vp, ci]),
         "apus_cuda_model_forward": (ci, [vp, vp, ci, vp, vp]),
+        "apus_cuda_model_forward_all": (ci, [vp, vp, ci, vp, vp]),
         "apus_cuda_model_generate": (ci, [vp, vp, ci, ci, vp, C.POINTER(cf), C.POINTER(cf)]),
         "apus_cuda_apply_rope": (ci, [vp, vp, vp, ci, ci, ci, ci]),
         "apus_cuda_hadamard": (ci, [vp, ci, ci]),

@@ -631,6 +631,36 @@ int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s, float *
     return apus_cuda_model_forward_group(&m, 1, &ids, s, &logits, &next);
 }
 
+// c/model.h:651-720 with logits_all: the rows of every position (the verify batch of
+// speculative decoding, c/mtp.h step 2).  Positions are consumed as consecutive steps,
+// which the reference defines to be equal to its batched call.
+int apus_cuda_model_forward_all(ApusCudaModel *m, const int64_t *ids, int s, float *logits_all, int32_t *next_all) {
+    if (!m) { set_error("NULL model"); return 1; }
+    if (s <= 0) return 0;
+    APUS_REQUIRE(m->pos + s <= m->max_pos, "model_forward: position %lld + %d exceeds max_pos %d", m->pos, s, m->max_pos);
+    cudaStream_t st = mstream(m);
+    const size_t B = m->B, V = m->vocab;
+    std::vector<int64_t> cols((size_t)s * B);
+    for (int t = 0; t < s; t++)
+        for (size_t b = 0; b < B; b++) cols[(size_t)t * B + b] = ids[b * s + t];
+    void *dcols;
+    if (m->ws[23].get(cols.size() * 8, &dcols)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dcols, cols.data(), cols.size() * 8, cudaMemcpyHostToDevice, st));
+    for (int t = 0; t < s; t++) {
+        APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, (const int64_t *)dcols + (size_t)t * B, B * 8, cudaMemcpyDeviceToDevice, st));
+        if (model_step(m, true, st)) return 1;
+        if (logits_all)        // row b of this position -> logits_all[b][t]
+            APUS_CUDA_OK(cudaMemcpy2DAsync(logits_all + (size_t)t * V, (size_t)s * V * 4, m->logits.p, V * 4, V * 4, B,
+                                           cudaMemcpyDeviceToHost, st));
+        if (next_all)
+            APUS_CUDA_OK(cudaMemcpy2DAsync(next_all + t, (size_t)s * 4, m->tok.p, 4, 4, B, cudaMemcpyDeviceToHost, st));
+    }
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "model_forward: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
 int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n, const int64_t *const *prompts, int n_prompt,
                                    int n_gen, int32_t *const *out_tokens, float *ms_prefill, float *ms_decode) {
     if (group_check(ms, n, "model_generate")) return 1;

@@ -520,6 +520,11 @@ ApusCudaMoe *apus_cuda_model_moe(ApusCudaModel *m, int layer);
  * copied back when non-NULL. */
 int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s,
                             float *logits, int32_t *next);
+/* The same with the reference's logits_all: logits_all [batch, s, vocab] and
+ * next_all [batch, s] (both nullable) receive every position's row and greedy
+ * (or sampled) pick -- the verify batch of speculative decoding (c/mtp.h). */
+int apus_cuda_model_forward_all(ApusCudaModel *m, const int64_t *ids, int s,
+                                float *logits_all, int32_t *next_all);
 /* c/apus.c:895-944, greedy: prompt [batch, n_prompt] then n_gen tokens per
  * sequence, the sampled token fed back on the device; out_tokens [batch,
  * n_gen].  ms_prefill / ms_decode (nullable) receive the CUDA-event times of

@@ -601,6 +601,16 @@ def test_snapshot_restore_rolls_back():
         assert np.array_equal(nxt, a_tok[:, 2]) and np.array_equal(bits(lg), bits(a_lg[:, 2]))
         c_tok, c_lg = run(nxt.copy(), n - 3)
         assert np.array_equal(c_tok, a_tok[:, 3:]) and np.array_equal(bits(c_lg), bits(a_lg[:, 3:]))
+        # the verify batch: every position's row from one call equals the one-by-one rows
+        assert L.apus_cuda_model_restore(h, snap) == 0
+        k = 5
+        batch_ids = np.ascontiguousarray(np.concatenate([first[:, None], a_tok[:, :k - 1]], 1).astype(np.int64))
+        all_lg, all_nx = np.empty((B, k, V), np.float32), np.empty((B, k), np.int32)
+        assert L.apus_cuda_model_forward_all(h, P(batch_ids), k, P(all_lg), P(all_nx)) == 0, L.apus_cuda_last_error()
+        assert np.array_equal(bits(all_lg), bits(a_lg[:, :k])) and np.array_equal(all_nx, a_tok[:, :k])
+        assert L.apus_cuda_model_pos(h) == n_prompt + k
+        c2_tok, _ = run(all_nx[:, -1].copy(), n - k)
+        assert np.array_equal(c2_tok, a_tok[:, k:])
         # the snapshot object can be overwritten in place; one of another shape is refused
         assert L.apus_cuda_model_snapshot(h, snap) == snap
         d_tok, _ = run(c_tok[:, -1], 2)
