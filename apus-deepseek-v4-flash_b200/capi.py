@@ -27,6 +27,7 @@ class QW(C.Structure):
                 ("O", C.c_int64), ("K", C.c_int64)]
 
 
+DRAFT_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int64, C.POINTER(C.c_int64), C.c_int)
 RESOLVE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int,
                          C.POINTER(QW), C.POINTER(QW), C.POINTER(QW))
 HINT_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int, C.c_int)
@@ -205,6 +206,7 @@ def load(path=LIB_PATH):
         "apus_cuda_model_create_ep": (vp, [C.POINTER(ModelDesc), ci, ci, ci, ci]),
         "apus_cuda_model_load": (vp, [C.c_char_p, ci, ci, ci, ci]),
         "apus_cuda_model_set_stream": (ci, [vp, vp, ci]),
+        "apus_cuda_model_spec_generate": (ci, [vp, vp, ci, ci, ci, DRAFT_FN, vp, vp, vp]),
         "apus_cuda_model_snapshot": (vp, [vp, vp]),
         "apus_cuda_model_restore": (ci, [vp, vp]),
         "apus_cuda_snap_free": (None, [vp]),

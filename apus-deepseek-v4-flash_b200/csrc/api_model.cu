@@ -789,6 +789,71 @@ void apus_cuda_snap_free(ApusCudaSnap *sn) {
     delete sn;
 }
 
+// ---- speculative decoding engine (c/mtp.h:142-190, 531-616 with a caller-supplied proposer) --------
+// The reference's accept rule: every emitted token is the main model's own pick from its
+// own logits row (greedy, or the sampler's draw: one uniform per token in position order),
+// a draft is accepted iff it equals that pick -- so the emitted stream is bit for bit the
+// non-speculative one.  Round: snapshot, verify batch [held, d2..dD], walk, and on a partial
+// match roll back and feed the true prefix again.  The picks are drawn on the device; the
+// rollback rewinds the sampler streams with the rest of the state, so a round consumes
+// exactly one uniform per token that stays.
+int apus_cuda_model_spec_generate(ApusCudaModel *m, const int64_t *prompt, int n_prompt, int n_gen, int depth,
+                                  ApusCudaDraftFn draft, void *draft_ctx, int32_t *out_tokens, uint64_t *stats) {
+    if (!m || !draft) { set_error("model_spec_generate: NULL argument"); return 1; }
+    APUS_REQUIRE(m->B == 1, "model_spec_generate: one sequence per model (batch %d given)", m->B);
+    APUS_REQUIRE(n_prompt >= 1 && n_gen >= 1 && depth >= 1 && depth <= 64, "model_spec_generate: bad sizes");
+    enum { EMITTED, BATCHES, BATCH_TOKENS, REFEED_TOKENS, OFFERED, ACCEPTED, D1_OFFERED, D1_HITS };
+    uint64_t st8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int32_t pick = 0;
+    if (apus_cuda_model_forward(m, prompt, n_prompt, nullptr, &pick)) return 1;
+    int64_t held = pick, q = m->pos;
+    std::vector<int64_t> drafts((size_t)depth), batch((size_t)depth);
+    std::vector<int32_t> picks((size_t)depth);
+    draft(draft_ctx, q, drafts.data(), depth);
+    ApusCudaSnap *snap = nullptr;
+    int emitted = 0, rc = 0;
+    while (emitted < n_gen && !rc) {
+        int D = depth;
+        if (q + D > m->max_pos) D = (int)(m->max_pos - q);
+        if (D <= 0) { set_error("model_spec_generate: position %lld reaches max_pos %d", (long long)q, m->max_pos); rc = 1; break; }
+        st8[D1_OFFERED]++;
+        if (drafts[0] == held) st8[D1_HITS]++;
+        ApusCudaSnap *s2 = apus_cuda_model_snapshot(m, snap);
+        if (!s2) { rc = 1; break; }
+        snap = s2;
+        batch[0] = held;
+        for (int j = 1; j < D; j++) batch[j] = drafts[j];
+        if (apus_cuda_model_forward_all(m, batch.data(), D, nullptr, picks.data())) { rc = 1; break; }
+        st8[BATCHES]++; st8[BATCH_TOKENS] += (uint64_t)D;
+        int matched = 0;
+        int64_t last = -1;
+        if (emitted < n_gen) out_tokens[emitted++] = (int32_t)held;
+        for (int j = 1; j < D; j++) {
+            const int32_t x = picks[j - 1];
+            st8[OFFERED]++;
+            if (drafts[j] == x) {
+                matched++; st8[ACCEPTED]++;
+                if (emitted < n_gen) out_tokens[emitted++] = x;
+            } else { last = x; break; }
+        }
+        if (last < 0) last = picks[D - 1];               // full match: the bonus token
+        if (matched < D - 1) {                           // partial: roll back, feed the true prefix again
+            if (apus_cuda_model_restore(m, snap) || apus_cuda_model_forward_all(m, batch.data(), matched + 1, nullptr, picks.data())) {
+                rc = 1;
+                break;
+            }
+            st8[REFEED_TOKENS] += (uint64_t)(matched + 1);
+        }
+        held = last;
+        q += matched + 1;
+        draft(draft_ctx, q, drafts.data(), depth);
+    }
+    st8[EMITTED] = (uint64_t)emitted;
+    if (snap) apus_cuda_snap_free(snap);
+    if (stats) memcpy(stats, st8, sizeof st8);
+    return rc;
+}
+
 // ---- one step in pieces (expert parallelism: the caller runs the MoE sublayer) ----------------
 int apus_cuda_model_set_ids(ApusCudaModel *m, const int64_t *ids) {
     if (!m) { set_error("NULL model"); return 1; }

@@ -568,6 +568,22 @@ ApusCudaSnap *apus_cuda_model_snapshot(ApusCudaModel *m, ApusCudaSnap *reuse);
 int apus_cuda_model_restore(ApusCudaModel *m, const ApusCudaSnap *snap);
 void apus_cuda_snap_free(ApusCudaSnap *snap);
 
+/* c/mtp.h:142-190, 531-616: the draft/verify engine with a caller-supplied proposer
+ * (the reference's draft_override hook: fill drafts[0..n-1], candidates for
+ * positions q..q+n-1; drafts[0] is only compared with the held token for the
+ * statistics).  One sequence per model.  Emits n_gen tokens after the prompt
+ * that are bit for bit those of apus_cuda_model_generate (greedy or sampled
+ * with the same seed): a draft is accepted iff it equals the model's own pick.
+ * stats (nullable, 8 counters as in ApusSpec): emitted, batches, batch_tokens,
+ * refeed_tokens, offered, accepted, d1_offered, d1_hits.  The verify batch is
+ * consumed as consecutive steps, so this is the engine and its exactness, not
+ * yet a speed-up. */
+typedef void (*ApusCudaDraftFn)(void *ctx, int64_t q, int64_t *drafts, int n);
+int apus_cuda_model_spec_generate(ApusCudaModel *m, const int64_t *prompt,
+                                  int n_prompt, int n_gen, int depth,
+                                  ApusCudaDraftFn draft, void *draft_ctx,
+                                  int32_t *out_tokens, uint64_t *stats);
+
 /* One decode step of all sequences in pieces, on the library stream, for callers
  * that run the MoE sublayer themselves (expert parallelism: route, exchange
  * rows with the expert owners, apus_cuda_moe_experts_dev, exchange back,

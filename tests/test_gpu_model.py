@@ -628,3 +628,64 @@ def test_snapshot_restore_rolls_back():
         if other:
             L.apus_cuda_snap_free(other)
         L.apus_cuda_model_destroy(h)
+
+
+@pytest.mark.parametrize("temp", [0.0, 0.8])
+def test_speculative_engine_emits_the_plain_stream(temp):
+    """apus_cuda_model_spec_generate (reference c/mtp.h:531-616 with its draft_override
+    hook): whatever the proposer offers -- the truth, garbage, or a mix -- the emitted
+    tokens are those of plain decoding, greedy and sampled (same seed), and the counters
+    add up."""
+    from apus_b200 import capi
+    L = lib()
+    tag = "model_one"
+    _, _, B, n_prompt, n_gen = MODEL_CASES[tag]
+    assert B == 1
+    n_gen = 20
+    Mdl, prompts, h = make_model(L, tag, B)
+    try:
+        if temp > 0:
+            assert L.apus_cuda_model_set_sampling(h, temp, 0.9, 77) == 0
+        ext = n_gen + 8                                  # the proposers know a little more than is compared
+        want = np.empty((1, ext), np.int32)
+        assert L.apus_cuda_model_generate(h, P(prompts), n_prompt, ext, P(want), None, None) == 0
+        known, truth = want[0], want[0][:n_gen]
+
+        def proposer(kind):
+            def fn(ctx, q, drafts, n):
+                for i in range(n):                       # drafts[i]: candidate for position q + i
+                    g = q + i - n_prompt                 # index into the generated tokens
+                    t = int(known[g]) if 0 <= g < ext else 0
+                    if kind == "wrong" or (kind == "mixed" and (q + i) % 3 == 0):
+                        t = (t + 1) % Mdl.M["vocab"]
+                    drafts[i] = t
+            return capi.DRAFT_FN(fn)
+        for kind, depth in (("truth", 4), ("wrong", 3), ("mixed", 5), ("truth", 1)):
+            assert L.apus_cuda_model_reset(h) == 0
+            if temp > 0:
+                assert L.apus_cuda_model_set_sampling(h, temp, 0.9, 77) == 0      # same stream again
+            got = np.empty(n_gen, np.int32)
+            st = (C.c_uint64 * 8)()
+            cb = proposer(kind)
+            rc = L.apus_cuda_model_spec_generate(h, P(prompts), n_prompt, n_gen, depth, cb, None, P(got), st)
+            assert rc == 0, L.apus_cuda_last_error()
+            assert np.array_equal(got, truth), (kind, depth, got, truth)
+            emitted, batches, batch_tokens, refeed, offered, accepted, d1_off, d1_hits = list(st)
+            assert emitted == n_gen and batches == d1_off and batch_tokens <= batches * depth
+            if kind == "truth":
+                assert accepted == offered and refeed == 0 and d1_hits == d1_off
+                assert batches <= -(-n_gen // depth) + 1
+            if kind == "wrong":
+                assert accepted == 0 and d1_hits == 0 and batches == n_gen
+                assert refeed == (batches if depth > 1 else 0)
+            if kind == "mixed":
+                assert 0 < accepted < offered and refeed > 0
+        # more than one sequence per model is refused
+        h3 = L.apus_cuda_model_create(C.byref(Mdl.desc), 2, 64)
+        two = np.ascontiguousarray(np.concatenate([prompts, prompts]))
+        assert L.apus_cuda_model_spec_generate(h3, P(two), n_prompt, 4, 2, proposer("truth"), None,
+                                               P(np.empty(4, np.int32)), None) != 0
+        assert b"one sequence" in L.apus_cuda_last_error()
+        L.apus_cuda_model_destroy(h3)
+    finally:
+        L.apus_cuda_model_destroy(h)
