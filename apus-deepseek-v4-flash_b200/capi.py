@@ -222,6 +222,7 @@ def load(path=LIB_PATH):
         "apus_cuda_ckpt_wo_a": (ci, [vp, ci, vp, C.c_uint64]),
         "apus_cuda_ckpt_rope": (ci, [vp, ci, i64, vp, vp]),
         "apus_cuda_ckpt_expert": (ci, [vp, ci, ci, vp, C.c_uint64, C.POINTER(QW), C.POINTER(QW), C.POINTER(QW)]),
+        "apus_cuda_ckpt_layer_digest": (ci, [vp, ci, ci, ci, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
         "apus_cuda_ckpt_read_count": (C.c_uint64, [vp]),
         "apus_cuda_ckpt_read_bytes": (C.c_uint64, [vp]),
         "apus_cuda_use_stream": (ci, [vp, ci]),

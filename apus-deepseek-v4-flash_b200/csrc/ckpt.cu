@@ -813,6 +813,35 @@ int apus_cuda_ckpt_expert(ApusCudaCkpt *c, int layer, int expert, void *slab, ui
     return 0;
 }
 
+int apus_cuda_ckpt_layer_digest(ApusCudaCkpt *c, int layer, int e_lo, int e_hi, uint64_t *digest, uint64_t *bytes) {
+    if (!c || layer < 0 || layer >= c->cfg.n_layers) { set_error("ckpt_layer_digest: bad layer %d", layer); return 1; }
+    CkLayerHost L;
+    std::string why;
+    if (ckpt_load_layer(c, layer, e_lo, e_hi, &L, &why)) { set_error("%s", why.c_str()); return 1; }
+    // FNV-1a over every tensor as the model would receive it, in descriptor order
+    uint64_t h = 1469598103934665603ull, n = 0;
+    auto eat = [&](const void *p, size_t len) {
+        const unsigned char *b = (const unsigned char *)p;
+        for (size_t i = 0; i < len; i++) { h ^= b[i]; h *= 1099511628211ull; }
+        n += len;
+    };
+    const ApusCudaLayerDesc &D = L.desc;
+    const ApusCudaCkptCfg &cf = c->cfg;
+    auto q8 = [&](const ApusFp8W &w) { eat(w.codes, (size_t)w.O * w.K); eat(w.scales, (size_t)(w.O / 128) * (w.K / 128)); };
+    q8(D.aw.wq_a); q8(D.aw.wq_b); q8(D.aw.wkv); q8(D.aw.wo_b);
+    eat(D.aw.wo_a, L.wo_a.size() * 2);
+    for (auto &v : L.f32) eat(v.data(), v.size() * 4);          // in load order (fixed for a layer kind)
+    if (D.mw.tid2eid) eat(D.mw.tid2eid, L.tid2eid.size() * 8);
+    for (int e = 0; e < cf.n_routed_experts; e++)
+        for (const ApusFp4W *w : {&D.mw.w1[e], &D.mw.w2[e], &D.mw.w3[e]})
+            if (w->packed) { eat(w->packed, (size_t)w->O * w->K / 2); eat(w->scales, (size_t)w->O * w->K / 32); }
+    q8(D.mw.sw1); q8(D.mw.sw2); q8(D.mw.sw3);
+    if (D.acfg.has_indexer) q8(D.aw.idx_wq_b);
+    if (digest) *digest = h;
+    if (bytes) *bytes = n;
+    return 0;
+}
+
 uint64_t apus_cuda_ckpt_read_count(const ApusCudaCkpt *c) { return c ? c->reads.load() : 0; }
 uint64_t apus_cuda_ckpt_read_bytes(const ApusCudaCkpt *c) { return c ? c->read_bytes.load() : 0; }
 

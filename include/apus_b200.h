@@ -669,6 +669,12 @@ int apus_cuda_ckpt_rope(const ApusCudaCkpt *c, int ratio, int64_t rows, float *c
  * positional read, otherwise six. */
 int apus_cuda_ckpt_expert(ApusCudaCkpt *c, int layer, int expert, void *slab, uint64_t cap,
                           ApusFp4W *w1, ApusFp4W *w2, ApusFp4W *w3);
+/* Loads one layer into host memory exactly as apus_cuda_model_load does (all
+ * conversions, experts [e_lo, e_hi) read by the I/O threads), and returns an
+ * FNV-1a digest of every tensor in descriptor order plus the byte count: a
+ * check of a container (or of the reader) that needs no GPU. */
+int apus_cuda_ckpt_layer_digest(ApusCudaCkpt *c, int layer, int e_lo, int e_hi,
+                                uint64_t *digest, uint64_t *bytes);
 /* c/st.h:143-144: positional reads issued so far and the bytes they returned. */
 uint64_t apus_cuda_ckpt_read_count(const ApusCudaCkpt *c);
 uint64_t apus_cuda_ckpt_read_bytes(const ApusCudaCkpt *c);

@@ -278,3 +278,69 @@ def test_missing_files_and_broken_shards(tmp_path, ckpt):
     assert lib().apus_cuda_ckpt_tensor(h, b"norm.weight", None, None, None, None) == 1
     assert b"bad header" in lib().apus_cuda_last_error()
     lib().apus_cuda_ckpt_close(h)
+
+
+def fnv1a(chunks):
+    h = 1469598103934665603
+    n = 0
+    for c in chunks:
+        b = bytes(c)
+        n += len(b)
+        for x in b:
+            h = ((h ^ x) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h, n
+
+
+def layer_chunks(L, e_lo, e_hi):
+    """The tensors of a block as a loader must hand them over, in descriptor order
+    (reference c/layer.h:202-330): FP8 views raw, wo_a as BF16 bits, everything loaded
+    through apus_load_f32 widened to f32, local experts raw."""
+    A, Mo = L.attn, L.moe
+    f = lambda a: np.ascontiguousarray(a, np.float32).tobytes()
+    out = []
+    for cs in (A.wq_a, A.wq_b, A.wkv, A.wo_b):
+        out += [cs[0].tobytes(), cs[1].tobytes()]
+    out.append(A.wo_a.tobytes())
+    out += [f(A.q_norm), f(A.kv_norm), f(A.sink), f(L.attn_norm_w), f(L.ffn_norm_w)]
+    if A.ratio:
+        c = A.comp
+        out += [f(c["wkv"]), f(c["wgate"]), f(c["ape"]), f(c["norm"])]
+        if A.ratio == 4:
+            ic = A.idx_comp
+            out += [f(A.idx_wproj), f(ic["wkv"]), f(ic["wgate"]), f(ic["ape"]), f(ic["norm"])]
+    out.append(f(Mo.gate_w))
+    if Mo.tid2eid is None:
+        out.append(f(Mo.gate_bias))
+    for fn, base, scale in (L.hc_attn, L.hc_ffn):
+        out += [f(fn), f(base), f(scale)]
+    if Mo.tid2eid is not None:
+        out.append(Mo.tid2eid.tobytes())
+    for e in range(e_lo, e_hi):
+        for p, s in ((Mo.w1p, Mo.w1s), (Mo.w2p, Mo.w2s), (Mo.w3p, Mo.w3s)):
+            out += [p[e].tobytes(), s[e].tobytes()]
+    for cs in (Mo.sw1, Mo.sw2, Mo.sw3):
+        out += [cs[0].tobytes(), cs[1].tobytes()]
+    if A.ratio == 4:
+        out += [A.idx_wq_b[0].tobytes(), A.idx_wq_b[1].tobytes()]
+    return out
+
+
+@pytest.mark.parametrize("threads", ["1", "3", "8"])
+def test_whole_layers_load_like_the_model_receives_them(ckpt, threads, monkeypatch):
+    """apus_cuda_ckpt_layer_digest runs the host half of apus_cuda_model_load (every
+    conversion, experts read by the I/O threads): same digest as the tensors written,
+    whatever the number of threads; an expert range loads only its experts."""
+    monkeypatch.setenv("APUS_IO_THREADS", threads)
+    tm = ckpt["tm"]
+    E = tm.M["E"]
+    for i, L in enumerate(tm.layers):
+        want, nbytes = fnv1a(layer_chunks(L, 0, E))
+        d, n = C.c_uint64(), C.c_uint64()
+        assert lib().apus_cuda_ckpt_layer_digest(ckpt["h"], i, 0, -1, C.byref(d), C.byref(n)) == 0, \
+            lib().apus_cuda_last_error()
+        assert (d.value, n.value) == (want, nbytes), i
+    want, nbytes = fnv1a(layer_chunks(tm.layers[1], 2, 6))
+    d, n = C.c_uint64(), C.c_uint64()
+    assert lib().apus_cuda_ckpt_layer_digest(ckpt["h"], 1, 2, 6, C.byref(d), C.byref(n)) == 0
+    assert (d.value, n.value) == (want, nbytes)
+    assert lib().apus_cuda_ckpt_layer_digest(ckpt["h"], 9, 0, -1, None, None) == 1
