@@ -159,10 +159,12 @@ def qw(codes, scales, O, K):
 
 
 def declared_symbols():
-    """Every function name include/apus_b200.h declares."""
-    text = HEADER.read_text()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(apus_cuda_\w+)\s*\(", text)))
+    """Every function name the headers under include/ declare."""
+    names = set()
+    for h in sorted(HEADER.parent.glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
+        names |= set(re.findall(r"\b(apus_(?:cuda|synth)_\w+|apus_fnv1a)\s*\(", text))
+    return sorted(names)
 
 
 def load(path=LIB_PATH):
@@ -201,6 +203,7 @@ def load(path=LIB_PATH):
         "apus_cuda_attention": (ci, [C.POINTER(AttnCfg), C.POINTER(AttnW), C.POINTER(AttnS), vp, ci, i64,
                                     vp, vp, vp, C.POINTER(AttnInterm)]),
         "apus_cuda_set_sum_order": (ci, [ci]),
+        "apus_cuda_set_tree_ops": (ci, [ci]),
         "apus_cuda_block_forward": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64]),
         "apus_cuda_model_create": (vp, [C.POINTER(ModelDesc), ci, ci]),
         "apus_cuda_model_create_ep": (vp, [C.POINTER(ModelDesc), ci, ci, ci, ci]),
@@ -282,6 +285,10 @@ def load(path=LIB_PATH):
         "apus_cuda_expert_fp4_dev": (ci, [vp, vp, vp, cf, vp, ci, vp, vp]),
         "apus_cuda_topk_stable_dev": (ci, [vp, ci, ci, vp, ci, vp]),
         "apus_cuda_sparse_attn_dev": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, i64, vp, vp]),
+        "apus_synth_key": (C.c_uint64, [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]),
+        "apus_synth_fill_host": (ci, [vp, ci, C.c_uint64, C.c_uint64, C.c_double, C.c_double, ci]),
+        "apus_synth_fill_dev": (ci, [vp, ci, C.c_uint64, C.c_uint64, C.c_double, C.c_double, vp]),
+        "apus_fnv1a": (C.c_uint64, [vp, C.c_uint64, C.c_uint64]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)

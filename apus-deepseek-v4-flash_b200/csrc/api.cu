@@ -309,9 +309,30 @@ void on_disable(void (*release_all)(), void (*forget_one)(const void *)) {
 }  // namespace apus
 
 namespace apus {
-static int g_sum_order = getenv("APUS_SUM_ORDER") && atoi(getenv("APUS_SUM_ORDER")) == 1 ? APUS_CUDA_SUM_TREE
-                                                                                         : APUS_CUDA_SUM_REFERENCE;
-int sum_order() { return g_sum_order; }
+static int initial_tree_ops() {
+    if (getenv("APUS_SUM_ORDER") && atoi(getenv("APUS_SUM_ORDER")) == 1) return APUS_CUDA_TREE_ALL;
+    if (const char *e = getenv("APUS_TREE_OPS")) return atoi(e) & APUS_CUDA_TREE_ALL;
+    return APUS_CUDA_TREE_DEFAULT;
+}
+static int g_tree_ops = initial_tree_ops();
+static unsigned long long g_sum_epoch = 0;     // bumped whenever the order changes
+int sum_order() { return g_tree_ops == APUS_CUDA_TREE_ALL ? APUS_CUDA_SUM_TREE : APUS_CUDA_SUM_REFERENCE; }
+int tree_ops() { return g_tree_ops; }
+unsigned long long sum_order_epoch() { return g_sum_epoch; }
+
+int ensure_dyn_smem(const void *func, size_t bytes) {
+    if (bytes <= 48 * 1024) return 0;
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> set;      // (kernel, device) -> largest size set
+    int dev = 0;
+    APUS_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = set[{func, dev}];
+    if (bytes <= have) return 0;
+    APUS_CUDA_OK(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    have = bytes;
+    return 0;
+}
 }  // namespace apus
 
 extern "C" {
@@ -355,9 +376,18 @@ int apus_cuda_sample_logits_u(const float *logits, size_t n, float temp, float t
     return 0;
 }
 
+int apus_cuda_set_tree_ops(int mask) {
+    if (mask >= 0 && (mask & APUS_CUDA_TREE_ALL) != apus::g_tree_ops) {
+        apus::g_tree_ops = mask & APUS_CUDA_TREE_ALL;
+        apus::g_sum_epoch++;               // recorded steps chose their kernels by the old setting
+    }
+    return apus::g_tree_ops;
+}
+
 int apus_cuda_set_sum_order(int order) {
-    if (order == APUS_CUDA_SUM_REFERENCE || order == APUS_CUDA_SUM_TREE) apus::g_sum_order = order;
-    return apus::g_sum_order;
+    if (order == APUS_CUDA_SUM_REFERENCE) apus_cuda_set_tree_ops(0);
+    else if (order == APUS_CUDA_SUM_TREE) apus_cuda_set_tree_ops(APUS_CUDA_TREE_ALL);
+    return apus::sum_order();
 }
 
 void apus_cuda_disable(void) {
@@ -546,7 +576,6 @@ int apus_cuda_fp4_gemm_tc(const uint8_t *w, const uint8_t *ws, const uint8_t *ac
     a.scales_a = (const uint8_t *)ds; a.ascales = (const float *)das;
     a.groups = (const TcGroup *)dg; a.n_groups = ng; a.O = O; a.K = K; a.pair = 0; a.round_out = 0;
     a.out = (float *)dout;
-    if (const char *e = getenv("APUS_TC_TX")) a.tx_bytes = atoi(e);
     gemm_tc_status(1);
     if (gemm_tc(a, c.stream)) return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)M * O * 4, cudaMemcpyDeviceToHost, c.stream));

@@ -154,7 +154,8 @@ static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, in
     StepBufs b = b0;
     if (second_set) { b.ckv = b0.ckv2; b.csc = b0.csc2; b.pooled = b0.pooled2; }
     const int cd = (1 + W.overlap) * W.d;
-    if (f32_linear(W.wkv, x, b.ckv, B, dim, cd, 0, st) || f32_linear(W.wgate, x, b.csc, B, dim, cd, 0, st))
+    if (f32_linear(W.wkv, x, b.ckv, B, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st) ||
+        f32_linear(W.wgate, x, b.csc, B, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st))
         return 1;
     const int slot = (int)(pos % W.ratio);
     const int should = (pos + 1) % W.ratio == 0;
@@ -230,7 +231,9 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
                         0.f, rd, cs_pos, B * ih, 0, sc, dp))
                 return 1;
             if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, sc, pos_dev, cs_table, true)) return 1;
-            if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, ih, APUS_CUDA_R_IN | APUS_CUDA_R_OUT, sc)) return 1;
+            if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, ih,
+                           APUS_CUDA_R_IN | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_IDX_WPROJ), sc))
+                return 1;
             const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
             compw = (int)(c.idx_topk < nbs ? c.idx_topk : nbs);
             if (pos_dev) {                         // capacities; the live counts are derived on the device
@@ -273,7 +276,7 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     // grouped low-rank o-projection (c/attn.h:1692-1737)
     const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
     if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, B, sub, ol,
-                           APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT, st))
+                           APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_WO_A), st))
         return 1;
     return qlinear_dev(A.wo_b, b.y, out, B, b.xq, b.xs, true, st);
 }

@@ -166,6 +166,7 @@ struct ApusCudaModel {
     // CUDA graph (one with the head, one without) after the first step ran eagerly
     DevBuf pos_dev;
     cudaGraphExec_t gexec[2] = {nullptr, nullptr};
+    unsigned long long graph_epoch = 0;    // sum_order_epoch() the recorded steps were captured under
     // sampling (temp <= 0: greedy argmax): per-sequence splitmix64 states and the
     // probability scratch live on the device
     float temp = 0.f, top_p = 1.f;
@@ -209,7 +210,7 @@ static int model_head(ApusCudaModel *m, cudaStream_t st) {
         return 1;
     if (rms_norm(m->yh.as<float>(), m->norm_w, m->norm_eps, m->yn.as<float>(), dim, B, st)) return 1;
     if (f32_linear(m->head, m->yn.as<float>(), m->logits.as<float>(), B, dim, m->vocab,
-                   m->head_bf16 ? APUS_CUDA_W_BF16 : 0, st))
+                   (m->head_bf16 ? APUS_CUDA_W_BF16 : 0) | APUS_LIN_CLASS(APUS_CUDA_TREE_HEAD), st))
         return 1;
     if (m->temp > 0.f)                                   // c/sample.h:173-178; greedy otherwise (c/sample.h:76-81)
         return sample_rows(m->logits.as<float>(), m->vocab, B, m->temp, m->top_p, nullptr,
@@ -264,6 +265,11 @@ static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
             APUS_REQUIRE(m->states[i].comp.nb < m->states[i].comp.cap, "layer %d: compressed cache is full", i);
     }
     const int gi = want_logits ? 1 : 0;
+    if (m->graph_epoch != sum_order_epoch()) {            // the sum order picks the kernels: record again
+        for (int i = 0; i < 2; i++)
+            if (m->gexec[i]) { cudaGraphExecDestroy(m->gexec[i]); m->gexec[i] = nullptr; }
+        m->graph_epoch = sum_order_epoch();
+    }
     if (m->use_graph && m->steps_run >= 1 && !model_timing_on(m)) {
         if (!m->gexec[gi]) {
             // capture the launches of one step; nothing in here allocates or synchronises
@@ -778,6 +784,15 @@ ApusCudaSnap *apus_cuda_model_snapshot(ApusCudaModel *m, ApusCudaSnap *reuse) {
 int apus_cuda_model_restore(ApusCudaModel *m, const ApusCudaSnap *sn) {
     if (!m || !sn) { set_error("model_restore: NULL argument"); return 1; }
     APUS_REQUIRE((int)sn->layers.size() == m->n_layers && sn->B == m->B, "model_restore: snapshot of another model shape");
+    for (int i = 0; i < m->n_layers; i++) {               // same layer count and batch is not enough: sizes too
+        const ApusAttnCfg &c = m->layers[i].attn.cfg;
+        const ApusCudaSnap::Layer &L = sn->layers[i];
+        const size_t wb = (size_t)m->B * c.window * c.head_dim * 4, cb = m->states[i].comp.carry * (size_t)m->B * 4,
+                     ib = m->states[i].idx.carry * (size_t)m->B * 4;
+        APUS_REQUIRE(L.win.cap >= wb && (!c.ratio || (L.ckv.cap >= cb && L.csc.cap >= cb)) &&
+                         (!(c.ratio && c.has_indexer) || (L.ikv.cap >= ib && L.isc.cap >= ib)),
+                     "model_restore: layer %d of the snapshot has other sizes than the model's", i);
+    }
     return snap_move(m, const_cast<ApusCudaSnap *>(sn), false);
 }
 

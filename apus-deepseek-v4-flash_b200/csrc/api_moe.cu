@@ -181,7 +181,7 @@ static int shared_run(ApusCudaMoe *m, const float *x, int s, float *shared, cuda
 
 static int route_run(ApusCudaMoe *m, const float *x, const int64_t *ids, const int64_t *table,
                      int s, int32_t *idx, float *wgt, float *sp, float *biased, cudaStream_t st) {
-    if (f32_linear(m->gate_w, x, m->b_logits.as<float>(), s, m->dim, m->E, 0, st)) return 1;
+    if (f32_linear(m->gate_w, x, m->b_logits.as<float>(), s, m->dim, m->E, APUS_LIN_CLASS(APUS_CUDA_TREE_ROUTER), st)) return 1;
     if (!sp) sp = m->b_sp.as<float>();
     if (m->hash) {
         APUS_REQUIRE(table && ids, "hash-routed layer: no tid2eid table / ids on device");
@@ -540,7 +540,7 @@ int apus_cuda_router_score(const ApusMoeW *w, const float *x, int s, float *sp, 
         c.ws[5].get((size_t)s * w->topk * 4, &didx) || c.ws[6].get((size_t)s * w->topk * 4, &dwgt))
         return 1;
     APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)s * w->dim * 4, cudaMemcpyHostToDevice, c.stream));
-    if (f32_linear(gw, (float *)dx, (float *)dl, s, w->dim, w->E, 0, c.stream)) return 1;
+    if (f32_linear(gw, (float *)dx, (float *)dl, s, w->dim, w->E, APUS_LIN_CLASS(APUS_CUDA_TREE_ROUTER), c.stream)) return 1;
     // scores only: run the finish kernel with a zero bias when none is wanted
     if (biased && w->gate_bias)
         APUS_CUDA_OK(cudaMemcpyAsync(dbias, w->gate_bias, (size_t)w->E * 4, cudaMemcpyHostToDevice, c.stream));

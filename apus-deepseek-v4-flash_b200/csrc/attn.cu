@@ -346,23 +346,10 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
     dim3 g1((unsigned)ceil_div(idxw, SA_IDS), (unsigned)ceil_div(h, SA_HEADS), (unsigned)s);
     size_t sm2 = (size_t)idxw * sizeof(float);
     dim3 g2((unsigned)h, (unsigned)s);
-    static size_t cfg1[2] = {0, 0}, cfg2[2] = {0, 0};        // largest sizes configured so far (f32 / BF16 KV)
-    const int kb = kv_bf16 ? 1 : 0;
-    if (sm1 > cfg1[kb] || sm2 > cfg2[kb]) {
-        if (kv_bf16) {
-            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_scores_kernel<true>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1));
-            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)(sm2 > cfg2[kb] ? sm2 : cfg2[kb])));
-        } else {
-            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_scores_kernel<false>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1));
-            APUS_CUDA_OK(cudaFuncSetAttribute(sparse_pv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)(sm2 > cfg2[kb] ? sm2 : cfg2[kb])));
-        }
-        if (sm1 > cfg1[kb]) cfg1[kb] = sm1;
-        if (sm2 > cfg2[kb]) cfg2[kb] = sm2;
-    }
+    // each kernel's limit only ever grows (per device): a later call with a smaller size keeps the larger one
+    if (ensure_dyn_smem(kv_bf16 ? (const void *)sparse_scores_kernel<true> : (const void *)sparse_scores_kernel<false>, sm1) ||
+        ensure_dyn_smem(kv_bf16 ? (const void *)sparse_pv_kernel<true> : (const void *)sparse_pv_kernel<false>, sm2))
+        return 1;
     if (kv_bf16) {
         sparse_scores_kernel<true><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
                                                                        kv_a, na, kv_b, sc, sa, sb);

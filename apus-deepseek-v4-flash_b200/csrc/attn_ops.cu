@@ -130,7 +130,7 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
     APUS_REQUIRE(!(flags & ROW_HADAMARD) || (n & (n - 1)) == 0, "row_ops: Hadamard needs a power of two, n=%d", n);
     if (rows <= 0) return 0;
     size_t smem = (size_t)(n + 64) * sizeof(float);
-    if (sum_order() != APUS_CUDA_SUM_TREE) flags |= ROW_SEQ_SUM;
+    if (!sum_tree(APUS_CUDA_TREE_NORMS)) flags |= ROW_SEQ_SUM;
     const RowDyn none = {nullptr, 0, 0, 0};
     row_ops_kernel<<<rows, n, smem, st>>>(x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
                                           rows_per_cs > 0 ? rows_per_cs : 1, cs_stride, dyn ? *dyn : none);
@@ -259,11 +259,7 @@ int idx_scores(const float *q, const float *wt_raw, float wscale, const float *c
     APUS_REQUIRE(ih <= 64 && ih >= 1, "indexer: %d heads unsupported", ih);
     if (nb <= 0 || n_seq <= 0) return 0;
     size_t smem = ((size_t)ih * idm + IDX_B * idm + IDX_B * ih) * sizeof(float);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(idx_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    if (ensure_dyn_smem((const void *)idx_score_kernel, smem)) return 1;
     dim3 grid((unsigned)((nb + IDX_B - 1) / IDX_B), (unsigned)n_seq);
     idx_score_kernel<<<grid, ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc,
                                                      dyn_pos, ratio);

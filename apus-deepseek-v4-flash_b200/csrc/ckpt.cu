@@ -634,10 +634,24 @@ int ApusCudaCkpt::read_at(int shard, uint64_t off, void *dst, uint64_t n, std::s
     return 0;
 }
 
-// Parses the header of a shard on first use (c/st.h:212-276).
-static int parse_shard(ApusCudaCkpt *c, int si, std::string *why) {
+// Bytes per element of a safetensors dtype this reader knows; 0 = unknown (such tensors are
+// listed but never read through a typed accessor).
+static uint64_t dtype_size(int dt) {
+    switch (dt) {
+    case APUS_CUDA_ST_I8: case APUS_CUDA_ST_U8: case APUS_CUDA_ST_F8_E8M0: case APUS_CUDA_ST_F8_E4M3: return 1;
+    case APUS_CUDA_ST_BF16: case APUS_CUDA_ST_F16: return 2;
+    case APUS_CUDA_ST_F32: case APUS_CUDA_ST_I32: return 4;
+    case APUS_CUDA_ST_I64: return 8;
+    default: return 0;
+    }
+}
+
+// Parses the header of a shard on first use (c/st.h:212-276).  Unlike the reference,
+// which reads a payload into a buffer of the payload's own size, the loader here sizes
+// its buffers from the shape, so a tensor whose data_offsets disagree with dtype x shape
+// is rejected here (as are negative or overflowing shapes).
+static int parse_shard_body(ApusCudaCkpt *c, int si, std::string *why) {
     CkShard &s = c->shards[si];
-    if (s.parsed) return 0;
     const std::string path = c->wdir + "/" + s.file;
     s.fd = open(path.c_str(), O_RDONLY);
     if (s.fd < 0) { *why = fmt("st: cannot open %s", path.c_str()); return 1; }
@@ -667,19 +681,49 @@ static int parse_shard(ApusCudaCkpt *c, int si, std::string *why) {
         t.name = kv.first;
         const JV *dt = kv.second.get("dtype"), *sh = kv.second.get("shape"), *off = kv.second.get("data_offsets");
         t.dtype = dtype_of(dt && dt->kind == JV::STR ? dt->str : "");
+        uint64_t nelem = 1;
         if (sh && sh->kind == JV::ARR) {
-            t.ndim = (int)sh->arr.size() > 8 ? 8 : (int)sh->arr.size();
-            for (int d = 0; d < t.ndim; d++) t.shape[d] = (int64_t)sh->arr[d].num;
+            if (sh->arr.size() > 8) { *why = fmt("st: %s has more than 8 dimensions in %s", t.name.c_str(), path.c_str()); return 1; }
+            t.ndim = (int)sh->arr.size();
+            for (int d = 0; d < t.ndim; d++) {
+                const double v = sh->arr[d].num;
+                if (!(v >= 0) || v > 9.0e15 || v != (double)(int64_t)v) {
+                    *why = fmt("st: bad shape of %s in %s", t.name.c_str(), path.c_str());
+                    return 1;
+                }
+                t.shape[d] = (int64_t)v;
+                if (t.shape[d] && nelem > (uint64_t)1 << 62) { *why = fmt("st: bad shape of %s in %s", t.name.c_str(), path.c_str()); return 1; }
+                if (t.shape[d] && nelem > ((uint64_t)1 << 62) / (uint64_t)t.shape[d]) {
+                    *why = fmt("st: bad shape of %s in %s", t.name.c_str(), path.c_str());
+                    return 1;
+                }
+                nelem *= (uint64_t)t.shape[d];
+            }
         }
         if (!off || off->kind != JV::ARR || off->arr.size() != 2) { *why = fmt("st: bad header in %s", path.c_str()); return 1; }
         const uint64_t a = (uint64_t)off->arr[0].num, b = (uint64_t)off->arr[1].num;
         if (b < a || data_base + b > fsz) { *why = fmt("st: tensor past EOF in %s", path.c_str()); return 1; }
         t.shard = si; t.off = data_base + a; t.nbytes = b - a;
+        const uint64_t esz = dtype_size(t.dtype);
+        if (esz && t.nbytes != nelem * esz) {
+            *why = fmt("st: %s holds %llu bytes but its shape and dtype need %llu in %s", t.name.c_str(),
+                       (unsigned long long)t.nbytes, (unsigned long long)(nelem * esz), path.c_str());
+            return 1;
+        }
         s.by_name[t.name] = (int)s.tensors.size();
         s.tensors.push_back(std::move(t));
     }
     s.parsed = true;
     return 0;
+}
+static int parse_shard(ApusCudaCkpt *c, int si, std::string *why) {
+    CkShard &s = c->shards[si];
+    if (s.parsed) return 0;
+    if (parse_shard_body(c, si, why) == 0) return 0;
+    if (s.fd >= 0) { close(s.fd); s.fd = -1; }          // leave nothing half-filled behind
+    s.tensors.clear();
+    s.by_name.clear();
+    return 1;
 }
 
 const CkTensor *ApusCudaCkpt::find(const std::string &name, std::string *why) {

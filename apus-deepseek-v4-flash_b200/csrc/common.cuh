@@ -16,7 +16,29 @@ extern unsigned long long g_dispatches;        // api.cu: kernels launched
 #define APUS_CUDA_SUM_REFERENCE 0
 #define APUS_CUDA_SUM_TREE 1
 #endif
-int sum_order();                               // api.cu
+int sum_order();                               // api.cu: TREE only when every operator class is in tree order
+unsigned long long sum_order_epoch();          // api.cu: changes whenever the order does
+// Operator classes whose long f32 sums may leave the reference's loop order (public:
+// apus_cuda_set_tree_ops).  sum_tree(op) = this class currently sums in tree / tensor-core order.
+#ifndef APUS_CUDA_TREE_MHC_MAPS
+#define APUS_CUDA_TREE_MHC_MAPS 1
+#define APUS_CUDA_TREE_NORMS 2
+#define APUS_CUDA_TREE_HEAD 4
+#define APUS_CUDA_TREE_WO_A 8
+#define APUS_CUDA_TREE_ROUTER 16
+#define APUS_CUDA_TREE_COMPRESSOR 32
+#define APUS_CUDA_TREE_IDX_WPROJ 64
+#define APUS_CUDA_TREE_LINEAR 128
+#define APUS_CUDA_TREE_ALL 255
+#endif
+int tree_ops();                                // api.cu
+static inline bool sum_tree(int op) { return (tree_ops() & op) != 0; }
+// dense-linear callers name their operator class in bits 8..15 of `flags` (0 = the generic class)
+#define APUS_LIN_CLASS(op) ((op) << 8)
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-DEVICE setting of a kernel: raises it to
+// `bytes` for `func` on the current device unless a size at least as large was set there
+// before (sizes up to 48 KB need no setting).  Thread-safe.  Nonzero + message on failure.
+int ensure_dyn_smem(const void *func, size_t bytes);    // api.cu
 
 #define APUS_CUDA_OK(expr)                                                     \
     do {                                                                       \

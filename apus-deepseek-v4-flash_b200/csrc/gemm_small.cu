@@ -305,12 +305,7 @@ static int launch(const GemmSmallArgs &a, cudaStream_t st) {
         if (part > smem) smem = part;
     }
     auto kern = gemm_small_kernel<FMT, NT, PAIR, ZS>;
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)smem));
-        configured = smem;
-    }
+    if (ensure_dyn_smem((const void *)kern, smem)) return 1;
     dim3 grid((unsigned)(FMT == 8 ? a.O / 16 : ceil_div(a.O, 128)), (unsigned)a.n_groups);
     kern<<<grid, 256, smem, st>>>(a);
     APUS_LAUNCHED();

@@ -282,11 +282,7 @@ static int launch_tc(const TcArgs &a, cudaStream_t st) {
     constexpr int STAGE = TC_A_BYTES * (PAIR ? 2 : 1) + TC_B_BYTES;
     const size_t smem = (size_t)NS * STAGE + 1024 + 256;
     auto kern = gemm_tc_kernel<PAIR, NS>;
-    static bool configured = false;
-    if (!configured) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    if (ensure_dyn_smem((const void *)kern, smem)) return 1;
     dim3 grid((unsigned)(a.O / 128), (unsigned)a.n_groups);
     kern<<<grid, TC_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.pair ? a.map_b : a.map_a),

@@ -366,11 +366,7 @@ int launch_tc8(const Tc8Args &a, cudaStream_t st) {
     const int NC = a.K >> 7;
     const size_t smem = (size_t)NS * STAGE + 1024 + 256 + (size_t)NC * T8_N * 4 + 2 * (size_t)NC * 4;
     auto kern = gemm_tc8_kernel<PAIR, NS>;
-    static bool configured = false;
-    if (!configured) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
-        configured = true;
-    }
+    if (ensure_dyn_smem((const void *)kern, 224 * 1024)) return 1;
     dim3 grid((unsigned)(a.O / 128), (unsigned)((a.M + T8_N - 1) / T8_N));
     kern<<<grid, T8_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.pair ? a.map_b : a.map_a),
@@ -404,11 +400,7 @@ int gemm_tc8_wide(const Tc8Args &a, cudaStream_t st) {
     if (a.M <= 0) return 0;
     const int NC = a.K >> 7;
     const size_t smem = (size_t)T8W_NS * (T8_A_BYTES + T8W_N * 128) + 1024 + 256 + (size_t)NC * T8W_N * 4 + (size_t)NC * 4;
-    static bool configured = false;
-    if (!configured) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(gemm_tc8_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
-        configured = true;
-    }
+    if (ensure_dyn_smem((const void *)gemm_tc8_wide_kernel, 224 * 1024)) return 1;
     dim3 grid((unsigned)(a.O / 128), (unsigned)((a.M + T8W_N - 1) / T8W_N));
     gemm_tc8_wide_kernel<<<grid, T8_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
                                                          *reinterpret_cast<const CUtensorMap *>(a.map_x), a);

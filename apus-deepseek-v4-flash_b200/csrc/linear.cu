@@ -395,12 +395,7 @@ static cudaError_t seq_launch(cudaStream_t st, int batch, const void *w, const f
                               int O, int flags, long long ws, long long xs, int x_ld, long long os, int out_ld) {
     using Cf = SeqCfg<WBF16, R, MTT, MG, NST>;
     auto kern = f32_linear_seq_kernel<WBF16, R, MTT, MG, NST>;
-    static bool configured = false;
-    if (!configured && Cf::SMEM > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::SMEM);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    if (ensure_dyn_smem((const void *)kern, Cf::SMEM)) return cudaErrorInvalidValue;
     const dim3 grid((unsigned)ceil_div(O, Cf::ROWS), (unsigned)ceil_div(M, Cf::TPC), (unsigned)batch);
     kern<<<grid, SQ_THREADS, Cf::SMEM, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
     return cudaSuccess;
@@ -453,7 +448,9 @@ int f32_linear_batched(const void *w, long long w_stride, const float *x, long l
     APUS_REQUIRE(K % 4 == 0 && x_ld % 4 == 0 && x_stride % 4 == 0 && w_stride % 4 == 0,
                  "f32_linear: K=%d and the strides must be multiples of 4", K);
     if (M <= 0 || O <= 0 || batch <= 0) return 0;
-    if (sum_order() != APUS_CUDA_SUM_TREE) {
+    const int op = (flags >> 8) & 0xff;
+    flags &= 0xff;
+    if (!sum_tree(op ? op : APUS_CUDA_TREE_LINEAR)) {
         APUS_REQUIRE(K % 8 == 0 && (w_stride * ((flags & APUS_CUDA_W_BF16) ? 2 : 4)) % 16 == 0,
                      "f32_linear: K=%d must be a multiple of 8", K);
         if ((flags & APUS_CUDA_W_BF16)

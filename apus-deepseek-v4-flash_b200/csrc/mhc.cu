@@ -360,19 +360,16 @@ static float *ensure_raw(size_t floats, float *callers) {
 // raw[row, 0..nmix] for `rows` tokens in the sum order now in force.
 static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float *raw, int rows,
                       cudaStream_t st) {
-    if (sum_order() == APUS_CUDA_SUM_TREE) {
+    if (sum_tree(APUS_CUDA_TREE_MHC_MAPS)) {
         mhc_mix_kernel<<<dim3(nmix + 1, rows), 256, 0, st>>>(x4, fn, nx, nmix, raw);
         APUS_LAUNCHED();
         return 0;
     }
     const int C = nmix + 1;
-    static bool attr_set = false;
-    if (!attr_set) {
-        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_mix_seq_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-        APUS_CUDA_OK(cudaFuncSetAttribute(mhc_pre_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
-        attr_set = true;
-    }
+    if (ensure_dyn_smem((const void *)mhc_mix_seq_kernel<1>, 100 * 1024) ||
+        ensure_dyn_smem((const void *)mhc_mix_seq_kernel<2>, 100 * 1024) ||
+        ensure_dyn_smem((const void *)mhc_pre_finish_kernel, 128 * 1024))
+        return 1;
     const unsigned gy = (unsigned)((C + MIX_CPG - 1) / MIX_CPG);
     if (rows >= 2) {
         // two tokens share a CTA and its read of fn (measured at batch 32: 2 tokens per CTA
@@ -390,7 +387,7 @@ static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float 
     APUS_LAUNCHED();
     return 0;
 }
-static inline int finish_seq() { return sum_order() == APUS_CUDA_SUM_TREE ? 0 : 1; }
+static inline int finish_seq() { return sum_tree(APUS_CUDA_TREE_NORMS) ? 0 : 1; }
 static inline size_t finish_smem(int d) { return finish_seq() ? (size_t)d * sizeof(float) : 0; }
 
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
@@ -443,7 +440,7 @@ int mhc_post(const float *f, const float *res4, const float *post,
 // that must not take the allocator's lock.  For them the scratch of the mHC
 // pre step (the raw map dots, (2+n)*n+1 floats per token) lives in a fixed
 // file-scope device array instead of a grown buffer.  Every GPU that loads the
-// library carries the array (MHC_NOALLOC_MAX_ROWS * 65 floats = 66,560 bytes)
+// library carries the array (MHC_NOALLOC_MAX_ROWS * (MHC_MAX_N * (MHC_MAX_N + 2) + 1) = 256 * 81 floats = 82,944 bytes)
 // until the process exits.
 #define MHC_NOALLOC_MAX_ROWS 256
 #define MHC_NOALLOC_MAX_DEVICES 64

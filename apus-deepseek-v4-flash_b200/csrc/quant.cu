@@ -79,16 +79,10 @@ int rms_norm(const float *x, const float *w, float eps, float *y, int64_t n,
              int64_t rows, cudaStream_t st) {
     if (rows <= 0) return 0;
     int threads = n >= 1024 ? 256 : 128;
-    const int seq = sum_order() == APUS_CUDA_SUM_TREE ? 0 : 1;
+    const int seq = sum_tree(APUS_CUDA_TREE_NORMS) ? 0 : 1;
     const size_t smem = seq ? (size_t)n * sizeof(float) : 0;
     APUS_REQUIRE(smem <= 200 * 1024, "rms_norm: row of %lld elements exceeds the staging buffer", (long long)n);
-    if (smem > 48 * 1024) {
-        static bool attr_set = false;
-        if (!attr_set) {
-            APUS_CUDA_OK(cudaFuncSetAttribute(rms_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-            attr_set = true;
-        }
-    }
+    if (smem > 48 * 1024 && ensure_dyn_smem((const void *)rms_norm_kernel, 200 * 1024)) return 1;
     rms_norm_kernel<<<(unsigned)rows, threads, smem, st>>>(x, w, eps, y, n, seq);
     APUS_LAUNCHED();
     return 0;

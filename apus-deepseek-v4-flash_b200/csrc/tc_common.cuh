@@ -8,7 +8,15 @@
 
 namespace apus {
 
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+// A wait that is not satisfied within this much device time gives up (the kernel then
+// records a code, frees its tensor memory and returns): about a second, far beyond any
+// wait of a healthy launch (whole kernels here run for well under a millisecond).
+constexpr unsigned long long TC_WAIT_BUDGET_NS = 1000000000ull;
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -26,7 +34,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 }
 // Bounded wait for the phase with the given parity; false on expiry or abort.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0;; ++it) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -34,9 +43,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
         if (ok) return true;
-        if ((it & 1023u) == 1023u && *abort_flag) return false;
+        if ((it & 255u) == 255u) {                     // off the fast path: the clock and the abort flag
+            if (*abort_flag) return false;
+            const unsigned long long now = global_ns();
+            if (!t0) t0 = now;
+            else if (now - t0 > TC_WAIT_BUDGET_NS) return false;
+        }
     }
-    return false;
 }
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1,
                                             uint64_t *bar) {

@@ -4,8 +4,11 @@ value distributions of the benchmark's single-operator configurations, and
 handed to the C library as DEVICE pointers inside the same descriptors a host
 loader would fill (the library uses device buffers in place).
 
-torch is used here only as the device allocator and random generator; all
-arithmetic of the token loop is the library's.
+The values come from the library's counter-based generator
+(include/apus_synth.h), which has a host twin: the same model, or any layers
+of it, can be regenerated in host memory for a CPU checker.  torch is used
+here only as the device allocator; all arithmetic of the token loop is the
+library's.
 """
 import ctypes as C
 import math
@@ -80,129 +83,180 @@ def rope_tables(cfg, compressed, rows):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
-class RandomFlashModel:
-    """All weights of the model on one device (experts [e_lo, e_hi) only) plus
-    the ApusCudaModelDesc that points at them.  Keeps every tensor alive."""
+# tensor ids of the synthetic model (the `tensor` argument of apus_synth_key); the
+# layer argument is the layer index, TOP for the tensors outside the blocks
+TOP = 1000
+TENSOR_IDS = {n: i for i, n in enumerate((
+    "wq_a", "wq_a.s", "wq_b", "wq_b.s", "wkv", "wkv.s", "wo_b", "wo_b.s", "wo_a", "q_norm", "kv_norm", "sink",
+    "comp.wkv", "comp.wgate", "comp.ape", "comp.norm", "idx.wkv", "idx.wgate", "idx.ape", "idx.norm",
+    "idx_wq_b", "idx_wq_b.s", "idx_wproj", "gate_w", "gate_bias", "tid2eid",
+    "w1", "w1.s", "w3", "w3.s", "w2", "w2.s", "sw1", "sw1.s", "sw3", "sw3.s", "sw2", "sw2.s",
+    "attn_norm", "ffn_norm", "hc_attn_fn", "hc_attn_base", "hc_ffn_fn", "hc_ffn_base",
+    "embed", "head", "norm", "hc_head_fn", "hc_head_base", "prompt"))}
+# apus_synth.h kinds
+K_U8, K_U8_RANGE, K_F32, K_F32_BF16, K_BF16, K_E4M3, K_I64_MOD, K_I64_SUBSET = range(8)
 
-    def __init__(self, cfg, seed, device, e_lo=0, e_hi=None, max_pos=1024):
-        import torch
+
+def prompt_ids(seed, first_seq, n_seq, n_prompt, vocab):
+    """Prompt token ids [n_seq, n_prompt] of the sequences first_seq..: uniform over
+    the vocabulary, one generator key per GLOBAL sequence index, so rank r of an
+    N-rank job (sequences r*B..) and a single-GPU job agree on sequence 0..B-1."""
+    import apus_b200
+    L = apus_b200.lib()
+    out = np.empty((n_seq, n_prompt), np.int64)
+    for b in range(n_seq):
+        key = L.apus_synth_key(seed, TOP, TENSOR_IDS["prompt"], first_seq + b)
+        apus_b200.check(L.apus_synth_fill_host(out[b].ctypes.data, K_I64_MOD, n_prompt, key, float(vocab), 0.0, 1),
+                        "synth_fill_host")
+    return out
+
+
+class RandomFlashModel:
+    """All weights of the model (experts [e_lo, e_hi) only) plus the
+    ApusCudaModelDesc that points at them.  Keeps every tensor alive.
+
+    Every tensor is filled by the library's counter-based generator
+    (include/apus_synth.h) from a key (seed, layer, tensor id, expert): with
+    device = a CUDA device the tensors are generated in HBM and the descriptors
+    carry device pointers (the library uses them in place); with device =
+    "host" the SAME bits are generated into numpy arrays, which is how a CPU
+    checker runs the reference on the identical model, whole or layer by layer.
+    Ranks of an expert-parallel job build the same model by construction."""
+
+    def __init__(self, cfg, seed, device, e_lo=0, e_hi=None, max_pos=1024, rope=None):
+        import apus_b200
+        self.lib = apus_b200.lib()
+        self.check = apus_b200.check
         self.cfg, self.device = cfg, device
+        self.host = device == "host"
         self.e_lo, self.e_hi = e_lo, cfg.n_experts if e_hi is None else e_hi
         self.keep = []
         self.bytes = 0
-        # replicated tensors come from one generator stream per layer and every
-        # expert from its own stream keyed by (seed, layer, expert), so that the
-        # ranks of an expert-parallel job hold the same model
         self.seed = seed
-        self.g = torch.Generator(device=device)
-        self.g.manual_seed(seed)
-        self.ge = torch.Generator(device=device)
-        self.torch = torch
-        self.rope = {c: rope_tables(cfg, c, max_pos) for c in (False, True)}
+        if not self.host:
+            import torch
+            self.torch = torch
+            self.stream = torch.cuda.current_stream(device).cuda_stream
+        # rope tables are inputs (host cos/sin); `rope` = {False: (cos, sin), True: (cos, sin)} overrides
+        # the ones computed here, e.g. with the very tables a committed reference run used
+        self.rope = rope or {c: rope_tables(cfg, c, max_pos) for c in (False, True)}
         descs = [self._layer(i, r) for i, r in enumerate(cfg.layer_kinds())]
         self._descs = (capi.LayerDesc * cfg.n_layers)(*descs)
-        self.g.manual_seed(self.seed * 1000003 + 999983)
         d = capi.ModelDesc()
         d.n_layers, d.dim, d.hc_mult, d.hc_sinkhorn_iters, d.vocab = (cfg.n_layers, cfg.dim, cfg.hc_mult,
                                                                       cfg.hc_iters, cfg.vocab)
         d.hc_eps, d.norm_eps = cfg.hc_eps, cfg.norm_eps
         d.layers = C.cast(self._descs, C.POINTER(capi.LayerDesc))
         hc, dim = cfg.hc_mult, cfg.dim
-        d.embed, d.embed_bf16 = self._bf16((cfg.vocab, dim), 1.0), 1
-        d.head, d.head_bf16 = self._bf16((cfg.vocab, dim), 0.02), 1
-        d.norm_w = self._f32((dim,), 0.05, 1.0)
-        d.hc_head_fn = self._f32((hc, hc * dim), 0.01)
-        d.hc_head_base = self._f32((hc,), 0.5)
+        d.embed, d.embed_bf16 = self._fill(TOP, "embed", K_BF16, (cfg.vocab, dim), 0.0, 1.0), 1
+        d.head, d.head_bf16 = self._fill(TOP, "head", K_BF16, (cfg.vocab, dim), 0.0, 0.02), 1
+        d.norm_w = self._fill(TOP, "norm", K_F32, (dim,), 1.0, 0.05)
+        d.hc_head_fn = self._fill(TOP, "hc_head_fn", K_F32, (hc, hc * dim), 0.0, 0.01)
+        d.hc_head_base = self._fill(TOP, "hc_head_base", K_F32, (hc,), 0.0, 0.5)
         d.hc_head_scale = 0.8
         self.desc = d
+        if not self.host:
+            self.torch.cuda.synchronize(device)
 
-    # ---- tensor factories (device pointers) ------------------------------------------
-    def _hold(self, t):
+    # ---- tensor factory (device or host pointers) ---------------------------------------
+    _NP = {K_U8: np.uint8, K_U8_RANGE: np.uint8, K_F32: np.float32, K_F32_BF16: np.float32, K_BF16: np.uint16,
+           K_E4M3: np.uint8, K_I64_MOD: np.int64, K_I64_SUBSET: np.int64}
+
+    def _alloc(self, shape, npdtype):
+        if self.host:
+            t = np.empty(shape, npdtype)
+            p, nbytes = t.ctypes.data, t.nbytes
+        else:
+            torch = self.torch
+            td = {np.uint8: torch.uint8, np.float32: torch.float32, np.uint16: torch.int16, np.int64: torch.int64}[npdtype]
+            t = torch.empty(shape, device=self.device, dtype=td)
+            p, nbytes = t.data_ptr(), t.numel() * t.element_size()
         self.keep.append(t)
-        self.bytes += t.numel() * t.element_size()
+        self.bytes += nbytes
+        return t, p
+
+    def _fill_at(self, ptr, layer, name, kind, n, a, b, expert=0):
+        key = self.lib.apus_synth_key(self.seed, layer, TENSOR_IDS[name], expert)
+        if self.host:
+            self.check(self.lib.apus_synth_fill_host(ptr, kind, n, key, a, b, 0), "synth_fill_host")
+        else:
+            self.check(self.lib.apus_synth_fill_dev(ptr, kind, n, key, a, b, self.stream), "synth_fill_dev")
+
+    def _fill(self, layer, name, kind, shape, a=0.0, b=0.0, expert=0):
+        t, p = self._alloc(shape, self._NP[kind])
+        self._fill_at(p, layer, name, kind, int(np.prod(shape)), a, b, expert)
+        return p
+
+    def _const(self, values):
+        if self.host:
+            t = np.asarray(values, np.float32)
+            self.keep.append(t)
+            return t.ctypes.data
+        t = self.torch.tensor(values, device=self.device, dtype=self.torch.float32)
+        self.keep.append(t)
         return t.data_ptr()
 
-    def _f32(self, shape, std, mean=0.0, bf16=False):
-        torch = self.torch
-        t = torch.randn(shape, generator=self.g, device=self.device, dtype=torch.float32) * std + mean
-        if bf16:                        # f32 storage carrying BF16 values, like the reference's widened tensors
-            t = t.to(torch.bfloat16).to(torch.float32)
-        return self._hold(t.contiguous())
-
-    def _bf16(self, shape, std):
-        torch = self.torch
-        t = (torch.randn(shape, generator=self.g, device=self.device, dtype=torch.float32) * std).to(torch.bfloat16)
-        return self._hold(t.view(torch.int16).contiguous())
-
-    def _bytes(self, shape, lo, hi):
-        torch = self.torch
-        return self._hold(torch.randint(lo, hi, shape, generator=self.g, device=self.device, dtype=torch.uint8))
-
-    def _fp8(self, O, K, std=0.02):
+    def _fp8(self, layer, name, O, K, std=0.02):
         """E4M3 codes of N(0, std) / 2^-7 with UE8M0 tile-scale bytes in {119, 120, 121}."""
-        torch = self.torch
-        w = torch.randn((O, K), generator=self.g, device=self.device, dtype=torch.float32) * (std * 128.0)
-        codes = w.to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
-        del w
-        scales = torch.randint(119, 122, ((O + 127) // 128, K // 128), generator=self.g, device=self.device,
-                               dtype=torch.uint8)
-        return capi.QW(self._hold(codes), self._hold(scales), O, K)
+        codes = self._fill(layer, name, K_E4M3, (O, K), 0.0, std * 128.0)
+        scales = self._fill(layer, name + ".s", K_U8_RANGE, ((O + 127) // 128, K // 128), 119, 121)
+        return capi.QW(codes, scales, O, K)
 
-    def _fp4_slab(self, layer, which, O, K):
+    def _fp4_slab(self, layer, name, O, K):
         """The local experts' MXFP4 matrices, expert-major: uniform nibbles, scale
-        bytes uniform in [120, 126]; expert e is drawn from its own stream."""
-        torch = self.torch
+        bytes uniform in [120, 126]; expert e has its own generator key."""
         n = self.e_hi - self.e_lo
-        codes = torch.empty((n, O, K // 2), device=self.device, dtype=torch.uint8)
-        scales = torch.empty((n, O, K // 32), device=self.device, dtype=torch.uint8)
+        _, pc = self._alloc((n, O, K // 2), np.uint8)
+        _, ps = self._alloc((n, O, K // 32), np.uint8)
         for le in range(n):
-            self.ge.manual_seed(((self.seed * 64 + layer) * 1024 + self.e_lo + le) * 4 + which)
-            codes[le].random_(0, 256, generator=self.ge)
-            scales[le].random_(120, 127, generator=self.ge)
-        return self._hold(codes), self._hold(scales)
+            self._fill_at(pc + le * O * (K // 2), layer, name, K_U8, O * (K // 2), 0, 0, self.e_lo + le)
+            self._fill_at(ps + le * O * (K // 32), layer, name + ".s", K_U8_RANGE, O * (K // 32), 120, 126,
+                          self.e_lo + le)
+        return pc, ps
 
     # ---- one layer ----------------------------------------------------------------------------
     def _layer(self, i, ratio):
-        cfg, torch = self.cfg, self.torch
-        self.g.manual_seed(self.seed * 1000003 + i)
+        cfg = self.cfg
         dim, h, hd = cfg.dim, cfg.n_heads, cfg.head_dim
         G, ol, ql = cfg.o_groups, cfg.o_lora, cfg.q_lora
         csa = ratio == 4
         acfg = capi.AttnCfg(dim, h, hd, cfg.rope_dim, ql, G, ol, cfg.window, ratio, int(csa), cfg.idx_heads,
                             cfg.idx_dim, cfg.idx_topk, cfg.norm_eps, 1 << 20)
         aw = capi.AttnW()
-        aw.wq_a, aw.wq_b = self._fp8(ql, dim), self._fp8(h * hd, ql)
-        aw.wkv, aw.wo_b = self._fp8(hd, dim), self._fp8(dim, G * ol)
-        aw.wo_a = self._bf16((G * ol, h * hd // G), 0.02)
-        aw.q_norm, aw.kv_norm = self._f32((ql,), 0.05, 1.0), self._f32((hd,), 0.05, 1.0)
-        aw.sink = self._f32((h,), 0.5)
+        aw.wq_a, aw.wq_b = self._fp8(i, "wq_a", ql, dim), self._fp8(i, "wq_b", h * hd, ql)
+        aw.wkv, aw.wo_b = self._fp8(i, "wkv", hd, dim), self._fp8(i, "wo_b", dim, G * ol)
+        aw.wo_a = self._fill(i, "wo_a", K_BF16, (G * ol, h * hd // G), 0.0, 0.02)
+        aw.q_norm = self._fill(i, "q_norm", K_F32, (ql,), 1.0, 0.05)
+        aw.kv_norm = self._fill(i, "kv_norm", K_F32, (hd,), 1.0, 0.05)
+        aw.sink = self._fill(i, "sink", K_F32, (h,), 0.0, 0.5)
 
-        def comp(dd, overlap, rotate):
+        def comp(pre, dd, overlap, rotate):
             cd = (1 + overlap) * dd
-            return capi.CompW(self._f32((cd, dim), 0.02, bf16=True), self._f32((cd, dim), 0.02, bf16=True),
-                              self._f32((max(ratio, 1), cd), 0.5), self._f32((dd,), 0.05, 1.0),
+            return capi.CompW(self._fill(i, pre + ".wkv", K_F32_BF16, (cd, dim), 0.0, 0.02),
+                              self._fill(i, pre + ".wgate", K_F32_BF16, (cd, dim), 0.0, 0.02),
+                              self._fill(i, pre + ".ape", K_F32, (max(ratio, 1), cd), 0.0, 0.5),
+                              self._fill(i, pre + ".norm", K_F32, (dd,), 1.0, 0.05),
                               ratio, overlap, dd, cfg.rope_dim, rotate, cfg.norm_eps)
         if ratio:
-            aw.comp = comp(hd, int(csa), 0)
+            aw.comp = comp("comp", hd, int(csa), 0)
         if csa:
-            aw.idx_comp = comp(cfg.idx_dim, 1, 1)
-            aw.idx_wq_b = self._fp8(cfg.idx_heads * cfg.idx_dim, ql)
-            aw.idx_wproj = self._f32((cfg.idx_heads, dim), 0.02, bf16=True)
+            aw.idx_comp = comp("idx", cfg.idx_dim, 1, 1)
+            aw.idx_wq_b = self._fp8(i, "idx_wq_b", cfg.idx_heads * cfg.idx_dim, ql)
+            aw.idx_wproj = self._fill(i, "idx_wproj", K_F32_BF16, (cfg.idx_heads, dim), 0.0, 0.02)
 
-        E, inter, nl = cfg.n_experts, cfg.inter, self.e_hi - self.e_lo
+        E, inter = cfg.n_experts, cfg.inter
         mw = capi.MoeW()
         mw.E, mw.topk, mw.inter, mw.dim = E, cfg.topk, inter, dim
         mw.hash = int(i < cfg.n_hash_layers)
         mw.route_scale, mw.limit = cfg.route_scale, cfg.swiglu_limit
-        mw.gate_w = self._f32((E, dim), 0.01, bf16=True)
+        mw.gate_w = self._fill(i, "gate_w", K_F32_BF16, (E, dim), 0.0, 0.01)
         if mw.hash:
-            t = torch.rand((cfg.vocab, E), generator=self.g, device=self.device).argsort(dim=1)[:, :cfg.topk]
-            mw.tid2eid = self._hold(t.to(torch.int64).contiguous())
+            mw.tid2eid = self._fill(i, "tid2eid", K_I64_SUBSET, (cfg.vocab, cfg.topk), float(E), float(cfg.topk))
         else:
-            mw.gate_bias = self._f32((E,), 0.01)
-        p1, s1 = self._fp4_slab(i, 0, inter, dim)
-        p3, s3 = self._fp4_slab(i, 1, inter, dim)
-        p2, s2 = self._fp4_slab(i, 2, dim, inter)
+            mw.gate_bias = self._fill(i, "gate_bias", K_F32, (E,), 0.0, 0.01)
+        p1, s1 = self._fp4_slab(i, "w1", inter, dim)
+        p3, s3 = self._fp4_slab(i, "w3", inter, dim)
+        p2, s2 = self._fp4_slab(i, "w2", dim, inter)
         a1, a2, a3 = (capi.QW * E)(), (capi.QW * E)(), (capi.QW * E)()
         c13, z13 = inter * dim // 2, inter * dim // 32
         for e in range(self.e_lo, self.e_hi):
@@ -212,18 +266,22 @@ class RandomFlashModel:
             a2[e] = capi.QW(p2 + le * c13, s2 + le * z13, dim, inter)
         self.keep += [a1, a2, a3]
         mw.w1, mw.w2, mw.w3 = (C.cast(a, C.POINTER(capi.QW)) for a in (a1, a2, a3))
-        mw.sw1, mw.sw3, mw.sw2 = self._fp8(inter, dim), self._fp8(inter, dim), self._fp8(dim, inter)
+        mw.sw1, mw.sw3 = self._fp8(i, "sw1", inter, dim), self._fp8(i, "sw3", inter, dim)
+        mw.sw2 = self._fp8(i, "sw2", dim, inter)
         mw.layer_id = i
 
         hc = cfg.hc_mult
         nmix = (2 + hc) * hc
         d = capi.LayerDesc()
         d.acfg, d.aw, d.mw = acfg, aw, mw
-        d.attn_norm_w, d.ffn_norm_w = self._f32((dim,), 0.05, 1.0), self._f32((dim,), 0.05, 1.0)
-        d.hc_attn_fn, d.hc_attn_base = self._f32((nmix, hc * dim), 0.01), self._f32((nmix,), 0.5)
-        d.hc_attn_scale = self._hold(torch.tensor([0.7, 1.3, 0.9], device=self.device))
-        d.hc_ffn_fn, d.hc_ffn_base = self._f32((nmix, hc * dim), 0.01), self._f32((nmix,), 0.5)
-        d.hc_ffn_scale = self._hold(torch.tensor([0.7, 1.3, 0.9], device=self.device))
+        d.attn_norm_w = self._fill(i, "attn_norm", K_F32, (dim,), 1.0, 0.05)
+        d.ffn_norm_w = self._fill(i, "ffn_norm", K_F32, (dim,), 1.0, 0.05)
+        d.hc_attn_fn = self._fill(i, "hc_attn_fn", K_F32, (nmix, hc * dim), 0.0, 0.01)
+        d.hc_attn_base = self._fill(i, "hc_attn_base", K_F32, (nmix,), 0.0, 0.5)
+        d.hc_attn_scale = self._const([0.7, 1.3, 0.9])
+        d.hc_ffn_fn = self._fill(i, "hc_ffn_fn", K_F32, (nmix, hc * dim), 0.0, 0.01)
+        d.hc_ffn_base = self._fill(i, "hc_ffn_base", K_F32, (nmix,), 0.0, 0.5)
+        d.hc_ffn_scale = self._const([0.7, 1.3, 0.9])
         cos, sin = self.rope[ratio != 0]
         d.cos, d.sin, d.rope_rows = capi.ptr(cos), capi.ptr(sin), cos.shape[0]
         return d

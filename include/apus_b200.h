@@ -180,24 +180,39 @@ const char *apus_cuda_last_error(void);
 int apus_cuda_kernel_status(int reset);
 /* Order of the long f32 sums whose result the reference defines by its loop
  * order: the mHC map dots and sum of squares (c/mhc.h:159-176), the RMSNorm
- * sum of squares (c/attn.h:371-378).
- *   APUS_CUDA_SUM_REFERENCE (default): one accumulator, index ascending, products
- *     rounded before each add -- the bits of the CPU path; the sums become
- *     chains of dependent adds (about 35 us per mHC map at hc_mult 4 x dim 4096).
- *   APUS_CUDA_SUM_TREE: pairwise tree sums with FMA; faster and closer to the exact
- *     sum, but off the reference by ~1e-5 relative, which flips a BF16 step in a
- *     fraction of a percent of the sublayer inputs (the reference's own NEON
- *     variants differ from its scalar code by as much, c/mhc.h:296-330).
- * order < 0 only queries.  Returns the order now in force.  Environment
- * APUS_SUM_ORDER=1 selects the tree order at load time. */
+ * sum of squares (c/attn.h:371-378), the dense f32/BF16 linears (c/attn.h:460-465).
+ *   APUS_CUDA_SUM_REFERENCE: one accumulator, index ascending, products rounded
+ *     before each add -- the bits of the CPU path; the sums become chains of
+ *     dependent adds (about 35 us per mHC map at hc_mult 4 x dim 4096).
+ *   APUS_CUDA_SUM_TREE: pairwise tree / tensor-core sums with FMA; faster and
+ *     closer to the exact sum, but off the reference by ~1e-6..1e-5 relative, which
+ *     can flip a BF16 step downstream (the reference's own NEON and BLAS variants
+ *     differ from its scalar code by as much, c/mhc.h:296-330, c/blas.h:25-40).
+ * The choice is per operator class (apus_cuda_set_tree_ops, a bit mask of the
+ * classes summed in tree order; mask < 0 only queries; returns the mask in force).
+ * apus_cuda_set_sum_order(REFERENCE / TREE) clears / sets every class; order < 0
+ * only queries; it returns TREE only when every class is in tree order.
+ * Environment at load time: APUS_TREE_OPS=<mask>, or APUS_SUM_ORDER=1 for all. */
+#define APUS_CUDA_SUM_REFERENCE 0
+#define APUS_CUDA_SUM_TREE 1
+#define APUS_CUDA_TREE_MHC_MAPS   1    /* mHC map dots + sum of squares over hc_mult*dim */
+#define APUS_CUDA_TREE_NORMS      2    /* RMSNorm sums of squares (norm, q/kv norm rows, mHC collapse + norm) */
+#define APUS_CUDA_TREE_HEAD       4    /* vocabulary head: logits are unrounded and feed only the pick */
+#define APUS_CUDA_TREE_WO_A       8    /* grouped low-rank o-projection (c/attn.h:1692-1737) */
+#define APUS_CUDA_TREE_ROUTER    16    /* router gate matmul (c/moe.h:352-367) */
+#define APUS_CUDA_TREE_COMPRESSOR 32   /* compressor wkv / wgate projections (c/attn.h:892-1011) */
+#define APUS_CUDA_TREE_IDX_WPROJ 64    /* indexer weights projection (c/attn.h:1105-1168) */
+#define APUS_CUDA_TREE_LINEAR   128    /* apus_cuda_f32_linear / the f32_linear hook */
+#define APUS_CUDA_TREE_ALL      255
+/* The classes in tree order when nothing else is asked for. */
+#define APUS_CUDA_TREE_DEFAULT    0
+int apus_cuda_set_tree_ops(int mask);
+int apus_cuda_set_sum_order(int order);
 /* Run the entry points that take no stream argument (host-pointer tier, model
  * loop) on the caller's stream instead of the library's own, e.g. to order them
  * with the caller's collectives without events; use_own != 0 switches back.
  * The previous stream is synchronised first. */
 int apus_cuda_use_stream(void *stream, int use_own);
-#define APUS_CUDA_SUM_REFERENCE 0
-#define APUS_CUDA_SUM_TREE 1
-int apus_cuda_set_sum_order(int order);
 /* Forget the cached device copy of a weight buffer (the reference frees and
  * reuses host addresses between tests, tests/m7b/README.md:90-94). */
 void apus_cuda_forget(const void *host_ptr);
@@ -452,7 +467,7 @@ int apus_cuda_sparse_attn_dev(const float *q, const float *sink, int h, int d,
 
 /* The fields of the reference's ApusLayer (c/layer.h:45-71) that
  * apus_block_forward reads, gathered in one plain descriptor (the integrator
- * fills it from its ApusLayer).  cos/sin are the rope
+ * fills it from its ApusLayer, field by field).  cos/sin are the rope
  * tables of this layer's theta class, [rope_rows, rope_dim/2]. */
 typedef struct {
     ApusAttnCfg acfg;
@@ -689,7 +704,7 @@ ApusCudaModel *apus_cuda_model_load(const char *dir, int batch, int max_pos, int
  * callers that must not allocate device memory while they run (an engine whose
  * own arena already owns the HBM, a region where allocation is forbidden, a loop
  * that must stay off the allocator's lock): the scratch between its two kernels
- * is a fixed array inside the library, 66,560 bytes on every GPU that loads it,
+ * is a fixed array inside the library, 82,944 bytes on every GPU that loads it,
  * enough for rows <= 256; more rows are rejected with an error.  It calls no
  * cudaMalloc/cudaFree.  The first call on a device resolves the array's device
  * address: make it before any stream capture.  All calls on a device share the

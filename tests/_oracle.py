@@ -74,13 +74,21 @@ def ora():
     return _ora
 
 
+def reference_dir():
+    """Where the reference checkout lies when it is mounted: $APUS_REFERENCE, else a
+    directory named `reference` beside this repository."""
+    import os
+    env = os.environ.get("APUS_REFERENCE")
+    return Path(env) if env else ROOT.parent / "reference"
+
+
 def ref():
     """The unmodified reference build, or None when it is not available."""
     global _ref
     if _ref is None:
         so = ORA_DIR / "_ref" / "libapus_ref.so"
         if not so.exists():
-            if Path("/root/reference/c").exists():
+            if (reference_dir() / "c").exists():
                 subprocess.check_call(["make", "-C", str(ORA_DIR), "ref"],
                                       stdout=subprocess.DEVNULL)
             else:

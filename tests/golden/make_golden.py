@@ -2,7 +2,7 @@
 """Regenerates the committed golden vectors from the reference itself.
 
 Run in a container where the reference checkout is mounted (its location: the
-APUS_REFERENCE environment variable, else the default below):
+APUS_REFERENCE environment variable, else a directory named `reference` beside this repository):
 
   1. m3/ and m4a/: the reference's OWN golden generators
      (tests/m3/gen_golden.py, tests/m4a/gen_golden.py; seed 20260729) are
@@ -10,6 +10,9 @@ APUS_REFERENCE environment variable, else the default below):
      the known-answer fixtures its C tests check the kernels against.
   2. ref_cases.npz: outputs of the unmodified reference C code
      (oracle/_ref/libapus_ref.so) on the seeded cases of tests/cases.py.
+  3. ckpt_case.npz (argument `ckpt`) and flash_case.npz (argument `flash`): the
+     reference's loader + greedy loop on a written checkpoint directory, and its
+     greedy loop on six real-dimension layers of the benchmarked model.
 
 Nothing on the GPU box reads the reference checkout; it only reads these files.
 """
@@ -25,10 +28,9 @@ HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
-REF = Path(os.environ.get("APUS_REFERENCE", "/root/reference"))
-
 import cases                                   # noqa: E402
-from _oracle import P, ref                     # noqa: E402
+from _oracle import P, ref, reference_dir      # noqa: E402
+REF = reference_dir()
 from apus_b200 import capi                     # noqa: E402
 
 
@@ -223,6 +225,18 @@ def ref_checkpoint(L, seed, n_layers, n_prompt, n_gen):
                 hash=hash_, wo_a0=wo, cos_plain=rope[0], sin_plain=rope[1], cos_yarn=rope[2], sin_yarn=rope[3])
 
 
+def main_flash():
+    """The real-dimension six-layer case (tests/flash_case.py): tokens, top-1 margins and a
+    summary of every logits row of the reference's greedy loop -> flash_case.npz."""
+    import flash_case
+    L = ref()
+    assert L is not None, "reference build not available"
+    G = flash_case.run_reference(L, progress=True)
+    G.update(flash_case.rope_arrays())
+    np.savez_compressed(HERE / "flash_case.npz", **G)
+    print("wrote flash_case.npz:", {k: v.shape for k, v in G.items()})
+
+
 def main_ckpt():
     L = ref()
     assert L is not None, "reference build not available"
@@ -406,6 +420,9 @@ if __name__ == "__main__":
     import sys
     if sys.argv[1:] == ["ckpt"]:      # only the checkpoint case (its own file)
         main_ckpt()
+    elif sys.argv[1:] == ["flash"]:   # only the real-dimension model case (its own file; ~23 GB of host memory)
+        main_flash()
     else:
         main()
         main_ckpt()
+        main_flash()

@@ -280,6 +280,43 @@ def test_missing_files_and_broken_shards(tmp_path, ckpt):
     lib().apus_cuda_ckpt_close(h)
 
 
+@pytest.mark.parametrize("delta", [+64, -64])
+def test_shard_whose_offsets_disagree_with_the_shape_is_rejected(tmp_path, ckpt, delta):
+    """The loader sizes its buffers from a tensor's shape, so a header whose data_offsets
+    hold more (or fewer) bytes than dtype x shape must be refused when the shard is
+    parsed, not copied: grow / shrink one tensor's payload range in the header."""
+    d = tmp_path / "bad"
+    shutil.copytree(ckpt["dir"], d)
+    shard = d / "apus-00001.safetensors"
+    raw = shard.read_bytes()
+    hlen = struct.unpack("<Q", raw[:8])[0]
+    hdr = json.loads(raw[8:8 + hlen])
+    names = [n for n in hdr if n != "__metadata__"]
+    last = max(names, key=lambda n: hdr[n]["data_offsets"][1] - hdr[n]["data_offsets"][0])   # the largest payload
+    hdr[last]["data_offsets"][1] += delta
+    doc = json.dumps(hdr, separators=(",", ":")).encode()
+    doc += b" " * ((-len(doc)) % 8)
+    body = raw[8 + hlen:] + (b"\0" * delta if delta > 0 else b"")
+    shard.write_bytes(struct.pack("<Q", len(doc)) + doc + body)
+    h, err = open_ckpt(d)
+    assert h, err
+    assert lib().apus_cuda_ckpt_tensor(h, last.encode(), None, None, None, None) == 1
+    assert b"its shape and dtype need" in lib().apus_cuda_last_error()
+    # nothing half-parsed is left behind: asking again fails the same way
+    assert lib().apus_cuda_ckpt_tensor(h, last.encode(), None, None, None, None) == 1
+    lib().apus_cuda_ckpt_close(h)
+    # negative and absurd shapes
+    hdr[last]["data_offsets"][1] -= delta
+    hdr[last]["shape"] = [-4, 7]
+    doc = json.dumps(hdr, separators=(",", ":")).encode()
+    doc += b" " * ((-len(doc)) % 8)
+    shard.write_bytes(struct.pack("<Q", len(doc)) + doc + raw[8 + hlen:])
+    h, err = open_ckpt(d)
+    assert lib().apus_cuda_ckpt_tensor(h, last.encode(), None, None, None, None) == 1
+    assert b"bad shape" in lib().apus_cuda_last_error()
+    lib().apus_cuda_ckpt_close(h)
+
+
 def fnv1a(chunks):
     h = 1469598103934665603
     n = 0
