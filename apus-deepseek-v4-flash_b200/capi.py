@@ -205,6 +205,7 @@ def load(path=LIB_PATH):
         "apus_cuda_set_sum_order": (ci, [ci]),
         "apus_cuda_set_tree_ops": (ci, [ci]),
         "apus_cuda_block_forward": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64]),
+        "apus_cuda_block_forward_v": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64, i64]),
         "apus_cuda_model_create": (vp, [C.POINTER(ModelDesc), ci, ci]),
         "apus_cuda_model_create_ep": (vp, [C.POINTER(ModelDesc), ci, ci, ci, ci]),
         "apus_cuda_model_load": (vp, [C.c_char_p, ci, ci, ci, ci]),

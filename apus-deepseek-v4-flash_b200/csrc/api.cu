@@ -320,6 +320,33 @@ int sum_order() { return g_tree_ops == APUS_CUDA_TREE_ALL ? APUS_CUDA_SUM_TREE :
 int tree_ops() { return g_tree_ops; }
 unsigned long long sum_order_epoch() { return g_sum_epoch; }
 
+int stream_scratch(cudaStream_t st, size_t bytes, void **ws, size_t n_counters, int **counters) {
+    struct Slot { DevBuf ws, cnt; };
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, Slot> slots;
+    int dev = 0;
+    APUS_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    Slot &s = slots[{dev, st}];
+    if (bytes > s.ws.cap) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cs);
+        APUS_REQUIRE(cs == cudaStreamCaptureStatusNone, "stream scratch would have to grow to %zu bytes inside a stream capture", bytes);
+        if (s.ws.get(bytes + bytes / 4, nullptr)) return 1;
+    }
+    const size_t cb = n_counters * sizeof(int);
+    if (cb > s.cnt.cap) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cs);
+        APUS_REQUIRE(cs == cudaStreamCaptureStatusNone, "stream counters would have to grow inside a stream capture");
+        if (s.cnt.get(cb < 4096 ? 4096 : 2 * cb, nullptr)) return 1;
+        APUS_CUDA_OK(cudaMemset(s.cnt.p, 0, s.cnt.cap));
+    }
+    if (ws) *ws = s.ws.p;
+    if (counters) *counters = s.cnt.as<int>();
+    return 0;
+}
+
 int ensure_dyn_smem(const void *func, size_t bytes) {
     if (bytes <= 48 * 1024) return 0;
     static std::mutex mu;
@@ -377,6 +404,7 @@ int apus_cuda_sample_logits_u(const float *logits, size_t n, float temp, float t
 }
 
 int apus_cuda_set_tree_ops(int mask) {
+    if (mask == -2) return APUS_CUDA_TREE_DEFAULT;
     if (mask >= 0 && (mask & APUS_CUDA_TREE_ALL) != apus::g_tree_ops) {
         apus::g_tree_ops = mask & APUS_CUDA_TREE_ALL;
         apus::g_sum_epoch++;               // recorded steps chose their kernels by the old setting

@@ -482,6 +482,11 @@ ApusCudaModel *apus_cuda_model_load(const char *dir, int batch, int max_pos, int
 
 int apus_cuda_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float hc_eps, float norm_eps,
                             ApusAttnS *st, float *h, const int64_t *ids, int s, int64_t start_pos) {
+    return apus_cuda_block_forward_v(d, hc, iters, hc_eps, norm_eps, st, h, ids, s, start_pos, 0);
+}
+
+int apus_cuda_block_forward_v(const ApusCudaLayerDesc *d, int hc, int iters, float hc_eps, float norm_eps,
+                              ApusAttnS *st, float *h, const int64_t *ids, int s, int64_t start_pos, int64_t vocab) {
     if (ensure_enabled()) return 1;
     if (s <= 0) return 0;
     cudaStream_t sm = ctx().stream;
@@ -489,11 +494,12 @@ int apus_cuda_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float
     const int dim = c.dim, half = c.rope_dim / 2;
     APUS_REQUIRE(start_pos + s <= d->rope_rows, "block_forward: rope table too short");
     LayerDev L;
-    if (layer_weights(*d, hc, 1 << 30, &L, nullptr)) return 1;
-    if (d->mw.hash) {
-        set_error("block_forward: hash-routed layers need the model entry points (vocab size unknown here)");
+    if (d->mw.hash && (vocab <= 0 || !ids)) {
+        set_error("block_forward: a hash-routed layer needs the token ids and the vocabulary size "
+                  "(apus_cuda_block_forward_v)");
         return 1;
     }
+    if (layer_weights(*d, hc, d->mw.hash ? (int)vocab : 1 << 30, &L, nullptr)) return 1;
     L.cs = rope_rows_dev(d->cos, d->sin, d->rope_rows, half);
     L.rope_rows = d->rope_rows;
     if (!L.cs) return 1;

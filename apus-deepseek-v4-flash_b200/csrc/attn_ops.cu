@@ -8,6 +8,7 @@
 // quant-dequant), 371-378 (RMSNorm), 797-819 (compressor finish), 892-1011
 // (compressor decode step), 1027-1067 (indexer q prep and scores),
 // 1356-1388 (q norm + RoPE, window KV finish), 692-737 (index sets).
+#include <cooperative_groups.h>
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -355,9 +356,62 @@ argmax_rows_kernel(const float *__restrict__ x, int n, int32_t *__restrict__ out
     }
 }
 
+// The same for long rows (a vocabulary of 129,280 logits is 517 KB): a cluster of eight CTAs
+// per row, 16-byte loads, the eight candidates combined through distributed shared memory
+// with the same rule (larger value, lower index on ties), so the pick is the scan order's.
+#define AMAX_CL 8
+__device__ __forceinline__ void amax_take(float &v, int &vi, float ov, int oi) {
+    if (ov > v || (ov == v && oi < vi)) { v = ov; vi = oi; }
+}
+__global__ void __cluster_dims__(AMAX_CL, 1, 1) __launch_bounds__(512)
+argmax_rows_cl_kernel(const float *__restrict__ x, int n, int32_t *__restrict__ out) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    __shared__ float s_bv;
+    __shared__ int s_bi;
+    const int row = blockIdx.x / AMAX_CL, rank = (int)cluster.block_rank();
+    const float *r = x + (size_t)row * n;
+    const int n4 = n >> 2;
+    const int per = (n4 + AMAX_CL - 1) / AMAX_CL, q0 = min(n4, rank * per), q1 = min(n4, q0 + per);
+    float v = -INFINITY;
+    int vi = 0x7fffffff;
+    for (int q = q0 + threadIdx.x; q < q1; q += blockDim.x) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(r) + q);
+        amax_take(v, vi, t.x, 4 * q); amax_take(v, vi, t.y, 4 * q + 1);
+        amax_take(v, vi, t.z, 4 * q + 2); amax_take(v, vi, t.w, 4 * q + 3);
+    }
+    if (rank == AMAX_CL - 1)                               // the tail when n is not a multiple of 4
+        for (int i = 4 * n4 + threadIdx.x; i < n; i += blockDim.x) amax_take(v, vi, r[i], i);
+#pragma unroll
+    for (int o = 16; o; o >>= 1)
+        amax_take(v, vi, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, vi, o));
+    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = v; s_i[threadIdx.x >> 5] = vi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        v = threadIdx.x < (blockDim.x >> 5) ? s_v[threadIdx.x] : -INFINITY;
+        vi = threadIdx.x < (blockDim.x >> 5) ? s_i[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o; o >>= 1)
+            amax_take(v, vi, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, vi, o));
+        if (threadIdx.x == 0) { s_bv = v; s_bi = vi; }
+    }
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        v = -INFINITY; vi = 0x7fffffff;
+        for (int q = 0; q < AMAX_CL; q++) amax_take(v, vi, *cluster.map_shared_rank(&s_bv, q), *cluster.map_shared_rank(&s_bi, q));
+        out[row] = vi == 0x7fffffff ? 0 : vi;
+    }
+    cluster.sync();                                        // nobody leaves while its candidate may still be read
+}
+
 int argmax_rows(const float *x, int n, int rows, int32_t *out, cudaStream_t st) {
     if (rows <= 0) return 0;
-    argmax_rows_kernel<<<rows, 1024, 0, st>>>(x, n, out);
+    if (n >= 16384 && n % 4 == 0 && ((uintptr_t)x & 15) == 0)
+        argmax_rows_cl_kernel<<<rows * AMAX_CL, 512, 0, st>>>(x, n, out);
+    else
+        argmax_rows_kernel<<<rows, 1024, 0, st>>>(x, n, out);
     APUS_LAUNCHED();
     return 0;
 }

@@ -29,7 +29,8 @@ unsigned long long sum_order_epoch();          // api.cu: changes whenever the o
 #define APUS_CUDA_TREE_COMPRESSOR 32
 #define APUS_CUDA_TREE_IDX_WPROJ 64
 #define APUS_CUDA_TREE_LINEAR 128
-#define APUS_CUDA_TREE_ALL 255
+#define APUS_CUDA_TREE_FP8_SPLITK 256
+#define APUS_CUDA_TREE_ALL 511
 #endif
 int tree_ops();                                // api.cu
 static inline bool sum_tree(int op) { return (tree_ops() & op) != 0; }

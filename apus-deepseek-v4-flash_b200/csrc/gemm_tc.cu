@@ -306,7 +306,8 @@ int gemm_tc_status(int reset) {
         cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int));
     }
     const int v8 = gemm_tc8_status(reset);          // the FP8 kernel keeps its own word (codes 11..15)
-    return v ? v : v8;
+    const int vb = gemm_tcbf_status(reset);         // and the BF16 kernel (codes 21..23)
+    return v ? v : (v8 ? v8 : vb);
 }
 
 }  // namespace apus

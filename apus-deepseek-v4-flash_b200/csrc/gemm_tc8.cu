@@ -86,11 +86,16 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     if (nrows <= 0) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile_row = (int)blockIdx.x * 128;
+    // K chunk of this CTA: blocks [c0, c1) (the whole K unless the launch splits it, gridDim.z > 1)
+    const int S = (int)gridDim.z, z = (int)blockIdx.z;
+    const int c0 = (int)(((long long)NC * z) / S), c1 = (int)(((long long)NC * (z + 1)) / S);
+    int *s_last = reinterpret_cast<int *>(s_tmem + 2);
 
     if (tid == 0) {
         for (int s = 0; s < NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < NACC; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
         *s_abort = 0;
+        *s_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
@@ -119,9 +124,9 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     if (warp == 4) {
         // ---- TMA producer ----------------------------------------------------------
         if (lane == 0) {
-            for (int i = 0; i < NC && !fail; i++) {
-                const int s = i % NS;
-                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+            for (int i = c0; i < c1 && !fail; i++) {
+                const int it = i - c0, s = it % NS;
+                const uint32_t ph = (uint32_t)(it / NS) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, s_abort)) { fail = 11; break; }
                 uint8_t *st = smem + (size_t)s * STAGE;
                 mbar_expect_tx(&full[s], STAGE);
@@ -134,9 +139,9 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         // ---- MMA issuer: block i accumulates into accumulator i % NACC -------------------
         if (lane == 0) {
             const uint32_t idesc = idesc_f8();
-            for (int i = 0; i < NC && !fail; i++) {
-                const int s = i % NS, b = i % NACC;
-                const uint32_t ph = (uint32_t)(i / NS) & 1u, pb = (uint32_t)(i / NACC) & 1u;
+            for (int i = c0; i < c1 && !fail; i++) {
+                const int it = i - c0, s = it % NS, b = it % NACC;
+                const uint32_t ph = (uint32_t)(it / NS) & 1u, pb = (uint32_t)(it / NACC) & 1u;
                 if (!mbar_wait(&acc_empty[b], pb ^ 1u, s_abort)) { fail = 12; break; }
                 if (!mbar_wait(&full[s], ph, s_abort)) { fail = 13; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -163,9 +168,9 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 #pragma unroll
             for (int n = 0; n < T8_N; n++) accB[n] = 0.f;
         }
-        for (int i = 0; i < NC && !fail; i++) {
-            const int b = i % NACC;
-            const uint32_t pb = (uint32_t)(i / NACC) & 1u;
+        for (int i = c0; i < c1 && !fail; i++) {
+            const int b = (i - c0) % NACC;
+            const uint32_t pb = (uint32_t)((i - c0) / NACC) & 1u;
             if (!mbar_wait(&acc_full[b], pb, s_abort)) { fail = 14; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t d0[32], d1[32];
@@ -193,7 +198,7 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
         if (!fail) {
             const int o = tile_row + tid;
-            if (o < O) {
+            if (o < O && S == 1) {
 #pragma unroll
                 for (int n = 0; n < T8_N; n++) {
                     if (n >= nrows) break;
@@ -202,15 +207,52 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     else v = a.round_out ? bf16_round(accA[n]) : accA[n];
                     a.out[(size_t)(row0 + n) * O + o] = v;
                 }
+            } else if (o < O) {
+                // K split: park this chunk's folded sums, part[(matrix, chunk)][row][o]
+                float *pa = a.part + ((size_t)z * M) * O;
+                float *pb2 = a.part + ((size_t)(S + z) * M) * O;
+#pragma unroll
+                for (int n = 0; n < T8_N; n++) {
+                    if (n >= nrows) break;
+                    pa[(size_t)(row0 + n) * O + o] = accA[n];
+                    if (PAIR) pb2[(size_t)(row0 + n) * O + o] = accB[n];
+                }
+                __threadfence();
             }
         }
     }
     if (fail) {
         *s_abort = 1;
         atomicCAS(&g_tc8_status, 0, fail);
-        // give copies already issued to this CTA's shared memory time to land
-        for (int i = 0; i < 2000; i++) __nanosleep(1000);
     }
+    if (S > 1) {
+        // the chunk that arrives last at this output tile adds the chunks in chunk order and finishes the row
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0 && !*s_abort) {
+            const int slot = (int)blockIdx.y * (int)gridDim.x + (int)blockIdx.x;
+            const int prev = atomicAdd(&a.counters[slot], 1);
+            if (prev == S - 1) { a.counters[slot] = 0; *s_last = 1; }     // left clean for the next launch
+            __threadfence();
+        }
+        __syncthreads();
+        const int o = tile_row + tid;
+        if (*s_last && tid < 128 && o < O) {
+            for (int n = 0; n < nrows; n++) {
+                float va = 0.f, vb = 0.f;
+                for (int c = 0; c < S; c++) {
+                    va = __fadd_rn(va, __ldcg(a.part + ((size_t)c * M + row0 + n) * O + o));
+                    if (PAIR) vb = __fadd_rn(vb, __ldcg(a.part + ((size_t)(S + c) * M + row0 + n) * O + o));
+                }
+                float v;
+                if (PAIR) v = swiglu8(va, vb, a.limit);
+                else v = a.round_out ? bf16_round(va) : va;
+                a.out[(size_t)(row0 + n) * O + o] = v;
+            }
+        }
+    }
+    if (fail)       // give copies already issued to this CTA's shared memory time to land
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 5)
@@ -367,7 +409,7 @@ int launch_tc8(const Tc8Args &a, cudaStream_t st) {
     const size_t smem = (size_t)NS * STAGE + 1024 + 256 + (size_t)NC * T8_N * 4 + 2 * (size_t)NC * 4;
     auto kern = gemm_tc8_kernel<PAIR, NS>;
     if (ensure_dyn_smem((const void *)kern, 224 * 1024)) return 1;
-    dim3 grid((unsigned)(a.O / 128), (unsigned)((a.M + T8_N - 1) / T8_N));
+    dim3 grid((unsigned)(a.O / 128), (unsigned)((a.M + T8_N - 1) / T8_N), (unsigned)(a.ksplit > 1 ? a.ksplit : 1));
     kern<<<grid, T8_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.pair ? a.map_b : a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.map_x), a);
@@ -413,13 +455,33 @@ int tc8_make_act_map_wide(void *out_map, const void *codes, long long rows, int 
     return tc8_make_weight_map(out_map, codes, rows, K);
 }
 
-int gemm_tc8(const Tc8Args &a, cudaStream_t st) {
+int gemm_tc8(const Tc8Args &a0, cudaStream_t st) {
+    Tc8Args a = a0;
     APUS_REQUIRE(a.K % 128 == 0 && a.K <= 128 * T8_MAX_NC && a.O % 128 == 0,
                  "gemm_tc8: unsupported shape O=%d K=%d", a.O, a.K);
     if (a.M <= 0) return 0;
-    // few CTAs (small O): one CTA per SM with a deep ring, so that each CTA keeps
-    // ~200 KB of weight tiles in flight; many CTAs: two per SM with a short ring
-    const long long ctas = (long long)(a.O / 128) * ((a.M + T8_N - 1) / T8_N);
+    long long ctas = (long long)(a.O / 128) * ((a.M + T8_N - 1) / T8_N);
+    // A matrix with fewer output tiles than SMs streams on a few SMs only (each pulls ~25-45
+    // GB/s): split K over grid.z so that most SMs take part.  Every chunk folds its blocks in
+    // order; the chunk sums are added in chunk order by the CTA that finishes last -- a
+    // deterministic result, but not the bits of the single in-order fold, hence tied to the
+    // tree-order setting (apus_cuda_set_tree_ops).
+    a.ksplit = 1;
+    if (sum_tree(APUS_CUDA_TREE_FP8_SPLITK) && ctas < 74) {
+        const int NC = a.K >> 7;
+        int S = (int)(148 / ctas);
+        if (S > NC) S = NC;
+        if (S > 32) S = 32;
+        if (S > 1) {
+            void *ws = nullptr;
+            int *cnt = nullptr;
+            if (stream_scratch(st, (size_t)S * (a.pair ? 2 : 1) * a.M * a.O * 4, &ws, (size_t)ctas, &cnt)) return 1;
+            a.ksplit = S; a.part = (float *)ws; a.counters = cnt;
+            ctas *= S;
+        }
+    }
+    // few CTAs: one CTA per SM with a deep ring, so that each CTA keeps ~200 KB of weight
+    // tiles in flight; many CTAs: two per SM with a short ring
     if (a.pair) return ctas <= 148 ? launch_tc8<true, 5>(a, st) : launch_tc8<true, 3>(a, st);
     return ctas <= 148 ? launch_tc8<false, 10>(a, st) : launch_tc8<false, 4>(a, st);
 }

@@ -90,12 +90,38 @@ struct Tc8Args {
     int M, O, K, pair, round_out;        // activation rows 32*y .. of CTA row y
     float limit;
     float *out;                          // [M, O]
+    int ksplit;                          // set by gemm_tc8: K chunks (grid.z); > 1 uses part + counters
+    float *part;                         // [(pair ? 2 : 1) * ksplit, M, O] chunk sums
+    int *counters;                       // zeroed, one per (output tile, row group); left zeroed
 };
 int gemm_tc8(const Tc8Args &a, cudaStream_t st);
 int gemm_tc8_wide(const Tc8Args &a, cudaStream_t st);      // 128 activation rows per CTA; map_x from tc8_make_act_map_wide
 int tc8_make_act_map_wide(void *out_map, const void *codes, long long rows, int K);
 int gemm_tc8_status(int reset);
 int tc8_make_weight_map(void *out_map, const void *codes, long long rows, int K);
+
+// ---- tcgen05 BF16 GEMM on row-major BF16 weights (gemm_tcbf.cu) ---------------------------
+// out[m, g*O + o] = sum_k x[m, g*x_koff + k] * w[g*O + o, k] for g < batch (tree-order class).
+struct TcbfArgs {
+    const void *map_w, *map_x;           // host pointers to CUtensorMap objects (tcbf_make_*_map)
+    int M, O, K, batch;
+    int x_koff;                          // activation column offset between problems (elements)
+    int out_ld, round_out;
+    float *out;                          // [M, out_ld]
+    int ksplit;                          // K chunks (tcbf_ksplit); > 1 needs part + counters
+    float *part;                         // [ksplit, M, batch*O] scratch
+    int *counters;                       // zeroed, one per (output tile, row group); left zeroed
+};
+int gemm_tcbf(const TcbfArgs &a, cudaStream_t st);
+int gemm_tcbf_status(int reset);
+int tcbf_ksplit(int O, int K, int batch, int M);
+int tcbf_make_weight_map(void *out_map, const void *w_bf16, long long rows, int K);
+int tcbf_make_act_map(void *out_map, const void *x_bf16, long long rows, long long cols);
+int f32_to_bf16(const float *x, uint16_t *y, long long n, cudaStream_t st);
+// Scratch memory that belongs to a stream (launches on one stream run one after another, so
+// they may share it): `bytes` of workspace and, separately, `n_counters` ints that are zero
+// whenever no kernel is using them.  Grows on demand (not while the stream is being captured).
+int stream_scratch(cudaStream_t st, size_t bytes, void **ws, size_t n_counters, int **counters);
 
 // ---- temperature / top-p sampling (sample.cu; reference c/sample.h) ------------------------
 int sample_rows(const float *logits, int n, int rows, float temp, float top_p, const double *u,

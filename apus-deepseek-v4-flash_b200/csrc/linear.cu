@@ -442,6 +442,30 @@ static void launch_linear(const void *w, long long ws, const float *x, long long
     }
 }
 
+// BF16 weights [batch*O, K] on the tcgen05 kernel (gemm_tcbf.cu): the activations [M, x_ld] are
+// copied as BF16 (exact for BF16-valued rows; APUS_CUDA_R_IN asks for that rounding anyway) into
+// the stream's scratch, which also holds the K-split partial sums.
+static int linear_tcbf(const void *w, const float *x, int x_koff, int x_ld, float *out, int out_ld, int batch, int M,
+                       int K, int O, int flags, cudaStream_t st) {
+    const int S = tcbf_ksplit(O, K, batch, M);
+    const size_t xb = (((size_t)M * x_ld * 2) + 255) & ~(size_t)255;
+    const size_t pb = S > 1 ? (size_t)S * M * batch * O * 4 : 0;
+    const size_t n_cnt = (size_t)(O / 128) * batch * ((M + 31) / 32);
+    void *ws = nullptr;
+    int *cnt = nullptr;
+    if (stream_scratch(st, xb + pb, &ws, n_cnt, &cnt)) return 1;
+    uint16_t *xh = (uint16_t *)ws;
+    if (f32_to_bf16(x, xh, (long long)M * x_ld, st)) return 1;
+    alignas(64) unsigned char map_w[128], map_x[128];
+    if (tcbf_make_weight_map(map_w, w, (long long)batch * O, K) || tcbf_make_act_map(map_x, xh, M, x_ld)) return 1;
+    TcbfArgs a = {};
+    a.map_w = map_w; a.map_x = map_x;
+    a.M = M; a.O = O; a.K = K; a.batch = batch; a.x_koff = x_koff;
+    a.out_ld = out_ld; a.round_out = (flags & APUS_CUDA_R_OUT) ? 1 : 0; a.out = out;
+    a.ksplit = S; a.part = (float *)((char *)ws + xb); a.counters = cnt;
+    return gemm_tcbf(a, st);
+}
+
 int f32_linear_batched(const void *w, long long w_stride, const float *x, long long x_stride, int x_ld,
                        float *out, long long out_stride, int out_ld, int batch, int M, int K, int O,
                        int flags, cudaStream_t st) {
@@ -450,7 +474,12 @@ int f32_linear_batched(const void *w, long long w_stride, const float *x, long l
     if (M <= 0 || O <= 0 || batch <= 0) return 0;
     const int op = (flags >> 8) & 0xff;
     flags &= 0xff;
-    if (!sum_tree(op ? op : APUS_CUDA_TREE_LINEAR)) {
+    const bool tree = sum_tree(op ? op : APUS_CUDA_TREE_LINEAR);
+    // BF16 weights in tree order: the tensor-core kernel, when the problems are laid out as it reads them
+    if (tree && (flags & APUS_CUDA_W_BF16) && O % 128 == 0 && K % 64 == 0 && x_ld % 8 == 0 && ((uintptr_t)w & 15) == 0 &&
+        (batch == 1 || (w_stride == (long long)O * K && out_stride == O)) && x_stride * (long long)(batch - 1) + K <= x_ld)
+        return linear_tcbf(w, x, (int)x_stride, x_ld, out, out_ld, batch, M, K, O, flags, st);
+    if (!tree) {
         APUS_REQUIRE(K % 8 == 0 && (w_stride * ((flags & APUS_CUDA_W_BF16) ? 2 : 4)) % 16 == 0,
                      "f32_linear: K=%d must be a multiple of 8", K);
         if ((flags & APUS_CUDA_W_BF16)

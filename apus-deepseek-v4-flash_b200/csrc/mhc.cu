@@ -12,6 +12,7 @@
 //      collapsed row in the same kernel (reference c/attn.h:371-378).
 // Bytes per token: fn (nmix*n*d*4, L2-resident across tokens) + 2 reads of the
 // n*d state.
+#include <cooperative_groups.h>
 #include <map>
 #include "common.cuh"
 #include "kernels.cuh"
@@ -318,6 +319,105 @@ mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ ra
     }
 }
 
+// The same step with a token spread over a cluster of MHC_CL CTAs (tree-order norms only):
+// one CTA walking a 4 x 4096 state alone takes ~30 us, most of it latency (gates -> 64 KB of
+// loads through one SM -> sum of squares -> second pass), and at small batches that chain
+// sits twice in every layer.  Here every CTA of the cluster collapses its slice of the row,
+// the slices' sums of squares meet through distributed shared memory (added in rank order,
+// the same total in every CTA), and each CTA normalises its own slice; the Sinkhorn part,
+// which nothing in this kernel waits for, runs on one warp of the last CTA afterwards.
+#define MHC_CL 8
+__global__ void __cluster_dims__(MHC_CL, 1, 1) __launch_bounds__(128)
+mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__ raw, int d, int n,
+                         int nmix, const float *__restrict__ scale, float head_scale,
+                         const float *__restrict__ base, float norm_eps, float hc_eps, int iters,
+                         int head_mode, const float *__restrict__ norm_w, float rms_eps,
+                         float *__restrict__ pre_out, float *__restrict__ post_out,
+                         float *__restrict__ comb_out, float *__restrict__ y,
+                         float *__restrict__ y_normed) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float s_pre[MHC_MAX_N];
+    __shared__ float red[32];
+    __shared__ float s_part;
+    const int row = blockIdx.x / MHC_CL, rank = (int)cluster.block_rank();
+    const int tid = threadIdx.x;
+    const float *rw = raw + (size_t)row * (nmix + 1);
+    const float mean = __fdiv_rn(rw[nmix], (float)(n * d));
+    const float r = __fdiv_rn(1.0f, sqrtf(__fadd_rn(mean, norm_eps)));
+    if (tid < n) {
+        const float m = __fmul_rn(rw[tid], r);
+        const float sc = head_mode ? head_scale : scale[0];
+        s_pre[tid] = __fadd_rn(sigm(__fadd_rn(__fmul_rn(m, sc), base[tid])), hc_eps);
+        if (pre_out && rank == 0) pre_out[(size_t)row * n + tid] = s_pre[tid];
+    }
+    __syncthreads();
+    // this CTA's slice of the row: [i0, i1), a multiple of 4 wide
+    const int per = ((d + MHC_CL * 4 - 1) / (MHC_CL * 4)) * 4;
+    const int i0 = min(d, rank * per), i1 = min(d, i0 + per);
+    const float *x = x4 + (size_t)row * n * d;
+    float ss = 0.f;
+    if (y) {
+        for (int i = i0 + tid * 4; i < i1; i += blockDim.x * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < n; j++) {
+                const float4 v = *reinterpret_cast<const float4 *>(x + (size_t)j * d + i);
+                const float p = s_pre[j];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(p, v.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(p, v.y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(p, v.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(p, v.w));
+            }
+            acc.x = bf16_round(acc.x); acc.y = bf16_round(acc.y); acc.z = bf16_round(acc.z); acc.w = bf16_round(acc.w);
+            *reinterpret_cast<float4 *>(y + (size_t)row * d + i) = acc;
+            ss = fmaf(acc.x, acc.x, ss); ss = fmaf(acc.y, acc.y, ss); ss = fmaf(acc.z, acc.z, ss); ss = fmaf(acc.w, acc.w, ss);
+        }
+    }
+    if (y && y_normed) {
+        const float mine = block_sum(ss, red);
+        if (tid == 0) s_part = mine;
+        cluster.sync();
+        float tot = 0.f;
+        for (int q = 0; q < MHC_CL; q++) tot = __fadd_rn(tot, *cluster.map_shared_rank(&s_part, q));
+        cluster.sync();                            // nobody leaves while its partial sum may still be read
+        const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)d), rms_eps)));
+        for (int i = i0 + tid * 4; i < i1; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(y + (size_t)row * d + i);
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
+            float4 o;
+            o.x = bf16_round(__fmul_rn(w.x, __fmul_rn(v.x, inv))); o.y = bf16_round(__fmul_rn(w.y, __fmul_rn(v.y, inv)));
+            o.z = bf16_round(__fmul_rn(w.z, __fmul_rn(v.z, inv))); o.w = bf16_round(__fmul_rn(w.w, __fmul_rn(v.w, inv)));
+            *reinterpret_cast<float4 *>(y_normed + (size_t)row * d + i) = o;
+        }
+    }
+    if (head_mode || rank != MHC_CL - 1 || (tid >> 5) != 1) return;
+    // post gates and the Sinkhorn-normalised comb matrix (reference c/mhc.h:181-234), one warp
+    const int l = tid & 31;
+    if (l < n) {
+        const float m2 = __fmul_rn(rw[n + l], r);
+        const float po = __fmul_rn(2.0f, sigm(__fadd_rn(__fmul_rn(m2, scale[1]), base[n + l])));
+        if (post_out) post_out[(size_t)row * n + l] = po;
+    }
+    const bool on = l < n * n;
+    const int j = on ? l / n : 0, k = on ? l - j * n : 0;
+    float c = on ? __fadd_rn(__fmul_rn(__fmul_rn(rw[2 * n + l], r), scale[2]), base[2 * n + l]) : 0.f;
+    float mx = __shfl_sync(0xffffffffu, c, j * n);
+    for (int q = 1; q < n; q++) mx = fmaxf(mx, __shfl_sync(0xffffffffu, c, j * n + q));
+    c = exp_rn(c - mx);
+    float sum = 0.f;
+    for (int q = 0; q < n; q++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, c, j * n + q));
+    c = __fadd_rn(__fdiv_rn(c, sum), hc_eps);
+    for (int it = 0; it < iters; it++) {
+        if (it) {
+            float s2 = 0.f;
+            for (int q = 0; q < n; q++) s2 = __fadd_rn(s2, __shfl_sync(0xffffffffu, c, j * n + q));
+            c = __fdiv_rn(c, __fadd_rn(s2, hc_eps));
+        }
+        float s3 = 0.f;
+        for (int q = 0; q < n; q++) s3 = __fadd_rn(s3, __shfl_sync(0xffffffffu, c, q * n + k));
+        c = __fdiv_rn(c, __fadd_rn(s3, hc_eps));
+    }
+    if (on && comb_out) comb_out[(size_t)row * n * n + l] = c;
+}
+
 // Y[j,i] = bf16(post[j]*f[i] + sum_k comb[k,j]*R[k,i]) (reference c/mhc.h:259-270,
 // c/layer.h:445-456).
 __global__ void mhc_post_kernel(const float *__restrict__ f, const float *__restrict__ res,
@@ -390,6 +490,25 @@ static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float 
 static inline int finish_seq() { return sum_tree(APUS_CUDA_TREE_NORMS) ? 0 : 1; }
 static inline size_t finish_smem(int d) { return finish_seq() ? (size_t)d * sizeof(float) : 0; }
 
+// pre/post/comb + collapse (+ RMSNorm) of `rows` tokens from the raw dots: the cluster kernel in
+// tree order (when the shapes fit its layout), else one CTA per token.
+static int launch_finish(const float *x4, const float *raw, int d, int n, int nmix, const float *scale,
+                         float head_scale, const float *base, float norm_eps, float hc_eps, int iters, int head_mode,
+                         const float *norm_w, float rms_eps, float *pre, float *post, float *comb, float *y,
+                         float *y_normed, int rows, cudaStream_t st) {
+    if (!finish_seq() && d % 4 == 0 && n * n <= 32 && y) {
+        mhc_pre_finish_cl_kernel<<<rows * MHC_CL, 128, 0, st>>>(x4, raw, d, n, nmix, scale, head_scale, base, norm_eps,
+                                                              hc_eps, iters, head_mode, norm_w, rms_eps, pre, post, comb,
+                                                              y, y_normed);
+    } else {
+        mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, head_scale, base, norm_eps,
+                                                                 hc_eps, iters, head_mode, norm_w, rms_eps, pre, post,
+                                                                 comb, y, y_normed, finish_seq());
+    }
+    APUS_LAUNCHED();
+    return 0;
+}
+
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
             const float *base, float norm_eps, float hc_eps, int iters,
             const float *norm_w, float rms_eps, float *pre, float *post,
@@ -400,11 +519,8 @@ int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
     float *raw = ensure_raw((size_t)rows * (nmix + 1), raw_in);
     if (!raw) return 1;
     if (launch_mix(x4, fn, n * d, nmix, raw, rows, st)) return 1;
-    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, 0.f, base,
-                                                norm_eps, hc_eps, iters, 0, norm_w, rms_eps,
-                                                pre, post, comb, y, norm_w ? y_normed : nullptr, finish_seq());
-    APUS_LAUNCHED();
-    return 0;
+    return launch_finish(x4, raw, d, n, nmix, scale, 0.f, base, norm_eps, hc_eps, iters, 0, norm_w, rms_eps, pre, post,
+                         comb, y, norm_w ? y_normed : nullptr, rows, st);
 }
 
 int mhc_head(const float *x4, int d, int n, const float *fn, float scale,
@@ -415,11 +531,8 @@ int mhc_head(const float *x4, int d, int n, const float *fn, float scale,
     float *raw = ensure_raw((size_t)rows * (n + 1), raw_in);
     if (!raw) return 1;
     if (launch_mix(x4, fn, n * d, n, raw, rows, st)) return 1;
-    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, n, nullptr, scale, base,
-                                                norm_eps, hc_eps, 0, 1, nullptr, 0.f,
-                                                nullptr, nullptr, nullptr, y, nullptr, finish_seq());
-    APUS_LAUNCHED();
-    return 0;
+    return launch_finish(x4, raw, d, n, n, nullptr, scale, base, norm_eps, hc_eps, 0, 1, nullptr, 0.f, nullptr, nullptr,
+                         nullptr, y, nullptr, rows, st);
 }
 
 int mhc_post(const float *f, const float *res4, const float *post,
@@ -478,11 +591,8 @@ int mhc_pre_noalloc(const float *x4, int d, int n, const float *fn, const float 
     // every raw[row, 0..nmix] slot read by the finish kernel is written by the mix
     // kernel of the same call, so nothing left over from an earlier call is used
     if (launch_mix(x4, fn, n * d, nmix, raw, rows, st)) return 1;
-    mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, 0.f, base, norm_eps,
-                                                hc_eps, iters, 0, norm_w, rms_eps, nullptr, post,
-                                                comb, y, norm_w ? y_normed : nullptr, finish_seq());
-    APUS_LAUNCHED();
-    return 0;
+    return launch_finish(x4, raw, d, n, nmix, scale, 0.f, base, norm_eps, hc_eps, iters, 0, norm_w, rms_eps, nullptr,
+                         post, comb, y, norm_w ? y_normed : nullptr, rows, st);
 }
 
 }  // namespace apus

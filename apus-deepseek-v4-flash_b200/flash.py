@@ -123,7 +123,7 @@ class RandomFlashModel:
     checker runs the reference on the identical model, whole or layer by layer.
     Ranks of an expert-parallel job build the same model by construction."""
 
-    def __init__(self, cfg, seed, device, e_lo=0, e_hi=None, max_pos=1024, rope=None):
+    def __init__(self, cfg, seed, device, e_lo=0, e_hi=None, max_pos=1024, rope=None, layer_ids=None):
         import apus_b200
         self.lib = apus_b200.lib()
         self.check = apus_b200.check
@@ -131,6 +131,7 @@ class RandomFlashModel:
         self.host = device == "host"
         self.e_lo, self.e_hi = e_lo, cfg.n_experts if e_hi is None else e_hi
         self.keep = []
+        self.named = {}                  # (layer, tensor name) -> the array / tensor that holds it
         self.bytes = 0
         self.seed = seed
         if not self.host:
@@ -140,10 +141,13 @@ class RandomFlashModel:
         # rope tables are inputs (host cos/sin); `rope` = {False: (cos, sin), True: (cos, sin)} overrides
         # the ones computed here, e.g. with the very tables a committed reference run used
         self.rope = rope or {c: rope_tables(cfg, c, max_pos) for c in (False, True)}
-        descs = [self._layer(i, r) for i, r in enumerate(cfg.layer_kinds())]
-        self._descs = (capi.LayerDesc * cfg.n_layers)(*descs)
+        # layer_ids: instantiate only these layers of the model (their true indices select
+        # the kind, the routing mode and the generator keys), e.g. to check one layer on a CPU
+        self.layer_ids = list(range(cfg.n_layers)) if layer_ids is None else list(layer_ids)
+        descs = [self._layer(i, cfg.ratios[i]) for i in self.layer_ids]
+        self._descs = (capi.LayerDesc * len(descs))(*descs)
         d = capi.ModelDesc()
-        d.n_layers, d.dim, d.hc_mult, d.hc_sinkhorn_iters, d.vocab = (cfg.n_layers, cfg.dim, cfg.hc_mult,
+        d.n_layers, d.dim, d.hc_mult, d.hc_sinkhorn_iters, d.vocab = (len(descs), cfg.dim, cfg.hc_mult,
                                                                       cfg.hc_iters, cfg.vocab)
         d.hc_eps, d.norm_eps = cfg.hc_eps, cfg.norm_eps
         d.layers = C.cast(self._descs, C.POINTER(capi.LayerDesc))
@@ -185,6 +189,7 @@ class RandomFlashModel:
     def _fill(self, layer, name, kind, shape, a=0.0, b=0.0, expert=0):
         t, p = self._alloc(shape, self._NP[kind])
         self._fill_at(p, layer, name, kind, int(np.prod(shape)), a, b, expert)
+        self.named[(layer, name)] = t
         return p
 
     def _const(self, values):

@@ -189,7 +189,8 @@ int apus_cuda_kernel_status(int reset);
  *     can flip a BF16 step downstream (the reference's own NEON and BLAS variants
  *     differ from its scalar code by as much, c/mhc.h:296-330, c/blas.h:25-40).
  * The choice is per operator class (apus_cuda_set_tree_ops, a bit mask of the
- * classes summed in tree order; mask < 0 only queries; returns the mask in force).
+ * classes summed in tree order; mask == -1 only queries and returns the mask in
+ * force; mask == -2 returns APUS_CUDA_TREE_DEFAULT and changes nothing).
  * apus_cuda_set_sum_order(REFERENCE / TREE) clears / sets every class; order < 0
  * only queries; it returns TREE only when every class is in tree order.
  * Environment at load time: APUS_TREE_OPS=<mask>, or APUS_SUM_ORDER=1 for all. */
@@ -203,9 +204,15 @@ int apus_cuda_kernel_status(int reset);
 #define APUS_CUDA_TREE_COMPRESSOR 32   /* compressor wkv / wgate projections (c/attn.h:892-1011) */
 #define APUS_CUDA_TREE_IDX_WPROJ 64    /* indexer weights projection (c/attn.h:1105-1168) */
 #define APUS_CUDA_TREE_LINEAR   128    /* apus_cuda_f32_linear / the f32_linear hook */
-#define APUS_CUDA_TREE_ALL      255
-/* The classes in tree order when nothing else is asked for. */
-#define APUS_CUDA_TREE_DEFAULT    0
+#define APUS_CUDA_TREE_FP8_SPLITK 256  /* FP8 matrices with few output tiles: K split over CTAs, chunk sums
+                                          added in chunk order (c/fp8.h:166-218 folds all blocks in one chain) */
+#define APUS_CUDA_TREE_ALL      511
+/* The classes in tree order when nothing else is asked for: the mHC maps, the norms,
+ * the head and the grouped o-projection.  Their results stay within ~1e-6..1e-5
+ * relative of the reference order (the same class as the tensor-core block sums
+ * of the MXFP4 / FP8 products); the router gate keeps the reference order so that
+ * the expert choice is the reference's except at exact score ties. */
+#define APUS_CUDA_TREE_DEFAULT  (15 + 256)
 int apus_cuda_set_tree_ops(int mask);
 int apus_cuda_set_sum_order(int order);
 /* Run the entry points that take no stream argument (host-pointer tier, model
@@ -501,6 +508,14 @@ int apus_cuda_block_forward(const ApusCudaLayerDesc *L, int hc_mult,
                             int hc_sinkhorn_iters, float hc_eps,
                             float norm_eps, ApusAttnS *st, float *h,
                             const int64_t *ids, int s, int64_t start_pos);
+/* The same for hash-routed layers too (c/moe.h:391-394 looks the experts up in
+ * tid2eid [vocab, topk] by token id; the reference's ApusLayer carries the
+ * vocabulary size in its cfg, c/layer.h:32-43): `vocab` rows of L->mw.tid2eid. */
+int apus_cuda_block_forward_v(const ApusCudaLayerDesc *L, int hc_mult,
+                              int hc_sinkhorn_iters, float hc_eps,
+                              float norm_eps, ApusAttnS *st, float *h,
+                              const int64_t *ids, int s, int64_t start_pos,
+                              int64_t vocab);
 /* c/model.h:396 + 485 apus_model_load / apus_model_state_init replaced by HBM
  * residency: uploads every weight, allocates the state of `batch` sequences
  * (1..32, advancing in lockstep) for positions < max_pos. */

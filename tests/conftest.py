@@ -8,6 +8,10 @@ ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 16)))
+# The parity tests written against the reference's bits run the long f32 sums in the
+# reference's loop order; the tests of the default (tree / tensor-core) order select it
+# themselves with apus_cuda_set_tree_ops (tests/test_gpu_flash_parity.py and others).
+os.environ.setdefault("APUS_TREE_OPS", "0")
 
 
 def pytest_configure(config):

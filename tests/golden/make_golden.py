@@ -232,7 +232,16 @@ def main_flash():
     L = ref()
     assert L is not None, "reference build not available"
     G = flash_case.run_reference(L, progress=True)
+    # the reference against itself with one input value moved by one BF16 ulp, teacher-forced
+    Gp = flash_case.run_reference(L, progress=True, perturb=True, feed=G["tokens"])
+    G["sens"] = np.array([[flash_case.rel(Gp["sub"][b, g], G["sub"][b, g]) for g in range(G["sub"].shape[1])]
+                          for b in range(G["sub"].shape[0])])
+    G["sens_flips"] = (Gp["tokens"] != G["tokens"])
     G.update(flash_case.rope_arrays())
+    G.update(flash_case.run_reference_layers(L, progress=True))
+    # the same loop on the model cut after its first layer: depth 1 is where the stated
+    # logits / token bars can be held (see tests/test_gpu_flash_parity.py)
+    G.update({f"one.{k}": v for k, v in flash_case.run_reference(L, batch=2, n_layers=1, progress=True).items()})
     np.savez_compressed(HERE / "flash_case.npz", **G)
     print("wrote flash_case.npz:", {k: v.shape for k, v in G.items()})
 

@@ -229,6 +229,38 @@ def test_f32_linear_bitwise_reference_order(M, flags):
     assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("M,K,O", [(1, 4096, 1280), (5, 512, 256), (32, 4096, 1024), (70, 1024, 384), (3, 448, 128)])
+@pytest.mark.parametrize("flags", [4, 5, 7])
+def test_bf16_linear_on_the_tensor_core(M, K, O, flags):
+    """BF16 weights in tree order run on the tcgen05 BF16 kernel (one or several K
+    chunks, one to three row groups): products are exact, only the order of the f32
+    adds differs from the reference's chain -- rel-L2 <= 1e-5 unrounded, within one
+    BF16 step on <= 0.2 % of the outputs when rounded; run to run identical bits."""
+    rng = np.random.default_rng(M * 7 + K + O + flags)
+    x = synth.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = synth.bf16_bits((rng.standard_normal((O, K)) * 0.02).astype(np.float32))
+    out, again, want = (np.empty((M, O), np.float32) for _ in range(3))
+    L = lib()
+    old = L.apus_cuda_set_tree_ops(-1)
+    try:
+        L.apus_cuda_set_tree_ops(511)
+        assert L.apus_cuda_f32_linear(P(w), P(x), P(out), M, K, O, flags) == 0, L.apus_cuda_last_error()
+        assert L.apus_cuda_f32_linear(P(w), P(x), P(again), M, K, O, flags) == 0
+    finally:
+        L.apus_cuda_set_tree_ops(old)
+    L.apus_cuda_forget(P(w))
+    ora().ora_f32_linear(P(w), P(x), P(want), M, K, O, flags)
+    assert L.apus_cuda_kernel_status(1) == 0
+    assert np.array_equal(out.view(np.uint32), again.view(np.uint32))
+    if flags & 2:
+        u = bf16_ulps(out, want)
+        big = np.abs(want) > 1e-3 * np.abs(want).max()       # an output next to zero has no meaningful step count
+        assert u[big].max() <= 1 and (u > 0).mean() <= 2e-3, (u[big].max(), (u > 0).mean())
+        assert rel_l2(out, want) <= 1e-3
+    else:
+        assert rel_l2(out, want) <= 1e-5, rel_l2(out, want)
+
+
 def test_head_gemv_bf16_and_hook_table():
     rng = np.random.default_rng(9)
     O, K = 12928, 4096                         # a tenth of the 129280-row LM head

@@ -335,6 +335,25 @@ def test_sampler_vs_reference(tag):
     assert tok.tolist() == G[f"{tag}.tokens"].tolist()
 
 
+@pytest.mark.parametrize("n", [129280, 129283, 16384, 20000])
+def test_greedy_pick_on_long_rows_is_the_first_maximum(n):
+    """Greedy pick over a vocabulary-sized row (the clustered argmax): the lowest index of
+    the maximum, as the reference's scan returns it (c/sample.h:76-81), on rows full of
+    ties, with the maximum first, last, and repeated across the cluster's slices."""
+    L = lib()
+    rng = np.random.default_rng(n)
+    rows = 5
+    lg = (np.round(rng.standard_normal((rows, n)) * 4) / 4).astype(np.float32)      # many exact ties
+    lg[1, n - 1] = 50.0
+    lg[2, 0] = 50.0; lg[2, n // 2] = 50.0; lg[2, n - 1] = 50.0
+    lg[3, :] = -1.5
+    lg[4, n - 3] = 60.0; lg[4, n - 2] = 60.0
+    tok = np.empty(rows, np.int32)
+    u = np.zeros(rows)
+    assert L.apus_cuda_sample_logits_u(P(lg), n, 0.0, 1.0, P(u), P(tok), rows) == 0, L.apus_cuda_last_error()
+    assert tok.tolist() == [int(np.argmax(lg[r])) for r in range(rows)]
+
+
 def test_sampled_generation_vs_reference():
     """The token loop with temperature / top-p sampling and the per-sequence
     splitmix64 streams on the device against the reference loop."""
