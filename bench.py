@@ -1,23 +1,26 @@
 #!/usr/bin/env python3
-"""Benchmark of the hot path: decode through one full MoE sublayer at
-DeepSeek-V4-Flash dimensions (hidden 4096, 256 MXFP4 routed experts of
-intermediate 2048, top-6, FP8 shared expert), `--tokens` decode tokens per GPU
-per step, synthetic seeded weights and activations.
+"""Benchmark of the hot path: the full DeepSeek-V4-Flash token loop (43 layers,
+256 MXFP4 routed experts + FP8 shared expert per layer, vocabulary 129,280) with
+random-init weights generated in HBM by the library's counter-based generator,
+a 512-token prompt per sequence, then greedy decode at batch 32 (and batch 1).
 
     python bench.py --gpus N --steps K --warmup W            # this repository
     python bench.py --impl reference --gpus N --steps K ...  # reference C code on the host cores
 
-One JSON line on stdout (rank 0).  `value` is whole-job decode tokens/s with
-inputs resident in HBM; `e2e` is the same metric through the host-pointer C ABI
-(apus_cuda_moe_forward: pinned host activations in, host result out, copies
-inside the timed region); `roofline` describes the dominant kernel (MXFP4
-gate/up expert GEMV with fused SwiGLU) from CUDA events recorded around its
-launches inside the timed region; `cpu_baseline` is the unmodified reference
-`apus_moe_forward` timed on the host cores in the same run.
+One JSON line on stdout (rank 0).  `value` is whole-job decode tokens/s with the
+sampled token fed back on the device; `e2e` is the same metric with HOST token ids
+in and HOST sampled ids out every step (copies inside the timed region);
+`roofline` describes the dominant kernel (MXFP4 gate/up expert GEMV with fused
+SwiGLU) from CUDA events recorded around its launches; `cpu_baseline` is the
+unmodified reference timed on the host cores in the same run; `tokens_fnv1a` is a
+digest of the tokens rank 0's sequences produced -- the same prompts at every N,
+so equal digests across N mean the expert-parallel loop decodes what one GPU does.
 
-N > 1: experts are sharded expert-parallel (contiguous blocks), each rank brings
-its own `--tokens` tokens (weak scaling), dispatch and combine are NCCL
-all-to-alls.
+N > 1: the routed experts are sharded over the ranks (contiguous blocks), every
+rank decodes its own `--batch` sequences (weak scaling; `strong_bs32` / `strong_bs1`
+add the fixed-total-batch figures), dispatch and combine are NCCL all-to-alls.
+
+Other workloads: --workload moe_layer (one MoE sublayer), fp8_gemm (config 1).
 """
 import argparse
 import ctypes as C
@@ -179,7 +182,7 @@ def reference_arm(a):
 MODEL_METRIC = "decode_tokens_per_s"
 
 
-def model_config(a, n, cfg):
+def model_config(a, n, cfg, L=None):
     kinds = cfg.layer_kinds()
     return {"workload": f"config4: full DeepSeek-V4-Flash token loop, random-init weights generated on the device, "
                         f"{a.prompt}-token prompt then greedy decode at batch {a.batch}",
@@ -187,8 +190,21 @@ def model_config(a, n, cfg):
             "hidden": cfg.dim, "n_routed_experts": cfg.n_experts, "topk": cfg.topk, "vocab": cfg.vocab,
             "batch": a.batch, "prompt_tokens": a.prompt, "parallelism": f"ep{n}" if n > 1 else "single",
             "microbatches": 1 if n > 1 else max(1, a.microbatches),
-            "sum_order": "tree" if os.environ.get("APUS_SUM_ORDER", "0") == "1" else "reference",
+            "sum_order": sum_order_name(L),
             "l2": "each step streams the touched experts and all dense weights (>20 GB at batch 32), far above the 126 MB L2"}
+
+
+def token_digest(L, toks):
+    """64-bit FNV-1a over the int32 tokens [sequences, steps], as a hex string."""
+    t = np.ascontiguousarray(toks.astype(np.int32))
+    return f"{L.apus_fnv1a(t.ctypes.data, t.nbytes, 0xcbf29ce484222325):016x}"
+
+
+def sum_order_name(L=None):
+    if L is None:
+        return "default"
+    m = L.apus_cuda_set_tree_ops(-1)
+    return "reference" if m == 0 else f"tree mask {m}" + (" (default)" if m == L.apus_cuda_set_tree_ops(-2) else "")
 
 
 def flash_config(a):
@@ -201,10 +217,12 @@ def flash_config(a):
     return cfg
 
 
-def cpu_model_baseline(cfg, seed, budget_s):
+def cpu_model_baseline(cfg, seed, budget_s, prompt=512):
     """The reference's decode step composed from its own apus_block_forward timed
-    on one layer of each kind at full size (E experts, one token at position 8
-    after an 8-token prefill) plus the head: t = sum_kinds n_kind * t_kind + t_head."""
+    on one layer of each kind at full size (E experts, one token per call at the
+    positions the GPU arm decodes at: after a `prompt`-token prefill of that layer)
+    plus the head: t = sum_kinds n_kind * t_kind + t_head.  A projection: the whole
+    model (158 GB) does not fit the time budget of a benchmark run on the host."""
     import cases
     from _oracle import P, ref
     from apus_b200 import capi, synth
@@ -215,17 +233,17 @@ def cpu_model_baseline(cfg, seed, budget_s):
     rng = np.random.default_rng(seed)
     dims = dict(dim=cfg.dim, n_heads=cfg.n_heads, head_dim=cfg.head_dim, rope_dim=cfg.rope_dim, q_lora=cfg.q_lora,
                 o_groups=cfg.o_groups, o_lora=cfg.o_lora, window=cfg.window, idx_heads=cfg.idx_heads,
-                idx_dim=cfg.idx_dim, idx_topk=cfg.idx_topk, max_pos=256)
+                idx_dim=cfg.idx_dim, idx_topk=cfg.idx_topk, max_pos=prompt + 64)
     mdims = dict(E=cfg.n_experts, topk=cfg.topk, inter=cfg.inter)
     L.ref_block_forward.restype = None
     L.ref_block_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_int, C.c_int64]
     kinds = cfg.layer_kinds()
-    t_kind, moe = {}, None
+    t_kind, moe, calls = {}, None, 0
     for ratio, kind in ((0, "swa"), (4, "csa"), (128, "hca128")):
         if ratio not in kinds:
             continue
-        cos, sin = rope_tables(cfg, ratio != 0, 256)
+        cos, sin = rope_tables(cfg, ratio != 0, prompt + 64)
         B = cases.BlockLayer(seed + ratio, kind, cos, sin, dims=mdims, attn_dims=dims)
         if moe is None:
             moe = B.moe                                  # 3.4 GB of experts: generated once, shared by the kinds
@@ -233,17 +251,18 @@ def cpu_model_baseline(cfg, seed, budget_s):
             B.moe = moe
             B.desc.mw = moe.moew()
         S = cases.AttnState(B.attn)
-        h = cases.block_inputs(seed + 3, 9, cfg.hc_mult, cfg.dim)
-        ids = np.zeros(9, np.int64)
+        h = cases.block_inputs(seed + 3, prompt + 1, cfg.hc_mult, cfg.dim)
+        ids = np.zeros(prompt + 1, np.int64)
         L.ref_block_forward(C.byref(B.desc), cfg.hc_mult, cfg.hc_iters, cfg.hc_eps, cfg.norm_eps, C.byref(S.st),
-                            P(h[:8]), P(ids[:8]), 8, 0)
+                            P(h[:prompt]), P(ids[:prompt]), prompt, 0)           # untimed: fills the window and the caches
         n, t0 = 0, time.perf_counter()
         while n < 3 or (time.perf_counter() - t0 < budget_s / 3 and n < 40):
-            hh = h[8:9].copy()
+            hh = h[prompt:prompt + 1].copy()
             L.ref_block_forward(C.byref(B.desc), cfg.hc_mult, cfg.hc_iters, cfg.hc_eps, cfg.norm_eps, C.byref(S.st),
-                                P(hh), P(ids[8:9]), 1, 8 + n)
+                                P(hh), P(ids[prompt:prompt + 1]), 1, prompt + n)
             n += 1
         t_kind[ratio] = (time.perf_counter() - t0) / n
+        calls += n
     # head: BF16 [vocab, dim] GEMV
     head = synth.bf16_bits((rng.standard_normal((cfg.vocab, cfg.dim)) * 0.02).astype(np.float32))
     x = synth.activations(rng, 1, cfg.dim)
@@ -259,8 +278,9 @@ def cpu_model_baseline(cfg, seed, budget_s):
     t_head = (time.perf_counter() - t0) / n
     t_step = sum(t_kind[r] for r in kinds) + t_head
     return {"value": 1.0 / t_step, "unit": "tok/s", "cores": L.ref_pool_threads(), "kind": "reference",
-            "sample": "one decode token (position 8+) through the unmodified apus_block_forward at full sizes, "
-                      "one layer of each kind with 256 experts ("
+            "projected": True, "timed_calls": calls + 3,
+            "sample": f"one decode token per call (positions {prompt}+, after a {prompt}-token prefill of the layer) through "
+                      "the unmodified apus_block_forward at full sizes, one layer of each kind with 256 experts ("
                       + ", ".join(f"{k}: {v * 1e3:.0f} ms" for k, v in t_kind.items())
                       + f"), head GEMV {t_head * 1e3:.0f} ms; step = sum over the {cfg.n_layers} layers + head; "
                         "the reference decodes sequences one at a time, so its tok/s does not grow with the batch"}
@@ -272,14 +292,16 @@ def model_reference_arm(a):
         return
     os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 32)))
     cfg = flash_config(a)
-    cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0)
+    cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0, prompt=a.prompt)
     if cb is None:
         emit({"impl": "reference", "unavailable": "the reference build (oracle/_ref) is not present"})
         return
+    import apus_b200
+    # `steps` = the block calls actually timed (the step time is composed from them, see cpu_baseline.sample)
     line = {"impl": "reference", "metric": MODEL_METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": a.gpus,
-            "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": model_config(a, a.gpus, cfg), "cpu_baseline": cb,
+            "steps": cb["timed_calls"], "warmup": 1, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "projected": True,
+            "config": model_config(a, a.gpus, cfg, apus_b200.lib()), "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     emit(line)
@@ -316,8 +338,15 @@ def model_main_ep(a):
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
     ep = EpModel(W.desc, cfg.n_layers, cfg.n_experts, cfg.topk, cfg.dim, B, max_pos, rank, world, device=dev)
-    rng = np.random.default_rng([a.seed, 4242, rank])
-    prompt = rng.integers(0, cfg.vocab, size=(B, a.prompt)).astype(np.int64)
+    from apus_b200.flash import prompt_ids
+    # sequence g of the job (rank r holds g = r*B ..) has the prompt of sequence g of a one-GPU run
+    prompt = prompt_ids(a.seed, rank * B, B, a.prompt, cfg.vocab)
+    hist = torch.zeros(Wm + K + 3, B, dtype=torch.int64, device=dev)      # the token every step picked
+    n_hist = [0]
+
+    def keep_tokens():
+        hist[n_hist[0]].copy_(ep.ids)                  # the pick was fed back into the ids on the device
+        n_hist[0] += 1
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid) if rank == 0 else None
 
@@ -335,13 +364,16 @@ def model_main_ep(a):
     e1.record()
     torch.cuda.synchronize()
     prefill_ms = e0.elapsed_time(e1)
+    keep_tokens()
     mark("warm-up steps")
     for _ in range(Wm):
         ep.step()
+        keep_tokens()
     torch.cuda.synchronize()
     mark("warm-up done")
     d0 = L.apus_cuda_dispatches()
     ep.step()
+    keep_tokens()
     per_step = int(L.apus_cuda_dispatches() - d0)       # kernels of one step, counted on plain launches
     graph_note = "each step replayed from one CUDA graph (library kernels + NCCL all-to-alls)"
     if os.environ.get("APUS_EP_GRAPH", "1") != "0":
@@ -354,15 +386,18 @@ def model_main_ep(a):
         graph_note = "plain launches"
     mark(graph_note)
     ep.step()
+    keep_tokens()
     barrier()
     mark("timed region")
     w0 = time.time()
     e0.record()
     for _ in range(K):
         ep.step()
+        keep_tokens()
     e1.record()
     barrier()
     w1 = time.time()
+    digest = token_digest(L, hist[:Wm + K + 2].t().cpu().numpy()) if rank == 0 else None
     launches = per_step * K
     tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(tms, op=dist.ReduceOp.MAX)
@@ -376,32 +411,70 @@ def model_main_ep(a):
     t0 = time.perf_counter()
     for _ in range(ne):
         ep.set_ids(nxt.astype(np.int64))
-        ep.step(feed_back=False)
+        ep.step()                            # the recorded step; its own feed-back is overwritten by the next set_ids
         ep.read(tokens=nxt)
     barrier()
     te = torch.tensor([time.perf_counter() - t0], device=dev)
     dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_val = world * B * ne / float(te.item())
+    ep.graph = None
     ep.close()
+
+    # ---- fixed total batch (strong scaling): `gb` sequences over all ranks; at gb = 1 every rank steps
+    # the same single sequence (the dense path is replicated and deterministic), its routed experts
+    # still live on their owners, so dispatch and combine cross the links as they would
+    def strong(gb):
+        per_rank = max(1, gb // world)
+        first = rank * per_rank if gb >= world else 0
+        m2 = EpModel(W.desc, cfg.n_layers, cfg.n_experts, cfg.topk, cfg.dim, per_rank, max_pos, rank, world, device=dev)
+        try:
+            m2.prefill(prompt_ids(a.seed, first, per_rank, min(a.prompt, 16), cfg.vocab))
+            for _ in range(2):
+                m2.step()
+            if os.environ.get("APUS_EP_GRAPH", "1") != "0":
+                try:
+                    m2.capture()
+                except Exception:
+                    torch.cuda.synchronize()
+            m2.step()
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ks = max(8, K // 2)
+            s0.record()
+            for _ in range(ks):
+                m2.step()
+            s1.record()
+            barrier()
+            t = torch.tensor([s0.elapsed_time(s1)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            seqs = gb if gb >= world else 1
+            return {"global_batch": seqs, "per_rank": per_rank, "steps": ks, "ms_per_step": float(t.item()) / ks,
+                    "value": seqs * ks / (float(t.item()) * 1e-3), "unit": "tok/s", "prompt_tokens": min(a.prompt, 16)}
+        finally:
+            m2.graph = None
+            m2.close()
+    strong32 = strong(32) if world <= 32 else None
+    strong1 = strong(1)
     if rank == 0:
         line = {
             "metric": MODEL_METRIC, "value": world * B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": K, "warmup": Wm, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None,
             "dtype": "f32 accumulate over E2M1xE4M3 / E4M3xE4M3 tensor-core products; BF16-valued activations",
-            "data": "synthetic", "config": model_config(a, world, cfg), "clocks": clocks,
+            "data": "synthetic", "config": model_config(a, world, cfg, L), "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": world * B * 8,
                     "d2h_bytes_per_step": world * B * 4, "steps": ne},
             "gpu_launches": launches,
+            "tokens_fnv1a": digest, "digest_tokens_per_seq": Wm + K + 2,
+            "strong_bs32": strong32, "strong_bs1": strong1,
             "prefill": {"tokens": world * B * a.prompt, "ms": prefill_ms,
                         "note": "prompt consumed as consecutive decode steps"},
             "roofline": None, "weights": {"bytes_per_rank": W.bytes}, "cuda_graph": graph_note,
             "note": "expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine per layer; "
                     "the per-kernel roofline is reported by the 1-GPU run"}
         emit(line)
-    # a captured graph holds NCCL work; release it and leave without tearing the
-    # communicator down (destroying the group with such graphs alive can block)
-    ep.graph = None
+    # captured graphs held NCCL work; leave without tearing the communicator down
+    # (destroying the group with such graphs alive can block)
     barrier()
     sys.stdout.flush()
     sys.stderr.flush()
@@ -437,7 +510,7 @@ def model_main(a):
         if not h:
             apus_b200.check(1, "apus_cuda_model_create")
         return h
-    rng = np.random.default_rng([a.seed, 4242])
+    from apus_b200.flash import prompt_ids
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
 
@@ -458,8 +531,7 @@ def model_main(a):
             for h in hs:
                 apus_b200.check(L.apus_cuda_model_set_stream(h, None, 1), "model_set_stream")
         harr = (C.c_void_p * groups)(*hs)
-        prompts = [np.ascontiguousarray(rng.integers(0, cfg.vocab, size=(per, a.prompt)).astype(np.int64))
-                   for _ in range(groups)]
+        prompts = [np.ascontiguousarray(prompt_ids(a.seed, g * per, per, a.prompt, cfg.vocab)) for g in range(groups)]
         toks = [np.empty((per, Wm + 1), np.int32) for _ in range(groups)]
         ms_pre, ms_dec = C.c_float(0), C.c_float(0)
         apus_b200.check(L.apus_cuda_model_generate_group(harr, groups, parr(prompts), a.prompt, Wm + 1, parr(toks),
@@ -498,6 +570,7 @@ def model_main(a):
             g13 += x.value; g2 += y.value; nl += n.value
             items += L.apus_cuda_moe_work_items(m, 0)
         stats = (g13, g2, nl, items, kt, ms_plain)
+        stream_toks = [np.concatenate([toks[g], out[g]], axis=1) for g in range(groups)]   # t0 .. t(Wm+K+1) per sequence
         # the other models catch up with the first one's event pass (same position for the e2e loop)
         for g in range(1, groups):
             lg = np.ascontiguousarray(out[g][:, -1:].astype(np.int64))
@@ -506,12 +579,13 @@ def model_main(a):
                             "generate (catch up)")
             out[g] = o2
         out[0] = out2
-        return hs, ms, prefill_ms, per_step * K * groups, out, (w0, w1), stats
+        return hs, ms, prefill_ms, per_step * K * groups, out, (w0, w1), stats, np.concatenate(stream_toks, axis=0)
 
     G = max(1, a.microbatches)
     if B % G:
         raise SystemExit(f"--batch {B} is not a multiple of --microbatches {G}")
-    hs, ms, prefill_ms, launches, out, wall, stats = run(B, G)
+    hs, ms, prefill_ms, launches, out, wall, stats, stream = run(B, G)
+    digest = token_digest(L, stream[:, :Wm + K + 2])
     clocks = sampler.stop(*wall)
     value = B * K / (ms * 1e-3)
 
@@ -536,7 +610,7 @@ def model_main(a):
         L.apus_cuda_model_destroy(h)
 
     # ---- batch 1 ------------------------------------------------------------------------------
-    h1, ms1, prefill1, launches1, out1, _, st1 = run(1, 1)
+    h1, ms1, prefill1, launches1, out1, _, st1, _ = run(1, 1)
     L.apus_cuda_model_destroy(h1[0])
 
     peak, peak_kind = peak_hbm()
@@ -548,12 +622,20 @@ def model_main(a):
         "metric": MODEL_METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 accumulate over E2M1xE4M3 / E4M3xE4M3 tensor-core products; BF16-valued activations",
-        "data": "synthetic", "config": model_config(a, 1, cfg), "clocks": clocks,
+        "data": "synthetic", "config": model_config(a, 1, cfg, L), "clocks": clocks,
         "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 4,
                 "steps": ne},
         "gpu_launches": launches,
+        "tokens_fnv1a": digest, "digest_tokens_per_seq": Wm + K + 2,
         "batch1": {"value": 1 * K / (ms1 * 1e-3), "unit": "tok/s", "ms_per_step": ms1 / K,
-                   "gpu_launches": launches1, "prefill_ms": prefill1, "ms_per_step_plain_launches": st1[5]},
+                   "gpu_launches": launches1, "prefill_ms": prefill1, "ms_per_step_plain_launches": st1[5],
+                   # the expert gate/up GEMV at batch 1: 6 experts per launch, same accounting as `roofline`
+                   "roofline": {"kernel": "gemm_tc_kernel<pair> at batch 1", "bound": "hbm",
+                                "achieved": st1[3] * W13_BYTES / (st1[0] * 1e-3) / 1e9 if st1[0] > 0 else None,
+                                "peak": peak, "unit": "GB/s",
+                                "frac": st1[3] * W13_BYTES / (st1[0] * 1e-3) / 1e9 / peak if st1[0] > 0 else None,
+                                "avg_launch_us": st1[0] / max(st1[2], 1) * 1e3, "avg_unique_experts": st1[3] / max(st1[2], 1),
+                                "down_proj_frac": st1[3] * W2_BYTES / (st1[1] * 1e-3) / 1e9 / peak if st1[1] > 0 else None}},
         "prefill": {"tokens": B * a.prompt, "ms": prefill_ms, "tok_s": B * a.prompt / (prefill_ms * 1e-3),
                     "note": "prompt consumed as consecutive decode steps (no batched prefill kernel yet)"},
         "weights": {"bytes": W.bytes, "generate_s": t_gen},
@@ -576,7 +658,7 @@ def model_main(a):
     }
     if not a.no_cpu_baseline:
         os.environ.setdefault("APUS_THREADS", str(min(os.cpu_count() or 1, 32)))
-        cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0)
+        cb = cpu_model_baseline(cfg, a.seed, budget_s=20.0, prompt=a.prompt)
         if cb:
             line["cpu_baseline"] = cb
     emit(line)

@@ -207,12 +207,13 @@ int apus_cuda_kernel_status(int reset);
 #define APUS_CUDA_TREE_FP8_SPLITK 256  /* FP8 matrices with few output tiles: K split over CTAs, chunk sums
                                           added in chunk order (c/fp8.h:166-218 folds all blocks in one chain) */
 #define APUS_CUDA_TREE_ALL      511
-/* The classes in tree order when nothing else is asked for: the mHC maps, the norms,
- * the head and the grouped o-projection.  Their results stay within ~1e-6..1e-5
- * relative of the reference order (the same class as the tensor-core block sums
- * of the MXFP4 / FP8 products); the router gate keeps the reference order so that
- * the expert choice is the reference's except at exact score ties. */
-#define APUS_CUDA_TREE_DEFAULT  (15 + 256)
+/* The classes in tree order when nothing else is asked for: those the reference's own
+ * ARM build sums in another order than its scalar code (the mHC map dots and sum of
+ * squares, c/mhc.h:288-316; the o-projection, c/attn.h:1457-1466, "accepted SIMD
+ * tolerance class") and the head, whose unrounded logits only feed the pick.  The
+ * norms, the router gate, the compressor and indexer projections (c/attn.h:450-458:
+ * "leave no room for reorder noise") and the FP8 fold keep the reference's order. */
+#define APUS_CUDA_TREE_DEFAULT  (1 + 4 + 8)
 int apus_cuda_set_tree_ops(int mask);
 int apus_cuda_set_sum_order(int order);
 /* Run the entry points that take no stream argument (host-pointer tier, model
