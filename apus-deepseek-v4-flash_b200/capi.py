@@ -286,6 +286,7 @@ def load(path=LIB_PATH):
         "apus_cuda_expert_fp4_dev": (ci, [vp, vp, vp, cf, vp, ci, vp, vp]),
         "apus_cuda_topk_stable_dev": (ci, [vp, ci, ci, vp, ci, vp]),
         "apus_cuda_sparse_attn_dev": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, vp, i64, vp, vp]),
+        "apus_cuda_sparse_attn_batch_dev": (ci, [vp, vp, ci, ci, vp, ci, ci, cf, vp, i64, i64, vp, i64, i64, vp, vp]),
         "apus_synth_key": (C.c_uint64, [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]),
         "apus_synth_fill_host": (ci, [vp, ci, C.c_uint64, C.c_uint64, C.c_double, C.c_double, ci]),
         "apus_synth_fill_dev": (ci, [vp, ci, C.c_uint64, C.c_uint64, C.c_double, C.c_double, vp]),

@@ -920,4 +920,14 @@ int apus_cuda_sparse_attn_dev(const float *q, const float *sink, int h, int d, c
                        (cudaStream_t)stream);
 }
 
+int apus_cuda_sparse_attn_batch_dev(const float *q, const float *sink, int h, int d, const int32_t *idxs,
+                                    int idxw, int s, float scale, const uint16_t *kv_a, int64_t na,
+                                    int64_t kv_a_stride, const uint16_t *kv_b, int64_t nb, int64_t kv_b_stride,
+                                    float *o, void *stream) {
+    if (ensure_enabled()) return 1;
+    APUS_REQUIRE(kv_a_stride >= 0 && kv_b_stride >= 0, "sparse_attn_batch: negative stride");
+    return sparse_attn(q, sink, h, d, idxs, idxw, s, scale, kv_a, na, kv_b, nb, 1, o, (cudaStream_t)stream,
+                       (long long)kv_a_stride * d, (long long)kv_b_stride * d);
+}
+
 }  // extern "C"

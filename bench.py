@@ -54,9 +54,12 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--batches", type=int, default=8, help="distinct activation batches cycled")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default=None, choices=["model", "moe_layer", "fp8_gemm"],
+    ap.add_argument("--workload", default=None, choices=["model", "moe_layer", "fp8_gemm", "attn"],
                     help="model: full 43-layer token loop (default); moe_layer: one MoE sublayer (config 2); "
-                         "fp8_gemm: the FP8 dense GEMM of config 1 (W [4096,4096], M = 1, 32, 512, 4096)")
+                         "fp8_gemm: the FP8 dense GEMM of config 1 (W [4096,4096], M = 1, 32, 512, 4096); "
+                         "attn: sparse-attention decode over long synthetic KV caches (config 3)")
+    ap.add_argument("--ctx", default="8192,131072,1048576", help="attn workload: context lengths")
+    ap.add_argument("--attn-batches", default="1,32", help="attn workload: decode queries per step (per GPU)")
     ap.add_argument("--batch", type=int, default=32, help="model workload: sequences decoded in lockstep")
     ap.add_argument("--prompt", type=int, default=512, help="model workload: prompt tokens per sequence")
     ap.add_argument("--layers", type=int, default=43, help="model workload: layers (43 = the real model)")
@@ -713,6 +716,193 @@ def fp8_gemm_main(a):
     emit(line)
 
 
+# ---- config 3: sparse-attention decode step over a long synthetic KV cache -----------------------
+ATTN_H, ATTN_D, ATTN_WIN, ATTN_TOPK = 64, 512, 128, 512
+
+
+def attn_case_host(seed, kind, ctx, b, nb_cap=None):
+    """Inputs of one sequence of the config-3 case on the host (generator keys per sequence):
+    q [64,512] BF16-valued f32, sink [64], window ring [128,512] and compressed cache [nb,512]
+    as BF16 bits, indexer scores [nb] (CSA)."""
+    import apus_b200
+    L = apus_b200.lib()
+    ratio = 4 if kind == "csa" else 128
+    nb = ctx // ratio
+
+    def fill(tid, n, k, a_, b_, dt):
+        out = np.empty(n, dt)
+        apus_b200.check(L.apus_synth_fill_host(out.ctypes.data, k, n, L.apus_synth_key(seed, 3000 + ratio, tid, b), a_, b_, 0), "fill")
+        return out
+    return dict(q=fill(1, ATTN_H * ATTN_D, 3, 0.0, 1.0, np.float32).reshape(ATTN_H, ATTN_D),
+                sink=fill(2, ATTN_H, 2, 0.0, 0.5, np.float32),
+                ring=fill(3, ATTN_WIN * ATTN_D, 4, 0.0, 1.0, np.uint16).reshape(ATTN_WIN, ATTN_D),
+                cache=fill(4, nb * ATTN_D, 4, 0.0, 1.0, np.uint16).reshape(nb, ATTN_D),
+                scores=fill(5, nb, 2, 0.0, 1.0, np.float32) if kind == "csa" else None, nb=nb, ratio=ratio)
+
+
+class AttnDecodeCase:
+    """Device-resident config-3 case: B sequences, each with its own ring and compressed cache
+    (same generator keys as attn_case_host), and one decode step = top-512 selection over the
+    indexer scores (CSA; HCA attends every entry) + index row + gathered attention."""
+
+    def __init__(self, L, seed, kind, ctx, B, dev, first_seq=0):
+        import torch
+        import apus_b200
+        self.L, self.kind, self.B, self.dev = L, kind, B, dev
+        ratio = 4 if kind == "csa" else 128
+        nb = ctx // ratio
+        self.nb, self.ratio = nb, ratio
+        st = torch.cuda.current_stream().cuda_stream
+        f32, i16 = torch.float32, torch.int16
+        self.q = torch.empty(B, ATTN_H, ATTN_D, dtype=f32, device=dev)
+        self.sink = torch.empty(ATTN_H, dtype=f32, device=dev)
+        self.ring = torch.empty(B, ATTN_WIN, ATTN_D, dtype=i16, device=dev)
+        self.cache = torch.empty(B, nb, ATTN_D, dtype=i16, device=dev)
+        self.scores = torch.empty(B, nb, dtype=f32, device=dev) if kind == "csa" else None
+        key = lambda tid, b: L.apus_synth_key(seed, 3000 + ratio, tid, first_seq + b)
+        for b in range(B):
+            for t, tid, k, a_, b_ in ((self.q[b], 1, 3, 0.0, 1.0), (self.ring[b], 3, 4, 0.0, 1.0), (self.cache[b], 4, 4, 0.0, 1.0)):
+                apus_b200.check(L.apus_synth_fill_dev(t.data_ptr(), k, t.numel(), key(tid, b), a_, b_, st), "fill")
+            if self.scores is not None:
+                apus_b200.check(L.apus_synth_fill_dev(self.scores[b].data_ptr(), 2, nb, key(5, b), 0.0, 1.0, st), "fill")
+        apus_b200.check(L.apus_synth_fill_dev(self.sink.data_ptr(), 2, ATTN_H, L.apus_synth_key(seed, 3000 + ratio, 2, first_seq), 0.0, 0.5, st), "fill")
+        self.k = min(ATTN_TOPK, nb) if kind == "csa" else nb
+        self.idxw = ATTN_WIN + self.k
+        self.idx = torch.empty(B, self.idxw, dtype=torch.int32, device=dev)
+        self.idx[:, :ATTN_WIN] = torch.arange(ATTN_WIN, dtype=torch.int32, device=dev)      # a full window, ring order 0..127
+        if kind != "csa":
+            self.idx[:, ATTN_WIN:] = ATTN_WIN + torch.arange(nb, dtype=torch.int32, device=dev)
+        self.topk = torch.empty(B, self.k, dtype=torch.int32, device=dev) if kind == "csa" else None
+        self.o = torch.empty(B, ATTN_H, ATTN_D, dtype=f32, device=dev)
+        torch.cuda.synchronize()
+
+    def step(self):
+        import torch
+        import apus_b200
+        L, st = self.L, torch.cuda.current_stream().cuda_stream
+        if self.kind == "csa":
+            apus_b200.check(L.apus_cuda_topk_stable_dev(self.scores.data_ptr(), self.nb, self.k, self.topk.data_ptr(), self.B, st), "topk")
+            torch.add(self.topk, ATTN_WIN, out=self.idx[:, ATTN_WIN:])
+        apus_b200.check(L.apus_cuda_sparse_attn_batch_dev(self.q.data_ptr(), self.sink.data_ptr(), ATTN_H, ATTN_D, self.idx.data_ptr(),
+                                                          self.idxw, self.B, ATTN_D ** -0.5, self.ring.data_ptr(), ATTN_WIN, ATTN_WIN,
+                                                          self.cache.data_ptr(), self.nb, self.nb, self.o.data_ptr(), st), "sparse_attn")
+
+    def bytes_per_query(self):
+        """Algorithmic bytes of one query: the scan of its score row (CSA) + the gathered KV rows (BF16)."""
+        return (self.nb * 4 if self.kind == "csa" else 0) + self.idxw * ATTN_D * 2
+
+
+def attn_reference_query(Lr, c, kind):
+    """One query of the case through the reference: apus_topk_stable (c/attn.h:668) + window ids, then
+    apus_sparse_attn (c/attn.h:1308) on f32 copies of the BF16 caches."""
+    from _oracle import P
+    widen = lambda u: (u.astype(np.uint32) << 16).view(np.float32)
+    ring, cache = widen(c["ring"]), widen(c["cache"])
+    nb = c["nb"]
+    k = min(ATTN_TOPK, nb) if kind == "csa" else nb
+    idx = np.empty(ATTN_WIN + k, np.int32)
+    idx[:ATTN_WIN] = np.arange(ATTN_WIN)
+    if kind == "csa":
+        top = np.empty(k, np.int32)
+        Lr.apus_topk_stable(P(c["scores"]), nb, k, P(top))
+        idx[ATTN_WIN:] = top + ATTN_WIN
+    else:
+        idx[ATTN_WIN:] = ATTN_WIN + np.arange(nb)
+    o = np.empty((ATTN_H, ATTN_D), np.float32)
+    Lr.ref_sparse_attn(P(c["q"]), P(c["sink"]), ATTN_H, ATTN_D, P(idx), len(idx), 1, ATTN_D ** -0.5, P(ring), ATTN_WIN, P(cache), P(o))
+    return o, idx
+
+
+def attn_main(a):
+    import torch
+    import apus_b200
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import datetime
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+    apus_b200.build()
+    L = apus_b200.lib()
+    err = C.create_string_buffer(512)
+    if L.apus_cuda_enable(err, 512):
+        raise RuntimeError(err.value.decode())
+    peak, peak_kind = peak_hbm()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    res = {}
+    n_it = max(3, min(a.steps, 20))
+    for kind in ("csa", "hca"):
+        for ctx in [int(x) for x in a.ctx.split(",")]:
+            for B in [int(x) for x in a.attn_batches.split(",")]:
+                case = AttnDecodeCase(L, a.seed, kind, ctx, B, dev, first_seq=rank * B)
+                for _ in range(max(a.warmup, 3)):
+                    case.step()
+                torch.cuda.synchronize()
+                # the step's five launches replayed from a CUDA graph, so that the events time the GPU
+                # and not the host's launch calls (a decode loop issues them from a graph as well)
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(torch.cuda.current_stream())
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    case.step()
+                torch.cuda.current_stream().wait_stream(side)
+                graph.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                tot = 0.0
+                for _ in range(n_it):
+                    flush.zero_()                                  # 256 MB write: evicts the 126 MB L2
+                    e0.record()
+                    graph.replay()
+                    e1.record()
+                    e1.synchronize()
+                    tot += e0.elapsed_time(e1)
+                ms = tot / n_it
+                if world > 1:
+                    t = torch.tensor([ms], device=dev)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    ms = float(t.item())
+                gbs = case.bytes_per_query() * B / (ms * 1e-3) / 1e9
+                res[f"{kind}_ctx{ctx}_B{B}"] = {"us_per_step": ms * 1e3, "queries_per_s": world * B / (ms * 1e-3),
+                                                "bytes_per_query": case.bytes_per_query(), "achieved_GBs_per_gpu": gbs,
+                                                "frac_of_hbm": gbs / peak, "kv_rows_per_query": case.idxw}
+                del graph, case
+                torch.cuda.empty_cache()
+    if rank != 0:
+        return
+    key = f"csa_ctx{a.ctx.split(',')[-1]}_B{a.attn_batches.split(',')[-1]}"
+    line = {"metric": "sparse_attn_decode_queries_per_s", "value": res[key]["queries_per_s"], "unit": "queries/s",
+            "n_gpus": world, "steps": n_it, "warmup": max(a.warmup, 3), "ms_per_step": res[key]["us_per_step"] / 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over BF16 KV",
+            "data": "synthetic",
+            "config": {"workload": "config3: sparse-attention decode step (stable top-512 of the indexer scores + gathered "
+                                   "attention over window ++ compressed cache; HCA attends every compressed entry), "
+                                   "per-sequence BF16 caches", "headline_case": key, "heads": ATTN_H, "head_dim": ATTN_D,
+                       "window": ATTN_WIN, "topk": ATTN_TOPK, "parallelism": f"batch split, {world} GPUs, no collective",
+                       "l2": "256 MB written between timed steps"},
+            "results": res, "hbm_peak_GBs": peak, "peak_kind": peak_kind,
+            "roofline": {"kernel": "topk_stable_kernel + sparse_scores_kernel + sparse_pv_kernel (one decode step)",
+                         "bound": "hbm", "achieved": res[key]["achieved_GBs_per_gpu"], "peak": peak, "unit": "GB/s",
+                         "frac": res[key]["frac_of_hbm"], "traffic": None}}
+    if not a.no_cpu_baseline:
+        from _oracle import ref
+        Lr = ref()
+        if Lr is not None:
+            ctx = int(a.ctx.split(",")[-1])
+            c = attn_case_host(a.seed, "csa", ctx, 0)
+            attn_reference_query(Lr, c, "csa")
+            t0, n = time.perf_counter(), 0
+            while n < 2 or (time.perf_counter() - t0 < 10.0 and n < 50):
+                attn_reference_query(Lr, c, "csa")
+                n += 1
+            dt = (time.perf_counter() - t0) / n
+            line["cpu_baseline"] = {"value": 1.0 / dt, "unit": "queries/s", "cores": Lr.ref_pool_threads(), "kind": "reference",
+                                    "sample": f"{n} CSA queries at context {ctx}: apus_topk_stable + apus_sparse_attn on the host"}
+    emit(line)
+
+
 # ---- this repository's arm (one MoE sublayer) --------------------------------------------------
 _RESULT_OUT = None
 
@@ -735,6 +925,8 @@ def main():
     os.dup2(2, 1)
     if a.workload == "fp8_gemm":
         return fp8_gemm_main(a)
+    if a.workload == "attn":
+        return attn_main(a)
     if a.workload == "model":
         return model_reference_arm(a) if a.impl == "reference" else model_main(a)
     if a.impl == "reference":

@@ -471,6 +471,16 @@ int apus_cuda_sparse_attn_dev(const float *q, const float *sink, int h, int d,
                               const uint16_t *kv_b, int64_t nb, float *o,
                               void *stream);
 
+/* The decode form of c/attn.h:1308 for `s` sequences that each attend their OWN caches
+ * (row t of q / idxs belongs to sequence t): kv_a [s, >= na, d] and kv_b [s, >= nb, d]
+ * BF16, kv_a_stride / kv_b_stride = rows between consecutive sequences' caches (0: one
+ * cache shared by all rows, as apus_cuda_sparse_attn_dev). */
+int apus_cuda_sparse_attn_batch_dev(const float *q, const float *sink, int h, int d,
+                                    const int32_t *idxs, int idxw, int s, float scale,
+                                    const uint16_t *kv_a, int64_t na, int64_t kv_a_stride,
+                                    const uint16_t *kv_b, int64_t nb, int64_t kv_b_stride,
+                                    float *o, void *stream);
+
 /* ---- block and model (c/layer.h, c/model.h) --------------------------------- */
 
 /* The fields of the reference's ApusLayer (c/layer.h:45-71) that
