@@ -122,6 +122,7 @@ static int experts_run_tc(ApusCudaMoe *m, const float *xrows, const int32_t *rou
     a.scales_a = m->rs1; a.scales_b = m->rs3; a.ascales = m->b_xs.as<float>();
     a.groups = m->b_t13.as<TcGroup>(); a.n_groups_dev = ng; a.n_groups = max_groups;
     a.O = inter; a.K = dim; a.pair = 1; a.limit = m->limit; a.out = m->b_h.as<float>();
+    a.total_rows = n_rout;
     if (m->mark(st) || gemm_tc(a, st) || m->mark(st)) return 1;
     if (act_quant(m->b_h.as<float>(), nullptr, n_rout, inter, m->b_hq.as<uint8_t>(), m->b_hs.as<float>(),
                   ng + 1, st))
@@ -131,6 +132,7 @@ static int experts_run_tc(ApusCudaMoe *m, const float *xrows, const int32_t *rou
     b.scales_a = m->rs2; b.ascales = m->b_hs.as<float>();
     b.groups = m->b_t2.as<TcGroup>(); b.n_groups_dev = ng; b.n_groups = max_groups;
     b.O = dim; b.K = inter; b.pair = 0; b.round_out = 1; b.orow = m->b_spos.as<int>(); b.out = eo;
+    b.total_rows = n_rout;
     if (m->mark(st) || gemm_tc(b, st) || m->mark(st)) return 1;
     return 0;
 }

@@ -81,6 +81,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     uint64_t *full = bars, *empty = bars + NS, *sf_full = bars + 2 * NS, *done = bars + 3 * NS;
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 3 * NS + 1);
     volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
+    int *s_last = reinterpret_cast<int *>(s_tmem + 2);
 
     const int n_groups = a.n_groups_dev ? *a.n_groups_dev : a.n_groups;
     if ((int)blockIdx.y >= n_groups) return;
@@ -90,11 +91,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = a.K, O = a.O, NC = K >> 7;
     const int tile_row = grp.a_row + (int)blockIdx.x * 128;     // row in the weight slab
+    // K chunk of this CTA (gridDim.z > 1: a launch with few work items splits K so that most SMs
+    // stream): 128-wide chunks [c0, c1), whole batches of four (the scale loaders fetch 16 bytes)
+    const int S = (int)gridDim.z, z = (int)blockIdx.z;
+    const int b0 = (int)(((long long)(NC >> 2) * z) / S), b1 = (int)(((long long)(NC >> 2) * (z + 1)) / S);
+    const int c0 = 4 * b0, c1 = 4 * b1;
 
     if (tid == 0) {
         for (int s = 0; s < NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 128); }
         mbar_init(done, 1);
         *s_abort = 0;
+        *s_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {                                   // tensor-memory allocation (one warp)
@@ -111,9 +118,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (warp == 4) {
         // ---- TMA producer --------------------------------------------------------
         if (lane == 0) {
-            for (int i = 0; i < NC && !fail; i++) {
-                const int s = i % NS;
-                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+            for (int i = c0; i < c1 && !fail; i++) {
+                const int s = (i - c0) % NS;
+                const uint32_t ph = (uint32_t)((i - c0) / NS) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, s_abort)) { fail = 1; break; }
                 uint8_t *st = smem + (size_t)s * STAGE;
                 // the transaction count of a packed 4-bit tile is its global-memory size
@@ -128,9 +135,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     } else if (warp == 5) {
         // ---- MMA issuer -------------------------------------------------------------
         if (lane == 0) {
-            for (int i = 0; i < NC && !fail; i++) {
-                const int s = i % NS;
-                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+            for (int i = c0; i < c1 && !fail; i++) {
+                const int s = (i - c0) % NS;
+                const uint32_t ph = (uint32_t)((i - c0) / NS) & 1u;
                 if (!mbar_wait(&full[s], ph, s_abort)) { fail = 2; break; }
                 if (!mbar_wait(&sf_full[s], ph, s_abort)) { fail = 5; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -142,7 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const uint32_t idesc = umma_idesc(j, j);
-                    const uint32_t acc = (i | j) ? 1u : 0u;
+                    const uint32_t acc = ((i - c0) | j) ? 1u : 0u;
                     umma_mxf8f6f4(tmem + TC_COL_D0, da + 2 * j, dx + 2 * j, idesc, sf, sf + 8, acc);
                     if (PAIR) umma_mxf8f6f4(tmem + TC_COL_D1, db + 2 * j, dx + 2 * j, idesc, sf + 4, sf + 8, acc);
                 }
@@ -173,15 +180,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         };
         auto comp = [](const uint4 &v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; };
         auto compf = [](const float4 &v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; };
-        const int NB4 = NC >> 2;                       // K is a multiple of 512 on this path
-        load_batch(0, ca, cb, cx);
-        for (int i4 = 0; i4 < NB4 && !fail; i4++) {
-            if (i4 + 1 < NB4) load_batch(i4 + 1, na, nb, nx);
+        // K is a multiple of 512 on this path: batches [b0, b1) of four chunks
+        load_batch(b0, ca, cb, cx);
+        for (int i4 = b0; i4 < b1 && !fail; i4++) {
+            if (i4 + 1 < b1) load_batch(i4 + 1, na, nb, nx);
 #pragma unroll
             for (int cc = 0; cc < 4; cc++) {
                 const int i = i4 * 4 + cc;
-                const int s = i % NS;
-                const uint32_t ph = (uint32_t)(i / NS) & 1u;
+                const int s = (i - c0) % NS;
+                const uint32_t ph = (uint32_t)((i - c0) / NS) & 1u;
                 uint32_t xb = 0;
                 if (xrow_ok) xb = ((__float_as_uint(compf(cx, cc)) >> 23) & 0xffu) * 0x01010101u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, s_abort)) { fail = 3; break; }
@@ -206,7 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (PAIR) tmem_ld32(tmem + lane_base + TC_COL_D1, d1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             const int o = (int)blockIdx.x * 128 + tid;
-            if (o < O) {
+            if (o < O && S == 1) {
 #pragma unroll
                 for (int n = 0; n < TC_N; n++) {
                     if (n >= nrows) break;
@@ -216,15 +223,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     else v = a.round_out ? bf16_round(__uint_as_float(d0[n])) : __uint_as_float(d0[n]);
                     a.out[(size_t)dst * O + o] = v;
                 }
+            } else if (o < O) {
+                // park this chunk's sums: part[(matrix, chunk)][sorted row][o]
+                float *pa = a.part + ((size_t)z * a.total_rows) * O;
+                float *pb = a.part + ((size_t)(S + z) * a.total_rows) * O;
+#pragma unroll
+                for (int n = 0; n < TC_N; n++) {
+                    if (n >= nrows) break;
+                    pa[(size_t)(row0 + n) * O + o] = __uint_as_float(d0[n]);
+                    if (PAIR) pb[(size_t)(row0 + n) * O + o] = __uint_as_float(d1[n]);
+                }
+                __threadfence();
             }
         }
     }
     if (fail) {
         *s_abort = 1;
         atomicCAS(&g_tc_status, 0, fail);
-        // give copies already issued to this CTA's shared memory time to land
-        for (int i = 0; i < 2000; i++) __nanosleep(1000);
     }
+    if (S > 1) {
+        // the chunk that arrives last at this (tile, work item) adds the chunks in order and finishes the rows
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0 && !*s_abort) {
+            const int slot = (int)blockIdx.y * (int)gridDim.x + (int)blockIdx.x;
+            const int prev = atomicAdd(&a.counters[slot], 1);
+            if (prev == S - 1) { a.counters[slot] = 0; *s_last = 1; }
+            __threadfence();
+        }
+        __syncthreads();
+        const int o = (int)blockIdx.x * 128 + tid;
+        if (*s_last && tid < 128 && o < O) {
+            for (int n = 0; n < nrows; n++) {
+                float va = 0.f, vb = 0.f;
+                for (int c = 0; c < S; c++) {
+                    va = __fadd_rn(va, __ldcg(a.part + ((size_t)c * a.total_rows + row0 + n) * O + o));
+                    if (PAIR) vb = __fadd_rn(vb, __ldcg(a.part + ((size_t)(S + c) * a.total_rows + row0 + n) * O + o));
+                }
+                const int dst = a.orow ? a.orow[row0 + n] : row0 + n;
+                float v;
+                if (PAIR) v = swiglu_tc(va, vb, a.limit);
+                else v = a.round_out ? bf16_round(va) : va;
+                a.out[(size_t)dst * O + o] = v;
+            }
+        }
+    }
+    if (fail)       // give copies already issued to this CTA's shared memory time to land
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 5)
@@ -283,7 +328,7 @@ static int launch_tc(const TcArgs &a, cudaStream_t st) {
     const size_t smem = (size_t)NS * STAGE + 1024 + 256;
     auto kern = gemm_tc_kernel<PAIR, NS>;
     if (ensure_dyn_smem((const void *)kern, smem)) return 1;
-    dim3 grid((unsigned)(a.O / 128), (unsigned)a.n_groups);
+    dim3 grid((unsigned)(a.O / 128), (unsigned)a.n_groups, (unsigned)(a.ksplit > 1 ? a.ksplit : 1));
     kern<<<grid, TC_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.pair ? a.map_b : a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.map_x), a);
@@ -291,9 +336,30 @@ static int launch_tc(const TcArgs &a, cudaStream_t st) {
     return 0;
 }
 
-int gemm_tc(const TcArgs &a, cudaStream_t st) {
+int gemm_tc(const TcArgs &a0, cudaStream_t st) {
+    TcArgs a = a0;
     APUS_REQUIRE(a.K % 512 == 0 && a.O % 128 == 0, "gemm_tc: unsupported shape O=%d K=%d", a.O, a.K);
     if (a.n_groups <= 0) return 0;
+    // Optional K split of the gate/up pair (APUS_TC_KSPLIT=2 or 4; off by default): grid.z chunks
+    // whose sums the CTA that finishes last adds in chunk order.  It depends on the shape only,
+    // never on the number of work items, so a token's result does not depend on the batch it is in
+    // or on how many experts the rank holds.  Measured on the six-layer slice it buys nothing at
+    // batch 1 (2.31 vs 2.32 ms per step: the launch is bound by the per-chunk hand-offs of a CTA,
+    // not by the number of CTAs) and costs 8 % at batch 32, hence off.
+    a.ksplit = 1;
+    const long long ctas = (long long)(a.O / 128) * a.n_groups;
+    static const int want = getenv("APUS_TC_KSPLIT") ? atoi(getenv("APUS_TC_KSPLIT")) : 1;
+    if (a.total_rows > 0 && a.pair && want > 1) {
+        const int nb4 = a.K >> 9;
+        int S = want;
+        while (S > 1 && (nb4 % S || S > nb4)) S--;
+        if (S > 1) {
+            void *ws = nullptr;
+            int *cnt = nullptr;
+            if (stream_scratch(st, (size_t)S * (a.pair ? 2 : 1) * a.total_rows * a.O * 4, &ws, (size_t)ctas, &cnt)) return 1;
+            a.ksplit = S; a.part = (float *)ws; a.counters = cnt;
+        }
+    }
     return a.pair ? launch_tc<true, 3>(a, st) : launch_tc<false, 5>(a, st);
 }
 

@@ -76,6 +76,10 @@ struct TcArgs {
     const int *orow;                     // nullable: output row of sorted position p
     float *out;
     int tx_bytes;                        // 0 = default transaction bytes per stage
+    int total_rows;                      // activation rows over all work items (0: unknown, K is never split)
+    int ksplit;                          // set by gemm_tc: K chunks (grid.z); > 1 uses part + counters
+    float *part;                         // [(pair ? 2 : 1) * ksplit, total_rows, O] chunk sums
+    int *counters;                       // zeroed, one per (output tile, work item); left zeroed
 };
 int gemm_tc(const TcArgs &a, cudaStream_t st);
 int gemm_tc_status(int reset);

@@ -319,13 +319,16 @@ mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ ra
     }
 }
 
-// The same step with a token spread over a cluster of MHC_CL CTAs (tree-order norms only):
-// one CTA walking a 4 x 4096 state alone takes ~30 us, most of it latency (gates -> 64 KB of
-// loads through one SM -> sum of squares -> second pass), and at small batches that chain
-// sits twice in every layer.  Here every CTA of the cluster collapses its slice of the row,
-// the slices' sums of squares meet through distributed shared memory (added in rank order,
-// the same total in every CTA), and each CTA normalises its own slice; the Sinkhorn part,
-// which nothing in this kernel waits for, runs on one warp of the last CTA afterwards.
+// The same step with a token spread over a cluster of MHC_CL CTAs: one CTA walking a
+// 4 x 4096 state alone takes ~30 us, most of it latency (gates -> 64 KB of loads through one
+// SM -> sum of squares -> second pass), and at small batches that chain sits twice in every
+// layer.  Here every CTA of the cluster collapses its slice of the row and each CTA normalises
+// its own slice; the Sinkhorn part, which nothing in this kernel waits for, runs on one warp
+// of the last CTA afterwards.  The sum of squares of the norm meets through distributed shared
+// memory: in tree order the slices' sums are added in rank order (the same total in every
+// CTA); in the reference's order (seq) every CTA stores its squares into rank 0's shared
+// memory and one lane there adds all d of them in index order -- the reference's chain, about
+// 8 us at d = 4096, without the rest of the kernel queued behind one SM.
 #define MHC_CL 8
 __global__ void __cluster_dims__(MHC_CL, 1, 1) __launch_bounds__(128)
 mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__ raw, int d, int n,
@@ -334,9 +337,10 @@ mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__
                          int head_mode, const float *__restrict__ norm_w, float rms_eps,
                          float *__restrict__ pre_out, float *__restrict__ post_out,
                          float *__restrict__ comb_out, float *__restrict__ y,
-                         float *__restrict__ y_normed) {
+                         float *__restrict__ y_normed, int seq) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ __align__(16) float s_sq[];   // seq: the d squares of the collapsed row (rank 0's copy is used)
     __shared__ float s_pre[MHC_MAX_N];
     __shared__ float red[32];
     __shared__ float s_part;
@@ -368,16 +372,29 @@ mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__
             }
             acc.x = bf16_round(acc.x); acc.y = bf16_round(acc.y); acc.z = bf16_round(acc.z); acc.w = bf16_round(acc.w);
             *reinterpret_cast<float4 *>(y + (size_t)row * d + i) = acc;
-            ss = fmaf(acc.x, acc.x, ss); ss = fmaf(acc.y, acc.y, ss); ss = fmaf(acc.z, acc.z, ss); ss = fmaf(acc.w, acc.w, ss);
+            if (seq && y_normed) {
+                float *sq0 = cluster.map_shared_rank(s_sq, 0);
+                *reinterpret_cast<float4 *>(sq0 + i) = make_float4(__fmul_rn(acc.x, acc.x), __fmul_rn(acc.y, acc.y),
+                                                                   __fmul_rn(acc.z, acc.z), __fmul_rn(acc.w, acc.w));
+            } else {
+                ss = fmaf(acc.x, acc.x, ss); ss = fmaf(acc.y, acc.y, ss); ss = fmaf(acc.z, acc.z, ss); ss = fmaf(acc.w, acc.w, ss);
+            }
         }
     }
     if (y && y_normed) {
-        const float mine = block_sum(ss, red);
-        if (tid == 0) s_part = mine;
-        cluster.sync();
         float tot = 0.f;
-        for (int q = 0; q < MHC_CL; q++) tot = __fadd_rn(tot, *cluster.map_shared_rank(&s_part, q));
-        cluster.sync();                            // nobody leaves while its partial sum may still be read
+        if (seq) {
+            cluster.sync();                        // every slice's squares have landed in rank 0
+            if (rank == 0 && tid == 0) s_part = seq_sum_smem(s_sq, d, 0.f);
+            cluster.sync();
+            tot = *cluster.map_shared_rank(&s_part, 0);
+        } else {
+            const float mine = block_sum(ss, red);
+            if (tid == 0) s_part = mine;
+            cluster.sync();
+            for (int q = 0; q < MHC_CL; q++) tot = __fadd_rn(tot, *cluster.map_shared_rank(&s_part, q));
+        }
+        cluster.sync();                            // nobody leaves while its shared memory may still be read
         const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)d), rms_eps)));
         for (int i = i0 + tid * 4; i < i1; i += blockDim.x * 4) {
             const float4 v = *reinterpret_cast<const float4 *>(y + (size_t)row * d + i);
@@ -496,10 +513,10 @@ static int launch_finish(const float *x4, const float *raw, int d, int n, int nm
                          float head_scale, const float *base, float norm_eps, float hc_eps, int iters, int head_mode,
                          const float *norm_w, float rms_eps, float *pre, float *post, float *comb, float *y,
                          float *y_normed, int rows, cudaStream_t st) {
-    if (!finish_seq() && d % 4 == 0 && n * n <= 32 && y) {
-        mhc_pre_finish_cl_kernel<<<rows * MHC_CL, 128, 0, st>>>(x4, raw, d, n, nmix, scale, head_scale, base, norm_eps,
-                                                              hc_eps, iters, head_mode, norm_w, rms_eps, pre, post, comb,
-                                                              y, y_normed);
+    if (d % 4 == 0 && n * n <= 32 && y && (size_t)d * sizeof(float) <= 48 * 1024) {
+        mhc_pre_finish_cl_kernel<<<rows * MHC_CL, 128, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, head_scale, base,
+                                                                            norm_eps, hc_eps, iters, head_mode, norm_w,
+                                                                            rms_eps, pre, post, comb, y, y_normed, finish_seq());
     } else {
         mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, head_scale, base, norm_eps,
                                                                  hc_eps, iters, head_mode, norm_w, rms_eps, pre, post,
