@@ -290,6 +290,8 @@ def load(path=LIB_PATH):
         "apus_synth_key": (C.c_uint64, [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]),
         "apus_synth_fill_host": (ci, [vp, ci, C.c_uint64, C.c_uint64, C.c_double, C.c_double, ci]),
         "apus_synth_fill_dev": (ci, [vp, ci, C.c_uint64, C.c_uint64, C.c_double, C.c_double, vp]),
+        "apus_synth_fill_slab_dev": (ci, [vp, ci, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32,
+                                          C.c_double, C.c_double, vp]),
         "apus_fnv1a": (C.c_uint64, [vp, C.c_uint64, C.c_uint64]),
     }
     for name, (res, args) in sigs.items():

@@ -90,6 +90,14 @@ __host__ __device__ __forceinline__ long long sy_subset(uint64_t key, uint64_t r
     return (long long)got[j];
 }
 
+__host__ __device__ __forceinline__ uint64_t sy_key(uint64_t seed, uint32_t layer, uint32_t tensor, uint32_t expert) {
+    uint64_t k = sy_mix(seed ^ 0xA5A5F00DDEADBEEFull);
+    k = sy_mix(k + 0x9E3779B97F4A7C15ull * ((uint64_t)layer + 1));
+    k = sy_mix(k + 0xC2B2AE3D27D4EB4Full * ((uint64_t)tensor + 1));
+    k = sy_mix(k + 0x165667B19E3779F9ull * ((uint64_t)expert + 1));
+    return k;
+}
+
 struct SyArgs { void *dst; int kind; uint64_t n, key; float a, b; };
 
 // elements [lo, hi) of the tensor; lo is a multiple of 8 for the byte kinds
@@ -143,6 +151,16 @@ __global__ void synth_fill_kernel(SyArgs p, uint64_t units) {
     sy_fill_range(p, t, units, (uint64_t)gridDim.x * blockDim.x);
 }
 
+// n_seg consecutive tensors of n elements each (an expert-major slab): blockIdx.y = segment, whose
+// key is that of expert first_expert + segment -- the bytes of n_seg separate fills, in one launch
+__global__ void synth_fill_slab_kernel(SyArgs p, uint64_t units, uint64_t seg_bytes, uint64_t seed, uint32_t layer,
+                                       uint32_t tensor, uint32_t first_expert) {
+    p.dst = (char *)p.dst + seg_bytes * blockIdx.y;
+    p.key = sy_key(seed, layer, tensor, first_expert + blockIdx.y);
+    const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    sy_fill_range(p, t, units, (uint64_t)gridDim.x * blockDim.x);
+}
+
 int sy_check(const void *dst, int kind, uint64_t n, double a, double b, uint64_t *units) {
     APUS_REQUIRE(dst || !n, "synth_fill: NULL destination");
     APUS_REQUIRE(kind >= APUS_SYNTH_U8 && kind <= APUS_SYNTH_I64_SUBSET, "synth_fill: unknown kind %d", kind);
@@ -161,11 +179,25 @@ int sy_check(const void *dst, int kind, uint64_t n, double a, double b, uint64_t
 extern "C" {
 
 uint64_t apus_synth_key(uint64_t seed, uint32_t layer, uint32_t tensor, uint32_t expert) {
-    uint64_t k = sy_mix(seed ^ 0xA5A5F00DDEADBEEFull);
-    k = sy_mix(k + 0x9E3779B97F4A7C15ull * ((uint64_t)layer + 1));
-    k = sy_mix(k + 0xC2B2AE3D27D4EB4Full * ((uint64_t)tensor + 1));
-    k = sy_mix(k + 0x165667B19E3779F9ull * ((uint64_t)expert + 1));
-    return k;
+    return sy_key(seed, layer, tensor, expert);
+}
+
+int apus_synth_fill_slab_dev(void *dst, int kind, uint64_t n, uint32_t n_seg, uint64_t seed, uint32_t layer,
+                             uint32_t tensor, uint32_t first_expert, double a, double b, void *stream) {
+    uint64_t units = 0;
+    if (sy_check(dst, kind, n, a, b, &units)) return 1;
+    APUS_REQUIRE(kind <= APUS_SYNTH_E4M3 && n_seg <= 65535, "synth_fill_slab: kind %d / %u segments", kind, n_seg);
+    if (!units || !n_seg) return 0;
+    if (kind == APUS_SYNTH_U8) { a = 0; b = 255; }
+    static const uint64_t esz[] = {1, 1, 4, 4, 2, 1};
+    APUS_REQUIRE((n * esz[kind]) % 8 == 0, "synth_fill_slab: segments must be a multiple of 8 bytes");
+    SyArgs p = {dst, kind, n, 0, (float)a, (float)b};
+    uint64_t blocks = (units + 255) / 256;
+    if (blocks > 148 * 2) blocks = 148 * 2;
+    synth_fill_slab_kernel<<<dim3((unsigned)blocks, n_seg), 256, 0, (cudaStream_t)stream>>>(p, units, n * esz[kind], seed,
+                                                                                            layer, tensor, first_expert);
+    APUS_LAUNCHED();
+    return 0;
 }
 
 int apus_synth_fill_host(void *dst, int kind, uint64_t n, uint64_t key, double a, double b, int threads) {

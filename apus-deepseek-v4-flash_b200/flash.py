@@ -213,6 +213,13 @@ class RandomFlashModel:
         n = self.e_hi - self.e_lo
         _, pc = self._alloc((n, O, K // 2), np.uint8)
         _, ps = self._alloc((n, O, K // 32), np.uint8)
+        if not self.host and n:                # one launch per slab; the same bytes as the per-expert fills below
+            T = TENSOR_IDS
+            self.check(self.lib.apus_synth_fill_slab_dev(pc, K_U8, O * (K // 2), n, self.seed, layer, T[name], self.e_lo,
+                                                         0.0, 0.0, self.stream), "synth_fill_slab_dev")
+            self.check(self.lib.apus_synth_fill_slab_dev(ps, K_U8_RANGE, O * (K // 32), n, self.seed, layer, T[name + ".s"],
+                                                         self.e_lo, 120.0, 126.0, self.stream), "synth_fill_slab_dev")
+            return pc, ps
         for le in range(n):
             self._fill_at(pc + le * O * (K // 2), layer, name, K_U8, O * (K // 2), 0, 0, self.e_lo + le)
             self._fill_at(ps + le * O * (K // 32), layer, name + ".s", K_U8_RANGE, O * (K // 32), 120, 126,

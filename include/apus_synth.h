@@ -50,6 +50,13 @@ int apus_synth_fill_host(void *dst, int kind, uint64_t n, uint64_t key, double a
 int apus_synth_fill_dev(void *dst, int kind, uint64_t n, uint64_t key, double a, double b,
                         void *stream);
 
+/* n_seg consecutive tensors of n elements each (an expert-major slab) in ONE launch: segment s
+ * is filled with the key apus_synth_key(seed, layer, tensor, first_expert + s), i.e. with the
+ * bytes n_seg separate fills would write.  Kinds U8 .. E4M3. */
+int apus_synth_fill_slab_dev(void *dst, int kind, uint64_t n, uint32_t n_seg, uint64_t seed,
+                             uint32_t layer, uint32_t tensor, uint32_t first_expert, double a,
+                             double b, void *stream);
+
 /* 64-bit FNV-1a over a byte string, continued from `h` (start with
  * APUS_FNV1A_INIT): the digest the token streams are compared by. */
 #define APUS_FNV1A_INIT 0xcbf29ce484222325ull

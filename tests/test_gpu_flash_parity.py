@@ -176,6 +176,22 @@ def test_each_layer_at_real_dims_stage_by_stage(li, sum_order):
         L.apus_cuda_disable()
 
 
+def test_slab_fill_equals_per_expert_fills():
+    """The one-launch slab fill writes the bytes of the per-expert fills (host build)."""
+    import torch
+    L = lib()
+    n, n_seg, seed, layer, tensor, first = 4096 * 8, 5, 3, 7, 26, 11
+    for kind, a, b in ((0, 0.0, 0.0), (1, 120.0, 126.0)):
+        dev = torch.zeros(n_seg * n, dtype=torch.uint8, device="cuda")
+        assert L.apus_synth_fill_slab_dev(dev.data_ptr(), kind, n, n_seg, seed, layer, tensor, first, a, b,
+                                          torch.cuda.current_stream().cuda_stream) == 0, L.apus_cuda_last_error()
+        torch.cuda.synchronize()
+        host = np.empty((n_seg, n), np.uint8)
+        for s in range(n_seg):
+            assert L.apus_synth_fill_host(P(host[s]), kind, n, L.apus_synth_key(seed, layer, tensor, first + s), a, b, 1) == 0
+        assert np.array_equal(dev.cpu().numpy(), host.ravel())
+
+
 @pytest.fixture(scope="module")
 def gold():
     if not GOLD.exists():
