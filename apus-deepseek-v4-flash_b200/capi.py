@@ -275,6 +275,10 @@ def load(path=LIB_PATH):
         "apus_cuda_moe_shared_dev": (ci, [vp, vp, ci, vp, vp]),
         "apus_cuda_moe_ep_plan_dev": (ci, [vp, ci, ci, ci, ci, vp, vp, vp]),
         "apus_cuda_moe_ep_rows_dev": (ci, [vp, ci, vp, ci, ci, ci, vp, vp]),
+        "apus_cuda_moe_ep_row_bytes": (C.c_size_t, [vp]),
+        "apus_cuda_moe_ep_pack_dev": (ci, [vp, vp, ci, vp, ci, vp, vp]),
+        "apus_cuda_moe_experts_q_dev": (ci, [vp, vp, ci, vp, vp, vp]),
+        "apus_cuda_moe_ep_unpack_dev": (ci, [vp, ci, vp, ci, vp, vp]),
         "apus_cuda_moe_forward_dev": (ci, [vp, vp, vp, ci, vp, vp]),
         "apus_cuda_moe_last_routing": (ci, [vp, ci, vp, vp, vp]),
         "apus_cuda_fp4_upload": (vp, [C.POINTER(QW)]),

@@ -103,19 +103,23 @@ static int pick_chunk(int n_rout, int n_local) {
 
 // Routed experts on the tcgen05 path: group first, quantise the token rows
 // straight into sorted order, then two block-scaled tensor-core GEMMs.
+// qrows != NULL: the token rows arrive quantised (EP exchange: dim codes + dim/128 scales per row,
+// quantised once on the token's home rank -- the quantisation is per token, so the codes are the
+// ones this rank would compute); they are gathered into sorted order instead of being quantised here.
 static int experts_run_tc(ApusCudaMoe *m, const float *xrows, const int32_t *rout_row,
-                          const int32_t *rout_eid, int n_rout, float *eo, cudaStream_t st) {
+                          const int32_t *rout_eid, int n_rout, float *eo, cudaStream_t st,
+                          const uint8_t *qrows = nullptr) {
     const int dim = m->dim, inter = m->inter;
     const int n_local = m->e_hi - m->e_lo;
     const int chunk = 32;
     const int max_groups = n_rout < n_local + n_rout / chunk + 1 ? n_rout : n_local + n_rout / chunk + 1;
     int *ng = m->b_ng.as<int>();
-    if (moe_group(rout_eid, rout_row, m->topk, n_rout, m->sl, chunk, m->b_spos.as<int>(), m->b_srow.as<int>(),
+    if (moe_group(rout_eid, rout_row, qrows ? 1 : m->topk, n_rout, m->sl, chunk, m->b_spos.as<int>(), m->b_srow.as<int>(),
                   m->b_g13.as<GemmGroup>(), m->b_g2.as<GemmGroup>(), ng, max_groups, st,
                   m->b_t13.as<TcGroup>(), m->b_t2.as<TcGroup>(), inter, dim))
         return 1;
-    if (act_quant(xrows, m->b_srow.as<int>(), n_rout, dim, m->b_xq.as<uint8_t>(), m->b_xs.as<float>(),
-                  ng + 1, st))
+    if (qrows ? ep_gather_q(qrows, dim, m->b_srow.as<int>(), ng + 1, n_rout, m->b_xq.as<uint8_t>(), m->b_xs.as<float>(), st)
+              : act_quant(xrows, m->b_srow.as<int>(), n_rout, dim, m->b_xq.as<uint8_t>(), m->b_xs.as<float>(), ng + 1, st))
         return 1;
     TcArgs a = {};
     a.map_a = m->map_w1; a.map_b = m->map_w3; a.map_x = m->map_xq;
@@ -481,6 +485,38 @@ int apus_cuda_moe_experts_dev(ApusCudaMoe *m, const float *xrows, int n_rows, co
     if (n_rout <= 0) return 0;
     if (m->ensure(n_rows, n_rout)) return 1;
     return experts_run(m, xrows, n_rows, rout_row, rout_eid, n_rout, eo, (cudaStream_t)stream);
+}
+
+// ---- expert parallelism with the compact payload -------------------------------------------
+size_t apus_cuda_moe_ep_row_bytes(const ApusCudaMoe *m) { return m ? (size_t)m->dim + (size_t)(m->dim / 128) * 4 : 0; }
+
+int apus_cuda_moe_ep_pack_dev(ApusCudaMoe *m, const float *x, int s, const int32_t *slot_of, int n_rout,
+                              uint8_t *send, void *stream) {
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    if (s <= 0 || n_rout <= 0) return 0;
+    APUS_REQUIRE(m->dim % 128 == 0, "moe_ep_pack: dim=%d must be a multiple of 128", m->dim);
+    if (m->ensure(s, n_rout)) return 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    // one quantisation per token (c/moe.h:246-254), then every routing's copy goes into its slot
+    if (act_quant(x, nullptr, s, m->dim, m->b_xq.as<uint8_t>(), m->b_xs.as<float>(), nullptr, st)) return 1;
+    return ep_pack_q(m->b_xq.as<uint8_t>(), m->b_xs.as<float>(), m->dim, slot_of, n_rout, m->topk, send, st);
+}
+
+int apus_cuda_moe_experts_q_dev(ApusCudaMoe *m, const uint8_t *qrows, int n_rows, const int32_t *rout_eid,
+                                uint16_t *eo_bf16, void *stream) {
+    if (!m) { set_error("NULL moe handle"); return 1; }
+    if (n_rows <= 0) return 0;
+    APUS_REQUIRE(m->use_tc, "moe_experts_q: needs the tcgen05 expert path (shapes that are multiples of 512)");
+    if (m->ensure(n_rows, n_rows)) return 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    // routing i is row i; the rows' expert outputs are BF16 values (c/attn.h:447): their bits travel back
+    if (experts_run_tc(m, nullptr, nullptr, rout_eid, n_rows, m->b_eo.as<float>(), st, qrows)) return 1;
+    return f32_to_bf16(m->b_eo.as<float>(), eo_bf16, (long long)n_rows * m->dim, st);
+}
+
+int apus_cuda_moe_ep_unpack_dev(const uint16_t *back, int dim, const int32_t *slot_of, int n_rout, float *eo,
+                                void *stream) {
+    return ep_unpack_bf16(back, dim, slot_of, n_rout, eo, (cudaStream_t)stream);
 }
 
 int apus_cuda_moe_shared_dev(ApusCudaMoe *m, const float *x, int s, float *shared, void *stream) {

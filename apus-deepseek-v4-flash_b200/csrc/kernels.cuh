@@ -158,6 +158,12 @@ int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int row_div, int
               const MoeSlab &slab, int chunk, int *sorted_pos, int *sorted_row,
               GemmGroup *g13, GemmGroup *g2, int *n_groups, int max_groups,
               cudaStream_t st, TcGroup *t13 = nullptr, TcGroup *t2 = nullptr, int o13 = 0, int o2 = 0);
+// quantised rows for the expert-parallel exchange (dim codes + dim/128 f32 scales per row)
+int ep_pack_q(const uint8_t *codes, const float *scales, int dim, const int32_t *slot_of, int n_rout, int topk,
+              uint8_t *packed, cudaStream_t st);
+int ep_gather_q(const uint8_t *packed, int dim, const int *sorted_row, const int *n_dev, int n_max, uint8_t *codes,
+                float *scales, cudaStream_t st);
+int ep_unpack_bf16(const uint16_t *src, int dim, const int32_t *slot_of, int n_rout, float *dst, cudaStream_t st);
 // y[t] = sum_j wgt[t,j]*eo[t*topk+j] (j order) ; out = bf16(y + shared).
 int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
                 int topk, int dim, float *out, float *routed, cudaStream_t st);

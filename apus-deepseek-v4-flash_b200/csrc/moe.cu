@@ -309,6 +309,69 @@ ep_rows_kernel(const float *__restrict__ src, int dim, const int32_t *__restrict
     for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) d4[i] = s4[i];
 }
 
+// Quantised token rows as they travel between ranks: `dim` E4M3 codes followed by dim/128 f32
+// scales (powers of two), EP_QROW(dim) bytes per row.
+// pack: slot slot_of[p] of `packed` <- codes/scales of token row p / topk.
+__global__ void __launch_bounds__(256)
+ep_pack_q_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ scales, int dim,
+                 const int32_t *__restrict__ slot_of, int topk, uint8_t *__restrict__ packed) {
+    const int p = blockIdx.x, row = p / topk, nab = dim >> 7;
+    const size_t rb = (size_t)dim + (size_t)nab * 4;
+    uint8_t *dst = packed + (size_t)slot_of[p] * rb;
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(codes + (size_t)row * dim);
+    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+    for (int i = threadIdx.x; i < dim / 16; i += blockDim.x) d4[i] = s4[i];
+    float *ds = reinterpret_cast<float *>(dst + dim);
+    for (int i = threadIdx.x; i < nab; i += blockDim.x) ds[i] = scales[(size_t)row * nab + i];
+}
+// unpack into sorted order: row p of codes/scales <- packed row sorted_row[p], for p < *n_dev
+__global__ void __launch_bounds__(256)
+ep_gather_q_kernel(const uint8_t *__restrict__ packed, int dim, const int *__restrict__ sorted_row,
+                   const int *__restrict__ n_dev, uint8_t *__restrict__ codes, float *__restrict__ scales) {
+    const int p = blockIdx.x, nab = dim >> 7;
+    if (p >= *n_dev) return;
+    const size_t rb = (size_t)dim + (size_t)nab * 4;
+    const uint8_t *src = packed + (size_t)sorted_row[p] * rb;
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+    uint4 *d4 = reinterpret_cast<uint4 *>(codes + (size_t)p * dim);
+    for (int i = threadIdx.x; i < dim / 16; i += blockDim.x) d4[i] = s4[i];
+    const float *ss = reinterpret_cast<const float *>(src + dim);
+    for (int i = threadIdx.x; i < nab; i += blockDim.x) scales[(size_t)p * nab + i] = ss[i];
+}
+// expert outputs that came back as BF16 bits, to (t, j) order as f32: dst[p] = widen(src[slot_of[p]])
+__global__ void __launch_bounds__(256)
+ep_unpack_bf16_kernel(const uint16_t *__restrict__ src, int dim, const int32_t *__restrict__ slot_of,
+                      float *__restrict__ dst) {
+    const int p = blockIdx.x;
+    const uint2 *s2 = reinterpret_cast<const uint2 *>(src + (size_t)slot_of[p] * dim);
+    float4 *d4 = reinterpret_cast<float4 *>(dst + (size_t)p * dim);
+    for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) {
+        const uint2 v = s2[i];
+        d4[i] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                            __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+    }
+}
+int ep_pack_q(const uint8_t *codes, const float *scales, int dim, const int32_t *slot_of, int n_rout, int topk,
+              uint8_t *packed, cudaStream_t st) {
+    if (n_rout <= 0) return 0;
+    ep_pack_q_kernel<<<n_rout, 256, 0, st>>>(codes, scales, dim, slot_of, topk, packed);
+    APUS_LAUNCHED();
+    return 0;
+}
+int ep_gather_q(const uint8_t *packed, int dim, const int *sorted_row, const int *n_dev, int n_max, uint8_t *codes,
+                float *scales, cudaStream_t st) {
+    if (n_max <= 0) return 0;
+    ep_gather_q_kernel<<<n_max, 256, 0, st>>>(packed, dim, sorted_row, n_dev, codes, scales);
+    APUS_LAUNCHED();
+    return 0;
+}
+int ep_unpack_bf16(const uint16_t *src, int dim, const int32_t *slot_of, int n_rout, float *dst, cudaStream_t st) {
+    if (n_rout <= 0) return 0;
+    ep_unpack_bf16_kernel<<<n_rout, 256, 0, st>>>(src, dim, slot_of, dst);
+    APUS_LAUNCHED();
+    return 0;
+}
+
 int ep_plan(const int32_t *idx, int n_rout, int per_rank, int world, int slots, int32_t *send_eids,
             int32_t *slot_of, cudaStream_t st) {
     ep_plan_kernel<<<1, 1024, (size_t)n_rout * sizeof(int), st>>>(idx, n_rout, per_rank, world, slots, send_eids, slot_of);

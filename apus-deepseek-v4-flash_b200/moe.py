@@ -175,6 +175,27 @@ class ExpertParallelMoe:
         R = s * self.topk
         C = R                                            # slots per destination
         fused = x.is_cuda and idx.dtype == torch.int32 and x.dtype == torch.float32
+        if fused and self._compact_ok():
+            # compact payload: a row travels as E4M3 codes + per-128 scales (quantised once, here),
+            # an expert output as its BF16 bits -- 4,224 B out and 8,192 B back per routing slot
+            # instead of 16,384 B each way
+            L, st = lib(), self._stream()
+            rb = int(L.apus_cuda_moe_ep_row_bytes(self.handle))
+            send_q, recv_q, send_eids, recv_eids, eo_send, eo_back, eo, slot = self._compact_bufs(x.device, W * C, R, rb)
+            check(L.apus_cuda_moe_ep_plan_dev(idx.data_ptr(), R, self.E, W, C, send_eids.data_ptr(), slot.data_ptr(), st),
+                  "moe_ep_plan_dev")
+            check(L.apus_cuda_moe_ep_pack_dev(self.handle, x.data_ptr(), s, slot.data_ptr(), R, send_q.data_ptr(), st),
+                  "moe_ep_pack_dev")
+            dist.all_to_all_single(recv_q, send_q, group=self.group)
+            dist.all_to_all_single(recv_eids, send_eids, group=self.group)
+            check(L.apus_cuda_moe_experts_q_dev(self.handle, recv_q.data_ptr(), W * C, recv_eids.data_ptr(),
+                                                eo_send.data_ptr(), st), "moe_experts_q_dev")
+            dist.all_to_all_single(eo_back, eo_send, group=self.group)
+            check(L.apus_cuda_moe_ep_unpack_dev(eo_back.data_ptr(), dim, slot.data_ptr(), R, eo.data_ptr(), st),
+                  "moe_ep_unpack_dev")
+            cur.wait_stream(side)
+            shared.record_stream(cur)
+            return self.combine_fn(eo, wgt, shared)
         if fused:
             # three library kernels instead of a dozen tensor ops: slots + expert ids, rows in
             send_rows, send_eids, recv_rows, recv_eids, eo_back, eo, slot = self._exchange_bufs(x.device, W * C, R)
@@ -218,6 +239,30 @@ class ExpertParallelMoe:
         return self.combine_fn(eo, wgt, shared)
 
     _bufs = {}
+
+    def _compact_ok(self):
+        """The compact payload needs the library's own expert path on the tcgen05 kernels."""
+        ok = getattr(self, "_compact", None)
+        if ok is None:
+            import os
+            ok = (self.handle is not None and self.experts_fn == self._experts_cuda
+                  and os.environ.get("APUS_EP_COMPACT", "1") != "0"
+                  and lib().apus_cuda_moe_use_tc(self.handle, -1) == 1)
+            self._compact = ok
+        return ok
+
+    def _compact_bufs(self, device, n_slots, n_rout, row_bytes):
+        key = ("q", str(device), n_slots, n_rout, self.dim, row_bytes)
+        b = ExpertParallelMoe._bufs.get(key)
+        if b is None:
+            u8 = dict(dtype=torch.uint8, device=device)
+            i32 = dict(dtype=torch.int32, device=device)
+            i16 = dict(dtype=torch.bfloat16, device=device)      # BF16 bits (NCCL has no 16-bit integer type)
+            b = (torch.zeros(n_slots, row_bytes, **u8), torch.empty(n_slots, row_bytes, **u8), torch.empty(n_slots, **i32),
+                 torch.empty(n_slots, **i32), torch.zeros(n_slots, self.dim, **i16), torch.empty(n_slots, self.dim, **i16),
+                 torch.empty(n_rout, self.dim, dtype=torch.float32, device=device), torch.empty(n_rout, **i32))
+            ExpertParallelMoe._bufs[key] = b
+        return b
 
     def _exchange_bufs(self, device, n_slots, n_rout):
         """Exchange buffers, kept per (device, shape) and shared by the sublayers, which run

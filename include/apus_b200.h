@@ -433,6 +433,23 @@ int apus_cuda_moe_ep_plan_dev(const int32_t *idx, int n_rout, int n_experts,
 int apus_cuda_moe_ep_rows_dev(const float *src, int dim, const int32_t *slot_of,
                               int n_rout, int topk, int gather, float *dst,
                               void *stream);
+/* The same exchange with the compact payload (what crosses the links is what the arithmetic
+ * needs): a token row travels as its E4M3 codes + per-128 scales, quantised ONCE on the token's
+ * home rank (the quantisation is per token, c/moe.h:246-254, so the owner of the expert would
+ * compute the same codes), apus_cuda_moe_ep_row_bytes() = dim + dim/128*4 bytes per row slot;
+ * expert outputs are BF16 values (c/attn.h:447) and travel back as their 16 bits.
+ * pack: quantise x [s, dim] and copy the row of routing p = t*topk + j into slot slot_of[p] of
+ * `send` [world * slots rows].  experts_q: routing i = received row i with global expert id
+ * rout_eid[i] (-1: empty slot, skipped), outputs as BF16 bits [n_rows, dim].  unpack: eo[p] =
+ * widen(back[slot_of[p]]), back to (t, j) order for apus_cuda_moe_combine_dev.  Needs the
+ * tcgen05 expert path. */
+size_t apus_cuda_moe_ep_row_bytes(const ApusCudaMoe *m);
+int apus_cuda_moe_ep_pack_dev(ApusCudaMoe *m, const float *x, int s, const int32_t *slot_of,
+                              int n_rout, uint8_t *send, void *stream);
+int apus_cuda_moe_experts_q_dev(ApusCudaMoe *m, const uint8_t *qrows, int n_rows,
+                                const int32_t *rout_eid, uint16_t *eo_bf16, void *stream);
+int apus_cuda_moe_ep_unpack_dev(const uint16_t *back, int dim, const int32_t *slot_of,
+                                int n_rout, float *eo, void *stream);
 /* c/moe.h:570-581 on device: the FP8 shared expert for s tokens. */
 int apus_cuda_moe_shared_dev(ApusCudaMoe *m, const float *x, int s,
                              float *shared, void *stream);
