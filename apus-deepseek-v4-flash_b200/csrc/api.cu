@@ -1,6 +1,7 @@
 // C ABI, part 1: lifecycle, weight cache, kernel-level host-pointer entry points
 // and the single-matrix device-resident entry points (include/apus_b200.h).
 #include <stdarg.h>
+#include <tuple>
 #include <stdlib.h>
 
 #include "runtime.cuh"
@@ -106,6 +107,10 @@ int ensure_enabled() {
     return 0;
 }
 
+// which main chain each side stream is working for right now (set when a branch begins; enqueueing
+// is host-sequential, so this is the chain whose launches are being issued)
+static cudaStream_t g_aux_owner[Ctx::N_AUX] = {nullptr, nullptr, nullptr};
+
 cudaStream_t branch_begin(cudaStream_t main, int i) {
     Ctx &c = ctx();
     static const bool off = getenv("APUS_NO_BRANCH") && getenv("APUS_NO_BRANCH")[0] == '1';
@@ -114,6 +119,7 @@ cudaStream_t branch_begin(cudaStream_t main, int i) {
         cudaGetLastError();
         return main;                            // no side stream: the chain simply runs in line
     }
+    g_aux_owner[i] = main;
     return c.aux[i];
 }
 int branch_end(int i, cudaStream_t main) {
@@ -323,11 +329,22 @@ unsigned long long sum_order_epoch() { return g_sum_epoch; }
 int stream_scratch(cudaStream_t st, size_t bytes, void **ws, size_t n_counters, int **counters) {
     struct Slot { DevBuf ws, cnt; };
     static std::mutex mu;
-    static std::map<std::pair<int, cudaStream_t>, Slot> slots;
+    static std::map<std::tuple<int, cudaStream_t, int>, Slot> slots;
     int dev = 0;
     APUS_CUDA_OK(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
-    Slot &s = slots[{dev, st}];
+    // the stream the entry points without a stream argument run on is ONE chain whichever handle it
+    // has at the moment (apus_cuda_use_stream lets a caller swap it, e.g. for a stream capture):
+    // its scratch goes with the role, not with the handle
+    // A side stream works for one main chain at a time, and recorded steps of different chains
+    // (models stepping side by side) run concurrently whatever stream they were recorded on: a side
+    // chain's scratch belongs to (the main chain it branched from, which branch).
+    cudaStream_t owner = st;
+    int branch = 0;
+    for (int i = 0; i < Ctx::N_AUX; i++)
+        if (st == ctx().aux[i] && g_aux_owner[i]) { owner = g_aux_owner[i]; branch = i + 1; }
+    const cudaStream_t key = owner == ctx().stream ? reinterpret_cast<cudaStream_t>(~(uintptr_t)0) : owner;
+    Slot &s = slots[std::make_tuple(dev, key, branch)];
     if (bytes > s.ws.cap) {
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
         cudaStreamIsCapturing(st, &cs);

@@ -127,9 +127,14 @@ static int experts_run_tc(ApusCudaMoe *m, const float *xrows, const int32_t *rou
     a.groups = m->b_t13.as<TcGroup>(); a.n_groups_dev = ng; a.n_groups = max_groups;
     a.O = inter; a.K = dim; a.pair = 1; a.limit = m->limit; a.out = m->b_h.as<float>();
     a.total_rows = n_rout;
+    // the gate/up kernel quantises its SwiGLU outputs for the down projection in its epilogue
+    // (unless K is split, when the outputs only exist after the chunks are added)
+    static const bool fuse_hq = !(getenv("APUS_FUSE_HQ") && getenv("APUS_FUSE_HQ")[0] == '0');
+    const bool split = getenv("APUS_TC_KSPLIT") && atoi(getenv("APUS_TC_KSPLIT")) > 1;
+    if (fuse_hq && !split) { a.q_out = m->b_hq.as<uint8_t>(); a.qs_out = m->b_hs.as<float>(); }
     if (m->mark(st) || gemm_tc(a, st) || m->mark(st)) return 1;
-    if (act_quant(m->b_h.as<float>(), nullptr, n_rout, inter, m->b_hq.as<uint8_t>(), m->b_hs.as<float>(),
-                  ng + 1, st))
+    if (!a.q_out && act_quant(m->b_h.as<float>(), nullptr, n_rout, inter, m->b_hq.as<uint8_t>(), m->b_hs.as<float>(),
+                              ng + 1, st))
         return 1;
     TcArgs b = {};
     b.map_a = m->map_w2; b.map_b = m->map_w2; b.map_x = m->map_hq;

@@ -213,7 +213,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (PAIR) tmem_ld32(tmem + lane_base + TC_COL_D1, d1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             const int o = (int)blockIdx.x * 128 + tid;
-            if (o < O && S == 1) {
+            if (PAIR && S == 1 && a.q_out) {
+                // The SwiGLU outputs feed the down projection, whose activation quantisation works on 128
+                // consecutive elements of a row (c/fp4.h:293-321): exactly this tile's 128 outputs of
+                // one token.  Quantise here (amax over the four epilogue warps, power-of-two scale,
+                // hardware E4M3 conversion -- the arithmetic of act_quant_kernel, hence its bits) and
+                // write codes + scales instead of the f32 values and a separate launch.
+                float *s_amax = reinterpret_cast<float *>(smem);       // [4][TC_N]: the stages are idle by now
+                float hv[TC_N];
+#pragma unroll
+                for (int n = 0; n < TC_N; n++) {
+                    if (n >= nrows) break;                 // a work item at decode sizes holds one to three rows
+                    hv[n] = swiglu_tc(__uint_as_float(d0[n]), __uint_as_float(d1[n]), a.limit);
+                    const float m = warp_max(fabsf(hv[n]));
+                    if (lane == 0) s_amax[warp * TC_N + n] = m;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int nab = O >> 7;
+#pragma unroll
+                for (int n = 0; n < TC_N; n++) {
+                    if (n >= nrows) break;
+                    float amax = fmaxf(fmaxf(s_amax[n], s_amax[TC_N + n]), fmaxf(s_amax[2 * TC_N + n], s_amax[3 * TC_N + n]));
+                    amax = fmaxf(amax, 1e-4f);
+                    const float sc = ceil_pow2(__fmul_rn(amax, 1.0f / 448.0f));
+                    const float inv = __uint_as_float(0x7f000000u - __float_as_uint(sc));
+                    a.q_out[(size_t)(row0 + n) * O + o] = (uint8_t)(e4m3x2_from_f32(hv[n] * inv, 0.f) & 0xffu);
+                    if (tid == 0) a.qs_out[(size_t)(row0 + n) * nab + blockIdx.x] = sc;
+                }
+            } else if (o < O && S == 1) {
 #pragma unroll
                 for (int n = 0; n < TC_N; n++) {
                     if (n >= nrows) break;

@@ -181,6 +181,22 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             mbar_arrive(&acc_empty[b]);                // the tensor core may overwrite this accumulator
             const float wsa = s_ws[i], wsb = PAIR ? s_ws[NC + i] : 0.f;
             const float4 *as4 = reinterpret_cast<const float4 *>(s_as + (size_t)i * T8_N);
+            if (S > 1) {
+                // K split: park this block's TERM dot * (as * ws) for every live row; the CTA that
+                // finishes last adds all blocks' terms in block order -- the same values in the same
+                // order as the single fold below, hence the same bits
+                const int o = tile_row + tid;
+                if (o < O) {
+                    float *pa = a.part + ((size_t)i * M + row0) * O + o;
+                    float *pb2 = a.part + ((size_t)(NC + i) * M + row0) * O + o;
+                    for (int n = 0; n < nrows; n++) {
+                        const float sv = s_as[(size_t)i * T8_N + n];
+                        pa[(size_t)n * O] = __fmul_rn(__uint_as_float(d0[n]), __fmul_rn(sv, wsa));
+                        if (PAIR) pb2[(size_t)n * O] = __fmul_rn(__uint_as_float(d1[n]), __fmul_rn(sv, wsb));
+                    }
+                }
+                continue;
+            }
 #pragma unroll
             for (int q = 0; q < T8_N / 4; q++) {
                 const float4 s4 = as4[q];
@@ -208,16 +224,7 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     a.out[(size_t)(row0 + n) * O + o] = v;
                 }
             } else if (o < O) {
-                // K split: park this chunk's folded sums, part[(matrix, chunk)][row][o]
-                float *pa = a.part + ((size_t)z * M) * O;
-                float *pb2 = a.part + ((size_t)(S + z) * M) * O;
-#pragma unroll
-                for (int n = 0; n < T8_N; n++) {
-                    if (n >= nrows) break;
-                    pa[(size_t)(row0 + n) * O + o] = accA[n];
-                    if (PAIR) pb2[(size_t)(row0 + n) * O + o] = accB[n];
-                }
-                __threadfence();
+                __threadfence();                       // this chunk's block terms are parked (fold loop above)
             }
         }
     }
@@ -226,7 +233,7 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         atomicCAS(&g_tc8_status, 0, fail);
     }
     if (S > 1) {
-        // the chunk that arrives last at this output tile adds the chunks in chunk order and finishes the row
+        // the chunk that arrives last at this output tile adds every block's term in block order and finishes the rows
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (tid == 0 && !*s_abort) {
@@ -240,9 +247,9 @@ gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (*s_last && tid < 128 && o < O) {
             for (int n = 0; n < nrows; n++) {
                 float va = 0.f, vb = 0.f;
-                for (int c = 0; c < S; c++) {
+                for (int c = 0; c < NC; c++) {
                     va = __fadd_rn(va, __ldcg(a.part + ((size_t)c * M + row0 + n) * O + o));
-                    if (PAIR) vb = __fadd_rn(vb, __ldcg(a.part + ((size_t)(S + c) * M + row0 + n) * O + o));
+                    if (PAIR) vb = __fadd_rn(vb, __ldcg(a.part + ((size_t)(NC + c) * M + row0 + n) * O + o));
                 }
                 float v;
                 if (PAIR) v = swiglu8(va, vb, a.limit);
@@ -462,12 +469,14 @@ int gemm_tc8(const Tc8Args &a0, cudaStream_t st) {
     if (a.M <= 0) return 0;
     long long ctas = (long long)(a.O / 128) * ((a.M + T8_N - 1) / T8_N);
     // A matrix with fewer output tiles than SMs streams on a few SMs only (each pulls ~25-45
-    // GB/s): split K over grid.z so that most SMs take part.  Every chunk folds its blocks in
-    // order; the chunk sums are added in chunk order by the CTA that finishes last -- a
-    // deterministic result, but not the bits of the single in-order fold, hence tied to the
-    // tree-order setting (apus_cuda_set_tree_ops).
+    // GB/s): with few activation rows K is split over grid.z so that most SMs take part.  A chunk
+    // does not fold: it parks every block's term dot * (as * ws); the CTA that finishes last adds
+    // all terms in block order, which is the single in-order fold value for value -- the same
+    // bits, whatever the split (so it needs no sum-order setting and a row's result does not
+    // depend on the batch it is in).  Bounded to M <= 8 by the size of the parked terms.
     a.ksplit = 1;
-    if (sum_tree(APUS_CUDA_TREE_FP8_SPLITK) && ctas < 74) {
+    static const bool split_on = !(getenv("APUS_FP8_KSPLIT") && getenv("APUS_FP8_KSPLIT")[0] == '0');
+    if (split_on && a.M <= 8 && ctas < 74) {
         const int NC = a.K >> 7;
         int S = (int)(148 / ctas);
         if (S > NC) S = NC;
@@ -475,7 +484,7 @@ int gemm_tc8(const Tc8Args &a0, cudaStream_t st) {
         if (S > 1) {
             void *ws = nullptr;
             int *cnt = nullptr;
-            if (stream_scratch(st, (size_t)S * (a.pair ? 2 : 1) * a.M * a.O * 4, &ws, (size_t)ctas, &cnt)) return 1;
+            if (stream_scratch(st, (size_t)NC * (a.pair ? 2 : 1) * a.M * a.O * 4, &ws, (size_t)ctas, &cnt)) return 1;
             a.ksplit = S; a.part = (float *)ws; a.counters = cnt;
             ctas *= S;
         }

@@ -76,6 +76,8 @@ struct TcArgs {
     const int *orow;                     // nullable: output row of sorted position p
     float *out;
     int tx_bytes;                        // 0 = default transaction bytes per stage
+    uint8_t *q_out;                      // pair mode, optional: write the outputs quantised for the next GEMM
+    float *qs_out;                       //   (E4M3 codes [rows, O] + scales [rows, O/128], sorted order) instead of `out`
     int total_rows;                      // activation rows over all work items (0: unknown, K is never split)
     int ksplit;                          // set by gemm_tc: K chunks (grid.z); > 1 uses part + counters
     float *part;                         // [(pair ? 2 : 1) * ksplit, total_rows, O] chunk sums
@@ -95,7 +97,7 @@ struct Tc8Args {
     float limit;
     float *out;                          // [M, O]
     int ksplit;                          // set by gemm_tc8: K chunks (grid.z); > 1 uses part + counters
-    float *part;                         // [(pair ? 2 : 1) * ksplit, M, O] chunk sums
+    float *part;                         // [(pair ? 2 : 1) * K/128, M, O] per-block terms
     int *counters;                       // zeroed, one per (output tile, row group); left zeroed
 };
 int gemm_tc8(const Tc8Args &a, cudaStream_t st);

@@ -204,8 +204,8 @@ int apus_cuda_kernel_status(int reset);
 #define APUS_CUDA_TREE_COMPRESSOR 32   /* compressor wkv / wgate projections (c/attn.h:892-1011) */
 #define APUS_CUDA_TREE_IDX_WPROJ 64    /* indexer weights projection (c/attn.h:1105-1168) */
 #define APUS_CUDA_TREE_LINEAR   128    /* apus_cuda_f32_linear / the f32_linear hook */
-#define APUS_CUDA_TREE_FP8_SPLITK 256  /* FP8 matrices with few output tiles: K split over CTAs, chunk sums
-                                          added in chunk order (c/fp8.h:166-218 folds all blocks in one chain) */
+#define APUS_CUDA_TREE_FP8_SPLITK 256  /* reserved (the FP8 K split adds the per-block terms in block order: the
+                                          bits of the single fold, c/fp8.h:166-218, so it needs no setting) */
 #define APUS_CUDA_TREE_ALL      511
 /* The classes in tree order when nothing else is asked for: those the reference's own
  * ARM build sums in another order than its scalar code (the mHC map dots and sum of
