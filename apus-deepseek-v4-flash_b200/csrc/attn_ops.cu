@@ -124,6 +124,92 @@ row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y,
     if (on) y[(size_t)row * y_stride + i] = v;
 }
 
+// Two frequent shapes of the row pipeline on MANY rows (every head of every sequence) get kernels
+// of their own; same operations, same order, same bits as row_ops_kernel.
+// (a) RoPE only, in place: only the last rd elements of a row change -- one thread per pair.
+__global__ void __launch_bounds__(256)
+rope_rows_kernel(float *__restrict__ y, int stride, int n, int rows, int inverse, int rd, const float *__restrict__ cs,
+                 int rows_per_cs, int cs_stride, const RowDyn dyn) {
+    if (dyn.pos && cs) {
+        const long long r = *dyn.pos + dyn.cs_bias;
+        cs += (r > 0 ? r : 0) * rd;
+    }
+    const int half = rd >> 1;
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)rows * half) return;
+    const int row = (int)(t / half), i = (int)(t - (long long)row * half);
+    const float *c = cs + (size_t)(row / rows_per_cs) * cs_stride;
+    const float co = c[i], si = inverse ? -c[half + i] : c[half + i];
+    float2 *p = reinterpret_cast<float2 *>(y + (size_t)row * stride + n - rd) + i;
+    const float2 v = *p;
+    *p = make_float2(bf16_round(__fsub_rn(__fmul_rn(v.x, co), __fmul_rn(v.y, si))),
+                     bf16_round(__fadd_rn(__fmul_rn(v.x, si), __fmul_rn(v.y, co))));
+}
+// (b) weight-free RMSNorm + RoPE (the per-head q rows, c/attn.h:1356-1370): one warp per row, eight
+// rows per CTA; the sum of squares in the reference's order is one lane's walk over the warp's
+// squares in shared memory, otherwise a warp reduction.
+template <int NV>                                  // NV float4 per lane: n = 128 * NV
+__global__ void __launch_bounds__(256)
+qnorm_rope_rows_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y, int y_stride, int rows,
+                       float eps, int rd, int seq, const float *__restrict__ cs, int rows_per_cs, int cs_stride,
+                       const RowDyn dyn) {
+    constexpr int N = 128 * NV;
+    __shared__ __align__(16) float s_sq[8][N];
+    if (dyn.pos && cs) {
+        const long long r = *dyn.pos + dyn.cs_bias;
+        cs += (r > 0 ? r : 0) * rd;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + warp;
+    if (row >= rows) return;
+    float4 v[NV];
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * x_stride);
+#pragma unroll
+    for (int j = 0; j < NV; j++) v[j] = xr[lane + 32 * j];
+    float tot;
+    if (seq) {
+        float4 *sq = reinterpret_cast<float4 *>(s_sq[warp]);
+#pragma unroll
+        for (int j = 0; j < NV; j++)
+            sq[lane + 32 * j] = make_float4(__fmul_rn(v[j].x, v[j].x), __fmul_rn(v[j].y, v[j].y),
+                                            __fmul_rn(v[j].z, v[j].z), __fmul_rn(v[j].w, v[j].w));
+        __syncwarp();
+        tot = lane == 0 ? seq_sum_smem(s_sq[warp], N, 0.f) : 0.f;
+        tot = __shfl_sync(0xffffffffu, tot, 0);
+    } else {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; j++)
+            ss += __fmul_rn(v[j].x, v[j].x) + __fmul_rn(v[j].y, v[j].y) + __fmul_rn(v[j].z, v[j].z) + __fmul_rn(v[j].w, v[j].w);
+        tot = warp_sum(ss);
+    }
+    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)N), eps)));
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        v[j].x = bf16_round(__fmul_rn(v[j].x, inv)); v[j].y = bf16_round(__fmul_rn(v[j].y, inv));
+        v[j].z = bf16_round(__fmul_rn(v[j].z, inv)); v[j].w = bf16_round(__fmul_rn(v[j].w, inv));
+    }
+    // RoPE on the last rd elements: element e = 4 * (lane + 32 * j) + c; a float4 holds two pairs
+    const int half = rd >> 1;
+    const float *c = cs + (size_t)(row / rows_per_cs) * cs_stride;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const int e = 4 * (lane + 32 * j) - (N - rd);          // offset inside the rotated tail
+        if (e >= 0) {
+            const int i0 = e >> 1;
+            const float c0 = c[i0], s0 = c[half + i0], c1 = c[i0 + 1], s1 = c[half + i0 + 1];
+            const float4 w = v[j];
+            v[j].x = bf16_round(__fsub_rn(__fmul_rn(w.x, c0), __fmul_rn(w.y, s0)));
+            v[j].y = bf16_round(__fadd_rn(__fmul_rn(w.x, s0), __fmul_rn(w.y, c0)));
+            v[j].z = bf16_round(__fsub_rn(__fmul_rn(w.z, c1), __fmul_rn(w.w, s1)));
+            v[j].w = bf16_round(__fadd_rn(__fmul_rn(w.z, s1), __fmul_rn(w.w, c1)));
+        }
+    }
+    float4 *yr = reinterpret_cast<float4 *>(y + (size_t)row * y_stride);
+#pragma unroll
+    for (int j = 0; j < NV; j++) yr[lane + 32 * j] = v[j];
+}
+
 int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
             const float *norm_w, float eps, int rd, const float *cs, int rows_per_cs, int cs_stride,
             cudaStream_t st, const RowDyn *dyn) {
@@ -133,6 +219,28 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
     size_t smem = (size_t)(n + 64) * sizeof(float);
     if (!sum_tree(APUS_CUDA_TREE_NORMS)) flags |= ROW_SEQ_SUM;
     const RowDyn none = {nullptr, 0, 0, 0};
+    const bool no_gate = !dyn || dyn->gate_ratio == 0;
+    const int base = flags & ~ROW_SEQ_SUM;
+    if (rows >= 32 && no_gate && cs && rd % 4 == 0 && rd <= n && (base == ROW_ROPE || base == ROW_ROPE_INV) && x == y &&
+        x_stride == y_stride && x_stride % 2 == 0 && (n - rd) % 2 == 0) {
+        const long long pairs = (long long)rows * (rd / 2);
+        rope_rows_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, y_stride, n, rows, base == ROW_ROPE_INV, rd, cs,
+                                                                         rows_per_cs > 0 ? rows_per_cs : 1, cs_stride,
+                                                                         dyn ? *dyn : none);
+        APUS_LAUNCHED();
+        return 0;
+    }
+    if (rows >= 32 && no_gate && cs && base == (ROW_RMS_PLAIN | ROW_ROPE) && (n == 512 || n == 256 || n == 128) &&
+        rd % 4 == 0 && rd <= n && x_stride % 4 == 0 && y_stride % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0) {
+        const unsigned g = (unsigned)((rows + 7) / 8);
+        const int seq = (flags & ROW_SEQ_SUM) ? 1 : 0, rpc = rows_per_cs > 0 ? rows_per_cs : 1;
+        const RowDyn d = dyn ? *dyn : none;
+        if (n == 512) qnorm_rope_rows_kernel<4><<<g, 256, 0, st>>>(x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
+        else if (n == 256) qnorm_rope_rows_kernel<2><<<g, 256, 0, st>>>(x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
+        else qnorm_rope_rows_kernel<1><<<g, 256, 0, st>>>(x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
+        APUS_LAUNCHED();
+        return 0;
+    }
     row_ops_kernel<<<rows, n, smem, st>>>(x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
                                           rows_per_cs > 0 ? rows_per_cs : 1, cs_stride, dyn ? *dyn : none);
     APUS_LAUNCHED();
