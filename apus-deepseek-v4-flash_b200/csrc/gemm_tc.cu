@@ -387,7 +387,15 @@ int gemm_tc(const TcArgs &a0, cudaStream_t st) {
             a.ksplit = S; a.part = (float *)ws; a.counters = cnt;
         }
     }
-    return a.pair ? launch_tc<true, 3>(a, st) : launch_tc<false, 5>(a, st);
+    static const int pns = getenv("APUS_TC_PAIR_NS") ? atoi(getenv("APUS_TC_PAIR_NS")) : 3;
+    if (a.pair) return pns == 2 ? launch_tc<true, 2>(a, st) : launch_tc<true, 3>(a, st);
+    // single matrix (the down projection, K = 2048: 16 chunks per CTA): the K loop is short, so the
+    // fill and drain of a CTA's ring weigh as much as its steady state; a shallower ring lets more
+    // CTAs share an SM (shared memory is what bounds them) and overlap each other's ends
+    static const int ns = getenv("APUS_TC_DOWN_NS") ? atoi(getenv("APUS_TC_DOWN_NS")) : 3;
+    if (ns == 2) return launch_tc<false, 2>(a, st);
+    if (ns == 3) return launch_tc<false, 3>(a, st);
+    return launch_tc<false, 5>(a, st);
 }
 
 // Status word of the bounded waits (0 = no failure since the last reset).
