@@ -244,6 +244,8 @@ def load(path=LIB_PATH):
         "apus_cuda_model_reset": (ci, [vp]),
         "apus_cuda_model_pos": (i64, [vp]),
         "apus_cuda_model_moe": (vp, [vp, ci]),
+        "apus_cuda_model_info": (ci, [vp, C.POINTER(ci), C.POINTER(ci), C.POINTER(ci), C.POINTER(ci)]),
+        "apus_cuda_serve": (ci, [vp, ci, ci, ci]),
         "apus_cuda_model_use_graph": (ci, [vp, ci]),
         "apus_cuda_model_set_sampling": (ci, [vp, cf, cf, C.c_uint64]),
         "apus_cuda_sample_logits_u": (ci, [vp, C.c_size_t, cf, cf, vp, vp, ci]),

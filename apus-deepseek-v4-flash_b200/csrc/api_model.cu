@@ -536,6 +536,15 @@ int apus_cuda_block_forward_v(const ApusCudaLayerDesc *d, int hc, int iters, flo
 
 int64_t apus_cuda_model_pos(const ApusCudaModel *m) { return m ? m->pos : -1; }
 
+int apus_cuda_model_info(const ApusCudaModel *m, int *batch, int *max_pos, int *vocab, int *n_layers) {
+    if (!m) { set_error("NULL model"); return 1; }
+    if (batch) *batch = m->B;
+    if (max_pos) *max_pos = m->max_pos;
+    if (vocab) *vocab = m->vocab;
+    if (n_layers) *n_layers = m->n_layers;
+    return 0;
+}
+
 int apus_cuda_model_set_sampling(ApusCudaModel *m, float temp, float top_p, uint64_t seed) {
     if (!m) { set_error("NULL model"); return 1; }
     cudaStream_t st = mstream(m);
@@ -606,13 +615,24 @@ static int group_check(ApusCudaModel *const *ms, int n, const char *who) {
     return 0;
 }
 
+// Token ids index the embedding table (and the hash-routing table): one outside [0, vocab) is
+// refused on the host, where the reference would read past its table (c/model.h:663-671).
+static int ids_in_range(const ApusCudaModel *m, const int64_t *ids, size_t n, const char *what) {
+    for (size_t i = 0; i < n; i++)
+        APUS_REQUIRE(ids[i] >= 0 && ids[i] < m->vocab, "%s: token id %lld at index %zu is outside [0, %d)", what,
+                     (long long)ids[i], i, m->vocab);
+    return 0;
+}
+
 int apus_cuda_model_forward_group(ApusCudaModel *const *ms, int n, const int64_t *const *ids, int s,
                                   float *const *logits, int32_t *const *next) {
     if (group_check(ms, n, "model_forward")) return 1;
     if (s <= 0) return 0;
-    for (int i = 0; i < n; i++)
+    for (int i = 0; i < n; i++) {
         APUS_REQUIRE(ms[i]->pos + s <= ms[i]->max_pos, "model_forward: position %lld + %d exceeds max_pos %d",
                      ms[i]->pos, s, ms[i]->max_pos);
+        if (ids_in_range(ms[i], ids[i], (size_t)ms[i]->B * s, "model_forward")) return 1;
+    }
     std::vector<std::vector<int64_t>> col((size_t)n);
     for (int t = 0; t < s; t++) {
         for (int i = 0; i < n; i++) {
@@ -650,6 +670,7 @@ int apus_cuda_model_forward_all(ApusCudaModel *m, const int64_t *ids, int s, flo
     if (!m) { set_error("NULL model"); return 1; }
     if (s <= 0) return 0;
     APUS_REQUIRE(m->pos + s <= m->max_pos, "model_forward: position %lld + %d exceeds max_pos %d", m->pos, s, m->max_pos);
+    if (ids_in_range(m, ids, (size_t)m->B * s, "model_forward_all")) return 1;
     cudaStream_t st = mstream(m);
     const size_t B = m->B, V = m->vocab;
     std::vector<int64_t> cols((size_t)s * B);
@@ -677,9 +698,11 @@ int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n, const int64_
                                    int n_gen, int32_t *const *out_tokens, float *ms_prefill, float *ms_decode) {
     if (group_check(ms, n, "model_generate")) return 1;
     APUS_REQUIRE(n_prompt >= 1 && n_gen >= 1, "model_generate: needs a prompt and at least one token to generate");
-    for (int i = 0; i < n; i++)
+    for (int i = 0; i < n; i++) {
         APUS_REQUIRE(ms[i]->pos + n_prompt + n_gen - 1 <= ms[i]->max_pos, "model_generate: %d + %d tokens exceed max_pos %d",
                      n_prompt, n_gen, ms[i]->max_pos);
+        if (ids_in_range(ms[i], prompts[i], (size_t)ms[i]->B * n_prompt, "model_generate")) return 1;
+    }
     cudaEvent_t e0, e1, e2, tmp[16];
     APUS_CUDA_OK(cudaEventCreate(&e0)); APUS_CUDA_OK(cudaEventCreate(&e1)); APUS_CUDA_OK(cudaEventCreate(&e2));
     for (int i = 0; i < n; i++) APUS_CUDA_OK(cudaEventCreateWithFlags(&tmp[i], cudaEventDisableTiming));

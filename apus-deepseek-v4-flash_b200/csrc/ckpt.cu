@@ -889,4 +889,165 @@ int apus_cuda_ckpt_layer_digest(ApusCudaCkpt *c, int layer, int e_lo, int e_hi, 
 uint64_t apus_cuda_ckpt_read_count(const ApusCudaCkpt *c) { return c ? c->reads.load() : 0; }
 uint64_t apus_cuda_ckpt_read_bytes(const ApusCudaCkpt *c) { return c ? c->read_bytes.load() : 0; }
 
+
+// ---- NDJSON serve loop (reference c/apus.c:451-662, `apus serve`) -------------------------------
+// One JSON object per line in, one per line out; every response carries the request's "id" and a
+// "type".  generate: {"id", "cmd":"generate", "ids":[...], "max_tokens", "temperature", "top_p",
+// "seed"} -> {"type":"prompt","prompt_tokens"}, one {"type":"token","token_id"} per emitted token,
+// {"type":"done","finish_reason","prompt_tokens","completion_tokens","text"}.  The reference's
+// defaults and clamps are kept (max_tokens 32, temperature 1, top_p 1, seed 0; the prompt must be
+// shorter than max_pos and the completion is cut to fit; the end-of-sequence token ends the
+// completion with finish_reason "stop" and is not emitted).  The tokenizer is outside this library,
+// so "text" / "messages" prompts and "encode" get the reference's "no tokenizer in model dir" error
+// and tokens carry no text; a front end that speaks ids (the reference's tools/server.py does when
+// the engine reports no tokenizer) works unchanged.
 }  // extern "C"
+
+namespace apus {
+namespace {
+
+void json_dump(const JV &v, std::string *o) {
+    char buf[64];
+    switch (v.kind) {
+    case JV::NUL: *o += "null"; break;
+    case JV::BOOL: *o += v.b ? "true" : "false"; break;
+    case JV::NUM:
+        if (v.num == (double)(long long)v.num && fabs(v.num) < 9e15) snprintf(buf, sizeof buf, "%lld", (long long)v.num);
+        else snprintf(buf, sizeof buf, "%.17g", v.num);
+        *o += buf;
+        break;
+    case JV::STR:
+        *o += '"';
+        for (unsigned char c : v.str) {
+            if (c == '"' || c == '\\') { *o += '\\'; *o += (char)c; }
+            else if (c == '\n') *o += "\\n";
+            else if (c == '\r') *o += "\\r";
+            else if (c == '\t') *o += "\\t";
+            else if (c < 0x20) { snprintf(buf, sizeof buf, "\\u%04x", c); *o += buf; }
+            else *o += (char)c;
+        }
+        *o += '"';
+        break;
+    case JV::ARR:
+        *o += '[';
+        for (size_t i = 0; i < v.arr.size(); i++) { if (i) *o += ','; json_dump(v.arr[i], o); }
+        *o += ']';
+        break;
+    case JV::OBJ:
+        *o += '{';
+        for (size_t i = 0; i < v.obj.size(); i++) {
+            if (i) *o += ',';
+            JV k; k.kind = JV::STR; k.str = v.obj[i].first;
+            json_dump(k, o); *o += ':'; json_dump(v.obj[i].second, o);
+        }
+        *o += '}';
+        break;
+    }
+}
+
+struct Serve {
+    ApusCudaModel *m;
+    int out_fd, eos, max_pos;
+    // {"id":<id>,"type":"<type>"<rest>}\n, written in one piece
+    void send(const JV *id, const char *type, const std::string &rest) {
+        std::string s = "{\"id\":";
+        if (id) json_dump(*id, &s); else s += "null";
+        s += ",\"type\":\""; s += type; s += "\"" + rest + "}\n";
+        size_t done = 0;
+        while (done < s.size()) {
+            ssize_t w = write(out_fd, s.data() + done, s.size() - done);
+            if (w <= 0) return;
+            done += (size_t)w;
+        }
+    }
+    void error(const JV *id, const char *msg) {
+        JV t; t.kind = JV::STR; t.str = msg;
+        std::string r = ",\"message\":";
+        json_dump(t, &r);
+        send(id, "error", r);
+    }
+    void generate(const JV &req, const JV *id) {
+        const JV *jids = req.get("ids");
+        if (!jids || jids->kind != JV::ARR) {
+            if ((req.get("text") && req.get("text")->kind == JV::STR) || req.get("messages")) error(id, "no tokenizer in model dir");
+            else error(id, "generate needs messages, text, or ids");
+            return;
+        }
+        std::vector<int64_t> ids;
+        for (const JV &v : jids->arr) {
+            if (v.kind != JV::NUM) { error(id, "ids must be an array of numbers"); return; }
+            ids.push_back((int64_t)v.num);
+        }
+        if (ids.empty()) { error(id, "empty prompt"); return; }
+        int max_tokens = 32;
+        double temperature = 1.0, top_p = 1.0;
+        uint64_t seed = 0;
+        const JV *v;
+        if ((v = req.get("max_tokens")) && v->kind == JV::NUM) max_tokens = (int)v->num;
+        if (max_tokens < 0) max_tokens = 0;
+        if ((v = req.get("temperature")) && v->kind == JV::NUM) temperature = v->num;
+        if ((v = req.get("top_p")) && v->kind == JV::NUM) top_p = v->num;
+        if ((v = req.get("seed")) && v->kind == JV::NUM) seed = (uint64_t)v->num;
+        if ((int64_t)ids.size() >= max_pos) { error(id, "prompt too long for model max_pos"); return; }
+        if ((int64_t)ids.size() + max_tokens > max_pos) max_tokens = (int)(max_pos - (int64_t)ids.size());
+        char buf[96];
+        snprintf(buf, sizeof buf, ",\"prompt_tokens\":%zu", ids.size());
+        send(id, "prompt", buf);
+        int completion = 0;
+        const char *finish = "length";
+        bool ok = apus_cuda_model_reset(m) == 0 && apus_cuda_model_set_sampling(m, (float)temperature, (float)top_p, seed) == 0;
+        int32_t t = 0;
+        // the pick after the prompt, then one step per emitted token (c/apus.c:541-585)
+        if (ok && max_tokens > 0) ok = apus_cuda_model_forward(m, ids.data(), (int)ids.size(), nullptr, &t) == 0;
+        for (int step = 0; ok && step < max_tokens; step++) {
+            if (t == eos) { finish = "stop"; break; }
+            completion++;
+            snprintf(buf, sizeof buf, ",\"token_id\":%d", (int)t);
+            send(id, "token", buf);
+            if (step + 1 < max_tokens) {
+                const int64_t next = t;
+                ok = apus_cuda_model_forward(m, &next, 1, nullptr, &t) == 0;
+            }
+        }
+        if (!ok) { error(id, apus_cuda_last_error()); return; }
+        snprintf(buf, sizeof buf, "\",\"prompt_tokens\":%zu,\"completion_tokens\":%d,\"text\":\"\"", ids.size(), completion);
+        send(id, "done", std::string(",\"finish_reason\":\"") + finish + buf);
+    }
+};
+
+}  // namespace
+}  // namespace apus
+
+extern "C" int apus_cuda_serve(ApusCudaModel *m, int in_fd, int out_fd, int eos_id) {
+    int batch = 0, max_pos = 0;
+    if (apus_cuda_model_info(m, &batch, &max_pos, nullptr, nullptr)) return 1;
+    APUS_REQUIRE(batch == 1, "serve: the model must hold one sequence (batch %d given)", batch);
+    Serve sv = {m, out_fd, eos_id, max_pos};
+    std::string pending;
+    char chunk[4096];
+    for (;;) {
+        size_t nl;
+        while ((nl = pending.find('\n')) == std::string::npos) {
+            ssize_t r = read(in_fd, chunk, sizeof chunk);
+            if (r <= 0) {                               // end of input: a last line without a newline still counts
+                if (pending.empty()) return 0;
+                pending += '\n';
+                continue;
+            }
+            pending.append(chunk, (size_t)r);
+        }
+        std::string line = pending.substr(0, nl);
+        pending.erase(0, nl + 1);
+        if (line.find_first_not_of(" \t\r") == std::string::npos) continue;
+        JV req;
+        std::string perr;
+        if (!json_parse(line.data(), line.size(), &req, &perr) || req.kind != JV::OBJ) {
+            sv.error(nullptr, "bad request line (not a JSON object)");
+            continue;
+        }
+        const JV *id = req.get("id"), *cmd = req.get("cmd");
+        if (cmd && cmd->kind == JV::STR && cmd->str == "generate") sv.generate(req, id);
+        else if (cmd && cmd->kind == JV::STR && cmd->str == "encode") sv.error(id, "no tokenizer in model dir");
+        else sv.error(id, "unknown cmd (want encode|generate)");
+    }
+}

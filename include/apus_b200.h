@@ -743,6 +743,18 @@ uint64_t apus_cuda_ckpt_read_bytes(const ApusCudaCkpt *c);
  * message in apus_cuda_last_error(). */
 ApusCudaModel *apus_cuda_model_load(const char *dir, int batch, int max_pos, int e_lo, int e_hi);
 
+/* Sizes of a model object (any pointer may be NULL). */
+int apus_cuda_model_info(const ApusCudaModel *m, int *batch, int *max_pos, int *vocab, int *n_layers);
+
+/* c/apus.c:451-662 `apus serve`: the newline-delimited JSON loop on file descriptors, until end of
+ * input.  Requests {"id", "cmd":"generate", "ids":[...], "max_tokens", "temperature", "top_p",
+ * "seed"}; responses {"id","type":"prompt"|"token"|"done"|"error", ...} with the reference's
+ * fields, defaults (32 tokens, temperature 1, top_p 1, seed 0), clamps and messages.  eos_id ends a
+ * completion ("finish_reason":"stop").  Text prompts, chat messages and "encode" need the
+ * tokenizer, which is outside this library: they get the reference's "no tokenizer in model dir"
+ * error, and tokens carry no text.  The model must hold one sequence. */
+int apus_cuda_serve(ApusCudaModel *m, int in_fd, int out_fd, int eos_id);
+
 /* No counterpart in the reference.  apus_cuda_hc_pre on device pointers for
  * callers that must not allocate device memory while they run (an engine whose
  * own arena already owns the HBM, a region where allocation is forbidden, a loop
