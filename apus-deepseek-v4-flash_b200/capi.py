@@ -204,6 +204,7 @@ def load(path=LIB_PATH):
                                     vp, vp, vp, C.POINTER(AttnInterm)]),
         "apus_cuda_set_sum_order": (ci, [ci]),
         "apus_cuda_set_tree_ops": (ci, [ci]),
+        "apus_cuda_set_prefill_chunk": (ci, [ci]),
         "apus_cuda_block_forward": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64]),
         "apus_cuda_block_forward_v": (ci, [C.POINTER(LayerDesc), ci, ci, cf, cf, C.POINTER(AttnS), vp, vp, ci, i64, i64]),
         "apus_cuda_model_create": (vp, [C.POINTER(ModelDesc), ci, ci]),

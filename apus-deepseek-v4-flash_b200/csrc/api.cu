@@ -20,9 +20,12 @@ void set_error(const char *fmt, ...) {
 }
 
 // ---- device buffers ------------------------------------------------------------------
+// A buffer that grows moves: steps recorded into CUDA graphs hold the old address.  Every such move
+// advances the epoch recorded steps are checked against (sum_order_epoch), so they are recorded again.
+static unsigned long long g_buf_moves = 0;
 int DevBuf::get(size_t bytes, void **out) {
     if (bytes > cap) {
-        if (p) { cudaDeviceSynchronize(); cudaFree(p); p = nullptr; cap = 0; }
+        if (p) { cudaDeviceSynchronize(); cudaFree(p); p = nullptr; cap = 0; g_buf_moves++; }
         size_t want = bytes + (bytes >> 2) + 256;
         APUS_CUDA_OK(cudaMalloc(&p, want));
         cap = want;
@@ -324,7 +327,19 @@ static int g_tree_ops = initial_tree_ops();
 static unsigned long long g_sum_epoch = 0;     // bumped whenever the order changes
 int sum_order() { return g_tree_ops == APUS_CUDA_TREE_ALL ? APUS_CUDA_SUM_TREE : APUS_CUDA_SUM_REFERENCE; }
 int tree_ops() { return g_tree_ops; }
-unsigned long long sum_order_epoch() { return g_sum_epoch; }
+unsigned long long sum_order_epoch() { return g_sum_epoch + g_buf_moves; }
+// s > 1 calls run as chunks of positions (one pass) unless switched off: APUS_PREFILL=0 or
+// apus_cuda_set_prefill_chunk(0) bring back one step per position
+static int g_chunk_rows = -1;
+int chunk_rows() {
+    if (g_chunk_rows < 0) {
+        const char *e = getenv("APUS_PREFILL");
+        g_chunk_rows = e && e[0] ? atoi(e) : 2048;
+        if (g_chunk_rows < 0) g_chunk_rows = 0;
+    }
+    return g_chunk_rows;
+}
+bool chunks_enabled() { return chunk_rows() > 0; }
 
 int stream_scratch(cudaStream_t st, size_t bytes, void **ws, size_t n_counters, int **counters) {
     struct Slot { DevBuf ws, cnt; };
@@ -427,6 +442,12 @@ int apus_cuda_set_tree_ops(int mask) {
         apus::g_sum_epoch++;               // recorded steps chose their kernels by the old setting
     }
     return apus::g_tree_ops;
+}
+
+int apus_cuda_set_prefill_chunk(int rows) {
+    const int before = apus::chunk_rows();
+    if (rows >= 0) apus::g_chunk_rows = rows;
+    return before;
 }
 
 int apus_cuda_set_sum_order(int order) {

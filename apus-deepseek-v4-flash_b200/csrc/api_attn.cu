@@ -281,6 +281,102 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     return qlinear_dev(A.wo_b, b.y, out, B, b.xq, b.xs, true, st);
 }
 
+// The compressor over a chunk: the two projections of every row at once, then the state machine
+// position by position (it is sequential in t by definition, c/attn.h:960-1008; a launch per
+// position on B CTAs) with the entries it completes appended as it goes.
+static int compressor_chunk(const CompDev &W, CompStateDev &S, const float *x, int B, int s, int dim, long long pos0,
+                            const float *cs_table, const StepBufs &b0, cudaStream_t st, bool second_set = false) {
+    StepBufs b = b0;
+    if (second_set) { b.ckv = b0.ckv2; b.csc = b0.csc2; b.pooled = b0.pooled2; }
+    const int cd = (1 + W.overlap) * W.d, T = B * s;
+    if (f32_linear(W.wkv, x, b.ckv, T, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st) ||
+        f32_linear(W.wgate, x, b.csc, T, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st))
+        return 1;
+    const int flags = ROW_BF16_IN | ROW_RMS_W | ROW_ROPE | ROW_BF16_OUT | (W.rotate ? (ROW_HADAMARD | ROW_FP4QAT) : ROW_FP8QAT);
+    for (int t = 0; t < s; t++) {
+        const long long pos = pos0 + t;
+        const int slot = (int)(pos % W.ratio), should = (pos + 1) % W.ratio == 0;
+        float *pooled = b.pooled + (size_t)t * B * W.d;
+        if (comp_step(S.kv.as<float>(), S.sc.as<float>(), (long long)S.carry, b.ckv + (size_t)t * B * cd,
+                      b.csc + (size_t)t * B * cd, cd, W.ape, W.ratio, W.overlap, W.d, slot, should, pooled, W.d, B, st))
+            return 1;
+        if (!should) continue;
+        APUS_REQUIRE(S.nb < S.cap, "compressed cache is full (%d entries)", S.cap);
+        if (row_ops(pooled, W.d, S.cache.as<float>() + (size_t)S.nb * W.d, S.cap * W.d, B, W.d, flags, W.norm, W.eps,
+                    W.rd, cs_table + (size_t)(pos + 1 - W.ratio) * W.rd, B, 0, st))
+            return 1;
+        S.nb++;
+    }
+    return 0;
+}
+
+int attn_chunk(const AttnDev &A, StateDev &S, const float *x, long long pos0, int s, const float *cs_table,
+               float *out, const StepBufs &b, cudaStream_t st) {
+    const ApusAttnCfg &c = A.cfg;
+    const int B = S.B, T = B * s;
+    const int h = c.n_heads, d = c.head_dim, rd = c.rope_dim, win = c.window, ratio = c.ratio;
+    const int hd = h * d;
+    const float *cs0 = cs_table + (size_t)pos0 * rd;       // row t of the chunk rotates by table row pos0 + t
+    APUS_REQUIRE(b.ext != nullptr, "attn_chunk: no window buffer");
+    if (act_quant(x, nullptr, T, c.dim, b.xq, b.xs, nullptr, st)) return 1;
+    // window KV rows (c/attn.h:1552-1569)
+    if (qgemm_dev(A.wkv, nullptr, b.xq, b.xs, T, b.kva, true, 0.f, st)) return 1;
+    if (row_ops(b.kva, d, b.kv, d, T, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd, cs0, B, rd, st))
+        return 1;
+    // q path (c/attn.h:1525-1548)
+    if (qgemm_dev(A.wq_a, nullptr, b.xq, b.xs, T, b.qa, true, 0.f, st)) return 1;
+    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, T, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st)) return 1;
+    if (act_quant(b.qr, nullptr, T, c.q_lora, b.xq2, b.xs2, nullptr, st)) return 1;
+    if (qgemm_dev(A.wq_b, nullptr, b.xq2, b.xs2, T, b.q, true, 0.f, st)) return 1;
+    if (row_ops(b.q, d, b.q, d, T * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs0, B * h, rd, st)) return 1;
+    // compressed entries and the ids each row may attend to (c/attn.h:1105-1168, 1660-1665): an entry is
+    // final once appended, and row t reads only the (pos0 + t + 1) / ratio entries complete at its position
+    int compcap = 0;
+    const int32_t *sel = nullptr;
+    if (ratio) {
+        if (compressor_chunk(A.comp, S.comp, x, B, s, c.dim, pos0, cs_table, b, st)) return 1;
+        const long long nb_end = (pos0 + s) / ratio;
+        if (c.has_indexer) {
+            const int ih = c.idx_heads, idm = c.idx_dim;
+            if (qgemm_dev(A.idx_wq_b, nullptr, b.xq2, b.xs2, T, b.iq, true, 0.f, st)) return 1;
+            if (row_ops(b.iq, idm, b.iq, idm, T * ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr, 0.f,
+                        rd, cs0, B * ih, rd, st))
+                return 1;
+            if (compressor_chunk(A.idx_comp, S.idx, x, B, s, c.dim, pos0, cs_table, b, st, true)) return 1;
+            if (f32_linear(A.idx_wproj, x, b.wt, T, c.dim, ih,
+                           APUS_CUDA_R_IN | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_IDX_WPROJ), st))
+                return 1;
+            const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
+            compcap = (int)(c.idx_topk < nb_end ? c.idx_topk : nb_end);
+            if (compcap > 0) {
+                if (idx_scores(b.iq, b.wt, wscale, S.idx.cache.as<float>(), (long long)S.idx.cap * idm, nb_end, ih, idm,
+                               b.scores, T, st, nullptr, ratio, pos0, B))
+                    return 1;
+                if (topk_stable(b.scores, (int)nb_end, compcap, b.sel, T, st, nullptr, ratio, pos0, B)) return 1;
+                sel = b.sel;
+            }
+        } else {
+            compcap = (int)nb_end;
+        }
+    }
+    // window candidates in position order, index rows, gathered attention, inverse RoPE
+    if (win_ext(b.ext, S.win.as<float>(), b.kv, win, s, d, B, pos0, st)) return 1;
+    if (build_idx_chunk(b.idxs, win, s, pos0, B, sel, compcap, ratio, st)) return 1;
+    const float scale = (float)pow((double)d, -0.5);
+    if (sparse_attn(b.q, A.sink, h, d, b.idxs, win + compcap, T, scale, b.ext, win + s, ratio ? S.comp.cache.p : nullptr,
+                    ratio ? S.comp.nb : 0, 0, b.o, st, (long long)(win + s) * d, ratio ? (long long)S.comp.cap * d : 0, b.sa,
+                    b.sa_cap, B))
+        return 1;
+    if (ring_update(S.win.as<float>(), b.kv, win, s, d, B, pos0, st)) return 1;
+    if (row_ops(b.o, d, b.o, d, T * h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs0, B * h, rd, st)) return 1;
+    // grouped low-rank o-projection (c/attn.h:1692-1737)
+    const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
+    if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, T, sub, ol,
+                           APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_WO_A), st))
+        return 1;
+    return qlinear_dev(A.wo_b, b.y, out, T, b.xq, b.xs, true, st);
+}
+
 static int upload_comp(const ApusCompS &h, CompStateDev &d, int extra, cudaStream_t st) {
     const size_t sb = (size_t)h.rows * h.cols * 4;
     d.carry = (size_t)h.rows * h.cols;
@@ -371,6 +467,61 @@ int apus_cuda_attention(const ApusAttnCfg *cfg, const ApusAttnW *w, ApusAttnS *s
     // state in
     const int extra = ratio ? s / ratio + 2 : 0;
     if (attn_state_upload(*cfg, st, g_state, extra, sm)) return 1;
+    if (s > 1 && chunks_enabled()) {
+        // one pass over the s positions; rope rows [p_lo, start_pos + s) staged as a table indexed by position
+        const long long p_lo = ratio && start_pos + 1 - ratio < 0 ? 0 : (ratio ? start_pos + 1 - ratio : start_pos);
+        const size_t n_cs = (size_t)(start_pos + s - p_lo);
+        std::vector<float> cs(n_cs * 2 * half);
+        for (size_t i = 0; i < n_cs; i++) {
+            memcpy(&cs[i * 2 * half], cos + (p_lo + (long long)i) * half, half * 4);
+            memcpy(&cs[i * 2 * half + half], sin + (p_lo + (long long)i) * half, half * 4);
+        }
+        StepBufs bc;
+        if (attn_step_bufs(*cfg, max_nb, s, g_ws, &bc)) return 1;
+        void *dcs, *dx, *dout, *dext;
+        if (g_ws[22].get(cs.size() * 4, &dcs) || g_ws[23].get((size_t)s * cfg->dim * 4, &dx) ||
+            g_ws[24].get((size_t)s * cfg->dim * 4, &dout) || g_ws[25].get((size_t)(win + s) * d * 4, &dext))
+            return 1;
+        bc.ext = (float *)dext;
+        APUS_CUDA_OK(cudaMemcpyAsync(dcs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, sm));
+        APUS_CUDA_OK(cudaMemcpyAsync(dx, x, (size_t)s * cfg->dim * 4, cudaMemcpyHostToDevice, sm));
+        const int nb0 = ratio ? st->comp.nb : 0, inb0 = (ratio && cfg->has_indexer) ? st->idx_comp.nb : 0;
+        // the table pointer is only ever dereferenced at rows >= p_lo
+        const float *table = (const float *)dcs - (ptrdiff_t)p_lo * 2 * half;
+        if (attn_chunk(A, g_state, (const float *)dx, start_pos, s, table, (float *)dout, bc, sm)) return 1;
+        if (interm) {
+            if (interm->q) APUS_CUDA_OK(cudaMemcpyAsync(interm->q, bc.q, (size_t)s * hd * 4, cudaMemcpyDeviceToHost, sm));
+            if (interm->win_kv) APUS_CUDA_OK(cudaMemcpyAsync(interm->win_kv, bc.kv, (size_t)s * d * 4, cudaMemcpyDeviceToHost, sm));
+            if (interm->attn_out) APUS_CUDA_OK(cudaMemcpyAsync(interm->attn_out, bc.o, (size_t)s * hd * 4, cudaMemcpyDeviceToHost, sm));
+            const long long nb_end = ratio ? (start_pos + s) / ratio : 0;
+            const int compcap = (int)(cfg->idx_topk < nb_end ? cfg->idx_topk : nb_end);
+            if (cfg->has_indexer && ratio) {
+                std::vector<int32_t> hsel((size_t)s * (compcap > 0 ? compcap : 1));
+                if (compcap > 0 && interm->idx_topk) {
+                    APUS_CUDA_OK(cudaMemcpyAsync(hsel.data(), bc.sel, (size_t)s * compcap * 4, cudaMemcpyDeviceToHost, sm));
+                    APUS_CUDA_OK(cudaStreamSynchronize(sm));
+                }
+                int idx_k = 0;
+                for (int t = 0; t < s; t++) {
+                    const long long nbs = (start_pos + t + 1) / ratio;
+                    idx_k = (int)(cfg->idx_topk < nbs ? cfg->idx_topk : nbs);
+                    if (interm->idx_topk)                 // ids as the attention sees them in a step: entry + window
+                        for (int j = 0; j < idx_k; j++) interm->idx_topk[(size_t)t * cfg->idx_topk + j] = hsel[(size_t)t * compcap + j] + win;
+                }
+                interm->idx_k = idx_k;
+            }
+        }
+        APUS_CUDA_OK(cudaMemcpyAsync(out, dout, (size_t)s * cfg->dim * 4, cudaMemcpyDeviceToHost, sm));
+        if (interm && interm->o_out)
+            APUS_CUDA_OK(cudaMemcpyAsync(interm->o_out, dout, (size_t)s * cfg->dim * 4, cudaMemcpyDeviceToHost, sm));
+        if (attn_state_download(*cfg, st, g_state, sm)) return 1;
+        APUS_CUDA_OK(cudaStreamSynchronize(sm));
+        attn_state_commit(*cfg, st, g_state);
+        if (ratio && interm) { interm->comp_nb = st->comp.nb - nb0; interm->idx_nb = cfg->has_indexer ? st->idx_comp.nb - inb0 : 0; }
+        int stt = gemm_tc_status(1);
+        APUS_REQUIRE(stt == 0, "attention: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+        return 0;
+    }
     // rope rows: per token [cos | sin] at its position and at the first position of the block it completes
     std::vector<float> cs((size_t)s * 4 * half, 0.f);
     for (int t = 0; t < s; t++) {

@@ -74,6 +74,21 @@ int block_step(const LayerDev &L, StateDev &S, float **h, float **hn, const int6
     return block_ffn_post(L, bb.sub, h, hn, B, hc, bb, st);
 }
 
+// A chunk of s positions of B sequences through one block: the same pieces on s * B time-major rows.
+int block_chunk(const LayerDev &L, StateDev &S, float **h, float **hn, const int64_t *ids, int B, int s, long long pos0,
+                int hc, int iters, float hc_eps, float norm_eps, const BlockBufs &bb, const StepBufs &sb, cudaStream_t st) {
+    const int dim = L.attn.cfg.dim, T = B * s;
+    APUS_REQUIRE(pos0 + s <= L.rope_rows, "position %lld is beyond the rope table (%d rows)", pos0 + s - 1, L.rope_rows);
+    if (mhc_pre(*h, dim, hc, L.hc_attn_fn, L.hc_attn_scale, L.hc_attn_base, norm_eps, hc_eps, iters, L.attn_norm_w,
+                norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, T, st, bb.raw))
+        return 1;
+    if (attn_chunk(L.attn, S, bb.x, pos0, s, L.cs, bb.sub, sb, st)) return 1;
+    if (block_ffn_post(L, bb.sub, h, hn, T, hc, bb, st)) return 1;               // mHC post of the attention half
+    if (block_ffn_pre(L, *h, T, hc, iters, hc_eps, norm_eps, bb, st)) return 1;
+    if (apus_cuda_moe_forward_dev(L.moe, bb.x, ids, T, bb.sub, st)) return 1;
+    return block_ffn_post(L, bb.sub, h, hn, T, hc, bb, st);
+}
+
 // own == NULL: weights of the global cache (host-pointer tier); otherwise they
 // belong to `own` and the MoE object to the caller.
 int layer_weights(const ApusCudaLayerDesc &d, int hc, int vocab, LayerDev *L, WeightOwner *own, int e_lo = 0,
@@ -178,6 +193,19 @@ struct ApusCudaModel {
     std::map<const void *, DevBuf *> rope; // rope rows by host table (layers of a kind share one)
     DevBuf h0, h1, x, y, sub, post, comb, yh, yn, logits, tok, ids, hist, raw, sa, ws[24];
     StepBufs sb;
+    // a chunk of positions in one pass (s > 1 calls): the same buffers for positions x sequences rows,
+    // allocated by the first such call
+    struct Chunk {
+        int rows = 0, s = 0;
+        DevBuf h0, h1, x, y, sub, post, comb, raw, sa, ext, logits, tok, ws[24];
+        StepBufs sb;
+        void release() {
+            DevBuf *b[] = {&h0, &h1, &x, &y, &sub, &post, &comb, &raw, &sa, &ext, &logits, &tok};
+            for (DevBuf *p : b) p->release();
+            for (auto &w : ws) w.release();
+            rows = s = 0;
+        }
+    } ck;
 };
 
 // What a rollback needs (reference c/mtp.h:113-138, 398-439): per layer the ring, the
@@ -296,6 +324,87 @@ static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
     return model_host_advance(m);
 }
 
+// ---- a chunk of positions in one pass (reference c/model.h:651-720 with s > 1) ---------------------
+// Rows are time-major (row = t * B + sequence).  Every operator of a step is row-wise except the
+// attention state, which attn_chunk walks in position order, so a chunk leaves the hidden states,
+// the state and the logits of s consecutive steps, bit for bit; what it saves is reading every
+// weight once per chunk instead of once per position.
+__global__ void advance_pos_by_kernel(long long *pos, int by) { *pos += by; }
+
+static int model_chunk_bufs(ApusCudaModel *m, int s) {
+    ApusCudaModel::Chunk &C = m->ck;
+    const size_t T = (size_t)m->B * s, dim = m->dim, hc = m->hc;
+    if ((int)T <= C.rows && s <= C.s) return 0;
+    const int rows = (int)T > C.rows ? (int)T : C.rows, sc = s > C.s ? s : C.s;
+    const size_t R = rows;
+    if (C.h0.get(R * hc * dim * 4, nullptr) || C.h1.get(R * hc * dim * 4, nullptr) || C.x.get(R * dim * 4, nullptr) ||
+        C.y.get(R * dim * 4, nullptr) || C.sub.get(R * dim * 4, nullptr) || C.post.get(R * hc * 4, nullptr) ||
+        C.comb.get(R * hc * hc * 4, nullptr) || C.raw.get(R * ((2 + hc) * hc + 1) * 4, nullptr))
+        return 1;
+    ApusAttnCfg widest = m->layers[0].attn.cfg;
+    size_t ext = 0;
+    for (int i = 0; i < m->n_layers; i++) {
+        const ApusAttnCfg &c = m->layers[i].attn.cfg;
+        if (c.has_indexer) { widest.idx_heads = c.idx_heads; widest.idx_dim = c.idx_dim; widest.idx_topk = c.idx_topk; }
+        const size_t e = (size_t)m->B * (c.window + sc) * c.head_dim * 4;
+        if (e > ext) ext = e;
+    }
+    widest.has_indexer = 0;                      // size the index row for the dense (largest) case
+    const long long wide_nb = m->max_nb > widest.idx_topk ? m->max_nb : widest.idx_topk;
+    if (attn_step_bufs(widest, wide_nb, rows, C.ws, &C.sb)) return 1;
+    C.sb.sa_cap = sparse_attn_scratch(widest.n_heads, (int)(widest.window + wide_nb + 8), rows);
+    if (C.sa.get(C.sb.sa_cap, &C.sb.sa)) return 1;
+    if (C.ext.get(ext, nullptr)) return 1;
+    C.sb.ext = C.ext.as<float>();
+    C.rows = rows; C.s = sc;
+    return 0;
+}
+
+// ids_tm: device, [s][B].  want_head: the head and the pick run on the last position's rows.
+static int model_chunk(ApusCudaModel *m, const int64_t *ids_tm, int s, bool want_head, cudaStream_t st) {
+    APUS_REQUIRE(m->e_lo == 0 && m->e_hi == m->n_experts,
+                 "this model holds experts [%d,%d) of %d: drive it layer by layer (apus_cuda_model_attn_half ...)",
+                 m->e_lo, m->e_hi, m->n_experts);
+    APUS_REQUIRE(m->pos + s <= m->max_pos, "model chunk: position %lld + %d exceeds max_pos %d", m->pos, s, m->max_pos);
+    if (model_chunk_bufs(m, s)) return 1;
+    ApusCudaModel::Chunk &C = m->ck;
+    const int T = m->B * s, dim = m->dim, hc = m->hc;
+    float *h = C.h0.as<float>(), *hn = C.h1.as<float>();
+    const BlockBufs bb = {C.x.as<float>(), C.y.as<float>(), C.sub.as<float>(), C.post.as<float>(), C.comb.as<float>(),
+                          C.raw.as<float>()};
+    if (embed_rows(m->embed, m->embed_bf16, ids_tm, T, hc, dim, h, st)) return 1;
+    for (int i = 0; i < m->n_layers; i++)
+        if (block_chunk(m->layers[i], m->states[i], &h, &hn, ids_tm, m->B, s, m->pos, hc, m->iters, m->hc_eps, m->norm_eps,
+                        bb, C.sb, st))
+            return 1;
+    if (want_head) {
+        m->h_cur = h + (size_t)(s - 1) * m->B * hc * dim;
+        if (model_head(m, st)) return 1;
+    }
+    m->h_cur = m->h0.as<float>(); m->h_alt = m->h1.as<float>();
+    advance_pos_by_kernel<<<1, 1, 0, st>>>(m->pos_dev.as<long long>(), s);
+    APUS_LAUNCHED();
+    m->pos += s;                                  // the entry counts were advanced by attn_chunk
+    return 0;
+}
+
+// s positions from device ids [s][B]: chunks of at most chunk_rows() rows, or one step per position
+static int model_consume(ApusCudaModel *m, const int64_t *ids_tm, int s, bool want_head, cudaStream_t st) {
+    const int per = chunks_enabled() && s > 1 && m->e_lo == 0 && m->e_hi == m->n_experts ? chunk_rows() / m->B : 0;
+    if (per < 2) {
+        for (int t = 0; t < s; t++) {
+            APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, ids_tm + (size_t)t * m->B, (size_t)m->B * 8, cudaMemcpyDeviceToDevice, st));
+            if (model_step(m, want_head && t == s - 1, st)) return 1;
+        }
+        return 0;
+    }
+    for (int t = 0; t < s; t += per) {
+        const int n = s - t < per ? s - t : per;
+        if (model_chunk(m, ids_tm + (size_t)t * m->B, n, want_head && t + n == s, st)) return 1;
+    }
+    return 0;
+}
+
 extern "C" {
 
 void apus_cuda_model_destroy(ApusCudaModel *m) {
@@ -313,6 +422,7 @@ void apus_cuda_model_destroy(ApusCudaModel *m) {
                       &m->tok, &m->ids, &m->hist, &m->raw, &m->sa};
     for (DevBuf *b : bufs) b->release();
     for (auto &b : m->ws) b.release();
+    m->ck.release();
     delete m;
 }
 
@@ -507,6 +617,40 @@ int apus_cuda_block_forward_v(const ApusCudaLayerDesc *d, int hc, int iters, flo
     DevBuf *ws = g_block_ws, *hb = g_block_hb;
     StepBufs sb;
     const long long max_nb = c.ratio ? (start_pos + s) / c.ratio + 2 : 0;
+    if (s > 1 && chunks_enabled()) {
+        // the s positions in passes of at most chunk_rows() rows (one sequence: rows are positions)
+        const int per = chunk_rows() < s ? chunk_rows() : s;
+        if (attn_step_bufs(c, max_nb, per, ws, &sb)) return 1;
+        if (attn_state_upload(c, st, S, c.ratio ? s / c.ratio + 2 : 0, sm)) return 1;
+        void *q[11];
+        const size_t R = per;
+        size_t qs[11] = {(size_t)s * hc * dim * 4, R * hc * dim * 4, R * dim * 4, R * dim * 4, R * dim * 4, R * hc * 4,
+                         R * hc * hc * 4, (size_t)s * 8, R * ((2 + hc) * hc + 1) * 4, (size_t)(c.window + per) * c.head_dim * 4,
+                         sparse_attn_scratch(c.n_heads, (int)(c.window + (c.has_indexer && c.idx_topk > max_nb ? c.idx_topk : max_nb) + 8), per)};
+        for (int i = 0; i < 8; i++) if (hb[i].get(qs[i], &q[i])) return 1;
+        if (hb[8].get(qs[8], &q[8]) || hb[9].get(qs[9], &q[9]) || ws[22].get(qs[10], &q[10])) return 1;
+        sb.ext = (float *)q[9]; sb.sa = q[10]; sb.sa_cap = qs[10];
+        float *hall = (float *)q[0];
+        APUS_CUDA_OK(cudaMemcpyAsync(hall, h, qs[0], cudaMemcpyHostToDevice, sm));
+        if (ids) APUS_CUDA_OK(cudaMemcpyAsync(q[7], ids, (size_t)s * 8, cudaMemcpyHostToDevice, sm));
+        BlockBufs bb = {(float *)q[2], (float *)q[3], (float *)q[4], (float *)q[5], (float *)q[6], (float *)q[8]};
+        for (int t = 0; t < s; t += per) {
+            const int n = s - t < per ? s - t : per;
+            float *ht = hall + (size_t)t * hc * dim;
+            float *cur = ht, *alt = (float *)q[1];
+            if (block_chunk(L, S, &cur, &alt, ids ? (const int64_t *)q[7] + t : nullptr, 1, n, start_pos + t, hc, iters, hc_eps,
+                            norm_eps, bb, sb, sm))
+                return 1;
+            if (cur != ht) APUS_CUDA_OK(cudaMemcpyAsync(ht, cur, (size_t)n * hc * dim * 4, cudaMemcpyDeviceToDevice, sm));
+        }
+        APUS_CUDA_OK(cudaMemcpyAsync(h, hall, qs[0], cudaMemcpyDeviceToHost, sm));
+        if (attn_state_download(c, st, S, sm)) return 1;
+        APUS_CUDA_OK(cudaStreamSynchronize(sm));
+        attn_state_commit(c, st, S);
+        int stt2 = gemm_tc_status(1);
+        APUS_REQUIRE(stt2 == 0, "block_forward: a bounded wait expired inside a tcgen05 kernel (code %d)", stt2);
+        return 0;
+    }
     if (attn_step_bufs(c, max_nb, 1, ws, &sb)) return 1;
     if (attn_state_upload(c, st, S, c.ratio ? s / c.ratio + 2 : 0, sm)) return 1;
     void *p[8];
@@ -633,17 +777,29 @@ int apus_cuda_model_forward_group(ApusCudaModel *const *ms, int n, const int64_t
                      ms[i]->pos, s, ms[i]->max_pos);
         if (ids_in_range(ms[i], ids[i], (size_t)ms[i]->B * s, "model_forward")) return 1;
     }
-    std::vector<std::vector<int64_t>> col((size_t)n);
-    for (int t = 0; t < s; t++) {
-        for (int i = 0; i < n; i++) {
-            ApusCudaModel *m = ms[i];
-            col[i].resize((size_t)m->B);
-            for (int b = 0; b < m->B; b++) col[i][b] = ids[i][(size_t)b * s + t];
-            APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, col[i].data(), (size_t)m->B * 8, cudaMemcpyHostToDevice, mstream(m)));
-        }
-        if (s > 1 && group_sync(ms, n)) return 1;         // `col` is reused by the next position
+    // the ids of every position go to the device first, time-major ([s][B]); one model after the
+    // other when a call holds several positions, position by position side by side otherwise
+    std::vector<std::vector<int64_t>> cols((size_t)n);
+    std::vector<void *> dcols((size_t)n);
+    for (int i = 0; i < n; i++) {
+        ApusCudaModel *m = ms[i];
+        cols[i].resize((size_t)s * m->B);
+        for (int t = 0; t < s; t++)
+            for (int b = 0; b < m->B; b++) cols[i][(size_t)t * m->B + b] = ids[i][(size_t)b * s + t];
+        if (m->ws[23].get(cols[i].size() * 8, &dcols[i])) return 1;
+        APUS_CUDA_OK(cudaMemcpyAsync(dcols[i], cols[i].data(), cols[i].size() * 8, cudaMemcpyHostToDevice, mstream(m)));
+    }
+    if (s > 1 && chunks_enabled()) {
         for (int i = 0; i < n; i++)
-            if (model_step(ms[i], t == s - 1, mstream(ms[i]))) return 1;
+            if (model_consume(ms[i], (const int64_t *)dcols[i], s, true, mstream(ms[i]))) return 1;
+    } else {
+        for (int t = 0; t < s; t++)
+            for (int i = 0; i < n; i++) {
+                ApusCudaModel *m = ms[i];
+                APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, (const int64_t *)dcols[i] + (size_t)t * m->B, (size_t)m->B * 8,
+                                             cudaMemcpyDeviceToDevice, mstream(m)));
+                if (model_step(m, t == s - 1, mstream(m))) return 1;
+            }
     }
     for (int i = 0; i < n; i++) {
         ApusCudaModel *m = ms[i];
@@ -719,13 +875,18 @@ int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n, const int64_
         APUS_CUDA_OK(cudaMemcpyAsync(dcols[i], cols[i].data(), cols[i].size() * 8, cudaMemcpyHostToDevice, mstream(m)));
     }
     if (group_mark(ms, n, tmp, e0)) return 1;
-    for (int t = 0; t < n_prompt; t++)
-        for (int i = 0; i < n; i++) {
-            ApusCudaModel *m = ms[i];
-            APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, (const int64_t *)dcols[i] + (size_t)t * m->B, (size_t)m->B * 8,
-                                         cudaMemcpyDeviceToDevice, mstream(m)));
-            if (model_step(m, t == n_prompt - 1, mstream(m))) return 1;
-        }
+    if (n_prompt > 1 && chunks_enabled()) {
+        for (int i = 0; i < n; i++)
+            if (model_consume(ms[i], (const int64_t *)dcols[i], n_prompt, true, mstream(ms[i]))) return 1;
+    } else {
+        for (int t = 0; t < n_prompt; t++)
+            for (int i = 0; i < n; i++) {
+                ApusCudaModel *m = ms[i];
+                APUS_CUDA_OK(cudaMemcpyAsync(m->ids.p, (const int64_t *)dcols[i] + (size_t)t * m->B, (size_t)m->B * 8,
+                                             cudaMemcpyDeviceToDevice, mstream(m)));
+                if (model_step(m, t == n_prompt - 1, mstream(m))) return 1;
+            }
+    }
     if (group_mark(ms, n, tmp, e1)) return 1;
     for (int g = 0; g < n_gen; g++)
         for (int i = 0; i < n; i++) {                     // the models' steps alternate, each on its own stream

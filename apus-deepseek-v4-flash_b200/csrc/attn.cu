@@ -27,14 +27,14 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 
 __global__ void __launch_bounds__(TOPK_THREADS)
 topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__restrict__ idx_out,
-                   const long long *__restrict__ dyn_pos, int ratio) {
+                   const long long *__restrict__ dyn_pos, int ratio, long long chunk_pos0, int rows_per_pos) {
     __shared__ unsigned hist[256];
     __shared__ unsigned s_prefix, s_need, s_greater, s_taken, s_base;
     __shared__ unsigned long long sel[TOPK_MAX_K];
     const float *row = scores + (size_t)blockIdx.x * n;     // n, k as given are the row strides
     int32_t *out = idx_out + (size_t)blockIdx.x * k;
-    if (dyn_pos) {                                          // live sizes from the position on the device
-        const long long nbs = (*dyn_pos + 1) / ratio;
+    if (dyn_pos || rows_per_pos > 0) {                      // live sizes from the position (of the row, in a chunk)
+        const long long nbs = ((dyn_pos ? *dyn_pos : chunk_pos0 + blockIdx.x / rows_per_pos) + 1) / ratio;
         n = (int)(nbs < n ? nbs : n);
         k = k < n ? k : n;
         if (k <= 0) return;
@@ -123,10 +123,10 @@ topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__re
 }
 
 int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
-                cudaStream_t st, const long long *dyn_pos, int ratio) {
-    APUS_REQUIRE(k >= 1 && (k <= n || dyn_pos) && k <= TOPK_MAX_K, "topk: n=%d k=%d unsupported", n, k);
+                cudaStream_t st, const long long *dyn_pos, int ratio, long long chunk_pos0, int rows_per_pos) {
+    APUS_REQUIRE(k >= 1 && (k <= n || dyn_pos || rows_per_pos > 0) && k <= TOPK_MAX_K, "topk: n=%d k=%d unsupported", n, k);
     if (rows <= 0) return 0;
-    topk_stable_kernel<<<rows, TOPK_THREADS, 0, st>>>(scores, n, k, idx, dyn_pos, ratio);
+    topk_stable_kernel<<<rows, TOPK_THREADS, 0, st>>>(scores, n, k, idx, dyn_pos, ratio, chunk_pos0, rows_per_pos);
     APUS_LAUNCHED();
     return 0;
 }
@@ -162,11 +162,12 @@ __global__ void __launch_bounds__(SA_IDS * SA_HEADS)
 sparse_scores_kernel(const float *__restrict__ q, int h, int d, const int32_t *__restrict__ ids,
                      const int *__restrict__ ns, int idxw, float scale, const void *kv_a,
                      int64_t na, const void *kv_b, float *__restrict__ sc, size_t a_stride,
-                     size_t b_stride) {
+                     size_t b_stride, int seq_mod) {
     extern __shared__ float sm[];
     const int t = blockIdx.z, hb = blockIdx.y, tile = blockIdx.x;
-    kv_a = reinterpret_cast<const char *>(kv_a) + (size_t)t * a_stride;
-    kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)t * b_stride;
+    const int own = seq_mod > 0 ? t % seq_mod : t;         // whose caches: rows of a chunk are time-major
+    kv_a = reinterpret_cast<const char *>(kv_a) + (size_t)own * a_stride;
+    kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride;
     const int n = ns[t];
     if (tile * SA_IDS >= n) return;
     const int pitch = d + 1;
@@ -207,13 +208,14 @@ __global__ void __launch_bounds__(256)
 sparse_pv_kernel(const float *__restrict__ sc, const float *__restrict__ sink, int h, int d,
                  const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw,
                  const void *kv_a, int64_t na, const void *kv_b, float *__restrict__ o, size_t a_stride,
-                 size_t b_stride) {
+                 size_t b_stride, int seq_mod) {
     extern __shared__ float s_p[];             // [idxw]
     __shared__ float red[32];
     __shared__ float s_mx, s_sum;
     const int t = blockIdx.y, head = blockIdx.x, tid = threadIdx.x;
-    kv_a = reinterpret_cast<const char *>(kv_a) + (size_t)t * a_stride;
-    kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)t * b_stride;
+    const int own = seq_mod > 0 ? t % seq_mod : t;
+    kv_a = reinterpret_cast<const char *>(kv_a) + (size_t)own * a_stride;
+    kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride;
     const int n = ns[t];
     float *ov = o + ((size_t)t * h + head) * d;
     if (n == 0) {
@@ -323,7 +325,7 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
                 int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride, long long kv_b_stride,
-                void *callers, size_t callers_cap) {
+                void *callers, size_t callers_cap, int seq_mod) {
     (void)nb;
     const size_t esz = kv_bf16 ? 2 : 4;
     const size_t sa = (size_t)kv_a_stride * esz, sb = (size_t)kv_b_stride * esz;
@@ -352,15 +354,15 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         return 1;
     if (kv_bf16) {
         sparse_scores_kernel<true><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
-                                                                       kv_a, na, kv_b, sc, sa, sb);
+                                                                       kv_a, na, kv_b, sc, sa, sb, seq_mod);
         APUS_LAUNCHED();
-        sparse_pv_kernel<true><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb);
+        sparse_pv_kernel<true><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);
         APUS_LAUNCHED();
     } else {
         sparse_scores_kernel<false><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
-                                                                        kv_a, na, kv_b, sc, sa, sb);
+                                                                        kv_a, na, kv_b, sc, sa, sb, seq_mod);
         APUS_LAUNCHED();
-        sparse_pv_kernel<false><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb);
+        sparse_pv_kernel<false><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);
         APUS_LAUNCHED();
     }
     return 0;

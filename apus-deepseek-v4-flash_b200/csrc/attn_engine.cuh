@@ -41,6 +41,8 @@ struct StepBufs {
     // sparse-attention scratch of the owner (NULL: the library's shared one)
     void *sa = nullptr;
     size_t sa_cap = 0;
+    // chunks of positions only (attn_chunk): the position-ordered window rows [B][window + s][head_dim]
+    float *ext = nullptr;
 };
 
 // Device copies that belong to one object (a model) instead of the global cache.
@@ -63,6 +65,15 @@ int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, St
 int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
               const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st,
               const long long *pos_dev = nullptr, const float *cs_table = nullptr);
+
+// A chunk of s consecutive positions of the B sequences in one pass (batched prefill, the
+// s > 1 calls of reference c/attn.h:1514-1740): x, out [s * B, dim] with time-major rows
+// (row = t * B + sequence), positions pos0 .. pos0 + s - 1, rope rows from cs_table.  `b` holds
+// step buffers for s * B rows plus b.ext.  Every row goes through the operations of attn_step in
+// the same order, so outputs and final state equal those of s consecutive steps bit for bit; the
+// entry counts S.*.nb are advanced here.
+int attn_chunk(const AttnDev &A, StateDev &S, const float *x, long long pos0, int s, const float *cs_table,
+               float *out, const StepBufs &b, cudaStream_t st);
 
 // Host-state exchange of the host-pointer tier (one sequence).
 int attn_state_upload(const ApusAttnCfg &c, const ApusAttnS *st, StateDev &S, int extra, cudaStream_t sm);

@@ -327,14 +327,16 @@ int comp_step(float *kv_state, float *sc_state, long long state_stride, const fl
 __global__ void __launch_bounds__(64 * IDX_B)
 idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, float wscale,
                  const float *__restrict__ cache, long long cache_stride, long long nb, int ih, int idm,
-                 float *__restrict__ sc, const long long *__restrict__ dyn_pos, int ratio) {
+                 float *__restrict__ sc, const long long *__restrict__ dyn_pos, int ratio, long long chunk_pos0,
+                 int chunk_seqs) {
     extern __shared__ float sm[];             // q [ih*idm], k [IDX_B*idm], terms [IDX_B*ih]
     q += (size_t)blockIdx.y * ih * idm;
     wt_raw += (size_t)blockIdx.y * ih;
-    cache += (size_t)blockIdx.y * cache_stride;
-    sc += (size_t)blockIdx.y * nb;             // row stride: the capacity when the count is read on the device
-    if (dyn_pos) {
-        nb = (*dyn_pos + 1) / ratio;
+    // rows of a chunk are time-major: row = t * chunk_seqs + sequence, at position chunk_pos0 + t
+    cache += (size_t)(chunk_seqs > 0 ? blockIdx.y % chunk_seqs : blockIdx.y) * cache_stride;
+    sc += (size_t)blockIdx.y * nb;             // row stride: the capacity when the count is derived on the device
+    if (dyn_pos || chunk_seqs > 0) {
+        nb = ((dyn_pos ? *dyn_pos : chunk_pos0 + blockIdx.y / chunk_seqs) + 1) / ratio;
         if ((long long)blockIdx.x * IDX_B >= nb) return;
     }
     float *s_q = sm, *s_k = sm + ih * idm, *s_t = s_k + IDX_B * idm;
@@ -364,14 +366,14 @@ idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, 
 
 int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long cache_stride,
                long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st, const long long *dyn_pos,
-               int ratio) {
+               int ratio, long long chunk_pos0, int chunk_seqs) {
     APUS_REQUIRE(ih <= 64 && ih >= 1, "indexer: %d heads unsupported", ih);
     if (nb <= 0 || n_seq <= 0) return 0;
     size_t smem = ((size_t)ih * idm + IDX_B * idm + IDX_B * ih) * sizeof(float);
     if (ensure_dyn_smem((const void *)idx_score_kernel, smem)) return 1;
     dim3 grid((unsigned)((nb + IDX_B - 1) / IDX_B), (unsigned)n_seq);
     idx_score_kernel<<<grid, ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc,
-                                                     dyn_pos, ratio);
+                                                     dyn_pos, ratio, chunk_pos0, chunk_seqs);
     APUS_LAUNCHED();
     return 0;
 }
@@ -427,6 +429,73 @@ int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int 
                  const long long *dyn_pos, int win) {
     if (rows <= 0) return 0;
     scatter_rows_kernel<<<dim3(ceil_div(n, 256), rows), 256, 0, st>>>(dst, dst_stride, src, n, dyn_pos, win);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+// ---- a chunk of consecutive positions (batched prefill, reference c/attn.h:1621-1680) ----------
+// Rows of a chunk are time-major: row = t * n_seq + sequence, at position pos0 + t.  The window
+// candidates of a chunk live in a position-ordered buffer per sequence,
+//   ext[seq][j] = KV row of position pos0 - win + j,   j in [0, win + s),
+// the first `win` rows copied from the ring, the rest the chunk's own rows; the index row of a
+// token lists its window oldest first (the order of c/attn.h:692-720 once the -1 entries are
+// dropped) and then its compressed ids, offset by win + s.
+__global__ void win_ext_kernel(float *__restrict__ ext, const float *__restrict__ ring, const float *__restrict__ kv,
+                               int win, int s, int d, int n_seq, long long pos0) {
+    const int j = blockIdx.y, seq = blockIdx.z;
+    float *dst = ext + ((size_t)seq * (win + s) + j) * d;
+    const float *src = nullptr;
+    if (j >= win) src = kv + ((size_t)(j - win) * n_seq + seq) * d;
+    else {
+        const long long q = pos0 - win + j;
+        if (q >= 0) src = ring + ((size_t)seq * win + (size_t)(q % win)) * d;
+    }
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < d; i += gridDim.x * blockDim.x) dst[i] = src ? src[i] : 0.f;
+}
+// the ring after the chunk: the last min(s, win) rows at their slots (c/attn.h:1642-1658)
+__global__ void ring_update_kernel(float *__restrict__ ring, const float *__restrict__ kv, int win, int s, int d,
+                                   int n_seq, long long pos0, int t0) {
+    const int t = t0 + blockIdx.y, seq = blockIdx.z;
+    float *dst = ring + ((size_t)seq * win + (size_t)((pos0 + t) % win)) * d;
+    const float *src = kv + ((size_t)t * n_seq + seq) * d;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < d; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+int win_ext(float *ext, const float *ring, const float *kv, int win, int s, int d, int n_seq, long long pos0,
+            cudaStream_t st) {
+    if (s <= 0 || n_seq <= 0) return 0;
+    win_ext_kernel<<<dim3(ceil_div(d, 256), win + s, n_seq), 256, 0, st>>>(ext, ring, kv, win, s, d, n_seq, pos0);
+    APUS_LAUNCHED();
+    return 0;
+}
+int ring_update(float *ring, const float *kv, int win, int s, int d, int n_seq, long long pos0, cudaStream_t st) {
+    if (s <= 0 || n_seq <= 0) return 0;
+    const int t0 = s > win ? s - win : 0;
+    ring_update_kernel<<<dim3(ceil_div(d, 256), s - t0, n_seq), 256, 0, st>>>(ring, kv, win, s, d, n_seq, pos0, t0);
+    APUS_LAUNCHED();
+    return 0;
+}
+
+__global__ void build_idx_chunk_kernel(int32_t *__restrict__ out, int win, int s, long long pos0, int n_seq,
+                                       const int32_t *__restrict__ sel, int compcap, int ratio) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+    if (j >= win + compcap) return;
+    const int t = row / n_seq;
+    const long long p = pos0 + t;
+    int v = -1;
+    if (j < win) {
+        if (p - win + 1 + j >= 0) v = t + 1 + j;                 // position p - win + 1 + j in ext coordinates
+    } else {
+        const long long nbs = ratio ? (p + 1) / ratio : 0;
+        const int jj = j - win;
+        if (jj < nbs) v = (sel ? sel[(size_t)row * compcap + jj] : jj) + win + s;
+    }
+    out[(size_t)row * (win + compcap) + j] = v;
+}
+int build_idx_chunk(int32_t *out, int win, int s, long long pos0, int n_seq, const int32_t *sel, int compcap, int ratio,
+                    cudaStream_t st) {
+    if (s <= 0 || n_seq <= 0) return 0;
+    build_idx_chunk_kernel<<<dim3(ceil_div(win + compcap, 256), s * n_seq), 256, 0, st>>>(out, win, s, pos0, n_seq, sel,
+                                                                                          compcap, ratio);
     APUS_LAUNCHED();
     return 0;
 }

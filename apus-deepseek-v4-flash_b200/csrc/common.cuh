@@ -17,7 +17,9 @@ extern unsigned long long g_dispatches;        // api.cu: kernels launched
 #define APUS_CUDA_SUM_TREE 1
 #endif
 int sum_order();                               // api.cu: TREE only when every operator class is in tree order
-unsigned long long sum_order_epoch();          // api.cu: changes whenever the order does
+unsigned long long sum_order_epoch();          // api.cu: changes whenever the order does, or a workspace buffer moved
+int chunk_rows();                              // api.cu: rows (positions x sequences) one chunk of a s > 1 call may hold; 0 = one step per position
+bool chunks_enabled();
 // Operator classes whose long f32 sums may leave the reference's loop order (public:
 // apus_cuda_set_tree_ops).  sum_tree(op) = this class currently sums in tree / tensor-core order.
 #ifndef APUS_CUDA_TREE_MHC_MAPS

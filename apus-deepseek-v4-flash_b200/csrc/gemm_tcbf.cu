@@ -224,8 +224,11 @@ int f32_to_bf16(const float *x, uint16_t *y, long long n, cudaStream_t st) {
 }
 
 // K chunks so that a launch with few output tiles still covers most SMs (each chunk at least 4 K tiles)
+// The number of K chunks follows from the weight's shape alone: a row's sum is then cut the same
+// way whatever the number of rows beside it, so one position and a chunk of positions agree bit for bit.
 int tcbf_ksplit(int O, int K, int batch, int M) {
-    const long long ctas = (long long)(O / 128) * batch * ((M + TB_N - 1) / TB_N);
+    (void)M;
+    const long long ctas = (long long)(O / 128) * batch;
     const int nt = K / TB_KT;
     int s = (int)(148 / (ctas > 0 ? ctas : 1));
     if (s > nt / 4) s = nt / 4;

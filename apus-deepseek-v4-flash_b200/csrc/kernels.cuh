@@ -172,14 +172,18 @@ int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
 
 // ---- selection + attention (attn.cu) ----------------------------------------------------------
 int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
-                cudaStream_t st, const long long *dyn_pos = nullptr, int ratio = 0);
-// dyn_pos: n and k are capacities (row strides); live n = (*dyn_pos + 1) / ratio, live k = min(k, n)
+                cudaStream_t st, const long long *dyn_pos = nullptr, int ratio = 0, long long chunk_pos0 = 0,
+                int rows_per_pos = 0);
+// dyn_pos: n and k are capacities (row strides); live n = (*dyn_pos + 1) / ratio, live k = min(k, n).
+// rows_per_pos > 0 (a chunk of positions, time-major rows): the same with the row's own position
+// chunk_pos0 + row / rows_per_pos.
 int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
                 int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride = 0,
                 long long kv_b_stride = 0,    // strides (elements) between the tokens' own caches; 0 = shared
-                void *scratch = nullptr, size_t scratch_cap = 0);   // caller's scratch (sparse_attn_scratch bytes) or the shared one
+                void *scratch = nullptr, size_t scratch_cap = 0,    // caller's scratch (sparse_attn_scratch bytes) or the shared one
+                int seq_mod = 0);    // > 0: token t reads the caches of sequence t % seq_mod (time-major rows of a chunk)
 size_t sparse_attn_scratch(int h, int idxw, int s);
 
 // ---- attention row helpers, compressor and indexer steps (attn_ops.cu) -----------------------
@@ -216,8 +220,10 @@ int comp_step(float *kv_state, float *sc_state, long long state_stride, const fl
 // apart, sc [n_seq, nb].
 int idx_scores(const float *q, const float *wt_raw, float wscale, const float *cache, long long cache_stride,
                long long nb, int ih, int idm, float *sc, int n_seq, cudaStream_t st,
-               const long long *dyn_pos = nullptr, int ratio = 0);
-// dyn_pos: nb is the capacity (grid size and row stride of sc); the live count is (*dyn_pos + 1) / ratio
+               const long long *dyn_pos = nullptr, int ratio = 0, long long chunk_pos0 = 0, int chunk_seqs = 0);
+// dyn_pos: nb is the capacity (grid size and row stride of sc); the live count is (*dyn_pos + 1) / ratio.
+// chunk_seqs > 0: n_seq counts the time-major rows of a chunk of positions; row r scores the cache of
+// sequence r % chunk_seqs up to its own position chunk_pos0 + r / chunk_seqs.
 // out [n_seq, win + compw]; sel [n_seq, compw] or NULL for the dense list.
 int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st,
               const long long *dyn_pos = nullptr, int ratio = 0);
@@ -226,6 +232,14 @@ int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int comp
 // dst[b * dst_stride + i] = src[b * n + i] for b < rows (ring / cache row scatter).
 int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st,
                  const long long *dyn_pos = nullptr, int win = 0);   // dyn_pos: dst += (*dyn_pos % win) * n
+// A chunk of s consecutive positions of n_seq sequences (time-major rows): the position-ordered window
+// buffer ext [n_seq][win + s][d] from the ring and the chunk's rows, the ring after the chunk, and the
+// index rows [s * n_seq][win + compcap] (window ids into ext, compressed ids + win + s, -1 padding).
+int win_ext(float *ext, const float *ring, const float *kv, int win, int s, int d, int n_seq, long long pos0,
+            cudaStream_t st);
+int ring_update(float *ring, const float *kv, int win, int s, int d, int n_seq, long long pos0, cudaStream_t st);
+int build_idx_chunk(int32_t *out, int win, int s, long long pos0, int n_seq, const int32_t *sel, int compcap, int ratio,
+                    cudaStream_t st);
 // First index of the row maximum (reference c/sample.h:76-81), rows of n.
 int argmax_rows(const float *x, int n, int rows, int32_t *out, cudaStream_t st);
 // Embedding rows replicated hc times (reference c/model.h:512-517): out [rows, hc, dim].

@@ -216,6 +216,18 @@ int apus_cuda_kernel_status(int reset);
 #define APUS_CUDA_TREE_DEFAULT  (1 + 4 + 8)
 int apus_cuda_set_tree_ops(int mask);
 int apus_cuda_set_sum_order(int order);
+/* Calls that carry s > 1 positions (apus_cuda_attention, apus_cuda_block_forward,
+ * apus_cuda_model_forward / _generate on the prompt) run them as chunks of positions: every
+ * weight is read once per chunk, rows are (position, sequence) pairs, and only the
+ * attention state is walked in position order -- the batched forms of the reference
+ * (c/attn.h:1621-1680 prefill, 1576-1620 mid-stream batch, c/moe.h:217-330 expert
+ * grouping, c/model.h:651-720).  Each row goes through the operations of a single step in
+ * the same order, so a chunk leaves the outputs and the state of s consecutive steps bit
+ * for bit, whatever the chunk size (the reference's chunk invariance, tests/m4c).
+ * `rows` = the most rows (positions x sequences) one chunk may hold; 0 = one step per
+ * position; negative only queries.  Returns the previous value (default 2048;
+ * environment at load time: APUS_PREFILL=<rows>). */
+int apus_cuda_set_prefill_chunk(int rows);
 /* Run the entry points that take no stream argument (host-pointer tier, model
  * loop) on the caller's stream instead of the library's own, e.g. to order them
  * with the caller's collectives without events; use_own != 0 switches back.
