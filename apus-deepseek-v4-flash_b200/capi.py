@@ -116,6 +116,13 @@ class ModelDesc(C.Structure):
                 ("hc_head_fn", C.c_void_p), ("hc_head_base", C.c_void_p), ("hc_head_scale", C.c_float)]
 
 
+class MtpDesc(C.Structure):
+    """ApusCudaMtpDesc: what apus_mtp_forward reads of ApusMtp (c/mtp.h:66-76)."""
+    _fields_ = [("block", LayerDesc), ("e_proj", QW), ("h_proj", QW), ("enorm_w", C.c_void_p), ("hnorm_w", C.c_void_p),
+                ("norm_w", C.c_void_p), ("hc_head_fn", C.c_void_p), ("hc_head_base", C.c_void_p),
+                ("hc_head_scale", C.c_float)]
+
+
 class Fp4GemmEnt(C.Structure):
     """ApusFp4GemmEnt (c/fp4.h:184-188)."""
     _fields_ = [("w", C.c_void_p), ("ws", C.c_void_p), ("out", C.c_void_p),
@@ -254,6 +261,13 @@ def load(path=LIB_PATH):
         "apus_cuda_moe_work_items": (C.c_longlong, [vp, ci]),
         "apus_cuda_model_forward": (ci, [vp, vp, ci, vp, vp]),
         "apus_cuda_model_forward_all": (ci, [vp, vp, ci, vp, vp]),
+        "apus_cuda_model_forward_h": (ci, [vp, vp, ci, vp, ci, vp, vp]),
+        "apus_cuda_model_forward_mh": (ci, [vp, vp, ci, vp, ci, vp, vp, ci, vp]),
+        "apus_cuda_mtp_create": (vp, [vp, vp]),
+        "apus_cuda_mtp_destroy": (None, [vp]),
+        "apus_cuda_mtp_reset": (ci, [vp]),
+        "apus_cuda_mtp_forward": (ci, [vp, vp, vp, ci, C.c_int64, vp, vp, vp]),
+        "apus_cuda_model_spec_generate_mtp": (ci, [vp, vp, vp, ci, ci, ci, vp, vp]),
         "apus_cuda_model_generate": (ci, [vp, vp, ci, ci, vp, C.POINTER(cf), C.POINTER(cf)]),
         "apus_cuda_apply_rope": (ci, [vp, vp, vp, ci, ci, ci, ci]),
         "apus_cuda_hadamard": (ci, [vp, ci, ci]),

@@ -197,10 +197,10 @@ struct ApusCudaModel {
     // allocated by the first such call
     struct Chunk {
         int rows = 0, s = 0;
-        DevBuf h0, h1, x, y, sub, post, comb, raw, sa, ext, logits, tok, ws[24];
+        DevBuf h0, h1, x, y, sub, post, comb, raw, sa, ext, logits, tok, hx, mhx, ws[24];
         StepBufs sb;
         void release() {
-            DevBuf *b[] = {&h0, &h1, &x, &y, &sub, &post, &comb, &raw, &sa, &ext, &logits, &tok};
+            DevBuf *b[] = {&h0, &h1, &x, &y, &sub, &post, &comb, &raw, &sa, &ext, &logits, &tok, &hx, &mhx};
             for (DevBuf *p : b) p->release();
             for (auto &w : ws) w.release();
             rows = s = 0;
@@ -230,20 +230,11 @@ static int model_embed(ApusCudaModel *m, cudaStream_t st) {
     m->h_cur = m->h0.as<float>(); m->h_alt = m->h1.as<float>();
     return embed_rows(m->embed, m->embed_bf16, m->ids.as<int64_t>(), m->B, m->hc, m->dim, m->h_cur, st);
 }
-// head: hc_head collapse -> BF16 -> RMSNorm -> LM-head GEMV (reference c/model.h:706-718) -> greedy pick
+static int head_rows(ApusCudaModel *m, const float *h, int rows, float *yh, float *yn, float *logits, int32_t *tok,
+                     cudaStream_t st);
+// head of one position (reference c/model.h:706-718) and the pick
 static int model_head(ApusCudaModel *m, cudaStream_t st) {
-    const int B = m->B, dim = m->dim;
-    if (mhc_head(m->h_cur, dim, m->hc, m->hc_head_fn, m->hc_head_scale, m->hc_head_base, m->norm_eps, m->hc_eps,
-                 m->yh.as<float>(), B, st, m->raw.as<float>()))
-        return 1;
-    if (rms_norm(m->yh.as<float>(), m->norm_w, m->norm_eps, m->yn.as<float>(), dim, B, st)) return 1;
-    if (f32_linear(m->head, m->yn.as<float>(), m->logits.as<float>(), B, dim, m->vocab,
-                   (m->head_bf16 ? APUS_CUDA_W_BF16 : 0) | APUS_LIN_CLASS(APUS_CUDA_TREE_HEAD), st))
-        return 1;
-    if (m->temp > 0.f)                                   // c/sample.h:173-178; greedy otherwise (c/sample.h:76-81)
-        return sample_rows(m->logits.as<float>(), m->vocab, B, m->temp, m->top_p, nullptr,
-                           m->rng.as<unsigned long long>(), m->probs.as<float>(), m->tok.as<int32_t>(), st);
-    return argmax_rows(m->logits.as<float>(), m->vocab, B, m->tok.as<int32_t>(), st);
+    return head_rows(m, m->h_cur, m->B, m->yh.as<float>(), m->yn.as<float>(), m->logits.as<float>(), m->tok.as<int32_t>(), st);
 }
 __global__ void advance_pos_kernel(long long *pos) { *pos += 1; }
 
@@ -360,8 +351,55 @@ static int model_chunk_bufs(ApusCudaModel *m, int s) {
     return 0;
 }
 
+// What a chunk may leave besides the state (device pointers, time-major rows, all nullable):
+//   logits_all / tok_all: the head and the pick of EVERY row (c/model.h:706-718 with logits_all)
+//   h_all: the hidden state after the last block, [rows][hc * dim] (c/model.h:694-696, the MTP input)
+//   mh_all: after each layer listed in `targets`, the mean over the hc streams of every row, BF16,
+//           [rows][n_targets * dim] (c/model.h:676-693, the DSpark input)
+struct ChunkExtra {
+    float *logits_all = nullptr;
+    int32_t *tok_all = nullptr;
+    float *h_all = nullptr;
+    float *mh_all = nullptr;
+    const int *targets = nullptr;
+    int n_targets = 0;
+};
+
+// mean over the hc streams in stream order, one accumulator, then BF16 (c/model.h:684-690)
+__global__ void hc_mean_kernel(const float *__restrict__ h, int hc, int dim, float *__restrict__ out, int out_ld) {
+    const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dim) return;
+    float acc = 0.f;
+    for (int j = 0; j < hc; j++) acc = __fadd_rn(acc, h[((size_t)r * hc + j) * dim + i]);
+    out[(size_t)r * out_ld + i] = bf16_round(__fdiv_rn(acc, (float)hc));
+}
+
+// head: hc_head collapse -> BF16 -> RMSNorm -> LM-head GEMV -> pick, on `rows` rows of hidden states;
+// a sampled pick draws one uniform per sequence and position, in position order (c/sample.h:173-178)
+static int head_rows(ApusCudaModel *m, const float *h, int rows, float *yh, float *yn, float *logits, int32_t *tok,
+                     cudaStream_t st) {
+    const int dim = m->dim, B = m->B;
+    if (mhc_head(h, dim, m->hc, m->hc_head_fn, m->hc_head_scale, m->hc_head_base, m->norm_eps, m->hc_eps, yh, rows, st,
+                 rows <= B ? m->raw.as<float>() : m->ck.raw.as<float>()))
+        return 1;
+    if (rms_norm(yh, m->norm_w, m->norm_eps, yn, dim, rows, st)) return 1;
+    if (f32_linear(m->head, yn, logits, rows, dim, m->vocab,
+                   (m->head_bf16 ? APUS_CUDA_W_BF16 : 0) | APUS_LIN_CLASS(APUS_CUDA_TREE_HEAD), st))
+        return 1;
+    if (!tok) return 0;
+    if (m->temp > 0.f) {
+        for (int t = 0; t < rows / B; t++)
+            if (sample_rows(logits + (size_t)t * B * m->vocab, m->vocab, B, m->temp, m->top_p, nullptr,
+                            m->rng.as<unsigned long long>(), m->probs.as<float>(), tok + (size_t)t * B, st))
+                return 1;
+        return 0;
+    }
+    return argmax_rows(logits, m->vocab, rows, tok, st);
+}
+
 // ids_tm: device, [s][B].  want_head: the head and the pick run on the last position's rows.
-static int model_chunk(ApusCudaModel *m, const int64_t *ids_tm, int s, bool want_head, cudaStream_t st) {
+static int model_chunk(ApusCudaModel *m, const int64_t *ids_tm, int s, bool want_head, cudaStream_t st,
+                       const ChunkExtra *ex = nullptr) {
     APUS_REQUIRE(m->e_lo == 0 && m->e_hi == m->n_experts,
                  "this model holds experts [%d,%d) of %d: drive it layer by layer (apus_cuda_model_attn_half ...)",
                  m->e_lo, m->e_hi, m->n_experts);
@@ -373,11 +411,30 @@ static int model_chunk(ApusCudaModel *m, const int64_t *ids_tm, int s, bool want
     const BlockBufs bb = {C.x.as<float>(), C.y.as<float>(), C.sub.as<float>(), C.post.as<float>(), C.comb.as<float>(),
                           C.raw.as<float>()};
     if (embed_rows(m->embed, m->embed_bf16, ids_tm, T, hc, dim, h, st)) return 1;
-    for (int i = 0; i < m->n_layers; i++)
+    for (int i = 0; i < m->n_layers; i++) {
         if (block_chunk(m->layers[i], m->states[i], &h, &hn, ids_tm, m->B, s, m->pos, hc, m->iters, m->hc_eps, m->norm_eps,
                         bb, C.sb, st))
             return 1;
-    if (want_head) {
+        if (ex && ex->mh_all)
+            for (int tg = 0; tg < ex->n_targets; tg++)
+                if (ex->targets[tg] == i) {
+                    hc_mean_kernel<<<dim3(ceil_div(dim, 256), T), 256, 0, st>>>(h, hc, dim, ex->mh_all + (size_t)tg * dim,
+                                                                               ex->n_targets * dim);
+                    APUS_LAUNCHED();
+                }
+    }
+    if (ex && ex->h_all)
+        APUS_CUDA_OK(cudaMemcpyAsync(ex->h_all, h, (size_t)T * hc * dim * 4, cudaMemcpyDeviceToDevice, st));
+    if (ex && ex->logits_all) {
+        // x and y of the chunk are free by now: they hold the collapsed and the normed rows
+        if (head_rows(m, h, T, bb.x, bb.y, ex->logits_all, ex->tok_all, st)) return 1;
+        // the last position's rows are also what a plain call leaves in the model's own buffers
+        const size_t last = (size_t)(s - 1) * m->B;
+        APUS_CUDA_OK(cudaMemcpyAsync(m->logits.p, ex->logits_all + last * m->vocab, (size_t)m->B * m->vocab * 4,
+                                     cudaMemcpyDeviceToDevice, st));
+        if (ex->tok_all)
+            APUS_CUDA_OK(cudaMemcpyAsync(m->tok.p, ex->tok_all + last, (size_t)m->B * 4, cudaMemcpyDeviceToDevice, st));
+    } else if (want_head) {
         m->h_cur = h + (size_t)(s - 1) * m->B * hc * dim;
         if (model_head(m, st)) return 1;
     }
@@ -819,12 +876,85 @@ int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s, float *
     return apus_cuda_model_forward_group(&m, 1, &ids, s, &logits, &next);
 }
 
+// c/model.h:651-720 with every output the reference's variants offer (logits_all, h_out of
+// apus_model_forward_h, mh_out of apus_model_forward_mh), B sequences: ids [B][s]; logits
+// [B][V] (last position) or [B][s][V]; next [B] or [B][s]; h_out [B][s][hc*dim]; mh_out
+// [B][s][n_targets*dim].  The positions run as chunks; a row of a chunk equals the step's.
+static int forward_ex(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int logits_all, int32_t *next,
+                      float *h_out, float *mh_out, const int *targets, int n_targets, const char *what,
+                      bool keep_h_dev = false) {
+    if (!m) { set_error("NULL model"); return 1; }
+    if (s <= 0) return 0;
+    APUS_REQUIRE(m->pos + s <= m->max_pos, "%s: position %lld + %d exceeds max_pos %d", what, m->pos, s, m->max_pos);
+    APUS_REQUIRE(!mh_out || (targets && n_targets >= 1), "%s: mh_out needs the target layers", what);
+    for (int i = 0; mh_out && i < n_targets; i++)
+        APUS_REQUIRE(targets[i] >= 0 && targets[i] < m->n_layers, "%s: target layer %d of %d", what, targets[i], m->n_layers);
+    if (ids_in_range(m, ids, (size_t)m->B * s, what)) return 1;
+    cudaStream_t st = mstream(m);
+    const size_t B = m->B, V = m->vocab, hd = (size_t)m->hc * m->dim, md = (size_t)n_targets * m->dim;
+    std::vector<int64_t> cols((size_t)s * B);
+    for (int t = 0; t < s; t++)
+        for (size_t b = 0; b < B; b++) cols[(size_t)t * B + b] = ids[b * s + t];
+    void *dcols;
+    if (m->ws[23].get(cols.size() * 8, &dcols)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(dcols, cols.data(), cols.size() * 8, cudaMemcpyHostToDevice, st));
+    int per = chunks_enabled() ? chunk_rows() / (int)B : 1;
+    if (per < 1) per = 1;
+    if (per > s) per = s;
+    ApusCudaModel::Chunk &C = m->ck;
+    const bool all = logits_all != 0;
+    if (all && (C.logits.get((size_t)per * B * V * 4, nullptr) || C.tok.get((size_t)per * B * 4, nullptr))) return 1;
+    APUS_REQUIRE(!keep_h_dev || per >= s, "%s: %d positions do not fit one chunk", what, s);
+    if ((h_out || keep_h_dev) && C.hx.get((size_t)per * B * hd * 4, nullptr)) return 1;
+    if (mh_out && C.mhx.get((size_t)per * B * md * 4, nullptr)) return 1;
+    for (int t0 = 0; t0 < s; t0 += per) {
+        const int n = s - t0 < per ? s - t0 : per;
+        ChunkExtra ex;
+        if (all) { ex.logits_all = C.logits.as<float>(); ex.tok_all = C.tok.as<int32_t>(); }
+        if (h_out || keep_h_dev) ex.h_all = C.hx.as<float>();
+        if (mh_out) { ex.mh_all = C.mhx.as<float>(); ex.targets = targets; ex.n_targets = n_targets; }
+        if (model_chunk(m, (const int64_t *)dcols + (size_t)t0 * B, n, !all && t0 + n == s, st, &ex)) return 1;
+        for (int t = 0; t < n; t++) {                      // row (t, b) of the chunk -> [b][t0 + t] of the caller
+            if (all && logits)
+                APUS_CUDA_OK(cudaMemcpy2DAsync(logits + (size_t)(t0 + t) * V, (size_t)s * V * 4, C.logits.as<float>() + (size_t)t * B * V,
+                                               V * 4, V * 4, B, cudaMemcpyDeviceToHost, st));
+            if (all && next)
+                APUS_CUDA_OK(cudaMemcpy2DAsync(next + t0 + t, (size_t)s * 4, C.tok.as<int32_t>() + (size_t)t * B, 4, 4, B,
+                                               cudaMemcpyDeviceToHost, st));
+            if (h_out)
+                APUS_CUDA_OK(cudaMemcpy2DAsync(h_out + (size_t)(t0 + t) * hd, (size_t)s * hd * 4, C.hx.as<float>() + (size_t)t * B * hd,
+                                               hd * 4, hd * 4, B, cudaMemcpyDeviceToHost, st));
+            if (mh_out)
+                APUS_CUDA_OK(cudaMemcpy2DAsync(mh_out + (size_t)(t0 + t) * md, (size_t)s * md * 4, C.mhx.as<float>() + (size_t)t * B * md,
+                                               md * 4, md * 4, B, cudaMemcpyDeviceToHost, st));
+        }
+    }
+    if (!all) {
+        if (logits) APUS_CUDA_OK(cudaMemcpyAsync(logits, m->logits.p, B * V * 4, cudaMemcpyDeviceToHost, st));
+        if (next) APUS_CUDA_OK(cudaMemcpyAsync(next, m->tok.p, B * 4, cudaMemcpyDeviceToHost, st));
+    }
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "%s: a bounded wait expired inside a tcgen05 kernel (code %d)", what, stt);
+    return 0;
+}
+
+int apus_cuda_model_forward_h(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int logits_all, int32_t *next,
+                              float *h_out) {
+    return forward_ex(m, ids, s, logits, logits_all, next, h_out, nullptr, nullptr, 0, "model_forward_h");
+}
+int apus_cuda_model_forward_mh(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int logits_all, int32_t *next,
+                               const int *targets, int n_targets, float *mh_out) {
+    return forward_ex(m, ids, s, logits, logits_all, next, nullptr, mh_out, targets, n_targets, "model_forward_mh");
+}
+
 // c/model.h:651-720 with logits_all: the rows of every position (the verify batch of
-// speculative decoding, c/mtp.h step 2).  Positions are consumed as consecutive steps,
-// which the reference defines to be equal to its batched call.
+// speculative decoding, c/mtp.h step 2), in one pass over the positions unless chunks are off.
 int apus_cuda_model_forward_all(ApusCudaModel *m, const int64_t *ids, int s, float *logits_all, int32_t *next_all) {
     if (!m) { set_error("NULL model"); return 1; }
     if (s <= 0) return 0;
+    if (chunks_enabled() && m->e_lo == 0 && m->e_hi == m->n_experts)
+        return forward_ex(m, ids, s, logits_all, 1, next_all, nullptr, nullptr, nullptr, 0, "model_forward_all");
     APUS_REQUIRE(m->pos + s <= m->max_pos, "model_forward: position %lld + %d exceeds max_pos %d", m->pos, s, m->max_pos);
     if (ids_in_range(m, ids, (size_t)m->B * s, "model_forward_all")) return 1;
     cudaStream_t st = mstream(m);
@@ -924,25 +1054,25 @@ static int snap_copy(DevBuf &dst, const DevBuf &src, size_t bytes, bool to_snap,
     APUS_CUDA_OK(cudaMemcpyAsync(dst.p, src.p, bytes, cudaMemcpyDeviceToDevice, st));
     return 0;
 }
+static int snap_layer(const ApusAttnCfg &c, StateDev &S, ApusCudaSnap::Layer &L, size_t B, bool take, cudaStream_t st) {
+    const size_t wb = B * c.window * c.head_dim * 4, cb = S.comp.carry * B * 4, ib = S.idx.carry * B * 4;
+    DevBuf *pairs[5][2] = {{&L.win, &S.win}, {&L.ckv, &S.comp.kv}, {&L.csc, &S.comp.sc}, {&L.ikv, &S.idx.kv},
+                           {&L.isc, &S.idx.sc}};
+    const size_t bytes[5] = {wb, c.ratio ? cb : 0, c.ratio ? cb : 0, c.ratio && c.has_indexer ? ib : 0,
+                             c.ratio && c.has_indexer ? ib : 0};
+    for (int k = 0; k < 5; k++)
+        if (take ? snap_copy(*pairs[k][0], *pairs[k][1], bytes[k], true, st)
+                 : snap_copy(*pairs[k][1], *pairs[k][0], bytes[k], false, st))
+            return 1;
+    if (take) { L.comp_nb = S.comp.nb; L.idx_nb = S.idx.nb; }
+    else { S.comp.nb = L.comp_nb; S.idx.nb = L.idx_nb; }
+    return 0;
+}
 static int snap_move(ApusCudaModel *m, ApusCudaSnap *sn, bool take) {
     cudaStream_t st = mstream(m);
     const size_t B = m->B;
-    for (int i = 0; i < m->n_layers; i++) {
-        const ApusAttnCfg &c = m->layers[i].attn.cfg;
-        StateDev &S = m->states[i];
-        ApusCudaSnap::Layer &L = sn->layers[i];
-        const size_t wb = B * c.window * c.head_dim * 4, cb = S.comp.carry * B * 4, ib = S.idx.carry * B * 4;
-        DevBuf *pairs[5][2] = {{&L.win, &S.win}, {&L.ckv, &S.comp.kv}, {&L.csc, &S.comp.sc}, {&L.ikv, &S.idx.kv},
-                               {&L.isc, &S.idx.sc}};
-        const size_t bytes[5] = {wb, c.ratio ? cb : 0, c.ratio ? cb : 0, c.ratio && c.has_indexer ? ib : 0,
-                                 c.ratio && c.has_indexer ? ib : 0};
-        for (int k = 0; k < 5; k++)
-            if (take ? snap_copy(*pairs[k][0], *pairs[k][1], bytes[k], true, st)
-                     : snap_copy(*pairs[k][1], *pairs[k][0], bytes[k], false, st))
-                return 1;
-        if (take) { L.comp_nb = S.comp.nb; L.idx_nb = S.idx.nb; }
-        else { S.comp.nb = L.comp_nb; S.idx.nb = L.idx_nb; }
-    }
+    for (int i = 0; i < m->n_layers; i++)
+        if (snap_layer(m->layers[i].attn.cfg, m->states[i], sn->layers[i], B, take, st)) return 1;
     DevBuf *top[3][2] = {{&sn->pos_dev, &m->pos_dev}, {&sn->tok, &m->tok}, {&sn->ids, &m->ids}};
     const size_t tb[3] = {256, B * 4, B * 8};
     for (int k = 0; k < 3; k++)
@@ -1002,19 +1132,265 @@ void apus_cuda_snap_free(ApusCudaSnap *sn) {
 // match roll back and feed the true prefix again.  The picks are drawn on the device; the
 // rollback rewinds the sampler streams with the rest of the state, so a round consumes
 // exactly one uniform per token that stays.
+// ---- MTP draft head (c/mtp.h:66-110, 303-357) -----------------------------------------------------
+// e = enorm(embed(id)) -> e_proj; x_j = hnorm(h_j) -> h_proj per hc stream; bf16(e + x_j) -> one full
+// block (its own attention state) -> its own hc_head collapse and norm -> the parent's LM head.
+struct ApusCudaMtp {
+    ApusCudaModel *m = nullptr;
+    LayerDev block;
+    StateDev state;
+    DevQW *e_proj = nullptr, *h_proj = nullptr;
+    const float *enorm_w = nullptr, *hnorm_w = nullptr, *norm_w = nullptr, *hc_head_fn = nullptr, *hc_head_base = nullptr;
+    float hc_head_scale = 0.f;
+    WeightOwner own;
+    int rows = 0, s_cap = 0;                     // capacity of the buffers below: rows = positions x sequences
+    DevBuf e, en, ep, hn, hp, x0, x1, bx, by, bsub, post, comb, raw, sa, ext, xq, xs, ids, hin, yh, yn, logits, tok, hlast, ws[24];
+    StepBufs sb;
+    ApusCudaSnap::Layer snap;
+    void release() {
+        DevBuf *b[] = {&e, &en, &ep, &hn, &hp, &x0, &x1, &bx, &by, &bsub, &post, &comb, &raw, &sa, &ext, &xq, &xs, &ids, &hin,
+                       &yh, &yn, &logits, &tok, &hlast, &snap.win, &snap.ckv, &snap.csc, &snap.ikv, &snap.isc};
+        for (DevBuf *p : b) p->release();
+        for (auto &w : ws) w.release();
+        state.release();
+        if (block.moe) apus_cuda_moe_destroy(block.moe);
+        block.moe = nullptr;
+        own.release();
+    }
+};
+
+__global__ void mtp_mix_kernel(const float *__restrict__ ep, const float *__restrict__ hp, int hc, int dim, float *__restrict__ x) {
+    const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;       // r = token * hc + stream
+    if (i < dim) x[(size_t)r * dim + i] = bf16_round(__fadd_rn(ep[(size_t)(r / hc) * dim + i], hp[(size_t)r * dim + i]));
+}
+
+static int mtp_bufs(ApusCudaMtp *mt, int s) {
+    ApusCudaModel *m = mt->m;
+    const size_t T = (size_t)m->B * s, dim = m->dim, hc = m->hc;
+    if ((int)T <= mt->rows && s <= mt->s_cap) return 0;
+    const size_t R = (int)T > mt->rows ? T : (size_t)mt->rows;
+    const int sc = s > mt->s_cap ? s : mt->s_cap;
+    const ApusAttnCfg &c = mt->block.attn.cfg;
+    const long long max_nb = c.ratio ? m->max_pos / c.ratio + 2 : 8;
+    const long long wide = c.has_indexer && c.idx_topk > max_nb ? c.idx_topk : max_nb;
+    if (mt->e.get(R * dim * 4, nullptr) || mt->en.get(R * dim * 4, nullptr) || mt->ep.get(R * dim * 4, nullptr) ||
+        mt->hn.get(R * hc * dim * 4, nullptr) || mt->hp.get(R * hc * dim * 4, nullptr) || mt->x0.get(R * hc * dim * 4, nullptr) ||
+        mt->x1.get(R * hc * dim * 4, nullptr) || mt->bx.get(R * dim * 4, nullptr) || mt->by.get(R * dim * 4, nullptr) ||
+        mt->bsub.get(R * dim * 4, nullptr) || mt->post.get(R * hc * 4, nullptr) || mt->comb.get(R * hc * hc * 4, nullptr) ||
+        mt->raw.get(R * ((2 + hc) * hc + 1) * 4, nullptr) || mt->xq.get(R * hc * dim, nullptr) ||
+        mt->xs.get(R * hc * (dim / 128 + 1) * 4, nullptr) || mt->ids.get(R * 8, nullptr) ||
+        mt->ext.get((size_t)m->B * (c.window + sc) * c.head_dim * 4, nullptr))
+        return 1;
+    ApusAttnCfg sized = c;
+    sized.has_indexer = 0;
+    if (attn_step_bufs(sized, wide, (int)R, mt->ws, &mt->sb)) return 1;
+    mt->sb.sa_cap = sparse_attn_scratch(c.n_heads, (int)(c.window + wide + 8), (int)R);
+    if (mt->sa.get(mt->sb.sa_cap, &mt->sb.sa)) return 1;
+    mt->sb.ext = mt->ext.as<float>();
+    mt->rows = (int)R; mt->s_cap = sc;
+    return 0;
+}
+
+// h_in (device) [s][B][hc*dim] time-major, ids_tm (device) [s][B]; leaves the last position's logits,
+// pick and post-block hidden in mt->logits / tok / hlast.  Positions start_pos .. start_pos + s - 1.
+static int mtp_forward_dev(ApusCudaMtp *mt, const float *h_in, const int64_t *ids_tm, int s, long long start_pos,
+                           cudaStream_t st) {
+    ApusCudaModel *m = mt->m;
+    const int B = m->B, dim = m->dim, hc = m->hc;
+    APUS_REQUIRE(s >= 1 && start_pos >= 0 && start_pos + s <= m->max_pos, "mtp_forward: positions %lld + %d exceed max_pos %d",
+                 start_pos, s, m->max_pos);
+    int per = chunk_rows() / B;
+    if (per < 1) per = 1;
+    if (per > s) per = s;
+    if (mtp_bufs(mt, per)) return 1;
+    const BlockBufs bb = {mt->bx.as<float>(), mt->by.as<float>(), mt->bsub.as<float>(), mt->post.as<float>(),
+                          mt->comb.as<float>(), mt->raw.as<float>()};
+    float *last = nullptr;
+    for (int t0 = 0; t0 < s; t0 += per) {
+        const int n = s - t0 < per ? s - t0 : per, T = n * B;
+        const int64_t *ids = ids_tm + (size_t)t0 * B;
+        const float *hin = h_in + (size_t)t0 * B * hc * dim;
+        if (embed_rows(m->embed, m->embed_bf16, ids, T, 1, dim, mt->e.as<float>(), st)) return 1;
+        if (rms_norm(mt->e.as<float>(), mt->enorm_w, m->norm_eps, mt->en.as<float>(), dim, T, st)) return 1;
+        if (qlinear_dev(mt->e_proj, mt->en.as<float>(), mt->ep.as<float>(), T, mt->xq.as<uint8_t>(), mt->xs.as<float>(), true, st)) return 1;
+        if (rms_norm(hin, mt->hnorm_w, m->norm_eps, mt->hn.as<float>(), dim, (int64_t)T * hc, st)) return 1;
+        if (qlinear_dev(mt->h_proj, mt->hn.as<float>(), mt->hp.as<float>(), T * hc, mt->xq.as<uint8_t>(), mt->xs.as<float>(), true, st)) return 1;
+        float *x = mt->x0.as<float>(), *xa = mt->x1.as<float>();
+        mtp_mix_kernel<<<dim3(ceil_div(dim, 256), T * hc), 256, 0, st>>>(mt->ep.as<float>(), mt->hp.as<float>(), hc, dim, x);
+        APUS_LAUNCHED();
+        if (block_chunk(mt->block, mt->state, &x, &xa, ids, B, n, start_pos + t0, hc, m->iters, m->hc_eps, m->norm_eps, bb,
+                        mt->sb, st))
+            return 1;
+        last = x + (size_t)(n - 1) * B * hc * dim;
+    }
+    // the block's own collapse and norm, the parent's head (c/mtp.h:341-355), last position only
+    if (mt->hlast.get((size_t)B * hc * dim * 4, nullptr) || mt->yh.get((size_t)B * dim * 4, nullptr) ||
+        mt->yn.get((size_t)B * dim * 4, nullptr) || mt->logits.get((size_t)B * m->vocab * 4, nullptr) ||
+        mt->tok.get((size_t)B * 4, nullptr))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(mt->hlast.p, last, (size_t)B * hc * dim * 4, cudaMemcpyDeviceToDevice, st));
+    if (mhc_head(last, dim, hc, mt->hc_head_fn, mt->hc_head_scale, mt->hc_head_base, m->norm_eps, m->hc_eps,
+                 mt->yh.as<float>(), B, st, mt->raw.as<float>()))
+        return 1;
+    if (rms_norm(mt->yh.as<float>(), mt->norm_w, m->norm_eps, mt->yn.as<float>(), dim, B, st)) return 1;
+    if (f32_linear(m->head, mt->yn.as<float>(), mt->logits.as<float>(), B, dim, m->vocab,
+                   (m->head_bf16 ? APUS_CUDA_W_BF16 : 0) | APUS_LIN_CLASS(APUS_CUDA_TREE_HEAD), st))
+        return 1;
+    return argmax_rows(mt->logits.as<float>(), m->vocab, B, mt->tok.as<int32_t>(), st);
+}
+
+void apus_cuda_mtp_destroy(ApusCudaMtp *mt) {
+    if (!mt) return;
+    cudaDeviceSynchronize();
+    mt->release();
+    delete mt;
+}
+
+int apus_cuda_mtp_reset(ApusCudaMtp *mt) {
+    if (!mt) { set_error("NULL mtp"); return 1; }
+    const ApusAttnCfg &c = mt->block.attn.cfg;
+    if (attn_state_init(c, mt->state, mt->m->B, c.ratio ? mt->m->max_pos / c.ratio + 2 : 0)) return 1;
+    APUS_CUDA_OK(cudaStreamSynchronize(ctx().stream));
+    return 0;
+}
+
+ApusCudaMtp *apus_cuda_mtp_create(ApusCudaModel *m, const ApusCudaMtpDesc *d) {
+    if (!m || !d) { set_error("mtp_create: NULL argument"); return nullptr; }
+    if (m->e_lo != 0 || m->e_hi != m->n_experts) { set_error("mtp_create: the parent holds a slice of the experts"); return nullptr; }
+    const int dim = m->dim, hc = m->hc;
+    if (d->block.acfg.dim != dim || d->e_proj.O != dim || d->e_proj.K != dim || d->h_proj.O != dim || d->h_proj.K != dim) {
+        set_error("mtp_create: block / e_proj / h_proj do not match the parent's dim %d", dim);
+        return nullptr;
+    }
+    ApusCudaMtp *mt = new ApusCudaMtp();
+    mt->m = m;
+    bool ok = layer_weights(d->block, hc, m->vocab, &mt->block, &mt->own, 0, -1) == 0;
+    if (ok) {
+        const int half = d->block.acfg.rope_dim / 2;
+        mt->block.cs = rope_rows_dev(d->block.cos, d->block.sin, d->block.rope_rows, half, m->rope);
+        mt->block.rope_rows = d->block.rope_rows;
+        if (!mt->block.cs || d->block.rope_rows < m->max_pos) {
+            set_error("mtp_create: the block's rope table has %d rows, %d needed", d->block.rope_rows, m->max_pos);
+            ok = false;
+        }
+    }
+    if (ok) {
+        mt->e_proj = get_qw(&mt->own, 8, d->e_proj.codes, d->e_proj.scales, dim, dim);
+        mt->h_proj = get_qw(&mt->own, 8, d->h_proj.codes, d->h_proj.scales, dim, dim);
+        mt->enorm_w = (const float *)get_dense(&mt->own, d->enorm_w, (size_t)dim * 4);
+        mt->hnorm_w = (const float *)get_dense(&mt->own, d->hnorm_w, (size_t)dim * 4);
+        mt->norm_w = (const float *)get_dense(&mt->own, d->norm_w, (size_t)dim * 4);
+        mt->hc_head_fn = (const float *)get_dense(&mt->own, d->hc_head_fn, (size_t)hc * hc * dim * 4);
+        mt->hc_head_base = (const float *)get_dense(&mt->own, d->hc_head_base, (size_t)hc * 4);
+        mt->hc_head_scale = d->hc_head_scale;
+        ok = mt->e_proj && mt->h_proj && mt->enorm_w && mt->hnorm_w && mt->norm_w && mt->hc_head_fn && mt->hc_head_base;
+    }
+    if (ok) ok = apus_cuda_mtp_reset(mt) == 0;
+    if (!ok) { apus_cuda_mtp_destroy(mt); return nullptr; }
+    return mt;
+}
+
+// c/mtp.h:303-357 apus_mtp_forward for every sequence: h_in [B][s][hc*dim], ids [B][s] (host);
+// logits [B][V], next [B], h_last [B][hc*dim] of the last position (all nullable).
+int apus_cuda_mtp_forward(ApusCudaMtp *mt, const float *h_in, const int64_t *ids, int s, int64_t start_pos, float *logits,
+                          int32_t *next, float *h_last) {
+    if (!mt || !h_in || !ids) { set_error("mtp_forward: NULL argument"); return 1; }
+    if (s <= 0) return 0;
+    ApusCudaModel *m = mt->m;
+    cudaStream_t st = mstream(m);
+    const size_t B = m->B, hd = (size_t)m->hc * m->dim;
+    if (ids_in_range(m, ids, B * s, "mtp_forward")) return 1;
+    std::vector<int64_t> cols((size_t)s * B);
+    for (int t = 0; t < s; t++)
+        for (size_t b = 0; b < B; b++) cols[(size_t)t * B + b] = ids[b * s + t];
+    if (mt->ids.get(cols.size() * 8, nullptr) || mt->hin.get((size_t)s * B * hd * 4, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(mt->ids.p, cols.data(), cols.size() * 8, cudaMemcpyHostToDevice, st));
+    for (int t = 0; t < s; t++)                          // [b][t] of the caller -> row (t, b)
+        APUS_CUDA_OK(cudaMemcpy2DAsync(mt->hin.as<float>() + (size_t)t * B * hd, hd * 4, h_in + (size_t)t * hd, (size_t)s * hd * 4,
+                                       hd * 4, B, cudaMemcpyHostToDevice, st));
+    if (mtp_forward_dev(mt, mt->hin.as<float>(), mt->ids.as<int64_t>(), s, start_pos, st)) return 1;
+    if (logits) APUS_CUDA_OK(cudaMemcpyAsync(logits, mt->logits.p, B * m->vocab * 4, cudaMemcpyDeviceToHost, st));
+    if (next) APUS_CUDA_OK(cudaMemcpyAsync(next, mt->tok.p, B * 4, cudaMemcpyDeviceToHost, st));
+    if (h_last) APUS_CUDA_OK(cudaMemcpyAsync(h_last, mt->hlast.p, B * hd * 4, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "mtp_forward: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
+// The proposer of the draft/verify loop below when it is the MTP head (c/mtp.h:441-470, 500-528, 600-612).
+struct MtpProposer {
+    ApusCudaMtp *mt;
+    DevBuf ids1;                  // one draft token on the device
+    // draft chain from the logits the last mtp_forward_dev left: d1 = their argmax; d_{i+1} = MTP(own hidden, d_i)
+    int chain(long long start_pos, int64_t *drafts, int depth) {
+        ApusCudaModel *m = mt->m;
+        cudaStream_t st = mstream(m);
+        int32_t tok = 0;
+        if (ids1.get(8, nullptr)) return 1;
+        for (int i = 0; i < depth; i++) {
+            APUS_CUDA_OK(cudaMemcpyAsync(&tok, mt->tok.p, 4, cudaMemcpyDeviceToHost, st));
+            APUS_CUDA_OK(cudaStreamSynchronize(st));
+            drafts[i] = tok;
+            if (i + 1 == depth || start_pos + i >= m->max_pos) { for (int j = i + 1; j < depth; j++) drafts[j] = tok; break; }
+            const int64_t id = tok;
+            APUS_CUDA_OK(cudaMemcpyAsync(ids1.p, &id, 8, cudaMemcpyHostToDevice, st));
+            // the head's own hidden (copied out of its buffers first: the next call overwrites them)
+            if (mt->hin.get((size_t)m->hc * m->dim * 4, nullptr)) return 1;
+            APUS_CUDA_OK(cudaMemcpyAsync(mt->hin.p, mt->hlast.p, (size_t)m->hc * m->dim * 4, cudaMemcpyDeviceToDevice, st));
+            if (mtp_forward_dev(mt, mt->hin.as<float>(), ids1.as<int64_t>(), 1, start_pos + i, st)) return 1;
+        }
+        return 0;
+    }
+    int snap(bool take) {
+        return snap_layer(mt->block.attn.cfg, mt->state, mt->snap, (size_t)mt->m->B, take, mstream(mt->m));
+    }
+};
+
+static int spec_loop(ApusCudaModel *m, const int64_t *prompt, int n_prompt, int n_gen, int depth, ApusCudaDraftFn draft,
+                     void *draft_ctx, ApusCudaMtp *mt, int32_t *out_tokens, uint64_t *stats);
+
+int apus_cuda_model_spec_generate_mtp(ApusCudaModel *m, ApusCudaMtp *mt, const int64_t *prompt, int n_prompt, int n_gen,
+                                      int depth, int32_t *out_tokens, uint64_t *stats) {
+    if (!m || !mt || mt->m != m) { set_error("model_spec_generate_mtp: the draft head belongs to another model"); return 1; }
+    return spec_loop(m, prompt, n_prompt, n_gen, depth, nullptr, nullptr, mt, out_tokens, stats);
+}
+
 int apus_cuda_model_spec_generate(ApusCudaModel *m, const int64_t *prompt, int n_prompt, int n_gen, int depth,
                                   ApusCudaDraftFn draft, void *draft_ctx, int32_t *out_tokens, uint64_t *stats) {
     if (!m || !draft) { set_error("model_spec_generate: NULL argument"); return 1; }
+    return spec_loop(m, prompt, n_prompt, n_gen, depth, draft, draft_ctx, nullptr, out_tokens, stats);
+}
+
+// c/mtp.h:472-616: prefill, then draft / verify / accept-walk / state fix-up per step.
+static int spec_loop(ApusCudaModel *m, const int64_t *prompt, int n_prompt, int n_gen, int depth, ApusCudaDraftFn draft,
+                     void *draft_ctx, ApusCudaMtp *mt, int32_t *out_tokens, uint64_t *stats) {
     APUS_REQUIRE(m->B == 1, "model_spec_generate: one sequence per model (batch %d given)", m->B);
     APUS_REQUIRE(n_prompt >= 1 && n_gen >= 1 && depth >= 1 && depth <= 64, "model_spec_generate: bad sizes");
+    APUS_REQUIRE(!mt || chunks_enabled(), "model_spec_generate_mtp: needs the chunked forward (apus_cuda_set_prefill_chunk)");
     enum { EMITTED, BATCHES, BATCH_TOKENS, REFEED_TOKENS, OFFERED, ACCEPTED, D1_OFFERED, D1_HITS };
     uint64_t st8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    cudaStream_t st = mstream(m);
+    const size_t hd = (size_t)m->hc * m->dim;
     int32_t pick = 0;
-    if (apus_cuda_model_forward(m, prompt, n_prompt, nullptr, &pick)) return 1;
-    int64_t held = pick, q = m->pos;
     std::vector<int64_t> drafts((size_t)depth), batch((size_t)depth);
     std::vector<int32_t> picks((size_t)depth);
-    draft(draft_ctx, q, drafts.data(), depth);
+    MtpProposer mp{mt, {}};
+    DevBuf h_keep, ids_keep;                              // hiddens and ids of the rows the draft head replays
+    if (mt) {
+        // main prefill keeping every position's hidden, then the head over the true (hidden, id) pairs
+        APUS_REQUIRE(n_prompt * m->B <= chunk_rows(), "model_spec_generate_mtp: a prompt of %d tokens does not fit one chunk", n_prompt);
+        if (apus_cuda_mtp_reset(mt)) return 1;
+        if (forward_ex(m, prompt, n_prompt, nullptr, 0, &pick, nullptr, nullptr, nullptr, 0, "model_spec_generate_mtp", true)) return 1;
+        if (ids_keep.get((size_t)(n_prompt > depth ? n_prompt : depth) * 8, nullptr)) return 1;
+        APUS_CUDA_OK(cudaMemcpyAsync(ids_keep.p, prompt, (size_t)n_prompt * 8, cudaMemcpyHostToDevice, st));
+        if (mtp_forward_dev(mt, m->ck.hx.as<float>(), ids_keep.as<int64_t>(), n_prompt, 0, st)) return 1;
+        if (mp.snap(true) || mp.chain(m->pos, drafts.data(), depth)) return 1;
+    } else {
+        if (apus_cuda_model_forward(m, prompt, n_prompt, nullptr, &pick)) return 1;
+        draft(draft_ctx, m->pos, drafts.data(), depth);
+    }
+    int64_t held = pick, q = m->pos;
     ApusCudaSnap *snap = nullptr;
     int emitted = 0, rc = 0;
     while (emitted < n_gen && !rc) {
@@ -1028,7 +1404,9 @@ int apus_cuda_model_spec_generate(ApusCudaModel *m, const int64_t *prompt, int n
         snap = s2;
         batch[0] = held;
         for (int j = 1; j < D; j++) batch[j] = drafts[j];
-        if (apus_cuda_model_forward_all(m, batch.data(), D, nullptr, picks.data())) { rc = 1; break; }
+        // verify batch: one pass over the D positions, every row's pick (and hidden, for the draft head)
+        if (mt ? forward_ex(m, batch.data(), D, nullptr, 1, picks.data(), nullptr, nullptr, nullptr, 0, "model_spec_generate_mtp", true)
+               : apus_cuda_model_forward_all(m, batch.data(), D, nullptr, picks.data())) { rc = 1; break; }
         st8[BATCHES]++; st8[BATCH_TOKENS] += (uint64_t)D;
         int matched = 0;
         int64_t last = -1;
@@ -1042,6 +1420,10 @@ int apus_cuda_model_spec_generate(ApusCudaModel *m, const int64_t *prompt, int n
             } else { last = x; break; }
         }
         if (last < 0) last = picks[D - 1];               // full match: the bonus token
+        if (mt) {                                         // the verify batch's hiddens outlive the re-feed below
+            if (h_keep.get((size_t)depth * hd * 4, nullptr)) { rc = 1; break; }
+            if (cudaMemcpyAsync(h_keep.p, m->ck.hx.p, (size_t)(matched + 1) * hd * 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess) { rc = 1; break; }
+        }
         if (matched < D - 1) {                           // partial: roll back, feed the true prefix again
             if (apus_cuda_model_restore(m, snap) || apus_cuda_model_forward_all(m, batch.data(), matched + 1, nullptr, picks.data())) {
                 rc = 1;
@@ -1051,10 +1433,20 @@ int apus_cuda_model_spec_generate(ApusCudaModel *m, const int64_t *prompt, int n
         }
         held = last;
         q += matched + 1;
-        draft(draft_ctx, q, drafts.data(), depth);
+        if (mt) {
+            // the head's clean state (true pairs only), the newly accepted pairs in one pass, the next chain
+            if (mp.snap(false)) { rc = 1; break; }
+            if (cudaMemcpyAsync(ids_keep.p, batch.data(), (size_t)(matched + 1) * 8, cudaMemcpyHostToDevice, st) != cudaSuccess) { rc = 1; break; }
+            if (mtp_forward_dev(mt, h_keep.as<float>(), ids_keep.as<int64_t>(), matched + 1, q - matched - 1, st) || mp.snap(true) ||
+                mp.chain(q, drafts.data(), depth)) { rc = 1; break; }
+        } else {
+            draft(draft_ctx, q, drafts.data(), depth);
+        }
     }
     st8[EMITTED] = (uint64_t)emitted;
     if (snap) apus_cuda_snap_free(snap);
+    if (mt) cudaStreamSynchronize(st);
+    h_keep.release(); ids_keep.release(); mp.ids1.release();
     if (stats) memcpy(stats, st8, sizeof st8);
     return rc;
 }

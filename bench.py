@@ -471,7 +471,7 @@ def model_main_ep(a):
             "tokens_fnv1a": digest, "digest_tokens_per_seq": Wm + K + 2,
             "strong_bs32": strong32, "strong_bs1": strong1,
             "prefill": {"tokens": world * B * a.prompt, "ms": prefill_ms,
-                        "note": "prompt consumed as consecutive decode steps"},
+                        "note": "expert-parallel loop: prompt consumed as consecutive decode steps"},
             "roofline": None, "weights": {"bytes_per_rank": W.bytes}, "cuda_graph": graph_note,
             "note": "expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine per layer; "
                     "the per-kernel roofline is reported by the 1-GPU run"}
@@ -640,7 +640,7 @@ def model_main(a):
                                 "avg_launch_us": st1[0] / max(st1[2], 1) * 1e3, "avg_unique_experts": st1[3] / max(st1[2], 1),
                                 "down_proj_frac": st1[3] * W2_BYTES / (st1[1] * 1e-3) / 1e9 / peak if st1[1] > 0 else None}},
         "prefill": {"tokens": B * a.prompt, "ms": prefill_ms, "tok_s": B * a.prompt / (prefill_ms * 1e-3),
-                    "note": "prompt consumed as consecutive decode steps (no batched prefill kernel yet)"},
+                    "note": "prompt consumed in chunks of positions (2048 rows = positions x sequences per pass)"},
         "weights": {"bytes": W.bytes, "generate_s": t_gen},
         "roofline": {"kernel": "gemm_tc_kernel<pair> (tcgen05 block-scaled MXFP4 expert gate/up GEMV + SwiGLU), "
                                "all layers of the timed steps",

@@ -624,6 +624,46 @@ int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n,
                                    int n_gen, int32_t *const *out_tokens,
                                    float *ms_prefill, float *ms_decode);
 
+/* c/model.h:115-129, 731-743 apus_model_forward_h / apus_model_forward_mh for every sequence: the
+ * forward with, besides the logits, the hidden state after the last block of every position
+ * (h_out [batch, s, hc_mult * dim], BF16-valued f32, the MTP head's input) or, after each layer
+ * listed in `targets`, the mean over the hc streams of every position (mh_out
+ * [batch, s, n_targets * dim], f32 accumulate in stream order, BF16 result: the DSpark
+ * drafter's main_hidden; the reference reads the target list from the checkpoint's dspark
+ * config, here the caller passes it).  ids [batch, s]; logits [batch, vocab] of the last
+ * position, or [batch, s, vocab] when logits_all; next [batch] or [batch, s] the picks
+ * (greedy, or sampled under apus_cuda_model_set_sampling); all outputs nullable. */
+int apus_cuda_model_forward_h(ApusCudaModel *m, const int64_t *ids, int s, float *logits,
+                              int logits_all, int32_t *next, float *h_out);
+int apus_cuda_model_forward_mh(ApusCudaModel *m, const int64_t *ids, int s, float *logits,
+                               int logits_all, int32_t *next, const int *targets,
+                               int n_targets, float *mh_out);
+
+/* c/mtp.h:66-110 ApusMtp: the MTP draft head of a model -- e = enorm(embed(id)) -> e_proj,
+ * x_j = hnorm(h_j) -> h_proj per hc stream, bf16(e + x_j) -> one full block (sliding-window
+ * attention with its own state, the full MoE) -> its own hc_head collapse and norm -> the
+ * parent's LM head.  The head shares the parent's embedding, head, sizes, batch and stream;
+ * its weights are copied to HBM at creation (the host copies may go afterwards). */
+typedef struct {
+    ApusCudaLayerDesc block;              /* "mtp.<idx>.*" block (c/mtp.h:223-226) */
+    ApusFp8W e_proj, h_proj;              /* FP8 [dim, dim] */
+    const float *enorm_w, *hnorm_w, *norm_w;      /* [dim] */
+    const float *hc_head_fn, *hc_head_base;       /* [hc, hc*dim], [hc] */
+    float hc_head_scale;
+} ApusCudaMtpDesc;
+typedef struct ApusCudaMtp ApusCudaMtp;
+ApusCudaMtp *apus_cuda_mtp_create(ApusCudaModel *parent, const ApusCudaMtpDesc *d);
+void apus_cuda_mtp_destroy(ApusCudaMtp *mt);
+/* c/mtp.h:293-299: a fresh attention state. */
+int apus_cuda_mtp_reset(ApusCudaMtp *mt);
+/* c/mtp.h:303-357 apus_mtp_forward for every sequence: h_in [batch, s, hc_mult * dim] (the
+ * main model's hidden after its last block, or the head's own when chaining), ids [batch, s]
+ * at positions start_pos .. start_pos + s - 1; advances the head's attention state.  Of the
+ * LAST position: logits [batch, vocab], the greedy pick next [batch], and the head's own
+ * post-block hidden h_last [batch, hc_mult * dim] (all nullable). */
+int apus_cuda_mtp_forward(ApusCudaMtp *mt, const float *h_in, const int64_t *ids, int s,
+                          int64_t start_pos, float *logits, int32_t *next, float *h_last);
+
 /* c/mtp.h:113-138, 398-439 apus_snap_take / apus_snap_restore on the device (the
  * rollback of speculative decoding: draft and verify a few positions, keep the
  * accepted prefix).  A snapshot holds, per layer, the sliding-window ring, the
@@ -645,10 +685,16 @@ void apus_cuda_snap_free(ApusCudaSnap *snap);
  * that are bit for bit those of apus_cuda_model_generate (greedy or sampled
  * with the same seed): a draft is accepted iff it equals the model's own pick.
  * stats (nullable, 8 counters as in ApusSpec): emitted, batches, batch_tokens,
- * refeed_tokens, offered, accepted, d1_offered, d1_hits.  The verify batch is
- * consumed as consecutive steps, so this is the engine and its exactness, not
- * yet a speed-up. */
+ * refeed_tokens, offered, accepted, d1_offered, d1_hits.  The verify batch is one pass
+ * over its positions (a chunk), each row bit for bit the single step's.
+ * apus_cuda_model_spec_generate_mtp: the same loop with the MTP head as the proposer
+ * (c/mtp.h:441-528, 600-612): the head replays the true (hidden, token) pairs, chains
+ * `depth` drafts from its own hidden, and is rolled back to the true pairs after every
+ * verify batch.  Hiddens and drafts stay on the device except the draft ids. */
 typedef void (*ApusCudaDraftFn)(void *ctx, int64_t q, int64_t *drafts, int n);
+int apus_cuda_model_spec_generate_mtp(ApusCudaModel *m, ApusCudaMtp *mt, const int64_t *prompt,
+                                      int n_prompt, int n_gen, int depth, int32_t *out_tokens,
+                                      uint64_t *stats);
 int apus_cuda_model_spec_generate(ApusCudaModel *m, const int64_t *prompt,
                                   int n_prompt, int n_gen, int depth,
                                   ApusCudaDraftFn draft, void *draft_ctx,

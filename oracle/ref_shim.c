@@ -26,6 +26,7 @@
 #define APUS_LAYER_IMPLEMENTATION
 #define APUS_MODEL_IMPLEMENTATION
 #define APUS_SAMPLE_IMPLEMENTATION
+#define APUS_MTP_IMPLEMENTATION
 
 #include <math.h>
 #include <stdio.h>
@@ -36,6 +37,7 @@
 #include "mhc.h"
 #include "model.h"
 #include "sample.h"
+#include "mtp.h"
 /* after the reference headers: their include guards make this header skip its
  * layout-identical copies of the reference types and only add the plain
  * descriptors ApusCudaLayerDesc / ApusCudaModelDesc used below */
@@ -130,37 +132,139 @@ void ref_block_forward(const ApusCudaLayerDesc *d, int hc, int iters, float hc_e
 
 /* c/model.h:722 apus_model_forward on an ApusModel assembled from a descriptor.
  * states[i] is layer i's attention state; *pos is advanced by s. */
+typedef struct {
+    ApusModel m;
+    ApusModelState st;
+    ApusLayer *Ls;
+    ApusRopeTab *tabs;
+    ApusLayerState *lst;
+    ApusStTensor te, th;
+} ShimModel;
+
+static void shim_model_open(ShimModel *S, const ApusCudaModelDesc *d, ApusAttnS *states, int64_t pos) {
+    memset(S, 0, sizeof *S);
+    ApusModel *m = &S->m;
+    m->n_layers = d->n_layers;
+    m->cfg.dim = d->dim; m->cfg.hc_mult = d->hc_mult; m->cfg.vocab_size = d->vocab;
+    m->cfg.hc_eps = d->hc_eps; m->cfg.norm_eps = d->norm_eps; m->cfg.hc_sinkhorn_iters = d->hc_sinkhorn_iters;
+    m->cfg.n_activated_experts = d->layers[0].mw.topk;
+    m->cfg.max_pos = d->layers[0].acfg.max_pos;
+    S->Ls = calloc((size_t)d->n_layers, sizeof *S->Ls);
+    S->tabs = calloc((size_t)d->n_layers, sizeof *S->tabs);
+    S->lst = calloc((size_t)d->n_layers, sizeof *S->lst);
+    for (int i = 0; i < d->n_layers; i++) {
+        shim_fill_layer(&S->Ls[i], &S->tabs[i], &d->layers[i], d->hc_mult, d->hc_sinkhorn_iters, d->hc_eps, d->norm_eps);
+        S->Ls[i].cfg.vocab_size = d->vocab;
+        S->lst[i].attn = states[i];
+    }
+    m->layers = S->Ls;
+    S->te.dtype = d->embed_bf16 ? APUS_ST_BF16 : APUS_ST_F32; S->te.data = d->embed;
+    S->th.dtype = d->head_bf16 ? APUS_ST_BF16 : APUS_ST_F32; S->th.data = d->head;
+    m->embed = &S->te; m->head = &S->th;
+    m->norm_w = (float *)d->norm_w;
+    m->hc_head_fn = (float *)d->hc_head_fn; m->hc_head_base = (float *)d->hc_head_base;
+    m->hc_head_scale = d->hc_head_scale;
+    S->st.layers = S->lst; S->st.pos = pos;
+}
+static void shim_model_close(ShimModel *S, ApusAttnS *states, int64_t *pos) {
+    *pos = S->st.pos;
+    for (int i = 0; i < S->m.n_layers; i++) states[i] = S->lst[i].attn;
+    free(S->Ls); free(S->tabs); free(S->lst);
+}
+
+/* c/model.h:722 apus_model_forward on an ApusModel assembled from a descriptor.
+ * states[i] is layer i's attention state; *pos is advanced by s. */
 void ref_model_forward(const ApusCudaModelDesc *d, ApusAttnS *states, int64_t *pos,
                        const int64_t *ids, int s, float *logits, int logits_all) {
-    ApusModel m;
-    memset(&m, 0, sizeof m);
-    m.n_layers = d->n_layers;
-    m.cfg.dim = d->dim; m.cfg.hc_mult = d->hc_mult; m.cfg.vocab_size = d->vocab;
-    m.cfg.hc_eps = d->hc_eps; m.cfg.norm_eps = d->norm_eps; m.cfg.hc_sinkhorn_iters = d->hc_sinkhorn_iters;
-    m.cfg.n_activated_experts = d->layers[0].mw.topk;
-    ApusLayer *Ls = calloc((size_t)d->n_layers, sizeof *Ls);
-    ApusRopeTab *tabs = calloc((size_t)d->n_layers, sizeof *tabs);
-    ApusLayerState *lst = calloc((size_t)d->n_layers, sizeof *lst);
-    for (int i = 0; i < d->n_layers; i++) {
-        shim_fill_layer(&Ls[i], &tabs[i], &d->layers[i], d->hc_mult, d->hc_sinkhorn_iters, d->hc_eps, d->norm_eps);
-        Ls[i].cfg.vocab_size = d->vocab;
-        lst[i].attn = states[i];
+    ShimModel S;
+    shim_model_open(&S, d, states, *pos);
+    apus_model_forward(&S.m, &S.st, ids, s, logits, logits_all);
+    shim_model_close(&S, states, pos);
+}
+
+/* c/model.h:731-743 apus_model_forward_h / _mh: h_out [s, hc*dim] or, with the target layers
+ * given, mh_out [s, n_targets*dim] (both nullable). */
+void ref_model_forward_hm(const ApusCudaModelDesc *d, ApusAttnS *states, int64_t *pos, const int64_t *ids, int s,
+                          float *logits, int logits_all, float *h_out, const int *targets, int n_targets,
+                          float *mh_out) {
+    ShimModel S;
+    shim_model_open(&S, d, states, *pos);
+    if (mh_out) {
+        S.m.dspark = 1;
+        S.m.dsc.n_targets = n_targets;
+        for (int i = 0; i < n_targets; i++) S.m.dsc.targets[i] = targets[i];
+        apus_model_forward_mh(&S.m, &S.st, ids, s, logits, logits_all, mh_out);
+    } else {
+        apus_model_forward_h(&S.m, &S.st, ids, s, logits, logits_all, h_out);
     }
-    m.layers = Ls;
-    ApusStTensor te, th;
-    memset(&te, 0, sizeof te); memset(&th, 0, sizeof th);
-    te.dtype = d->embed_bf16 ? APUS_ST_BF16 : APUS_ST_F32; te.data = d->embed;
-    th.dtype = d->head_bf16 ? APUS_ST_BF16 : APUS_ST_F32; th.data = d->head;
-    m.embed = &te; m.head = &th;
-    m.norm_w = (float *)d->norm_w;
-    m.hc_head_fn = (float *)d->hc_head_fn; m.hc_head_base = (float *)d->hc_head_base;
-    m.hc_head_scale = d->hc_head_scale;
-    ApusModelState st;
-    st.layers = lst; st.pos = *pos;
-    apus_model_forward(&m, &st, ids, s, logits, logits_all);
-    *pos = st.pos;
-    for (int i = 0; i < d->n_layers; i++) states[i] = lst[i].attn;
-    free(Ls); free(tabs); free(lst);
+    shim_model_close(&S, states, pos);
+}
+
+static void shim_fill_mtp(ApusMtp *mt, ApusRopeTab *tab, const ApusModel *m, const ApusCudaMtpDesc *md,
+                          const ApusCudaModelDesc *d) {
+    memset(mt, 0, sizeof *mt);
+    mt->m = m;
+    shim_fill_layer(&mt->block, tab, &md->block, d->hc_mult, d->hc_sinkhorn_iters, d->hc_eps, d->norm_eps);
+    mt->block.cfg.vocab_size = d->vocab;
+    mt->e_proj = md->e_proj; mt->h_proj = md->h_proj;
+    mt->enorm_w = (float *)md->enorm_w; mt->hnorm_w = (float *)md->hnorm_w; mt->norm_w = (float *)md->norm_w;
+    mt->hc_head_fn = (float *)md->hc_head_fn; mt->hc_head_base = (float *)md->hc_head_base;
+    mt->hc_head_scale = md->hc_head_scale;
+}
+
+/* c/mtp.h:303 apus_mtp_forward on an ApusMtp assembled from descriptors (the parent model only
+ * lends its embedding, head and sizes). */
+void ref_mtp_forward(const ApusCudaModelDesc *d, const ApusCudaMtpDesc *md, ApusAttnS *mtp_state, const float *h_in,
+                     const int64_t *ids, int s, int64_t start_pos, float *logits, float *h_last) {
+    ShimModel S;
+    ApusAttnS none[64];
+    memset(none, 0, sizeof none);
+    int64_t pos = 0;
+    shim_model_open(&S, d, none, 0);
+    ApusMtp mt;
+    ApusRopeTab tab;
+    ApusMtpState mst;
+    shim_fill_mtp(&mt, &tab, &S.m, md, d);
+    mst.block.attn = *mtp_state;
+    apus_mtp_forward(&mt, &mst, h_in, ids, s, start_pos, logits, h_last);
+    *mtp_state = mst.block.attn;
+    shim_model_close(&S, none, &pos);
+}
+
+/* c/mtp.h:472-616 apus_spec_prefill + apus_spec_step until n_gen tokens are out, with the MTP head
+ * as the proposer (greedy).  out_tokens [n_gen]; stats [8] = emitted, batches, batch_tokens,
+ * refeed_tokens, offered, accepted, d1_offered, d1_hits; first_drafts [depth] = the chain after
+ * the prompt. */
+int ref_spec_generate_mtp(const ApusCudaModelDesc *d, const ApusCudaMtpDesc *md, ApusAttnS *states,
+                          ApusAttnS *mtp_state, const int64_t *prompt, int n_prompt, int n_gen, int depth,
+                          int32_t *out_tokens, uint64_t *stats, int64_t *first_drafts) {
+    ShimModel S;
+    int64_t pos = 0;
+    shim_model_open(&S, d, states, 0);
+    ApusMtp mt;
+    ApusRopeTab tab;
+    ApusMtpState mst;
+    shim_fill_mtp(&mt, &tab, &S.m, md, d);
+    mst.block.attn = *mtp_state;
+    ApusSpec sp;
+    ApusRng rng;
+    apus_rng_seed(&rng, 0);
+    apus_spec_init(&sp, &S.m, &S.st, &mt, &mst, depth, 0.0f, 1.0f, &rng, NULL);
+    apus_spec_prefill(&sp, prompt, n_prompt);
+    for (int i = 0; i < depth; i++) first_drafts[i] = sp.drafts[i];
+    int n = 0, buf[80];
+    while (n < n_gen) {
+        int ne = apus_spec_step(&sp, buf, 80);
+        if (ne <= 0) break;
+        for (int i = 0; i < ne && n < n_gen; i++) out_tokens[n++] = buf[i];
+    }
+    uint64_t st8[8] = {sp.emitted, sp.batches, sp.batch_tokens, sp.refeed_tokens, sp.offered, sp.accepted,
+                       sp.d1_offered, sp.d1_hits};
+    memcpy(stats, st8, sizeof st8);
+    apus_spec_free(&sp);
+    *mtp_state = mst.block.attn;
+    shim_model_close(&S, states, &pos);
+    return n;
 }
 
 /* c/model.h:638-647 (static apus_head_gemv) on a BF16 [O, K] matrix. */

@@ -285,6 +285,35 @@ class TinyModel:
         return S, arr
 
 
+class TinyMtp:
+    """The MTP draft head of a TinyModel (reference c/mtp.h:66-76): one more sliding-window block
+    with scored routing, the two FP8 [dim, dim] projections, three norm weights and its own
+    mHC head parameters."""
+
+    def __init__(self, seed, rope):
+        from apus_b200 import capi
+        M = dict(MODEL_DIMS)
+        dim, hc = ATTN_DIMS["dim"], M["hc"]
+        cos, sin = rope["plain"]
+        self.block = BlockLayer(seed, "swa", cos, sin)
+        rng = np.random.default_rng(seed + 31)
+        self.e_proj, self.h_proj = synth.fp8_weight(rng, dim, dim, std=0.06), synth.fp8_weight(rng, dim, dim, std=0.06)
+        nrm = lambda n: (1 + 0.05 * rng.standard_normal(n)).astype(np.float32)
+        self.enorm_w, self.hnorm_w, self.norm_w = nrm(dim), nrm(dim), nrm(dim)
+        self.hc_head_fn = (rng.standard_normal((hc, hc * dim)) * 0.05).astype(np.float32)
+        self.hc_head_base = (rng.standard_normal(hc) * 0.5).astype(np.float32)
+        d = capi.MtpDesc()
+        d.block = self.block.desc
+        d.e_proj, d.h_proj = capi.qw(*self.e_proj, dim, dim), capi.qw(*self.h_proj, dim, dim)
+        d.enorm_w, d.hnorm_w, d.norm_w = capi.ptr(self.enorm_w), capi.ptr(self.hnorm_w), capi.ptr(self.norm_w)
+        d.hc_head_fn, d.hc_head_base, d.hc_head_scale = capi.ptr(self.hc_head_fn), capi.ptr(self.hc_head_base), 0.9
+        self.desc = d
+
+    def state(self):
+        S = AttnState(self.block.attn)
+        return S, S.st
+
+
 def block_inputs(seed, n_tokens, hc, dim):
     rng = np.random.default_rng(seed)
     return synth.activations(rng, n_tokens, hc * dim, std=1.2).reshape(n_tokens, hc, dim)

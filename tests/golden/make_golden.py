@@ -10,9 +10,10 @@ APUS_REFERENCE environment variable, else a directory named `reference` beside t
      the known-answer fixtures its C tests check the kernels against.
   2. ref_cases.npz: outputs of the unmodified reference C code
      (oracle/_ref/libapus_ref.so) on the seeded cases of tests/cases.py.
-  3. ckpt_case.npz (argument `ckpt`) and flash_case.npz (argument `flash`): the
-     reference's loader + greedy loop on a written checkpoint directory, and its
-     greedy loop on six real-dimension layers of the benchmarked model.
+  3. ckpt_case.npz (argument `ckpt`), mtp_case.npz (argument `mtp`) and flash_case.npz
+     (argument `flash`): the reference's loader + greedy loop on a written checkpoint
+     directory, its hidden-collecting forwards, MTP draft head and speculative loop on the
+     small model, and its greedy loop on six real-dimension layers of the benchmarked model.
 
 Nothing on the GPU box reads the reference checkout; it only reads these files.
 """
@@ -254,6 +255,68 @@ def main_ckpt():
     print("wrote ckpt_case.npz:", {k: v.shape for k, v in G.items()})
 
 
+def ref_mtp(L, seed, n_layers, n_prompt, n_gen, depth, targets):
+    """The reference's hidden-collecting forwards (c/model.h:731-743), its MTP head over the
+    prompt's true (hidden, token) pairs and one chained call (c/mtp.h:303-357), and its
+    speculative loop with that head as the proposer (c/mtp.h:472-616), greedy."""
+    Mdl = cases.TinyModel(seed, rope_pair(L), n_layers)
+    Mtp = cases.TinyMtp(seed + 3, rope_pair(L))
+    V, hd, dim = Mdl.M["vocab"], Mdl.M["hc"] * cases.ATTN_DIMS["dim"], cases.ATTN_DIMS["dim"]
+    prompt = np.ascontiguousarray(cases.prompt_ids(seed + 5, 1, n_prompt, V)[0])
+    vp = C.c_void_p
+    L.ref_model_forward_hm.restype = None
+    L.ref_model_forward_hm.argtypes = [vp, vp, vp, vp, C.c_int, vp, C.c_int, vp, vp, C.c_int, vp]
+    L.ref_mtp_forward.restype = None
+    L.ref_mtp_forward.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.c_int64, vp, vp]
+    L.ref_spec_generate_mtp.restype = C.c_int
+    L.ref_spec_generate_mtp.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp, vp, vp]
+    out = {}
+    # forward_h with every position's logits
+    keep, st = Mdl.states()
+    pos = C.c_int64(0)
+    lg_all, h_all = np.empty((n_prompt, V), np.float32), np.empty((n_prompt, hd), np.float32)
+    L.ref_model_forward_hm(C.byref(Mdl.desc), st, C.byref(pos), P(prompt), n_prompt, P(lg_all), 1, P(h_all), None, 0, None)
+    out["h_all"], out["logits_all"] = h_all, lg_all
+    # forward_mh
+    keep2, st2 = Mdl.states()
+    pos = C.c_int64(0)
+    tg = np.array(targets, np.int32)
+    mh, lg = np.empty((n_prompt, len(targets) * dim), np.float32), np.empty(V, np.float32)
+    L.ref_model_forward_hm(C.byref(Mdl.desc), st2, C.byref(pos), P(prompt), n_prompt, P(lg), 0, None, P(tg), len(targets), P(mh))
+    out["mh_all"] = mh
+    assert np.array_equal(lg, lg_all[-1])
+    # the head over the true pairs, then one chained position
+    keepm, stm = Mtp.state()
+    ml, mhl = np.empty(V, np.float32), np.empty(hd, np.float32)
+    L.ref_mtp_forward(C.byref(Mdl.desc), C.byref(Mtp.desc), C.byref(stm), P(h_all), P(prompt), n_prompt, 0, P(ml), P(mhl))
+    out["mtp_logits"], out["mtp_h_last"] = ml.copy(), mhl.copy()
+    d1 = np.array([int(np.argmax(ml))], np.int64)
+    own = mhl.copy()                                    # the head's own hidden is the chaining input
+    L.ref_mtp_forward(C.byref(Mdl.desc), C.byref(Mtp.desc), C.byref(stm), P(own), P(d1), 1, n_prompt, P(ml), P(mhl))
+    out["mtp_logits_chained"], out["mtp_h_chained"] = ml.copy(), mhl.copy()
+    out["mtp_win"] = keepm.win.copy()
+    # the speculative loop
+    keep3, st3 = Mdl.states()
+    keepm2, stm2 = Mtp.state()
+    toks, stats, fd = np.zeros(n_gen, np.int32), np.zeros(8, np.uint64), np.zeros(depth, np.int64)
+    n = L.ref_spec_generate_mtp(C.byref(Mdl.desc), C.byref(Mtp.desc), st3, C.byref(stm2), P(prompt), n_prompt, n_gen, depth,
+                                P(toks), P(stats), P(fd))
+    assert n == n_gen
+    out["spec_tokens"], out["spec_stats"], out["spec_first_drafts"] = toks, stats, fd
+    # and the plain greedy stream it must reproduce
+    plain = ref_generate(L, seed, n_layers, 1, n_prompt, n_gen)["tokens"][0]
+    assert np.array_equal(plain, toks), (plain, toks)
+    return out
+
+
+def main_mtp():
+    L = ref()
+    assert L is not None, "reference build not available"
+    G = ref_mtp(L, **MTP_CASE)
+    np.savez_compressed(HERE / "mtp_case.npz", **G)
+    print("wrote mtp_case.npz:", {k: v.shape for k, v in G.items()}, "stats", G["spec_stats"].tolist())
+
+
 def main():
     L = ref()
     assert L is not None, "reference build not available"
@@ -424,14 +487,19 @@ SAMPLE_CASES = {
     "sample_greedy": (118, 8, 5000, "ties", 0.0, 0.9),
 }
 MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
+# the MTP draft head on the small model (c/mtp.h): targets = the layers whose mean hidden forward_mh collects
+MTP_CASE = dict(seed=91, n_layers=3, n_prompt=9, n_gen=24, depth=3, targets=[0, 2])
 
 if __name__ == "__main__":
     import sys
     if sys.argv[1:] == ["ckpt"]:      # only the checkpoint case (its own file)
         main_ckpt()
+    elif sys.argv[1:] == ["mtp"]:     # only the MTP draft-head case (its own file)
+        main_mtp()
     elif sys.argv[1:] == ["flash"]:   # only the real-dimension model case (its own file; ~23 GB of host memory)
         main_flash()
     else:
         main()
         main_ckpt()
+        main_mtp()
         main_flash()
