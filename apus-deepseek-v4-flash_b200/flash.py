@@ -92,7 +92,10 @@ TENSOR_IDS = {n: i for i, n in enumerate((
     "idx_wq_b", "idx_wq_b.s", "idx_wproj", "gate_w", "gate_bias", "tid2eid",
     "w1", "w1.s", "w3", "w3.s", "w2", "w2.s", "sw1", "sw1.s", "sw3", "sw3.s", "sw2", "sw2.s",
     "attn_norm", "ffn_norm", "hc_attn_fn", "hc_attn_base", "hc_ffn_fn", "hc_ffn_base",
-    "embed", "head", "norm", "hc_head_fn", "hc_head_base", "prompt"))}
+    "embed", "head", "norm", "hc_head_fn", "hc_head_base", "prompt",
+    "e_proj", "e_proj.s", "h_proj", "h_proj.s", "enorm", "hnorm"))}
+# the MTP draft head's block is generated as layer MTP_LAYER + idx (c/mtp.h:223-226: "mtp.<idx>.*")
+MTP_LAYER = 2000
 # apus_synth.h kinds
 K_U8, K_U8_RANGE, K_F32, K_F32_BF16, K_BF16, K_E4M3, K_I64_MOD, K_I64_SUBSET = range(8)
 
@@ -225,6 +228,26 @@ class RandomFlashModel:
             self._fill_at(ps + le * O * (K // 32), layer, name + ".s", K_U8_RANGE, O * (K // 32), 120, 126,
                           self.e_lo + le)
         return pc, ps
+
+    def mtp_desc(self, idx=0):
+        """ApusCudaMtpDesc of MTP draft head `idx` (reference c/mtp.h:66-76): a sliding-window block
+        with scored routing and the full expert set, the FP8 [dim, dim] e/h projections, the three
+        norm weights and its own mHC head parameters -- random-init like everything else."""
+        cfg, L = self.cfg, MTP_LAYER + idx
+        dim, hc = cfg.dim, cfg.hc_mult
+        d = capi.MtpDesc()
+        d.block = self._layer(L, 0)
+        d.e_proj, d.h_proj = self._fp8(L, "e_proj", dim, dim), self._fp8(L, "h_proj", dim, dim)
+        d.enorm_w = self._fill(L, "enorm", K_F32, (dim,), 1.0, 0.05)
+        d.hnorm_w = self._fill(L, "hnorm", K_F32, (dim,), 1.0, 0.05)
+        d.norm_w = self._fill(L, "norm", K_F32, (dim,), 1.0, 0.05)
+        d.hc_head_fn = self._fill(L, "hc_head_fn", K_F32, (hc, hc * dim), 0.0, 0.01)
+        d.hc_head_base = self._fill(L, "hc_head_base", K_F32, (hc,), 0.0, 0.5)
+        d.hc_head_scale = 0.8
+        if not self.host:
+            self.torch.cuda.synchronize(self.device)
+        self.keep.append(d)
+        return d
 
     # ---- one layer ----------------------------------------------------------------------------
     def _layer(self, i, ratio):

@@ -62,6 +62,8 @@ def parse():
     ap.add_argument("--attn-batches", default="1,32", help="attn workload: decode queries per step (per GPU)")
     ap.add_argument("--batch", type=int, default=32, help="model workload: sequences decoded in lockstep")
     ap.add_argument("--prompt", type=int, default=512, help="model workload: prompt tokens per sequence")
+    ap.add_argument("--no-mtp", action="store_true", help="model workload: skip the batch-1 run with MTP speculative drafting")
+    ap.add_argument("--mtp-depth", type=int, default=2, help="drafts chained per speculative step")
     ap.add_argument("--layers", type=int, default=43, help="model workload: layers (43 = the real model)")
     ap.add_argument("--microbatches", type=int, default=1,
                     help="model workload, 1 GPU: model objects the batch is split over; they share the weights "
@@ -218,6 +220,46 @@ def flash_config(a):
     if a.experts != cfg.n_experts:
         cfg.n_experts = a.experts
     return cfg
+
+
+def mtp_arm(L, W, h, a, cfg):
+    """Batch 1 with MTP speculative drafting (reference c/mtp.h:472-616): the draft head chains
+    `depth` candidates, the main model verifies them in one pass, accepted ones are emitted with
+    the model's own pick.  The head is random-init like the model, so it predicts nothing: the
+    acceptance rate is what a random head earns, and the line shows what the machinery costs;
+    the emitted stream must be the plain greedy stream either way."""
+    import apus_b200
+    from apus_b200 import capi
+    from apus_b200.flash import prompt_ids
+    depth, n_gen = a.mtp_depth, min(a.steps, 64)
+    d = W.mtp_desc(0)
+    mt = L.apus_cuda_mtp_create(h, C.byref(d))
+    if not mt:
+        apus_b200.check(1, "apus_cuda_mtp_create")
+    prompt = np.ascontiguousarray(prompt_ids(a.seed, 0, 1, a.prompt, cfg.vocab))
+    try:
+        plain = np.zeros((1, n_gen), np.int32)
+        apus_b200.check(L.apus_cuda_model_reset(h), "model_reset")
+        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(prompt), a.prompt, n_gen, capi.ptr(plain), None, None), "generate")
+        toks, stats = np.zeros(n_gen, np.int32), np.zeros(8, np.uint64)
+        times = []
+        for n in (4, n_gen):                                  # the short run warms the head's buffers up
+            apus_b200.check(L.apus_cuda_model_reset(h), "model_reset")
+            t0 = time.perf_counter()
+            apus_b200.check(L.apus_cuda_model_spec_generate_mtp(h, mt, capi.ptr(prompt), a.prompt, n, depth, capi.ptr(toks),
+                                                                 capi.ptr(stats)), "spec_generate_mtp")
+            times.append(time.perf_counter() - t0)
+        # both runs consume the prompt; their difference is n_gen - 4 emitted tokens of draft/verify steps
+        dt = times[1] - times[0]
+        emitted = n_gen - 4
+    finally:
+        L.apus_cuda_mtp_destroy(mt)
+    return {"value": emitted / dt if dt > 0 else None, "unit": "tok/s", "batch": 1, "depth": depth, "tokens": n_gen,
+            "ms_per_token": dt / max(emitted, 1) * 1e3, "tokens_equal_plain_greedy": bool(np.array_equal(toks, plain[0])),
+            "verify_batches": int(stats[1]), "batch_tokens": int(stats[2]), "refeed_tokens": int(stats[3]),
+            "drafts_offered": int(stats[4]), "drafts_accepted": int(stats[5]), "d1_hits": int(stats[7]),
+            "head": "random-init MTP block (sliding window, 256 experts) + e/h projections, generated on the device",
+            "timing": "host clock around the loop (it synchronises every step to read the draft ids)"}
 
 
 def cpu_model_baseline(cfg, seed, budget_s, prompt=512):
@@ -613,7 +655,8 @@ def model_main(a):
         L.apus_cuda_model_destroy(h)
 
     # ---- batch 1 ------------------------------------------------------------------------------
-    h1, ms1, prefill1, launches1, out1, _, st1, _ = run(1, 1)
+    h1, ms1, prefill1, launches1, out1, _, st1, stream1 = run(1, 1)
+    mtp_line = None if a.no_mtp else mtp_arm(L, W, h1[0], a, cfg)
     L.apus_cuda_model_destroy(h1[0])
 
     peak, peak_kind = peak_hbm()
@@ -639,6 +682,7 @@ def model_main(a):
                                 "frac": st1[3] * W13_BYTES / (st1[0] * 1e-3) / 1e9 / peak if st1[0] > 0 else None,
                                 "avg_launch_us": st1[0] / max(st1[2], 1) * 1e3, "avg_unique_experts": st1[3] / max(st1[2], 1),
                                 "down_proj_frac": st1[3] * W2_BYTES / (st1[1] * 1e-3) / 1e9 / peak if st1[1] > 0 else None}},
+        "mtp": mtp_line,
         "prefill": {"tokens": B * a.prompt, "ms": prefill_ms, "tok_s": B * a.prompt / (prefill_ms * 1e-3),
                     "note": "prompt consumed in chunks of positions (2048 rows = positions x sequences per pass)"},
         "weights": {"bytes": W.bytes, "generate_s": t_gen},
