@@ -272,6 +272,295 @@ sparse_pv_kernel(const float *__restrict__ sc, const float *__restrict__ sink, i
     }
 }
 
+// ---- the same two steps, register-tiled ---------------------------------------------------------
+// Same arithmetic, same order, same bits as the two kernels above; what changes is how often a
+// number is fetched per flop.
+//
+// Scores: a warp owns a tile of 16 heads x 32 candidates and walks k in chunks of 64 staged in shared
+// memory TRANSPOSED (q chunk [k][16 heads], KV chunk [k][32 ids], pitch 36 words so the 16-byte
+// stores of four gathered rows at one k do not collide); a lane owns 4 heads x 4 candidates, so one
+// k costs it two 16-byte shared loads for 16 multiply-add pairs -- the kernel is bound by the FP32
+// pipes (its floor: every (head, candidate) dot is 512 dependent multiply/add pairs), where the
+// kernel above is bound by shared-memory loads at one 4-byte load per flop.
+// softmax: max, p_j = bf16(exp(s_j - max)) written over the scores, denominator per (row, head).
+// P.V: a CTA owns HG heads of a row; a thread owns one channel pair for all HG heads (accumulators
+// in registers), so a gathered KV row is fetched once per HG heads instead of once per head; the
+// probabilities of a chunk of candidates sit transposed in shared memory ([j][HG], one 16-byte
+// broadcast load per 4 heads).
+#define SS_ROWB 128                       // bytes of a KV row staged per chunk: 64 BF16 or 32 f32 values of k
+#define SS_PITCHW 36                      // row pitch of the staged tile in 32-bit words (128 B + 16 B pad)
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int sz = valid ? 16 : 0;        // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz) : "memory");
+}
+
+// Scores.  A warp owns 16 heads x 32 candidates; lane = (hg, jg) owns heads 4hg..4hg+3 and candidates
+// jg, jg+8, jg+16, jg+24.  The warp's 32 gathered rows are staged 128 bytes of k at a time in their
+// natural layout by 16-byte cp.async (two buffers: the next chunk is in flight while this one is
+// consumed); with a pitch of 36 words the eight rows the lanes of a load touch fall into different
+// banks.  The q chunk is shared by the CTA's warps, transposed ([k][16 heads]: one 16-byte load gives
+// a lane its four heads).  Per k a lane issues 5 shared loads for 16 multiply/add pairs.
+template <bool BF16, int W>
+__global__ void __launch_bounds__(32 * W)
+sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32_t *__restrict__ ids,
+                          const int *__restrict__ ns, int idxw, float scale, const void *kv_a, int64_t na,
+                          const void *kv_b, float *__restrict__ sc, size_t a_stride, size_t b_stride, int seq_mod) {
+    constexpr int KC = BF16 ? 64 : 32;                         // k values per chunk
+    extern __shared__ __align__(16) unsigned char ss_raw[];
+    float (*s_q)[KC][16] = reinterpret_cast<float (*)[KC][16]>(ss_raw);                       // [2][KC][16]
+    uint32_t (*s_kv)[2][32][SS_PITCHW] =
+        reinterpret_cast<uint32_t (*)[2][32][SS_PITCHW]>(ss_raw + 2 * KC * 16 * 4);           // [W][2][32][pitch]
+    const int t = blockIdx.z, hb = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n = ns[t];
+    const int j0 = ((int)blockIdx.x * W + warp) * 32;          // first candidate of this warp's tile
+    if ((int)blockIdx.x * W * 32 >= n) return;                  // whole CTA past the row
+    const int own = seq_mod > 0 ? t % seq_mod : t;
+    const size_t esz = BF16 ? 2 : 4;
+    // lane u-th copy of a chunk: row (lane + 32u) / 8, 16-byte segment (lane + 32u) % 8; the four rows a
+    // lane copies from are fixed, so their base pointers stay in registers
+    const char *rowp[8];
+    const char *dummy = reinterpret_cast<const char *>(kv_a ? kv_a : kv_b);
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        const int r = (lane + 32 * u) >> 3, j = j0 + r;
+        const char *ptr = nullptr;
+        if (j < n) {
+            const int32_t id = ids[(size_t)t * idxw + j];
+            ptr = id < na ? reinterpret_cast<const char *>(kv_a) + (size_t)own * a_stride + (size_t)id * d * esz
+                          : reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride + (size_t)(id - na) * d * esz;
+        }
+        rowp[u] = ptr;
+    }
+    const bool live = j0 < n;                                   // warps past the row still help with the q chunk
+    const int hg = lane & 3, jg = lane >> 2;
+    const int nchunk = d / KC;
+    // the q chunk of the NEXT step travels through registers: loaded before this step's arithmetic,
+    // stored (transposed) after it, so its latency hides behind the multiply/adds
+    constexpr int QN = (KC * 16 + 32 * W - 1) / (32 * W);
+    float qreg[QN];
+    auto q_load = [&](int c) {
+#pragma unroll
+        for (int u = 0; u < QN; u++) {
+            const int i = tid + 32 * W * u, hh = i / KC, kk = i - hh * KC, head = hb * 16 + hh;
+            qreg[u] = (i < KC * 16 && head < h) ? q[((size_t)t * h + head) * d + c * KC + kk] : 0.f;
+        }
+    };
+    auto q_store = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < QN; u++) {
+            const int i = tid + 32 * W * u, hh = i / KC, kk = i - hh * KC;
+            if (i < KC * 16) s_q[buf][kk][hh] = qreg[u];
+        }
+    };
+    auto kv_stage = [&](int c, int buf) {
+        if (live) {
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = lane + 32 * u, r = i >> 3, seg = i & 7;
+                cp_async16(&s_kv[warp][buf][r][seg * 4], rowp[u] ? rowp[u] + (size_t)c * SS_ROWB + seg * 16 : dummy, rowp[u] != nullptr);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
+    kv_stage(0, 0);
+    if (nchunk > 1) kv_stage(1, 1);
+    q_load(0);
+    q_store(0);
+    for (int c = 0; c < nchunk; c++) {
+        const int buf = c & 1;
+        if (c + 1 < nchunk) {
+            q_load(c + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();                                        // chunk c (q and the warp's rows) is visible
+        if (live) {
+            if (BF16) {
+#pragma unroll 4
+                for (int k2 = 0; k2 < KC / 2; k2++) {           // one 32-bit word holds k = 2 k2 and 2 k2 + 1
+                    const float4 qa = *reinterpret_cast<const float4 *>(&s_q[buf][2 * k2][4 * hg]);
+                    const float4 qb = *reinterpret_cast<const float4 *>(&s_q[buf][2 * k2 + 1][4 * hg]);
+                    const float q0[4] = {qa.x, qa.y, qa.z, qa.w}, q1[4] = {qb.x, qb.y, qb.z, qb.w};
+                    float k0v[4], k1v[4];
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        const uint32_t w = s_kv[warp][buf][jg + 8 * b][k2];
+                        k0v[b] = __uint_as_float(w << 16);
+                        k1v[b] = __uint_as_float(w & 0xffff0000u);
+                    }
+#pragma unroll
+                    for (int a = 0; a < 4; a++)
+#pragma unroll
+                        for (int b = 0; b < 4; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(q0[a], k0v[b]));
+#pragma unroll
+                    for (int a = 0; a < 4; a++)
+#pragma unroll
+                        for (int b = 0; b < 4; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(q1[a], k1v[b]));
+                }
+            } else {
+#pragma unroll 8
+                for (int kk = 0; kk < KC; kk++) {
+                    const float4 q4 = *reinterpret_cast<const float4 *>(&s_q[buf][kk][4 * hg]);
+                    const float qa[4] = {q4.x, q4.y, q4.z, q4.w};
+                    float kb[4];
+#pragma unroll
+                    for (int b = 0; b < 4; b++) kb[b] = __uint_as_float(s_kv[warp][buf][jg + 8 * b][kk]);
+#pragma unroll
+                    for (int a = 0; a < 4; a++)
+#pragma unroll
+                        for (int b = 0; b < 4; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(qa[a], kb[b]));
+                }
+            }
+        }
+        if (c + 1 < nchunk) q_store(buf ^ 1);                   // read last at step c - 1, behind that step's barrier
+        __syncthreads();                                        // this step's buffers are free again
+        if (c + 2 < nchunk) kv_stage(c + 2, buf);
+    }
+    if (!live) return;
+#pragma unroll
+    for (int a = 0; a < 4; a++) {
+        const int head = hb * 16 + 4 * hg + a;
+        if (head >= h) continue;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int j = j0 + jg + 8 * b;
+            if (j < n) sc[((size_t)t * h + head) * idxw + j] = __fmul_rn(acc[a][b], scale);
+        }
+    }
+}
+
+// max, p over the scores, the denominator sum_j p_j + exp(sink - max): the sums in the order of
+// sparse_pv_kernel (one accumulator for n <= 1024, the strided tree above it)
+__global__ void __launch_bounds__(256)
+sparse_softmax_kernel(float *__restrict__ sc, const float *__restrict__ sink, int h, const int *__restrict__ ns, int idxw,
+                      float *__restrict__ den) {
+    extern __shared__ float s_p[];             // [idxw]
+    __shared__ float red[32];
+    __shared__ float s_mx, s_sum;
+    const int t = blockIdx.y, head = blockIdx.x, tid = threadIdx.x;
+    const int n = ns[t];
+    if (n == 0) return;
+    float *sr = sc + ((size_t)t * h + head) * idxw;
+    float mx = -INFINITY;
+    for (int j = tid; j < n; j += blockDim.x) mx = fmaxf(mx, sr[j]);
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    if (tid < 32) {
+        float v = tid < (blockDim.x >> 5) ? red[tid] : -INFINITY;
+        v = warp_max(v);
+        if (tid == 0) s_mx = v;
+    }
+    __syncthreads();
+    mx = s_mx;
+    for (int j = tid; j < n; j += blockDim.x) {
+        const float p = bf16_round(exp_rn(__fsub_rn(sr[j], mx)));
+        s_p[j] = p;
+        sr[j] = p;
+    }
+    __syncthreads();
+    if (tid == 0 && n <= 1024) {
+        float sum = 0.f;
+        for (int j = 0; j < n; j++) sum = __fadd_rn(sum, s_p[j]);
+        s_sum = sum;
+    }
+    if (n > 1024) {                            // long rows: tree sum
+        float part = 0.f;
+        for (int j = tid; j < n; j += blockDim.x) part += s_p[j];
+        part = warp_sum(part);
+        __syncthreads();
+        if ((tid & 31) == 0) red[tid >> 5] = part;
+        __syncthreads();
+        if (tid == 0) {
+            float sum = 0.f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); w++) sum += red[w];
+            s_sum = sum;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) den[(size_t)t * h + head] = __fadd_rn(s_sum, exp_rn(__fsub_rn(sink[head], mx)));
+}
+
+#define PV_JC 128
+template <bool BF16, int HG>
+__global__ void __launch_bounds__(256)
+sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den, int h, int d,
+                      const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw, const void *kv_a, int64_t na,
+                      const void *kv_b, float *__restrict__ o, size_t a_stride, size_t b_stride, int seq_mod) {
+    __shared__ __align__(16) float s_p[PV_JC][HG];
+    __shared__ int32_t s_id[PV_JC];
+    const int t = blockIdx.y, h0 = (int)blockIdx.x * HG, tid = threadIdx.x;
+    const int own = seq_mod > 0 ? t % seq_mod : t;
+    kv_a = reinterpret_cast<const char *>(kv_a) + (size_t)own * a_stride;
+    kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride;
+    const int n = ns[t];
+    const int32_t *idr = ids + (size_t)t * idxw;
+    for (int c0 = 0; c0 < d / 2; c0 += 256) {
+        const int k2 = c0 + tid;
+        const bool on = k2 < d / 2;
+        float a0[HG], a1[HG];
+#pragma unroll
+        for (int a = 0; a < HG; a++) a0[a] = a1[a] = 0.f;
+        for (int j0 = 0; j0 < n; j0 += PV_JC) {
+            const int cnt = min(PV_JC, n - j0);
+            __syncthreads();
+            for (int i = tid; i < PV_JC * HG; i += 256) {
+                const int a = i / PV_JC, jj = i - a * PV_JC;
+                s_p[jj][a] = (jj < cnt && h0 + a < h) ? p[((size_t)t * h + h0 + a) * idxw + j0 + jj] : 0.f;
+            }
+            for (int i = tid; i < cnt; i += 256) s_id[i] = idr[j0 + i];
+            __syncthreads();
+            if (on) {
+                // LB gathered rows in flight per thread: the rows come from L2 / HBM with nothing else to
+                // hide their latency behind (few heads per CTA: little arithmetic per row, so more rows)
+                constexpr int LB = HG >= 16 ? 16 : 32;
+                for (int jb = 0; jb < cnt; jb += LB) {
+                    float2 v[LB];
+#pragma unroll
+                    for (int u = 0; u < LB; u++) {
+                        const int jj = jb + u < cnt ? jb + u : cnt - 1;
+                        const int32_t id = s_id[jj];
+                        v[u] = id < na ? kv_pair<BF16>(kv_a, (size_t)id, d, k2) : kv_pair<BF16>(kv_b, (size_t)(id - na), d, k2);
+                    }
+#pragma unroll
+                    for (int u = 0; u < LB; u++) {
+                        if (jb + u >= cnt) break;
+#pragma unroll
+                        for (int m = 0; m < HG / 4; m++) {
+                            const float4 p4 = *reinterpret_cast<const float4 *>(&s_p[jb + u][4 * m]);
+                            const float pa[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                a0[4 * m + e] = __fadd_rn(a0[4 * m + e], __fmul_rn(pa[e], v[u].x));
+                                a1[4 * m + e] = __fadd_rn(a1[4 * m + e], __fmul_rn(pa[e], v[u].y));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (on) {
+#pragma unroll
+            for (int a = 0; a < HG; a++) {
+                if (h0 + a >= h) continue;
+                float *ov = o + ((size_t)t * h + h0 + a) * d;
+                if (n == 0) { ov[2 * k2] = 0.f; ov[2 * k2 + 1] = 0.f; continue; }
+                const float dn = den[(size_t)t * h + h0 + a];
+                ov[2 * k2] = bf16_round(__fdiv_rn(a0[a], dn));
+                ov[2 * k2 + 1] = bf16_round(__fdiv_rn(a1[a], dn));
+            }
+        }
+    }
+}
+
 // Drops negative ids keeping order (reference c/attn.h:1314-1321).
 __global__ void compact_ids_kernel(const int32_t *__restrict__ idxs, int idxw,
                                    int32_t *__restrict__ out, int *__restrict__ ns) {
@@ -318,7 +607,8 @@ static void *ensure_scratch(size_t bytes) {
 }
 size_t sparse_attn_scratch(int h, int idxw, int s) {
     const size_t sc_bytes = (size_t)s * h * idxw * sizeof(float), ids_bytes = (size_t)s * idxw * sizeof(int32_t);
-    return ((sc_bytes + ids_bytes + 255) & ~(size_t)255) + (size_t)s * sizeof(int);
+    const size_t ns_off = (sc_bytes + ids_bytes + 255) & ~(size_t)255;
+    return ((ns_off + (size_t)s * sizeof(int) + 255) & ~(size_t)255) + (size_t)s * h * sizeof(float);
 }
 
 int sparse_attn(const float *q, const float *sink, int h, int d,
@@ -335,15 +625,54 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
     size_t sc_bytes = (size_t)s * h * idxw * sizeof(float);
     size_t ids_bytes = (size_t)s * idxw * sizeof(int32_t);
     size_t ns_off = (sc_bytes + ids_bytes + 255) & ~(size_t)255;
-    const size_t need = ns_off + (size_t)s * sizeof(int);
+    const size_t den_off = (ns_off + (size_t)s * sizeof(int) + 255) & ~(size_t)255;
+    const size_t need = den_off + (size_t)s * h * sizeof(float);
     APUS_REQUIRE(!callers || need <= callers_cap, "sparse_attn: scratch of %zu bytes given, %zu needed", callers_cap, need);
     void *scratch = callers ? callers : ensure_scratch(need);
     if (!scratch) return 1;
     float *sc = (float *)scratch;
     int32_t *ids = (int32_t *)((char *)scratch + sc_bytes);
     int *ns = (int *)((char *)scratch + ns_off);
+    float *den = (float *)((char *)scratch + den_off);
     compact_ids_kernel<<<s, 256, 0, st>>>(idxs, idxw, ids, ns);
     APUS_LAUNCHED();
+    static const int tiled = [] { const char *e = getenv("APUS_ATTN_TILED"); return !(e && e[0] == '0'); }();
+    if (tiled && d % 64 == 0) {
+        // register-tiled kernels: enough CTAs to cover the SMs decide the tile sizes
+        const long long wide = (long long)ceil_div(idxw, 256) * ceil_div(h, 16) * s;
+        const size_t sm2 = (size_t)idxw * sizeof(float);
+        if (ensure_dyn_smem((const void *)sparse_softmax_kernel, sm2)) return 1;
+        const int hgs = h >= 16 && (long long)s * ceil_div(h, 16) >= 96 ? 16 : 4;
+        const size_t kc = kv_bf16 ? 64 : 32;
+        const size_t ss8 = 2 * kc * 16 * 4 + 8 * (2 * 32 * SS_PITCHW * 4), ss2 = 2 * kc * 16 * 4 + 2 * (2 * 32 * SS_PITCHW * 4);
+        if (ensure_dyn_smem(kv_bf16 ? (const void *)sparse_scores_tile_kernel<true, 8> : (const void *)sparse_scores_tile_kernel<false, 8>, ss8))
+            return 1;
+#define APUS_SA_LAUNCH(BF)                                                                                              \
+        do {                                                                                                            \
+            if (wide >= 148) {                                                                                          \
+                dim3 g((unsigned)ceil_div(idxw, 256), (unsigned)ceil_div(h, 16), (unsigned)s);                          \
+                sparse_scores_tile_kernel<BF, 8><<<g, 256, ss8, st>>>(q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,  \
+                                                                   sa, sb, seq_mod);                                    \
+            } else {                                                                                                    \
+                dim3 g((unsigned)ceil_div(idxw, 64), (unsigned)ceil_div(h, 16), (unsigned)s);                           \
+                sparse_scores_tile_kernel<BF, 2><<<g, 64, ss2, st>>>(q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,   \
+                                                                  sa, sb, seq_mod);                                     \
+            }                                                                                                           \
+            APUS_LAUNCHED();                                                                                            \
+            sparse_softmax_kernel<<<dim3((unsigned)h, (unsigned)s), 256, sm2, st>>>(sc, sink, h, ns, idxw, den);       \
+            APUS_LAUNCHED();                                                                                            \
+            if (hgs == 16)                                                                                              \
+                sparse_pv_tile_kernel<BF, 16><<<dim3((unsigned)ceil_div(h, 16), (unsigned)s), 256, 0, st>>>(            \
+                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);                                  \
+            else                                                                                                        \
+                sparse_pv_tile_kernel<BF, 4><<<dim3((unsigned)ceil_div(h, 4), (unsigned)s), 256, 0, st>>>(              \
+                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);                                  \
+            APUS_LAUNCHED();                                                                                            \
+        } while (0)
+        if (kv_bf16) APUS_SA_LAUNCH(true); else APUS_SA_LAUNCH(false);
+#undef APUS_SA_LAUNCH
+        return 0;
+    }
     size_t sm1 = ((size_t)SA_IDS * (d + 1) + (size_t)SA_HEADS * d) * sizeof(float);
     dim3 g1((unsigned)ceil_div(idxw, SA_IDS), (unsigned)ceil_div(h, SA_HEADS), (unsigned)s);
     size_t sm2 = (size_t)idxw * sizeof(float);
