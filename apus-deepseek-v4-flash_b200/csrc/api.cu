@@ -340,6 +340,10 @@ int chunk_rows() {
     return g_chunk_rows;
 }
 bool chunks_enabled() { return chunk_rows() > 0; }
+bool pdl_enabled() {
+    static const int on = [] { const char *e = getenv("APUS_PDL"); return !(e && e[0] == '0'); }();
+    return on != 0;
+}
 
 int stream_scratch(cudaStream_t st, size_t bytes, void **ws, size_t n_counters, int **counters) {
     struct Slot { DevBuf ws, cnt; };

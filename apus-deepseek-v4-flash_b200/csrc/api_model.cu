@@ -152,6 +152,8 @@ void model_forget(const void *host) {
 struct ModelReg { ModelReg() { apus::on_disable(model_release_all, model_forget); } } g_model_reg;
 
 __global__ void next_ids_kernel(const int32_t *tok, int64_t *ids, int32_t *hist, int B, int step, int n_steps) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < B) {
         ids[b] = tok[b];
@@ -236,7 +238,9 @@ static int head_rows(ApusCudaModel *m, const float *h, int rows, float *yh, floa
 static int model_head(ApusCudaModel *m, cudaStream_t st) {
     return head_rows(m, m->h_cur, m->B, m->yh.as<float>(), m->yn.as<float>(), m->logits.as<float>(), m->tok.as<int32_t>(), st);
 }
-__global__ void advance_pos_kernel(long long *pos) { *pos += 1; }
+__global__ void advance_pos_kernel(long long *pos) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO(); *pos += 1; }
 
 // host mirror of what a step does to the sequence state: entry counts follow the position
 static int model_host_advance(ApusCudaModel *m) {
@@ -262,7 +266,7 @@ static int model_step_enqueue(ApusCudaModel *m, bool want_logits, cudaStream_t s
                        m->iters, m->hc_eps, m->norm_eps, bb, m->sb, st, pd))
             return 1;
     if (want_logits && model_head(m, st)) return 1;
-    advance_pos_kernel<<<1, 1, 0, st>>>(m->pos_dev.as<long long>());
+    launch_k(advance_pos_kernel, 1, 1, 0, st, m->pos_dev.as<long long>());
     APUS_LAUNCHED();
     return 0;
 }
@@ -320,7 +324,9 @@ static int model_step(ApusCudaModel *m, bool want_logits, cudaStream_t st) {
 // attention state, which attn_chunk walks in position order, so a chunk leaves the hidden states,
 // the state and the logits of s consecutive steps, bit for bit; what it saves is reading every
 // weight once per chunk instead of once per position.
-__global__ void advance_pos_by_kernel(long long *pos, int by) { *pos += by; }
+__global__ void advance_pos_by_kernel(long long *pos, int by) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO(); *pos += by; }
 
 static int model_chunk_bufs(ApusCudaModel *m, int s) {
     ApusCudaModel::Chunk &C = m->ck;
@@ -367,6 +373,8 @@ struct ChunkExtra {
 
 // mean over the hc streams in stream order, one accumulator, then BF16 (c/model.h:684-690)
 __global__ void hc_mean_kernel(const float *__restrict__ h, int hc, int dim, float *__restrict__ out, int out_ld) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= dim) return;
     float acc = 0.f;
@@ -418,7 +426,7 @@ static int model_chunk(ApusCudaModel *m, const int64_t *ids_tm, int s, bool want
         if (ex && ex->mh_all)
             for (int tg = 0; tg < ex->n_targets; tg++)
                 if (ex->targets[tg] == i) {
-                    hc_mean_kernel<<<dim3(ceil_div(dim, 256), T), 256, 0, st>>>(h, hc, dim, ex->mh_all + (size_t)tg * dim,
+                    launch_k(hc_mean_kernel, dim3(ceil_div(dim, 256), T), 256, 0, st, h, hc, dim, ex->mh_all + (size_t)tg * dim,
                                                                                ex->n_targets * dim);
                     APUS_LAUNCHED();
                 }
@@ -439,7 +447,7 @@ static int model_chunk(ApusCudaModel *m, const int64_t *ids_tm, int s, bool want
         if (model_head(m, st)) return 1;
     }
     m->h_cur = m->h0.as<float>(); m->h_alt = m->h1.as<float>();
-    advance_pos_by_kernel<<<1, 1, 0, st>>>(m->pos_dev.as<long long>(), s);
+    launch_k(advance_pos_by_kernel, 1, 1, 0, st, m->pos_dev.as<long long>(), s);
     APUS_LAUNCHED();
     m->pos += s;                                  // the entry counts were advanced by attn_chunk
     return 0;
@@ -1021,7 +1029,7 @@ int apus_cuda_model_generate_group(ApusCudaModel *const *ms, int n, const int64_
     for (int g = 0; g < n_gen; g++)
         for (int i = 0; i < n; i++) {                     // the models' steps alternate, each on its own stream
             ApusCudaModel *m = ms[i];
-            next_ids_kernel<<<1, 32, 0, mstream(m)>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), m->hist.as<int32_t>(),
+            launch_k(next_ids_kernel, 1, 32, 0, mstream(m), m->tok.as<int32_t>(), m->ids.as<int64_t>(), m->hist.as<int32_t>(),
                                                      m->B, g, n_gen);
             if (g + 1 < n_gen && model_step(m, true, mstream(m))) return 1;
         }
@@ -1160,6 +1168,8 @@ struct ApusCudaMtp {
 };
 
 __global__ void mtp_mix_kernel(const float *__restrict__ ep, const float *__restrict__ hp, int hc, int dim, float *__restrict__ x) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;       // r = token * hc + stream
     if (i < dim) x[(size_t)r * dim + i] = bf16_round(__fadd_rn(ep[(size_t)(r / hc) * dim + i], hp[(size_t)r * dim + i]));
 }
@@ -1216,7 +1226,7 @@ static int mtp_forward_dev(ApusCudaMtp *mt, const float *h_in, const int64_t *id
         if (rms_norm(hin, mt->hnorm_w, m->norm_eps, mt->hn.as<float>(), dim, (int64_t)T * hc, st)) return 1;
         if (qlinear_dev(mt->h_proj, mt->hn.as<float>(), mt->hp.as<float>(), T * hc, mt->xq.as<uint8_t>(), mt->xs.as<float>(), true, st)) return 1;
         float *x = mt->x0.as<float>(), *xa = mt->x1.as<float>();
-        mtp_mix_kernel<<<dim3(ceil_div(dim, 256), T * hc), 256, 0, st>>>(mt->ep.as<float>(), mt->hp.as<float>(), hc, dim, x);
+        launch_k(mtp_mix_kernel, dim3(ceil_div(dim, 256), T * hc), 256, 0, st, mt->ep.as<float>(), mt->hp.as<float>(), hc, dim, x);
         APUS_LAUNCHED();
         if (block_chunk(mt->block, mt->state, &x, &xa, ids, B, n, start_pos + t0, hc, m->iters, m->hc_eps, m->norm_eps, bb,
                         mt->sb, st))
@@ -1484,9 +1494,9 @@ int apus_cuda_model_end_step(ApusCudaModel *m, int want_logits, int feed_back) {
     if (want_logits) {
         if (model_head(m, st)) return 1;
         if (feed_back)
-            next_ids_kernel<<<1, 32, 0, st>>>(m->tok.as<int32_t>(), m->ids.as<int64_t>(), nullptr, m->B, 0, 1);
+            launch_k(next_ids_kernel, 1, 32, 0, st, m->tok.as<int32_t>(), m->ids.as<int64_t>(), nullptr, m->B, 0, 1);
     }
-    advance_pos_kernel<<<1, 1, 0, st>>>(m->pos_dev.as<long long>());
+    launch_k(advance_pos_kernel, 1, 1, 0, st, m->pos_dev.as<long long>());
     APUS_LAUNCHED();
     return m->capturing ? 0 : model_host_advance(m);
 }

@@ -28,6 +28,8 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 __global__ void __launch_bounds__(TOPK_THREADS)
 topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__restrict__ idx_out,
                    const long long *__restrict__ dyn_pos, int ratio, long long chunk_pos0, int rows_per_pos) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ unsigned hist[256];
     __shared__ unsigned s_prefix, s_need, s_greater, s_taken, s_base;
     __shared__ unsigned long long sel[TOPK_MAX_K];
@@ -126,7 +128,7 @@ int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
                 cudaStream_t st, const long long *dyn_pos, int ratio, long long chunk_pos0, int rows_per_pos) {
     APUS_REQUIRE(k >= 1 && (k <= n || dyn_pos || rows_per_pos > 0) && k <= TOPK_MAX_K, "topk: n=%d k=%d unsupported", n, k);
     if (rows <= 0) return 0;
-    topk_stable_kernel<<<rows, TOPK_THREADS, 0, st>>>(scores, n, k, idx, dyn_pos, ratio, chunk_pos0, rows_per_pos);
+    launch_k(topk_stable_kernel, rows, TOPK_THREADS, 0, st, scores, n, k, idx, dyn_pos, ratio, chunk_pos0, rows_per_pos);
     APUS_LAUNCHED();
     return 0;
 }
@@ -163,6 +165,8 @@ sparse_scores_kernel(const float *__restrict__ q, int h, int d, const int32_t *_
                      const int *__restrict__ ns, int idxw, float scale, const void *kv_a,
                      int64_t na, const void *kv_b, float *__restrict__ sc, size_t a_stride,
                      size_t b_stride, int seq_mod) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ float sm[];
     const int t = blockIdx.z, hb = blockIdx.y, tile = blockIdx.x;
     const int own = seq_mod > 0 ? t % seq_mod : t;         // whose caches: rows of a chunk are time-major
@@ -209,6 +213,8 @@ sparse_pv_kernel(const float *__restrict__ sc, const float *__restrict__ sink, i
                  const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw,
                  const void *kv_a, int64_t na, const void *kv_b, float *__restrict__ o, size_t a_stride,
                  size_t b_stride, int seq_mod) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ float s_p[];             // [idxw]
     __shared__ float red[32];
     __shared__ float s_mx, s_sum;
@@ -307,6 +313,8 @@ __global__ void __launch_bounds__(32 * W)
 sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32_t *__restrict__ ids,
                           const int *__restrict__ ns, int idxw, float scale, const void *kv_a, int64_t na,
                           const void *kv_b, float *__restrict__ sc, size_t a_stride, size_t b_stride, int seq_mod) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     constexpr int KC = BF16 ? 64 : 32;                         // k values per chunk
     extern __shared__ __align__(16) unsigned char ss_raw[];
     float (*s_q)[KC][16] = reinterpret_cast<float (*)[KC][16]>(ss_raw);                       // [2][KC][16]
@@ -442,6 +450,8 @@ sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32
 __global__ void __launch_bounds__(256)
 sparse_softmax_kernel(float *__restrict__ sc, const float *__restrict__ sink, int h, const int *__restrict__ ns, int idxw,
                       float *__restrict__ den) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ float s_p[];             // [idxw]
     __shared__ float red[32];
     __shared__ float s_mx, s_sum;
@@ -495,6 +505,8 @@ __global__ void __launch_bounds__(256)
 sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den, int h, int d,
                       const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw, const void *kv_a, int64_t na,
                       const void *kv_b, float *__restrict__ o, size_t a_stride, size_t b_stride, int seq_mod) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ __align__(16) float s_p[PV_JC][HG];
     __shared__ int32_t s_id[PV_JC];
     const int t = blockIdx.y, h0 = (int)blockIdx.x * HG, tid = threadIdx.x;
@@ -564,6 +576,8 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
 // Drops negative ids keeping order (reference c/attn.h:1314-1321).
 __global__ void compact_ids_kernel(const int32_t *__restrict__ idxs, int idxw,
                                    int32_t *__restrict__ out, int *__restrict__ ns) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ int s_base;
     __shared__ int w_cnt[32];
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -634,7 +648,7 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
     int32_t *ids = (int32_t *)((char *)scratch + sc_bytes);
     int *ns = (int *)((char *)scratch + ns_off);
     float *den = (float *)((char *)scratch + den_off);
-    compact_ids_kernel<<<s, 256, 0, st>>>(idxs, idxw, ids, ns);
+    launch_k(compact_ids_kernel, s, 256, 0, st, idxs, idxw, ids, ns);
     APUS_LAUNCHED();
     static const int tiled = [] { const char *e = getenv("APUS_ATTN_TILED"); return !(e && e[0] == '0'); }();
     if (tiled && d % 64 == 0) {
@@ -651,21 +665,21 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         do {                                                                                                            \
             if (wide >= 148) {                                                                                          \
                 dim3 g((unsigned)ceil_div(idxw, 256), (unsigned)ceil_div(h, 16), (unsigned)s);                          \
-                sparse_scores_tile_kernel<BF, 8><<<g, 256, ss8, st>>>(q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,  \
+                launch_k(sparse_scores_tile_kernel<BF, 8>, g, 256, ss8, st, q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,  \
                                                                    sa, sb, seq_mod);                                    \
             } else {                                                                                                    \
                 dim3 g((unsigned)ceil_div(idxw, 64), (unsigned)ceil_div(h, 16), (unsigned)s);                           \
-                sparse_scores_tile_kernel<BF, 2><<<g, 64, ss2, st>>>(q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,   \
+                launch_k(sparse_scores_tile_kernel<BF, 2>, g, 64, ss2, st, q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,   \
                                                                   sa, sb, seq_mod);                                     \
             }                                                                                                           \
             APUS_LAUNCHED();                                                                                            \
-            sparse_softmax_kernel<<<dim3((unsigned)h, (unsigned)s), 256, sm2, st>>>(sc, sink, h, ns, idxw, den);       \
+            launch_k(sparse_softmax_kernel, dim3((unsigned)h, (unsigned)s), 256, sm2, st, sc, sink, h, ns, idxw, den);       \
             APUS_LAUNCHED();                                                                                            \
             if (hgs == 16)                                                                                              \
-                sparse_pv_tile_kernel<BF, 16><<<dim3((unsigned)ceil_div(h, 16), (unsigned)s), 256, 0, st>>>(            \
+                launch_k(sparse_pv_tile_kernel<BF, 16>, dim3((unsigned)ceil_div(h, 16), (unsigned)s), 256, 0, st,             \
                     sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);                                  \
             else                                                                                                        \
-                sparse_pv_tile_kernel<BF, 4><<<dim3((unsigned)ceil_div(h, 4), (unsigned)s), 256, 0, st>>>(              \
+                launch_k(sparse_pv_tile_kernel<BF, 4>, dim3((unsigned)ceil_div(h, 4), (unsigned)s), 256, 0, st,               \
                     sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);                                  \
             APUS_LAUNCHED();                                                                                            \
         } while (0)
@@ -682,16 +696,16 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         ensure_dyn_smem(kv_bf16 ? (const void *)sparse_pv_kernel<true> : (const void *)sparse_pv_kernel<false>, sm2))
         return 1;
     if (kv_bf16) {
-        sparse_scores_kernel<true><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
+        launch_k(sparse_scores_kernel<true>, g1, SA_IDS * SA_HEADS, sm1, st, q, h, d, ids, ns, idxw, scale,
                                                                        kv_a, na, kv_b, sc, sa, sb, seq_mod);
         APUS_LAUNCHED();
-        sparse_pv_kernel<true><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);
+        launch_k(sparse_pv_kernel<true>, g2, 256, sm2, st, sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);
         APUS_LAUNCHED();
     } else {
-        sparse_scores_kernel<false><<<g1, SA_IDS * SA_HEADS, sm1, st>>>(q, h, d, ids, ns, idxw, scale,
+        launch_k(sparse_scores_kernel<false>, g1, SA_IDS * SA_HEADS, sm1, st, q, h, d, ids, ns, idxw, scale,
                                                                         kv_a, na, kv_b, sc, sa, sb, seq_mod);
         APUS_LAUNCHED();
-        sparse_pv_kernel<false><<<g2, 256, sm2, st>>>(sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);
+        launch_k(sparse_pv_kernel<false>, g2, 256, sm2, st, sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);
         APUS_LAUNCHED();
     }
     return 0;

@@ -31,6 +31,8 @@ __global__ void __launch_bounds__(1024)
 row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y, int y_stride, int n,
                int flags, const float *__restrict__ norm_w, float eps, int rd,
                const float *__restrict__ cs, int rows_per_cs, int cs_stride, const RowDyn dyn) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     if (dyn.pos) {                             // position read on the device (see RowDyn)
         const long long p = *dyn.pos;
         if (dyn.gate_ratio > 0) {
@@ -130,6 +132,8 @@ row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y,
 __global__ void __launch_bounds__(256)
 rope_rows_kernel(float *__restrict__ y, int stride, int n, int rows, int inverse, int rd, const float *__restrict__ cs,
                  int rows_per_cs, int cs_stride, const RowDyn dyn) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     if (dyn.pos && cs) {
         const long long r = *dyn.pos + dyn.cs_bias;
         cs += (r > 0 ? r : 0) * rd;
@@ -153,6 +157,8 @@ __global__ void __launch_bounds__(256)
 qnorm_rope_rows_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y, int y_stride, int rows,
                        float eps, int rd, int seq, const float *__restrict__ cs, int rows_per_cs, int cs_stride,
                        const RowDyn dyn) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     constexpr int N = 128 * NV;
     __shared__ __align__(16) float s_sq[8][N];
     if (dyn.pos && cs) {
@@ -224,7 +230,7 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
     if (rows >= 32 && no_gate && cs && rd % 4 == 0 && rd <= n && (base == ROW_ROPE || base == ROW_ROPE_INV) && x == y &&
         x_stride == y_stride && x_stride % 2 == 0 && (n - rd) % 2 == 0) {
         const long long pairs = (long long)rows * (rd / 2);
-        rope_rows_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, y_stride, n, rows, base == ROW_ROPE_INV, rd, cs,
+        launch_k(rope_rows_kernel, (unsigned)((pairs + 255) / 256), 256, 0, st, y, y_stride, n, rows, base == ROW_ROPE_INV, rd, cs,
                                                                          rows_per_cs > 0 ? rows_per_cs : 1, cs_stride,
                                                                          dyn ? *dyn : none);
         APUS_LAUNCHED();
@@ -235,13 +241,13 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
         const unsigned g = (unsigned)((rows + 7) / 8);
         const int seq = (flags & ROW_SEQ_SUM) ? 1 : 0, rpc = rows_per_cs > 0 ? rows_per_cs : 1;
         const RowDyn d = dyn ? *dyn : none;
-        if (n == 512) qnorm_rope_rows_kernel<4><<<g, 256, 0, st>>>(x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
-        else if (n == 256) qnorm_rope_rows_kernel<2><<<g, 256, 0, st>>>(x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
-        else qnorm_rope_rows_kernel<1><<<g, 256, 0, st>>>(x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
+        if (n == 512) launch_k(qnorm_rope_rows_kernel<4>, g, 256, 0, st, x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
+        else if (n == 256) launch_k(qnorm_rope_rows_kernel<2>, g, 256, 0, st, x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
+        else launch_k(qnorm_rope_rows_kernel<1>, g, 256, 0, st, x, x_stride, y, y_stride, rows, eps, rd, seq, cs, rpc, cs_stride, d);
         APUS_LAUNCHED();
         return 0;
     }
-    row_ops_kernel<<<rows, n, smem, st>>>(x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
+    launch_k(row_ops_kernel, rows, n, smem, st, x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
                                           rows_per_cs > 0 ? rows_per_cs : 1, cs_stride, dyn ? *dyn : none);
     APUS_LAUNCHED();
     return 0;
@@ -258,6 +264,8 @@ comp_step_kernel(float *__restrict__ kv_state, float *__restrict__ sc_state, lon
                  const float *__restrict__ kv_new, const float *__restrict__ sc_new, int new_stride,
                  const float *__restrict__ ape, int ratio, int overlap, int d, int slot, int should,
                  float *__restrict__ pooled, int pooled_stride, const long long *__restrict__ dyn_pos) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     if (dyn_pos) {
         const long long p = *dyn_pos;
         slot = (int)(p % ratio);
@@ -311,7 +319,7 @@ int comp_step(float *kv_state, float *sc_state, long long state_stride, const fl
     const int cd = (1 + overlap) * d;
     APUS_REQUIRE(cd <= 1024, "compressor: state width %d exceeds 1024", cd);
     if (n_seq <= 0) return 0;
-    comp_step_kernel<<<n_seq, ((cd + 31) / 32) * 32, 0, st>>>(kv_state, sc_state, state_stride, kv_new,
+    launch_k(comp_step_kernel, n_seq, ((cd + 31) / 32) * 32, 0, st, kv_state, sc_state, state_stride, kv_new,
                                                               sc_new, new_stride, ape, ratio, overlap, d,
                                                               slot, should, pooled, pooled_stride, dyn_pos);
     APUS_LAUNCHED();
@@ -329,6 +337,8 @@ idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, 
                  const float *__restrict__ cache, long long cache_stride, long long nb, int ih, int idm,
                  float *__restrict__ sc, const long long *__restrict__ dyn_pos, int ratio, long long chunk_pos0,
                  int chunk_seqs) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ float sm[];             // q [ih*idm], k [IDX_B*idm], terms [IDX_B*ih]
     q += (size_t)blockIdx.y * ih * idm;
     wt_raw += (size_t)blockIdx.y * ih;
@@ -372,7 +382,7 @@ int idx_scores(const float *q, const float *wt_raw, float wscale, const float *c
     size_t smem = ((size_t)ih * idm + IDX_B * idm + IDX_B * ih) * sizeof(float);
     if (ensure_dyn_smem((const void *)idx_score_kernel, smem)) return 1;
     dim3 grid((unsigned)((nb + IDX_B - 1) / IDX_B), (unsigned)n_seq);
-    idx_score_kernel<<<grid, ih * IDX_B, smem, st>>>(q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc,
+    launch_k(idx_score_kernel, grid, ih * IDX_B, smem, st, q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc,
                                                      dyn_pos, ratio, chunk_pos0, chunk_seqs);
     APUS_LAUNCHED();
     return 0;
@@ -384,6 +394,8 @@ int idx_scores(const float *q, const float *wt_raw, float wscale, const float *c
 __global__ void build_idx_kernel(int32_t *__restrict__ out, int win, long long pos,
                                  const int32_t *__restrict__ sel, int compw,
                                  const long long *__restrict__ dyn_pos, int ratio) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     out += (size_t)blockIdx.y * (win + compw);
     if (sel) sel += (size_t)blockIdx.y * compw;
@@ -411,7 +423,7 @@ __global__ void build_idx_kernel(int32_t *__restrict__ out, int win, long long p
 int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int compw, int n_seq, cudaStream_t st,
               const long long *dyn_pos, int ratio) {
     if (n_seq <= 0) return 0;
-    build_idx_kernel<<<dim3(ceil_div(win + compw, 256), n_seq), 256, 0, st>>>(out, win, pos, sel, compw, dyn_pos,
+    launch_k(build_idx_kernel, dim3(ceil_div(win + compw, 256), n_seq), 256, 0, st, out, win, pos, sel, compw, dyn_pos,
                                                                               ratio);
     APUS_LAUNCHED();
     return 0;
@@ -420,6 +432,8 @@ int build_idx(int32_t *out, int win, long long pos, const int32_t *sel, int comp
 __global__ void scatter_rows_kernel(float *__restrict__ dst, long long dst_stride,
                                     const float *__restrict__ src, int n,
                                     const long long *__restrict__ dyn_pos, int win) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     if (dyn_pos) dst += (size_t)(*dyn_pos % win) * n;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[(size_t)blockIdx.y * dst_stride + i] = src[(size_t)blockIdx.y * n + i];
@@ -428,7 +442,7 @@ __global__ void scatter_rows_kernel(float *__restrict__ dst, long long dst_strid
 int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int rows, cudaStream_t st,
                  const long long *dyn_pos, int win) {
     if (rows <= 0) return 0;
-    scatter_rows_kernel<<<dim3(ceil_div(n, 256), rows), 256, 0, st>>>(dst, dst_stride, src, n, dyn_pos, win);
+    launch_k(scatter_rows_kernel, dim3(ceil_div(n, 256), rows), 256, 0, st, dst, dst_stride, src, n, dyn_pos, win);
     APUS_LAUNCHED();
     return 0;
 }
@@ -442,6 +456,8 @@ int scatter_rows(float *dst, long long dst_stride, const float *src, int n, int 
 // dropped) and then its compressed ids, offset by win + s.
 __global__ void win_ext_kernel(float *__restrict__ ext, const float *__restrict__ ring, const float *__restrict__ kv,
                                int win, int s, int d, int n_seq, long long pos0) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int j = blockIdx.y, seq = blockIdx.z;
     float *dst = ext + ((size_t)seq * (win + s) + j) * d;
     const float *src = nullptr;
@@ -455,6 +471,8 @@ __global__ void win_ext_kernel(float *__restrict__ ext, const float *__restrict_
 // the ring after the chunk: the last min(s, win) rows at their slots (c/attn.h:1642-1658)
 __global__ void ring_update_kernel(float *__restrict__ ring, const float *__restrict__ kv, int win, int s, int d,
                                    int n_seq, long long pos0, int t0) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int t = t0 + blockIdx.y, seq = blockIdx.z;
     float *dst = ring + ((size_t)seq * win + (size_t)((pos0 + t) % win)) * d;
     const float *src = kv + ((size_t)t * n_seq + seq) * d;
@@ -463,20 +481,22 @@ __global__ void ring_update_kernel(float *__restrict__ ring, const float *__rest
 int win_ext(float *ext, const float *ring, const float *kv, int win, int s, int d, int n_seq, long long pos0,
             cudaStream_t st) {
     if (s <= 0 || n_seq <= 0) return 0;
-    win_ext_kernel<<<dim3(ceil_div(d, 256), win + s, n_seq), 256, 0, st>>>(ext, ring, kv, win, s, d, n_seq, pos0);
+    launch_k(win_ext_kernel, dim3(ceil_div(d, 256), win + s, n_seq), 256, 0, st, ext, ring, kv, win, s, d, n_seq, pos0);
     APUS_LAUNCHED();
     return 0;
 }
 int ring_update(float *ring, const float *kv, int win, int s, int d, int n_seq, long long pos0, cudaStream_t st) {
     if (s <= 0 || n_seq <= 0) return 0;
     const int t0 = s > win ? s - win : 0;
-    ring_update_kernel<<<dim3(ceil_div(d, 256), s - t0, n_seq), 256, 0, st>>>(ring, kv, win, s, d, n_seq, pos0, t0);
+    launch_k(ring_update_kernel, dim3(ceil_div(d, 256), s - t0, n_seq), 256, 0, st, ring, kv, win, s, d, n_seq, pos0, t0);
     APUS_LAUNCHED();
     return 0;
 }
 
 __global__ void build_idx_chunk_kernel(int32_t *__restrict__ out, int win, int s, long long pos0, int n_seq,
                                        const int32_t *__restrict__ sel, int compcap, int ratio) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int j = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
     if (j >= win + compcap) return;
     const int t = row / n_seq;
@@ -494,7 +514,7 @@ __global__ void build_idx_chunk_kernel(int32_t *__restrict__ out, int win, int s
 int build_idx_chunk(int32_t *out, int win, int s, long long pos0, int n_seq, const int32_t *sel, int compcap, int ratio,
                     cudaStream_t st) {
     if (s <= 0 || n_seq <= 0) return 0;
-    build_idx_chunk_kernel<<<dim3(ceil_div(win + compcap, 256), s * n_seq), 256, 0, st>>>(out, win, s, pos0, n_seq, sel,
+    launch_k(build_idx_chunk_kernel, dim3(ceil_div(win + compcap, 256), s * n_seq), 256, 0, st, out, win, s, pos0, n_seq, sel,
                                                                                           compcap, ratio);
     APUS_LAUNCHED();
     return 0;
@@ -503,6 +523,8 @@ int build_idx_chunk(int32_t *out, int win, int s, long long pos0, int n_seq, con
 // First index of the maximum: strict greater-than scan order (reference c/sample.h:76-81).
 __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(const float *__restrict__ x, int n, int32_t *__restrict__ out) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const float *r = x + (size_t)blockIdx.x * n;
@@ -588,13 +610,15 @@ int argmax_rows(const float *x, int n, int rows, int32_t *out, cudaStream_t st) 
     if (n >= 16384 && n % 4 == 0 && ((uintptr_t)x & 15) == 0)
         argmax_rows_cl_kernel<<<rows * AMAX_CL, 512, 0, st>>>(x, n, out);
     else
-        argmax_rows_kernel<<<rows, 1024, 0, st>>>(x, n, out);
+        launch_k(argmax_rows_kernel, rows, 1024, 0, st, x, n, out);
     APUS_LAUNCHED();
     return 0;
 }
 
 __global__ void embed_rows_kernel(const void *__restrict__ table, int bf16, const int64_t *__restrict__ ids,
                                   int hc, int dim, float *__restrict__ out) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= dim) return;
     const int64_t id = ids[r];
@@ -606,7 +630,7 @@ __global__ void embed_rows_kernel(const void *__restrict__ table, int bf16, cons
 int embed_rows(const void *table, int bf16, const int64_t *ids, int rows, int hc, int dim, float *out,
                cudaStream_t st) {
     if (rows <= 0) return 0;
-    embed_rows_kernel<<<dim3(ceil_div(dim, 256), rows), 256, 0, st>>>(table, bf16, ids, hc, dim, out);
+    launch_k(embed_rows_kernel, dim3(ceil_div(dim, 256), rows), 256, 0, st, table, bf16, ids, hc, dim, out);
     APUS_LAUNCHED();
     return 0;
 }

@@ -1,6 +1,8 @@
 // Shared device/host helpers for libapus_b200: numeric format conversions that
 // reproduce the reference bit for bit, error plumbing, and the launch counter.
 #pragma once
+#include <string.h>
+#include <utility>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -52,6 +54,31 @@ int ensure_dyn_smem(const void *func, size_t bytes);    // api.cu
             return 1;                                                          \
         }                                                                      \
     } while (0)
+
+// ---- programmatic dependent launch ----------------------------------------------------------
+// A step is a chain of short kernels; each launch_k'd kernel may be scheduled while the one before it
+// on the stream is still running (its blocks are placed, parameters read, prologue run) and then
+// waits in APUS_PDL_WAIT until that kernel has completed and its writes are visible.  Rule: a kernel
+// launched through launch_k executes APUS_PDL_WAIT before it touches global memory at all (also
+// before it overwrites anything: the kernel before it may still be reading it).  APUS_PDL_GO lets
+// the kernel after this one be scheduled; both are no-ops when there is nothing to wait for.
+// APUS_PDL=0 in the environment launches everything fully serialised.
+#define APUS_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+#define APUS_PDL_GO() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+bool pdl_enabled();                             // api.cu
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                   Args &&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 #define APUS_LAUNCHED()                                                        \
     do {                                                                       \

@@ -77,6 +77,8 @@ __device__ __forceinline__ float wscale(uint32_t word, int b) {
 template <int FMT, int NT, bool PAIR, bool ZS>
 __global__ void __launch_bounds__(256, (NT <= 2 ? 2 : 1))
 gemm_small_kernel(const GemmSmallArgs a) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ __align__(16) uint8_t smem[];
     const int K = a.K, O = a.O, KG = K >> 7;
     const int pitch = K + 32;               // +32 B: bank-conflict-free 8-byte reads
@@ -307,7 +309,7 @@ static int launch(const GemmSmallArgs &a, cudaStream_t st) {
     auto kern = gemm_small_kernel<FMT, NT, PAIR, ZS>;
     if (ensure_dyn_smem((const void *)kern, smem)) return 1;
     dim3 grid((unsigned)(FMT == 8 ? a.O / 16 : ceil_div(a.O, 128)), (unsigned)a.n_groups);
-    kern<<<grid, 256, smem, st>>>(a);
+    launch_k(kern, grid, 256, smem, st, a);
     APUS_LAUNCHED();
     return 0;
 }

@@ -74,6 +74,8 @@ template <bool PAIR, int NS>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int STAGE = TC_A_BYTES * (PAIR ? 2 : 1) + TC_B_BYTES;
@@ -356,7 +358,7 @@ static int launch_tc(const TcArgs &a, cudaStream_t st) {
     auto kern = gemm_tc_kernel<PAIR, NS>;
     if (ensure_dyn_smem((const void *)kern, smem)) return 1;
     dim3 grid((unsigned)(a.O / 128), (unsigned)a.n_groups, (unsigned)(a.ksplit > 1 ? a.ksplit : 1));
-    kern<<<grid, TC_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
+    launch_k(kern, grid, TC_THREADS, smem, st, *reinterpret_cast<const CUtensorMap *>(a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.pair ? a.map_b : a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.map_x), a);
     APUS_LAUNCHED();

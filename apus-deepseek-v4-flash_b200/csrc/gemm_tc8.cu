@@ -66,6 +66,8 @@ template <bool PAIR, int NS>
 __global__ void __launch_bounds__(T8_THREADS, 2)
 gemm_tc8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_x, const Tc8Args a) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int STAGE = T8_A_BYTES * (PAIR ? 2 : 1) + T8_B_BYTES;
@@ -285,6 +287,8 @@ __device__ __forceinline__ uint32_t idesc_f8_wide() {
 __global__ void __launch_bounds__(T8_THREADS, 1)
 gemm_tc8_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_x,
                      const Tc8Args a) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_BYTES = T8W_N * 128, STAGE = T8_A_BYTES + B_BYTES, NS = T8W_NS, NACC = T8W_NACC;
@@ -417,7 +421,7 @@ int launch_tc8(const Tc8Args &a, cudaStream_t st) {
     auto kern = gemm_tc8_kernel<PAIR, NS>;
     if (ensure_dyn_smem((const void *)kern, 224 * 1024)) return 1;
     dim3 grid((unsigned)(a.O / 128), (unsigned)((a.M + T8_N - 1) / T8_N), (unsigned)(a.ksplit > 1 ? a.ksplit : 1));
-    kern<<<grid, T8_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
+    launch_k(kern, grid, T8_THREADS, smem, st, *reinterpret_cast<const CUtensorMap *>(a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.pair ? a.map_b : a.map_a),
                                         *reinterpret_cast<const CUtensorMap *>(a.map_x), a);
     APUS_LAUNCHED();
@@ -451,7 +455,7 @@ int gemm_tc8_wide(const Tc8Args &a, cudaStream_t st) {
     const size_t smem = (size_t)T8W_NS * (T8_A_BYTES + T8W_N * 128) + 1024 + 256 + (size_t)NC * T8W_N * 4 + (size_t)NC * 4;
     if (ensure_dyn_smem((const void *)gemm_tc8_wide_kernel, 224 * 1024)) return 1;
     dim3 grid((unsigned)(a.O / 128), (unsigned)((a.M + T8W_N - 1) / T8W_N));
-    gemm_tc8_wide_kernel<<<grid, T8_THREADS, smem, st>>>(*reinterpret_cast<const CUtensorMap *>(a.map_a),
+    launch_k(gemm_tc8_wide_kernel, grid, T8_THREADS, smem, st, *reinterpret_cast<const CUtensorMap *>(a.map_a),
                                                          *reinterpret_cast<const CUtensorMap *>(a.map_x), a);
     APUS_LAUNCHED();
     return 0;

@@ -52,6 +52,8 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
 template <int NS>
 __global__ void __launch_bounds__(TB_THREADS, 2)
 gemm_tcbf_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const TcbfArgs a) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)NS * TB_STAGE);
@@ -181,6 +183,8 @@ gemm_tcbf_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 }
 
 __global__ void f32_to_bf16_kernel(const float *x, uint16_t *y, long long n) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i + 3 < n) {
         const float4 v = *reinterpret_cast<const float4 *>(x + i);
@@ -218,7 +222,7 @@ int tcbf_make_act_map(void *out_map, const void *x_bf16, long long rows, long lo
 
 int f32_to_bf16(const float *x, uint16_t *y, long long n, cudaStream_t st) {
     if (n <= 0) return 0;
-    f32_to_bf16_kernel<<<(unsigned)((n + 1023) / 1024), 256, 0, st>>>(x, y, n);
+    launch_k(f32_to_bf16_kernel, (unsigned)((n + 1023) / 1024), 256, 0, st, x, y, n);
     APUS_LAUNCHED();
     return 0;
 }
@@ -247,11 +251,11 @@ int gemm_tcbf(const TcbfArgs &a, cudaStream_t st) {
     if (ctas <= 148) {                                   // one CTA per SM: a deep ring hides the memory latency
         constexpr int NS = 10;
         if (ensure_dyn_smem((const void *)gemm_tcbf_kernel<NS>, NS * TB_STAGE + 2048)) return 1;
-        gemm_tcbf_kernel<NS><<<grid, TB_THREADS, NS * TB_STAGE + 2048, st>>>(*mw, *mx, a);
+        launch_k(gemm_tcbf_kernel<NS>, grid, TB_THREADS, NS * TB_STAGE + 2048, st, *mw, *mx, a);
     } else {
         constexpr int NS = 5;
         if (ensure_dyn_smem((const void *)gemm_tcbf_kernel<NS>, NS * TB_STAGE + 2048)) return 1;
-        gemm_tcbf_kernel<NS><<<grid, TB_THREADS, NS * TB_STAGE + 2048, st>>>(*mw, *mx, a);
+        launch_k(gemm_tcbf_kernel<NS>, grid, TB_THREADS, NS * TB_STAGE + 2048, st, *mw, *mx, a);
     }
     APUS_LAUNCHED();
     return 0;

@@ -34,6 +34,8 @@ __global__ void __launch_bounds__(256)
 f32_linear_kernel(const void *__restrict__ wv, const float *__restrict__ x,
                   float *__restrict__ out, int M, int K, int O, int flags, long long w_stride,
                   long long x_stride, int x_ld, long long out_stride, int out_ld) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ float part[8][OT * MT];
     wv = WBF16 ? (const void *)(reinterpret_cast<const uint16_t *>(wv) + blockIdx.z * w_stride)
                : (const void *)(reinterpret_cast<const float *>(wv) + blockIdx.z * w_stride);
@@ -235,6 +237,8 @@ __global__ void __launch_bounds__(SQ_THREADS, 1)
 f32_linear_seq_kernel(const void *__restrict__ wv, const float *__restrict__ x, float *__restrict__ out,
                       int M, int K, int O, int flags, long long w_stride, long long x_stride, int x_ld,
                       long long out_stride, int out_ld) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     using Cf = SeqCfg<WBF16, R, MTT, MG, NST>;
     constexpr int ROWS = Cf::ROWS, TPC = Cf::TPC, ESZ = Cf::ESZ, WP_RAW = Cf::WP_RAW, STAGE = Cf::STAGE;
     constexpr int W_CH = SQ_KT * ESZ / 16;               // 16-byte chunks per stored weight row of a tile
@@ -397,7 +401,7 @@ static cudaError_t seq_launch(cudaStream_t st, int batch, const void *w, const f
     auto kern = f32_linear_seq_kernel<WBF16, R, MTT, MG, NST>;
     if (ensure_dyn_smem((const void *)kern, Cf::SMEM)) return cudaErrorInvalidValue;
     const dim3 grid((unsigned)ceil_div(O, Cf::ROWS), (unsigned)ceil_div(M, Cf::TPC), (unsigned)batch);
-    kern<<<grid, SQ_THREADS, Cf::SMEM, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
+    launch_k(kern, grid, SQ_THREADS, Cf::SMEM, st, w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
     return cudaSuccess;
 }
 
@@ -432,13 +436,13 @@ static void launch_linear(const void *w, long long ws, const float *x, long long
                           cudaStream_t st) {
     if (M == 1) {
         dim3 grid((unsigned)ceil_div(O, 8), 1, (unsigned)batch);
-        f32_linear_kernel<WBF16, 8, 1><<<grid, 256, 0, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
+        launch_k(f32_linear_kernel<WBF16, 8, 1>, grid, 256, 0, st, w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
     } else if (M <= 4) {
         dim3 grid((unsigned)ceil_div(O, 4), 1, (unsigned)batch);
-        f32_linear_kernel<WBF16, 4, 4><<<grid, 256, 0, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
+        launch_k(f32_linear_kernel<WBF16, 4, 4>, grid, 256, 0, st, w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
     } else {
         dim3 grid((unsigned)ceil_div(O, 4), (unsigned)ceil_div(M, 8), (unsigned)batch);
-        f32_linear_kernel<WBF16, 4, 8><<<grid, 256, 0, st>>>(w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
+        launch_k(f32_linear_kernel<WBF16, 4, 8>, grid, 256, 0, st, w, x, out, M, K, O, flags, ws, xs, x_ld, os, out_ld);
     }
 }
 

@@ -39,6 +39,8 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 __global__ void __launch_bounds__(256)
 mhc_mix_kernel(const float *__restrict__ x4, const float *__restrict__ fn, int nx, int nmix,
                float *__restrict__ raw) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ float red[32];
     const int j = blockIdx.x, row = blockIdx.y;
     const float *x = x4 + (size_t)row * nx;
@@ -78,6 +80,8 @@ template <int TOK>
 __global__ void __launch_bounds__(288)
 mhc_mix_seq_kernel(const float *__restrict__ x4, const float *__restrict__ fn, int nx, int nmix,
                    int MIX_TI, int rows, float *__restrict__ raw) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ __align__(16) float s_prod[];
     const int C = nmix + 1, stride = MIX_TI + 4, tid = threadIdx.x;
     const int row0 = blockIdx.x * TOK, c_lo = blockIdx.y * MIX_CPG, Cl = min(MIX_CPG, C - c_lo);
@@ -224,6 +228,8 @@ mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ ra
                       float *__restrict__ pre_out, float *__restrict__ post_out,
                       float *__restrict__ comb_out, float *__restrict__ y,
                       float *__restrict__ y_normed, int seq) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ __align__(16) float s_sq[];   // seq: d squares of the collapsed row
     __shared__ float s_pre[MHC_MAX_N];
     __shared__ float red[32];
@@ -440,6 +446,8 @@ mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__
 __global__ void mhc_post_kernel(const float *__restrict__ f, const float *__restrict__ res,
                                 const float *__restrict__ post, const float *__restrict__ comb,
                                 float *__restrict__ y4, int d, int n) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int row = blockIdx.y;
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= d) return;
@@ -478,7 +486,7 @@ static float *ensure_raw(size_t floats, float *callers) {
 static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float *raw, int rows,
                       cudaStream_t st) {
     if (sum_tree(APUS_CUDA_TREE_MHC_MAPS)) {
-        mhc_mix_kernel<<<dim3(nmix + 1, rows), 256, 0, st>>>(x4, fn, nx, nmix, raw);
+        launch_k(mhc_mix_kernel, dim3(nmix + 1, rows), 256, 0, st, x4, fn, nx, nmix, raw);
         APUS_LAUNCHED();
         return 0;
     }
@@ -495,11 +503,11 @@ static int launch_mix(const float *x4, const float *fn, int nx, int nmix, float 
         const int tok = 2, ti = 256;
         const size_t smem = (size_t)2 * tok * MIX_CPG * (ti + 4) * sizeof(float);
         const dim3 grid((unsigned)((rows + tok - 1) / tok), gy);
-        mhc_mix_seq_kernel<2><<<grid, 288, smem, st>>>(x4, fn, nx, nmix, ti, rows, raw);
+        launch_k(mhc_mix_seq_kernel<2>, grid, 288, smem, st, x4, fn, nx, nmix, ti, rows, raw);
     } else {
         const int ti = 1024;
         const size_t smem = (size_t)2 * MIX_CPG * (ti + 4) * sizeof(float);
-        mhc_mix_seq_kernel<1><<<dim3((unsigned)rows, gy), 288, smem, st>>>(x4, fn, nx, nmix, ti, rows, raw);
+        launch_k(mhc_mix_seq_kernel<1>, dim3((unsigned)rows, gy), 288, smem, st, x4, fn, nx, nmix, ti, rows, raw);
     }
     APUS_LAUNCHED();
     return 0;
@@ -518,7 +526,7 @@ static int launch_finish(const float *x4, const float *raw, int d, int n, int nm
                                                                             norm_eps, hc_eps, iters, head_mode, norm_w,
                                                                             rms_eps, pre, post, comb, y, y_normed, finish_seq());
     } else {
-        mhc_pre_finish_kernel<<<rows, 256, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, head_scale, base, norm_eps,
+        launch_k(mhc_pre_finish_kernel, rows, 256, finish_smem(d), st, x4, raw, d, n, nmix, scale, head_scale, base, norm_eps,
                                                                  hc_eps, iters, head_mode, norm_w, rms_eps, pre, post,
                                                                  comb, y, y_normed, finish_seq());
     }
@@ -557,7 +565,7 @@ int mhc_post(const float *f, const float *res4, const float *post,
              cudaStream_t st) {
     APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N, "mhc: n=%d unsupported", n);
     if (rows <= 0) return 0;
-    mhc_post_kernel<<<dim3(ceil_div(d, 256), rows), 256, 0, st>>>(f, res4, post, comb, y4, d, n);
+    launch_k(mhc_post_kernel, dim3(ceil_div(d, 256), rows), 256, 0, st, f, res4, post, comb, y4, d, n);
     APUS_LAUNCHED();
     return 0;
 }

@@ -20,6 +20,8 @@ __global__ void router_finish_kernel(const float *__restrict__ logits,
                                      float *__restrict__ biased_out,
                                      int32_t *__restrict__ idx_out,
                                      float *__restrict__ wgt_out) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ float s_sp[];          // [E] unbiased scores
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
@@ -91,7 +93,7 @@ int router_finish(const float *logits, const float *bias, const int64_t *tid2eid
     if (s <= 0) return 0;
     int threads = ((E + 31) / 32) * 32;
     if (threads < 64) threads = 64;
-    router_finish_kernel<<<s, threads, E * sizeof(float), st>>>(
+    launch_k(router_finish_kernel, s, threads, E * sizeof(float), st, 
         logits, tid2eid ? nullptr : bias, tid2eid, ids, E, topk, route_scale, sp, biased,
         idx, wgt);
     APUS_LAUNCHED();
@@ -116,6 +118,8 @@ moe_group_kernel(const int32_t *__restrict__ eid, const int32_t *__restrict__ ro
                  int *__restrict__ sorted_row, GemmGroup *__restrict__ g13,
                  GemmGroup *__restrict__ g2, int *__restrict__ n_groups, int max_groups,
                  TcGroup *__restrict__ t13, TcGroup *__restrict__ t2, int o13, int o2) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ int s_cnt[1024], s_off[1024], s_goff[1024];
     __shared__ int s_eid[GROUP_SMEM_N];
     __shared__ int s_wsum[32], s_wgsum[32];
@@ -228,7 +232,7 @@ int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int row_div, int
               cudaStream_t st, TcGroup *t13, TcGroup *t2, int o13, int o2) {
     APUS_REQUIRE(slab.e_hi - slab.e_lo <= 1024, "moe_group: more than 1024 local experts");
     APUS_REQUIRE(rout_row || row_div > 0, "moe_group: no row mapping");
-    moe_group_kernel<<<1, 1024, 0, st>>>(rout_eid, rout_row, row_div, n_rout, slab, chunk, sorted_pos,
+    launch_k(moe_group_kernel, 1, 1024, 0, st, rout_eid, rout_row, row_div, n_rout, slab, chunk, sorted_pos,
                                          sorted_row, g13, g2, n_groups, max_groups, t13, t2, o13, o2);
     APUS_LAUNCHED();
     return 0;
@@ -242,6 +246,8 @@ int moe_group(const int32_t *rout_eid, const int32_t *rout_row, int row_div, int
 __global__ void moe_combine_kernel(const float *__restrict__ eo, const float *__restrict__ wgt,
                                    const float *__restrict__ shared, int topk, int dim,
                                    float *__restrict__ out, float *__restrict__ routed) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     int t = blockIdx.y;
     int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= dim) return;
@@ -272,7 +278,7 @@ int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
     APUS_REQUIRE(dim % 4 == 0, "moe_combine: dim=%d", dim);
     if (s <= 0) return 0;
     dim3 grid((unsigned)ceil_div(dim / 4, 256), (unsigned)s);
-    moe_combine_kernel<<<grid, 256, 0, st>>>(eo, wgt, shared, topk, dim, out, routed);
+    launch_k(moe_combine_kernel, grid, 256, 0, st, eo, wgt, shared, topk, dim, out, routed);
     APUS_LAUNCHED();
     return 0;
 }
@@ -285,6 +291,8 @@ int moe_combine(const float *eo, const float *wgt, const float *shared, int s,
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int32_t *__restrict__ idx, int n_rout, int per_rank, int world, int slots,
                int32_t *__restrict__ send_eids, int32_t *__restrict__ slot_of) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ int s_dest[];
     for (int i = threadIdx.x; i < world * slots; i += blockDim.x) send_eids[i] = -1;
     for (int p = threadIdx.x; p < n_rout; p += blockDim.x) s_dest[p] = idx[p] / per_rank;
@@ -303,6 +311,8 @@ ep_plan_kernel(const int32_t *__restrict__ idx, int n_rout, int per_rank, int wo
 __global__ void __launch_bounds__(256)
 ep_rows_kernel(const float *__restrict__ src, int dim, const int32_t *__restrict__ slot_of, int topk, int gather,
                float *__restrict__ dst) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int p = blockIdx.x, slot = slot_of[p];
     const float4 *s4 = reinterpret_cast<const float4 *>(src + (size_t)(gather ? slot : p / topk) * dim);
     float4 *d4 = reinterpret_cast<float4 *>(dst + (size_t)(gather ? p : slot) * dim);
@@ -315,6 +325,8 @@ ep_rows_kernel(const float *__restrict__ src, int dim, const int32_t *__restrict
 __global__ void __launch_bounds__(256)
 ep_pack_q_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ scales, int dim,
                  const int32_t *__restrict__ slot_of, int topk, uint8_t *__restrict__ packed) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int p = blockIdx.x, row = p / topk, nab = dim >> 7;
     const size_t rb = (size_t)dim + (size_t)nab * 4;
     uint8_t *dst = packed + (size_t)slot_of[p] * rb;
@@ -328,6 +340,8 @@ ep_pack_q_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ sc
 __global__ void __launch_bounds__(256)
 ep_gather_q_kernel(const uint8_t *__restrict__ packed, int dim, const int *__restrict__ sorted_row,
                    const int *__restrict__ n_dev, uint8_t *__restrict__ codes, float *__restrict__ scales) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int p = blockIdx.x, nab = dim >> 7;
     if (p >= *n_dev) return;
     const size_t rb = (size_t)dim + (size_t)nab * 4;
@@ -342,6 +356,8 @@ ep_gather_q_kernel(const uint8_t *__restrict__ packed, int dim, const int *__res
 __global__ void __launch_bounds__(256)
 ep_unpack_bf16_kernel(const uint16_t *__restrict__ src, int dim, const int32_t *__restrict__ slot_of,
                       float *__restrict__ dst) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     const int p = blockIdx.x;
     const uint2 *s2 = reinterpret_cast<const uint2 *>(src + (size_t)slot_of[p] * dim);
     float4 *d4 = reinterpret_cast<float4 *>(dst + (size_t)p * dim);
@@ -354,33 +370,33 @@ ep_unpack_bf16_kernel(const uint16_t *__restrict__ src, int dim, const int32_t *
 int ep_pack_q(const uint8_t *codes, const float *scales, int dim, const int32_t *slot_of, int n_rout, int topk,
               uint8_t *packed, cudaStream_t st) {
     if (n_rout <= 0) return 0;
-    ep_pack_q_kernel<<<n_rout, 256, 0, st>>>(codes, scales, dim, slot_of, topk, packed);
+    launch_k(ep_pack_q_kernel, n_rout, 256, 0, st, codes, scales, dim, slot_of, topk, packed);
     APUS_LAUNCHED();
     return 0;
 }
 int ep_gather_q(const uint8_t *packed, int dim, const int *sorted_row, const int *n_dev, int n_max, uint8_t *codes,
                 float *scales, cudaStream_t st) {
     if (n_max <= 0) return 0;
-    ep_gather_q_kernel<<<n_max, 256, 0, st>>>(packed, dim, sorted_row, n_dev, codes, scales);
+    launch_k(ep_gather_q_kernel, n_max, 256, 0, st, packed, dim, sorted_row, n_dev, codes, scales);
     APUS_LAUNCHED();
     return 0;
 }
 int ep_unpack_bf16(const uint16_t *src, int dim, const int32_t *slot_of, int n_rout, float *dst, cudaStream_t st) {
     if (n_rout <= 0) return 0;
-    ep_unpack_bf16_kernel<<<n_rout, 256, 0, st>>>(src, dim, slot_of, dst);
+    launch_k(ep_unpack_bf16_kernel, n_rout, 256, 0, st, src, dim, slot_of, dst);
     APUS_LAUNCHED();
     return 0;
 }
 
 int ep_plan(const int32_t *idx, int n_rout, int per_rank, int world, int slots, int32_t *send_eids,
             int32_t *slot_of, cudaStream_t st) {
-    ep_plan_kernel<<<1, 1024, (size_t)n_rout * sizeof(int), st>>>(idx, n_rout, per_rank, world, slots, send_eids, slot_of);
+    launch_k(ep_plan_kernel, 1, 1024, (size_t)n_rout * sizeof(int), st, idx, n_rout, per_rank, world, slots, send_eids, slot_of);
     APUS_LAUNCHED();
     return 0;
 }
 int ep_rows(const float *src, int dim, const int32_t *slot_of, int n_rout, int topk, int gather, float *dst,
             cudaStream_t st) {
-    ep_rows_kernel<<<n_rout, 256, 0, st>>>(src, dim, slot_of, topk, gather, dst);
+    launch_k(ep_rows_kernel, n_rout, 256, 0, st, src, dim, slot_of, topk, gather, dst);
     APUS_LAUNCHED();
     return 0;
 }

@@ -10,6 +10,8 @@ namespace apus {
 __global__ void act_quant_kernel(const float *__restrict__ x, const int *__restrict__ arow,
                                  int M, int K, uint8_t *__restrict__ codes,
                                  float *__restrict__ scales, const int *m_dev) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     int nab = K >> 7;
     if (m_dev) M = min(M, *m_dev);
     long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -37,7 +39,7 @@ int act_quant(const float *x, const int *arow, int M, int K, uint8_t *codes,
     APUS_REQUIRE(K % 128 == 0, "act_quant: K=%d must be a multiple of 128", K);
     if (M <= 0) return 0;
     long long warps = (long long)M * (K / 128);
-    act_quant_kernel<<<ceil_div(warps * 32, 256), 256, 0, st>>>(x, arow, M, K, codes,
+    launch_k(act_quant_kernel, ceil_div(warps * 32, 256), 256, 0, st, x, arow, M, K, codes,
                                                               scales, m_dev);
     APUS_LAUNCHED();
     return 0;
@@ -49,6 +51,8 @@ int act_quant(const float *x, const int *arow, int M, int K, uint8_t *codes,
 // it is a tree reduction.
 __global__ void rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ w,
                                 float eps, float *__restrict__ y, int64_t n, int seq) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     extern __shared__ __align__(16) float s_sq[];
     const float *xr = x + (size_t)blockIdx.x * n;
     float *yr = y + (size_t)blockIdx.x * n;
@@ -83,7 +87,7 @@ int rms_norm(const float *x, const float *w, float eps, float *y, int64_t n,
     const size_t smem = seq ? (size_t)n * sizeof(float) : 0;
     APUS_REQUIRE(smem <= 200 * 1024, "rms_norm: row of %lld elements exceeds the staging buffer", (long long)n);
     if (smem > 48 * 1024 && ensure_dyn_smem((const void *)rms_norm_kernel, 200 * 1024)) return 1;
-    rms_norm_kernel<<<(unsigned)rows, threads, smem, st>>>(x, w, eps, y, n, seq);
+    launch_k(rms_norm_kernel, (unsigned)rows, threads, smem, st, x, w, eps, y, n, seq);
     APUS_LAUNCHED();
     return 0;
 }

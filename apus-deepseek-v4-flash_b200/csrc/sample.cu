@@ -130,6 +130,8 @@ __global__ void __launch_bounds__(SMP_THREADS)
 sample_rows_kernel(const float *__restrict__ logits, int n, float temp, float top_p,
                    const double *__restrict__ u_in, unsigned long long *__restrict__ rng,
                    float *probs, int32_t *__restrict__ out) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     __shared__ unsigned long long s_hist[256];
     __shared__ __align__(8) unsigned s_misc[8];
     __shared__ int s_cnt[SMP_THREADS];
@@ -208,7 +210,7 @@ int sample_rows(const float *logits, int n, int rows, float temp, float top_p, c
     if (rows <= 0) return 0;
     if (temp <= 0.f) return argmax_rows(logits, n, rows, out, st);
     APUS_REQUIRE(u || rng, "sample: neither uniforms nor generator states given");
-    sample_rows_kernel<<<rows, SMP_THREADS, 0, st>>>(logits, n, temp, top_p, u, rng, probs, out);
+    launch_k(sample_rows_kernel, rows, SMP_THREADS, 0, st, logits, n, temp, top_p, u, rng, probs, out);
     APUS_LAUNCHED();
     return 0;
 }
