@@ -43,6 +43,14 @@ topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__re
     }
     const int tid = threadIdx.x;
 
+    const int lane = tid & 31, warp = tid >> 5;
+    if (k >= n) {
+        // every score is selected (a row shorter than k: the first 4 k positions of a sequence): only the order is left
+        for (int i = tid; i < n; i += TOPK_THREADS)
+            sel[i] = ((unsigned long long)order_key(row[i]) << 32) | (0xffffffffu - (unsigned)i);
+        k = n;
+        __syncthreads();
+    } else {
     // radix select: after the loop `prefix` is the key of the k-th largest score
     if (tid == 0) { s_prefix = 0; s_need = (unsigned)k; s_greater = 0; }
     for (int pass = 0; pass < 4; pass++) {
@@ -56,16 +64,36 @@ topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__re
             if ((key & himask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
         }
         __syncthreads();
-        if (tid == 0) {
-            unsigned need = s_need, acc = 0;
-            int b = 255;
-            for (; b > 0; b--) {
-                if (acc + hist[b] >= need) break;
-                acc += hist[b];
+        if (warp == 0) {
+            // the bin where the count from the top reaches `need` (bin 0 if it never does before it):
+            // lane L sums bins 255 - 8L .. 248 - 8L, a warp scan finds the lane, the lane walks its 8 bins
+            const unsigned need = s_need;
+            unsigned c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { c[j] = hist[255 - 8 * lane - j]; tot += c[j]; }
+            unsigned inc = tot;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const unsigned v = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) inc += v;
             }
-            s_greater += acc;
-            s_need = need - acc;
-            s_prefix = prefix | ((unsigned)b << shift);
+            const unsigned exc = inc - tot;
+            const unsigned hit = __ballot_sync(0xffffffffu, exc < need && inc >= need);
+            const int owner = hit ? __ffs(hit) - 1 : 31;
+            if (lane == owner) {
+                unsigned acc = exc;
+                int b = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int bin = 255 - 8 * lane - j;
+                    if (bin == 0) break;                          // bin 0 takes whatever is left
+                    if (acc + c[j] >= need) { b = bin; break; }
+                    acc += c[j];
+                }
+                s_greater += acc;
+                s_need = need - acc;
+                s_prefix = prefix | ((unsigned)b << shift);
+            }
         }
         __syncthreads();
     }
@@ -77,7 +105,6 @@ topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__re
 
     // index-ordered sweep: greater keys go to slots [0, n_greater) in any order
     // (sorted below); ties are appended in ascending index order.
-    const int lane = tid & 31, warp = tid >> 5;
     __shared__ unsigned w_tie[TOPK_THREADS / 32];
     for (int base = 0; base < n; base += TOPK_THREADS) {
         int i = base + tid;
@@ -101,6 +128,7 @@ topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__re
         __syncthreads();
         if (tid == 0) s_base += total;
         __syncthreads();
+    }
     }
 
     // bitonic sort, descending, on the composite (key, -index)

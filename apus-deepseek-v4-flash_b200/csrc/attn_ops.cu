@@ -349,16 +349,19 @@ idx_score_kernel(const float *__restrict__ q, const float *__restrict__ wt_raw, 
         nb = ((dyn_pos ? *dyn_pos : chunk_pos0 + blockIdx.y / chunk_seqs) + 1) / ratio;
         if ((long long)blockIdx.x * IDX_B >= nb) return;
     }
-    float *s_q = sm, *s_k = sm + ih * idm, *s_t = s_k + IDX_B * idm;
+    // q rows are padded by one word: the lanes of a warp walk different heads at the same k, and a
+    // pitch of idm (a multiple of 32) would put all of them on one bank
+    const int qp = idm + 1;
+    float *s_q = sm, *s_k = sm + ih * qp, *s_t = s_k + IDX_B * idm;
     const int hh = threadIdx.x % ih, bl = threadIdx.x / ih;
     const long long b = (long long)blockIdx.x * IDX_B + bl;
-    for (int i = threadIdx.x; i < ih * idm; i += blockDim.x) s_q[i] = q[i];
+    for (int i = threadIdx.x; i < ih * idm; i += blockDim.x) s_q[(i / idm) * qp + i % idm] = q[i];
     for (int i = threadIdx.x; i < IDX_B * idm; i += blockDim.x) {
         long long bb = (long long)blockIdx.x * IDX_B + i / idm;
         s_k[i] = bb < nb ? cache[bb * idm + i % idm] : 0.f;
     }
     __syncthreads();
-    const float *qv = s_q + hh * idm, *kv = s_k + bl * idm;
+    const float *qv = s_q + hh * qp, *kv = s_k + bl * idm;
     float dot = 0.f;
     for (int i = 0; i < idm; i++) dot = __fadd_rn(dot, __fmul_rn(qv[i], kv[i]));
     dot = bf16_round(dot);
@@ -379,7 +382,7 @@ int idx_scores(const float *q, const float *wt_raw, float wscale, const float *c
                int ratio, long long chunk_pos0, int chunk_seqs) {
     APUS_REQUIRE(ih <= 64 && ih >= 1, "indexer: %d heads unsupported", ih);
     if (nb <= 0 || n_seq <= 0) return 0;
-    size_t smem = ((size_t)ih * idm + IDX_B * idm + IDX_B * ih) * sizeof(float);
+    size_t smem = ((size_t)ih * (idm + 1) + IDX_B * idm + IDX_B * ih) * sizeof(float);
     if (ensure_dyn_smem((const void *)idx_score_kernel, smem)) return 1;
     dim3 grid((unsigned)((nb + IDX_B - 1) / IDX_B), (unsigned)n_seq);
     launch_k(idx_score_kernel, grid, ih * IDX_B, smem, st, q, wt_raw, wscale, cache, cache_stride, nb, ih, idm, sc,

@@ -62,7 +62,7 @@ int ensure_dyn_smem(const void *func, size_t bytes);    // api.cu
 // launched through launch_k executes APUS_PDL_WAIT before it touches global memory at all (also
 // before it overwrites anything: the kernel before it may still be reading it).  APUS_PDL_GO lets
 // the kernel after this one be scheduled; both are no-ops when there is nothing to wait for.
-// APUS_PDL=0 in the environment launches everything fully serialised.
+// APUS_PDL=0 in the environment launches everything fully serialised (the two instructions are then no-ops).
 #define APUS_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
 #define APUS_PDL_GO() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
 bool pdl_enabled();                             // api.cu

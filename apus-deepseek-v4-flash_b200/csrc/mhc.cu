@@ -367,6 +367,11 @@ mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__
     const int i0 = min(d, rank * per), i1 = min(d, i0 + per);
     const float *x = x4 + (size_t)row * n * d;
     float ss = 0.f;
+    // Shared memory of another CTA of the cluster may only be touched once that CTA runs: the CTAs of a
+    // cluster are placed together but need not have started together, and a store into rank 0's window
+    // before rank 0 has started is a fault (seen as sporadic "unspecified launch failure" once the grid
+    // held thousands of clusters).  The loop below stores into rank 0, so the cluster meets first.
+    if (y && y_normed && seq) cluster.sync();
     if (y) {
         for (int i = i0 + tid * 4; i < i1; i += blockDim.x * 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
