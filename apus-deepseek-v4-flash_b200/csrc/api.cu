@@ -113,6 +113,7 @@ int ensure_enabled() {
 // which main chain each side stream is working for right now (set when a branch begins; enqueueing
 // is host-sequential, so this is the chain whose launches are being issued)
 static cudaStream_t g_aux_owner[Ctx::N_AUX] = {nullptr, nullptr, nullptr};
+static bool g_aux_owned[Ctx::N_AUX] = {false, false, false};    // the owner may be the default stream (a null handle)
 
 cudaStream_t branch_begin(cudaStream_t main, int i) {
     Ctx &c = ctx();
@@ -123,6 +124,7 @@ cudaStream_t branch_begin(cudaStream_t main, int i) {
         return main;                            // no side stream: the chain simply runs in line
     }
     g_aux_owner[i] = main;
+    g_aux_owned[i] = true;
     return c.aux[i];
 }
 int branch_end(int i, cudaStream_t main) {
@@ -361,7 +363,7 @@ int stream_scratch(cudaStream_t st, size_t bytes, void **ws, size_t n_counters, 
     cudaStream_t owner = st;
     int branch = 0;
     for (int i = 0; i < Ctx::N_AUX; i++)
-        if (st == ctx().aux[i] && g_aux_owner[i]) { owner = g_aux_owner[i]; branch = i + 1; }
+        if (st == ctx().aux[i] && g_aux_owned[i]) { owner = g_aux_owner[i]; branch = i + 1; }
     const cudaStream_t key = owner == ctx().stream ? reinterpret_cast<cudaStream_t>(~(uintptr_t)0) : owner;
     Slot &s = slots[std::make_tuple(dev, key, branch)];
     if (bytes > s.ws.cap) {

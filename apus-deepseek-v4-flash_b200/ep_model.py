@@ -58,6 +58,8 @@ class EpModel:
         shapes, so the same graph serves every position.  Call after at least one
         plain step (workspaces are allocated by then)."""
         L, h = self.L, self.h
+        if self.graph:                                   # already recorded (the prompt does it after two positions)
+            return
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         check(L.apus_cuda_use_stream(side.cuda_stream, 0), "use_stream")      # synchronises outside the capture
@@ -75,7 +77,7 @@ class EpModel:
     def step(self, want_logits=True, feed_back=True):
         """One position of every sequence.  The ids of the step are whatever
         set_ids / the previous step's feed-back left on the device."""
-        if self.graph is not None and want_logits and feed_back:
+        if self.graph and want_logits and feed_back:
             self.graph.replay()
             check(self.L.apus_cuda_model_note_step(self.h), "note_step")
             return
@@ -102,14 +104,32 @@ class EpModel:
 
     def prefill(self, prompt):
         """prompt int64 numpy [batch, n]: consumed position by position; the greedy
-        token after the last position is left on the device as the next ids."""
+        token after the last position is left on the device as the next ids.  The
+        first two positions run as plain launches (they size every workspace), the
+        rest replay the recorded step: the prompt sits on the device, a position's
+        ids are copied over whatever the step before fed back, and nothing waits on
+        the host.  (The recorded step computes the head at every position; only the
+        last one's pick is used.)"""
+        import os
         import numpy as np
         n = prompt.shape[1]
+        check(self.L.apus_cuda_use_stream(torch.cuda.current_stream().cuda_stream, 0), "use_stream")
+        cols = torch.from_numpy(np.ascontiguousarray(prompt.T)).to(self.device)      # [n, batch]
+        record = os.environ.get("APUS_EP_GRAPH", "1") != "0"
         for t in range(n):
-            col = np.ascontiguousarray(prompt[:, t])
-            self.set_ids(col)
-            torch.cuda.current_stream().synchronize()       # `col` is host memory reused next turn
-            self.step(want_logits=(t == n - 1), feed_back=True)
+            self.ids.copy_(cols[t])
+            if record and t >= 2 and self.graph is None:
+                try:
+                    self.capture()
+                except Exception:                           # keep going on plain launches
+                    torch.cuda.synchronize()
+                    self.graph = False
+            if self.graph:
+                self.step(True, True)
+            else:
+                self.step(want_logits=(t == n - 1), feed_back=True)
+        if self.graph is False:
+            self.graph = None
 
     def read(self, logits=None, tokens=None):
         check(self.L.apus_cuda_model_read(self.h, capi.ptr(logits), capi.ptr(tokens)), "model_read")

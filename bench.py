@@ -417,13 +417,16 @@ def model_main_ep(a):
     torch.cuda.synchronize()
     mark("warm-up done")
     d0 = L.apus_cuda_dispatches()
+    recorded, ep.graph = ep.graph, None                 # the prompt may have left a recorded step behind
     ep.step()
+    ep.graph = recorded
     keep_tokens()
     per_step = int(L.apus_cuda_dispatches() - d0)       # kernels of one step, counted on plain launches
     graph_note = "each step replayed from one CUDA graph (library kernels + NCCL all-to-alls)"
     if os.environ.get("APUS_EP_GRAPH", "1") != "0":
         try:
-            ep.capture()
+            if not ep.graph:
+                ep.capture()
         except Exception as e:                          # keep going on plain launches
             graph_note = f"plain launches (graph capture failed: {type(e).__name__}: {e})"
             torch.cuda.synchronize()
@@ -513,7 +516,7 @@ def model_main_ep(a):
             "tokens_fnv1a": digest, "digest_tokens_per_seq": Wm + K + 2,
             "strong_bs32": strong32, "strong_bs1": strong1,
             "prefill": {"tokens": world * B * a.prompt, "ms": prefill_ms,
-                        "note": "expert-parallel loop: prompt consumed as consecutive decode steps"},
+                        "note": "expert-parallel loop: prompt consumed as consecutive decode steps replayed from the recorded step"},
             "roofline": None, "weights": {"bytes_per_rank": W.bytes}, "cuda_graph": graph_note,
             "note": "expert-parallel: experts sharded over the ranks, NCCL all-to-all dispatch/combine per layer; "
                     "the per-kernel roofline is reported by the 1-GPU run"}
