@@ -112,8 +112,8 @@ int ensure_enabled() {
 
 // which main chain each side stream is working for right now (set when a branch begins; enqueueing
 // is host-sequential, so this is the chain whose launches are being issued)
-static cudaStream_t g_aux_owner[Ctx::N_AUX] = {nullptr, nullptr, nullptr};
-static bool g_aux_owned[Ctx::N_AUX] = {false, false, false};    // the owner may be the default stream (a null handle)
+static cudaStream_t g_aux_owner[Ctx::N_AUX] = {};
+static bool g_aux_owned[Ctx::N_AUX] = {};    // the owner may be the default stream (a null handle)
 
 cudaStream_t branch_begin(cudaStream_t main, int i) {
     Ctx &c = ctx();

@@ -146,6 +146,20 @@ int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, St
     return 0;
 }
 
+// The two projections of a compressor (kv rows and gate scores, c/attn.h:960-975) read the same rows:
+// one launch over two problems when the two weights and the two outputs are a whole number of 16-byte
+// steps apart (device allocations are), else one launch each.  Same kernels, same sums either way.
+static int comp_project(const CompDev &W, const float *x, float *ckv, float *csc, int rows, int dim, int cd, cudaStream_t st) {
+    // distances in the flat device address space, in floats (the two tensors are separate allocations)
+    const long long bw = (long long)((uintptr_t)W.wgate - (uintptr_t)W.wkv), bo = (long long)((uintptr_t)csc - (uintptr_t)ckv);
+    const long long dw = bw / 4, dout = bo / 4;
+    if (bw > 0 && bo > 0 && bw % 16 == 0 && bo % 16 == 0)
+        return f32_linear_batched(W.wkv, (long long)dw, x, 0, dim, ckv, (long long)dout, cd, 2, rows, dim, cd,
+                                  APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st);
+    return f32_linear(W.wkv, x, ckv, rows, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st) ||
+           f32_linear(W.wgate, x, csc, rows, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st);
+}
+
 // One compressor decode step of B sequences; appends a finished entry to every
 // cache when the block completes (reference c/attn.h:960-1008 + 797-819).
 static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, int B, int dim, long long pos,
@@ -154,9 +168,7 @@ static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, in
     StepBufs b = b0;
     if (second_set) { b.ckv = b0.ckv2; b.csc = b0.csc2; b.pooled = b0.pooled2; }
     const int cd = (1 + W.overlap) * W.d;
-    if (f32_linear(W.wkv, x, b.ckv, B, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st) ||
-        f32_linear(W.wgate, x, b.csc, B, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st))
-        return 1;
+    if (comp_project(W, x, b.ckv, b.csc, B, dim, cd, st)) return 1;
     const int slot = (int)(pos % W.ratio);
     const int should = (pos + 1) % W.ratio == 0;
     if (comp_step(S.kv.as<float>(), S.sc.as<float>(), (long long)S.carry, b.ckv, b.csc, cd, W.ape, W.ratio,
@@ -212,6 +224,16 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
         sb = branch_begin(st, 1);
         if (compressor_step(A.comp, S.comp, x, B, c.dim, pos, cs_rp, b, sb, pos_dev, cs_table)) return 1;
     }
+    // the indexer's own compressor and its head weights read only x: they start with the step on a chain
+    // of their own (d) and meet the q-dependent part of the indexer (c) before the scores
+    cudaStream_t sd = st;
+    if (ratio && c.has_indexer) {
+        sd = branch_begin(st, 3);
+        if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, sd, pos_dev, cs_table, true)) return 1;
+        if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, c.idx_heads,
+                       APUS_CUDA_R_IN | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_IDX_WPROJ), sd))
+            return 1;
+    }
     // q path (c/attn.h:1525-1548)
     if (qgemm_dev(A.wq_a, nullptr, b.xq, b.xs, B, b.qa, true, 0.f, st)) return 1;
     if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st))
@@ -230,10 +252,7 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
             if (row_ops(b.iq, idm, b.iq, idm, B * ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr,
                         0.f, rd, cs_pos, B * ih, 0, sc, dp))
                 return 1;
-            if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, sc, pos_dev, cs_table, true)) return 1;
-            if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, ih,
-                           APUS_CUDA_R_IN | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_IDX_WPROJ), sc))
-                return 1;
+            if (sd != st && branch_end(3, sc)) return 1;          // (d) -> (c): cache entry and head weights are ready
             const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
             compw = (int)(c.idx_topk < nbs ? c.idx_topk : nbs);
             if (pos_dev) {                         // capacities; the live counts are derived on the device
@@ -289,9 +308,7 @@ static int compressor_chunk(const CompDev &W, CompStateDev &S, const float *x, i
     StepBufs b = b0;
     if (second_set) { b.ckv = b0.ckv2; b.csc = b0.csc2; b.pooled = b0.pooled2; }
     const int cd = (1 + W.overlap) * W.d, T = B * s;
-    if (f32_linear(W.wkv, x, b.ckv, T, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st) ||
-        f32_linear(W.wgate, x, b.csc, T, dim, cd, APUS_LIN_CLASS(APUS_CUDA_TREE_COMPRESSOR), st))
-        return 1;
+    if (comp_project(W, x, b.ckv, b.csc, T, dim, cd, st)) return 1;
     const int flags = ROW_BF16_IN | ROW_RMS_W | ROW_ROPE | ROW_BF16_OUT | (W.rotate ? (ROW_HADAMARD | ROW_FP4QAT) : ROW_FP8QAT);
     for (int t = 0; t < s; t++) {
         const long long pos = pos0 + t;

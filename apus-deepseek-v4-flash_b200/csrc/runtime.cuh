@@ -58,9 +58,9 @@ struct Ctx {
     cudaStream_t own_stream = nullptr;      // the one the library created (stream may be the caller's)
     // side streams for independent kernel chains inside a step (joined back before
     // the step goes on); each has an event for the fork and one for the join
-    static const int N_AUX = 3;
-    cudaStream_t aux[N_AUX] = {nullptr, nullptr, nullptr};
-    cudaEvent_t ev_fork[N_AUX] = {nullptr, nullptr, nullptr}, ev_join[N_AUX] = {nullptr, nullptr, nullptr};
+    static const int N_AUX = 4;
+    cudaStream_t aux[N_AUX] = {};
+    cudaEvent_t ev_fork[N_AUX] = {}, ev_join[N_AUX] = {};
     uint64_t bytes_uploaded = 0;
     std::unordered_map<const void *, DevQW *> qcache;      // quantised weights by host codes ptr
     std::unordered_map<const void *, DevBuf *> dcache;     // dense weights by host ptr
