@@ -123,6 +123,14 @@ class MtpDesc(C.Structure):
                 ("hc_head_scale", C.c_float)]
 
 
+class DsparkDesc(C.Structure):
+    """ApusCudaDsparkDesc: what the DSpark functions read of ApusDspark (c/dspark.h:88-107)."""
+    _fields_ = [("n_stages", C.c_int), ("block_size", C.c_int), ("noise_id", C.c_int), ("markov_rank", C.c_int),
+                ("n_targets", C.c_int), ("targets", C.c_int * 8), ("stages", C.POINTER(LayerDesc)), ("main_proj", QW),
+                ("main_norm_w", C.c_void_p), ("norm_w", C.c_void_p), ("hc_head_fn", C.c_void_p), ("hc_head_base", C.c_void_p),
+                ("hc_head_scale", C.c_float), ("markov_w1", C.c_void_p), ("markov_w2", C.c_void_p), ("conf_proj", C.c_void_p)]
+
+
 class Fp4GemmEnt(C.Structure):
     """ApusFp4GemmEnt (c/fp4.h:184-188)."""
     _fields_ = [("w", C.c_void_p), ("ws", C.c_void_p), ("out", C.c_void_p),
@@ -268,6 +276,12 @@ def load(path=LIB_PATH):
         "apus_cuda_mtp_reset": (ci, [vp]),
         "apus_cuda_mtp_forward": (ci, [vp, vp, vp, ci, C.c_int64, vp, vp, vp]),
         "apus_cuda_model_spec_generate_mtp": (ci, [vp, vp, vp, ci, ci, ci, vp, vp]),
+        "apus_cuda_dspark_create": (vp, [vp, vp]),
+        "apus_cuda_dspark_destroy": (None, [vp]),
+        "apus_cuda_dspark_reset": (ci, [vp]),
+        "apus_cuda_dspark_feed": (ci, [vp, vp, C.c_int64, ci]),
+        "apus_cuda_dspark_draft_round": (ci, [vp, C.c_int64, vp, C.c_int64, vp, vp, vp, vp]),
+        "apus_cuda_model_spec_generate_dspark": (ci, [vp, vp, vp, ci, ci, vp, vp]),
         "apus_cuda_model_generate": (ci, [vp, vp, ci, ci, vp, C.POINTER(cf), C.POINTER(cf)]),
         "apus_cuda_apply_rope": (ci, [vp, vp, vp, ci, ci, ci, ci]),
         "apus_cuda_hadamard": (ci, [vp, ci, ci]),

@@ -890,12 +890,12 @@ int apus_cuda_model_forward(ApusCudaModel *m, const int64_t *ids, int s, float *
 // [B][s][n_targets*dim].  The positions run as chunks; a row of a chunk equals the step's.
 static int forward_ex(ApusCudaModel *m, const int64_t *ids, int s, float *logits, int logits_all, int32_t *next,
                       float *h_out, float *mh_out, const int *targets, int n_targets, const char *what,
-                      bool keep_h_dev = false) {
+                      bool keep_h_dev = false, bool keep_mh_dev = false) {
     if (!m) { set_error("NULL model"); return 1; }
     if (s <= 0) return 0;
     APUS_REQUIRE(m->pos + s <= m->max_pos, "%s: position %lld + %d exceeds max_pos %d", what, m->pos, s, m->max_pos);
-    APUS_REQUIRE(!mh_out || (targets && n_targets >= 1), "%s: mh_out needs the target layers", what);
-    for (int i = 0; mh_out && i < n_targets; i++)
+    APUS_REQUIRE(!(mh_out || keep_mh_dev) || (targets && n_targets >= 1), "%s: mh_out needs the target layers", what);
+    for (int i = 0; (mh_out || keep_mh_dev) && i < n_targets; i++)
         APUS_REQUIRE(targets[i] >= 0 && targets[i] < m->n_layers, "%s: target layer %d of %d", what, targets[i], m->n_layers);
     if (ids_in_range(m, ids, (size_t)m->B * s, what)) return 1;
     cudaStream_t st = mstream(m);
@@ -912,15 +912,15 @@ static int forward_ex(ApusCudaModel *m, const int64_t *ids, int s, float *logits
     ApusCudaModel::Chunk &C = m->ck;
     const bool all = logits_all != 0;
     if (all && (C.logits.get((size_t)per * B * V * 4, nullptr) || C.tok.get((size_t)per * B * 4, nullptr))) return 1;
-    APUS_REQUIRE(!keep_h_dev || per >= s, "%s: %d positions do not fit one chunk", what, s);
+    APUS_REQUIRE(!(keep_h_dev || keep_mh_dev) || per >= s, "%s: %d positions do not fit one chunk", what, s);
     if ((h_out || keep_h_dev) && C.hx.get((size_t)per * B * hd * 4, nullptr)) return 1;
-    if (mh_out && C.mhx.get((size_t)per * B * md * 4, nullptr)) return 1;
+    if ((mh_out || keep_mh_dev) && C.mhx.get((size_t)per * B * md * 4, nullptr)) return 1;
     for (int t0 = 0; t0 < s; t0 += per) {
         const int n = s - t0 < per ? s - t0 : per;
         ChunkExtra ex;
         if (all) { ex.logits_all = C.logits.as<float>(); ex.tok_all = C.tok.as<int32_t>(); }
         if (h_out || keep_h_dev) ex.h_all = C.hx.as<float>();
-        if (mh_out) { ex.mh_all = C.mhx.as<float>(); ex.targets = targets; ex.n_targets = n_targets; }
+        if (mh_out || keep_mh_dev) { ex.mh_all = C.mhx.as<float>(); ex.targets = targets; ex.n_targets = n_targets; }
         if (model_chunk(m, (const int64_t *)dcols + (size_t)t0 * B, n, !all && t0 + n == s, st, &ex)) return 1;
         for (int t = 0; t < n; t++) {                      // row (t, b) of the chunk -> [b][t0 + t] of the caller
             if (all && logits)
@@ -1326,6 +1326,396 @@ int apus_cuda_mtp_forward(ApusCudaMtp *mt, const float *h_in, const int64_t *ids
     int stt = gemm_tc_status(1);
     APUS_REQUIRE(stt == 0, "mtp_forward: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
     return 0;
+}
+
+// ---- DSpark draft module (c/dspark.h) --------------------------------------------------------------
+// n_stages full sliding-window blocks whose rings hold, for every TRUE position, the KV row made from
+// main_x = main_norm(main_proj(main_hidden)) (one projection shared by the stages), plus a block of B
+// draft rows [anchor, noise x (B-1)] that attend over the ring and over each other (one shared,
+// non-causal index row), the last stage's own hc_head + norm, the parent's LM head, a bigram bias
+// w2 . w1[previous token] added row by row before each pick, and a confidence head (telemetry).
+struct ApusCudaDspark {
+    ApusCudaModel *m = nullptr;
+    int n_stages = 0, B = 0, noise_id = 0, rank = 0, n_targets = 0, targets[8] = {0};
+    std::vector<LayerDev> stages;
+    std::vector<StateDev> states;
+    DevQW *main_proj = nullptr;
+    const float *main_norm_w = nullptr, *norm_w = nullptr, *hc_head_fn = nullptr, *hc_head_base = nullptr,
+                *markov_w1 = nullptr, *markov_w2 = nullptr, *conf_proj = nullptr;
+    float hc_head_scale = 0.f;
+    WeightOwner own;
+    int rows_cap = 0;
+    DevBuf mh, mxa, mx, pq, ps, kva, kv, h0, h1, x, y, sub, post, comb, raw, sa, ids, idxs, yh, yn, logits, emb, tok, cur,
+        conf, drafts, ws[24];
+    StepBufs sb;
+    void release() {
+        DevBuf *b[] = {&mh, &mxa, &mx, &pq, &ps, &kva, &kv, &h0, &h1, &x, &y, &sub, &post, &comb, &raw, &sa, &ids, &idxs,
+                       &yh, &yn, &logits, &emb, &tok, &cur, &conf, &drafts};
+        for (DevBuf *p : b) p->release();
+        for (auto &w : ws) w.release();
+        for (auto &st : states) st.release();
+        for (auto &L : stages) if (L.moe) { apus_cuda_moe_destroy(L.moe); L.moe = nullptr; }
+        own.release();
+    }
+};
+
+// bias[v] = sum_r e[r] * w2[v][r] in index order (c/attn.h:460-465 apus_dot_f32_scalar: one accumulator,
+// product rounded before the add), e = w1[previous token]; row[v] += bias[v] (c/dspark.h:661-672)
+__global__ void markov_bias_kernel(const float *__restrict__ w1, const float *__restrict__ w2, const long long *__restrict__ cur,
+                                   int rank, int V, float *__restrict__ row, float *__restrict__ embed) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
+    const float *e = w1 + (size_t)(*cur) * rank;
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (blockIdx.x == 0 && embed)
+        for (int r = threadIdx.x; r < rank; r += blockDim.x) embed[r] = e[r];
+    if (v >= V) return;
+    float acc = 0.f;
+    for (int r = 0; r < rank; r++) acc = __fadd_rn(acc, __fmul_rn(e[r], w2[(size_t)v * rank + r]));
+    row[v] = __fadd_rn(row[v], acc);
+}
+__global__ void markov_take_kernel(const int32_t *__restrict__ tok, long long *__restrict__ cur, long long *__restrict__ drafts, int i) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
+    *cur = *tok;
+    drafts[i] = *tok;
+}
+// confidence[t] = sum over [collapsed row | bigram embedding] * proj, index order (c/dspark.h:679-694)
+__global__ void confidence_kernel(const float *__restrict__ xh, const float *__restrict__ emb, const float *__restrict__ proj,
+                                  int dim, int rank, float *__restrict__ out) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
+    const int t = blockIdx.x;
+    if (threadIdx.x) return;
+    float acc = 0.f;
+    for (int i = 0; i < dim; i++) acc = __fadd_rn(acc, __fmul_rn(xh[(size_t)t * dim + i], proj[i]));
+    for (int r = 0; r < rank; r++) acc = __fadd_rn(acc, __fmul_rn(emb[(size_t)t * rank + r], proj[dim + r]));
+    out[t] = acc;
+}
+
+static int ds_bufs(ApusCudaDspark *ds, int rows) {
+    ApusCudaModel *m = ds->m;
+    if (rows <= ds->rows_cap) return 0;
+    const size_t R = rows, dim = m->dim, hc = m->hc, mhd = (size_t)ds->n_targets * dim;
+    const ApusAttnCfg &c = ds->stages[0].attn.cfg;
+    if (ds->mh.get(R * mhd * 4, nullptr) || ds->mxa.get(R * dim * 4, nullptr) || ds->mx.get(R * dim * 4, nullptr) ||
+        ds->pq.get(R * mhd, nullptr) || ds->ps.get(R * (mhd / 128 + 1) * 4, nullptr) ||
+        ds->kva.get(R * c.head_dim * 4, nullptr) || ds->kv.get(R * c.head_dim * 4, nullptr))
+        return 1;
+    ds->rows_cap = rows;
+    return 0;
+}
+
+// main_x rows (c/dspark.h:365-376) from main-hidden rows on the device
+static int ds_project(ApusCudaDspark *ds, const float *mh, int rows, cudaStream_t st) {
+    ApusCudaModel *m = ds->m;
+    if (ds_bufs(ds, rows)) return 1;
+    if (qlinear_dev(ds->main_proj, mh, ds->mxa.as<float>(), rows, ds->pq.as<uint8_t>(), ds->ps.as<float>(), true, st)) return 1;
+    return rms_norm(ds->mxa.as<float>(), ds->main_norm_w, m->norm_eps, ds->mx.as<float>(), m->dim, rows, st);
+}
+// every stage's ring rows of positions pos0 .. pos0 + rows - 1 from ds->mx (c/dspark.h:378-455)
+static int ds_ring_rows(ApusCudaDspark *ds, int rows, long long pos0, cudaStream_t st) {
+    ApusCudaModel *m = ds->m;
+    if (act_quant(ds->mx.as<float>(), nullptr, rows, m->dim, ds->pq.as<uint8_t>(), ds->ps.as<float>(), nullptr, st)) return 1;
+    for (int k = 0; k < ds->n_stages; k++) {
+        const LayerDev &L = ds->stages[k];
+        const ApusAttnCfg &c = L.attn.cfg;
+        APUS_REQUIRE(pos0 + rows <= L.rope_rows, "dspark: position %lld is beyond the rope table", pos0 + rows - 1);
+        if (qgemm_dev(L.attn.wkv, nullptr, ds->pq.as<uint8_t>(), ds->ps.as<float>(), rows, ds->kva.as<float>(), true, 0.f, st)) return 1;
+        if (row_ops(ds->kva.as<float>(), c.head_dim, ds->kv.as<float>(), c.head_dim, rows, c.head_dim,
+                    ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, L.attn.kv_norm, c.eps, c.rope_dim,
+                    L.cs + (size_t)pos0 * c.rope_dim, 1, c.rope_dim, st))
+            return 1;
+        if (ring_update(ds->states[k].win.as<float>(), ds->kv.as<float>(), c.window, rows, c.head_dim, 1, pos0, st)) return 1;
+    }
+    return 0;
+}
+
+// c/dspark.h:459-575: the B draft rows through one stage's attention
+static int ds_attn(ApusCudaDspark *ds, int k, const float *x, long long start_pos, float *out, cudaStream_t st) {
+    const LayerDev &L = ds->stages[k];
+    const AttnDev &A = L.attn;
+    const ApusAttnCfg &c = A.cfg;
+    const StepBufs &b = ds->sb;
+    const int B = ds->B, h = c.n_heads, d = c.head_dim, rd = c.rope_dim, win = c.window, hd = h * d;
+    const float *cs1 = L.cs + (size_t)(start_pos + 1) * rd;            // draft row t rotates at start_pos + 1 + t
+    if (act_quant(x, nullptr, B, c.dim, b.xq, b.xs, nullptr, st)) return 1;
+    if (qgemm_dev(A.wq_a, nullptr, b.xq, b.xs, B, b.qa, true, 0.f, st)) return 1;
+    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st)) return 1;
+    if (act_quant(b.qr, nullptr, B, c.q_lora, b.xq2, b.xs2, nullptr, st)) return 1;
+    if (qgemm_dev(A.wq_b, nullptr, b.xq2, b.xs2, B, b.q, true, 0.f, st)) return 1;
+    if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs1, h, rd, st)) return 1;
+    // the draft rows' own KV: after the ring in the candidate list, never written into it
+    if (qgemm_dev(A.wkv, nullptr, b.xq, b.xs, B, b.kva, true, 0.f, st)) return 1;
+    if (row_ops(b.kva, d, b.kv, d, B, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd, cs1, 1, rd, st))
+        return 1;
+    const int nwin = (int)(start_pos + 1 < win ? start_pos + 1 : win), idxw = nwin + B;
+    const float scale = (float)pow((double)d, -0.5);
+    if (sparse_attn(b.q, A.sink, h, d, ds->idxs.as<int32_t>(), idxw, B, scale, ds->states[k].win.p, win, b.kv, B, 0, b.o, st, 0, 0,
+                    b.sa, b.sa_cap))
+        return 1;
+    if (row_ops(b.o, d, b.o, d, B * h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs1, h, rd, st)) return 1;
+    const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
+    if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, B, sub, ol,
+                           APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_WO_A), st))
+        return 1;
+    return qlinear_dev(A.wo_b, b.y, out, B, b.xq, b.xs, true, st);
+}
+
+// c/dspark.h:611-697 one draft round; mh_row (device) = main hidden of position start_pos.  Leaves the
+// B drafts in ds->drafts (device, int64) and copies them to `drafts` (host).
+static int ds_round(ApusCudaDspark *ds, long long anchor, const float *mh_row, long long start_pos, int64_t *drafts,
+                    float *confidence, float *logits_final, float *stage_h, cudaStream_t st) {
+    ApusCudaModel *m = ds->m;
+    const int B = ds->B, dim = m->dim, hc = m->hc, V = m->vocab;
+    APUS_REQUIRE(start_pos >= 0 && start_pos + 1 + B <= m->max_pos, "dspark: draft positions %lld + %d exceed max_pos %d",
+                 start_pos + 1, B, m->max_pos);
+    // ring slot of position start_pos in every stage (idempotent with the catch-up writes)
+    if (ds_project(ds, mh_row, 1, st) || ds_ring_rows(ds, 1, start_pos, st)) return 1;
+    const ApusAttnCfg &c0 = ds->stages[0].attn.cfg;
+    const int win = c0.window, nwin = (int)(start_pos + 1 < win ? start_pos + 1 : win), idxw = nwin + B;
+    std::vector<int64_t> ids((size_t)B, (int64_t)ds->noise_id);
+    ids[0] = anchor;
+    std::vector<int32_t> idx((size_t)B * idxw);
+    for (int t = 0; t < B; t++) {                        // one shared, non-causal row: ring slots in slot order, then the draft rows
+        for (int j = 0; j < nwin; j++) idx[(size_t)t * idxw + j] = j;
+        for (int j = 0; j < B; j++) idx[(size_t)t * idxw + nwin + j] = win + j;
+    }
+    if (ds->ids.get((size_t)B * 8, nullptr) || ds->idxs.get((size_t)B * (win + B) * 4, nullptr) || ds->cur.get(8, nullptr) ||
+        ds->drafts.get((size_t)B * 8, nullptr))
+        return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(ds->ids.p, ids.data(), (size_t)B * 8, cudaMemcpyHostToDevice, st));
+    APUS_CUDA_OK(cudaMemcpyAsync(ds->idxs.p, idx.data(), idx.size() * 4, cudaMemcpyHostToDevice, st));
+    APUS_CUDA_OK(cudaMemcpyAsync(ds->cur.p, &ids[0], 8, cudaMemcpyHostToDevice, st));
+    float *h = ds->h0.as<float>(), *hn = ds->h1.as<float>();
+    const BlockBufs bb = {ds->x.as<float>(), ds->y.as<float>(), ds->sub.as<float>(), ds->post.as<float>(), ds->comb.as<float>(),
+                          ds->raw.as<float>()};
+    if (embed_rows(m->embed, m->embed_bf16, ds->ids.as<int64_t>(), B, hc, dim, h, st)) return 1;
+    for (int k = 0; k < ds->n_stages; k++) {
+        const LayerDev &L = ds->stages[k];
+        if (mhc_pre(h, dim, hc, L.hc_attn_fn, L.hc_attn_scale, L.hc_attn_base, m->norm_eps, m->hc_eps, m->iters, L.attn_norm_w,
+                    m->norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st, bb.raw))
+            return 1;
+        if (ds_attn(ds, k, bb.x, start_pos, bb.sub, st)) return 1;
+        if (block_ffn_post(L, bb.sub, &h, &hn, B, hc, bb, st)) return 1;
+        if (block_ffn_pre(L, h, B, hc, m->iters, m->hc_eps, m->norm_eps, bb, st)) return 1;
+        if (apus_cuda_moe_forward_dev(L.moe, bb.x, ds->ids.as<int64_t>(), B, bb.sub, st)) return 1;
+        if (block_ffn_post(L, bb.sub, &h, &hn, B, hc, bb, st)) return 1;
+        if (stage_h)
+            APUS_CUDA_OK(cudaMemcpyAsync(stage_h + (size_t)k * B * hc * dim, h, (size_t)B * hc * dim * 4, cudaMemcpyDeviceToHost, st));
+    }
+    // head of the last stage, the parent's LM head, the bigram bias row by row
+    if (mhc_head(h, dim, hc, ds->hc_head_fn, ds->hc_head_scale, ds->hc_head_base, m->norm_eps, m->hc_eps, ds->yh.as<float>(), B, st,
+                 ds->raw.as<float>()))
+        return 1;
+    if (rms_norm(ds->yh.as<float>(), ds->norm_w, m->norm_eps, ds->yn.as<float>(), dim, B, st)) return 1;
+    if (f32_linear(m->head, ds->yn.as<float>(), ds->logits.as<float>(), B, dim, V,
+                   (m->head_bf16 ? APUS_CUDA_W_BF16 : 0) | APUS_LIN_CLASS(APUS_CUDA_TREE_HEAD), st))
+        return 1;
+    for (int i = 0; i < B; i++) {
+        float *row = ds->logits.as<float>() + (size_t)i * V;
+        launch_k(markov_bias_kernel, ceil_div(V, 256), 256, 0, st, ds->markov_w1, ds->markov_w2, ds->cur.as<long long>(), ds->rank, V,
+                 row, ds->emb.as<float>() + (size_t)i * ds->rank);
+        APUS_LAUNCHED();
+        if (argmax_rows(row, V, 1, ds->tok.as<int32_t>(), st)) return 1;
+        launch_k(markov_take_kernel, 1, 1, 0, st, ds->tok.as<int32_t>(), ds->cur.as<long long>(), ds->drafts.as<long long>(), i);
+        APUS_LAUNCHED();
+    }
+    if (confidence) {
+        launch_k(confidence_kernel, B, 32, 0, st, ds->yh.as<float>(), ds->emb.as<float>(), ds->conf_proj, dim, ds->rank,
+                 ds->conf.as<float>());
+        APUS_LAUNCHED();
+        APUS_CUDA_OK(cudaMemcpyAsync(confidence, ds->conf.p, (size_t)B * 4, cudaMemcpyDeviceToHost, st));
+    }
+    if (logits_final) APUS_CUDA_OK(cudaMemcpyAsync(logits_final, ds->logits.p, (size_t)B * V * 4, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaMemcpyAsync(drafts, ds->drafts.p, (size_t)B * 8, cudaMemcpyDeviceToHost, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    return 0;
+}
+
+void apus_cuda_dspark_destroy(ApusCudaDspark *ds) {
+    if (!ds) return;
+    cudaDeviceSynchronize();
+    ds->release();
+    delete ds;
+}
+
+// c/dspark.h:353-356: fresh (empty) stage rings
+int apus_cuda_dspark_reset(ApusCudaDspark *ds) {
+    if (!ds) { set_error("NULL dspark"); return 1; }
+    for (int k = 0; k < ds->n_stages; k++)
+        if (attn_state_init(ds->stages[k].attn.cfg, ds->states[k], 1, 0)) return 1;
+    APUS_CUDA_OK(cudaStreamSynchronize(ctx().stream));
+    return 0;
+}
+
+ApusCudaDspark *apus_cuda_dspark_create(ApusCudaModel *m, const ApusCudaDsparkDesc *d) {
+    if (!m || !d || !d->stages) { set_error("dspark_create: NULL argument"); return nullptr; }
+    const int dim = m->dim, hc = m->hc, V = m->vocab;
+    if (m->B != 1 || m->e_lo != 0 || m->e_hi != m->n_experts) { set_error("dspark_create: needs a one-sequence model that holds every expert"); return nullptr; }
+    if (d->n_stages < 1 || d->n_stages > 8 || d->block_size < 1 || d->block_size > 32 || d->n_targets < 1 || d->n_targets > 8 ||
+        d->noise_id < 0 || d->noise_id >= V || d->markov_rank < 1) {
+        set_error("dspark: bad config (stages %d, block %d, targets %d, noise %d, rank %d)", d->n_stages, d->block_size,
+                  d->n_targets, d->noise_id, d->markov_rank);
+        return nullptr;
+    }
+    for (int i = 0; i < d->n_targets; i++)
+        if (d->targets[i] < 0 || d->targets[i] >= m->n_layers) { set_error("dspark: target layer %d out of range", d->targets[i]); return nullptr; }
+    if (d->main_proj.O != dim || d->main_proj.K != (int64_t)d->n_targets * dim) { set_error("dspark: bad tensor main_proj"); return nullptr; }
+    ApusCudaDspark *ds = new ApusCudaDspark();
+    ds->m = m;
+    ds->n_stages = d->n_stages; ds->B = d->block_size; ds->noise_id = d->noise_id; ds->rank = d->markov_rank;
+    ds->n_targets = d->n_targets;
+    for (int i = 0; i < d->n_targets; i++) ds->targets[i] = d->targets[i];
+    ds->stages.resize(d->n_stages);
+    ds->states.resize(d->n_stages);
+    bool ok = true;
+    for (int k = 0; k < d->n_stages && ok; k++) {
+        const ApusCudaLayerDesc &ld = d->stages[k];
+        if (ld.acfg.ratio != 0 || ld.mw.hash || ld.acfg.dim != dim) { set_error("dspark: stage %d must be a sliding-window block with scored routing", k); ok = false; break; }
+        ok = layer_weights(ld, hc, V, &ds->stages[k], &ds->own, 0, -1) == 0;
+        if (!ok) break;
+        ds->stages[k].cs = rope_rows_dev(ld.cos, ld.sin, ld.rope_rows, ld.acfg.rope_dim / 2, m->rope);
+        ds->stages[k].rope_rows = ld.rope_rows;
+        if (!ds->stages[k].cs || ld.rope_rows < m->max_pos) { set_error("dspark: stage %d rope table has %d rows, %d needed", k, ld.rope_rows, m->max_pos); ok = false; }
+    }
+    if (ok) {
+        const size_t B = ds->B;
+        ds->main_proj = get_qw(&ds->own, 8, d->main_proj.codes, d->main_proj.scales, dim, d->n_targets * dim);
+        ds->main_norm_w = (const float *)get_dense(&ds->own, d->main_norm_w, (size_t)dim * 4);
+        ds->norm_w = (const float *)get_dense(&ds->own, d->norm_w, (size_t)dim * 4);
+        ds->hc_head_fn = (const float *)get_dense(&ds->own, d->hc_head_fn, (size_t)hc * hc * dim * 4);
+        ds->hc_head_base = (const float *)get_dense(&ds->own, d->hc_head_base, (size_t)hc * 4);
+        ds->hc_head_scale = d->hc_head_scale;
+        ds->markov_w1 = (const float *)get_dense(&ds->own, d->markov_w1, (size_t)V * d->markov_rank * 4);
+        ds->markov_w2 = (const float *)get_dense(&ds->own, d->markov_w2, (size_t)V * d->markov_rank * 4);
+        ds->conf_proj = (const float *)get_dense(&ds->own, d->conf_proj, (size_t)(dim + d->markov_rank) * 4);
+        ok = ds->main_proj && ds->main_norm_w && ds->norm_w && ds->hc_head_fn && ds->hc_head_base && ds->markov_w1 && ds->markov_w2 &&
+             ds->conf_proj;
+        const ApusAttnCfg &c = ds->stages[0].attn.cfg;
+        ApusAttnCfg sized = c;
+        sized.has_indexer = 0;
+        const long long wide = B + 8;
+        ok = ok && !(ds->h0.get(B * hc * dim * 4, nullptr) || ds->h1.get(B * hc * dim * 4, nullptr) || ds->x.get(B * dim * 4, nullptr) ||
+                     ds->y.get(B * dim * 4, nullptr) || ds->sub.get(B * dim * 4, nullptr) || ds->post.get(B * hc * 4, nullptr) ||
+                     ds->comb.get(B * hc * hc * 4, nullptr) || ds->raw.get(B * ((2 + hc) * hc + 1) * 4, nullptr) ||
+                     ds->yh.get(B * dim * 4, nullptr) || ds->yn.get(B * dim * 4, nullptr) || ds->logits.get(B * (size_t)V * 4, nullptr) ||
+                     ds->emb.get(B * d->markov_rank * 4, nullptr) || ds->tok.get(4, nullptr) || ds->conf.get(B * 4, nullptr) ||
+                     attn_step_bufs(sized, wide, (int)B, ds->ws, &ds->sb));
+        if (ok) {
+            ds->sb.sa_cap = sparse_attn_scratch(c.n_heads, (int)(c.window + wide + 8), (int)B);
+            ok = ds->sa.get(ds->sb.sa_cap, &ds->sb.sa) == 0;
+        }
+    }
+    if (ok) ok = apus_cuda_dspark_reset(ds) == 0;
+    if (!ok) { apus_cuda_dspark_destroy(ds); return nullptr; }
+    return ds;
+}
+
+// c/dspark.h:397-434 (rows = the whole prompt from position 0) and 436-455 (catch-up from pos0): the
+// stages' ring rows of n true positions from their main hiddens mh [n, n_targets * dim] (host).
+int apus_cuda_dspark_feed(ApusCudaDspark *ds, const float *mh, int64_t pos0, int n) {
+    if (!ds || !mh) { set_error("dspark_feed: NULL argument"); return 1; }
+    if (n <= 0) return 0;
+    ApusCudaModel *m = ds->m;
+    cudaStream_t st = mstream(m);
+    APUS_REQUIRE(pos0 >= 0 && pos0 + n <= m->max_pos, "dspark_feed: positions %lld + %d exceed max_pos %d", (long long)pos0, n, m->max_pos);
+    const size_t mhd = (size_t)ds->n_targets * m->dim;
+    if (ds_bufs(ds, n)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(ds->mh.p, mh, (size_t)n * mhd * 4, cudaMemcpyHostToDevice, st));
+    if (ds_project(ds, ds->mh.as<float>(), n, st) || ds_ring_rows(ds, n, pos0, st)) return 1;
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    return 0;
+}
+
+// c/dspark.h:611 apus_dspark_draft_round, greedy drafts: mh_row [n_targets * dim] (host) = main hidden of position
+// start_pos; drafts [block_size]; confidence [block_size], logits_final [block_size, vocab], stage_h
+// [n_stages, block_size, hc * dim] nullable.
+int apus_cuda_dspark_draft_round(ApusCudaDspark *ds, int64_t anchor, const float *mh_row, int64_t start_pos, int64_t *drafts,
+                                 float *confidence, float *logits_final, float *stage_h) {
+    if (!ds || !mh_row || !drafts) { set_error("dspark_draft_round: NULL argument"); return 1; }
+    ApusCudaModel *m = ds->m;
+    cudaStream_t st = mstream(m);
+    APUS_REQUIRE(anchor >= 0 && anchor < m->vocab, "dspark_draft_round: anchor %lld is outside [0, %d)", (long long)anchor, m->vocab);
+    if (ds_bufs(ds, 1)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(ds->mh.p, mh_row, (size_t)ds->n_targets * m->dim * 4, cudaMemcpyHostToDevice, st));
+    if (ds_round(ds, anchor, ds->mh.as<float>(), start_pos, drafts, confidence, logits_final, stage_h, st)) return 1;
+    int stt = gemm_tc_status(1);
+    APUS_REQUIRE(stt == 0, "dspark_draft_round: a bounded wait expired inside a tcgen05 kernel (code %d)", stt);
+    return 0;
+}
+
+// c/dspark.h:747-862 apus_dspec_prefill + apus_dspec_step until n_gen tokens are out (greedy or sampled main
+// stream; the drafts are greedy).  stats [7]: emitted, batches, batch_tokens, refeed_tokens, offered,
+// accepted, bonus_rounds.
+int apus_cuda_model_spec_generate_dspark(ApusCudaModel *m, ApusCudaDspark *ds, const int64_t *prompt, int n_prompt, int n_gen,
+                                         int32_t *out_tokens, uint64_t *stats) {
+    if (!m || !ds || ds->m != m) { set_error("model_spec_generate_dspark: the draft module belongs to another model"); return 1; }
+    APUS_REQUIRE(n_prompt >= 1 && n_gen >= 1, "model_spec_generate_dspark: bad sizes");
+    APUS_REQUIRE(chunks_enabled() && n_prompt <= chunk_rows(), "model_spec_generate_dspark: a prompt of %d tokens does not fit one chunk",
+                 n_prompt);
+    enum { EMITTED, BATCHES, BATCH_TOKENS, REFEED_TOKENS, OFFERED, ACCEPTED, BONUS };
+    uint64_t s7[7] = {0, 0, 0, 0, 0, 0, 0};
+    cudaStream_t st = mstream(m);
+    const int B = ds->B;
+    const size_t mhd = (size_t)ds->n_targets * m->dim;
+    if (apus_cuda_dspark_reset(ds)) return 1;
+    int32_t pick = 0;
+    // main prefill collecting the mean hiddens, the stage rings from them
+    if (forward_ex(m, prompt, n_prompt, nullptr, 0, &pick, nullptr, nullptr, ds->targets, ds->n_targets, "model_spec_generate_dspark",
+                   false, true))
+        return 1;
+    DevBuf mh_last;
+    if (mh_last.get(mhd * 4, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(mh_last.p, m->ck.mhx.as<float>() + (size_t)(n_prompt - 1) * mhd, mhd * 4, cudaMemcpyDeviceToDevice, st));
+    if (ds_project(ds, m->ck.mhx.as<float>(), n_prompt, st) || ds_ring_rows(ds, n_prompt, 0, st)) { mh_last.release(); return 1; }
+    long long f = n_prompt - 1;
+    int64_t held = pick;
+    std::vector<int64_t> drafts((size_t)B), batch((size_t)B + 1);
+    std::vector<int32_t> picks((size_t)B + 1);
+    ApusCudaSnap *snap = nullptr;
+    int emitted = 0, rc = 0;
+    while (emitted < n_gen && !rc) {
+        int Be = B;
+        if (f + 2 + Be > m->max_pos) Be = (int)(m->max_pos - f - 2);
+        if (Be <= 0) { set_error("model_spec_generate_dspark: position %lld reaches max_pos %d", f, m->max_pos); rc = 1; break; }
+        if (ds_round(ds, held, mh_last.as<float>(), f, drafts.data(), nullptr, nullptr, nullptr, st)) { rc = 1; break; }
+        ApusCudaSnap *s2 = apus_cuda_model_snapshot(m, snap);
+        if (!s2) { rc = 1; break; }
+        snap = s2;
+        batch[0] = held;
+        for (int j = 1; j <= Be; j++) batch[j] = drafts[j - 1];
+        if (forward_ex(m, batch.data(), Be + 1, nullptr, 1, picks.data(), nullptr, nullptr, ds->targets, ds->n_targets,
+                       "model_spec_generate_dspark", false, true)) { rc = 1; break; }
+        s7[BATCHES]++; s7[BATCH_TOKENS] += (uint64_t)(Be + 1);
+        int a = 0;
+        int64_t newheld = -1;
+        if (emitted < n_gen) out_tokens[emitted++] = (int32_t)held;
+        for (int j = 1; j <= Be; j++) {
+            const int32_t mj = picks[j - 1];
+            s7[OFFERED]++;
+            if (drafts[j - 1] == mj) {
+                a = j; s7[ACCEPTED]++;
+                if (emitted < n_gen) out_tokens[emitted++] = mj;
+            } else { newheld = mj; break; }
+        }
+        if (newheld < 0) { newheld = picks[Be]; s7[BONUS]++; }
+        // the verify batch's mean hiddens outlive the re-feed: the next round's main hidden, the rings' new rows
+        if (cudaMemcpyAsync(mh_last.p, m->ck.mhx.as<float>() + (size_t)a * mhd, mhd * 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess ||
+            ds_project(ds, m->ck.mhx.as<float>(), a + 1, st) || ds_ring_rows(ds, a + 1, f + 1, st)) { rc = 1; break; }
+        if (a < Be) {
+            if (apus_cuda_model_restore(m, snap) || apus_cuda_model_forward_all(m, batch.data(), a + 1, nullptr, picks.data())) { rc = 1; break; }
+            s7[REFEED_TOKENS] += (uint64_t)(a + 1);
+        }
+        held = newheld;
+        f += 1 + a;
+    }
+    s7[EMITTED] = (uint64_t)emitted;
+    if (snap) apus_cuda_snap_free(snap);
+    cudaStreamSynchronize(st);
+    mh_last.release();
+    if (stats) memcpy(stats, s7, sizeof s7);
+    return rc;
 }
 
 // The proposer of the draft/verify loop below when it is the MTP head (c/mtp.h:441-470, 500-528, 600-612).

@@ -664,6 +664,49 @@ int apus_cuda_mtp_reset(ApusCudaMtp *mt);
 int apus_cuda_mtp_forward(ApusCudaMtp *mt, const float *h_in, const int64_t *ids, int s,
                           int64_t start_pos, float *logits, int32_t *next, float *h_last);
 
+/* c/dspark.h:88-118 ApusDspark: the DSpark draft module -- n_stages full sliding-window blocks (scored
+ * routing) whose rings hold, for every true position, the KV row made from
+ * main_x = main_norm(main_proj(main_hidden)) (apus_cuda_model_forward_mh rows), the last stage's own
+ * hc_head and norm, the parent's LM head, the bigram ("markov") bias and the confidence head.  One
+ * sequence per model.  Weights are copied to HBM at creation. */
+typedef struct {
+    int n_stages, block_size, noise_id, markov_rank, n_targets;   /* ApusDsparkCfg (c/model.h:48-56) */
+    int targets[8];                         /* layers whose mean hidden feeds main_proj */
+    const ApusCudaLayerDesc *stages;        /* [n_stages] "mtp.<k>.*" blocks, ratio 0 */
+    ApusFp8W main_proj;                     /* FP8 [dim, n_targets * dim] */
+    const float *main_norm_w, *norm_w;      /* [dim] */
+    const float *hc_head_fn, *hc_head_base; /* [hc, hc*dim], [hc] */
+    float hc_head_scale;
+    const float *markov_w1, *markov_w2;     /* [vocab, markov_rank] f32 */
+    const float *conf_proj;                 /* [dim + markov_rank] */
+} ApusCudaDsparkDesc;
+typedef struct ApusCudaDspark ApusCudaDspark;
+ApusCudaDspark *apus_cuda_dspark_create(ApusCudaModel *parent, const ApusCudaDsparkDesc *d);
+void apus_cuda_dspark_destroy(ApusCudaDspark *ds);
+/* c/dspark.h:353-356: empty stage rings. */
+int apus_cuda_dspark_reset(ApusCudaDspark *ds);
+/* c/dspark.h:365-376 + 397-455 apus_dspark_stage0_project followed by apus_dspark_prefill (pos0 = 0,
+ * the whole prompt) or apus_dspark_catchup: the stage rings' rows of the n true positions
+ * pos0 .. pos0 + n - 1 from their main hiddens mh [n, n_targets * dim]. */
+int apus_cuda_dspark_feed(ApusCudaDspark *ds, const float *mh, int64_t pos0, int n);
+/* c/dspark.h:611-697 apus_dspark_draft_round with greedy drafts: anchor = the held token, mh_row
+ * [n_targets * dim] = main hidden of position start_pos (its ring slot is rewritten, idempotent
+ * with apus_cuda_dspark_feed); drafts [block_size] = candidates for start_pos + 2 ..; nullable
+ * outputs as in ApusDsparkDbg: confidence [block_size], logits_final [block_size, vocab], stage_h
+ * [n_stages, block_size, hc_mult * dim]. */
+int apus_cuda_dspark_draft_round(ApusCudaDspark *ds, int64_t anchor, const float *mh_row,
+                                 int64_t start_pos, int64_t *drafts, float *confidence,
+                                 float *logits_final, float *stage_h);
+/* c/dspark.h:747-862 apus_dspec_prefill + apus_dspec_step until n_gen tokens are out: draft a block,
+ * verify [held, d1 .. dB] in one pass, accept while the drafts equal the model's own picks, roll back
+ * and re-feed the true prefix otherwise; the stage rings are caught up from the verify pass's
+ * hiddens.  The emitted stream is the plain stream of apus_cuda_model_generate, bit for bit.
+ * stats (nullable) [7]: emitted, batches, batch_tokens, refeed_tokens, offered, accepted,
+ * bonus_rounds (ApusDspec). */
+int apus_cuda_model_spec_generate_dspark(ApusCudaModel *m, ApusCudaDspark *ds, const int64_t *prompt,
+                                         int n_prompt, int n_gen, int32_t *out_tokens,
+                                         uint64_t *stats);
+
 /* c/mtp.h:113-138, 398-439 apus_snap_take / apus_snap_restore on the device (the
  * rollback of speculative decoding: draft and verify a few positions, keep the
  * accepted prefix).  A snapshot holds, per layer, the sliding-window ring, the

@@ -27,6 +27,7 @@
 #define APUS_MODEL_IMPLEMENTATION
 #define APUS_SAMPLE_IMPLEMENTATION
 #define APUS_MTP_IMPLEMENTATION
+#define APUS_DSPARK_IMPLEMENTATION
 
 #include <math.h>
 #include <stdio.h>
@@ -38,6 +39,7 @@
 #include "model.h"
 #include "sample.h"
 #include "mtp.h"
+#include "dspark.h"
 /* after the reference headers: their include guards make this header skip its
  * layout-identical copies of the reference types and only add the plain
  * descriptors ApusCudaLayerDesc / ApusCudaModelDesc used below */
@@ -263,6 +265,91 @@ int ref_spec_generate_mtp(const ApusCudaModelDesc *d, const ApusCudaMtpDesc *md,
     memcpy(stats, st8, sizeof st8);
     apus_spec_free(&sp);
     *mtp_state = mst.block.attn;
+    shim_model_close(&S, states, &pos);
+    return n;
+}
+
+/* An ApusDspark assembled from descriptors (c/dspark.h:88-107); tabs [n_stages]. */
+static void shim_fill_dspark(ApusDspark *ds, ApusRopeTab *tabs, ApusModel *m, const ApusCudaDsparkDesc *dd,
+                             const ApusCudaModelDesc *d) {
+    memset(ds, 0, sizeof *ds);
+    m->dspark = 1;
+    m->dsc.block_size = dd->block_size; m->dsc.noise_id = dd->noise_id; m->dsc.markov_rank = dd->markov_rank;
+    m->dsc.n_stages = dd->n_stages; m->dsc.n_targets = dd->n_targets;
+    for (int i = 0; i < dd->n_targets; i++) m->dsc.targets[i] = dd->targets[i];
+    ds->m = m;
+    ds->cfg = m->dsc;
+    ds->n_stages = dd->n_stages;
+    for (int k = 0; k < dd->n_stages; k++) {
+        shim_fill_layer(&ds->stages[k], &tabs[k], &dd->stages[k], d->hc_mult, d->hc_sinkhorn_iters, d->hc_eps, d->norm_eps);
+        ds->stages[k].cfg.vocab_size = d->vocab;
+    }
+    ds->main_proj = dd->main_proj;
+    ds->main_norm_w = (float *)dd->main_norm_w; ds->norm_w = (float *)dd->norm_w;
+    ds->hc_head_fn = (float *)dd->hc_head_fn; ds->hc_head_base = (float *)dd->hc_head_base;
+    ds->hc_head_scale = dd->hc_head_scale;
+    ds->markov_w1 = (float *)dd->markov_w1; ds->markov_w2 = (float *)dd->markov_w2; ds->conf_proj = (float *)dd->conf_proj;
+}
+
+/* c/dspark.h:365-455, 611: stage-0 projection + ring prefill over the n main-hidden rows mh_all, then one
+ * draft round at start_pos = n - 1 from the last row (greedy); stage_states [n_stages] in/out. */
+void ref_dspark_prefill_round(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *stage_states,
+                              const float *mh_all, int n, int64_t anchor, int64_t *drafts, float *confidence,
+                              float *logits_final, float *stage_h) {
+    ShimModel S;
+    ApusAttnS none[64];
+    memset(none, 0, sizeof none);
+    int64_t pos = 0;
+    shim_model_open(&S, d, none, 0);
+    ApusDspark ds;
+    ApusRopeTab tabs[APUS_DSPARK_MAX_STAGES];
+    ApusDsparkState dst;
+    shim_fill_dspark(&ds, tabs, &S.m, dd, d);
+    for (int k = 0; k < ds.n_stages; k++) dst.stages[k].attn = stage_states[k];
+    int dim = d->dim, hcd = d->hc_mult * d->dim, B = dd->block_size;
+    float *mx = malloc((size_t)n * dim * sizeof(float));
+    apus_dspark_stage0_project(&ds, mh_all, n, mx);
+    apus_dspark_prefill(&ds, &dst, mx, n);
+    ApusDsparkDbg dbg;
+    memset(&dbg, 0, sizeof dbg);
+    dbg.confidence = confidence; dbg.logits_final = logits_final;
+    for (int k = 0; k < ds.n_stages && stage_h; k++) dbg.stage_h[k] = stage_h + (size_t)k * B * hcd;
+    ApusRng drng;
+    apus_rng_seed(&drng, 1);
+    apus_dspark_draft_round(&ds, &dst, anchor, mx + (size_t)(n - 1) * dim, n - 1, 0.0f, &drng, NULL, drafts, &dbg);
+    free(mx);
+    for (int k = 0; k < ds.n_stages; k++) stage_states[k] = dst.stages[k].attn;
+    shim_model_close(&S, none, &pos);
+}
+
+/* c/dspark.h:747-862 apus_dspec_prefill + apus_dspec_step until n_gen tokens are out (greedy).  stats [7] =
+ * emitted, batches, batch_tokens, refeed_tokens, offered, accepted, bonus_rounds. */
+int ref_spec_generate_dspark(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *states,
+                             ApusAttnS *stage_states, const int64_t *prompt, int n_prompt, int n_gen,
+                             int32_t *out_tokens, uint64_t *stats) {
+    ShimModel S;
+    int64_t pos = 0;
+    shim_model_open(&S, d, states, 0);
+    ApusDspark ds;
+    ApusRopeTab tabs[APUS_DSPARK_MAX_STAGES];
+    ApusDsparkState dst;
+    shim_fill_dspark(&ds, tabs, &S.m, dd, d);
+    for (int k = 0; k < ds.n_stages; k++) dst.stages[k].attn = stage_states[k];
+    ApusDspec sp;
+    ApusRng rng;
+    apus_rng_seed(&rng, 0);
+    apus_dspec_init(&sp, &S.m, &S.st, &ds, &dst, 0.0f, 1.0f, &rng, 7, NULL);
+    apus_dspec_prefill(&sp, prompt, n_prompt);
+    int n = 0, buf[80];
+    while (n < n_gen) {
+        int ne = apus_dspec_step(&sp, buf, 80);
+        if (ne <= 0) break;
+        for (int i = 0; i < ne && n < n_gen; i++) out_tokens[n++] = buf[i];
+    }
+    uint64_t s7[7] = {sp.emitted, sp.batches, sp.batch_tokens, sp.refeed_tokens, sp.offered, sp.accepted, sp.bonus_rounds};
+    memcpy(stats, s7, sizeof s7);
+    apus_dspec_free(&sp);
+    for (int k = 0; k < ds.n_stages; k++) stage_states[k] = dst.stages[k].attn;
     shim_model_close(&S, states, &pos);
     return n;
 }

@@ -314,6 +314,47 @@ class TinyMtp:
         return S, S.st
 
 
+class TinyDspark:
+    """The DSpark draft module of a TinyModel (reference c/dspark.h:88-107): `n_stages` sliding-window blocks
+    with scored routing, the FP8 [dim, n_targets * dim] main projection and its norm, the last stage's norm
+    and mHC head, the two [vocab, rank] bigram matrices and the confidence projection."""
+
+    def __init__(self, seed, rope, targets, n_stages=2, block_size=3, noise_id=5, rank=16):
+        import ctypes as C
+        from apus_b200 import capi
+        M = dict(MODEL_DIMS)
+        dim, hc, V = ATTN_DIMS["dim"], M["hc"], M["vocab"]
+        cos, sin = rope["plain"]
+        self.stages = [BlockLayer(seed + 10 * k, "swa", cos, sin) for k in range(n_stages)]
+        rng = np.random.default_rng(seed + 57)
+        nt = len(targets)
+        self.main_proj = synth.fp8_weight(rng, dim, nt * dim, std=0.05)
+        nrm = lambda n: (1 + 0.05 * rng.standard_normal(n)).astype(np.float32)
+        self.main_norm_w, self.norm_w = nrm(dim), nrm(dim)
+        self.hc_head_fn = (rng.standard_normal((hc, hc * dim)) * 0.05).astype(np.float32)
+        self.hc_head_base = (rng.standard_normal(hc) * 0.5).astype(np.float32)
+        bf = lambda *sh, std: synth.bf16_round((rng.standard_normal(sh) * std).astype(np.float32))
+        self.markov_w1, self.markov_w2 = bf(V, rank, std=0.5), bf(V, rank, std=0.5)
+        self.conf_proj = bf(dim + rank, std=0.05)
+        self._descs = (capi.LayerDesc * n_stages)(*[L.desc for L in self.stages])
+        d = capi.DsparkDesc()
+        d.n_stages, d.block_size, d.noise_id, d.markov_rank, d.n_targets = n_stages, block_size, noise_id, rank, nt
+        for i, t in enumerate(targets):
+            d.targets[i] = t
+        d.stages = C.cast(self._descs, C.POINTER(capi.LayerDesc))
+        d.main_proj = capi.qw(*self.main_proj, dim, nt * dim)
+        d.main_norm_w, d.norm_w = capi.ptr(self.main_norm_w), capi.ptr(self.norm_w)
+        d.hc_head_fn, d.hc_head_base, d.hc_head_scale = capi.ptr(self.hc_head_fn), capi.ptr(self.hc_head_base), 0.85
+        d.markov_w1, d.markov_w2, d.conf_proj = capi.ptr(self.markov_w1), capi.ptr(self.markov_w2), capi.ptr(self.conf_proj)
+        self.desc, self.block_size = d, block_size
+
+    def states(self):
+        from apus_b200 import capi
+        S = [AttnState(L.attn) for L in self.stages]
+        arr = (capi.AttnS * len(S))(*[s.st for s in S])
+        return S, arr
+
+
 def block_inputs(seed, n_tokens, hc, dim):
     rng = np.random.default_rng(seed)
     return synth.activations(rng, n_tokens, hc * dim, std=1.2).reshape(n_tokens, hc, dim)

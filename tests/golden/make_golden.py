@@ -309,6 +309,53 @@ def ref_mtp(L, seed, n_layers, n_prompt, n_gen, depth, targets):
     return out
 
 
+def ref_dspark(L, seed, n_layers, n_prompt, n_gen, targets, n_stages, block_size, noise_id, rank):
+    """The reference's DSpark module on the small model (c/dspark.h): the stage rings built from the prompt's
+    main hiddens and one draft round after them (drafts, final logits, confidence, every stage's block
+    output), and its speculative loop (greedy), which must emit the plain greedy stream."""
+    Mdl = cases.TinyModel(seed, rope_pair(L), n_layers)
+    Ds = cases.TinyDspark(seed + 4, rope_pair(L), targets, n_stages, block_size, noise_id, rank)
+    V, hd, dim = Mdl.M["vocab"], Mdl.M["hc"] * cases.ATTN_DIMS["dim"], cases.ATTN_DIMS["dim"]
+    prompt = np.ascontiguousarray(cases.prompt_ids(seed + 5, 1, n_prompt, V)[0])
+    vp = C.c_void_p
+    L.ref_model_forward_hm.restype = None
+    L.ref_model_forward_hm.argtypes = [vp, vp, vp, vp, C.c_int, vp, C.c_int, vp, vp, C.c_int, vp]
+    L.ref_dspark_prefill_round.restype = None
+    L.ref_dspark_prefill_round.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int64, vp, vp, vp, vp]
+    L.ref_spec_generate_dspark.restype = C.c_int
+    L.ref_spec_generate_dspark.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.c_int, vp, vp]
+    out = {}
+    keep, st = Mdl.states()
+    pos = C.c_int64(0)
+    tg = np.array(targets, np.int32)
+    mh, lg = np.empty((n_prompt, len(targets) * dim), np.float32), np.empty(V, np.float32)
+    L.ref_model_forward_hm(C.byref(Mdl.desc), st, C.byref(pos), P(prompt), n_prompt, P(lg), 0, None, P(tg), len(targets), P(mh))
+    anchor = int(np.argmax(lg))
+    keeps, sst = Ds.states()
+    drafts, conf = np.zeros(block_size, np.int64), np.zeros(block_size, np.float32)
+    lf, sh = np.zeros((block_size, V), np.float32), np.zeros((n_stages, block_size, hd), np.float32)
+    L.ref_dspark_prefill_round(C.byref(Mdl.desc), C.byref(Ds.desc), sst, P(mh), n_prompt, anchor, P(drafts), P(conf), P(lf), P(sh))
+    out.update(mh_all=mh, anchor=np.array([anchor]), drafts=drafts, confidence=conf, logits_final=lf, stage_h=sh,
+               rings=np.stack([k.win.copy() for k in keeps]))
+    keep3, st3 = Mdl.states()
+    keeps2, sst2 = Ds.states()
+    toks, stats = np.zeros(n_gen, np.int32), np.zeros(7, np.uint64)
+    n = L.ref_spec_generate_dspark(C.byref(Mdl.desc), C.byref(Ds.desc), st3, sst2, P(prompt), n_prompt, n_gen, P(toks), P(stats))
+    assert n == n_gen
+    plain = ref_generate(L, seed, n_layers, 1, n_prompt, n_gen)["tokens"][0]
+    assert np.array_equal(plain, toks), (plain, toks)
+    out.update(spec_tokens=toks, spec_stats=stats)
+    return out
+
+
+def main_dspark():
+    L = ref()
+    assert L is not None, "reference build not available"
+    G = ref_dspark(L, **DSPARK_CASE)
+    np.savez_compressed(HERE / "dspark_case.npz", **G)
+    print("wrote dspark_case.npz:", {k: v.shape for k, v in G.items()}, "stats", G["spec_stats"].tolist(), "drafts", G["drafts"].tolist())
+
+
 def main_mtp():
     L = ref()
     assert L is not None, "reference build not available"
@@ -489,6 +536,8 @@ SAMPLE_CASES = {
 MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
 # the MTP draft head on the small model (c/mtp.h): targets = the layers whose mean hidden forward_mh collects
 MTP_CASE = dict(seed=91, n_layers=3, n_prompt=9, n_gen=24, depth=3, targets=[0, 2])
+# the DSpark draft module on the small model (c/dspark.h); the prompt is longer than the window of 8
+DSPARK_CASE = dict(seed=91, n_layers=3, n_prompt=11, n_gen=24, targets=[0, 2], n_stages=2, block_size=3, noise_id=5, rank=16)
 
 if __name__ == "__main__":
     import sys
@@ -496,10 +545,13 @@ if __name__ == "__main__":
         main_ckpt()
     elif sys.argv[1:] == ["mtp"]:     # only the MTP draft-head case (its own file)
         main_mtp()
+    elif sys.argv[1:] == ["dspark"]:  # only the DSpark case (its own file)
+        main_dspark()
     elif sys.argv[1:] == ["flash"]:   # only the real-dimension model case (its own file; ~23 GB of host memory)
         main_flash()
     else:
         main()
         main_ckpt()
         main_mtp()
+        main_dspark()
         main_flash()
