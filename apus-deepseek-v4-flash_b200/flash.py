@@ -93,7 +93,8 @@ TENSOR_IDS = {n: i for i, n in enumerate((
     "w1", "w1.s", "w3", "w3.s", "w2", "w2.s", "sw1", "sw1.s", "sw3", "sw3.s", "sw2", "sw2.s",
     "attn_norm", "ffn_norm", "hc_attn_fn", "hc_attn_base", "hc_ffn_fn", "hc_ffn_base",
     "embed", "head", "norm", "hc_head_fn", "hc_head_base", "prompt",
-    "e_proj", "e_proj.s", "h_proj", "h_proj.s", "enorm", "hnorm"))}
+    "e_proj", "e_proj.s", "h_proj", "h_proj.s", "enorm", "hnorm",
+    "main_proj", "main_proj.s", "main_norm", "markov_w1", "markov_w2", "conf_proj"))}
 # the MTP draft head's block is generated as layer MTP_LAYER + idx (c/mtp.h:223-226: "mtp.<idx>.*")
 MTP_LAYER = 2000
 # apus_synth.h kinds
@@ -248,6 +249,49 @@ class RandomFlashModel:
             self.torch.cuda.synchronize(self.device)
         self.keep.append(d)
         return d
+
+    def dspark_desc(self, n_stages=3, block_size=5, targets=(13, 27, 41), noise_id=0, rank=64):
+        """ApusCudaDsparkDesc of a random-init DSpark draft module (reference c/dspark.h:88-107): `n_stages`
+        sliding-window blocks generated as layers MTP_LAYER + k (stage 0 is the block the MTP head uses),
+        the FP8 main projection over the mean hiddens of the `targets` layers, norms, the last stage's
+        mHC head, the two bigram matrices and the confidence projection.  The checkpoint's own values of
+        block size, targets and rank are not known here; these are stand-ins of the same shape."""
+        cfg = self.cfg
+        dim, hc, V = cfg.dim, cfg.hc_mult, cfg.vocab
+        targets = [t for t in targets if t < cfg.n_layers] or [cfg.n_layers - 1]
+        L = MTP_LAYER + n_stages - 1
+        stages = [self._layer(MTP_LAYER + k, 0) for k in range(n_stages)]
+        arr = (capi.LayerDesc * n_stages)(*stages)
+        d = capi.DsparkDesc()
+        d.n_stages, d.block_size, d.noise_id, d.markov_rank, d.n_targets = n_stages, block_size, noise_id, rank, len(targets)
+        for i, t in enumerate(targets):
+            d.targets[i] = t
+        d.stages = C.cast(arr, C.POINTER(capi.LayerDesc))
+        d.main_proj = self._fp8(MTP_LAYER, "main_proj", dim, len(targets) * dim)
+        d.main_norm_w = self._fill(MTP_LAYER, "main_norm", K_F32, (dim,), 1.0, 0.05)
+        d.norm_w = self._fill(L, "norm", K_F32, (dim,), 1.0, 0.05)
+        d.hc_head_fn = self._fill(L, "hc_head_fn", K_F32, (hc, hc * dim), 0.0, 0.01)
+        d.hc_head_base = self._fill(L, "hc_head_base", K_F32, (hc,), 0.0, 0.5)
+        d.hc_head_scale = 0.8
+        d.markov_w1 = self._fill(L, "markov_w1", K_F32_BF16, (V, rank), 0.0, 0.1)
+        d.markov_w2 = self._fill(L, "markov_w2", K_F32_BF16, (V, rank), 0.0, 0.1)
+        d.conf_proj = self._fill(L, "conf_proj", K_F32_BF16, (dim + rank,), 0.0, 0.02)
+        if not self.host:
+            self.torch.cuda.synchronize(self.device)
+        self.keep += [arr, d]
+        return d
+
+    def mark(self):
+        """A point to which drop() frees what was generated since (draft modules of a bench arm)."""
+        return len(self.keep), self.bytes
+
+    def drop(self, mark):
+        del self.keep[mark[0]:]
+        self.bytes = mark[1]
+        for k in [k for k in self.named if k[0] >= MTP_LAYER]:
+            del self.named[k]
+        if not self.host:
+            self.torch.cuda.empty_cache()
 
     # ---- one layer ----------------------------------------------------------------------------
     def _layer(self, i, ratio):

@@ -262,6 +262,44 @@ def mtp_arm(L, W, h, a, cfg):
             "timing": "host clock around the loop (it synchronises every step to read the draft ids)"}
 
 
+def dspark_arm(L, W, h, a, cfg):
+    """Batch 1 with the DSpark draft module (reference c/dspark.h:747-862): per round a block of 5 drafts from
+    three random-init stages, verified in one pass of 6 positions.  As with the MTP head a random module
+    predicts nothing; the line shows the cost of a round and that the stream is the plain greedy stream."""
+    import apus_b200
+    from apus_b200 import capi
+    from apus_b200.flash import prompt_ids
+    n_gen = min(a.steps, 64)
+    d = W.dspark_desc()
+    ds = L.apus_cuda_dspark_create(h, C.byref(d))
+    if not ds:
+        apus_b200.check(1, "apus_cuda_dspark_create")
+    prompt = np.ascontiguousarray(prompt_ids(a.seed, 0, 1, a.prompt, cfg.vocab))
+    try:
+        plain = np.zeros((1, n_gen), np.int32)
+        apus_b200.check(L.apus_cuda_model_reset(h), "model_reset")
+        apus_b200.check(L.apus_cuda_model_generate(h, capi.ptr(prompt), a.prompt, n_gen, capi.ptr(plain), None, None), "generate")
+        toks, stats = np.zeros(n_gen, np.int32), np.zeros(7, np.uint64)
+        times = []
+        for n in (4, n_gen):
+            apus_b200.check(L.apus_cuda_model_reset(h), "model_reset")
+            t0 = time.perf_counter()
+            apus_b200.check(L.apus_cuda_model_spec_generate_dspark(h, ds, capi.ptr(prompt), a.prompt, n, capi.ptr(toks),
+                                                                    capi.ptr(stats)), "spec_generate_dspark")
+            times.append(time.perf_counter() - t0)
+        dt, emitted = times[1] - times[0], n_gen - 4
+    finally:
+        L.apus_cuda_dspark_destroy(ds)
+    return {"value": emitted / dt if dt > 0 else None, "unit": "tok/s", "batch": 1, "block_size": int(d.block_size),
+            "stages": int(d.n_stages), "tokens": n_gen, "ms_per_token": dt / max(emitted, 1) * 1e3,
+            "tokens_equal_plain_greedy": bool(np.array_equal(toks, plain[0])), "verify_batches": int(stats[1]),
+            "batch_tokens": int(stats[2]), "refeed_tokens": int(stats[3]), "drafts_offered": int(stats[4]),
+            "drafts_accepted": int(stats[5]), "bonus_rounds": int(stats[6]),
+            "module": "random-init DSpark stages + main projection + bigram / confidence heads, generated on the device "
+                      "(block size, target layers and bigram rank are stand-ins)",
+            "timing": "host clock around the loop"}
+
+
 def cpu_model_baseline(cfg, seed, budget_s, prompt=512):
     """The reference's decode step composed from its own apus_block_forward timed
     on one layer of each kind at full size (E experts, one token per call at the
@@ -659,7 +697,13 @@ def model_main(a):
 
     # ---- batch 1 ------------------------------------------------------------------------------
     h1, ms1, prefill1, launches1, out1, _, st1, stream1 = run(1, 1)
-    mtp_line = None if a.no_mtp else mtp_arm(L, W, h1[0], a, cfg)
+    mtp_line = dspark_line = None
+    if not a.no_mtp:
+        mk = W.mark()
+        mtp_line = mtp_arm(L, W, h1[0], a, cfg)
+        W.drop(mk)
+        dspark_line = dspark_arm(L, W, h1[0], a, cfg)
+        W.drop(mk)
     L.apus_cuda_model_destroy(h1[0])
 
     peak, peak_kind = peak_hbm()
@@ -686,6 +730,7 @@ def model_main(a):
                                 "avg_launch_us": st1[0] / max(st1[2], 1) * 1e3, "avg_unique_experts": st1[3] / max(st1[2], 1),
                                 "down_proj_frac": st1[3] * W2_BYTES / (st1[1] * 1e-3) / 1e9 / peak if st1[1] > 0 else None}},
         "mtp": mtp_line,
+        "dspark": dspark_line,
         "prefill": {"tokens": B * a.prompt, "ms": prefill_ms, "tok_s": B * a.prompt / (prefill_ms * 1e-3),
                     "note": "prompt consumed in chunks of positions (2048 rows = positions x sequences per pass)"},
         "weights": {"bytes": W.bytes, "generate_s": t_gen},
