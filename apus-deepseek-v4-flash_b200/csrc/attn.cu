@@ -1,5 +1,6 @@
 // Stable top-k selection and index-gathered sparse attention.
 #include <map>
+#include <cooperative_groups.h>
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -152,10 +153,171 @@ topk_stable_kernel(const float *__restrict__ scores, int n, int k, int32_t *__re
         out[i] = (int32_t)(0xffffffffu - (unsigned)(sel[i] & 0xffffffffu));
 }
 
+// The same selection for long rows, a row spread over a cluster of TOPK_CL CTAs (one CTA sweeping 262,144
+// scores five times takes ~350 us): every CTA histograms its slice, all of them add the eight histograms
+// through distributed shared memory and derive the same digit, so no result has to be sent around; the
+// chosen entries are stored into rank 0's shared memory (greater keys at slots counted per slice, ties in
+// index order behind them), where rank 0 sorts and writes them out.  Nobody touches another CTA's shared
+// memory before a first cluster barrier (a CTA of the cluster may not have started yet), and nobody leaves
+// before the last reader is done.
+#define TOPK_CL 8
+__global__ void __cluster_dims__(TOPK_CL, 1, 1) __launch_bounds__(TOPK_THREADS)
+topk_stable_cl_kernel(const float *__restrict__ scores, int n, int k, int32_t *__restrict__ idx_out,
+                      const long long *__restrict__ dyn_pos, int ratio, long long chunk_pos0, int rows_per_pos) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ unsigned hist[256];
+    __shared__ unsigned ghist[2][256];                 // rank 0's copies: the eight slices' histograms added up
+    __shared__ unsigned s_digit[2];
+    __shared__ unsigned s_cnt[2];                      // this slice's keys > T and keys == T
+    __shared__ unsigned s_taken, s_base;
+    __shared__ unsigned w_tie[TOPK_THREADS / 32];
+    __shared__ unsigned long long sel[TOPK_MAX_K];     // rank 0's copy collects the choice
+    const int rowi = blockIdx.x / TOPK_CL, rank = (int)cluster.block_rank();
+    const float *row = scores + (size_t)rowi * n;       // n, k as given are the row strides
+    int32_t *out = idx_out + (size_t)rowi * k;
+    if (dyn_pos || rows_per_pos > 0) {
+        const long long nbs = ((dyn_pos ? *dyn_pos : chunk_pos0 + rowi / rows_per_pos) + 1) / ratio;
+        n = (int)(nbs < n ? nbs : n);
+        k = k < n ? k : n;
+    }
+    cluster.sync();                                    // every CTA of the cluster runs from here on
+    if (k <= 0) return;                                // the same decision in all eight
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = (n + TOPK_CL - 1) / TOPK_CL, i0 = min(n, rank * per), i1 = min(n, i0 + per);
+    unsigned prefix = 0, need = (unsigned)(k < n ? k : n), n_greater = 0;
+    const bool all = k >= n;                           // every score is taken: only the order is left
+    if (all) k = n;
+    unsigned *g0 = cluster.map_shared_rank(&ghist[0][0], 0);     // rank 0 holds the summed histograms (two, alternating)
+    for (int pass = 0; pass < 4 && !all; pass++) {
+        const int shift = 24 - 8 * pass;
+        unsigned *gh = g0 + (pass & 1) * 256;
+        for (int i = tid; i < 256; i += TOPK_THREADS) {
+            hist[i] = 0;
+            if (rank == 0) ghist[pass & 1][i] = 0;             // last read two barriers ago
+        }
+        cluster.sync();
+        const unsigned himask = pass ? (0xffffffffu << (shift + 8)) : 0u;
+        for (int i = i0 + tid; i < i1; i += TOPK_THREADS) {
+            const unsigned key = order_key(row[i]);
+            if ((key & himask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+        }
+        __syncthreads();
+        if (tid < 256 && hist[tid]) atomicAdd(gh + tid, hist[tid]);   // one remote add per bin and CTA
+        cluster.sync();                                // the sum is complete
+        if (warp == 0) {
+            // the digit from the summed histogram (lane L: bins 255-8L .. 248-8L), the same in every CTA
+            unsigned c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { c[j] = gh[255 - 8 * lane - j]; tot += c[j]; }
+            unsigned inc = tot;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const unsigned v = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) inc += v;
+            }
+            const unsigned exc = inc - tot;
+            const unsigned hit = __ballot_sync(0xffffffffu, exc < need && inc >= need);
+            const int owner = hit ? __ffs(hit) - 1 : 31;
+            if (lane == owner) {
+                unsigned acc = exc;
+                int b = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int bin = 255 - 8 * lane - j;
+                    if (bin == 0) break;                    // bin 0 takes whatever is left
+                    if (acc + c[j] >= need) { b = bin; break; }
+                    acc += c[j];
+                }
+                s_digit[0] = acc; s_digit[1] = (unsigned)b;
+            }
+        }
+        __syncthreads();
+        n_greater += s_digit[0];
+        need -= s_digit[0];
+        prefix |= s_digit[1] << shift;
+        __syncthreads();                               // s_digit is rewritten in the next pass
+    }
+    const unsigned T = all ? 0u : prefix;
+    const unsigned n_ties = all ? 0u : (unsigned)k - n_greater;
+    // this slice's counts, then where its entries go: greater keys after those of lower slices, ties (in
+    // index order) after the ties of lower slices
+    if (tid == 0) { s_cnt[0] = 0; s_cnt[1] = 0; s_taken = 0; s_base = 0; }
+    __syncthreads();
+    {
+        unsigned g = 0, e = 0;
+        for (int i = i0 + tid; i < i1; i += TOPK_THREADS) {
+            const unsigned key = order_key(row[i]);
+            g += all || key > T;
+            e += !all && key == T;
+        }
+        g = __reduce_add_sync(0xffffffffu, g);
+        e = __reduce_add_sync(0xffffffffu, e);
+        if (lane == 0) { atomicAdd(&s_cnt[0], g); atomicAdd(&s_cnt[1], e); }
+    }
+    cluster.sync();
+    unsigned g_base = 0, e_base = 0;
+    for (int q = 0; q < rank; q++) {
+        const unsigned *cq = cluster.map_shared_rank(s_cnt, q);
+        g_base += cq[0]; e_base += cq[1];
+    }
+    unsigned long long *sel0 = cluster.map_shared_rank(sel, 0);
+    for (int base = i0; base < i1; base += TOPK_THREADS) {
+        const int i = base + tid;
+        const unsigned key = i < i1 ? order_key(row[i]) : 0u;
+        const bool gt = i < i1 && (all || key > T);
+        const bool eq = i < i1 && !all && key == T;
+        if (gt) {
+            const unsigned slot = g_base + atomicAdd(&s_taken, 1u);
+            sel0[slot] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i);
+        }
+        const unsigned m = __ballot_sync(0xffffffffu, eq);
+        if (lane == 0) w_tie[warp] = __popc(m);
+        __syncthreads();
+        unsigned before = 0, total = 0;
+        for (int w = 0; w < TOPK_THREADS / 32; w++) {
+            if (w < warp) before += w_tie[w];
+            total += w_tie[w];
+        }
+        const unsigned trank = e_base + s_base + before + __popc(m & ((1u << lane) - 1u));
+        if (eq && trank < n_ties)
+            sel0[n_greater + trank] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i);
+        __syncthreads();
+        if (tid == 0) s_base += total;
+        __syncthreads();
+    }
+    cluster.sync();                                    // the whole choice sits in rank 0
+    if (rank != 0) return;
+    int kp = 1;
+    while (kp < k) kp <<= 1;
+    for (int i = k + tid; i < kp; i += TOPK_THREADS) sel[i] = 0ull;
+    __syncthreads();
+    for (int size = 2; size <= kp; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < kp; i += TOPK_THREADS) {
+                const int j = i ^ stride;
+                if (j > i) {
+                    const unsigned long long a = sel[i], b = sel[j];
+                    const bool desc = ((i & size) == 0);
+                    if (desc ? (a < b) : (a > b)) { sel[i] = b; sel[j] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    for (int i = tid; i < k; i += TOPK_THREADS)
+        out[i] = (int32_t)(0xffffffffu - (unsigned)(sel[i] & 0xffffffffu));
+}
+
 int topk_stable(const float *scores, int n, int k, int32_t *idx, int rows,
                 cudaStream_t st, const long long *dyn_pos, int ratio, long long chunk_pos0, int rows_per_pos) {
     APUS_REQUIRE(k >= 1 && (k <= n || dyn_pos || rows_per_pos > 0) && k <= TOPK_MAX_K, "topk: n=%d k=%d unsupported", n, k);
     if (rows <= 0) return 0;
+    static const int cl_min = [] { const char *e = getenv("APUS_TOPK_CLUSTER_MIN"); return e && e[0] ? atoi(e) : 16384; }();
+    if (n >= cl_min) {                                  // long rows: a cluster of CTAs per row
+        topk_stable_cl_kernel<<<rows * TOPK_CL, TOPK_THREADS, 0, st>>>(scores, n, k, idx, dyn_pos, ratio, chunk_pos0, rows_per_pos);
+        APUS_LAUNCHED();
+        return 0;
+    }
     launch_k(topk_stable_kernel, rows, TOPK_THREADS, 0, st, scores, n, k, idx, dyn_pos, ratio, chunk_pos0, rows_per_pos);
     APUS_LAUNCHED();
     return 0;
