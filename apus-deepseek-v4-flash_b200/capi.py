@@ -277,6 +277,8 @@ def load(path=LIB_PATH):
         "apus_cuda_mtp_forward": (ci, [vp, vp, vp, ci, C.c_int64, vp, vp, vp]),
         "apus_cuda_model_spec_generate_mtp": (ci, [vp, vp, vp, ci, ci, ci, vp, vp]),
         "apus_cuda_dspark_create": (vp, [vp, vp]),
+        "apus_cuda_dspark_load": (vp, [vp, C.c_char_p]),
+        "apus_cuda_mtp_load": (vp, [vp, C.c_char_p, ci]),
         "apus_cuda_dspark_destroy": (None, [vp]),
         "apus_cuda_dspark_reset": (ci, [vp]),
         "apus_cuda_dspark_feed": (ci, [vp, vp, C.c_int64, ci]),

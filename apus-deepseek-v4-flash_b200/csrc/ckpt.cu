@@ -197,8 +197,9 @@ bool cfg_num(const JV &root, const char *k1, const char *k2, double *out) {
     return true;
 }
 
+// ds (nullable) [13]: the DSpark section -- block_size, noise_id, markov_rank, n_stages, n_targets, targets[8]
 int parse_config(const std::string &path, ApusCudaCkptCfg *c, std::vector<int> *ratios, std::vector<int> *hash,
-                 std::string *why) {
+                 std::string *why, int *ds = nullptr) {
     std::string text, jerr;
     if (!read_file(path, &text)) { *why = fmt("json: cannot open %s", path.c_str()); return 1; }
     JV root;
@@ -311,6 +312,12 @@ int parse_config(const std::string &path, ApusCudaCkptCfg *c, std::vector<int> *
         if (dj_obj && cfg_num(src, nullptr, "n_mtp_layers", &v)) n_stages = (int)v;
         const JV *tj = src.get(dj_obj ? "target_layer_ids" : "dspark_target_layer_ids");
         if (tj && tj->kind == JV::ARR) targets = (int)tj->arr.size() > 8 ? 8 : (int)tj->arr.size();
+        if (ds) {
+            int noise = 0;
+            if (cfg_num(src, nullptr, dj_obj ? "noise_token_id" : "dspark_noise_token_id", &v)) noise = (int)v;
+            ds[0] = block; ds[1] = noise; ds[2] = rank; ds[3] = n_stages; ds[4] = targets;
+            for (int i = 0; i < targets; i++) ds[5 + i] = tj->arr[i].kind == JV::NUM ? (int)tj->arr[i].num : 0;
+        }
         if (block <= 0 || n_stages <= 0 || targets <= 0 || rank <= 0) {
             *why = fmt("config: incomplete DSpark section (block_size %d, stages %d, targets %d, markov_rank %d)",
                        block, n_stages, targets, rank);
@@ -418,13 +425,13 @@ int read_f32(ApusCudaCkpt *c, const CkTensor &t, float *out, std::string *why) {
 // Experts [e_lo, e_hi) of a layer: the six tensors of each into one slab.
 struct ExpertPlan { QView q[3]; uint64_t total; bool adjacent; uint64_t lo; int shard; };
 
-bool plan_expert(ApusCudaCkpt *c, int layer, int e, ExpertPlan *p, std::string *why) {
+bool plan_expert(ApusCudaCkpt *c, const std::string &px, int e, ExpertPlan *p, std::string *why) {
     static const char *wn[3] = {"w1", "w2", "w3"};
     uint64_t lo = ~0ull, hi = 0;
     p->total = 0; p->shard = -1; p->adjacent = true;
     for (int i = 0; i < 3; i++) {
-        if (!fp4_view(c, fmt("layers.%d.ffn.experts.%d.%s", layer, e, wn[i]), &p->q[i], why)) {
-            if (why->empty()) *why = fmt("layers.%d expert %d", layer, e);
+        if (!fp4_view(c, px + fmt(".ffn.experts.%d.%s", e, wn[i]), &p->q[i], why)) {
+            if (why->empty()) *why = px + fmt(" expert %d", e);
             return false;
         }
         for (const CkTensor *t : {p->q[i].w, p->q[i].s}) {
@@ -463,12 +470,16 @@ int read_expert(ApusCudaCkpt *c, const ExpertPlan &p, uint8_t *slab, ApusFp4W *w
 
 // ---- one layer (c/layer.h:202-330) ---------------------------------------------
 int ckpt_load_layer(ApusCudaCkpt *c, int layer, int e_lo, int e_hi, CkLayerHost *out, std::string *why) {
+    return ckpt_load_layer_named(c, fmt("layers.%d", layer), c->ratios[layer], c->hash[layer], layer, e_lo, e_hi, out, why);
+}
+
+// c/layer.h:202 apus_layer_load_named: the block under any prefix ("layers.<i>", "mtp.<k>"), its kind given
+int ckpt_load_layer_named(ApusCudaCkpt *c, const std::string &px, int ratio, int hash, int layer, int e_lo, int e_hi,
+                          CkLayerHost *out, std::string *why) {
     const ApusCudaCkptCfg &cfg = c->cfg;
-    const int ratio = c->ratios[layer], hash = c->hash[layer];
     const int dim = cfg.dim, h = cfg.n_heads, d = cfg.head_dim, ql = cfg.q_lora_rank, G = cfg.o_groups,
               ol = cfg.o_lora_rank, E = cfg.n_routed_experts, topk = cfg.n_activated_experts, hc = cfg.hc_mult,
               mix = (2 + hc) * hc, rd = cfg.rope_head_dim, idm = cfg.index_head_dim;
-    const std::string px = fmt("layers.%d", layer);
     ApusCudaLayerDesc &D = out->desc;
     memset(&D, 0, sizeof D);
     out->raw.clear(); out->f32.clear();
@@ -564,7 +575,7 @@ int ckpt_load_layer(ApusCudaCkpt *c, int layer, int e_lo, int e_hi, CkLayerHost 
         const int n = e_hi > e_lo ? e_hi - e_lo : 0;
         std::vector<ExpertPlan> plans(n);
         for (int i = 0; i < n; i++)                        // shard headers are parsed here, on this thread
-            if (!plan_expert(c, layer, e_lo + i, &plans[i], why)) return 1;
+            if (!plan_expert(c, px, e_lo + i, &plans[i], why)) return 1;
         const size_t base = out->raw.size();
         for (int i = 0; i < n; i++) out->raw.emplace_back(plans[i].total);
         const char *env = getenv("APUS_IO_THREADS");
@@ -747,7 +758,10 @@ ApusCudaCkpt *apus_cuda_ckpt_open(const char *dir, char *err, size_t errcap) {
     std::unique_ptr<ApusCudaCkpt> c(new ApusCudaCkpt());
     c->dir = dir;
     std::string why;
-    if (parse_config(c->dir + "/config.json", &c->cfg, &c->ratios, &c->hash, &why)) { put_err(err, errcap, why); return nullptr; }
+    int ds[13] = {0};
+    if (parse_config(c->dir + "/config.json", &c->cfg, &c->ratios, &c->hash, &why, ds)) { put_err(err, errcap, why); return nullptr; }
+    c->ds_block = ds[0]; c->ds_noise = ds[1]; c->ds_rank = ds[2]; c->ds_stages = ds[3]; c->ds_ntargets = ds[4];
+    for (int i = 0; i < 8; i++) c->ds_targets[i] = ds[5 + i];
     // <dir>/model.safetensors.index.json, else <dir>/weights/...
     c->wdir = c->dir;
     std::string text;
@@ -847,7 +861,7 @@ int apus_cuda_ckpt_expert(ApusCudaCkpt *c, int layer, int expert, void *slab, ui
     }
     std::string why;
     ExpertPlan p;
-    if (!plan_expert(c, layer, expert, &p, &why)) { set_error("%s", why.c_str()); return 1; }
+    if (!plan_expert(c, fmt("layers.%d", layer), expert, &p, &why)) { set_error("%s", why.c_str()); return 1; }
     if (p.total > cap) { set_error("ckpt_expert: slab of %llu bytes needed", (unsigned long long)p.total); return 1; }
     ApusFp4W w[3];
     if (read_expert(c, p, (uint8_t *)slab, w, &why)) { set_error("%s", why.c_str()); return 1; }
@@ -1017,6 +1031,144 @@ struct Serve {
 
 }  // namespace
 }  // namespace apus
+
+// ---- draft modules from the checkpoint directory (c/mtp.h:213-281, c/dspark.h:272-341) -------------
+namespace apus {
+namespace {
+
+// Host copies of what a draft module adds to its blocks, alive until the module is created.
+struct GlueHost {
+    std::vector<std::vector<uint8_t>> raw;
+    std::vector<std::vector<float>> f32;
+    std::string why;
+    bool fp8(ApusCudaCkpt *c, const std::string &name, int64_t O, int64_t K, ApusFp8W *w) {
+        QView q;
+        if (!fp8_view(c, name, &q, &why) || q.O != O || q.K != K) { why = "bad tensor " + name; return false; }
+        raw.emplace_back(q.w->nbytes);
+        raw.emplace_back(q.s->nbytes);
+        uint8_t *pw = raw[raw.size() - 2].data(), *ps = raw.back().data();
+        if (c->read(*q.w, pw, &why) || c->read(*q.s, ps, &why)) return false;
+        w->codes = pw; w->scales = ps; w->O = q.O; w->K = q.K;
+        return true;
+    }
+    const float *vec(ApusCudaCkpt *c, const std::string &name, size_t n, bool f32_only = false) {
+        const CkTensor *t = c->find(name, &why);
+        if (!t || t->nelem() != n || (f32_only ? t->dtype != APUS_CUDA_ST_F32
+                                               : (t->dtype != APUS_CUDA_ST_F32 && t->dtype != APUS_CUDA_ST_BF16))) {
+            why = "bad tensor " + name;
+            return nullptr;
+        }
+        f32.emplace_back(n);
+        if (read_f32(c, *t, f32.back().data(), &why)) return nullptr;
+        return f32.back().data();
+    }
+};
+
+// a draft block "mtp.<k>" with the rope table of its kind over max_pos rows
+int load_draft_block(ApusCudaCkpt *c, int k, int ratio, int hash, int max_pos, CkLayerHost *L, std::vector<float> *cs,
+                     std::string *why) {
+    if (ckpt_load_layer_named(c, fmt("mtp.%d", k), ratio, hash, c->cfg.n_layers + k, 0, -1, L, why)) return 1;
+    const size_t half = c->cfg.rope_head_dim / 2;
+    cs[0].resize((size_t)max_pos * half); cs[1].resize((size_t)max_pos * half);
+    ckpt_rope(c->cfg, ratio, max_pos, cs[0].data(), cs[1].data());
+    L->desc.cos = cs[0].data(); L->desc.sin = cs[1].data(); L->desc.rope_rows = max_pos;
+    L->desc.acfg.max_pos = max_pos;
+    return 0;
+}
+
+}  // namespace
+}  // namespace apus
+
+extern "C" {
+
+// c/mtp.h:213-281 apus_mtp_load: MTP block `idx` ("mtp.<idx>.*") of the checkpoint the model came from.
+ApusCudaMtp *apus_cuda_mtp_load(ApusCudaModel *m, const char *dir, int idx) {
+    int max_pos = 0;
+    if (!m || apus_cuda_model_info(m, nullptr, &max_pos, nullptr, nullptr)) { set_error("mtp_load: NULL model"); return nullptr; }
+    char err[512] = "";
+    ApusCudaCkpt *c = apus_cuda_ckpt_open(dir, err, sizeof err);
+    if (!c) return nullptr;
+    const ApusCudaCkptCfg &cfg = c->cfg;
+    ApusCudaMtp *mt = nullptr;
+    std::string why;
+    do {
+        if (idx < 0 || cfg.n_mtp <= idx) { why = fmt("mtp: model has no MTP block %d", idx); break; }
+        CkLayerHost L;
+        std::vector<float> cs[2];
+        GlueHost g;
+        if (load_draft_block(c, idx, cfg.mtp_ratio, cfg.mtp_hash, max_pos, &L, cs, &why)) break;
+        const std::string px = fmt("mtp.%d", idx);
+        const size_t dim = cfg.dim, hc = cfg.hc_mult;
+        ApusCudaMtpDesc d;
+        memset(&d, 0, sizeof d);
+        d.block = L.desc;
+        const float *scale = nullptr;
+        if (!g.fp8(c, px + ".e_proj", dim, dim, &d.e_proj) || !g.fp8(c, px + ".h_proj", dim, dim, &d.h_proj) ||
+            !(d.enorm_w = g.vec(c, px + ".enorm.weight", dim)) || !(d.hnorm_w = g.vec(c, px + ".hnorm.weight", dim)) ||
+            !(d.norm_w = g.vec(c, px + ".norm.weight", dim)) || !(d.hc_head_fn = g.vec(c, px + ".hc_head_fn", hc * hc * dim, true)) ||
+            !(d.hc_head_base = g.vec(c, px + ".hc_head_base", hc)) || !(scale = g.vec(c, px + ".hc_head_scale", 1))) {
+            why = "mtp: " + g.why;
+            break;
+        }
+        d.hc_head_scale = scale[0];
+        mt = apus_cuda_mtp_create(m, &d);               // copies everything to HBM
+        if (!mt) why = apus_cuda_last_error();
+    } while (0);
+    apus_cuda_ckpt_close(c);
+    if (!mt) set_error("%s", why.c_str());
+    return mt;
+}
+
+// c/dspark.h:272-341 apus_dspark_load: the DSpark stages "mtp.0 .. mtp.<n_stages-1>" and their glue.
+ApusCudaDspark *apus_cuda_dspark_load(ApusCudaModel *m, const char *dir) {
+    int max_pos = 0;
+    if (!m || apus_cuda_model_info(m, nullptr, &max_pos, nullptr, nullptr)) { set_error("dspark_load: NULL model"); return nullptr; }
+    char err[512] = "";
+    ApusCudaCkpt *c = apus_cuda_ckpt_open(dir, err, sizeof err);
+    if (!c) return nullptr;
+    const ApusCudaCkptCfg &cfg = c->cfg;
+    ApusCudaDspark *ds = nullptr;
+    std::string why;
+    do {
+        if (!cfg.dspark || c->ds_stages <= 0 || c->ds_stages > 8) { why = "dspark: model declares no DSpark stages"; break; }
+        const int n = c->ds_stages, last = n - 1;
+        std::vector<CkLayerHost> Ls((size_t)n);
+        std::vector<std::vector<float>> cs((size_t)2 * n);
+        bool ok = true;
+        for (int k = 0; k < n && ok; k++) ok = load_draft_block(c, k, 0, 0, max_pos, &Ls[k], &cs[2 * k], &why) == 0;
+        if (!ok) break;
+        std::vector<ApusCudaLayerDesc> descs((size_t)n);
+        for (int k = 0; k < n; k++) descs[k] = Ls[k].desc;
+        GlueHost g;
+        const size_t dim = cfg.dim, hc = cfg.hc_mult, V = cfg.vocab_size, rank = (size_t)c->ds_rank;
+        ApusCudaDsparkDesc d;
+        memset(&d, 0, sizeof d);
+        d.n_stages = n; d.block_size = c->ds_block; d.noise_id = c->ds_noise; d.markov_rank = c->ds_rank;
+        d.n_targets = c->ds_ntargets;
+        for (int i = 0; i < 8; i++) d.targets[i] = c->ds_targets[i];
+        d.stages = descs.data();
+        const float *scale = nullptr;
+        const std::string pl = fmt("mtp.%d", last);
+        if (!g.fp8(c, "mtp.0.main_proj", dim, (int64_t)d.n_targets * dim, &d.main_proj) ||
+            !(d.main_norm_w = g.vec(c, "mtp.0.main_norm.weight", dim)) || !(d.norm_w = g.vec(c, pl + ".norm.weight", dim)) ||
+            !(d.hc_head_fn = g.vec(c, pl + ".hc_head_fn", hc * hc * dim, true)) || !(d.hc_head_base = g.vec(c, pl + ".hc_head_base", hc)) ||
+            !(scale = g.vec(c, pl + ".hc_head_scale", 1)) ||
+            !(d.markov_w1 = g.vec(c, pl + ".markov_head.markov_w1.weight", V * rank)) ||
+            !(d.markov_w2 = g.vec(c, pl + ".markov_head.markov_w2.weight", V * rank)) ||
+            !(d.conf_proj = g.vec(c, pl + ".confidence_head.proj.weight", dim + rank))) {
+            why = "dspark: " + g.why;
+            break;
+        }
+        d.hc_head_scale = scale[0];
+        ds = apus_cuda_dspark_create(m, &d);
+        if (!ds) why = apus_cuda_last_error();
+    } while (0);
+    apus_cuda_ckpt_close(c);
+    if (!ds) set_error("%s", why.c_str());
+    return ds;
+}
+
+}  // extern "C"
 
 extern "C" int apus_cuda_serve(ApusCudaModel *m, int in_fd, int out_fd, int eos_id) {
     int batch = 0, max_pos = 0;

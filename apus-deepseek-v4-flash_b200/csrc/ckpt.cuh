@@ -32,6 +32,8 @@ struct CkShard {
 struct ApusCudaCkpt {
     std::string dir, wdir;                  // wdir: where the index and the shards lie
     ApusCudaCkptCfg cfg;
+    // the DSpark section of the config (c/model.h:48-56, 336-373); valid when cfg.dspark
+    int ds_block = 0, ds_noise = 0, ds_rank = 0, ds_stages = 0, ds_ntargets = 0, ds_targets[8] = {0};
     std::vector<int> ratios, hash;
     std::vector<apus::CkShard> shards;
     std::map<std::string, int> shard_of;    // tensor name -> shard
@@ -58,6 +60,8 @@ struct CkLayerHost {
 };
 // Experts outside [e_lo, e_hi) are not read (their views stay NULL).
 int ckpt_load_layer(ApusCudaCkpt *c, int layer, int e_lo, int e_hi, CkLayerHost *out, std::string *why);
+int ckpt_load_layer_named(ApusCudaCkpt *c, const std::string &prefix, int ratio, int hash, int layer, int e_lo, int e_hi,
+                          CkLayerHost *out, std::string *why);
 int ckpt_rope(const ApusCudaCkptCfg &cfg, int ratio, int64_t rows, float *cos, float *sin);
 
 }  // namespace apus

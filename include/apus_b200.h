@@ -653,6 +653,9 @@ typedef struct {
 } ApusCudaMtpDesc;
 typedef struct ApusCudaMtp ApusCudaMtp;
 ApusCudaMtp *apus_cuda_mtp_create(ApusCudaModel *parent, const ApusCudaMtpDesc *d);
+/* c/mtp.h:213-281 apus_mtp_load: MTP block `idx` ("mtp.<idx>.*") read from the checkpoint directory
+ * `parent` was loaded from (same files, names and conversions as the reference's loader). */
+ApusCudaMtp *apus_cuda_mtp_load(ApusCudaModel *parent, const char *dir, int idx);
 void apus_cuda_mtp_destroy(ApusCudaMtp *mt);
 /* c/mtp.h:293-299: a fresh attention state. */
 int apus_cuda_mtp_reset(ApusCudaMtp *mt);
@@ -682,6 +685,9 @@ typedef struct {
 } ApusCudaDsparkDesc;
 typedef struct ApusCudaDspark ApusCudaDspark;
 ApusCudaDspark *apus_cuda_dspark_create(ApusCudaModel *parent, const ApusCudaDsparkDesc *d);
+/* c/dspark.h:272-341 apus_dspark_load: the stages "mtp.0 .. mtp.<n-1>" and their glue from the checkpoint
+ * directory, sizes from its DSpark config section (c/model.h:336-373). */
+ApusCudaDspark *apus_cuda_dspark_load(ApusCudaModel *parent, const char *dir);
 void apus_cuda_dspark_destroy(ApusCudaDspark *ds);
 /* c/dspark.h:353-356: empty stage rings. */
 int apus_cuda_dspark_reset(ApusCudaDspark *ds);

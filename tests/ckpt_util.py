@@ -66,12 +66,12 @@ def model_config(tm):
     }
 
 
-def layer_tensors(i, L, seed, coalesce):
-    """The tensors of block i in file order.  wo_a is drawn here as FP8 and the
-    layer's in-memory BF16 copy is overwritten with what a loader must derive."""
+def layer_tensors(i, L, seed, coalesce, px=None):
+    """The tensors of block i (or of the block under prefix `px`) in file order.  wo_a is drawn
+    here as FP8 and the layer's in-memory BF16 copy is overwritten with what a loader must derive."""
     A, W, Mo = L.attn, L.attn, L.moe
     D = A.D
-    px = f"layers.{i}"
+    px = px or f"layers.{i}"
     out = []
     f32 = lambda name, a: out.append((f"{px}.{name}", "F32", a.shape, np.ascontiguousarray(a, np.float32).tobytes()))
     bf16 = lambda name, a: out.append((f"{px}.{name}", "BF16", a.shape, bf16_payload(a)))
@@ -120,14 +120,53 @@ def layer_tensors(i, L, seed, coalesce):
     return out + late
 
 
-def write_checkpoint(path, tm, seed=0, n_shards=2, coalesce=True, subdir=False):
+def draft_tensors(mtp=None, dspark=None, seed=0, coalesce=True):
+    """The "mtp.<k>.*" tensors of an MTP head (cases.TinyMtp, c/mtp.h:213-281) or of a DSpark module
+    (cases.TinyDspark, c/dspark.h:272-341) and the config entries that declare them."""
+    out, cfg = [], {}
+    f32 = lambda name, a: out.append((name, "F32", np.shape(a), np.ascontiguousarray(a, np.float32).tobytes()))
+    bf16 = lambda name, a: out.append((name, "BF16", np.shape(a), bf16_payload(a)))
+
+    def fp8(name, cs):
+        out.append((f"{name}.weight", "F8_E4M3", cs[0].shape, cs[0].tobytes()))
+        out.append((f"{name}.scale", "F8_E8M0", cs[1].shape, cs[1].tobytes()))
+    if mtp is not None:
+        cfg["mtp"] = [{"compress_ratio": 0, "hash": False}]
+        out += layer_tensors(1000, mtp.block, seed, coalesce, px="mtp.0")
+        fp8("mtp.0.e_proj", mtp.e_proj); fp8("mtp.0.h_proj", mtp.h_proj)
+        f32("mtp.0.enorm.weight", mtp.enorm_w); f32("mtp.0.hnorm.weight", mtp.hnorm_w); f32("mtp.0.norm.weight", mtp.norm_w)
+        f32("mtp.0.hc_head_fn", mtp.hc_head_fn); f32("mtp.0.hc_head_base", mtp.hc_head_base)
+        f32("mtp.0.hc_head_scale", np.array([mtp.desc.hc_head_scale], np.float32))
+    if dspark is not None:
+        d = dspark.desc
+        cfg["dspark"] = {"block_size": int(d.block_size), "noise_token_id": int(d.noise_id), "markov_rank": int(d.markov_rank),
+                         "target_layer_ids": [int(d.targets[i]) for i in range(d.n_targets)], "n_mtp_layers": int(d.n_stages)}
+        last = d.n_stages - 1
+        for k, L in enumerate(dspark.stages):
+            out += layer_tensors(1000 + k, L, seed, coalesce, px=f"mtp.{k}")
+        fp8("mtp.0.main_proj", dspark.main_proj)
+        f32("mtp.0.main_norm.weight", dspark.main_norm_w); f32(f"mtp.{last}.norm.weight", dspark.norm_w)
+        f32(f"mtp.{last}.hc_head_fn", dspark.hc_head_fn); f32(f"mtp.{last}.hc_head_base", dspark.hc_head_base)
+        f32(f"mtp.{last}.hc_head_scale", np.array([d.hc_head_scale], np.float32))
+        bf16(f"mtp.{last}.markov_head.markov_w1.weight", dspark.markov_w1)
+        bf16(f"mtp.{last}.markov_head.markov_w2.weight", dspark.markov_w2)
+        bf16(f"mtp.{last}.confidence_head.proj.weight", dspark.conf_proj)
+    return out, cfg
+
+
+def write_checkpoint(path, tm, seed=0, n_shards=2, coalesce=True, subdir=False, mtp=None, dspark=None):
     """Writes `tm` under `path`; returns {tensor name: (dtype, shape, payload)}.
-    subdir: shards + index under <path>/weights (the fixture layout, c/model.h:414-417)."""
+    subdir: shards + index under <path>/weights (the fixture layout, c/model.h:414-417).
+    mtp / dspark: a draft module to write beside the model (both use the "mtp.*" names: one at a time)."""
     path = Path(path)
     wdir = path / "weights" if subdir else path
     wdir.mkdir(parents=True, exist_ok=True)
-    (path / "config.json").write_text(json.dumps(model_config(tm), indent=1))
+    config = model_config(tm)
+    extra, extra_cfg = draft_tensors(mtp, dspark, seed, coalesce)
+    config.update(extra_cfg)
+    (path / "config.json").write_text(json.dumps(config, indent=1))
     shards = [[] for _ in range(n_shards)]
+    shards[0] += extra
     for i, L in enumerate(tm.layers):
         shards[i % n_shards] += layer_tensors(i, L, seed, coalesce)
     V, dim, hc = tm.M["vocab"], cases.ATTN_DIMS["dim"], tm.M["hc"]

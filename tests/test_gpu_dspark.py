@@ -90,3 +90,29 @@ def test_speculative_loop_with_dspark(setup):
     toks2 = np.zeros(n_gen, np.int32)
     assert L.apus_cuda_model_spec_generate_dspark(h, ds, P(prompt), n, n_gen, P(toks2), None) == 0
     assert toks2.tolist() == toks.tolist()
+
+
+def test_dspark_loaded_from_a_checkpoint_directory(tmp_path):
+    """The module written as "mtp.<k>.*" tensors with its config section (reference c/dspark.h:272-341,
+    c/model.h:336-373) and read back by apus_cuda_dspark_load: the draft round of the in-memory module."""
+    import ckpt_util
+    L = lib()
+    Mdl = cases.TinyModel(D["seed"], rope(), D["n_layers"])
+    Ds = cases.TinyDspark(D["seed"] + 4, rope(), D["targets"], D["n_stages"], D["block_size"], D["noise_id"], D["rank"])
+    ckpt_util.write_checkpoint(tmp_path, Mdl, seed=3, dspark=Ds)
+    h_mem = L.apus_cuda_model_create(C.byref(Mdl.desc), 1, 64)
+    h_dir = L.apus_cuda_model_load(str(tmp_path).encode(), 1, 64, 0, -1)
+    assert h_mem and h_dir, L.apus_cuda_last_error()
+    ds_mem = L.apus_cuda_dspark_create(h_mem, C.byref(Ds.desc))
+    ds_dir = L.apus_cuda_dspark_load(h_dir, str(tmp_path).encode())
+    assert ds_mem and ds_dir, L.apus_cuda_last_error()
+    try:
+        a = one_round(L, Mdl, ds_mem, [D["n_prompt"]])
+        b = one_round(L, Mdl, ds_dir, [D["n_prompt"]])
+        assert a[0].tolist() == b[0].tolist()
+        for x, y in zip(a[1:], b[1:]):
+            assert np.array_equal(bits(x), bits(y))
+    finally:
+        L.apus_cuda_dspark_destroy(ds_mem); L.apus_cuda_dspark_destroy(ds_dir)
+        L.apus_cuda_model_destroy(h_mem); L.apus_cuda_model_destroy(h_dir)
+        L.apus_cuda_disable()

@@ -146,3 +146,36 @@ def test_speculative_loop_with_the_mtp_head(setup):
     toks2 = np.zeros(n_gen, np.int32)
     assert L.apus_cuda_model_spec_generate_mtp(h, mt, P(prompt), n, n_gen, depth, P(toks2), None) == 0
     assert toks2.tolist() == toks.tolist()
+
+
+def test_mtp_head_loaded_from_a_checkpoint_directory(tmp_path):
+    """The head written as "mtp.0.*" tensors beside the model (reference c/mtp.h:213-281) and read back by
+    apus_cuda_mtp_load: the same logits and hidden, bit for bit, as the head handed over in memory."""
+    import ckpt_util
+    L = lib()
+    Mdl = cases.TinyModel(MTP_CASE["seed"], rope(), MTP_CASE["n_layers"])
+    Mtp = cases.TinyMtp(MTP_CASE["seed"] + 3, rope())
+    ckpt_util.write_checkpoint(tmp_path, Mdl, seed=3, mtp=Mtp)         # also rewrites every wo_a as a loader derives it
+    V, hd, n = Mdl.M["vocab"], Mdl.M["hc"] * cases.ATTN_DIMS["dim"], MTP_CASE["n_prompt"]
+    prompt = np.ascontiguousarray(cases.prompt_ids(MTP_CASE["seed"] + 5, 1, n, V))
+    h_mem = L.apus_cuda_model_create(C.byref(Mdl.desc), 1, 64)
+    h_dir = L.apus_cuda_model_load(str(tmp_path).encode(), 1, 64, 0, -1)
+    assert h_mem and h_dir, L.apus_cuda_last_error()
+    mt_mem = L.apus_cuda_mtp_create(h_mem, C.byref(Mtp.desc))
+    mt_dir = L.apus_cuda_mtp_load(h_dir, str(tmp_path).encode(), 0)
+    assert mt_mem and mt_dir, L.apus_cuda_last_error()
+    try:
+        outs = []
+        for h, mt in ((h_mem, mt_mem), (h_dir, mt_dir)):
+            hh, lg, hl = np.empty((1, n, hd), np.float32), np.empty((1, V), np.float32), np.empty((1, hd), np.float32)
+            assert L.apus_cuda_model_forward_h(h, P(prompt), n, P(lg), 0, None, P(hh)) == 0, L.apus_cuda_last_error()
+            assert L.apus_cuda_mtp_forward(mt, P(hh), P(prompt), n, 0, P(lg), None, P(hl)) == 0, L.apus_cuda_last_error()
+            outs.append((hh, lg, hl))
+        for a, b in zip(outs[0], outs[1]):
+            assert np.array_equal(bits(a), bits(b))
+        assert not L.apus_cuda_mtp_load(h_dir, str(tmp_path).encode(), 1)
+        assert b"no MTP block 1" in L.apus_cuda_last_error()
+    finally:
+        L.apus_cuda_mtp_destroy(mt_mem); L.apus_cuda_mtp_destroy(mt_dir)
+        L.apus_cuda_model_destroy(h_mem); L.apus_cuda_model_destroy(h_dir)
+        L.apus_cuda_disable()
