@@ -197,7 +197,7 @@ static int compressor_step(const CompDev &W, CompStateDev &S, const float *x, in
 
 int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
               const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st,
-              const long long *pos_dev, const float *cs_table) {
+              const long long *pos_dev, const float *cs_table, bool x_codes) {
     const ApusAttnCfg &c = A.cfg;
     const int B = S.B;
     // pos_dev != NULL: every position-dependent value is read on the device from
@@ -213,11 +213,15 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     // its own scratch.  The reference's order (indexer, ring write, compressor,
     // attention; c/attn.h:1572-1665) only matters through the data each step
     // reads, which the joins preserve.
-    if (act_quant(x, nullptr, B, c.dim, b.xq, b.xs, nullptr, st)) return 1;            // x codes: wq_a and wkv
+    if (!x_codes && act_quant(x, nullptr, B, c.dim, b.xq, b.xs, nullptr, st)) return 1;   // x codes: wq_a and wkv
     cudaStream_t sa = branch_begin(st, 0);
     if (qgemm_dev(A.wkv, nullptr, b.xq, b.xs, B, b.kva, true, 0.f, sa)) return 1;       // (a) c/attn.h:1552-1569
     if (row_ops(b.kva, d, b.kv, d, B, d, ROW_RMS_W | ROW_ROPE | ROW_FP8QAT | ROW_BF16_OUT, A.kv_norm, c.eps, rd,
                 cs_pos, B, 0, sa, dp))
+        return 1;
+    // ring write (c/attn.h:1642-1658): nothing reads the ring before the gathered attention, so it stays on (a)
+    if (scatter_rows(S.win.as<float>() + (pos_dev ? 0 : (size_t)(pos % win) * d), (long long)win * d, b.kv, d, B, sa,
+                     pos_dev, win))
         return 1;
     cudaStream_t sb = st;
     if (ratio) {                                                                         // (b) c/attn.h:1660-1665
@@ -226,19 +230,20 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     }
     // the indexer's own compressor and its head weights read only x: they start with the step on a chain
     // of their own (d) and meet the q-dependent part of the indexer (c) before the scores
-    cudaStream_t sd = st;
+    cudaStream_t sd = st, se = st;
     if (ratio && c.has_indexer) {
         sd = branch_begin(st, 3);
         if (compressor_step(A.idx_comp, S.idx, x, B, c.dim, pos, cs_rp, b, sd, pos_dev, cs_table, true)) return 1;
+        se = branch_begin(st, 4);                                  // (e) the head weights, beside (d)
         if (f32_linear(A.idx_wproj, x, b.wt, B, c.dim, c.idx_heads,
-                       APUS_CUDA_R_IN | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_IDX_WPROJ), sd))
+                       APUS_CUDA_R_IN | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_IDX_WPROJ), se))
             return 1;
     }
     // q path (c/attn.h:1525-1548)
     if (qgemm_dev(A.wq_a, nullptr, b.xq, b.xs, B, b.qa, true, 0.f, st)) return 1;
-    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st))
+    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st, nullptr,
+                b.xq2, b.xs2))                                                           // + qr codes: wq_b and idx_wq_b
         return 1;
-    if (act_quant(b.qr, nullptr, B, c.q_lora, b.xq2, b.xs2, nullptr, st)) return 1;     // qr codes: wq_b and idx_wq_b
     // compressed ids (c): the indexer
     int compw = 0;
     const int32_t *sel = nullptr;
@@ -252,7 +257,8 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
             if (row_ops(b.iq, idm, b.iq, idm, B * ih, idm, ROW_ROPE | ROW_HADAMARD | ROW_FP4QAT | ROW_BF16_OUT, nullptr,
                         0.f, rd, cs_pos, B * ih, 0, sc, dp))
                 return 1;
-            if (sd != st && branch_end(3, sc)) return 1;          // (d) -> (c): cache entry and head weights are ready
+            if (sd != st && branch_end(3, sc)) return 1;          // (d), (e) -> (c): cache entry and head weights are ready
+            if (se != st && branch_end(4, sc)) return 1;
             const float wscale = (float)(pow((double)idm, -0.5) * pow((double)ih, -0.5));
             compw = (int)(c.idx_topk < nbs ? c.idx_topk : nbs);
             if (pos_dev) {                         // capacities; the live counts are derived on the device
@@ -273,6 +279,11 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
             compw = pos_dev ? S.comp.cap : (int)nbs;
         }
     }
+    // the index row of the step (c/attn.h:692-737) reads the indexer's picks, or only the position: it is
+    // written on the chain that has its last input, off the q path
+    if (build_idx(b.idxs, win, pos, sel, compw, B, sel ? sc : sa, pos_dev, ratio)) return 1;
+    // ... and compacted there, when the step has a scratch of its own to compact into
+    if (b.sa && sparse_attn_compact(b.idxs, h, win + compw, B, b.sa, b.sa_cap, sel ? sc : sa)) return 1;
     if (qgemm_dev(A.wq_b, nullptr, b.xq2, b.xs2, B, b.q, true, 0.f, st)) return 1;
     if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs_pos, B * h, 0, st, dp)) return 1;
     // join the side chains: everything below reads what they produced
@@ -280,18 +291,13 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
     if (sb != st && branch_end(1, st)) return 1;
     if (sc != st && branch_end(2, st)) return 1;
     if (idx_k_out) *idx_k_out = compw;
-    // ring write (c/attn.h:1642-1658)
-    if (scatter_rows(S.win.as<float>() + (pos_dev ? 0 : (size_t)(pos % win) * d), (long long)win * d, b.kv, d, B, st,
-                     pos_dev, win))
-        return 1;
     // gathered attention over ring ++ compressed cache, inverse RoPE
-    if (build_idx(b.idxs, win, pos, sel, compw, B, st, pos_dev, ratio)) return 1;
     const float scale = (float)pow((double)d, -0.5);
+    const SaRope back = {cs_pos, pos_dev, rd};        // the rows leave the attention rotated back (c/attn.h:1384-1388)
     if (sparse_attn(b.q, A.sink, h, d, b.idxs, win + compw, B, scale, S.win.p, win,
                     ratio ? S.comp.cache.p : nullptr, ratio ? S.comp.nb : 0, 0, b.o, st, (long long)win * d,
-                    ratio ? (long long)S.comp.cap * d : 0, b.sa, b.sa_cap))
+                    ratio ? (long long)S.comp.cap * d : 0, b.sa, b.sa_cap, 0, b.sa != nullptr, &back))
         return 1;
-    if (row_ops(b.o, d, b.o, d, B * h, d, ROW_ROPE_INV, nullptr, 0.f, rd, cs_pos, B * h, 0, st, dp)) return 1;
     // grouped low-rank o-projection (c/attn.h:1692-1737)
     const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
     if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, B, sub, ol,
@@ -342,8 +348,9 @@ int attn_chunk(const AttnDev &A, StateDev &S, const float *x, long long pos0, in
         return 1;
     // q path (c/attn.h:1525-1548)
     if (qgemm_dev(A.wq_a, nullptr, b.xq, b.xs, T, b.qa, true, 0.f, st)) return 1;
-    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, T, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st)) return 1;
-    if (act_quant(b.qr, nullptr, T, c.q_lora, b.xq2, b.xs2, nullptr, st)) return 1;
+    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, T, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st, nullptr, b.xq2,
+                b.xs2))
+        return 1;
     if (qgemm_dev(A.wq_b, nullptr, b.xq2, b.xs2, T, b.q, true, 0.f, st)) return 1;
     if (row_ops(b.q, d, b.q, d, T * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs0, B * h, rd, st)) return 1;
     // compressed entries and the ids each row may attend to (c/attn.h:1105-1168, 1660-1665): an entry is

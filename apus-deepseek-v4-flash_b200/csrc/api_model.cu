@@ -45,10 +45,11 @@ int block_attn_half(const LayerDev &L, StateDev &S, float **h, float **hn, int B
     const float *cs_pos = L.cs + (size_t)pos * half2;
     const long long rp = ratio ? pos + 1 - ratio : -1;
     const float *cs_rp = rp >= 0 ? L.cs + (size_t)rp * half2 : cs_pos;
+    int x_codes = 0;                            // the mHC step leaves the codes of the sublayer input where it can
     if (mhc_pre(*h, dim, hc, L.hc_attn_fn, L.hc_attn_scale, L.hc_attn_base, norm_eps, hc_eps, iters,
-                L.attn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st, bb.raw))
+                L.attn_norm_w, norm_eps, nullptr, bb.post, bb.comb, bb.y, bb.x, B, st, bb.raw, sb.xq, sb.xs, &x_codes))
         return 1;
-    if (attn_step(L.attn, S, bb.x, pos, cs_pos, cs_rp, bb.sub, sb, nullptr, st, pos_dev, L.cs)) return 1;
+    if (attn_step(L.attn, S, bb.x, pos, cs_pos, cs_rp, bb.sub, sb, nullptr, st, pos_dev, L.cs, x_codes != 0)) return 1;
     if (mhc_post(bb.sub, *h, bb.post, bb.comb, *hn, dim, hc, B, st)) return 1;
     { float *t = *h; *h = *hn; *hn = t; }
     return 0;
@@ -1441,8 +1442,9 @@ static int ds_attn(ApusCudaDspark *ds, int k, const float *x, long long start_po
     const float *cs1 = L.cs + (size_t)(start_pos + 1) * rd;            // draft row t rotates at start_pos + 1 + t
     if (act_quant(x, nullptr, B, c.dim, b.xq, b.xs, nullptr, st)) return 1;
     if (qgemm_dev(A.wq_a, nullptr, b.xq, b.xs, B, b.qa, true, 0.f, st)) return 1;
-    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st)) return 1;
-    if (act_quant(b.qr, nullptr, B, c.q_lora, b.xq2, b.xs2, nullptr, st)) return 1;
+    if (row_ops(b.qa, c.q_lora, b.qr, c.q_lora, B, c.q_lora, ROW_RMS_W, A.q_norm, c.eps, 0, nullptr, 1, 0, st, nullptr, b.xq2,
+                b.xs2))
+        return 1;
     if (qgemm_dev(A.wq_b, nullptr, b.xq2, b.xs2, B, b.q, true, 0.f, st)) return 1;
     if (row_ops(b.q, d, b.q, d, B * h, d, ROW_RMS_PLAIN | ROW_ROPE, nullptr, c.eps, rd, cs1, h, rd, st)) return 1;
     // the draft rows' own KV: after the ring in the candidate list, never written into it

@@ -694,7 +694,7 @@ template <bool BF16, int HG>
 __global__ void __launch_bounds__(256)
 sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den, int h, int d,
                       const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw, const void *kv_a, int64_t na,
-                      const void *kv_b, float *__restrict__ o, size_t a_stride, size_t b_stride, int seq_mod) {
+                      const void *kv_b, float *__restrict__ o, size_t a_stride, size_t b_stride, int seq_mod, const SaRope rope) {
     APUS_PDL_WAIT();
     APUS_PDL_GO();
     __shared__ __align__(16) float s_p[PV_JC][HG];
@@ -750,14 +750,28 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
             }
         }
         if (on) {
+            // a thread holds one (even, odd) pair of every head row: the pairs of the rotated tail are
+            // turned back here (the operations of the row kernel, c/attn.h:290-299 with -sin)
+            const int ri = rope.cs ? k2 - (d - rope.rd) / 2 : -1;
+            float co = 1.f, si = 0.f;
+            if (ri >= 0) {
+                const float *c = rope.cs + (rope.pos ? (size_t)*rope.pos * rope.rd : 0);
+                co = c[ri]; si = -c[rope.rd / 2 + ri];
+            }
 #pragma unroll
             for (int a = 0; a < HG; a++) {
                 if (h0 + a >= h) continue;
                 float *ov = o + ((size_t)t * h + h0 + a) * d;
                 if (n == 0) { ov[2 * k2] = 0.f; ov[2 * k2 + 1] = 0.f; continue; }
                 const float dn = den[(size_t)t * h + h0 + a];
-                ov[2 * k2] = bf16_round(__fdiv_rn(a0[a], dn));
-                ov[2 * k2 + 1] = bf16_round(__fdiv_rn(a1[a], dn));
+                float x1 = bf16_round(__fdiv_rn(a0[a], dn)), x2 = bf16_round(__fdiv_rn(a1[a], dn));
+                if (ri >= 0) {
+                    const float y1 = bf16_round(__fsub_rn(__fmul_rn(x1, co), __fmul_rn(x2, si)));
+                    const float y2 = bf16_round(__fadd_rn(__fmul_rn(x1, si), __fmul_rn(x2, co)));
+                    x1 = y1; x2 = y2;
+                }
+                ov[2 * k2] = x1;
+                ov[2 * k2 + 1] = x2;
             }
         }
     }
@@ -819,7 +833,7 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
                 const int32_t *idxs, int idxw, int s, float scale,
                 const void *kv_a, int64_t na, const void *kv_b, int64_t nb,
                 int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride, long long kv_b_stride,
-                void *callers, size_t callers_cap, int seq_mod) {
+                void *callers, size_t callers_cap, int seq_mod, bool ids_ready, const SaRope *rope) {
     (void)nb;
     const size_t esz = kv_bf16 ? 2 : 4;
     const size_t sa = (size_t)kv_a_stride * esz, sb = (size_t)kv_b_stride * esz;
@@ -838,8 +852,12 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
     int32_t *ids = (int32_t *)((char *)scratch + sc_bytes);
     int *ns = (int *)((char *)scratch + ns_off);
     float *den = (float *)((char *)scratch + den_off);
-    launch_k(compact_ids_kernel, s, 256, 0, st, idxs, idxw, ids, ns);
-    APUS_LAUNCHED();
+    APUS_REQUIRE(!ids_ready || callers, "sparse_attn: compacted ids need the caller's scratch");
+    if (!ids_ready) {
+        launch_k(compact_ids_kernel, s, 256, 0, st, idxs, idxw, ids, ns);
+        APUS_LAUNCHED();
+    }
+    const SaRope no_rope = {nullptr, nullptr, 0};
     static const int tiled = [] { const char *e = getenv("APUS_ATTN_TILED"); return !(e && e[0] == '0'); }();
     if (tiled && d % 64 == 0) {
         // register-tiled kernels: enough CTAs to cover the SMs decide the tile sizes
@@ -867,10 +885,10 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
             APUS_LAUNCHED();                                                                                            \
             if (hgs == 16)                                                                                              \
                 launch_k(sparse_pv_tile_kernel<BF, 16>, dim3((unsigned)ceil_div(h, 16), (unsigned)s), 256, 0, st,             \
-                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);                                  \
+                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
             else                                                                                                        \
                 launch_k(sparse_pv_tile_kernel<BF, 4>, dim3((unsigned)ceil_div(h, 4), (unsigned)s), 256, 0, st,               \
-                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);                                  \
+                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
             APUS_LAUNCHED();                                                                                            \
         } while (0)
         if (kv_bf16) APUS_SA_LAUNCH(true); else APUS_SA_LAUNCH(false);
@@ -898,6 +916,21 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         launch_k(sparse_pv_kernel<false>, g2, 256, sm2, st, sc, sink, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod);
         APUS_LAUNCHED();
     }
+    if (rope && rope->cs) {                           // these kernels do not rotate: the row kernel does
+        const RowDyn dyn = {rope->pos, 0, 0, 0};
+        return row_ops(o, d, o, d, s * h, d, ROW_ROPE_INV, nullptr, 0.f, rope->rd, rope->cs, s * h, 0, st, rope->pos ? &dyn : nullptr);
+    }
+    return 0;
+}
+
+int sparse_attn_compact(const int32_t *idxs, int h, int idxw, int s, void *scratch, size_t scratch_cap, cudaStream_t st) {
+    if (s <= 0 || idxw <= 0) return 0;
+    APUS_REQUIRE(scratch && sparse_attn_scratch(h, idxw, s) <= scratch_cap, "sparse_attn_compact: scratch of %zu bytes given, %zu needed",
+                 scratch_cap, sparse_attn_scratch(h, idxw, s));
+    const size_t sc_bytes = (size_t)s * h * idxw * sizeof(float), ids_bytes = (size_t)s * idxw * sizeof(int32_t);
+    const size_t ns_off = (sc_bytes + ids_bytes + 255) & ~(size_t)255;
+    launch_k(compact_ids_kernel, s, 256, 0, st, idxs, idxw, (int32_t *)((char *)scratch + sc_bytes), (int *)((char *)scratch + ns_off));
+    APUS_LAUNCHED();
     return 0;
 }
 

@@ -64,7 +64,8 @@ int attn_step_bufs(const ApusAttnCfg &c, long long max_nb, int B, DevBuf *ws, St
 // every position, and the entry counts S.*.nb are left to the caller.
 int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, const float *cs_pos,
               const float *cs_rp, float *out, const StepBufs &b, int *idx_k_out, cudaStream_t st,
-              const long long *pos_dev = nullptr, const float *cs_table = nullptr);
+              const long long *pos_dev = nullptr, const float *cs_table = nullptr,
+              bool x_codes = false);    // b.xq / b.xs already hold the activation codes of x
 
 // A chunk of s consecutive positions of the B sequences in one pass (batched prefill, the
 // s > 1 calls of reference c/attn.h:1514-1740): x, out [s * B, dim] with time-major rows

@@ -30,7 +30,8 @@ __device__ __forceinline__ float fp4_qat_value(float y) {
 __global__ void __launch_bounds__(1024)
 row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y, int y_stride, int n,
                int flags, const float *__restrict__ norm_w, float eps, int rd,
-               const float *__restrict__ cs, int rows_per_cs, int cs_stride, const RowDyn dyn) {
+               const float *__restrict__ cs, int rows_per_cs, int cs_stride, const RowDyn dyn,
+               uint8_t *__restrict__ q_codes, float *__restrict__ q_scales) {
     APUS_PDL_WAIT();
     APUS_PDL_GO();
     if (dyn.pos) {                             // position read on the device (see RowDyn)
@@ -124,6 +125,23 @@ row_ops_kernel(const float *__restrict__ x, int x_stride, float *__restrict__ y,
     }
     if (flags & ROW_BF16_OUT) v = bf16_round(v);
     if (on) y[(size_t)row * y_stride + i] = v;
+    if (q_codes) {
+        // activation codes of the finished row (the arithmetic of act_quant_kernel): a 128-group is four warps
+        const float vb = bf16_round(v);
+        const float m = warp_max(on ? fabsf(vb) : 0.f);
+        __syncthreads();
+        if ((i & 31) == 0) s_red[i >> 5] = m;
+        __syncthreads();
+        if (on) {
+            const int g = i >> 7;
+            float amax = fmaxf(fmaxf(s_red[4 * g], s_red[4 * g + 1]), fmaxf(s_red[4 * g + 2], s_red[4 * g + 3]));
+            amax = fmaxf(amax, 1e-4f);
+            const float s = ceil_pow2(__fmul_rn(amax, 1.0f / 448.0f));
+            const float inv = __uint_as_float(0x7f000000u - __float_as_uint(s));
+            q_codes[(size_t)row * n + i] = (uint8_t)(e4m3x2_from_f32(vb * inv, 0.f) & 0xffu);
+            if ((i & 127) == 0) q_scales[(size_t)row * (n >> 7) + g] = s;
+        }
+    }
 }
 
 // Two frequent shapes of the row pipeline on MANY rows (every head of every sequence) get kernels
@@ -218,8 +236,9 @@ qnorm_rope_rows_kernel(const float *__restrict__ x, int x_stride, float *__restr
 
 int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
             const float *norm_w, float eps, int rd, const float *cs, int rows_per_cs, int cs_stride,
-            cudaStream_t st, const RowDyn *dyn) {
+            cudaStream_t st, const RowDyn *dyn, uint8_t *q_codes, float *q_scales) {
     APUS_REQUIRE(n >= 32 && n <= 1024 && n % 32 == 0, "row_ops: n=%d unsupported", n);
+    APUS_REQUIRE(!q_codes || (n % 128 == 0 && q_scales && (!dyn || dyn->gate_ratio == 0)), "row_ops: codes need n %% 128 == 0 (n=%d)", n);
     APUS_REQUIRE(!(flags & ROW_HADAMARD) || (n & (n - 1)) == 0, "row_ops: Hadamard needs a power of two, n=%d", n);
     if (rows <= 0) return 0;
     size_t smem = (size_t)(n + 64) * sizeof(float);
@@ -227,7 +246,7 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
     const RowDyn none = {nullptr, 0, 0, 0};
     const bool no_gate = !dyn || dyn->gate_ratio == 0;
     const int base = flags & ~ROW_SEQ_SUM;
-    if (rows >= 32 && no_gate && cs && rd % 4 == 0 && rd <= n && (base == ROW_ROPE || base == ROW_ROPE_INV) && x == y &&
+    if (!q_codes && rows >= 32 && no_gate && cs && rd % 4 == 0 && rd <= n && (base == ROW_ROPE || base == ROW_ROPE_INV) && x == y &&
         x_stride == y_stride && x_stride % 2 == 0 && (n - rd) % 2 == 0) {
         const long long pairs = (long long)rows * (rd / 2);
         launch_k(rope_rows_kernel, (unsigned)((pairs + 255) / 256), 256, 0, st, y, y_stride, n, rows, base == ROW_ROPE_INV, rd, cs,
@@ -236,7 +255,7 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
         APUS_LAUNCHED();
         return 0;
     }
-    if (rows >= 32 && no_gate && cs && base == (ROW_RMS_PLAIN | ROW_ROPE) && (n == 512 || n == 256 || n == 128) &&
+    if (!q_codes && rows >= 32 && no_gate && cs && base == (ROW_RMS_PLAIN | ROW_ROPE) && (n == 512 || n == 256 || n == 128) &&
         rd % 4 == 0 && rd <= n && x_stride % 4 == 0 && y_stride % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0) {
         const unsigned g = (unsigned)((rows + 7) / 8);
         const int seq = (flags & ROW_SEQ_SUM) ? 1 : 0, rpc = rows_per_cs > 0 ? rows_per_cs : 1;
@@ -248,7 +267,7 @@ int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int 
         return 0;
     }
     launch_k(row_ops_kernel, rows, n, smem, st, x, x_stride, y, y_stride, n, flags, norm_w, eps, rd, cs,
-                                          rows_per_cs > 0 ? rows_per_cs : 1, cs_stride, dyn ? *dyn : none);
+                                          rows_per_cs > 0 ? rows_per_cs : 1, cs_stride, dyn ? *dyn : none, q_codes, q_scales);
     APUS_LAUNCHED();
     return 0;
 }

@@ -183,8 +183,20 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
                 int kv_bf16, float *o, cudaStream_t st, long long kv_a_stride = 0,
                 long long kv_b_stride = 0,    // strides (elements) between the tokens' own caches; 0 = shared
                 void *scratch = nullptr, size_t scratch_cap = 0,    // caller's scratch (sparse_attn_scratch bytes) or the shared one
-                int seq_mod = 0);    // > 0: token t reads the caches of sequence t % seq_mod (time-major rows of a chunk)
+                int seq_mod = 0,     // > 0: token t reads the caches of sequence t % seq_mod (time-major rows of a chunk)
+                bool ids_ready = false,              // sparse_attn_compact has run on this scratch with these index rows
+                const struct SaRope *rope = nullptr);   // rotate the output rows back before they are written
 size_t sparse_attn_scratch(int h, int idxw, int s);
+// The first launch of sparse_attn (negative ids dropped, order kept) on its own: a caller that has the
+// index rows before the queries (a side chain) runs it there, into the scratch it then hands to sparse_attn.
+int sparse_attn_compact(const int32_t *idxs, int h, int idxw, int s, void *scratch, size_t scratch_cap, cudaStream_t st);
+// Inverse RoPE of the output rows (reference c/attn.h:1384-1388), applied by the kernel that writes them:
+// the last rd elements of every head row, cos/sin row `cs` (or, pos != NULL, row *pos of the table `cs`).
+struct SaRope {
+    const float *cs;
+    const long long *pos;
+    int rd;
+};
 
 // ---- attention row helpers, compressor and indexer steps (attn_ops.cu) -----------------------
 enum {
@@ -211,7 +223,9 @@ struct RowDyn {
 };
 int row_ops(const float *x, int x_stride, float *y, int y_stride, int rows, int n, int flags,
             const float *norm_w, float eps, int rd, const float *cs, int rows_per_cs, int cs_stride,
-            cudaStream_t st, const RowDyn *dyn = nullptr);
+            cudaStream_t st, const RowDyn *dyn = nullptr, uint8_t *q_codes = nullptr, float *q_scales = nullptr);
+// q_codes != NULL (n % 128 == 0): the finished rows are also written as the E4M3 codes [rows, n] and the
+// per-128 scales [rows, n / 128] that act_quant would make of y -- the same arithmetic, one launch less.
 int comp_step(float *kv_state, float *sc_state, long long state_stride, const float *kv_new,
               const float *sc_new, int new_stride, const float *ape, int ratio, int overlap, int d,
               int slot, int should, float *pooled, int pooled_stride, int n_seq, cudaStream_t st,
@@ -257,7 +271,11 @@ int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
             const float *base, float norm_eps, float hc_eps, int iters,
             const float *norm_w, float rms_eps, float *pre, float *post,
             float *comb, float *y, float *y_normed, int rows, cudaStream_t st,
-            float *raw = nullptr);            // caller's scratch of rows * ((2+n)*n + 1) floats, or the shared one
+            float *raw = nullptr,             // caller's scratch of rows * ((2+n)*n + 1) floats, or the shared one
+            uint8_t *xq = nullptr, float *xs = nullptr, int *codes_written = nullptr);
+// xq != NULL: where the row layout allows it, the kernel that writes y_normed also writes its activation
+// codes [rows, d] and per-128 scales [rows, d / 128] (what act_quant makes of y_normed) and
+// *codes_written is set to 1; otherwise it is set to 0 and the caller quantises.
 int mhc_post(const float *f, const float *res4, const float *post,
              const float *comb, float *y4, int d, int n, int rows,
              cudaStream_t st);

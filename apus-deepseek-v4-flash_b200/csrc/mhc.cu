@@ -325,12 +325,44 @@ mhc_pre_finish_kernel(const float *__restrict__ x4, const float *__restrict__ ra
     }
 }
 
+// post gates and the Sinkhorn-normalised comb matrix of one token (reference c/mhc.h:181-234), one warp.
+__device__ __forceinline__ void mhc_gates_warp(const float *__restrict__ rw, float r, int n, const float *__restrict__ scale,
+                                               const float *__restrict__ base, float hc_eps, int iters, size_t row,
+                                               float *__restrict__ post_out, float *__restrict__ comb_out, int tid) {
+    const int l = tid & 31;
+    if (l < n) {
+        const float m2 = __fmul_rn(rw[n + l], r);
+        const float po = __fmul_rn(2.0f, sigm(__fadd_rn(__fmul_rn(m2, scale[1]), base[n + l])));
+        if (post_out) post_out[(size_t)row * n + l] = po;
+    }
+    const bool on = l < n * n;
+    const int j = on ? l / n : 0, k = on ? l - j * n : 0;
+    float c = on ? __fadd_rn(__fmul_rn(__fmul_rn(rw[2 * n + l], r), scale[2]), base[2 * n + l]) : 0.f;
+    float mx = __shfl_sync(0xffffffffu, c, j * n);
+    for (int q = 1; q < n; q++) mx = fmaxf(mx, __shfl_sync(0xffffffffu, c, j * n + q));
+    c = exp_rn(c - mx);
+    float sum = 0.f;
+    for (int q = 0; q < n; q++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, c, j * n + q));
+    c = __fadd_rn(__fdiv_rn(c, sum), hc_eps);
+    for (int it = 0; it < iters; it++) {
+        if (it) {
+            float s2 = 0.f;
+            for (int q = 0; q < n; q++) s2 = __fadd_rn(s2, __shfl_sync(0xffffffffu, c, j * n + q));
+            c = __fdiv_rn(c, __fadd_rn(s2, hc_eps));
+        }
+        float s3 = 0.f;
+        for (int q = 0; q < n; q++) s3 = __fadd_rn(s3, __shfl_sync(0xffffffffu, c, q * n + k));
+        c = __fdiv_rn(c, __fadd_rn(s3, hc_eps));
+    }
+    if (on && comb_out) comb_out[(size_t)row * n * n + l] = c;
+}
+
 // The same step with a token spread over a cluster of MHC_CL CTAs: one CTA walking a
 // 4 x 4096 state alone takes ~30 us, most of it latency (gates -> 64 KB of loads through one
 // SM -> sum of squares -> second pass), and at small batches that chain sits twice in every
 // layer.  Here every CTA of the cluster collapses its slice of the row and each CTA normalises
 // its own slice; the Sinkhorn part, which nothing in this kernel waits for, runs on one warp
-// of the last CTA afterwards.  The sum of squares of the norm meets through distributed shared
+// of the last CTA while rank 0 walks the sum of squares (after the row is out when the sum is a tree).  The sum of squares of the norm meets through distributed shared
 // memory: in tree order the slices' sums are added in rank order (the same total in every
 // CTA); in the reference's order (seq) every CTA stores its squares into rank 0's shared
 // memory and one lane there adds all d of them in index order -- the reference's chain, about
@@ -343,7 +375,9 @@ mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__
                          int head_mode, const float *__restrict__ norm_w, float rms_eps,
                          float *__restrict__ pre_out, float *__restrict__ post_out,
                          float *__restrict__ comb_out, float *__restrict__ y,
-                         float *__restrict__ y_normed, int seq) {
+                         float *__restrict__ y_normed, int seq, uint8_t *__restrict__ xq, float *__restrict__ xs) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(16) float s_sq[];   // seq: the d squares of the collapsed row (rank 0's copy is used)
@@ -392,11 +426,17 @@ mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__
             }
         }
     }
+    // The gates are needed only by the post step, far downstream: one warp of the last rank works them
+    // out (a few microseconds of dependent shuffles and divisions) while rank 0 walks the sum of
+    // squares, instead of after the normalised row is out, where the next kernel would wait for them.
+    const bool gates_warp = !head_mode && rank == MHC_CL - 1 && (tid >> 5) == 1;
+    bool gates_done = false;
     if (y && y_normed) {
         float tot = 0.f;
         if (seq) {
             cluster.sync();                        // every slice's squares have landed in rank 0
             if (rank == 0 && tid == 0) s_part = seq_sum_smem(s_sq, d, 0.f);
+            if (gates_warp) { mhc_gates_warp(rw, r, n, scale, base, hc_eps, iters, (size_t)row, post_out, comb_out, tid); gates_done = true; }
             cluster.sync();
             tot = *cluster.map_shared_rank(&s_part, 0);
         } else {
@@ -414,36 +454,21 @@ mhc_pre_finish_cl_kernel(const float *__restrict__ x4, const float *__restrict__
             o.x = bf16_round(__fmul_rn(w.x, __fmul_rn(v.x, inv))); o.y = bf16_round(__fmul_rn(w.y, __fmul_rn(v.y, inv)));
             o.z = bf16_round(__fmul_rn(w.z, __fmul_rn(v.z, inv))); o.w = bf16_round(__fmul_rn(w.w, __fmul_rn(v.w, inv)));
             *reinterpret_cast<float4 *>(y_normed + (size_t)row * d + i) = o;
+            if (xq) {
+                // activation codes of the normalised row (the arithmetic of act_quant_kernel): the launcher
+                // passes xq only when every slice is a whole number of 128-groups, so a group is one warp
+                float amax = fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w)));
+                amax = fmaxf(warp_max(amax), 1e-4f);
+                const float s = ceil_pow2(__fmul_rn(amax, 1.0f / 448.0f));
+                const float iv = __uint_as_float(0x7f000000u - __float_as_uint(s));
+                const uint32_t lo = e4m3x2_from_f32(o.x * iv, o.y * iv), hi = e4m3x2_from_f32(o.z * iv, o.w * iv);
+                *reinterpret_cast<uint32_t *>(xq + (size_t)row * d + i) = lo | (hi << 16);
+                if ((tid & 31) == 0) xs[(size_t)row * (d >> 7) + (i >> 7)] = s;
+            }
         }
     }
-    if (head_mode || rank != MHC_CL - 1 || (tid >> 5) != 1) return;
-    // post gates and the Sinkhorn-normalised comb matrix (reference c/mhc.h:181-234), one warp
-    const int l = tid & 31;
-    if (l < n) {
-        const float m2 = __fmul_rn(rw[n + l], r);
-        const float po = __fmul_rn(2.0f, sigm(__fadd_rn(__fmul_rn(m2, scale[1]), base[n + l])));
-        if (post_out) post_out[(size_t)row * n + l] = po;
-    }
-    const bool on = l < n * n;
-    const int j = on ? l / n : 0, k = on ? l - j * n : 0;
-    float c = on ? __fadd_rn(__fmul_rn(__fmul_rn(rw[2 * n + l], r), scale[2]), base[2 * n + l]) : 0.f;
-    float mx = __shfl_sync(0xffffffffu, c, j * n);
-    for (int q = 1; q < n; q++) mx = fmaxf(mx, __shfl_sync(0xffffffffu, c, j * n + q));
-    c = exp_rn(c - mx);
-    float sum = 0.f;
-    for (int q = 0; q < n; q++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, c, j * n + q));
-    c = __fadd_rn(__fdiv_rn(c, sum), hc_eps);
-    for (int it = 0; it < iters; it++) {
-        if (it) {
-            float s2 = 0.f;
-            for (int q = 0; q < n; q++) s2 = __fadd_rn(s2, __shfl_sync(0xffffffffu, c, j * n + q));
-            c = __fdiv_rn(c, __fadd_rn(s2, hc_eps));
-        }
-        float s3 = 0.f;
-        for (int q = 0; q < n; q++) s3 = __fadd_rn(s3, __shfl_sync(0xffffffffu, c, q * n + k));
-        c = __fdiv_rn(c, __fadd_rn(s3, hc_eps));
-    }
-    if (on && comb_out) comb_out[(size_t)row * n * n + l] = c;
+    if (!gates_done && gates_warp)
+        mhc_gates_warp(rw, r, n, scale, base, hc_eps, iters, (size_t)row, post_out, comb_out, tid);
 }
 
 // Y[j,i] = bf16(post[j]*f[i] + sum_k comb[k,j]*R[k,i]) (reference c/mhc.h:259-270,
@@ -525,11 +550,16 @@ static inline size_t finish_smem(int d) { return finish_seq() ? (size_t)d * size
 static int launch_finish(const float *x4, const float *raw, int d, int n, int nmix, const float *scale,
                          float head_scale, const float *base, float norm_eps, float hc_eps, int iters, int head_mode,
                          const float *norm_w, float rms_eps, float *pre, float *post, float *comb, float *y,
-                         float *y_normed, int rows, cudaStream_t st) {
+                         float *y_normed, int rows, cudaStream_t st, uint8_t *xq = nullptr, float *xs = nullptr,
+                         int *codes_written = nullptr) {
+    if (codes_written) *codes_written = 0;
     if (d % 4 == 0 && n * n <= 32 && y && (size_t)d * sizeof(float) <= 48 * 1024) {
-        mhc_pre_finish_cl_kernel<<<rows * MHC_CL, 128, finish_smem(d), st>>>(x4, raw, d, n, nmix, scale, head_scale, base,
-                                                                            norm_eps, hc_eps, iters, head_mode, norm_w,
-                                                                            rms_eps, pre, post, comb, y, y_normed, finish_seq());
+        // codes beside the normalised row when a CTA's slice (d / MHC_CL) is a whole number of 128-groups
+        const bool codes = xq && xs && y_normed && d % (MHC_CL * 128) == 0;
+        launch_k(mhc_pre_finish_cl_kernel, rows * MHC_CL, 128, finish_smem(d), st, x4, raw, d, n, nmix, scale, head_scale, base,
+                 norm_eps, hc_eps, iters, head_mode, norm_w, rms_eps, pre, post, comb, y, y_normed, finish_seq(),
+                 codes ? xq : (uint8_t *)nullptr, codes ? xs : (float *)nullptr);
+        if (codes && codes_written) *codes_written = 1;
     } else {
         launch_k(mhc_pre_finish_kernel, rows, 256, finish_smem(d), st, x4, raw, d, n, nmix, scale, head_scale, base, norm_eps,
                                                                  hc_eps, iters, head_mode, norm_w, rms_eps, pre, post,
@@ -542,7 +572,9 @@ static int launch_finish(const float *x4, const float *raw, int d, int n, int nm
 int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
             const float *base, float norm_eps, float hc_eps, int iters,
             const float *norm_w, float rms_eps, float *pre, float *post,
-            float *comb, float *y, float *y_normed, int rows, cudaStream_t st, float *raw_in) {
+            float *comb, float *y, float *y_normed, int rows, cudaStream_t st, float *raw_in, uint8_t *xq, float *xs,
+            int *codes_written) {
+    if (codes_written) *codes_written = 0;
     APUS_REQUIRE(n >= 1 && n <= MHC_MAX_N && (n * d) % 4 == 0, "mhc: n=%d d=%d unsupported", n, d);
     if (rows <= 0) return 0;
     int nmix = (2 + n) * n;
@@ -550,7 +582,7 @@ int mhc_pre(const float *x4, int d, int n, const float *fn, const float *scale,
     if (!raw) return 1;
     if (launch_mix(x4, fn, n * d, nmix, raw, rows, st)) return 1;
     return launch_finish(x4, raw, d, n, nmix, scale, 0.f, base, norm_eps, hc_eps, iters, 0, norm_w, rms_eps, pre, post,
-                         comb, y, norm_w ? y_normed : nullptr, rows, st);
+                         comb, y, norm_w ? y_normed : nullptr, rows, st, xq, xs, codes_written);
 }
 
 int mhc_head(const float *x4, int d, int n, const float *fn, float scale,

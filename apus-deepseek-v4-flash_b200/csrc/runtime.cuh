@@ -58,7 +58,7 @@ struct Ctx {
     cudaStream_t own_stream = nullptr;      // the one the library created (stream may be the caller's)
     // side streams for independent kernel chains inside a step (joined back before
     // the step goes on); each has an event for the fork and one for the join
-    static const int N_AUX = 4;
+    static const int N_AUX = 5;
     cudaStream_t aux[N_AUX] = {};
     cudaEvent_t ev_fork[N_AUX] = {}, ev_join[N_AUX] = {};
     uint64_t bytes_uploaded = 0;
