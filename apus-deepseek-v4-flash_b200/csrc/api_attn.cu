@@ -300,9 +300,11 @@ int attn_step(const AttnDev &A, StateDev &S, const float *x, long long pos, cons
         return 1;
     // grouped low-rank o-projection (c/attn.h:1692-1737)
     const int G = c.o_groups, ol = c.o_lora, sub = hd / G;
+    LinCodes yq = {b.xq, b.xs, 0};                    // the codes of y for wo_b, from the kernel that finishes y when it can
     if (f32_linear_batched(A.wo_a, (long long)ol * sub, b.o, sub, hd, b.y, ol, G * ol, G, B, sub, ol,
-                           APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_WO_A), st))
+                           APUS_CUDA_W_BF16 | APUS_CUDA_R_OUT | APUS_LIN_CLASS(APUS_CUDA_TREE_WO_A), st, &yq))
         return 1;
+    if (yq.written) return qgemm_dev(A.wo_b, nullptr, b.xq, b.xs, B, out, true, 0.f, st);
     return qlinear_dev(A.wo_b, b.y, out, B, b.xq, b.xs, true, st);
 }
 

@@ -55,6 +55,7 @@ gemm_tcbf_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     APUS_PDL_WAIT();
     APUS_PDL_GO();
     extern __shared__ uint8_t smem_raw[];
+    __shared__ float s_amax[4][TB_N];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)NS * TB_STAGE);
     uint64_t *full = bars, *empty = bars + NS, *acc_full = bars + 2 * NS;
@@ -166,11 +167,41 @@ gemm_tcbf_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         if (*s_last && tid < 128) {
             const int o = tile * 128 + tid;
             const size_t col = (size_t)g * a.O + o, ncol = (size_t)a.batch * a.O;
-            for (int n = 0; n < nrows; n++) {
-                float v = 0.f;
-                for (int c = 0; c < S; c++)
-                    v = __fadd_rn(v, __ldcg(a.part + ((size_t)c * a.M + row0 + n) * ncol + col));
-                a.out[(size_t)(row0 + n) * a.out_ld + col] = a.round_out ? bf16_round(v) : v;
+            if (!a.q_out) {
+                for (int n = 0; n < nrows; n++) {
+                    float v = 0.f;
+                    for (int c = 0; c < S; c++)
+                        v = __fadd_rn(v, __ldcg(a.part + ((size_t)c * a.M + row0 + n) * ncol + col));
+                    a.out[(size_t)(row0 + n) * a.out_ld + col] = a.round_out ? bf16_round(v) : v;
+                }
+            } else {
+                // The finished tile holds 128 consecutive outputs of every row: one group of the activation
+                // quantisation of the projection that reads them next (c/fp4.h:293-321).  Codes and scales
+                // are made here -- amax over the four warps, power-of-two scale, hardware E4M3 conversion:
+                // the arithmetic of act_quant_kernel -- instead of by a launch of their own.
+                float vb[TB_N];
+#pragma unroll
+                for (int n = 0; n < TB_N; n++) {
+                    if (n >= nrows) break;
+                    float v = 0.f;
+                    for (int c = 0; c < S; c++)
+                        v = __fadd_rn(v, __ldcg(a.part + ((size_t)c * a.M + row0 + n) * ncol + col));
+                    v = a.round_out ? bf16_round(v) : v;
+                    a.out[(size_t)(row0 + n) * a.out_ld + col] = v;
+                    vb[n] = bf16_round(v);
+                    const float m = warp_max(fabsf(vb[n]));
+                    if ((tid & 31) == 0) s_amax[tid >> 5][n] = m;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+                for (int n = 0; n < TB_N; n++) {
+                    if (n >= nrows) break;
+                    const float amax = fmaxf(fmaxf(fmaxf(s_amax[0][n], s_amax[1][n]), fmaxf(s_amax[2][n], s_amax[3][n])), 1e-4f);
+                    const float sc = ceil_pow2(__fmul_rn(amax, 1.0f / 448.0f));
+                    const float inv = __uint_as_float(0x7f000000u - __float_as_uint(sc));
+                    a.q_out[(size_t)(row0 + n) * a.out_ld + col] = (uint8_t)(e4m3x2_from_f32(vb[n] * inv, 0.f) & 0xffu);
+                    if (tid == 0) a.qs_out[((size_t)(row0 + n) * a.out_ld + col) >> 7] = sc;
+                }
             }
         }
     }
@@ -245,6 +276,7 @@ int gemm_tcbf(const TcbfArgs &a, cudaStream_t st) {
     if (a.M <= 0) return 0;
     const int S = a.ksplit < 1 ? 1 : a.ksplit;
     APUS_REQUIRE(S == 1 || (a.part && a.counters), "gemm_tcbf: a K split needs the scratch buffers");
+    APUS_REQUIRE(!a.q_out || (S > 1 && a.qs_out && a.out_ld % 128 == 0), "gemm_tcbf: codes are written by the K-split finish only");
     dim3 grid((unsigned)((a.O / 128) * a.batch), (unsigned)((a.M + TB_N - 1) / TB_N), (unsigned)S);
     const long long ctas = (long long)grid.x * grid.y * grid.z;
     const CUtensorMap *mw = reinterpret_cast<const CUtensorMap *>(a.map_w), *mx = reinterpret_cast<const CUtensorMap *>(a.map_x);

@@ -117,6 +117,8 @@ struct TcbfArgs {
     int ksplit;                          // K chunks (tcbf_ksplit); > 1 needs part + counters
     float *part;                         // [ksplit, M, batch*O] scratch
     int *counters;                       // zeroed, one per (output tile, row group); left zeroed
+    uint8_t *q_out;                      // ksplit > 1, out_ld % 128 == 0: also the E4M3 activation codes [M, out_ld] ...
+    float *qs_out;                       // ... and per-128 scales [M, out_ld / 128] of the finished rows (act_quant's)
 };
 int gemm_tcbf(const TcbfArgs &a, cudaStream_t st);
 int gemm_tcbf_status(int reset);
@@ -139,9 +141,16 @@ int f32_linear(const void *w, const float *x, float *out, int M, int K, int O,
                int flags, cudaStream_t st);
 // `batch` independent problems: problem b uses w + b*w_stride (elements of w's
 // type), x + b*x_stride with rows x_ld apart, out + b*out_stride with rows out_ld apart.
+// codes != NULL: a kernel that can also writes the activation codes and per-128 scales of the output rows
+// ([M, out_ld] seen as one row per token, what act_quant would make of them) and sets codes->written.
+struct LinCodes {
+    uint8_t *q;
+    float *s;
+    int written;
+};
 int f32_linear_batched(const void *w, long long w_stride, const float *x, long long x_stride, int x_ld,
                        float *out, long long out_stride, int out_ld, int batch, int M, int K, int O,
-                       int flags, cudaStream_t st);
+                       int flags, cudaStream_t st, LinCodes *codes = nullptr);
 
 // ---- MoE glue (moe.cu) ---------------------------------------------------------------------
 // sqrtsoftplus of gate logits, bias, stable top-k or hash lookup, weights.

@@ -450,7 +450,7 @@ static void launch_linear(const void *w, long long ws, const float *x, long long
 // copied as BF16 (exact for BF16-valued rows; APUS_CUDA_R_IN asks for that rounding anyway) into
 // the stream's scratch, which also holds the K-split partial sums.
 static int linear_tcbf(const void *w, const float *x, int x_koff, int x_ld, float *out, int out_ld, int batch, int M,
-                       int K, int O, int flags, cudaStream_t st) {
+                       int K, int O, int flags, cudaStream_t st, LinCodes *codes) {
     const int S = tcbf_ksplit(O, K, batch, M);
     const size_t xb = (((size_t)M * x_ld * 2) + 255) & ~(size_t)255;
     const size_t pb = S > 1 ? (size_t)S * M * batch * O * 4 : 0;
@@ -467,12 +467,14 @@ static int linear_tcbf(const void *w, const float *x, int x_koff, int x_ld, floa
     a.M = M; a.O = O; a.K = K; a.batch = batch; a.x_koff = x_koff;
     a.out_ld = out_ld; a.round_out = (flags & APUS_CUDA_R_OUT) ? 1 : 0; a.out = out;
     a.ksplit = S; a.part = (float *)((char *)ws + xb); a.counters = cnt;
+    if (codes && S > 1 && out_ld % 128 == 0 && out_ld == batch * O) { a.q_out = codes->q; a.qs_out = codes->s; codes->written = 1; }
     return gemm_tcbf(a, st);
 }
 
 int f32_linear_batched(const void *w, long long w_stride, const float *x, long long x_stride, int x_ld,
                        float *out, long long out_stride, int out_ld, int batch, int M, int K, int O,
-                       int flags, cudaStream_t st) {
+                       int flags, cudaStream_t st, LinCodes *codes) {
+    if (codes) codes->written = 0;
     APUS_REQUIRE(K % 4 == 0 && x_ld % 4 == 0 && x_stride % 4 == 0 && w_stride % 4 == 0,
                  "f32_linear: K=%d and the strides must be multiples of 4", K);
     if (M <= 0 || O <= 0 || batch <= 0) return 0;
@@ -482,7 +484,7 @@ int f32_linear_batched(const void *w, long long w_stride, const float *x, long l
     // BF16 weights in tree order: the tensor-core kernel, when the problems are laid out as it reads them
     if (tree && (flags & APUS_CUDA_W_BF16) && O % 128 == 0 && K % 64 == 0 && x_ld % 8 == 0 && ((uintptr_t)w & 15) == 0 &&
         (batch == 1 || (w_stride == (long long)O * K && out_stride == O)) && x_stride * (long long)(batch - 1) + K <= x_ld)
-        return linear_tcbf(w, x, (int)x_stride, x_ld, out, out_ld, batch, M, K, O, flags, st);
+        return linear_tcbf(w, x, (int)x_stride, x_ld, out, out_ld, batch, M, K, O, flags, st, codes);
     if (!tree) {
         APUS_REQUIRE(K % 8 == 0 && (w_stride * ((flags & APUS_CUDA_W_BF16) ? 2 : 4)) % 16 == 0,
                      "f32_linear: K=%d must be a multiple of 8", K);
