@@ -492,13 +492,14 @@ __device__ __forceinline__ void cp_async16(void *dst, const void *src, bool vali
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz) : "memory");
 }
 
-// Scores.  A warp owns 16 heads x 32 candidates; lane = (hg, jg) owns heads 4hg..4hg+3 and candidates
-// jg, jg+8, jg+16, jg+24.  The warp's 32 gathered rows are staged 128 bytes of k at a time in their
+// Scores.  A warp owns 16 heads x 8 NB candidates; lane = (hg, jg) owns heads 4hg..4hg+3 and candidates
+// jg, jg+8, ... (NB of them: 4 where the launch fills the GPU anyway; 1 for the few rows of a small step,
+// whose duration is one warp's instruction stream -- a quarter of it per warp and four times the warps).  The warp's 32 gathered rows are staged 128 bytes of k at a time in their
 // natural layout by 16-byte cp.async (two buffers: the next chunk is in flight while this one is
 // consumed); with a pitch of 36 words the eight rows the lanes of a load touch fall into different
 // banks.  The q chunk is shared by the CTA's warps, transposed ([k][16 heads]: one 16-byte load gives
 // a lane its four heads).  Per k a lane issues 5 shared loads for 16 multiply/add pairs.
-template <bool BF16, int W>
+template <bool BF16, int W, int NB>
 __global__ void __launch_bounds__(32 * W)
 sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32_t *__restrict__ ids,
                           const int *__restrict__ ns, int idxw, float scale, const void *kv_a, int64_t na,
@@ -508,20 +509,21 @@ sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32
     constexpr int KC = BF16 ? 64 : 32;                         // k values per chunk
     extern __shared__ __align__(16) unsigned char ss_raw[];
     float (*s_q)[KC][16] = reinterpret_cast<float (*)[KC][16]>(ss_raw);                       // [2][KC][16]
-    uint32_t (*s_kv)[2][32][SS_PITCHW] =
-        reinterpret_cast<uint32_t (*)[2][32][SS_PITCHW]>(ss_raw + 2 * KC * 16 * 4);           // [W][2][32][pitch]
+    constexpr int TJ = 8 * NB;                                  // candidates of a warp's tile
+    uint32_t (*s_kv)[2][TJ][SS_PITCHW] =
+        reinterpret_cast<uint32_t (*)[2][TJ][SS_PITCHW]>(ss_raw + 2 * KC * 16 * 4);           // [W][2][TJ][pitch]
     const int t = blockIdx.z, hb = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n = ns[t];
-    const int j0 = ((int)blockIdx.x * W + warp) * 32;          // first candidate of this warp's tile
-    if ((int)blockIdx.x * W * 32 >= n) return;                  // whole CTA past the row
+    const int j0 = ((int)blockIdx.x * W + warp) * TJ;          // first candidate of this warp's tile
+    if ((int)blockIdx.x * W * TJ >= n) return;                  // whole CTA past the row
     const int own = seq_mod > 0 ? t % seq_mod : t;
     const size_t esz = BF16 ? 2 : 4;
     // lane u-th copy of a chunk: row (lane + 32u) / 8, 16-byte segment (lane + 32u) % 8; the four rows a
     // lane copies from are fixed, so their base pointers stay in registers
-    const char *rowp[8];
+    const char *rowp[2 * NB];
     const char *dummy = reinterpret_cast<const char *>(kv_a ? kv_a : kv_b);
 #pragma unroll
-    for (int u = 0; u < 8; u++) {
+    for (int u = 0; u < 2 * NB; u++) {
         const int r = (lane + 32 * u) >> 3, j = j0 + r;
         const char *ptr = nullptr;
         if (j < n) {
@@ -555,18 +557,18 @@ sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32
     auto kv_stage = [&](int c, int buf) {
         if (live) {
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < 2 * NB; u++) {
                 const int i = lane + 32 * u, r = i >> 3, seg = i & 7;
                 cp_async16(&s_kv[warp][buf][r][seg * 4], rowp[u] ? rowp[u] + (size_t)c * SS_ROWB + seg * 16 : dummy, rowp[u] != nullptr);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    float acc[4][4];
+    float acc[4][NB];
 #pragma unroll
     for (int a = 0; a < 4; a++)
 #pragma unroll
-        for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
+        for (int b = 0; b < NB; b++) acc[a][b] = 0.f;
     kv_stage(0, 0);
     if (nchunk > 1) kv_stage(1, 1);
     q_load(0);
@@ -587,9 +589,9 @@ sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32
                     const float4 qa = *reinterpret_cast<const float4 *>(&s_q[buf][2 * k2][4 * hg]);
                     const float4 qb = *reinterpret_cast<const float4 *>(&s_q[buf][2 * k2 + 1][4 * hg]);
                     const float q0[4] = {qa.x, qa.y, qa.z, qa.w}, q1[4] = {qb.x, qb.y, qb.z, qb.w};
-                    float k0v[4], k1v[4];
+                    float k0v[NB], k1v[NB];
 #pragma unroll
-                    for (int b = 0; b < 4; b++) {
+                    for (int b = 0; b < NB; b++) {
                         const uint32_t w = s_kv[warp][buf][jg + 8 * b][k2];
                         k0v[b] = __uint_as_float(w << 16);
                         k1v[b] = __uint_as_float(w & 0xffff0000u);
@@ -597,24 +599,24 @@ sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32
 #pragma unroll
                     for (int a = 0; a < 4; a++)
 #pragma unroll
-                        for (int b = 0; b < 4; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(q0[a], k0v[b]));
+                        for (int b = 0; b < NB; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(q0[a], k0v[b]));
 #pragma unroll
                     for (int a = 0; a < 4; a++)
 #pragma unroll
-                        for (int b = 0; b < 4; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(q1[a], k1v[b]));
+                        for (int b = 0; b < NB; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(q1[a], k1v[b]));
                 }
             } else {
 #pragma unroll 8
                 for (int kk = 0; kk < KC; kk++) {
                     const float4 q4 = *reinterpret_cast<const float4 *>(&s_q[buf][kk][4 * hg]);
                     const float qa[4] = {q4.x, q4.y, q4.z, q4.w};
-                    float kb[4];
+                    float kb[NB];
 #pragma unroll
-                    for (int b = 0; b < 4; b++) kb[b] = __uint_as_float(s_kv[warp][buf][jg + 8 * b][kk]);
+                    for (int b = 0; b < NB; b++) kb[b] = __uint_as_float(s_kv[warp][buf][jg + 8 * b][kk]);
 #pragma unroll
                     for (int a = 0; a < 4; a++)
 #pragma unroll
-                        for (int b = 0; b < 4; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(qa[a], kb[b]));
+                        for (int b = 0; b < NB; b++) acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(qa[a], kb[b]));
                 }
             }
         }
@@ -628,7 +630,7 @@ sparse_scores_tile_kernel(const float *__restrict__ q, int h, int d, const int32
         const int head = hb * 16 + 4 * hg + a;
         if (head >= h) continue;
 #pragma unroll
-        for (int b = 0; b < 4; b++) {
+        for (int b = 0; b < NB; b++) {
             const int j = j0 + jg + 8 * b;
             if (j < n) sc[((size_t)t * h + head) * idxw + j] = __fmul_rn(acc[a][b], scale);
         }
@@ -705,7 +707,10 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
     kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride;
     const int n = ns[t];
     const int32_t *idr = ids + (size_t)t * idxw;
-    for (int c0 = 0; c0 < d / 2; c0 += 256) {
+    // gridDim.z CTAs share a (row, head group): each takes blockDim.x channel pairs of every 256 (a small step has
+    // few (row, head group)s, and one SM gathering all the rows alone is bound by what one SM can pull from L2)
+    const int nth = (int)blockDim.x;
+    for (int c0 = (int)blockIdx.z * nth; c0 < d / 2; c0 += nth * (int)gridDim.z) {
         const int k2 = c0 + tid;
         const bool on = k2 < d / 2;
         float a0[HG], a1[HG];
@@ -714,11 +719,11 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
         for (int j0 = 0; j0 < n; j0 += PV_JC) {
             const int cnt = min(PV_JC, n - j0);
             __syncthreads();
-            for (int i = tid; i < PV_JC * HG; i += 256) {
+            for (int i = tid; i < PV_JC * HG; i += nth) {
                 const int a = i / PV_JC, jj = i - a * PV_JC;
                 s_p[jj][a] = (jj < cnt && h0 + a < h) ? p[((size_t)t * h + h0 + a) * idxw + j0 + jj] : 0.f;
             }
-            for (int i = tid; i < cnt; i += 256) s_id[i] = idr[j0 + i];
+            for (int i = tid; i < cnt; i += nth) s_id[i] = idr[j0 + i];
             __syncthreads();
             if (on) {
                 // LB gathered rows in flight per thread: the rows come from L2 / HBM with nothing else to
@@ -867,17 +872,27 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         const int hgs = h >= 16 && (long long)s * ceil_div(h, 16) >= 96 ? 16 : 4;
         const size_t kc = kv_bf16 ? 64 : 32;
         const size_t ss8 = 2 * kc * 16 * 4 + 8 * (2 * 32 * SS_PITCHW * 4), ss2 = 2 * kc * 16 * 4 + 2 * (2 * 32 * SS_PITCHW * 4);
-        if (ensure_dyn_smem(kv_bf16 ? (const void *)sparse_scores_tile_kernel<true, 8> : (const void *)sparse_scores_tile_kernel<false, 8>, ss8))
+        const size_t ss1 = 2 * kc * 16 * 4 + 2 * (2 * 8 * SS_PITCHW * 4);
+        // a small step (few rows, few candidates): 8-candidate tiles, so that no warp walks more than a quarter
+        static const bool small_on = [] { const char *e = getenv("APUS_ATTN_SMALL"); return !(e && e[0] == '0'); }();
+        const bool narrow = small_on && (long long)ceil_div(idxw, 32) * ceil_div(h, 16) * s <= 296;
+        // ... and in P.V four CTAs of 64 channel pairs per (row, head group) instead of one of 256
+        const bool pv_split = small_on && d % 512 == 0 && (long long)s * ceil_div(h, 4) < 74;
+        if (ensure_dyn_smem(kv_bf16 ? (const void *)sparse_scores_tile_kernel<true, 8, 4> : (const void *)sparse_scores_tile_kernel<false, 8, 4>, ss8))
             return 1;
 #define APUS_SA_LAUNCH(BF)                                                                                              \
         do {                                                                                                            \
             if (wide >= 148) {                                                                                          \
                 dim3 g((unsigned)ceil_div(idxw, 256), (unsigned)ceil_div(h, 16), (unsigned)s);                          \
-                launch_k(sparse_scores_tile_kernel<BF, 8>, g, 256, ss8, st, q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,  \
+                launch_k(sparse_scores_tile_kernel<BF, 8, 4>, g, 256, ss8, st, q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,  \
                                                                    sa, sb, seq_mod);                                    \
+            } else if (narrow) {                                                                                        \
+                dim3 g((unsigned)ceil_div(idxw, 16), (unsigned)ceil_div(h, 16), (unsigned)s);                           \
+                launch_k(sparse_scores_tile_kernel<BF, 2, 1>, g, 64, ss1, st, q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,   \
+                                                                  sa, sb, seq_mod);                                     \
             } else {                                                                                                    \
                 dim3 g((unsigned)ceil_div(idxw, 64), (unsigned)ceil_div(h, 16), (unsigned)s);                           \
-                launch_k(sparse_scores_tile_kernel<BF, 2>, g, 64, ss2, st, q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,   \
+                launch_k(sparse_scores_tile_kernel<BF, 2, 4>, g, 64, ss2, st, q, h, d, ids, ns, idxw, scale, kv_a, na, kv_b, sc,   \
                                                                   sa, sb, seq_mod);                                     \
             }                                                                                                           \
             APUS_LAUNCHED();                                                                                            \
@@ -885,6 +900,9 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
             APUS_LAUNCHED();                                                                                            \
             if (hgs == 16)                                                                                              \
                 launch_k(sparse_pv_tile_kernel<BF, 16>, dim3((unsigned)ceil_div(h, 16), (unsigned)s), 256, 0, st,             \
+                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
+            else if (pv_split)                                                                                          \
+                launch_k(sparse_pv_tile_kernel<BF, 4>, dim3((unsigned)ceil_div(h, 4), (unsigned)s, 4), 64, 0, st,             \
                     sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
             else                                                                                                        \
                 launch_k(sparse_pv_tile_kernel<BF, 4>, dim3((unsigned)ceil_div(h, 4), (unsigned)s), 256, 0, st,               \
