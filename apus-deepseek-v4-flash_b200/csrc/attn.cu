@@ -707,10 +707,7 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
     kv_b = reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride;
     const int n = ns[t];
     const int32_t *idr = ids + (size_t)t * idxw;
-    // gridDim.z CTAs share a (row, head group): each takes blockDim.x channel pairs of every 256 (a small step has
-    // few (row, head group)s, and one SM gathering all the rows alone is bound by what one SM can pull from L2)
-    const int nth = (int)blockDim.x;
-    for (int c0 = (int)blockIdx.z * nth; c0 < d / 2; c0 += nth * (int)gridDim.z) {
+    for (int c0 = 0; c0 < d / 2; c0 += 256) {
         const int k2 = c0 + tid;
         const bool on = k2 < d / 2;
         float a0[HG], a1[HG];
@@ -719,11 +716,11 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
         for (int j0 = 0; j0 < n; j0 += PV_JC) {
             const int cnt = min(PV_JC, n - j0);
             __syncthreads();
-            for (int i = tid; i < PV_JC * HG; i += nth) {
+            for (int i = tid; i < PV_JC * HG; i += 256) {
                 const int a = i / PV_JC, jj = i - a * PV_JC;
                 s_p[jj][a] = (jj < cnt && h0 + a < h) ? p[((size_t)t * h + h0 + a) * idxw + j0 + jj] : 0.f;
             }
-            for (int i = tid; i < cnt; i += nth) s_id[i] = idr[j0 + i];
+            for (int i = tid; i < cnt; i += 256) s_id[i] = idr[j0 + i];
             __syncthreads();
             if (on) {
                 // LB gathered rows in flight per thread: the rows come from L2 / HBM with nothing else to
@@ -779,6 +776,113 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
                 ov[2 * k2 + 1] = x2;
             }
         }
+    }
+}
+
+// P.V for the few (row, head group)s of a small step.  There the kernel above is a chain of load latencies:
+// a thread fetches a batch of gathered rows into registers, waits, accumulates, fetches the next -- and one
+// or two warps per SM keep too few bytes in flight to pull the rows out of L2 any faster.  Here a CTA owns
+// 4 heads x PVS_NP channel pairs of a row and stages the row segments of PVS_T candidates at a time in
+// shared memory with 16-byte asynchronous copies, two tiles in flight while a third is consumed (the
+// probabilities travel the same way, 4 bytes each), so the copies of the whole row are issued back to
+// back and the accumulation reads shared memory.  Same products, same order of adds, same bits.
+#define PVS_T 64
+#define PVS_NP 64
+#define PVS_NS 3
+template <bool BF16>
+__global__ void __launch_bounds__(PVS_NP)
+sparse_pv_stage_kernel(const float *__restrict__ p, const float *__restrict__ den, int h, int d,
+                       const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw, const void *kv_a, int64_t na,
+                       const void *kv_b, float *__restrict__ o, size_t a_stride, size_t b_stride, int seq_mod, const SaRope rope) {
+    APUS_PDL_WAIT();
+    APUS_PDL_GO();
+    constexpr int ROWB = PVS_NP * (BF16 ? 4 : 8);              // bytes of a row's segment
+    constexpr int CPR = ROWB / 16;                             // 16-byte copies per row
+    constexpr int STAGE = PVS_T * ROWB + PVS_T * 16;           // rows, then the tile's probabilities [PVS_T][4]
+    extern __shared__ __align__(16) unsigned char pvs[];
+    const int t = blockIdx.y, h0 = (int)blockIdx.x * 4, tid = threadIdx.x;
+    const int k2 = (int)blockIdx.z * PVS_NP + tid;             // this thread's channel pair
+    const int own = seq_mod > 0 ? t % seq_mod : t;
+    const size_t esz = BF16 ? 2 : 4;
+    const char *base_a = reinterpret_cast<const char *>(kv_a) + (size_t)own * a_stride + (size_t)blockIdx.z * ROWB;
+    const char *base_b = reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride + (size_t)blockIdx.z * ROWB;
+    const int n = ns[t];
+    const int32_t *idr = ids + (size_t)t * idxw;
+    const int ntile = (n + PVS_T - 1) / PVS_T;
+    auto stage = [&](int c) {
+        if (c < ntile) {
+            unsigned char *st = pvs + (size_t)(c % PVS_NS) * STAGE;
+            const int j0 = c * PVS_T, cnt = min(PVS_T, n - j0);
+#pragma unroll 4
+            for (int i = tid; i < PVS_T * CPR; i += PVS_NP) {
+                const int r = i / CPR, seg = i - r * CPR;
+                if (r < cnt) {
+                    const int32_t id = idr[j0 + r];
+                    const char *src = id < na ? base_a + (size_t)id * d * esz : base_b + (size_t)(id - na) * d * esz;
+                    cp_async16(st + (size_t)r * ROWB + seg * 16, src + seg * 16, true);
+                }
+            }
+            for (int i = tid; i < PVS_T * 4; i += PVS_NP) {
+                const int r = i >> 2, a = i & 3;
+                if (r < cnt && h0 + a < h) {
+                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(st + PVS_T * ROWB + i * 4);
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(p + ((size_t)t * h + h0 + a) * idxw + j0 + r) : "memory");
+                } else {
+                    *reinterpret_cast<float *>(st + PVS_T * ROWB + i * 4) = 0.f;
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+    stage(0);
+    stage(1);
+    for (int c = 0; c < ntile; c++) {
+        stage(c + 2);                                          // its buffer was consumed at step c - 1, behind that step's barrier
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        __syncthreads();                                       // tile c of every thread has landed
+        const unsigned char *st = pvs + (size_t)(c % PVS_NS) * STAGE;
+        const float4 *sp = reinterpret_cast<const float4 *>(st + PVS_T * ROWB);
+        const int cnt = min(PVS_T, n - c * PVS_T);
+#pragma unroll 4
+        for (int j = 0; j < cnt; j++) {
+            float2 v;
+            if (BF16) {
+                const uint32_t w = *reinterpret_cast<const uint32_t *>(st + (size_t)j * ROWB + tid * 4);
+                v = make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+            } else {
+                v = *reinterpret_cast<const float2 *>(st + (size_t)j * ROWB + tid * 8);
+            }
+            const float4 p4 = sp[j];
+            const float pa[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                a0[e] = __fadd_rn(a0[e], __fmul_rn(pa[e], v.x));
+                a1[e] = __fadd_rn(a1[e], __fmul_rn(pa[e], v.y));
+            }
+        }
+        __syncthreads();                                       // this tile's buffer is free again
+    }
+    const int ri = rope.cs ? k2 - (d - rope.rd) / 2 : -1;
+    float co = 1.f, si = 0.f;
+    if (ri >= 0) {
+        const float *c = rope.cs + (rope.pos ? (size_t)*rope.pos * rope.rd : 0);
+        co = c[ri]; si = -c[rope.rd / 2 + ri];
+    }
+#pragma unroll
+    for (int a = 0; a < 4; a++) {
+        if (h0 + a >= h) continue;
+        float *ov = o + ((size_t)t * h + h0 + a) * d;
+        if (n == 0) { ov[2 * k2] = 0.f; ov[2 * k2 + 1] = 0.f; continue; }
+        const float dn = den[(size_t)t * h + h0 + a];
+        float x1 = bf16_round(__fdiv_rn(a0[a], dn)), x2 = bf16_round(__fdiv_rn(a1[a], dn));
+        if (ri >= 0) {
+            const float y1 = bf16_round(__fsub_rn(__fmul_rn(x1, co), __fmul_rn(x2, si)));
+            const float y2 = bf16_round(__fadd_rn(__fmul_rn(x1, si), __fmul_rn(x2, co)));
+            x1 = y1; x2 = y2;
+        }
+        ov[2 * k2] = x1;
+        ov[2 * k2 + 1] = x2;
     }
 }
 
@@ -876,8 +980,11 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         // a small step (few rows, few candidates): 8-candidate tiles, so that no warp walks more than a quarter
         static const bool small_on = [] { const char *e = getenv("APUS_ATTN_SMALL"); return !(e && e[0] == '0'); }();
         const bool narrow = small_on && (long long)ceil_div(idxw, 32) * ceil_div(h, 16) * s <= 296;
-        // ... and in P.V four CTAs of 64 channel pairs per (row, head group) instead of one of 256
-        const bool pv_split = small_on && d % 512 == 0 && (long long)s * ceil_div(h, 4) < 74;
+        // ... and P.V by the staging kernel, 64 channel pairs per CTA
+        const bool pv_split = small_on && d % (2 * PVS_NP) == 0 && (long long)s * ceil_div(h, 4) < 74;
+        const size_t pvs_smem = (size_t)PVS_NS * (PVS_T * PVS_NP * (kv_bf16 ? 4 : 8) + PVS_T * 16);
+        if (pv_split && ensure_dyn_smem(kv_bf16 ? (const void *)sparse_pv_stage_kernel<true> : (const void *)sparse_pv_stage_kernel<false>, pvs_smem))
+            return 1;
         if (ensure_dyn_smem(kv_bf16 ? (const void *)sparse_scores_tile_kernel<true, 8, 4> : (const void *)sparse_scores_tile_kernel<false, 8, 4>, ss8))
             return 1;
 #define APUS_SA_LAUNCH(BF)                                                                                              \
@@ -902,8 +1009,9 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
                 launch_k(sparse_pv_tile_kernel<BF, 16>, dim3((unsigned)ceil_div(h, 16), (unsigned)s), 256, 0, st,             \
                     sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
             else if (pv_split)                                                                                          \
-                launch_k(sparse_pv_tile_kernel<BF, 4>, dim3((unsigned)ceil_div(h, 4), (unsigned)s, 4), 64, 0, st,             \
-                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
+                launch_k(sparse_pv_stage_kernel<BF>, dim3((unsigned)ceil_div(h, 4), (unsigned)s, (unsigned)(d / 2 / PVS_NP)),   \
+                    PVS_NP, pvs_smem, st, sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod,             \
+                    rope ? *rope : no_rope);                                                                            \
             else                                                                                                        \
                 launch_k(sparse_pv_tile_kernel<BF, 4>, dim3((unsigned)ceil_div(h, 4), (unsigned)s), 256, 0, st,               \
                     sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
