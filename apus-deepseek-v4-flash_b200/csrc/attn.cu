@@ -786,35 +786,34 @@ sparse_pv_tile_kernel(const float *__restrict__ p, const float *__restrict__ den
 // shared memory with 16-byte asynchronous copies, two tiles in flight while a third is consumed (the
 // probabilities travel the same way, 4 bytes each), so the copies of the whole row are issued back to
 // back and the accumulation reads shared memory.  Same products, same order of adds, same bits.
-#define PVS_T 64
-#define PVS_NP 64
 #define PVS_NS 3
-template <bool BF16>
-__global__ void __launch_bounds__(PVS_NP)
+// HG heads x NP channel pairs per CTA (NP threads), T candidates per staged tile
+template <bool BF16, int HG, int NP, int T>
+__global__ void __launch_bounds__(NP)
 sparse_pv_stage_kernel(const float *__restrict__ p, const float *__restrict__ den, int h, int d,
                        const int32_t *__restrict__ ids, const int *__restrict__ ns, int idxw, const void *kv_a, int64_t na,
                        const void *kv_b, float *__restrict__ o, size_t a_stride, size_t b_stride, int seq_mod, const SaRope rope) {
     APUS_PDL_WAIT();
     APUS_PDL_GO();
-    constexpr int ROWB = PVS_NP * (BF16 ? 4 : 8);              // bytes of a row's segment
+    constexpr int ROWB = NP * (BF16 ? 4 : 8);              // bytes of a row's segment
     constexpr int CPR = ROWB / 16;                             // 16-byte copies per row
-    constexpr int STAGE = PVS_T * ROWB + PVS_T * 16;           // rows, then the tile's probabilities [PVS_T][4]
+    constexpr int STAGE = T * ROWB + T * HG * 4;       // rows, then the tile's probabilities [T][HG]
     extern __shared__ __align__(16) unsigned char pvs[];
-    const int t = blockIdx.y, h0 = (int)blockIdx.x * 4, tid = threadIdx.x;
-    const int k2 = (int)blockIdx.z * PVS_NP + tid;             // this thread's channel pair
+    const int t = blockIdx.y, h0 = (int)blockIdx.x * HG, tid = threadIdx.x;
+    const int k2 = (int)blockIdx.z * NP + tid;             // this thread's channel pair
     const int own = seq_mod > 0 ? t % seq_mod : t;
     const size_t esz = BF16 ? 2 : 4;
     const char *base_a = reinterpret_cast<const char *>(kv_a) + (size_t)own * a_stride + (size_t)blockIdx.z * ROWB;
     const char *base_b = reinterpret_cast<const char *>(kv_b) + (size_t)own * b_stride + (size_t)blockIdx.z * ROWB;
     const int n = ns[t];
     const int32_t *idr = ids + (size_t)t * idxw;
-    const int ntile = (n + PVS_T - 1) / PVS_T;
+    const int ntile = (n + T - 1) / T;
     auto stage = [&](int c) {
         if (c < ntile) {
             unsigned char *st = pvs + (size_t)(c % PVS_NS) * STAGE;
-            const int j0 = c * PVS_T, cnt = min(PVS_T, n - j0);
+            const int j0 = c * T, cnt = min(T, n - j0);
 #pragma unroll 4
-            for (int i = tid; i < PVS_T * CPR; i += PVS_NP) {
+            for (int i = tid; i < T * CPR; i += NP) {
                 const int r = i / CPR, seg = i - r * CPR;
                 if (r < cnt) {
                     const int32_t id = idr[j0 + r];
@@ -822,19 +821,21 @@ sparse_pv_stage_kernel(const float *__restrict__ p, const float *__restrict__ de
                     cp_async16(st + (size_t)r * ROWB + seg * 16, src + seg * 16, true);
                 }
             }
-            for (int i = tid; i < PVS_T * 4; i += PVS_NP) {
-                const int r = i >> 2, a = i & 3;
+            for (int i = tid; i < T * HG; i += NP) {
+                const int r = i / HG, a = i - r * HG;
                 if (r < cnt && h0 + a < h) {
-                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(st + PVS_T * ROWB + i * 4);
+                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(st + T * ROWB + i * 4);
                     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(p + ((size_t)t * h + h0 + a) * idxw + j0 + r) : "memory");
                 } else {
-                    *reinterpret_cast<float *>(st + PVS_T * ROWB + i * 4) = 0.f;
+                    *reinterpret_cast<float *>(st + T * ROWB + i * 4) = 0.f;
                 }
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+    float a0[HG], a1[HG];
+#pragma unroll
+    for (int a = 0; a < HG; a++) a0[a] = a1[a] = 0.f;
     stage(0);
     stage(1);
     for (int c = 0; c < ntile; c++) {
@@ -842,8 +843,8 @@ sparse_pv_stage_kernel(const float *__restrict__ p, const float *__restrict__ de
         asm volatile("cp.async.wait_group 2;" ::: "memory");
         __syncthreads();                                       // tile c of every thread has landed
         const unsigned char *st = pvs + (size_t)(c % PVS_NS) * STAGE;
-        const float4 *sp = reinterpret_cast<const float4 *>(st + PVS_T * ROWB);
-        const int cnt = min(PVS_T, n - c * PVS_T);
+        const float4 *sp = reinterpret_cast<const float4 *>(st + T * ROWB);
+        const int cnt = min(T, n - c * T);
 #pragma unroll 4
         for (int j = 0; j < cnt; j++) {
             float2 v;
@@ -853,12 +854,15 @@ sparse_pv_stage_kernel(const float *__restrict__ p, const float *__restrict__ de
             } else {
                 v = *reinterpret_cast<const float2 *>(st + (size_t)j * ROWB + tid * 8);
             }
-            const float4 p4 = sp[j];
-            const float pa[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                a0[e] = __fadd_rn(a0[e], __fmul_rn(pa[e], v.x));
-                a1[e] = __fadd_rn(a1[e], __fmul_rn(pa[e], v.y));
+            for (int m = 0; m < HG / 4; m++) {
+                const float4 p4 = sp[j * (HG / 4) + m];
+                const float pa[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    a0[4 * m + e] = __fadd_rn(a0[4 * m + e], __fmul_rn(pa[e], v.x));
+                    a1[4 * m + e] = __fadd_rn(a1[4 * m + e], __fmul_rn(pa[e], v.y));
+                }
             }
         }
         __syncthreads();                                       // this tile's buffer is free again
@@ -870,7 +874,7 @@ sparse_pv_stage_kernel(const float *__restrict__ p, const float *__restrict__ de
         co = c[ri]; si = -c[rope.rd / 2 + ri];
     }
 #pragma unroll
-    for (int a = 0; a < 4; a++) {
+    for (int a = 0; a < HG; a++) {
         if (h0 + a >= h) continue;
         float *ov = o + ((size_t)t * h + h0 + a) * d;
         if (n == 0) { ov[2 * k2] = 0.f; ov[2 * k2 + 1] = 0.f; continue; }
@@ -980,10 +984,17 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
         // a small step (few rows, few candidates): 8-candidate tiles, so that no warp walks more than a quarter
         static const bool small_on = [] { const char *e = getenv("APUS_ATTN_SMALL"); return !(e && e[0] == '0'); }();
         const bool narrow = small_on && (long long)ceil_div(idxw, 32) * ceil_div(h, 16) * s <= 296;
-        // ... and P.V by the staging kernel, 64 channel pairs per CTA
-        const bool pv_split = small_on && d % (2 * PVS_NP) == 0 && (long long)s * ceil_div(h, 4) < 74;
-        const size_t pvs_smem = (size_t)PVS_NS * (PVS_T * PVS_NP * (kv_bf16 ? 4 : 8) + PVS_T * 16);
-        if (pv_split && ensure_dyn_smem(kv_bf16 ? (const void *)sparse_pv_stage_kernel<true> : (const void *)sparse_pv_stage_kernel<false>, pvs_smem))
+        // P.V from staged rows where the row splits into whole CTAs' worth of channel pairs: 16 heads x 128 pairs
+        // per CTA when there are (row, 16 heads) groups enough to fill the GPU, else 4 heads x 64 pairs
+        static const bool stage_on = [] { const char *e = getenv("APUS_ATTN_STAGE"); return !(e && e[0] == '0'); }();
+        const bool pv_stage = stage_on && d % 256 == 0;
+        const size_t rowb = kv_bf16 ? 4 : 8;
+        const size_t pvs4 = (size_t)PVS_NS * (64 * 64 * rowb + 64 * 4 * 4);
+        const size_t pvs16 = (size_t)PVS_NS * ((kv_bf16 ? 64 : 32) * 128 * rowb + (kv_bf16 ? 64 : 32) * 16 * 4);
+        if (pv_stage && (ensure_dyn_smem(kv_bf16 ? (const void *)sparse_pv_stage_kernel<true, 4, 64, 64>
+                                                 : (const void *)sparse_pv_stage_kernel<false, 4, 64, 64>, pvs4) ||
+                         ensure_dyn_smem(kv_bf16 ? (const void *)sparse_pv_stage_kernel<true, 16, 128, 64>
+                                                 : (const void *)sparse_pv_stage_kernel<false, 16, 128, 32>, pvs16)))
             return 1;
         if (ensure_dyn_smem(kv_bf16 ? (const void *)sparse_scores_tile_kernel<true, 8, 4> : (const void *)sparse_scores_tile_kernel<false, 8, 4>, ss8))
             return 1;
@@ -1005,13 +1016,17 @@ int sparse_attn(const float *q, const float *sink, int h, int d,
             APUS_LAUNCHED();                                                                                            \
             launch_k(sparse_softmax_kernel, dim3((unsigned)h, (unsigned)s), 256, sm2, st, sc, sink, h, ns, idxw, den);       \
             APUS_LAUNCHED();                                                                                            \
-            if (hgs == 16)                                                                                              \
+            if (pv_stage && hgs == 16)                                                                                  \
+                launch_k(sparse_pv_stage_kernel<BF, 16, 128, (BF ? 64 : 32)>,                                           \
+                    dim3((unsigned)ceil_div(h, 16), (unsigned)s, (unsigned)(d / 2 / 128)), 128, pvs16, st,              \
+                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
+            else if (pv_stage)                                                                                          \
+                launch_k(sparse_pv_stage_kernel<BF, 4, 64, 64>,                                                         \
+                    dim3((unsigned)ceil_div(h, 4), (unsigned)s, (unsigned)(d / 2 / 64)), 64, pvs4, st,                  \
+                    sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
+            else if (hgs == 16)                                                                                         \
                 launch_k(sparse_pv_tile_kernel<BF, 16>, dim3((unsigned)ceil_div(h, 16), (unsigned)s), 256, 0, st,             \
                     sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \
-            else if (pv_split)                                                                                          \
-                launch_k(sparse_pv_stage_kernel<BF>, dim3((unsigned)ceil_div(h, 4), (unsigned)s, (unsigned)(d / 2 / PVS_NP)),   \
-                    PVS_NP, pvs_smem, st, sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod,             \
-                    rope ? *rope : no_rope);                                                                            \
             else                                                                                                        \
                 launch_k(sparse_pv_tile_kernel<BF, 4>, dim3((unsigned)ceil_div(h, 4), (unsigned)s), 256, 0, st,               \
                     sc, den, h, d, ids, ns, idxw, kv_a, na, kv_b, o, sa, sb, seq_mod, rope ? *rope : no_rope);          \

@@ -422,6 +422,9 @@ static int launch_linear_seq(const void *w, long long ws, const float *x, long l
     if (M == 1) SEQ_LAUNCH(1, 1, 1, 6);
     else if (M <= 2) SEQ_LAUNCH(1, 2, 1, 6);
     else if (M <= 4) SEQ_LAUNCH(1, 2, 2, 6);
+    // few output rows (router gate, indexer head weights): the launch is a handful of CTAs, each a chain of K
+    // adds per accumulator; one token per warp halves the walk of a warp and doubles the CTAs
+    else if (M > 8 && ctas32 < 32) SEQ_LAUNCH(1, 1, 4, 6);      // 4 tokens per CTA, one per warp
     else if (M <= 8 || ctas32 < 64) SEQ_LAUNCH(1, 2, 4, 6);     // 8 tokens per CTA, two per warp
     else if (M <= 16 || ctas32 < 148) SEQ_LAUNCH(1, 2, 8, 3);   // 16 tokens per CTA
     else if constexpr (WBF16) SEQ_LAUNCH(2, 4, 8, 3);           // 32 tokens x 64 rows per CTA
