@@ -77,6 +77,17 @@ static inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 blo
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    // Measurement aid (off unless APUS_DUP is set): every kernel whose name contains $APUS_DUP is launched
+    // twice.  The growth of a replayed step is then that kernel's cost ON the step's critical path, launch gap
+    // included, which a profiler's serialised per-kernel times do not show (a kernel on a side chain with
+    // slack costs nothing; doubling it gives an upper bound).  Only for kernels that may run twice: not the
+    // ones that advance the position or the sampler state.
+    static const char *dup = getenv("APUS_DUP");
+    if (dup && dup[0]) {
+        const char *name = nullptr;
+        if (cudaFuncGetName(&name, (const void *)kernel) == cudaSuccess && name && strstr(name, dup))
+            cudaLaunchKernelEx(&cfg, kernel, args...);
+    }
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
