@@ -381,3 +381,32 @@ def test_whole_layers_load_like_the_model_receives_them(ckpt, threads, monkeypat
     assert lib().apus_cuda_ckpt_layer_digest(ckpt["h"], 1, 2, 6, C.byref(d), C.byref(n)) == 0
     assert (d.value, n.value) == (want, nbytes)
     assert lib().apus_cuda_ckpt_layer_digest(ckpt["h"], 9, 0, -1, None, None) == 1
+
+
+@pytest.mark.parametrize("kind", ["mtp", "dspark"])
+def test_draft_module_sections_of_a_checkpoint(tmp_path, kind):
+    """A checkpoint that also carries a draft module ("mtp.<k>.*" tensors and the config entry that declares
+    them, reference c/model.h:336-373): the config fields say so, every written tensor resolves by name with
+    its dtype and shape, and the loaders refuse a missing model with a message (no GPU needed for that)."""
+    tm = cases.TinyModel(91, rope_pair(), 3)
+    extra = {"mtp": cases.TinyMtp(94, rope_pair())} if kind == "mtp" else \
+        {"dspark": cases.TinyDspark(95, rope_pair(), [0, 2], 2, 3, 5, 16)}
+    written = ckpt_util.write_checkpoint(tmp_path, tm, seed=3, **extra)
+    h, err = open_ckpt(tmp_path)
+    assert h, err
+    cfg = lib().apus_cuda_ckpt_cfg(h).contents
+    assert (cfg.n_mtp, cfg.mtp_ratio, cfg.mtp_hash, cfg.dspark) == ((1, 0, 0, 0) if kind == "mtp" else (0, 0, 0, 1))   # the stage count of a DSpark section is its own field
+    names = [n for n in written if n.startswith("mtp.")]
+    assert any(n.endswith("e_proj.weight") for n in names) == (kind == "mtp")
+    assert any("markov_head" in n for n in names) == (kind == "dspark")
+    for name in names:
+        dtype, shape, payload = written[name]
+        dt, nd, nb = C.c_int(), C.c_int(), C.c_uint64()
+        sh = (C.c_int64 * 8)()
+        assert lib().apus_cuda_ckpt_tensor(h, name.encode(), C.byref(dt), C.byref(nd), sh, C.byref(nb)) == 0, name
+        assert capi.ST_DTYPES[dt.value] == dtype and tuple(sh[: nd.value]) == tuple(shape) and nb.value == len(payload)
+    lib().apus_cuda_ckpt_close(h)
+    assert not lib().apus_cuda_mtp_load(None, str(tmp_path).encode(), 0)
+    assert b"NULL model" in lib().apus_cuda_last_error()
+    assert not lib().apus_cuda_dspark_load(None, str(tmp_path).encode())
+    assert b"NULL model" in lib().apus_cuda_last_error()
