@@ -1087,7 +1087,7 @@ ApusCudaMtp *apus_cuda_mtp_load(ApusCudaModel *m, const char *dir, int idx) {
     if (!m || apus_cuda_model_info(m, nullptr, &max_pos, nullptr, nullptr)) { set_error("mtp_load: NULL model"); return nullptr; }
     char err[512] = "";
     ApusCudaCkpt *c = apus_cuda_ckpt_open(dir, err, sizeof err);
-    if (!c) return nullptr;
+    if (!c) { set_error("mtp_load: %s", err); return nullptr; }
     const ApusCudaCkptCfg &cfg = c->cfg;
     ApusCudaMtp *mt = nullptr;
     std::string why;
@@ -1125,7 +1125,7 @@ ApusCudaDspark *apus_cuda_dspark_load(ApusCudaModel *m, const char *dir) {
     if (!m || apus_cuda_model_info(m, nullptr, &max_pos, nullptr, nullptr)) { set_error("dspark_load: NULL model"); return nullptr; }
     char err[512] = "";
     ApusCudaCkpt *c = apus_cuda_ckpt_open(dir, err, sizeof err);
-    if (!c) return nullptr;
+    if (!c) { set_error("dspark_load: %s", err); return nullptr; }
     const ApusCudaCkptCfg &cfg = c->cfg;
     ApusCudaDspark *ds = nullptr;
     std::string why;
