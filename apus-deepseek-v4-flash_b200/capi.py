@@ -281,6 +281,7 @@ def load(path=LIB_PATH):
         "apus_cuda_mtp_load": (vp, [vp, C.c_char_p, ci]),
         "apus_cuda_dspark_destroy": (None, [vp]),
         "apus_cuda_dspark_reset": (ci, [vp]),
+        "apus_cuda_dspark_set_sampling": (ci, [vp, C.c_float, C.c_uint64]),
         "apus_cuda_dspark_feed": (ci, [vp, vp, C.c_int64, ci]),
         "apus_cuda_dspark_draft_round": (ci, [vp, C.c_int64, vp, C.c_int64, vp, vp, vp, vp]),
         "apus_cuda_model_spec_generate_dspark": (ci, [vp, vp, vp, ci, ci, vp, vp]),

@@ -1347,11 +1347,12 @@ struct ApusCudaDspark {
     WeightOwner own;
     int rows_cap = 0;
     DevBuf mh, mxa, mx, pq, ps, kva, kv, h0, h1, x, y, sub, post, comb, raw, sa, ids, idxs, yh, yn, logits, emb, tok, cur,
-        conf, drafts, ws[24];
+        conf, drafts, drng, probs, ws[24];
+    float temp = 0.f;                       // > 0: the drafts are drawn at this temperature from the module's own stream (drng)
     StepBufs sb;
     void release() {
         DevBuf *b[] = {&mh, &mxa, &mx, &pq, &ps, &kva, &kv, &h0, &h1, &x, &y, &sub, &post, &comb, &raw, &sa, &ids, &idxs,
-                       &yh, &yn, &logits, &emb, &tok, &cur, &conf, &drafts};
+                       &yh, &yn, &logits, &emb, &tok, &cur, &conf, &drafts, &drng, &probs};
         for (DevBuf *p : b) p->release();
         for (auto &w : ws) w.release();
         for (auto &st : states) st.release();
@@ -1519,7 +1520,11 @@ static int ds_round(ApusCudaDspark *ds, long long anchor, const float *mh_row, l
         launch_k(markov_bias_kernel, ceil_div(V, 256), 256, 0, st, ds->markov_w1, ds->markov_w2, ds->cur.as<long long>(), ds->rank, V,
                  row, ds->emb.as<float>() + (size_t)i * ds->rank);
         APUS_LAUNCHED();
-        if (argmax_rows(row, V, 1, ds->tok.as<int32_t>(), st)) return 1;
+        // the pick of the row: greedy, or one draw at the draft temperature with top_p 1 from the module's own
+        // generator stream, one uniform per draft row (c/dspark.h:666-676)
+        if (sample_rows(row, V, 1, ds->temp, 1.0f, nullptr, ds->drng.as<unsigned long long>(), ds->probs.as<float>(),
+                        ds->tok.as<int32_t>(), st))
+            return 1;
         launch_k(markov_take_kernel, 1, 1, 0, st, ds->tok.as<int32_t>(), ds->cur.as<long long>(), ds->drafts.as<long long>(), i);
         APUS_LAUNCHED();
     }
@@ -1540,6 +1545,19 @@ void apus_cuda_dspark_destroy(ApusCudaDspark *ds) {
     cudaDeviceSynchronize();
     ds->release();
     delete ds;
+}
+
+// c/dspark.h:702-711 (apus_dspec_init): the temperature of the draft picks and the seed of the stream they are
+// drawn from -- a splitmix64 stream of its own (c/sample.h:159-170), advanced by one draw per draft row and
+// never rolled back.  temp <= 0: greedy drafts.
+int apus_cuda_dspark_set_sampling(ApusCudaDspark *ds, float temp, uint64_t draft_seed) {
+    if (!ds) { set_error("NULL dspark"); return 1; }
+    cudaStream_t st = mstream(ds->m);
+    ds->temp = temp > 0.f ? temp : 0.f;
+    if (ds->drng.get(8, nullptr) || ds->probs.get((size_t)ds->m->vocab * 4, nullptr)) return 1;
+    APUS_CUDA_OK(cudaMemcpyAsync(ds->drng.p, &draft_seed, 8, cudaMemcpyHostToDevice, st));
+    APUS_CUDA_OK(cudaStreamSynchronize(st));
+    return 0;
 }
 
 // c/dspark.h:353-356: fresh (empty) stage rings
@@ -1648,7 +1666,7 @@ int apus_cuda_dspark_draft_round(ApusCudaDspark *ds, int64_t anchor, const float
 }
 
 // c/dspark.h:747-862 apus_dspec_prefill + apus_dspec_step until n_gen tokens are out (greedy or sampled main
-// stream; the drafts are greedy).  stats [7]: emitted, batches, batch_tokens, refeed_tokens, offered,
+// stream; the drafts are greedy unless apus_cuda_dspark_set_sampling gave them a temperature).  stats [7]: emitted, batches, batch_tokens, refeed_tokens, offered,
 // accepted, bonus_rounds.
 int apus_cuda_model_spec_generate_dspark(ApusCudaModel *m, ApusCudaDspark *ds, const int64_t *prompt, int n_prompt, int n_gen,
                                          int32_t *out_tokens, uint64_t *stats) {

@@ -695,7 +695,12 @@ int apus_cuda_dspark_reset(ApusCudaDspark *ds);
  * the whole prompt) or apus_dspark_catchup: the stage rings' rows of the n true positions
  * pos0 .. pos0 + n - 1 from their main hiddens mh [n, n_targets * dim]. */
 int apus_cuda_dspark_feed(ApusCudaDspark *ds, const float *mh, int64_t pos0, int n);
-/* c/dspark.h:611-697 apus_dspark_draft_round with greedy drafts: anchor = the held token, mh_row
+/* c/dspark.h:702-711 apus_dspec_init's temp and draft_seed: temp > 0 makes every draft pick one draw at
+ * that temperature (top_p 1) from the module's own splitmix64 stream, seeded here, one uniform per draft
+ * row, never rolled back (c/dspark.h:666-676); temp <= 0 (the state after create / load) = greedy drafts.
+ * The reference drafts at the temperature of the main stream: pass the model's. */
+int apus_cuda_dspark_set_sampling(ApusCudaDspark *ds, float temp, uint64_t draft_seed);
+/* c/dspark.h:611-697 apus_dspark_draft_round: anchor = the held token, mh_row
  * [n_targets * dim] = main hidden of position start_pos (its ring slot is rewritten, idempotent
  * with apus_cuda_dspark_feed); drafts [block_size] = candidates for start_pos + 2 ..; nullable
  * outputs as in ApusDsparkDbg: confidence [block_size], logits_final [block_size, vocab], stage_h

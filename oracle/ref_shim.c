@@ -293,9 +293,18 @@ static void shim_fill_dspark(ApusDspark *ds, ApusRopeTab *tabs, ApusModel *m, co
 
 /* c/dspark.h:365-455, 611: stage-0 projection + ring prefill over the n main-hidden rows mh_all, then one
  * draft round at start_pos = n - 1 from the last row (greedy); stage_states [n_stages] in/out. */
+void ref_dspark_prefill_round_t(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *stage_states,
+                                const float *mh_all, int n, int64_t anchor, float temp, uint64_t draft_seed,
+                                int64_t *drafts, float *confidence, float *logits_final, float *stage_h);
 void ref_dspark_prefill_round(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *stage_states,
                               const float *mh_all, int n, int64_t anchor, int64_t *drafts, float *confidence,
                               float *logits_final, float *stage_h) {
+    ref_dspark_prefill_round_t(d, dd, stage_states, mh_all, n, anchor, 0.0f, 1, drafts, confidence, logits_final, stage_h);
+}
+/* the same with the draft picks drawn at `temp` from a stream seeded with draft_seed (c/dspark.h:666-676) */
+void ref_dspark_prefill_round_t(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *stage_states,
+                                const float *mh_all, int n, int64_t anchor, float temp, uint64_t draft_seed,
+                                int64_t *drafts, float *confidence, float *logits_final, float *stage_h) {
     ShimModel S;
     ApusAttnS none[64];
     memset(none, 0, sizeof none);
@@ -315,8 +324,8 @@ void ref_dspark_prefill_round(const ApusCudaModelDesc *d, const ApusCudaDsparkDe
     dbg.confidence = confidence; dbg.logits_final = logits_final;
     for (int k = 0; k < ds.n_stages && stage_h; k++) dbg.stage_h[k] = stage_h + (size_t)k * B * hcd;
     ApusRng drng;
-    apus_rng_seed(&drng, 1);
-    apus_dspark_draft_round(&ds, &dst, anchor, mx + (size_t)(n - 1) * dim, n - 1, 0.0f, &drng, NULL, drafts, &dbg);
+    apus_rng_seed(&drng, draft_seed);
+    apus_dspark_draft_round(&ds, &dst, anchor, mx + (size_t)(n - 1) * dim, n - 1, temp, &drng, NULL, drafts, &dbg);
     free(mx);
     for (int k = 0; k < ds.n_stages; k++) stage_states[k] = dst.stages[k].attn;
     shim_model_close(&S, none, &pos);
@@ -324,9 +333,19 @@ void ref_dspark_prefill_round(const ApusCudaModelDesc *d, const ApusCudaDsparkDe
 
 /* c/dspark.h:747-862 apus_dspec_prefill + apus_dspec_step until n_gen tokens are out (greedy).  stats [7] =
  * emitted, batches, batch_tokens, refeed_tokens, offered, accepted, bonus_rounds. */
+int ref_spec_generate_dspark_t(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *states,
+                               ApusAttnS *stage_states, const int64_t *prompt, int n_prompt, int n_gen, float temp,
+                               float top_p, uint64_t rng_seed, uint64_t draft_seed, int32_t *out_tokens, uint64_t *stats);
 int ref_spec_generate_dspark(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *states,
                              ApusAttnS *stage_states, const int64_t *prompt, int n_prompt, int n_gen,
                              int32_t *out_tokens, uint64_t *stats) {
+    return ref_spec_generate_dspark_t(d, dd, states, stage_states, prompt, n_prompt, n_gen, 0.0f, 1.0f, 0, 7, out_tokens, stats);
+}
+/* the same with a sampled main stream (temp, top_p, stream seeded with rng_seed) and drafts drawn at temp from a
+ * stream of their own (draft_seed), as apus_dspec_init sets them up */
+int ref_spec_generate_dspark_t(const ApusCudaModelDesc *d, const ApusCudaDsparkDesc *dd, ApusAttnS *states,
+                               ApusAttnS *stage_states, const int64_t *prompt, int n_prompt, int n_gen, float temp,
+                               float top_p, uint64_t rng_seed, uint64_t draft_seed, int32_t *out_tokens, uint64_t *stats) {
     ShimModel S;
     int64_t pos = 0;
     shim_model_open(&S, d, states, 0);
@@ -337,8 +356,8 @@ int ref_spec_generate_dspark(const ApusCudaModelDesc *d, const ApusCudaDsparkDes
     for (int k = 0; k < ds.n_stages; k++) dst.stages[k].attn = stage_states[k];
     ApusDspec sp;
     ApusRng rng;
-    apus_rng_seed(&rng, 0);
-    apus_dspec_init(&sp, &S.m, &S.st, &ds, &dst, 0.0f, 1.0f, &rng, 7, NULL);
+    apus_rng_seed(&rng, rng_seed);
+    apus_dspec_init(&sp, &S.m, &S.st, &ds, &dst, temp, top_p, &rng, draft_seed, NULL);
     apus_dspec_prefill(&sp, prompt, n_prompt);
     int n = 0, buf[80];
     while (n < n_gen) {

@@ -309,7 +309,8 @@ def ref_mtp(L, seed, n_layers, n_prompt, n_gen, depth, targets):
     return out
 
 
-def ref_dspark(L, seed, n_layers, n_prompt, n_gen, targets, n_stages, block_size, noise_id, rank):
+def ref_dspark(L, seed, n_layers, n_prompt, n_gen, targets, n_stages, block_size, noise_id, rank, temp, top_p, rng_seed,
+               draft_seed):
     """The reference's DSpark module on the small model (c/dspark.h): the stage rings built from the prompt's
     main hiddens and one draft round after them (drafts, final logits, confidence, every stage's block
     output), and its speculative loop (greedy), which must emit the plain greedy stream."""
@@ -345,6 +346,22 @@ def ref_dspark(L, seed, n_layers, n_prompt, n_gen, targets, n_stages, block_size
     plain = ref_generate(L, seed, n_layers, 1, n_prompt, n_gen)["tokens"][0]
     assert np.array_equal(plain, toks), (plain, toks)
     out.update(spec_tokens=toks, spec_stats=stats)
+    # sampled: the draft picks of a round drawn from the module's own stream, and the loop with a sampled main stream
+    L.ref_dspark_prefill_round_t.restype = None
+    L.ref_dspark_prefill_round_t.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int64, C.c_float, C.c_uint64, vp, vp, vp, vp]
+    L.ref_spec_generate_dspark_t.restype = C.c_int
+    L.ref_spec_generate_dspark_t.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_float, C.c_float, C.c_uint64, C.c_uint64, vp, vp]
+    keeps4, sst4 = Ds.states()
+    d_s, lf_s = np.zeros(block_size, np.int64), np.zeros((block_size, V), np.float32)
+    L.ref_dspark_prefill_round_t(C.byref(Mdl.desc), C.byref(Ds.desc), sst4, P(mh), n_prompt, anchor, temp, draft_seed, P(d_s), None,
+                                 P(lf_s), None)
+    keep5, st5 = Mdl.states()
+    keeps5, sst5 = Ds.states()
+    toks_s, stats_s = np.zeros(n_gen, np.int32), np.zeros(7, np.uint64)
+    n = L.ref_spec_generate_dspark_t(C.byref(Mdl.desc), C.byref(Ds.desc), st5, sst5, P(prompt), n_prompt, n_gen, temp, top_p, rng_seed,
+                                     draft_seed, P(toks_s), P(stats_s))
+    assert n == n_gen
+    out.update(drafts_sampled=d_s, logits_final_sampled=lf_s, spec_sampled_tokens=toks_s, spec_sampled_stats=stats_s)
     return out
 
 
@@ -353,7 +370,8 @@ def main_dspark():
     assert L is not None, "reference build not available"
     G = ref_dspark(L, **DSPARK_CASE)
     np.savez_compressed(HERE / "dspark_case.npz", **G)
-    print("wrote dspark_case.npz:", {k: v.shape for k, v in G.items()}, "stats", G["spec_stats"].tolist(), "drafts", G["drafts"].tolist())
+    print("wrote dspark_case.npz:", {k: v.shape for k, v in G.items()}, "stats", G["spec_stats"].tolist(), "drafts", G["drafts"].tolist(),
+          "sampled drafts", G["drafts_sampled"].tolist(), "sampled stats", G["spec_sampled_stats"].tolist())
 
 
 def main_mtp():
@@ -537,7 +555,8 @@ MHC_CASES = {"mhc_a": (61, 3, 64), "mhc_b": (62, 2, 256)}
 # the MTP draft head on the small model (c/mtp.h): targets = the layers whose mean hidden forward_mh collects
 MTP_CASE = dict(seed=91, n_layers=3, n_prompt=9, n_gen=24, depth=3, targets=[0, 2])
 # the DSpark draft module on the small model (c/dspark.h); the prompt is longer than the window of 8
-DSPARK_CASE = dict(seed=91, n_layers=3, n_prompt=11, n_gen=24, targets=[0, 2], n_stages=2, block_size=3, noise_id=5, rank=16)
+DSPARK_CASE = dict(seed=91, n_layers=3, n_prompt=11, n_gen=24, targets=[0, 2], n_stages=2, block_size=3, noise_id=5, rank=16,
+                   temp=0.8, top_p=0.9, rng_seed=1234, draft_seed=77)
 
 if __name__ == "__main__":
     import sys

@@ -92,6 +92,37 @@ def test_speculative_loop_with_dspark(setup):
     assert toks2.tolist() == toks.tolist()
 
 
+def test_sampled_drafts_and_sampled_loop(setup):
+    """Draft picks drawn at a temperature from the module's own generator stream (c/dspark.h:666-676): the
+    drafts of a round and the final logits behind them (every row's bigram bias follows the token drawn for
+    the row before) equal apus_dspark_draft_round with the same seed; the loop with a sampled main stream and
+    sampled drafts emits the reference's tokens and counters, which are those of plain sampled decoding."""
+    L, Mdl, _, prompt, h, ds = setup
+    n, n_gen = D["n_prompt"], D["n_gen"]
+    assert L.apus_cuda_dspark_set_sampling(ds, D["temp"], D["draft_seed"]) == 0, L.apus_cuda_last_error()
+    drafts, _, lf, _ = one_round(L, Mdl, ds, [n])
+    assert drafts.tolist() == R["drafts_sampled"].tolist()
+    assert np.array_equal(bits(lf), bits(R["logits_final_sampled"]))
+    assert drafts.tolist() != R["drafts"].tolist()                      # the case does tell greedy from sampled
+    # the loop: both streams seeded as apus_dspec_init seeds them
+    assert L.apus_cuda_model_reset(h) == 0
+    assert L.apus_cuda_model_set_sampling(h, D["temp"], D["top_p"], D["rng_seed"]) == 0
+    assert L.apus_cuda_dspark_set_sampling(ds, D["temp"], D["draft_seed"]) == 0
+    toks, stats = np.zeros(n_gen, np.int32), np.zeros(7, np.uint64)
+    rc = L.apus_cuda_model_spec_generate_dspark(h, ds, P(prompt), n, n_gen, P(toks), P(stats))
+    assert rc == 0, L.apus_cuda_last_error()
+    assert toks.tolist() == R["spec_sampled_tokens"].tolist()
+    assert stats[1:].tolist() == R["spec_sampled_stats"][1:].tolist(), (stats, R["spec_sampled_stats"])
+    plain = np.zeros((1, n_gen), np.int32)
+    assert L.apus_cuda_model_reset(h) == 0
+    assert L.apus_cuda_model_set_sampling(h, D["temp"], D["top_p"], D["rng_seed"]) == 0
+    assert L.apus_cuda_model_generate(h, P(prompt), n, n_gen, P(plain), None, None) == 0
+    assert plain[0].tolist() == toks.tolist()
+    # back to greedy drafts: the round of the greedy case again
+    assert L.apus_cuda_dspark_set_sampling(ds, 0.0, 0) == 0
+    assert one_round(L, Mdl, ds, [n])[0].tolist() == R["drafts"].tolist()
+
+
 def test_dspark_loaded_from_a_checkpoint_directory(tmp_path):
     """The module written as "mtp.<k>.*" tensors with its config section (reference c/dspark.h:272-341,
     c/model.h:336-373) and read back by apus_cuda_dspark_load: the draft round of the in-memory module."""
